@@ -1,0 +1,131 @@
+/*
+ * Launcher prototypes of the device layer (the drop-in boundary).
+ *
+ * Part 1 re-declares, with unchanged names, argument order and meaning, the
+ * 60 prototypes of the reference's generated header src/cuda/kernel_decls.h
+ * (20 launchers x {r16,r32,r64}); each group cites the reference kernel it
+ * replaces.  Part 2 is additive and follows the same conventions: void
+ * return, device pointers as void*, host scalars as double, sizes as len_t,
+ * StreamContext by value as the last argument, `_r16/_r32/_r64` suffix in the
+ * dtype-key order of src/core/scalar.zig:35-40 so that the host's 3-entry
+ * dispatch arrays (file_gen.zig:298-328, root.zig:36-43) keep working.
+ *
+ * Common semantics of every launcher here:
+ *  - asynchronous on ctx.cuda_stream, never synchronises, never allocates,
+ *    never retains a pointer;
+ *  - sizes are full 64-bit (the reference narrows them to 32 bits);
+ *  - "x + alpha*dst" blends do not read dst when alpha == 0, so a fresh
+ *    (uninitialised) output can never inject NaN;
+ *  - r16 I/O is computed in fp32 and rounded once.
+ */
+#ifndef MP_B200_KERNELS_H
+#define MP_B200_KERNELS_H
+
+#include "mp_types.h"
+
+#define MP_DECL3(name, ...)                                  \
+  MP_EXTERN_C void launch_##name##_r16(__VA_ARGS__);          \
+  MP_EXTERN_C void launch_##name##_r32(__VA_ARGS__);          \
+  MP_EXTERN_C void launch_##name##_r64(__VA_ARGS__);
+
+/* ======================= Part 1: reference symbols ======================= */
+
+/* reduce_ij_i.cu:35-54 — dst[i] = sum_j src[i,j] + alpha*dst[i] */
+MP_DECL3(reduce_ij_i, const void* src, void* dst, double alpha, len_t m, len_t n, StreamContext stream)
+/* reduce_ij_j.cu:48-66 — dst[j] = sum_i src[i,j] + alpha*dst[j] (the formula;
+ * the reference kernel is only right for alpha = 0 and m >= n) */
+MP_DECL3(reduce_ij_j, const void* src, void* dst, double alpha, len_t m, len_t n, StreamContext stream)
+/* broadcast_i_ij.cu:41-59 — dst[i,j] = src[i] + alpha*dst[i,j] */
+MP_DECL3(broadcast_i_ij, const void* src, void* dst, double alpha, len_t m, len_t n, StreamContext stream)
+/* broadcast_j_ij.cu:36-55 — dst[i,j] = src[j] + alpha*dst[i,j] */
+MP_DECL3(broadcast_j_ij, const void* src, void* dst, double alpha, len_t m, len_t n, StreamContext stream)
+/* dilate_reverse.cu:16-29 — b[i] += a[i]*value */
+MP_DECL3(dilate_reverse, const void* a, double value, void* b, len_t N, StreamContext stream)
+/* subtraction.cu:16-29 — c = a - b */
+MP_DECL3(subtraction, const void* a, const void* b, void* c, len_t N, StreamContext stream)
+/* relu_reverse.cu:18-31 — a_grads[i] += b_grads[i] * (a_value[i] >= 0) */
+MP_DECL3(relu_reverse, const void* a_value, void* a_grads, const void* b_grads, len_t N, StreamContext stream)
+/* dilate.cu:16-29 — c = a*value */
+MP_DECL3(dilate, const void* a, double value, void* c, len_t N, StreamContext stream)
+/* translate.cu:16-29 — c = a + value */
+MP_DECL3(translate, const void* a, double value, void* c, len_t N, StreamContext stream)
+/* permutate_ij_ji.cu:43-67 — dst[j,i] = src[i,j] + alpha*dst[j,i]; src is
+ * [row,col] row-major.  Bit-exact when alpha = 0. */
+MP_DECL3(permutate_ij_ji, const void* src, void* dst, double alpha, len_t row, len_t col, StreamContext ctx)
+/* negate.cu:15-26 — b = -a */
+MP_DECL3(negate, const void* a, void* b, len_t N, StreamContext stream)
+/* hadamard_reverse.cu:16-29 — c += a*b */
+MP_DECL3(hadamard_reverse, const void* a, const void* b, void* c, len_t N, StreamContext stream)
+/* inner_product_ij_jk_ik.cu:3-27 — C[m,k] = alpha*A[m,n]*B[n,k] + beta*C,
+ * all row-major.  The reference forwards to cuBLAS; here a TMA-fed
+ * tcgen05/TMEM kernel (r16, r32) or an FP64 SIMT tile kernel (r64). */
+MP_DECL3(inner_product_ij_jk_ik, const void* a_data, const void* b_data, const double alpha, void* c_data, const double beta, len_t m, len_t n, len_t k, StreamContext stream)
+/* hadamard.cu:16-29 — c = a*b */
+MP_DECL3(hadamard, const void* a, const void* b, void* c, len_t N, StreamContext stream)
+/* fill.cu:16-27 — a[i] = value */
+MP_DECL3(fill, void* dev_a, double value, len_t N, StreamContext stream)
+/* relu.cu:16-27 — b = a >= 0 ? a : 0 */
+MP_DECL3(relu, const void* a, void* b, len_t n, StreamContext stream)
+/* addition.cu:16-29 — c = a + b (c may alias a or b: the host's reverse pass
+ * calls it as g_x = g_z + g_x, addition.zig:67-81) */
+MP_DECL3(addition, const void* a, const void* b, void* c, len_t N, StreamContext stream)
+/* copy.cu:33-47 — dst = src */
+MP_DECL3(copy, const void* src, void* dst, len_t n, StreamContext stream)
+/* sequence.cu:18-31 — a[i] = init + step*T(i), evaluated in T */
+MP_DECL3(sequence, void* dev_a, double init, double step, len_t N, StreamContext stream)
+/* stepwise.cu:16-27 — b = a >= 0 ? 1 : 0.  (The reference body is a copy of
+ * relu; its only caller, relu.derive at relu.zig:56-58, needs the 0/1 step.) */
+MP_DECL3(stepwise, const void* a, void* b, len_t n, StreamContext stream)
+
+/* ============================ Part 2: additive =========================== */
+/* No launcher below has a kernel in the reference; the README names the ops
+ * (README.md:81,97) and the Zig layer sketches the optimizer call
+ * (src/optm/optimizer.zig:160-179). */
+
+/* b = selu(a) = 1.0507009873554805 * (a > 0 ? a : 1.6732632423543772*(exp(a)-1));
+ * argument order of relu.cu:16-21. */
+MP_DECL3(selu, const void* a, void* b, len_t n, StreamContext stream)
+/* a_grads += b_grads * selu'(a_value); argument order of relu_reverse.cu:18-24 */
+MP_DECL3(selu_reverse, const void* a_value, void* a_grads, const void* b_grads, len_t N, StreamContext stream)
+
+/* dst[i,:] = softmax(src[i,:]) over the last axis of a row-major [m,n] matrix
+ * ("ij|j" in the grammar of src/ops/expression_parsing.zig:319-340). */
+MP_DECL3(softmax_ij_j, const void* src, void* dst, len_t m, len_t n, StreamContext stream)
+/* gx = y o (gy - sum_j gy o y) + alpha*gx, y the forward output. */
+MP_DECL3(softmax_ij_j_reverse, const void* y, const void* gy, void* gx, double alpha, len_t m, len_t n, StreamContext stream)
+
+/* y[i,j] = x[i,j] * rstd_i * gain[j], rstd_i = rsqrt(mean_j x[i,j]^2 + eps).
+ * rstd (m values, r32 for r16/r32 and r64 for r64) may be NULL. */
+MP_DECL3(rmsnorm_ij_j, const void* x, const void* gain, double eps, void* y, void* rstd, len_t m, len_t n, StreamContext stream)
+/* gx     = rstd*(gy o gain) - x*rstd^3*mean_j(gy o gain o x) + alpha*gx
+ * ggain  = sum_i gy[i,:] o x[i,:]*rstd_i                    + alpha*ggain
+ * rstd may be NULL (it is then recomputed from x and eps at no extra traffic).
+ * scratch: caller-owned, mpRmsnormReverseScratchBytes(m,n,ctx) bytes, holds
+ * the per-CTA partial sums of ggain (deterministic two-stage reduction). */
+MP_DECL3(rmsnorm_ij_j_reverse, const void* x, const void* gain, const void* rstd, const void* gy, double eps, void* gx, void* ggain, double alpha, void* scratch, len_t m, len_t n, StreamContext stream)
+MP_EXTERN_C len_t mpRmsnormReverseScratchBytes(len_t m, len_t n, StreamContext stream);
+
+/* w -= rate * clip(g, clip_lo, clip_hi); argument set of optimizer.zig:170-178 */
+MP_DECL3(sgd, void* w, const void* g, double rate, double clip_lo, double clip_hi, len_t n, StreamContext stream)
+/* One fused Adam step over a flat buffer, g' = grad_scale*g:
+ *   m = b1*m + (1-b1)*g';  v = b2*v + (1-b2)*g'^2;
+ *   w -= lr * (m/(1-b1^step)) / (sqrt(v/(1-b2^step)) + eps)
+ * grad_scale folds the 1/world_size of a data-parallel all-reduce. */
+MP_DECL3(adam, void* w, const void* g, void* m, void* v, double lr, double beta1, double beta2, double eps, double grad_scale, len_t step, len_t n, StreamContext stream)
+
+/* Native transposed-operand contractions (the reference transposes into
+ * scratch first, inner_product.zig:305-330,364-389):
+ *   ij,kj->ik : C[m,k] = alpha*A[m,n]*B[k,n]^T + beta*C
+ *   ji,jk->ik : C[m,k] = alpha*A[n,m]^T*B[n,k] + beta*C */
+MP_DECL3(inner_product_ij_kj_ik, const void* a_data, const void* b_data, const double alpha, void* c_data, const double beta, len_t m, len_t n, len_t k, StreamContext stream)
+MP_DECL3(inner_product_ji_jk_ik, const void* a_data, const void* b_data, const double alpha, void* c_data, const double beta, len_t m, len_t n, len_t k, StreamContext stream)
+/* linear (README.md:81): C[m,k] = alpha*A[m,n]*B[n,k] + bias[k] + beta*C,
+ * bias added in the GEMM epilogue. */
+MP_DECL3(linear_ij_jk_ik, const void* a_data, const void* b_data, const void* bias, const double alpha, void* c_data, const double beta, len_t m, len_t n, len_t k, StreamContext stream)
+
+/* Status word values returned by mpGetStatus (mp_device_utils.h). */
+#define MP_STATUS_OK             0u
+#define MP_STATUS_WAIT_TIMEOUT   1u  /* a bounded mbarrier wait gave up    */
+#define MP_STATUS_BAD_ARGUMENT   2u  /* launcher rejected sizes/alignment  */
+
+#endif

@@ -1,0 +1,109 @@
+"""ctypes binding of the C ABI declared in ``include/*.h``.
+
+This module is plumbing for tests and benchmarks: it loads the in-tree
+``lib/libmp_kernels.so`` and attaches argument types to every exported entry
+point.  There is no fallback: if the shared library has not been built the
+import fails with an instruction to build it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libmp_kernels.so"
+
+
+class PaddedPtr(C.Structure):
+    _fields_ = [("ptr", C.c_void_p)]
+
+
+class StreamContext(C.Structure):
+    """Mirror of ``StreamContext`` in include/mp_types.h (two pointers, by value)."""
+    _fields_ = [("cuda_stream", PaddedPtr), ("blas_handle", PaddedPtr)]
+
+
+P, D, L, U32, CTX = C.c_void_p, C.c_double, C.c_ulong, C.c_uint32, StreamContext
+
+# name -> argument types (without the dtype suffix); every entry exists as
+# launch_<name>_{r16,r32,r64}.  Order of arguments = include/mp_kernels.h.
+LAUNCHERS = {
+    "reduce_ij_i": [P, P, D, L, L, CTX],
+    "reduce_ij_j": [P, P, D, L, L, CTX],
+    "broadcast_i_ij": [P, P, D, L, L, CTX],
+    "broadcast_j_ij": [P, P, D, L, L, CTX],
+    "dilate_reverse": [P, D, P, L, CTX],
+    "subtraction": [P, P, P, L, CTX],
+    "relu_reverse": [P, P, P, L, CTX],
+    "dilate": [P, D, P, L, CTX],
+    "translate": [P, D, P, L, CTX],
+    "permutate_ij_ji": [P, P, D, L, L, CTX],
+    "negate": [P, P, L, CTX],
+    "hadamard_reverse": [P, P, P, L, CTX],
+    "inner_product_ij_jk_ik": [P, P, D, P, D, L, L, L, CTX],
+    "hadamard": [P, P, P, L, CTX],
+    "fill": [P, D, L, CTX],
+    "relu": [P, P, L, CTX],
+    "addition": [P, P, P, L, CTX],
+    "copy": [P, P, L, CTX],
+    "sequence": [P, D, D, L, CTX],
+    "stepwise": [P, P, L, CTX],
+    # additive
+    "selu": [P, P, L, CTX],
+    "selu_reverse": [P, P, P, L, CTX],
+    "softmax_ij_j": [P, P, L, L, CTX],
+    "softmax_ij_j_reverse": [P, P, P, D, L, L, CTX],
+    "rmsnorm_ij_j": [P, P, D, P, P, L, L, CTX],
+    "rmsnorm_ij_j_reverse": [P, P, P, P, D, P, P, D, P, L, L, CTX],
+    "sgd": [P, P, D, D, D, L, CTX],
+    "adam": [P, P, P, P, D, D, D, D, D, L, L, CTX],
+    "inner_product_ij_kj_ik": [P, P, D, P, D, L, L, L, CTX],
+    "inner_product_ji_jk_ik": [P, P, D, P, D, L, L, L, CTX],
+    "linear_ij_jk_ik": [P, P, P, D, P, D, L, L, L, CTX],
+}
+
+# name -> (restype, argtypes)
+UTILS = {
+    "mpInitDevice": (None, [U32]),
+    "mpMemAlloc": (P, [L, CTX]),
+    "mpMemcpyHtoD": (None, [P, P, L, CTX]),
+    "mpMemcpyDtoH": (None, [P, P, L, CTX]),
+    "mpMemFree": (None, [P, CTX]),
+    "mpDeviceSynchronize": (None, []),
+    "mpStreamSynchronize": (None, [CTX]),
+    "mpInitStream": (CTX, []),
+    "mpDeinitStream": (None, [CTX]),
+    "mpCheckLastError": (None, []),
+    "mpDeviceTotalMemory": (L, [U32]),
+    "mpWrapStream": (CTX, [P]),
+    "mpGetStatus": (U32, [CTX]),
+    "mpWorkspaceBytes": (L, [CTX]),
+    "mpDeviceSmCount": (U32, [CTX]),
+    "mpHostAlloc": (P, [L]),
+    "mpHostFree": (None, [P]),
+    "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
+}
+
+SUFFIXES = ("r16", "r32", "r64")
+
+
+def load(path: Path | None = None) -> C.CDLL:
+    path = Path(path) if path is not None else LIB_PATH
+    if not path.exists():
+        raise ImportError(
+            f"{path} is missing: the CUDA library has not been built. "
+            "Run `python -m metaphor_b200.build` (needs nvcc); there is no CPU fallback.")
+    lib = C.CDLL(str(path))
+    for name, args in LAUNCHERS.items():
+        for sfx in SUFFIXES:
+            fn = getattr(lib, f"launch_{name}_{sfx}", None)
+            if fn is None:
+                continue  # reported by the symbol test, not at import
+            fn.restype = None
+            fn.argtypes = args
+    for name, (res, args) in UTILS.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue
+        fn.restype = res
+        fn.argtypes = args
+    return lib

@@ -1,0 +1,157 @@
+// mp* device utilities: the host-visible lifecycle / memory / copy calls.
+// Replaces the reference's src/cuda/device_utils.cu:4-99.  Differences that a
+// caller can observe are listed beside each function.
+#include "mp_common.cuh"
+
+#include <mutex>
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+int g_sm_count[kMaxDevices];
+std::once_flag g_sm_once[kMaxDevices];
+
+size_t workspace_bytes_from_env() {
+  const char* s = getenv("MP_WORKSPACE_MB");
+  size_t mb = 64;
+  if (s != nullptr) {
+    long v = strtol(s, nullptr, 10);
+    if (v > 0) mb = static_cast<size_t>(v);
+  }
+  return mb << 20;
+}
+
+StreamContext make_context(cudaStream_t stream, bool owns) {
+  int device = 0;
+  MP_CUDA_CHECK(cudaGetDevice(&device));
+  MpStreamState* st = new MpStreamState();
+  st->magic = MP_STATE_MAGIC;
+  st->stream = stream;
+  st->device = device;
+  st->sm_count = mp_sm_count_current_device();
+  st->owns_stream = owns;
+  st->workspace_bytes = workspace_bytes_from_env();
+  MP_CUDA_CHECK(cudaMalloc(&st->workspace, st->workspace_bytes));
+  MP_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&st->status_dev), 256));
+  MP_CUDA_CHECK(cudaMemsetAsync(st->status_dev, 0, 256, stream));
+  MP_CUDA_CHECK(cudaMallocHost(reinterpret_cast<void**>(&st->status_host), 256));
+  st->status_host[0] = 0;
+  StreamContext ctx;
+  ctx.cuda_stream.ptr = reinterpret_cast<void*>(stream);
+  ctx.blas_handle.ptr = reinterpret_cast<void*>(st);
+  return ctx;
+}
+
+}  // namespace
+
+int mp_sm_count_current_device() {
+  int device = 0;
+  MP_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= kMaxDevices) MP_FATAL("device index %d out of range", device);
+  std::call_once(g_sm_once[device], [device]() {
+    int n = 0;
+    MP_CUDA_CHECK(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device));
+    g_sm_count[device] = n;
+  });
+  return g_sm_count[device];
+}
+
+// The reference creates a fresh driver context (cuCtxCreate).  This binds the
+// device's primary context instead, so the library can share a process with
+// other CUDA runtime users (one process per GPU: call with the local rank).
+extern "C" void mpInitDevice(uint32_t device_number) {
+  int count = 0;
+  MP_CUDA_CHECK(cudaGetDeviceCount(&count));
+  if (count <= static_cast<int>(device_number)) {
+    fprintf(stderr, "Error: no devices supporting CUDA\n");
+    exit(-1);
+  }
+  MP_CUDA_CHECK(cudaSetDevice(static_cast<int>(device_number)));
+  MP_CUDA_CHECK(cudaFree(nullptr));  // force context creation
+}
+
+extern "C" void* mpMemAlloc(len_t N, StreamContext ctx) {
+  void* p = nullptr;
+  MP_CUDA_CHECK(cudaMallocAsync(&p, N, mp_stream(ctx)));
+  return p;
+}
+
+extern "C" void mpMemcpyHtoD(void* dptr, void const* hptr, len_t N, StreamContext ctx) {
+  MP_CUDA_CHECK(cudaMemcpyAsync(dptr, hptr, N, cudaMemcpyHostToDevice, mp_stream(ctx)));
+}
+
+extern "C" void mpMemcpyDtoH(void* hptr, void const* dptr, len_t N, StreamContext ctx) {
+  MP_CUDA_CHECK(cudaMemcpyAsync(hptr, dptr, N, cudaMemcpyDeviceToHost, mp_stream(ctx)));
+}
+
+extern "C" void mpMemFree(void* dptr, StreamContext ctx) {
+  MP_CUDA_CHECK(cudaFreeAsync(dptr, mp_stream(ctx)));
+}
+
+extern "C" void mpStreamSynchronize(StreamContext ctx) {
+  MP_CUDA_CHECK(cudaStreamSynchronize(mp_stream(ctx)));
+}
+
+extern "C" void mpDeviceSynchronize(void) { MP_CUDA_CHECK(cudaDeviceSynchronize()); }
+
+extern "C" void mpCheckLastError(void) {
+  MP_CUDA_CHECK(cudaDeviceSynchronize());
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) {
+    fprintf(stderr, "Error %s: %s", cudaGetErrorName(err), cudaGetErrorString(err));
+  }
+}
+
+extern "C" len_t mpDeviceTotalMemory(uint32_t device) {
+  cudaDeviceProp prop;
+  MP_CUDA_CHECK(cudaGetDeviceProperties(&prop, static_cast<int>(device)));
+  return static_cast<len_t>(prop.totalGlobalMem);
+}
+
+extern "C" StreamContext mpInitStream(void) {
+  cudaStream_t stream = nullptr;
+  MP_CUDA_CHECK(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+  return make_context(stream, true);
+}
+
+extern "C" StreamContext mpWrapStream(void* cuda_stream) {
+  return make_context(static_cast<cudaStream_t>(cuda_stream), false);
+}
+
+extern "C" void mpDeinitStream(StreamContext ctx) {
+  MpStreamState* st = mp_state_or_null(ctx);
+  cudaStream_t stream = mp_stream(ctx);
+  MP_CUDA_CHECK(cudaStreamSynchronize(stream));
+  if (st != nullptr) {
+    MP_CUDA_CHECK(cudaFree(st->workspace));
+    MP_CUDA_CHECK(cudaFree(st->status_dev));
+    MP_CUDA_CHECK(cudaFreeHost(st->status_host));
+    const bool owns = st->owns_stream;
+    st->magic = 0;
+    delete st;
+    if (owns) MP_CUDA_CHECK(cudaStreamDestroy(stream));
+  } else {
+    MP_CUDA_CHECK(cudaStreamDestroy(stream));
+  }
+}
+
+extern "C" uint32_t mpGetStatus(StreamContext ctx) {
+  MpStreamState* st = mp_state(ctx);
+  MP_CUDA_CHECK(cudaMemcpyAsync(st->status_host, st->status_dev, sizeof(uint32_t),
+                                cudaMemcpyDeviceToHost, st->stream));
+  MP_CUDA_CHECK(cudaMemsetAsync(st->status_dev, 0, sizeof(uint32_t), st->stream));
+  MP_CUDA_CHECK(cudaStreamSynchronize(st->stream));
+  return st->status_host[0];
+}
+
+extern "C" len_t mpWorkspaceBytes(StreamContext ctx) { return mp_state(ctx)->workspace_bytes; }
+
+extern "C" uint32_t mpDeviceSmCount(StreamContext ctx) { return static_cast<uint32_t>(mp_sm_count(ctx)); }
+
+extern "C" void* mpHostAlloc(len_t N) {
+  void* p = nullptr;
+  MP_CUDA_CHECK(cudaMallocHost(&p, N));
+  return p;
+}
+
+extern "C" void mpHostFree(void* hptr) { MP_CUDA_CHECK(cudaFreeHost(hptr)); }

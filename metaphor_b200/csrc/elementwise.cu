@@ -1,0 +1,341 @@
+// Flat element-wise launchers: one 128-bit vectorised, coalesced grid-stride
+// kernel template instantiated per (op, dtype).  HBM-bound: every element is
+// read once and written once, with streaming (evict-first) accesses.
+//
+// Replaces the reference kernels addition.cu, subtraction.cu, hadamard.cu,
+// hadamard_reverse.cu, negate.cu, translate.cu, dilate.cu, dilate_reverse.cu,
+// relu.cu, relu_reverse.cu, stepwise.cu, fill.cu, sequence.cu, copy.cu
+// (src/cuda/nvcc_src/) and adds selu, selu_reverse, sgd, adam.
+#include "mp_common.cuh"
+
+namespace {
+
+constexpr int EW_THREADS = 256;
+constexpr int EW_UNROLL = 4;        // 16-byte packs per thread per stream per trip
+constexpr int EW_CTAS_PER_SM = 8;   // 2048 resident threads per SM
+
+template <typename T> struct OpCopyTag;  // defined below as the copy functor
+
+// Op concept: NIN input streams (0..2), RMW = also reads the output's old
+// value, A = arithmetic type, operator()(x0, x1, old, index).
+template <typename T, typename Op, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS) ew_kernel(Op op, const T* in0, const T* in1, T* out, size_t n) {
+  using A = typename Acc<T>::type;
+  const size_t tid = threadIdx.x;
+  if constexpr (VEC) {
+    constexpr int PN = Pack<T>::N;
+    const size_t nvec = n / PN;
+    const size_t trip = static_cast<size_t>(EW_THREADS) * EW_UNROLL;
+    for (size_t base = blockIdx.x * trip; base < nvec; base += static_cast<size_t>(gridDim.x) * trip) {
+      Pack<T> x0[EW_UNROLL], x1[EW_UNROLL], old[EW_UNROLL];
+#pragma unroll
+      for (int u = 0; u < EW_UNROLL; ++u) {
+        const size_t i = base + u * EW_THREADS + tid;
+        if (i < nvec) {
+          if constexpr (Op::NIN >= 1) x0[u] = ld_pack_stream(in0, i);
+          if constexpr (Op::NIN >= 2) x1[u] = ld_pack_stream(in1, i);
+          if constexpr (Op::RMW) old[u] = ld_pack_stream(out, i);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < EW_UNROLL; ++u) {
+        const size_t i = base + u * EW_THREADS + tid;
+        if (i < nvec) {
+          if constexpr (std::is_same<Op, OpCopyTag<T>>::value) {  // bit-exact, no conversion
+            st_pack_stream(out, i, x0[u]);
+          } else {
+            Pack<T> r;
+#pragma unroll
+            for (int e = 0; e < PN; ++e) {
+              const A a0 = (Op::NIN >= 1) ? mp_up(x0[u].v[e]) : A(0);
+              const A a1 = (Op::NIN >= 2) ? mp_up(x1[u].v[e]) : A(0);
+              const A ao = Op::RMW ? mp_up(old[u].v[e]) : A(0);
+              r.v[e] = mp_down<T>(op(a0, a1, ao, i * PN + e));
+            }
+            st_pack_stream(out, i, r);
+          }
+        }
+      }
+    }
+    // ragged tail (< 16 bytes worth of elements)
+    if (blockIdx.x == 0) {
+      const size_t i = nvec * PN + tid;
+      if (i < n) {
+        const A a0 = (Op::NIN >= 1) ? mp_up(in0[i]) : A(0);
+        const A a1 = (Op::NIN >= 2) ? mp_up(in1[i]) : A(0);
+        const A ao = Op::RMW ? mp_up(out[i]) : A(0);
+        out[i] = mp_down<T>(op(a0, a1, ao, i));
+      }
+    }
+  } else {
+    // pointers not 16-byte aligned: scalar accesses, same arithmetic
+    for (size_t i = blockIdx.x * static_cast<size_t>(EW_THREADS) + tid; i < n;
+         i += static_cast<size_t>(gridDim.x) * EW_THREADS) {
+      const A a0 = (Op::NIN >= 1) ? mp_up(in0[i]) : A(0);
+      const A a1 = (Op::NIN >= 2) ? mp_up(in1[i]) : A(0);
+      const A ao = Op::RMW ? mp_up(out[i]) : A(0);
+      out[i] = mp_down<T>(op(a0, a1, ao, i));
+    }
+  }
+}
+
+template <typename T, typename Op>
+void ew_launch(Op op, const void* in0, const void* in1, void* out, len_t n, StreamContext ctx) {
+  if (n == 0) return;
+  const bool vec = mp_aligned16(in0) && mp_aligned16(in1) && mp_aligned16(out);
+  const size_t cap = static_cast<size_t>(mp_sm_count(ctx)) * EW_CTAS_PER_SM;
+  const T* p0 = static_cast<const T*>(in0);
+  const T* p1 = static_cast<const T*>(in1);
+  T* po = static_cast<T*>(out);
+  if (vec) {
+    const size_t per_cta = static_cast<size_t>(EW_THREADS) * EW_UNROLL * Pack<T>::N;
+    size_t grid = (n + per_cta - 1) / per_cta;
+    if (grid > cap) grid = cap;
+    ew_kernel<T, Op, true><<<static_cast<unsigned>(grid), EW_THREADS, 0, mp_stream(ctx)>>>(op, p0, p1, po, n);
+  } else {
+    size_t grid = (n + EW_THREADS - 1) / EW_THREADS;
+    if (grid > cap) grid = cap;
+    ew_kernel<T, Op, false><<<static_cast<unsigned>(grid), EW_THREADS, 0, mp_stream(ctx)>>>(op, p0, p1, po, n);
+  }
+  MP_LAUNCH_CHECK();
+}
+
+// ------------------------------- functors ---------------------------------
+template <typename T> struct OpBase { using A = typename Acc<T>::type; };
+
+template <typename T> struct OpAdd : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 2; static constexpr bool RMW = false;
+  __device__ __forceinline__ A operator()(A a, A b, A, size_t) const { return a + b; }
+};
+template <typename T> struct OpSub : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 2; static constexpr bool RMW = false;
+  __device__ __forceinline__ A operator()(A a, A b, A, size_t) const { return a - b; }
+};
+template <typename T> struct OpMul : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 2; static constexpr bool RMW = false;
+  __device__ __forceinline__ A operator()(A a, A b, A, size_t) const { return a * b; }
+};
+template <typename T> struct OpMulAcc : OpBase<T> {   // c += a*b
+  using A = typename OpBase<T>::A; static constexpr int NIN = 2; static constexpr bool RMW = true;
+  __device__ __forceinline__ A operator()(A a, A b, A c, size_t) const { return c + a * b; }
+};
+template <typename T> struct OpNeg : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = false;
+  __device__ __forceinline__ A operator()(A a, A, A, size_t) const { return -a; }
+};
+template <typename T> struct OpTranslate : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = false;
+  A value;
+  __device__ __forceinline__ A operator()(A a, A, A, size_t) const { return a + value; }
+};
+template <typename T> struct OpDilate : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = false;
+  A value;
+  __device__ __forceinline__ A operator()(A a, A, A, size_t) const { return a * value; }
+};
+template <typename T> struct OpDilateAcc : OpBase<T> {  // b += a*value
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = true;
+  A value;
+  __device__ __forceinline__ A operator()(A a, A, A b, size_t) const { return b + a * value; }
+};
+template <typename T> struct OpRelu : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = false;
+  __device__ __forceinline__ A operator()(A a, A, A, size_t) const { return a >= A(0) ? a : A(0); }
+};
+template <typename T> struct OpReluAcc : OpBase<T> {  // ga += gb * (a >= 0); in0 = a, in1 = gb
+  using A = typename OpBase<T>::A; static constexpr int NIN = 2; static constexpr bool RMW = true;
+  __device__ __forceinline__ A operator()(A a, A gb, A ga, size_t) const { return ga + gb * (a >= A(0) ? A(1) : A(0)); }
+};
+template <typename T> struct OpStep : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = false;
+  __device__ __forceinline__ A operator()(A a, A, A, size_t) const { return a >= A(0) ? A(1) : A(0); }
+};
+template <typename T> struct OpFill : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 0; static constexpr bool RMW = false;
+  A value;
+  __device__ __forceinline__ A operator()(A, A, A, size_t) const { return value; }
+};
+template <typename T> struct OpCopyTag : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = false;
+  __device__ __forceinline__ A operator()(A a, A, A, size_t) const { return a; }
+};
+// init + step*T(i) evaluated in T (sequence.cu:14): for r32/r64 that is the
+// arithmetic type already; r16 rounds the index and the product to half.
+template <typename T> struct OpSequence : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 0; static constexpr bool RMW = false;
+  A init, step;
+  __device__ __forceinline__ A operator()(A, A, A, size_t i) const {
+    if constexpr (std::is_same<T, __half>::value) {
+      const __half hi = __ull2half_rn(static_cast<unsigned long long>(i));
+      const __half prod = __hmul(__float2half_rn(step), hi);
+      return __half2float(__hadd(__float2half_rn(init), prod));
+    } else {
+      return init + step * static_cast<A>(i);
+    }
+  }
+};
+
+#define MP_SELU_LAMBDA 1.0507009873554805
+#define MP_SELU_ALPHA 1.6732632423543772
+
+__device__ __forceinline__ float mp_exp(float x) { return expf(x); }
+__device__ __forceinline__ double mp_exp(double x) { return exp(x); }
+
+template <typename T> struct OpSelu : OpBase<T> {
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = false;
+  __device__ __forceinline__ A operator()(A a, A, A, size_t) const {
+    return a > A(0) ? A(MP_SELU_LAMBDA) * a : A(MP_SELU_LAMBDA * MP_SELU_ALPHA) * (mp_exp(a) - A(1));
+  }
+};
+template <typename T> struct OpSeluAcc : OpBase<T> {  // ga += gb * selu'(a)
+  using A = typename OpBase<T>::A; static constexpr int NIN = 2; static constexpr bool RMW = true;
+  __device__ __forceinline__ A operator()(A a, A gb, A ga, size_t) const {
+    const A d = a > A(0) ? A(MP_SELU_LAMBDA) : A(MP_SELU_LAMBDA * MP_SELU_ALPHA) * mp_exp(a);
+    return ga + gb * d;
+  }
+};
+template <typename T> struct OpSgd : OpBase<T> {  // w -= rate*clip(g); in0 = g
+  using A = typename OpBase<T>::A; static constexpr int NIN = 1; static constexpr bool RMW = true;
+  A rate, lo, hi;
+  __device__ __forceinline__ A operator()(A g, A, A w, size_t) const {
+    const A c = g < lo ? lo : (g > hi ? hi : g);
+    return w - rate * c;
+  }
+};
+
+template <typename T> T scalar_as(double v) { return mp_host_cast<T>(v); }
+template <typename T> typename Acc<T>::type scalar_up(double v) {
+  // round to T first (the reference casts the host double to Scalar), then widen
+  if constexpr (std::is_same<T, __half>::value) return __half2float(__double2half(v));
+  else return static_cast<typename Acc<T>::type>(static_cast<T>(v));
+}
+
+// ------------------------------- adam -------------------------------------
+template <typename T> struct AdamParams {
+  typename Acc<T>::type lr, b1, b2, omb1, omb2, eps, gscale, inv_bc1, inv_bc2;
+};
+
+template <typename T>
+__device__ __forceinline__ void adam_one(const AdamParams<T>& p, T& w, T g, T& m, T& v) {
+  using A = typename Acc<T>::type;
+  const A gs = mp_up(g) * p.gscale;
+  const A mn = p.b1 * mp_up(m) + p.omb1 * gs;
+  const A vn = p.b2 * mp_up(v) + p.omb2 * gs * gs;
+  const A mhat = mn * p.inv_bc1;
+  const A vhat = vn * p.inv_bc2;
+  A denom;
+  if constexpr (std::is_same<A, double>::value) denom = sqrt(vhat) + p.eps; else denom = sqrtf(vhat) + p.eps;
+  w = mp_down<T>(mp_up(w) - p.lr * mhat / denom);
+  m = mp_down<T>(mn);
+  v = mp_down<T>(vn);
+}
+
+// Single pass over (w, g, m, v): 4 reads + 3 writes per element.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(EW_THREADS) adam_kernel(AdamParams<T> p, T* w, const T* g, T* m, T* v, size_t n) {
+  const size_t tid = threadIdx.x;
+  if constexpr (VEC) {
+    constexpr int PN = Pack<T>::N;
+    constexpr int U = 2;
+    const size_t nvec = n / PN;
+    const size_t trip = static_cast<size_t>(EW_THREADS) * U;
+    for (size_t base = blockIdx.x * trip; base < nvec; base += static_cast<size_t>(gridDim.x) * trip) {
+      Pack<T> pw[U], pg[U], pm[U], pv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t i = base + u * EW_THREADS + tid;
+        if (i < nvec) {
+          pw[u] = ld_pack_stream(w, i); pg[u] = ld_pack_stream(g, i);
+          pm[u] = ld_pack_stream(m, i); pv[u] = ld_pack_stream(v, i);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t i = base + u * EW_THREADS + tid;
+        if (i < nvec) {
+#pragma unroll
+          for (int e = 0; e < PN; ++e) adam_one<T>(p, pw[u].v[e], pg[u].v[e], pm[u].v[e], pv[u].v[e]);
+          st_pack_stream(w, i, pw[u]); st_pack_stream(m, i, pm[u]); st_pack_stream(v, i, pv[u]);
+        }
+      }
+    }
+    if (blockIdx.x == 0) {
+      const size_t i = nvec * PN + tid;
+      if (i < n) adam_one<T>(p, w[i], g[i], m[i], v[i]);
+    }
+  } else {
+    for (size_t i = blockIdx.x * static_cast<size_t>(EW_THREADS) + tid; i < n;
+         i += static_cast<size_t>(gridDim.x) * EW_THREADS)
+      adam_one<T>(p, w[i], g[i], m[i], v[i]);
+  }
+}
+
+}  // namespace
+
+// ------------------------------ launchers ---------------------------------
+template <typename T> static void addition_impl(const void* a, const void* b, void* c, len_t N, StreamContext s) { ew_launch<T>(OpAdd<T>{}, a, b, c, N, s); }
+template <typename T> static void subtraction_impl(const void* a, const void* b, void* c, len_t N, StreamContext s) { ew_launch<T>(OpSub<T>{}, a, b, c, N, s); }
+template <typename T> static void hadamard_impl(const void* a, const void* b, void* c, len_t N, StreamContext s) { ew_launch<T>(OpMul<T>{}, a, b, c, N, s); }
+template <typename T> static void hadamard_reverse_impl(const void* a, const void* b, void* c, len_t N, StreamContext s) { ew_launch<T>(OpMulAcc<T>{}, a, b, c, N, s); }
+template <typename T> static void negate_impl(const void* a, void* b, len_t N, StreamContext s) { ew_launch<T>(OpNeg<T>{}, a, nullptr, b, N, s); }
+template <typename T> static void translate_impl(const void* a, double value, void* c, len_t N, StreamContext s) { OpTranslate<T> op; op.value = scalar_up<T>(value); ew_launch<T>(op, a, nullptr, c, N, s); }
+template <typename T> static void dilate_impl(const void* a, double value, void* c, len_t N, StreamContext s) { OpDilate<T> op; op.value = scalar_up<T>(value); ew_launch<T>(op, a, nullptr, c, N, s); }
+template <typename T> static void dilate_reverse_impl(const void* a, double value, void* b, len_t N, StreamContext s) { OpDilateAcc<T> op; op.value = scalar_up<T>(value); ew_launch<T>(op, a, nullptr, b, N, s); }
+template <typename T> static void relu_impl(const void* a, void* b, len_t n, StreamContext s) { ew_launch<T>(OpRelu<T>{}, a, nullptr, b, n, s); }
+template <typename T> static void relu_reverse_impl(const void* a_value, void* a_grads, const void* b_grads, len_t N, StreamContext s) { ew_launch<T>(OpReluAcc<T>{}, a_value, b_grads, a_grads, N, s); }
+template <typename T> static void stepwise_impl(const void* a, void* b, len_t n, StreamContext s) { ew_launch<T>(OpStep<T>{}, a, nullptr, b, n, s); }
+template <typename T> static void fill_impl(void* a, double value, len_t N, StreamContext s) { OpFill<T> op; op.value = scalar_up<T>(value); ew_launch<T>(op, nullptr, nullptr, a, N, s); }
+template <typename T> static void copy_impl(const void* src, void* dst, len_t n, StreamContext s) { ew_launch<T>(OpCopyTag<T>{}, src, nullptr, dst, n, s); }
+template <typename T> static void sequence_impl(void* a, double init, double step, len_t N, StreamContext s) { OpSequence<T> op; op.init = scalar_up<T>(init); op.step = scalar_up<T>(step); ew_launch<T>(op, nullptr, nullptr, a, N, s); }
+template <typename T> static void selu_impl(const void* a, void* b, len_t n, StreamContext s) { ew_launch<T>(OpSelu<T>{}, a, nullptr, b, n, s); }
+template <typename T> static void selu_reverse_impl(const void* a_value, void* a_grads, const void* b_grads, len_t N, StreamContext s) { ew_launch<T>(OpSeluAcc<T>{}, a_value, b_grads, a_grads, N, s); }
+template <typename T> static void sgd_impl(void* w, const void* g, double rate, double lo, double hi, len_t n, StreamContext s) {
+  OpSgd<T> op; op.rate = scalar_up<T>(rate); op.lo = scalar_up<T>(lo); op.hi = scalar_up<T>(hi);
+  ew_launch<T>(op, g, nullptr, w, n, s);
+}
+
+template <typename T>
+static void adam_impl(void* w, const void* g, void* m, void* v, double lr, double beta1, double beta2, double eps,
+                      double grad_scale, len_t step, len_t n, StreamContext s) {
+  if (n == 0) return;
+  using A = typename Acc<T>::type;
+  AdamParams<T> p;
+  const double t = static_cast<double>(step < 1 ? 1 : step);
+  p.lr = static_cast<A>(lr); p.b1 = static_cast<A>(beta1); p.b2 = static_cast<A>(beta2);
+  p.omb1 = static_cast<A>(1.0 - beta1); p.omb2 = static_cast<A>(1.0 - beta2);
+  p.eps = static_cast<A>(eps); p.gscale = static_cast<A>(grad_scale);
+  p.inv_bc1 = static_cast<A>(1.0 / (1.0 - pow(beta1, t)));
+  p.inv_bc2 = static_cast<A>(1.0 / (1.0 - pow(beta2, t)));
+  const bool vec = mp_aligned16(w) && mp_aligned16(g) && mp_aligned16(m) && mp_aligned16(v);
+  const size_t cap = static_cast<size_t>(mp_sm_count(s)) * EW_CTAS_PER_SM;
+  if (vec) {
+    const size_t per_cta = static_cast<size_t>(EW_THREADS) * 2 * Pack<T>::N;
+    size_t grid = (n + per_cta - 1) / per_cta; if (grid > cap) grid = cap;
+    adam_kernel<T, true><<<static_cast<unsigned>(grid), EW_THREADS, 0, mp_stream(s)>>>(
+        p, static_cast<T*>(w), static_cast<const T*>(g), static_cast<T*>(m), static_cast<T*>(v), n);
+  } else {
+    size_t grid = (n + EW_THREADS - 1) / EW_THREADS; if (grid > cap) grid = cap;
+    adam_kernel<T, false><<<static_cast<unsigned>(grid), EW_THREADS, 0, mp_stream(s)>>>(
+        p, static_cast<T*>(w), static_cast<const T*>(g), static_cast<T*>(m), static_cast<T*>(v), n);
+  }
+  MP_LAUNCH_CHECK();
+}
+
+MP_STAMP3(addition, (const void* a, const void* b, void* c, len_t N, StreamContext s), (a, b, c, N, s))
+MP_STAMP3(subtraction, (const void* a, const void* b, void* c, len_t N, StreamContext s), (a, b, c, N, s))
+MP_STAMP3(hadamard, (const void* a, const void* b, void* c, len_t N, StreamContext s), (a, b, c, N, s))
+MP_STAMP3(hadamard_reverse, (const void* a, const void* b, void* c, len_t N, StreamContext s), (a, b, c, N, s))
+MP_STAMP3(negate, (const void* a, void* b, len_t N, StreamContext s), (a, b, N, s))
+MP_STAMP3(translate, (const void* a, double value, void* c, len_t N, StreamContext s), (a, value, c, N, s))
+MP_STAMP3(dilate, (const void* a, double value, void* c, len_t N, StreamContext s), (a, value, c, N, s))
+MP_STAMP3(dilate_reverse, (const void* a, double value, void* b, len_t N, StreamContext s), (a, value, b, N, s))
+MP_STAMP3(relu, (const void* a, void* b, len_t n, StreamContext s), (a, b, n, s))
+MP_STAMP3(relu_reverse, (const void* av, void* ag, const void* bg, len_t N, StreamContext s), (av, ag, bg, N, s))
+MP_STAMP3(stepwise, (const void* a, void* b, len_t n, StreamContext s), (a, b, n, s))
+MP_STAMP3(fill, (void* a, double value, len_t N, StreamContext s), (a, value, N, s))
+MP_STAMP3(copy, (const void* src, void* dst, len_t n, StreamContext s), (src, dst, n, s))
+MP_STAMP3(sequence, (void* a, double init, double step, len_t N, StreamContext s), (a, init, step, N, s))
+MP_STAMP3(selu, (const void* a, void* b, len_t n, StreamContext s), (a, b, n, s))
+MP_STAMP3(selu_reverse, (const void* av, void* ag, const void* bg, len_t N, StreamContext s), (av, ag, bg, N, s))
+MP_STAMP3(sgd, (void* w, const void* g, double rate, double lo, double hi, len_t n, StreamContext s), (w, g, rate, lo, hi, n, s))
+MP_STAMP3(adam, (void* w, const void* g, void* m, void* v, double lr, double b1, double b2, double eps, double gs, len_t step, len_t n, StreamContext s), (w, g, m, v, lr, b1, b2, eps, gs, step, n, s))

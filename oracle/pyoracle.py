@@ -1,0 +1,236 @@
+"""numpy front end of the C oracle (``oracle/liboracle.so``).
+
+TEST INFRASTRUCTURE: imported only by tests/, the smoke check and the
+benchmark's CPU-baseline / reference legs.  Arrays are float32 or float64
+numpy arrays (r16 inputs are widened to float64 by the caller and the result
+rounded back, which is what "fp64 oracle rounded to r16" means in the tests).
+In-place arguments (accumulators) are modified and also returned.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+_LIB = None
+
+
+def build() -> Path:
+    """Compile liboracle.so with gcc if it is missing or stale."""
+    so = HERE / "liboracle.so"
+    srcs = [HERE / "oracle.c", HERE / "oracle_body.inc"]
+    if not so.exists() or so.stat().st_mtime < max(s.stat().st_mtime for s in srcs):
+        subprocess.run(["make", "-C", str(HERE), "liboracle.so"], check=True, capture_output=True)
+    return so
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(str(build()))
+    return _LIB
+
+
+def _sfx(a: np.ndarray) -> str:
+    if a.dtype == np.float32:
+        return "f32"
+    if a.dtype == np.float64:
+        return "f64"
+    raise TypeError(f"oracle works on float32/float64 arrays, got {a.dtype}")
+
+
+def _p(a):
+    if a is None:
+        return C.c_void_p(0)
+    assert a.flags["C_CONTIGUOUS"]
+    return C.c_void_p(a.ctypes.data)
+
+
+def _call(name, like, *args):
+    fn = getattr(lib(), f"{name}_{_sfx(like)}")
+    fn.restype = None
+    conv = []
+    for a in args:
+        if isinstance(a, np.ndarray) or a is None:
+            conv.append(_p(a))
+        elif isinstance(a, float):
+            conv.append(C.c_double(a))
+        elif isinstance(a, (int, np.integer)):
+            conv.append(C.c_size_t(int(a)))
+        else:
+            raise TypeError(type(a))
+    fn(*conv)
+
+
+# ---- flat element-wise -----------------------------------------------------
+def addition(a, b):
+    c = np.empty_like(a); _call("orc_addition", a, a, b, c, a.size); return c
+
+
+def subtraction(a, b):
+    c = np.empty_like(a); _call("orc_subtraction", a, a, b, c, a.size); return c
+
+
+def hadamard(a, b):
+    c = np.empty_like(a); _call("orc_hadamard", a, a, b, c, a.size); return c
+
+
+def hadamard_reverse(a, b, c):
+    _call("orc_hadamard_reverse", a, a, b, c, a.size); return c
+
+
+def negate(a):
+    b = np.empty_like(a); _call("orc_negate", a, a, b, a.size); return b
+
+
+def translate(a, value):
+    c = np.empty_like(a); _call("orc_translate", a, a, float(value), c, a.size); return c
+
+
+def dilate(a, value):
+    c = np.empty_like(a); _call("orc_dilate", a, a, float(value), c, a.size); return c
+
+
+def dilate_reverse(a, value, b):
+    _call("orc_dilate_reverse", a, a, float(value), b, a.size); return b
+
+
+def relu(a):
+    b = np.empty_like(a); _call("orc_relu", a, a, b, a.size); return b
+
+
+def relu_reverse(a, ga, gb):
+    _call("orc_relu_reverse", a, a, ga, gb, a.size); return ga
+
+
+def stepwise(a):
+    b = np.empty_like(a); _call("orc_stepwise", a, a, b, a.size); return b
+
+
+def fill(a, value):
+    _call("orc_fill", a, a, float(value), a.size); return a
+
+
+def sequence(a, init, step):
+    _call("orc_sequence", a, a, float(init), float(step), a.size); return a
+
+
+def copy(a):
+    b = np.empty_like(a); _call("orc_copy", a, a, b, a.size); return b
+
+
+def selu(a):
+    b = np.empty_like(a); _call("orc_selu", a, a, b, a.size); return b
+
+
+def selu_reverse(a, ga, gb):
+    _call("orc_selu_reverse", a, a, ga, gb, a.size); return ga
+
+
+def sgd(w, g, rate, lo=-np.inf, hi=np.inf):
+    _call("orc_sgd", w, w, g, float(rate), float(lo), float(hi), w.size); return w
+
+
+def adam(w, g, m, v, lr, b1, b2, eps, grad_scale, step):
+    _call("orc_adam", w, w, g, m, v, float(lr), float(b1), float(b2), float(eps), float(grad_scale), int(step), w.size)
+    return w, m, v
+
+
+# ---- rank-2 ------------------------------------------------------------------
+def permutate_ij_ji(src, dst=None, alpha=0.0):
+    row, col = src.shape
+    if dst is None:
+        dst = np.zeros((col, row), dtype=src.dtype)
+    _call("orc_permutate_ij_ji", src, src, dst, float(alpha), row, col); return dst
+
+
+def reduce_ij_i(src, dst=None, alpha=0.0):
+    m, n = src.shape
+    if dst is None:
+        dst = np.zeros(m, dtype=src.dtype)
+    _call("orc_reduce_ij_i", src, src, dst, float(alpha), m, n); return dst
+
+
+def reduce_ij_j(src, dst=None, alpha=0.0):
+    m, n = src.shape
+    if dst is None:
+        dst = np.zeros(n, dtype=src.dtype)
+    _call("orc_reduce_ij_j", src, src, dst, float(alpha), m, n); return dst
+
+
+def broadcast_i_ij(src, dst, alpha=0.0):
+    m, n = dst.shape
+    _call("orc_broadcast_i_ij", src, src, dst, float(alpha), m, n); return dst
+
+
+def broadcast_j_ij(src, dst, alpha=0.0):
+    m, n = dst.shape
+    _call("orc_broadcast_j_ij", src, src, dst, float(alpha), m, n); return dst
+
+
+def inner_product(a, b, alpha=1.0, c=None, beta=0.0, ta=False, tb=False, bias=None):
+    """C = alpha*op(A)*op(B) + bias + beta*C (row-major); see orc_inner_product."""
+    m = a.shape[1] if ta else a.shape[0]
+    n = a.shape[0] if ta else a.shape[1]
+    k = b.shape[0] if tb else b.shape[1]
+    assert (b.shape[1] if tb else b.shape[0]) == n
+    if c is None:
+        c = np.zeros((m, k), dtype=a.dtype)
+    fn = getattr(lib(), f"orc_inner_product_{_sfx(a)}")
+    fn.restype = None
+    fn(_p(a), _p(b), _p(bias), C.c_double(alpha), _p(c), C.c_double(beta),
+       C.c_size_t(m), C.c_size_t(n), C.c_size_t(k), C.c_int(int(ta)), C.c_int(int(tb)))
+    return c
+
+
+# ---- row-wise ----------------------------------------------------------------
+def softmax_ij_j(x):
+    y = np.empty_like(x); _call("orc_softmax_ij_j", x, x, y, x.shape[0], x.shape[1]); return y
+
+
+def softmax_ij_j_reverse(y, gy, gx=None, alpha=0.0):
+    if gx is None:
+        gx = np.zeros_like(y)
+    _call("orc_softmax_ij_j_reverse", y, y, gy, gx, float(alpha), y.shape[0], y.shape[1]); return gx
+
+
+def rmsnorm_ij_j(x, gain, eps):
+    y = np.empty_like(x)
+    rstd = np.empty(x.shape[0], dtype=x.dtype)
+    _call("orc_rmsnorm_ij_j", x, x, gain, float(eps), y, rstd, x.shape[0], x.shape[1])
+    return y, rstd
+
+
+def rmsnorm_ij_j_reverse(x, gain, gy, eps, gx=None, ggain=None, alpha=0.0):
+    if gx is None:
+        gx = np.zeros_like(x)
+    if ggain is None:
+        ggain = np.zeros_like(gain)
+    _call("orc_rmsnorm_ij_j_reverse", x, x, gain, gy, float(eps), gx, ggain, float(alpha), x.shape[0], x.shape[1])
+    return gx, ggain
+
+
+# ---- SSD scan (float64 only) ---------------------------------------------------
+def ssd_forward(x, dt, A, Bm, Cm):
+    nb, L, H, P = x.shape
+    G, N = Bm.shape[2], Bm.shape[3]
+    y = np.empty_like(x)
+    fn = lib().orc_ssd_forward_f64
+    fn.restype = None
+    fn(_p(x), _p(dt), _p(A), _p(Bm), _p(Cm), _p(y), *(C.c_size_t(v) for v in (nb, L, H, P, N, G)))
+    return y
+
+
+def ssd_reverse(x, dt, A, Bm, Cm, gy):
+    nb, L, H, P = x.shape
+    G, N = Bm.shape[2], Bm.shape[3]
+    gx = np.empty_like(x); gdt = np.empty_like(dt); gA = np.empty_like(A)
+    gB = np.empty_like(Bm); gC = np.empty_like(Cm)
+    fn = lib().orc_ssd_reverse_f64
+    fn.restype = None
+    fn(_p(x), _p(dt), _p(A), _p(Bm), _p(Cm), _p(gy), _p(gx), _p(gdt), _p(gA), _p(gB), _p(gC),
+       *(C.c_size_t(v) for v in (nb, L, H, P, N, G)))
+    return gx, gdt, gA, gB, gC
