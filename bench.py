@@ -1,0 +1,404 @@
+#!/usr/bin/env python
+"""Benchmark of the row-reduction hot path (softmax and RMSNorm, forward and
+reverse, r32 and r16, X = [65536, 4096]) through the C ABI.
+
+One "step" = one pass over one batch: for each dtype, softmax forward, softmax
+reverse, RMSNorm forward, RMSNorm reverse (gradients overwritten, alpha = 0;
+rstd recomputed in the reverse).  Metric: algorithmic HBM GB/s = the bytes each
+kernel must read and write once, summed over the step, divided by the time.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Under torchrun (N > 1) every rank runs the same per-GPU workload on its own
+rows (weak scaling, no collective on the data path); the time is the maximum
+over ranks, the value the sum of all ranks' bytes over that time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M, N = 65536, 4096
+EPS = 1e-6
+METRIC = "row-reduction (softmax+RMSNorm fwd+rev, r32+r16) algorithmic HBM bandwidth"
+UNIT = "GB/s"
+
+# DRAM bytes per launch from ncu (dram__bytes_read.sum + dram__bytes_write.sum)
+# for the kernels of this step; filled from profiles/ (None = not captured).
+NCU_TRAFFIC_BYTES = {
+}
+
+
+def algorithmic_bytes(op: str, size: int, m: int = M, n: int = N) -> int:
+    """Bytes a kernel must move once (inputs read once, outputs written once)."""
+    mn = m * n * size
+    return {
+        "softmax_fwd": 2 * mn,                              # x -> y
+        "softmax_rev": 3 * mn,                              # y, gy -> gx
+        "rmsnorm_fwd": 2 * mn + n * size,                   # x, gain -> y
+        "rmsnorm_rev": 3 * mn + 2 * n * size,               # x, gy, gain -> gx, ggain
+    }[op]
+
+
+OPS = ["softmax_fwd", "softmax_rev", "rmsnorm_fwd", "rmsnorm_rev"]
+DTYPES = [("r32", 4), ("r16", 2)]
+STEP_BYTES = sum(algorithmic_bytes(op, size) for op in OPS for _, size in DTYPES)
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region."""
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.proc = None
+        self.path = None
+        self.index = device_index
+
+    def start(self):
+        exe = shutil.which("nvidia-smi")
+        if exe is None:
+            return
+        fd, self.path = tempfile.mkstemp(suffix=".csv")
+        os.close(fd)
+        self.proc = subprocess.Popen([exe, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                      "-i", str(self.index), "-lms", "100"],
+                                     stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in Path(self.path).read_text().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        # samples under load only (idle samples before/after the region sit at the floor clock)
+        load = [s for s in sm if s > 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(load) if load else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import metaphor_b200 as mp
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    lib = mp.lib()
+    lib.mpInitDevice(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    stream = mp.Stream()
+    ts = stream.torch_stream()
+
+    # ---- synthetic inputs, resident in HBM (seeded; rank-distinct rows) -------
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    bufs = {}
+    x32 = torch.randn(M, N, generator=gen, device="cuda")
+    g32 = torch.randn(M, N, generator=gen, device="cuda")
+    gain32 = 1.0 + 0.02 * torch.randn(N, generator=gen, device="cuda")
+    for sfx, size in DTYPES:
+        dt = torch.float32 if sfx == "r32" else torch.float16
+        b = {"dt": dt, "x": x32.to(dt), "gy": g32.to(dt), "gain": gain32.to(dt)}
+        b["y"] = torch.empty(M, N, device="cuda", dtype=dt)          # softmax output
+        b["gx"] = torch.empty(M, N, device="cuda", dtype=dt)
+        b["yn"] = torch.empty(M, N, device="cuda", dtype=dt)         # RMSNorm output
+        b["gxn"] = torch.empty(M, N, device="cuda", dtype=dt)
+        b["ggain"] = torch.empty(N, device="cuda", dtype=dt)
+        nb = lib.mpRmsnormReverseScratchBytes(M, N, stream.ctx)
+        b["scratch"] = torch.empty(nb, device="cuda", dtype=torch.uint8)
+        bufs[sfx] = b
+    del x32, g32
+    torch.cuda.synchronize()
+
+    def launch(op, sfx):
+        b = bufs[sfx]
+        if op == "softmax_fwd":
+            mp.launch("softmax_ij_j", b["dt"], b["x"], b["y"], M, N, stream)
+        elif op == "softmax_rev":
+            mp.launch("softmax_ij_j_reverse", b["dt"], b["y"], b["gy"], b["gx"], 0.0, M, N, stream)
+        elif op == "rmsnorm_fwd":
+            mp.launch("rmsnorm_ij_j", b["dt"], b["x"], b["gain"], EPS, b["yn"], None, M, N, stream)
+        else:
+            mp.launch("rmsnorm_ij_j_reverse", b["dt"], b["x"], b["gain"], None, b["gy"], EPS, b["gxn"], b["ggain"],
+                      0.0, b["scratch"], M, N, stream)
+
+    kernels = [(op, sfx) for sfx, _ in DTYPES for op in OPS]
+    launches_per_step = len(kernels) + 2      # each RMSNorm reverse = row kernel + fold kernel
+
+    def step(events=None):
+        for i, (op, sfx) in enumerate(kernels):
+            if events is not None:
+                events[i][0].record(ts)
+            launch(op, sfx)
+            if events is not None:
+                events[i][1].record(ts)
+
+    def barrier():
+        stream.sync()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    # ---- device-resident timing ----------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    per_kernel = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in kernels]
+                  for _ in range(args.steps)]
+    e0.record(ts)
+    for k in range(args.steps):
+        step(per_kernel[k])
+    e1.record(ts)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms_total = e0.elapsed_time(e1)
+    if stream.status() != 0:
+        raise SystemExit("a kernel reported a non-zero status word")
+    t = torch.tensor([ms_total], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_per_step = ms_total / args.steps
+    value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
+
+    # per-kernel averages -> roofline of the dominant kernel
+    kstats = {}
+    for i, (op, sfx) in enumerate(kernels):
+        ms = statistics.mean(per_kernel[k][i][0].elapsed_time(per_kernel[k][i][1]) for k in range(args.steps))
+        size = 4 if sfx == "r32" else 2
+        kstats[f"{op}_{sfx}"] = {"ms": ms, "bytes": algorithmic_bytes(op, size)}
+    peak, peak_kind = measured_peak()
+    dom = max(kstats, key=lambda k: kstats[k]["ms"])
+    achieved = kstats[dom]["bytes"] / (kstats[dom]["ms"] * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": round(achieved, 1), "peak": peak, "peak_kind": peak_kind,
+                "unit": "GB/s", "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES.get(dom),
+                "algorithmic_bytes": kstats[dom]["bytes"],
+                "per_kernel": {k: {"us": round(v["ms"] * 1e3, 1),
+                                   "achieved": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1),
+                                   "frac": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9 / peak, 4)}
+                               for k, v in kstats.items()}}
+
+    # ---- end to end: host buffers in, host buffers out, through the C ABI ------
+    e2e = run_e2e(args, mp, lib, stream, ts, bufs, kernels, launch, barrier, world)
+
+    cpu = None
+    if rank == 0 and world == 1:
+        cpu = cpu_baseline(sample_rows=args.cpu_rows)
+
+    if rank == 0:
+        out = {
+            "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic (seeded N(0,1) X and upstream gradient, gain ~ N(1, 0.02))",
+            "config": {"workload": "configs[1]: softmax + RMSNorm (eps 1e-6) forward+reverse over X[65536,4096], "
+                                   "r32 and r16, per GPU", "rows_per_gpu": M, "cols": N,
+                       "l2": "inputs (1 GiB / 0.5 GiB per tensor) exceed the 126 MB L2; no flush needed",
+                       "bytes_per_step_per_gpu": STEP_BYTES, "io": "r32 and r16 storage, fp32 arithmetic"},
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
+            "gpu_launches": launches_per_step * args.steps,
+        }
+        print(json.dumps(out), flush=True)
+    stream.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_e2e(args, mp, lib, stream, ts, bufs, kernels, launch, barrier, world):
+    """Same step, inputs copied from pinned host memory and every result copied
+    back to pinned host memory inside the timed region (mpMemcpyHtoD / DtoH)."""
+    import ctypes as C
+    import torch
+    steps = max(1, min(args.steps, args.e2e_steps))
+    host_in = {}
+    for sfx, size in DTYPES:
+        b = bufs[sfx]
+        nbytes = M * N * size
+        hx = lib.mpHostAlloc(nbytes); hg = lib.mpHostAlloc(nbytes); hgain = lib.mpHostAlloc(N * size)
+        lib.mpMemcpyDtoH(hx, C.c_void_p(b["x"].data_ptr()), nbytes, stream.ctx)
+        lib.mpMemcpyDtoH(hg, C.c_void_p(b["gy"].data_ptr()), nbytes, stream.ctx)
+        lib.mpMemcpyDtoH(hgain, C.c_void_p(b["gain"].data_ptr()), N * size, stream.ctx)
+        host_in[sfx] = (hx, hg, hgain, nbytes)
+    hout = lib.mpHostAlloc(M * N * 4)     # landing buffer, reused for every result
+    stream.sync()
+    h2d = sum(2 * M * N * size + N * size for _, size in DTYPES)
+    d2h = sum(4 * M * N * size + N * size for _, size in DTYPES)
+
+    def e2e_step():
+        for sfx, size in DTYPES:
+            b = bufs[sfx]
+            hx, hg, hgain, nbytes = host_in[sfx]
+            lib.mpMemcpyHtoD(C.c_void_p(b["x"].data_ptr()), hx, nbytes, stream.ctx)
+            lib.mpMemcpyHtoD(C.c_void_p(b["gy"].data_ptr()), hg, nbytes, stream.ctx)
+            lib.mpMemcpyHtoD(C.c_void_p(b["gain"].data_ptr()), hgain, N * size, stream.ctx)
+            for op in OPS:
+                launch(op, sfx)
+            for name in ("y", "gx", "yn", "gxn"):
+                lib.mpMemcpyDtoH(hout, C.c_void_p(b[name].data_ptr()), nbytes, stream.ctx)
+            lib.mpMemcpyDtoH(hout, C.c_void_p(b["ggain"].data_ptr()), N * size, stream.ctx)
+
+    e2e_step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(ts)
+    for _ in range(steps):
+        e2e_step()
+    e1.record(ts)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item()) / steps
+    for hx, hg, hgain, _ in host_in.values():
+        lib.mpHostFree(hx); lib.mpHostFree(hg); lib.mpHostFree(hgain)
+    lib.mpHostFree(hout)
+    return {"value": round(world * STEP_BYTES / (ms * 1e-3) / 1e9, 2), "unit": UNIT, "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": round(ms, 3), "steps": steps}
+
+
+# ----------------------------------------------------------------------------
+def cpu_step_sample(rows: int, threads: int, repeats: int = 1):
+    """The same step on `rows` rows with the CPU oracle (scalar C, float32
+    storage for both dtype halves), rows split statically over `threads` host
+    threads.  Returns (seconds per pass, algorithmic bytes per pass)."""
+    import numpy as np
+    from oracle import pyoracle as orc
+    orc.lib()
+    r = np.random.default_rng(0)
+    x = r.standard_normal((rows, N)).astype(np.float32)
+    gy = r.standard_normal((rows, N)).astype(np.float32)
+    gain = (1 + 0.02 * r.standard_normal(N)).astype(np.float32)
+    bounds = [(rows * i // threads, rows * (i + 1) // threads) for i in range(threads)]
+
+    def work(lo_hi):
+        lo, hi = lo_hi
+        if hi <= lo:
+            return
+        xs, gs = x[lo:hi], gy[lo:hi]
+        y = orc.softmax_ij_j(xs)
+        orc.softmax_ij_j_reverse(y, gs)
+        orc.rmsnorm_ij_j(xs, gain, EPS)
+        orc.rmsnorm_ij_j_reverse(xs, gain, gs, EPS)   # per-slice ggain partials; the sum over slices is negligible
+
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(max_workers=threads) as pool:
+        for _ in range(repeats):
+            for _ in range(len(DTYPES)):              # the r32 half and the r16 half of the step
+                list(pool.map(work, bounds))
+    dt = (time.perf_counter() - t0) / repeats
+    nbytes = sum(algorithmic_bytes(op, size, rows, N) for op in OPS for _, size in DTYPES)
+    return dt, nbytes
+
+
+def cpu_baseline(sample_rows: int):
+    threads = os.cpu_count() or 1
+    dt, nbytes = cpu_step_sample(sample_rows, threads)
+    return {"value": round(nbytes / dt / 1e9, 3), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"first {sample_rows} of {M} rows of the same step, scalar C oracle, "
+                      f"{threads} host threads over disjoint row ranges, {dt:.2f} s"}
+
+
+def run_reference(args):
+    """Reference arm.  The reference has no CPU (or any) implementation of
+    softmax / RMSNorm, so this times the CPU oracle port of the step on all host
+    threads, one bounded row sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    rows = args.cpu_rows
+    for _ in range(min(args.warmup, 1)):
+        cpu_step_sample(max(threads, rows // 8), threads)
+    times = []
+    nbytes = 0
+    for _ in range(args.steps):
+        dt, nbytes = cpu_step_sample(rows, threads)
+        times.append(dt)
+    dt = statistics.mean(times)
+    value = round(nbytes / dt / 1e9, 3)
+    sample = (f"each step = first {rows} of {M} rows, scalar C oracle port (the reference has no kernel for these "
+              f"ops), {threads} host threads")
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
+        "config": {"workload": "configs[1]: softmax + RMSNorm forward+reverse over X[65536,4096], r32 and r16",
+                   "rows_sampled_per_step": rows, "cols": N},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=10, help="upper bound on end-to-end steps (PCIe-bound)")
+    ap.add_argument("--cpu-rows", type=int, default=32768, help="rows in the CPU baseline sample")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

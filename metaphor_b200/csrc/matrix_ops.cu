@@ -11,11 +11,12 @@
 namespace {
 
 // ------------------------------ transpose ---------------------------------
-constexpr int TP_TILE = 64;
 constexpr int TP_THREADS = 256;
+// tile edge in elements: 128 for 2-byte types (256-byte row segments), else 64
+template <typename T> struct TpTile { static constexpr int value = sizeof(T) == 2 ? 128 : 64; };
 
 // dst[c, r] = src[r, c] + alpha*dst[c, r]; src is [row, col] row-major.
-// One 64x64 tile per CTA through padded shared memory; VL / VS select 128-bit
+// One square tile per CTA through padded shared memory; VL / VS select 128-bit
 // global loads / stores (legal when col resp. row is a multiple of the pack
 // width and the base pointer is 16-byte aligned).
 template <typename T, bool VL, bool VS, bool BLEND>
@@ -23,6 +24,7 @@ __global__ void __launch_bounds__(TP_THREADS) transpose_kernel(const T* __restri
                                                                typename Acc<T>::type alpha, size_t row, size_t col) {
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
+  constexpr int TP_TILE = TpTile<T>::value;
   constexpr int VPR = TP_TILE / PN;  // packs per tile row
   __shared__ T tile[TP_TILE][TP_TILE + 1];
   const size_t r0 = static_cast<size_t>(blockIdx.y) * TP_TILE;
@@ -240,23 +242,36 @@ __global__ void __launch_bounds__(256) broadcast_kernel(const T* __restrict__ sr
   const size_t total = m * n;
   if constexpr (VEC) {
     const size_t nvec = total / PN;  // n % PN == 0: a pack never straddles rows
-    for (size_t vi = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; vi < nvec;
-         vi += static_cast<size_t>(gridDim.x) * 256) {
-      const size_t e0 = vi * PN;
-      Pack<T> out;
-      if constexpr (BY_ROW) {
-        const T s = src[e0 / n];
+    constexpr int U = 4;
+    for (size_t base = static_cast<size_t>(blockIdx.x) * 256 * U; base < nvec;
+         base += static_cast<size_t>(gridDim.x) * 256 * U) {
+      Pack<T> out[U], old[U];
 #pragma unroll
-        for (int e = 0; e < PN; ++e) out.v[e] = s;
-      } else {
-        out = ld_pack(src, (e0 % n) / PN);
-      }
-      if constexpr (BLEND) {
-        const Pack<T> old = ld_pack_stream(dst, vi);
+      for (int u = 0; u < U; ++u) {
+        const size_t vi = base + u * 256 + threadIdx.x;
+        if (vi < nvec) {
+          const size_t e0 = vi * PN;
+          if constexpr (BY_ROW) {
+            const T s = src[e0 / n];
 #pragma unroll
-        for (int e = 0; e < PN; ++e) out.v[e] = mp_down<T>(mp_up(out.v[e]) + alpha * mp_up(old.v[e]));
+            for (int e = 0; e < PN; ++e) out[u].v[e] = s;
+          } else {
+            out[u] = ld_pack(src, (e0 % n) / PN);
+          }
+          if constexpr (BLEND) old[u] = ld_pack_stream(dst, vi);
+        }
       }
-      st_pack_stream(dst, vi, out);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const size_t vi = base + u * 256 + threadIdx.x;
+        if (vi < nvec) {
+          if constexpr (BLEND) {
+#pragma unroll
+            for (int e = 0; e < PN; ++e) out[u].v[e] = mp_down<T>(mp_up(out[u].v[e]) + alpha * mp_up(old[u].v[e]));
+          }
+          st_pack_stream(dst, vi, out[u]);
+        }
+      }
     }
   } else {
     for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < total;
@@ -276,9 +291,9 @@ void broadcast_launch(const void* src_, void* dst_, double alpha, len_t m, len_t
   T* dst = static_cast<T*>(dst_);
   constexpr int PN = Pack<T>::N;
   const bool vec = (n % PN == 0) && mp_aligned16(dst) && (BY_ROW || mp_aligned16(src));
-  const size_t work = vec ? (m * n) / PN : m * n;
-  size_t grid = (work + 255) / 256;
-  const size_t cap = static_cast<size_t>(mp_sm_count(ctx)) * 8;
+  const size_t work = vec ? ((m * n) / PN + 3) / 4 : m * n;  // 4 packs per thread when vectorised
+  size_t grid = (work + 255) / 256;   // one trip per CTA streams fastest on B200
+  const size_t cap = 1u << 30;
   if (grid > cap) grid = cap;
   cudaStream_t st = mp_stream(ctx);
   const A a = static_cast<A>(alpha);
@@ -301,8 +316,9 @@ static void permutate_ij_ji_impl(const void* src_, void* dst_, double alpha, len
   const T* src = static_cast<const T*>(src_);
   T* dst = static_cast<T*>(dst_);
   constexpr int PN = Pack<T>::N;
+  constexpr int TP_TILE = TpTile<T>::value;
   const size_t gx = (col + TP_TILE - 1) / TP_TILE, gy = (row + TP_TILE - 1) / TP_TILE;
-  if (gy > 65535) MP_FATAL("permutate_ij_ji: more than 65535*64 rows is not supported");
+  if (gy > 65535) MP_FATAL("permutate_ij_ji: more than 65535 row tiles is not supported");
   const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
   const bool vl = (col % PN == 0) && mp_aligned16(src);
   const bool vs = (row % PN == 0) && mp_aligned16(dst);
@@ -324,7 +340,7 @@ static void reduce_ij_i_impl(const void* src_, void* dst_, double alpha, len_t m
   const bool vec = (n % PN == 0) && mp_aligned16(src);
   const bool blend = alpha != 0.0;
   const A a = static_cast<A>(alpha);
-  const size_t cap = static_cast<size_t>(mp_sm_count(ctx)) * 8;
+  const size_t cap = 1u << 30;  // one row (group) per CTA; the loop only runs for larger m
   cudaStream_t st = mp_stream(ctx);
   if (n * sizeof(T) <= 4096) {  // short rows: one warp each, 8 rows per CTA
     size_t grid = (m + 7) / 8; if (grid > cap) grid = cap;
@@ -351,15 +367,14 @@ static void reduce_ij_j_impl(const void* src_, void* dst_, double alpha, len_t m
   cudaStream_t st = mp_stream(ctx);
   const size_t strip = 32 * (vec ? PN : 1);
   const size_t strips = (n + strip - 1) / strip;
-  // enough CTAs for ~4 per SM, at least 64 rows each, partials must fit the workspace
+  // ~256 rows per CTA: many short-lived CTAs stream faster than a few long
+  // ones; the partials (splits x n) must fit the stream's workspace
   MpStreamState* state = mp_state_or_null(ctx);
   size_t splits = 1;
   if (state != nullptr && m > 0) {
-    const size_t want = (static_cast<size_t>(state->sm_count) * 4 + strips - 1) / strips;
-    const size_t by_rows = (m + 63) / 64;
+    const size_t by_rows = (m + 255) / 256;
     const size_t by_ws = state->workspace_bytes / (n * sizeof(A));
-    splits = want;
-    if (splits > by_rows) splits = by_rows;
+    splits = by_rows;
     if (splits > by_ws) splits = by_ws;
     if (splits > 65535) splits = 65535;
     if (splits < 1) splits = 1;

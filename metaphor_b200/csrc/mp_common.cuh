@@ -148,6 +148,39 @@ __device__ __forceinline__ void st_pack(T* base, size_t vec_index, const Pack<T>
   *(reinterpret_cast<uint4*>(base) + vec_index) = x.u;
 }
 
+// Pack <-> arithmetic-type arrays.  The r16 forms convert two values per
+// instruction (half2 <-> float2).
+template <typename T>
+__device__ __forceinline__ void unpack(const Pack<T>& p, typename Acc<T>::type* out) {
+#pragma unroll
+  for (int e = 0; e < Pack<T>::N; ++e) out[e] = mp_up(p.v[e]);
+}
+template <>
+__device__ __forceinline__ void unpack<__half>(const Pack<__half>& p, float* out) {
+  const __half2* h = reinterpret_cast<const __half2*>(p.v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ Pack<T> pack(const typename Acc<T>::type* in) {
+  Pack<T> r;
+#pragma unroll
+  for (int e = 0; e < Pack<T>::N; ++e) r.v[e] = mp_down<T>(in[e]);
+  return r;
+}
+template <>
+__device__ __forceinline__ Pack<__half> pack<__half>(const float* in) {
+  Pack<__half> r;
+  __half2* h = reinterpret_cast<__half2*>(r.v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(in[2 * i], in[2 * i + 1]);
+  return r;
+}
+
 static inline bool mp_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------------------

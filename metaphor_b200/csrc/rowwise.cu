@@ -9,7 +9,7 @@
 //
 // The reference has no kernel for these ops; the op naming follows its "ij|j"
 // transform grammar (src/ops/expression_parsing.zig:319-340).
-#include "mp_common.cuh"
+#include "mp_async.cuh"
 
 #include <cfloat>
 
@@ -23,8 +23,15 @@ struct RowCfg {
 
 __device__ __forceinline__ float mp_neg_inf(float) { return -INFINITY; }
 __device__ __forceinline__ double mp_neg_inf(double) { return -INFINITY; }
-__device__ __forceinline__ float mp_exp_diff(float x, float mx) {
-  return exp2f((x - mx) * 1.4426950408889634f);
+// exp(x - mx) with the row maximum pre-scaled once per row: fp32 uses one FFMA
+// and one ex2.approx (rel. error 2^-22, inputs <= 0, results below 2^-126 flush
+// to zero); fp64 uses exp().
+__device__ __forceinline__ float mp_exp_prescale(float mx) { return mx * 1.4426950408889634f; }
+__device__ __forceinline__ double mp_exp_prescale(double mx) { return mx; }
+__device__ __forceinline__ float mp_exp_diff(float x, float mx_scaled) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(fmaf(x, 1.4426950408889634f, -mx_scaled)));
+  return y;
 }
 __device__ __forceinline__ double mp_exp_diff(double x, double mx) { return exp(x - mx); }
 __device__ __forceinline__ float mp_rsqrt(float x) { return 1.0f / sqrtf(x); }
@@ -54,10 +61,14 @@ __device__ __forceinline__ void group_sum2(A& a, A& b, A* smem) {
   }
 }
 
+// Thread t of a row group owns packs t, t+GROUP, ... (PPT of them).  FULL: the
+// row has exactly GROUP*PPT packs, so no pack needs a bounds guard.
+#define MP_PACK_VALID(u) (FULL || (t + static_cast<size_t>(u) * GROUP) < nv)
+#define MP_PACK_INDEX(u) (t + static_cast<size_t>(u) * GROUP)
+
 // ------------------------------- softmax ----------------------------------
-template <typename T, int GROUP, int PPT>
-__global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) softmax_fwd_kernel(const T* x, T* y,
-                                                                            size_t m, size_t n) {
+template <typename T, int GROUP, int PPT, bool FULL>
+__global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) softmax_fwd_kernel(const T* x, T* y, size_t m, size_t n) {
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
   constexpr int ROWS = RowCfg<GROUP>::ROWS;
@@ -69,51 +80,48 @@ __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) softmax_fwd_kernel(con
     T* yr = y + row * n;
     Pack<T> p[PPT];
 #pragma unroll
-    for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) p[u] = ld_pack_stream(xr, v);
-    }
+    for (int u = 0; u < PPT; ++u)
+      if (MP_PACK_VALID(u)) p[u] = ld_pack_stream(xr, MP_PACK_INDEX(u));
     A e[PPT][PN];
     A mx = mp_neg_inf(A(0));
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
+      if (MP_PACK_VALID(u)) {
+        unpack<T>(p[u], e[u]);
 #pragma unroll
-      for (int k = 0; k < PN; ++k) {
-        e[u][k] = mp_up(p[u].v[k]);
-        if (v < nv) mx = MaxOp::apply(mx, e[u][k]);
+        for (int k = 0; k < PN; ++k) mx = MaxOp::apply(mx, e[u][k]);
       }
     }
     mx = group_reduce<MaxOp, GROUP>(mx, red, mp_neg_inf(A(0)));
+    const A mxs = mp_exp_prescale(mx);
     A sum = A(0);
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
+      if (MP_PACK_VALID(u)) {
 #pragma unroll
-      for (int k = 0; k < PN; ++k) {
-        e[u][k] = mp_exp_diff(e[u][k], mx);
-        if (v < nv) sum += e[u][k];
+        for (int k = 0; k < PN; ++k) {
+          e[u][k] = mp_exp_diff(e[u][k], mxs);
+          sum += e[u][k];
+        }
       }
     }
     sum = group_reduce<SumOp, GROUP>(sum, red, A(0));
     const A inv = A(1) / sum;
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
-        Pack<T> o;
+      if (MP_PACK_VALID(u)) {
 #pragma unroll
-        for (int k = 0; k < PN; ++k) o.v[k] = mp_down<T>(e[u][k] * inv);
-        st_pack_stream(yr, v, o);
+        for (int k = 0; k < PN; ++k) e[u][k] *= inv;
+        st_pack_stream(yr, MP_PACK_INDEX(u), pack<T>(e[u]));
       }
     }
   }
 }
 
 // gx = y o (gy - <gy, y>) + alpha*gx
-template <typename T, int GROUP, int PPT, bool BLEND>
-__global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) softmax_rev_kernel(const T* y, const T* gy,
-                                                                            T* gx, typename Acc<T>::type alpha, size_t m, size_t n) {
+template <typename T, int GROUP, int PPT, bool FULL, bool BLEND>
+__global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) softmax_rev_kernel(const T* y, const T* gy, T* gx,
+                                                                            typename Acc<T>::type alpha, size_t m, size_t n) {
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
   constexpr int ROWS = RowCfg<GROUP>::ROWS;
@@ -127,43 +135,44 @@ __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) softmax_rev_kernel(con
     Pack<T> py[PPT], pg[PPT], po[PPT];
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
-        py[u] = ld_pack_stream(yr, v);
-        pg[u] = ld_pack_stream(gr, v);
-        if constexpr (BLEND) po[u] = ld_pack_stream(xr, v);
+      if (MP_PACK_VALID(u)) {
+        py[u] = ld_pack_stream(yr, MP_PACK_INDEX(u));
+        pg[u] = ld_pack_stream(gr, MP_PACK_INDEX(u));
+        if constexpr (BLEND) po[u] = ld_pack_stream(xr, MP_PACK_INDEX(u));
       }
     }
+    A fy[PPT][PN], fg[PPT][PN];
     A dot = A(0);
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
+      if (MP_PACK_VALID(u)) {
+        unpack<T>(py[u], fy[u]);
+        unpack<T>(pg[u], fg[u]);
 #pragma unroll
-        for (int k = 0; k < PN; ++k) dot += mp_up(py[u].v[k]) * mp_up(pg[u].v[k]);
+        for (int k = 0; k < PN; ++k) dot += fy[u][k] * fg[u][k];
       }
     }
     dot = group_reduce<SumOp, GROUP>(dot, red, A(0));
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
-        Pack<T> o;
+      if (MP_PACK_VALID(u)) {
+        A fo[PN];
+        if constexpr (BLEND) unpack<T>(po[u], fo);
 #pragma unroll
         for (int k = 0; k < PN; ++k) {
-          A r = mp_up(py[u].v[k]) * (mp_up(pg[u].v[k]) - dot);
-          if constexpr (BLEND) r += alpha * mp_up(po[u].v[k]);
-          o.v[k] = mp_down<T>(r);
+          A r = fy[u][k] * (fg[u][k] - dot);
+          if constexpr (BLEND) r += alpha * fo[k];
+          fy[u][k] = r;
         }
-        st_pack_stream(xr, v, o);
+        st_pack_stream(xr, MP_PACK_INDEX(u), pack<T>(fy[u]));
       }
     }
   }
 }
 
 // ------------------------------- RMSNorm ----------------------------------
-template <typename T, int GROUP, int PPT>
-__global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gain,
+template <typename T, int GROUP, int PPT, bool FULL>
+__global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_fwd_kernel(const T* x, const T* __restrict__ gain,
                                                                             typename Acc<T>::type eps, T* y,
                                                                             typename Acc<T>::type* __restrict__ rstd_out,
                                                                             size_t m, size_t n) {
@@ -175,27 +184,24 @@ __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_fwd_kernel(con
   const size_t nv = n / PN;
   Pack<T> pgain[PPT];
 #pragma unroll
-  for (int u = 0; u < PPT; ++u) {
-    const size_t v = t + static_cast<size_t>(u) * GROUP;
-    if (v < nv) pgain[u] = ld_pack(gain, v);
-  }
+  for (int u = 0; u < PPT; ++u)
+    if (MP_PACK_VALID(u)) pgain[u] = ld_pack(gain, MP_PACK_INDEX(u));
   const A inv_n = A(1) / static_cast<A>(n);
   for (size_t row = static_cast<size_t>(blockIdx.x) * ROWS + g; row < m; row += static_cast<size_t>(gridDim.x) * ROWS) {
     const T* xr = x + row * n;
     T* yr = y + row * n;
     Pack<T> p[PPT];
 #pragma unroll
-    for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) p[u] = ld_pack_stream(xr, v);
-    }
+    for (int u = 0; u < PPT; ++u)
+      if (MP_PACK_VALID(u)) p[u] = ld_pack_stream(xr, MP_PACK_INDEX(u));
+    A f[PPT][PN];
     A ss = A(0);
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
+      if (MP_PACK_VALID(u)) {
+        unpack<T>(p[u], f[u]);
 #pragma unroll
-        for (int k = 0; k < PN; ++k) { const A a = mp_up(p[u].v[k]); ss += a * a; }
+        for (int k = 0; k < PN; ++k) ss += f[u][k] * f[u][k];
       }
     }
     ss = group_reduce<SumOp, GROUP>(ss, red, A(0));
@@ -203,26 +209,76 @@ __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_fwd_kernel(con
     if (rstd_out != nullptr && t == 0) rstd_out[row] = rstd;
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
-        Pack<T> o;
+      if (MP_PACK_VALID(u)) {
+        A fgain[PN];
+        unpack<T>(pgain[u], fgain);
 #pragma unroll
-        for (int k = 0; k < PN; ++k) o.v[k] = mp_down<T>(mp_up(p[u].v[k]) * rstd * mp_up(pgain[u].v[k]));
-        st_pack_stream(yr, v, o);
+        for (int k = 0; k < PN; ++k) f[u][k] = f[u][k] * rstd * fgain[k];
+        st_pack_stream(yr, MP_PACK_INDEX(u), pack<T>(f[u]));
       }
     }
   }
 }
 
-// gx = rstd*(gy o gain) - x*rstd^3*mean_j(gy o gain o x) + alpha*gx, and the
-// CTA's partial of ggain_j = sum_i gy_ij*x_ij*rstd_i into partial[slot][n],
-// slot = blockIdx.x*ROWS + row-group.  Both row sums are independent of each
-// other, so they share one reduction.
-template <typename T, int GROUP, int PPT, bool BLEND>
+// One row of the RMSNorm reverse, shared by the register and the staged kernel:
+// px/pg hold this thread's packs of x and gy, acc its gain-gradient partials.
+//   gx = rstd*(gy o gain) - x*rstd^3*mean_j(gy o gain o x) + alpha*gx
+template <typename T, int GROUP, int PPT, bool FULL, bool BLEND>
+__device__ __forceinline__ void rmsnorm_rev_row(const Pack<T>* px, const Pack<T>* pg, const Pack<T>* pgain,
+                                                typename Acc<T>::type (*acc)[Pack<T>::N], const typename Acc<T>::type* rstd_in,
+                                                typename Acc<T>::type eps, typename Acc<T>::type inv_n,
+                                                typename Acc<T>::type alpha, T* out_row, size_t row, int t, size_t nv,
+                                                typename Acc<T>::type* red) {
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  A fx[PPT][PN], fu[PPT][PN], ft[PPT][PN];  // x, gy*gain, gy*x
+  A ss = A(0), dot = A(0);
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    if (MP_PACK_VALID(u)) {
+      A fg[PN], fgain[PN];
+      unpack<T>(px[u], fx[u]);
+      unpack<T>(pg[u], fg);
+      unpack<T>(pgain[u], fgain);
+#pragma unroll
+      for (int k = 0; k < PN; ++k) {
+        ss += fx[u][k] * fx[u][k];
+        fu[u][k] = fg[k] * fgain[k];
+        ft[u][k] = fg[k] * fx[u][k];
+        dot += fu[u][k] * fx[u][k];
+      }
+    }
+  }
+  group_sum2<GROUP>(ss, dot, red);
+  const A rstd = rstd_in != nullptr ? rstd_in[row] : mp_rsqrt(ss * inv_n + eps);
+  const A coef = rstd * rstd * rstd * dot * inv_n;
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    if (MP_PACK_VALID(u)) {
+      A fo[PN];
+      if constexpr (BLEND) {
+        const Pack<T> po = ld_pack_stream(out_row, MP_PACK_INDEX(u));
+        unpack<T>(po, fo);
+      }
+#pragma unroll
+      for (int k = 0; k < PN; ++k) {
+        A r = rstd * fu[u][k] - fx[u][k] * coef;
+        if constexpr (BLEND) r += alpha * fo[k];
+        acc[u][k] += ft[u][k] * rstd;
+        fu[u][k] = r;
+      }
+      st_pack_stream(out_row, MP_PACK_INDEX(u), pack<T>(fu[u]));
+    }
+  }
+}
+
+// Register variant: a CTA owns rows_per_cta consecutive row groups and writes
+// its gain-gradient partial to partial[blockIdx.x*ROWS + group][n].
+template <typename T, int GROUP, int PPT, bool FULL, bool BLEND>
 __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_rev_kernel(
-    const T* x, const T* __restrict__ gain, const typename Acc<T>::type* __restrict__ rstd_in,
-    const T* gy, typename Acc<T>::type eps, T* gx, typename Acc<T>::type alpha,
-    typename Acc<T>::type* __restrict__ partial, size_t m, size_t n) {
+    const T* x, const T* __restrict__ gain, const typename Acc<T>::type* __restrict__ rstd_in, const T* gy,
+    typename Acc<T>::type eps, T* gx, typename Acc<T>::type alpha, typename Acc<T>::type* __restrict__ partial, size_t m,
+    size_t n, size_t rows_per_cta) {
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
   constexpr int ROWS = RowCfg<GROUP>::ROWS;
@@ -233,67 +289,115 @@ __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_rev_kernel(
   A acc[PPT][PN];
 #pragma unroll
   for (int u = 0; u < PPT; ++u) {
-    const size_t v = t + static_cast<size_t>(u) * GROUP;
-    if (v < nv) pgain[u] = ld_pack(gain, v);
+    if (MP_PACK_VALID(u)) pgain[u] = ld_pack(gain, MP_PACK_INDEX(u));
 #pragma unroll
     for (int k = 0; k < PN; ++k) acc[u][k] = A(0);
   }
   const A inv_n = A(1) / static_cast<A>(n);
-  for (size_t row = static_cast<size_t>(blockIdx.x) * ROWS + g; row < m; row += static_cast<size_t>(gridDim.x) * ROWS) {
-    const T* xr = x + row * n;
-    const T* gr = gy + row * n;
-    T* or_ = gx + row * n;
-    Pack<T> px[PPT], pg[PPT], po[PPT];
+  for (size_t i = 0; i < rows_per_cta; ++i) {
+    const size_t row = (static_cast<size_t>(blockIdx.x) * rows_per_cta + i) * ROWS + g;
+    if (row >= m) break;
+    Pack<T> px[PPT], pg[PPT];
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
-        px[u] = ld_pack_stream(xr, v);
-        pg[u] = ld_pack_stream(gr, v);
-        if constexpr (BLEND) po[u] = ld_pack_stream(or_, v);
+      if (MP_PACK_VALID(u)) {
+        px[u] = ld_pack_stream(x + row * n, MP_PACK_INDEX(u));
+        pg[u] = ld_pack_stream(gy + row * n, MP_PACK_INDEX(u));
       }
     }
-    A ss = A(0), dot = A(0);
-#pragma unroll
-    for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
-#pragma unroll
-        for (int k = 0; k < PN; ++k) {
-          const A a = mp_up(px[u].v[k]);
-          ss += a * a;
-          dot += mp_up(pg[u].v[k]) * mp_up(pgain[u].v[k]) * a;
-        }
-      }
-    }
-    group_sum2<GROUP>(ss, dot, red);
-    const A rstd = rstd_in != nullptr ? rstd_in[row] : mp_rsqrt(ss * inv_n + eps);
-    const A coef = rstd * rstd * rstd * dot * inv_n;
-#pragma unroll
-    for (int u = 0; u < PPT; ++u) {
-      const size_t v = t + static_cast<size_t>(u) * GROUP;
-      if (v < nv) {
-        Pack<T> o;
-#pragma unroll
-        for (int k = 0; k < PN; ++k) {
-          const A a = mp_up(px[u].v[k]);
-          const A gk = mp_up(pg[u].v[k]);
-          A r = rstd * gk * mp_up(pgain[u].v[k]) - a * coef;
-          if constexpr (BLEND) r += alpha * mp_up(po[u].v[k]);
-          o.v[k] = mp_down<T>(r);
-          acc[u][k] += gk * a * rstd;
-        }
-        st_pack_stream(or_, v, o);
-      }
-    }
+    rmsnorm_rev_row<T, GROUP, PPT, FULL, BLEND>(px, pg, pgain, acc, rstd_in, eps, inv_n, alpha, gx + row * n, row, t, nv, red);
   }
   A* pr = partial + (static_cast<size_t>(blockIdx.x) * ROWS + g) * n;
 #pragma unroll
   for (int u = 0; u < PPT; ++u) {
-    const size_t v = t + static_cast<size_t>(u) * GROUP;
-    if (v < nv) {
+    if (MP_PACK_VALID(u)) {
 #pragma unroll
-      for (int k = 0; k < PN; ++k) pr[v * PN + k] = acc[u][k];
+      for (int k = 0; k < PN; ++k) pr[MP_PACK_INDEX(u) * PN + k] = acc[u][k];
+    }
+  }
+}
+
+// Shared-memory staged variant of the RMSNorm reverse kernel: the rows of x and
+// gy that a CTA will need are fetched ahead of time by 1-D bulk async copies
+// (TMA unit) into a ring of `stages` buffers, each guarded by an mbarrier, so
+// the bytes in flight are bounded by shared memory instead of by registers.
+// All 256 threads wait for a stage, copy their slice into registers, and meet
+// in the reduction barrier; after that barrier nobody reads the stage any more
+// and thread 0 refills it with the row `stages` ahead.  Waits are bounded
+// (mp_async.cuh); a timeout sets the status word and ends the CTA's loop.
+constexpr int STG_THREADS = 256;
+
+template <typename T, int PPT, bool FULL, bool BLEND>
+__global__ void __launch_bounds__(STG_THREADS) rmsnorm_rev_staged_kernel(
+    const T* x, const T* __restrict__ gain, const typename Acc<T>::type* __restrict__ rstd_in, const T* gy,
+    typename Acc<T>::type eps, T* gx, typename Acc<T>::type alpha, typename Acc<T>::type* __restrict__ partial,
+    size_t m, size_t n, size_t rows_per_cta, int stages, uint32_t* status) {
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  constexpr int GROUP = STG_THREADS;
+  extern __shared__ __align__(128) unsigned char stg_smem[];
+  __shared__ A red[64];
+  uint64_t* full = reinterpret_cast<uint64_t*>(stg_smem);  // one barrier per stage (<= 16)
+  unsigned char* data = stg_smem + 128;
+  const int t = threadIdx.x;
+  const size_t nv = n / PN;
+  const uint32_t row_bytes = static_cast<uint32_t>(n * sizeof(T));
+  const size_t stage_bytes = 2 * static_cast<size_t>(row_bytes);
+  const size_t r0 = static_cast<size_t>(blockIdx.x) * rows_per_cta;
+  const size_t count = (m - r0) < rows_per_cta ? (m - r0) : rows_per_cta;
+
+  if (t == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(full + s, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  auto issue = [&](size_t i) {  // row r0 + i into stage i % stages
+    const int s = static_cast<int>(i % stages);
+    unsigned char* dst = data + s * stage_bytes;
+    mbar_arrive_expect_tx(full + s, 2 * row_bytes);
+    bulk_load_1d(dst, x + (r0 + i) * n, row_bytes, full + s);
+    bulk_load_1d(dst + row_bytes, gy + (r0 + i) * n, row_bytes, full + s);
+  };
+  if (t == 0) {
+    for (size_t i = 0; i < count && i < static_cast<size_t>(stages); ++i) issue(i);
+  }
+
+  Pack<T> pgain[PPT];
+  A acc[PPT][PN];
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    if (MP_PACK_VALID(u)) pgain[u] = ld_pack(gain, MP_PACK_INDEX(u));
+#pragma unroll
+    for (int k = 0; k < PN; ++k) acc[u][k] = A(0);
+  }
+  const A inv_n = A(1) / static_cast<A>(n);
+  for (size_t i = 0; i < count; ++i) {
+    const int s = static_cast<int>(i % stages);
+    const uint32_t parity = static_cast<uint32_t>((i / stages) & 1);
+    if (!mbar_wait(full + s, parity, status)) break;  // every thread waits on the same phase
+    const size_t row = r0 + i;
+    const unsigned char* sx = data + s * stage_bytes;
+    const unsigned char* sg = sx + row_bytes;
+    Pack<T> px[PPT], pg[PPT];
+#pragma unroll
+    for (int u = 0; u < PPT; ++u) {
+      if (MP_PACK_VALID(u)) {
+        px[u] = *reinterpret_cast<const Pack<T>*>(sx + MP_PACK_INDEX(u) * 16);
+        pg[u] = *reinterpret_cast<const Pack<T>*>(sg + MP_PACK_INDEX(u) * 16);
+      }
+    }
+    // The first barrier inside the row function's reduction also tells thread 0
+    // that every thread has copied stage s to registers; the refill is issued
+    // right after the row is finished.
+    rmsnorm_rev_row<T, GROUP, PPT, FULL, BLEND>(px, pg, pgain, acc, rstd_in, eps, inv_n, alpha, gx + row * n, row, t, nv, red);
+    if (t == 0 && i + stages < count) issue(i + stages);
+  }
+  A* pr = partial + static_cast<size_t>(blockIdx.x) * n;
+#pragma unroll
+  for (int u = 0; u < PPT; ++u) {
+    if (MP_PACK_VALID(u)) {
+#pragma unroll
+      for (int k = 0; k < PN; ++k) pr[MP_PACK_INDEX(u) * PN + k] = acc[u][k];
     }
   }
 }
@@ -320,6 +424,57 @@ __global__ void __launch_bounds__(256) rmsnorm_fold_kernel(const typename Acc<T>
   }
 }
 
+// First stage of a two-stage fold for many partial rows: CTA (column block c,
+// split f) sums the partial rows f, f+F, f+2F, ... of 32*W columns (W = values
+// per 16-byte load) into partial2[f][:].  Eight warps stride the rows with four
+// independent 16-byte loads in flight each; the warps meet in shared memory.
+// The second stage is rmsnorm_fold_kernel over the F rows of partial2.
+constexpr int FOLD_SPLITS = 16;
+
+template <typename A>
+__global__ void __launch_bounds__(256) rmsnorm_fold_stage1_kernel(const A* __restrict__ partial, A* __restrict__ partial2,
+                                                                  size_t n, size_t slots) {
+  constexpr int W = 16 / sizeof(A);
+  __shared__ A sm[8][32 * W + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t c = (static_cast<size_t>(blockIdx.x) * 32 + lane) * W;
+  const size_t F = gridDim.y, f = blockIdx.y;
+  A acc[W];
+#pragma unroll
+  for (int e = 0; e < W; ++e) acc[e] = A(0);
+  if (c < n) {
+    // rows f + F*(warp + 8*j)
+    size_t r = f + F * warp;
+    const size_t step = F * 8;
+    for (; r + 3 * step < slots; r += 4 * step) {
+      Pack<A> q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = ld_pack(partial, ((r + u * step) * n + c) / W);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int e = 0; e < W; ++e) acc[e] += q[u].v[e];
+    }
+    for (; r < slots; r += step) {
+      const Pack<A> q = ld_pack(partial, (r * n + c) / W);
+#pragma unroll
+      for (int e = 0; e < W; ++e) acc[e] += q.v[e];
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < W; ++e) sm[warp][lane * W + e] = acc[e];
+  __syncthreads();
+  for (int j = threadIdx.x; j < 32 * W; j += 256) {
+    const size_t col = static_cast<size_t>(blockIdx.x) * 32 * W + j;
+    if (col < n) {
+      A t = A(0);
+#pragma unroll
+      for (int w = 0; w < 8; ++w) t += sm[w][j];
+      partial2[f * n + col] = t;
+    }
+  }
+}
+
 // --------------------- generic fallback (any n, any alignment) ------------
 // One CTA per row, scalar coalesced accesses, the row is re-read from L2 for
 // each pass.  Used when n is not a multiple of the pack width, a pointer is
@@ -336,10 +491,11 @@ __global__ void __launch_bounds__(GEN_THREADS) softmax_fwd_generic(const T* x, T
     for (size_t j = threadIdx.x; j < n; j += GEN_THREADS) mx = MaxOp::apply(mx, mp_up(xr[j]));
     mx = cta_reduce<MaxOp, GEN_THREADS>(mx, red, mp_neg_inf(A(0)));
     A sum = A(0);
-    for (size_t j = threadIdx.x; j < n; j += GEN_THREADS) sum += mp_exp_diff(mp_up(xr[j]), mx);
+    const A mxs = mp_exp_prescale(mx);
+    for (size_t j = threadIdx.x; j < n; j += GEN_THREADS) sum += mp_exp_diff(mp_up(xr[j]), mxs);
     sum = cta_reduce<SumOp, GEN_THREADS>(sum, red, A(0));
     const A inv = A(1) / sum;
-    for (size_t j = threadIdx.x; j < n; j += GEN_THREADS) yr[j] = mp_down<T>(mp_exp_diff(mp_up(xr[j]), mx) * inv);
+    for (size_t j = threadIdx.x; j < n; j += GEN_THREADS) yr[j] = mp_down<T>(mp_exp_diff(mp_up(xr[j]), mxs) * inv);
   }
 }
 
@@ -384,13 +540,16 @@ template <typename T>
 __global__ void __launch_bounds__(GEN_THREADS) rmsnorm_rev_generic(const T* x, const T* gain, const typename Acc<T>::type* rstd_in,
                                                                    const T* gy, typename Acc<T>::type eps, T* gx,
                                                                    typename Acc<T>::type alpha, bool blend,
-                                                                   typename Acc<T>::type* partial, size_t m, size_t n) {
+                                                                   typename Acc<T>::type* partial, size_t m, size_t n,
+                                                                   size_t rows_per_cta) {
   using A = typename Acc<T>::type;
   __shared__ A red[64];
   const A inv_n = A(1) / static_cast<A>(n);
   A* pr = partial + static_cast<size_t>(blockIdx.x) * n;
   for (size_t j = threadIdx.x; j < n; j += GEN_THREADS) pr[j] = A(0);
-  for (size_t row = blockIdx.x; row < m; row += gridDim.x) {
+  for (size_t i = 0; i < rows_per_cta; ++i) {
+    const size_t row = static_cast<size_t>(blockIdx.x) * rows_per_cta + i;
+    if (row >= m) break;
     const T* xr = x + row * n; const T* gr = gy + row * n; T* or_ = gx + row * n;
     A ss = A(0), dot = A(0);
     for (size_t j = threadIdx.x; j < n; j += GEN_THREADS) {
@@ -416,12 +575,13 @@ __global__ void __launch_bounds__(GEN_THREADS) rmsnorm_rev_generic(const T* x, c
 struct RowPlan {
   bool generic;
   int group, ppt, threads, rows;
+  bool full;
 };
 
 template <typename T>
 RowPlan plan_rows(size_t n, bool aligned) {
   constexpr int PN = Pack<T>::N;
-  RowPlan p{true, GEN_THREADS, 0, GEN_THREADS, 1};
+  RowPlan p{true, GEN_THREADS, 0, GEN_THREADS, 1, false};
   if (!aligned || n % PN != 0 || n == 0) return p;
   const size_t nv = n / PN;
   int group;
@@ -438,33 +598,88 @@ RowPlan plan_rows(size_t n, bool aligned) {
   if (group == 128 && p.ppt == 1) p.ppt = 2;
   p.threads = group < 128 ? 128 : group;
   p.rows = p.threads / group;
+  p.full = nv == static_cast<size_t>(p.group) * p.ppt;
   return p;
 }
 
-// CTAs per SM that keep roughly 2048 (streaming kernels) or 1024 (register-
-// heavy reverse kernels) threads resident.
+// Streaming row kernels launch one CTA per row group (measured faster on B200
+// than persistent CTAs looping in lock-step).  `threads_per_sm` != 0 asks for a
+// persistent grid instead (kernels that carry per-CTA state across rows).
 inline size_t row_grid(const RowPlan& p, size_t m, int sm_count, int threads_per_sm) {
-  size_t per_sm = static_cast<size_t>(threads_per_sm / p.threads);
-  if (per_sm < 1) per_sm = 1;
   size_t grid = (m + p.rows - 1) / p.rows;
-  const size_t cap = static_cast<size_t>(sm_count) * per_sm;
-  if (grid > cap) grid = cap;
+  if (threads_per_sm != 0) {
+    size_t per_sm = static_cast<size_t>(threads_per_sm / p.threads);
+    if (per_sm < 1) per_sm = 1;
+    const size_t cap = static_cast<size_t>(sm_count) * per_sm;
+    if (grid > cap) grid = cap;
+  }
+  if (grid > (1u << 30)) grid = 1u << 30;
   if (grid < 1) grid = 1;
   return grid;
 }
 
-#define MP_ROW_DISPATCH(PLAN, CALL)                                         \
-  do {                                                                      \
-    if ((PLAN).group == 32 && (PLAN).ppt == 1) { CALL(32, 1); }             \
-    else if ((PLAN).group == 32 && (PLAN).ppt == 2) { CALL(32, 2); }        \
-    else if ((PLAN).group == 32) { CALL(32, 4); }                           \
-    else if ((PLAN).group == 128 && (PLAN).ppt == 2) { CALL(128, 2); }      \
-    else if ((PLAN).group == 128) { CALL(128, 4); }                         \
-    else if ((PLAN).group == 256) { CALL(256, 4); }                         \
-    else { CALL(512, 4); }                                                  \
+#define MP_ROW_DISPATCH_F(PLAN, CALL, F)                                      \
+  do {                                                                        \
+    if ((PLAN).group == 32 && (PLAN).ppt == 1) { CALL(32, 1, F); }            \
+    else if ((PLAN).group == 32 && (PLAN).ppt == 2) { CALL(32, 2, F); }       \
+    else if ((PLAN).group == 32) { CALL(32, 4, F); }                          \
+    else if ((PLAN).group == 128 && (PLAN).ppt == 2) { CALL(128, 2, F); }     \
+    else if ((PLAN).group == 128) { CALL(128, 4, F); }                        \
+    else if ((PLAN).group == 256) { CALL(256, 4, F); }                        \
+    else { CALL(512, 4, F); }                                                 \
+  } while (0)
+// `full`: the row has exactly group*ppt packs, the kernel drops its bounds guards
+#define MP_ROW_DISPATCH(PLAN, CALL)                                           \
+  do {                                                                        \
+    if ((PLAN).full) MP_ROW_DISPATCH_F(PLAN, CALL, true);                     \
+    else MP_ROW_DISPATCH_F(PLAN, CALL, false);                                \
   } while (0)
 
-constexpr int REV_THREADS_PER_SM = 1024;
+// Row groups each CTA of the RMSNorm reverse kernel walks (its gain-gradient
+// partial costs one scratch row, so more rows per CTA = less scratch traffic,
+// fewer rows = more CTAs in flight).
+inline size_t rms_rev_rows_per_cta() {
+  static size_t r = 0;
+  if (r == 0) {
+    const char* e = getenv("MP_RMS_REV_ROWS");
+    long v = e ? strtol(e, nullptr, 10) : 0;
+    r = v > 0 ? static_cast<size_t>(v) : 32;
+  }
+  return r;
+}
+// Staged (bulk-copy) plan of the RMSNorm reverse: rows of n*sizeof(T) bytes,
+// 256 threads, up to 4 packs per thread, at least 2 stages in ~100 KB.
+struct StagedPlan { bool ok; int ppt, stages; size_t smem_bytes; bool full; };
+template <typename T>
+StagedPlan plan_staged(size_t n, bool aligned) {
+  constexpr int PN = Pack<T>::N;
+  StagedPlan p{false, 0, 0, 0, false};
+  if (!aligned || n % PN != 0 || getenv("MP_RMS_REV_NO_STAGING") != nullptr) return p;
+  const size_t nv = n / PN;
+  if (nv < 128 || nv > static_cast<size_t>(STG_THREADS) * 4) return p;
+  const size_t stage_bytes = 2 * n * sizeof(T);
+  static size_t budget_kb = 0;  // shared memory per CTA for the ring (MP_RMS_STAGE_KB overrides)
+  if (budget_kb == 0) {
+    const char* e = getenv("MP_RMS_STAGE_KB");
+    const long v = e ? strtol(e, nullptr, 10) : 0;
+    budget_kb = v > 0 ? static_cast<size_t>(v) : 100;
+  }
+  size_t stages = (budget_kb * 1024) / stage_bytes;
+  if (stages > 8) stages = 8;
+  if (stages < 2) return p;
+  const size_t need = (nv + STG_THREADS - 1) / STG_THREADS;
+  p.ok = true;
+  p.ppt = need <= 1 ? 1 : (need <= 2 ? 2 : 4);
+  p.stages = static_cast<int>(stages);
+  p.smem_bytes = 128 + stages * stage_bytes;
+  p.full = nv == static_cast<size_t>(STG_THREADS) * p.ppt;
+  return p;
+}
+inline size_t rms_rev_grid(const RowPlan& p, size_t m) {
+  const size_t groups = (m + p.rows - 1) / p.rows;
+  size_t grid = (groups + rms_rev_rows_per_cta() - 1) / rms_rev_rows_per_cta();
+  return grid < 1 ? 1 : grid;
+}
 
 }  // namespace
 
@@ -475,11 +690,11 @@ static void softmax_ij_j_impl(const void* src_, void* dst_, len_t m, len_t n, St
   T* dst = static_cast<T*>(dst_);
   const RowPlan p = plan_rows<T>(n, mp_aligned16(src) && mp_aligned16(dst));
   cudaStream_t st = mp_stream(ctx);
-  const unsigned grid = static_cast<unsigned>(row_grid(p, m, mp_sm_count(ctx), 2048));
+  const unsigned grid = static_cast<unsigned>(row_grid(p, m, mp_sm_count(ctx), 0));
   if (p.generic) {
     softmax_fwd_generic<T><<<grid, GEN_THREADS, 0, st>>>(src, dst, m, n);
   } else {
-#define CALL(G, P) softmax_fwd_kernel<T, G, P><<<grid, RowCfg<G>::THREADS, 0, st>>>(src, dst, m, n)
+#define CALL(G, P, F) softmax_fwd_kernel<T, G, P, F><<<grid, RowCfg<G>::THREADS, 0, st>>>(src, dst, m, n)
     MP_ROW_DISPATCH(p, CALL);
 #undef CALL
   }
@@ -498,15 +713,15 @@ static void softmax_ij_j_reverse_impl(const void* y_, const void* gy_, void* gx_
   cudaStream_t st = mp_stream(ctx);
   const A a = static_cast<A>(alpha);
   const bool blend = alpha != 0.0;
-  const unsigned grid = static_cast<unsigned>(row_grid(p, m, mp_sm_count(ctx), 2048));
+  const unsigned grid = static_cast<unsigned>(row_grid(p, m, mp_sm_count(ctx), 0));
   if (p.generic) {
     softmax_rev_generic<T><<<grid, GEN_THREADS, 0, st>>>(y, gy, gx, a, blend, m, n);
   } else if (blend) {
-#define CALL(G, P) softmax_rev_kernel<T, G, P, true><<<grid, RowCfg<G>::THREADS, 0, st>>>(y, gy, gx, a, m, n)
+#define CALL(G, P, F) softmax_rev_kernel<T, G, P, F, true><<<grid, RowCfg<G>::THREADS, 0, st>>>(y, gy, gx, a, m, n)
     MP_ROW_DISPATCH(p, CALL);
 #undef CALL
   } else {
-#define CALL(G, P) softmax_rev_kernel<T, G, P, false><<<grid, RowCfg<G>::THREADS, 0, st>>>(y, gy, gx, a, m, n)
+#define CALL(G, P, F) softmax_rev_kernel<T, G, P, F, false><<<grid, RowCfg<G>::THREADS, 0, st>>>(y, gy, gx, a, m, n)
     MP_ROW_DISPATCH(p, CALL);
 #undef CALL
   }
@@ -525,11 +740,11 @@ static void rmsnorm_ij_j_impl(const void* x_, const void* gain_, double eps, voi
   const RowPlan p = plan_rows<T>(n, mp_aligned16(x) && mp_aligned16(gain) && mp_aligned16(y));
   cudaStream_t st = mp_stream(ctx);
   const A e = static_cast<A>(eps);
-  const unsigned grid = static_cast<unsigned>(row_grid(p, m, mp_sm_count(ctx), 2048));
+  const unsigned grid = static_cast<unsigned>(row_grid(p, m, mp_sm_count(ctx), 0));
   if (p.generic) {
     rmsnorm_fwd_generic<T><<<grid, GEN_THREADS, 0, st>>>(x, gain, e, y, rstd, m, n);
   } else {
-#define CALL(G, P) rmsnorm_fwd_kernel<T, G, P><<<grid, RowCfg<G>::THREADS, 0, st>>>(x, gain, e, y, rstd, m, n)
+#define CALL(G, P, F) rmsnorm_fwd_kernel<T, G, P, F><<<grid, RowCfg<G>::THREADS, 0, st>>>(x, gain, e, y, rstd, m, n)
     MP_ROW_DISPATCH(p, CALL);
 #undef CALL
   }
@@ -542,7 +757,10 @@ static void rmsnorm_ij_j_impl(const void* x_, const void* gain_, double eps, voi
 template <typename T>
 static size_t rmsnorm_rev_slots(size_t m, size_t n, int sm_count, bool aligned) {
   const RowPlan p = plan_rows<T>(n, aligned);
-  return row_grid(p, m, sm_count, REV_THREADS_PER_SM) * p.rows;
+  (void)sm_count;
+  size_t slots = rms_rev_grid(p, m) * p.rows;
+  const size_t staged = (m + rms_rev_rows_per_cta() - 1) / rms_rev_rows_per_cta();  // one slot per CTA
+  return slots > staged ? slots : staged;
 }
 
 template <typename T>
@@ -567,22 +785,51 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
     if (scratch == nullptr) MP_FATAL("rmsnorm_ij_j_reverse: scratch must not be NULL");
     const bool aligned = mp_aligned16(x) && mp_aligned16(gain) && mp_aligned16(gy) && mp_aligned16(gx);
     const RowPlan p = plan_rows<T>(n, aligned);
-    const unsigned grid = static_cast<unsigned>(row_grid(p, m, mp_sm_count(ctx), REV_THREADS_PER_SM));
+    const StagedPlan sp = plan_staged<T>(n, aligned);
+    unsigned grid = static_cast<unsigned>(rms_rev_grid(p, m));
+    const size_t rpc = rms_rev_rows_per_cta();
     slots = static_cast<size_t>(grid) * p.rows;
-    if (p.generic) {
-      rmsnorm_rev_generic<T><<<grid, GEN_THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, blend, partial, m, n);
+    MpStreamState* state = mp_state_or_null(ctx);  // the staged kernel reports timeouts through the status word
+    if (sp.ok && state != nullptr) {
+      grid = static_cast<unsigned>((m + rpc - 1) / rpc);
+      slots = grid;
+      uint32_t* status = state->status_dev;
+#define STG(P, F, B)                                                                                       \
+  do {                                                                                                     \
+    MP_CUDA_CHECK(cudaFuncSetAttribute(rmsnorm_rev_staged_kernel<T, P, F, B>,                              \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));          \
+    rmsnorm_rev_staged_kernel<T, P, F, B><<<grid, STG_THREADS, sp.smem_bytes, st>>>(                       \
+        x, gain, rstd, gy, e, gx, a, partial, m, n, rpc, sp.stages, status);                               \
+  } while (0)
+#define STG_P(F, B)                                                                 \
+  do { if (sp.ppt == 1) STG(1, F, B); else if (sp.ppt == 2) STG(2, F, B); else STG(4, F, B); } while (0)
+      if (blend) { if (sp.full) STG_P(true, true); else STG_P(false, true); }
+      else { if (sp.full) STG_P(true, false); else STG_P(false, false); }
+#undef STG_P
+#undef STG
+    } else if (p.generic) {
+      rmsnorm_rev_generic<T><<<grid, GEN_THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, blend, partial, m, n, rpc);
     } else if (blend) {
-#define CALL(G, P) rmsnorm_rev_kernel<T, G, P, true><<<grid, RowCfg<G>::THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, partial, m, n)
+#define CALL(G, P, F) rmsnorm_rev_kernel<T, G, P, F, true><<<grid, RowCfg<G>::THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, partial, m, n, rpc)
       MP_ROW_DISPATCH(p, CALL);
 #undef CALL
     } else {
-#define CALL(G, P) rmsnorm_rev_kernel<T, G, P, false><<<grid, RowCfg<G>::THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, partial, m, n)
+#define CALL(G, P, F) rmsnorm_rev_kernel<T, G, P, F, false><<<grid, RowCfg<G>::THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, partial, m, n, rpc)
       MP_ROW_DISPATCH(p, CALL);
 #undef CALL
     }
     MP_LAUNCH_CHECK();
   }
-  rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial, ggain, a, blend, n, slots);
+  constexpr int W = 16 / sizeof(A);
+  if (slots >= 128 && n % W == 0 && mp_aligned16(partial)) {
+    A* partial2 = partial + slots * n;  // FOLD_SPLITS rows after the per-CTA partials
+    const dim3 g1(static_cast<unsigned>((n + 32 * W - 1) / (32 * W)), FOLD_SPLITS);
+    rmsnorm_fold_stage1_kernel<A><<<g1, 256, 0, st>>>(partial, partial2, n, slots);
+    MP_LAUNCH_CHECK();
+    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial2, ggain, a, blend, n, FOLD_SPLITS);
+  } else {
+    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial, ggain, a, blend, n, slots);
+  }
   MP_LAUNCH_CHECK();
 }
 
@@ -595,7 +842,7 @@ extern "C" len_t mpRmsnormReverseScratchBytes(len_t m, len_t n, StreamContext ct
       rmsnorm_rev_slots<float>(m, n, sms, true),  rmsnorm_rev_slots<float>(m, n, sms, false),
       rmsnorm_rev_slots<double>(m, n, sms, true), rmsnorm_rev_slots<double>(m, n, sms, false)};
   for (size_t c : cand) if (c > slots) slots = c;
-  return static_cast<len_t>(slots * n * sizeof(double));
+  return static_cast<len_t>((slots + FOLD_SPLITS) * n * sizeof(double));
 }
 
 MP_STAMP3(softmax_ij_j, (const void* src, void* dst, len_t m, len_t n, StreamContext ctx), (src, dst, m, n, ctx))

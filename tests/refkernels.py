@@ -33,6 +33,8 @@ class RefLib:
         self.ctx = self.lib.mpInitStream()
 
     def launch(self, name, sfx, *args):
+        import torch
+        torch.cuda.current_stream().synchronize()
         conv = [C.c_void_p(a.data_ptr()) if hasattr(a, "data_ptr") else a for a in args]
         getattr(self.lib, f"launch_{name}_{sfx}")(*conv, self.ctx)
         self.lib.mpStreamSynchronize(self.ctx)

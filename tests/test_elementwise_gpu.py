@@ -4,7 +4,7 @@ buffers and misaligned base pointers."""
 import numpy as np
 import pytest
 
-from util import TOL_EW, assert_close, dev, host, narrow, rng_normal, wide
+from util import run, TOL_EW, assert_close, dev, host, narrow, rng_normal, wide
 
 pytestmark = pytest.mark.gpu
 
@@ -12,10 +12,6 @@ SIZES = [0, 1, 31, 4097, (1 << 20) + 3]
 DTYPES = ["r16", "r32", "r64"]
 
 
-def run(mp, stream, name, sfx, *args):
-    import torch
-    mp.launch(name, {"r16": torch.float16, "r32": torch.float32, "r64": torch.float64}[sfx], *args, stream)
-    stream.sync()
 
 
 @pytest.mark.parametrize("sfx", DTYPES)

@@ -2,7 +2,7 @@
 import numpy as np
 import pytest
 
-from util import TOL_EW, TOL_RED, assert_close, dev, host, narrow, rng_normal, torch_dtype, wide
+from util import run, TOL_EW, TOL_RED, assert_close, dev, host, narrow, rng_normal, torch_dtype, wide
 
 pytestmark = pytest.mark.gpu
 
@@ -10,9 +10,6 @@ SHAPES = [(1, 1), (3, 2), (32, 256), (256, 256), (37, 53), (64, 65), (129, 1000)
 DTYPES = ["r16", "r32", "r64"]
 
 
-def run(mp, stream, name, sfx, *args):
-    mp.launch(name, torch_dtype(sfx), *args, stream)
-    stream.sync()
 
 
 @pytest.mark.parametrize("sfx", DTYPES)

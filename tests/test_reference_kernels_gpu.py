@@ -7,7 +7,7 @@ path is wrong or racy (reduce_ij_j, broadcast_i_ij)."""
 import numpy as np
 import pytest
 
-from util import TOL_EW, TOL_RED, assert_close, dev, host, narrow, rng_normal, torch_dtype, wide
+from util import run, TOL_EW, TOL_RED, assert_close, dev, host, narrow, rng_normal, torch_dtype, wide
 
 pytestmark = pytest.mark.gpu
 
@@ -21,8 +21,7 @@ def ref(stream):
 
 
 def ours(mp, stream, name, sfx, *args):
-    mp.launch(name, torch_dtype(sfx), *args, stream)
-    stream.sync()
+    run(mp, stream, name, sfx, *args)
 
 
 # r16 reference arithmetic is native half (and half-accumulated in reductions):

@@ -63,3 +63,13 @@ def rng_normal(seed, shape, sfx, scale=1.0, loc=0.0):
 def rng_uniform(seed, shape, sfx, lo=-1.0, hi=1.0):
     r = np.random.default_rng(seed)
     return r.uniform(lo, hi, shape).astype(np.float32).astype(NP_OF[sfx])
+
+
+def run(mp, stream, name, sfx, *args):
+    """Launch through the C ABI on the library's stream and wait for it.  The
+    stream is non-blocking, so work torch queued on its own stream (uploads,
+    random fills) is drained first."""
+    import torch
+    torch.cuda.current_stream().synchronize()
+    mp.launch(name, torch_dtype(sfx), *args, stream)
+    stream.sync()
