@@ -70,8 +70,10 @@ def measured_peak():
 
 # ----------------------------------------------------------------------------
 class ClockSampler:
-    """nvidia-smi sampling of SM clocks and throttle reasons during the timed region."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi sampling (every 20 ms) of SM clocks and throttle reasons.
+    Started before the warm-up; `stop(t0, t1)` keeps the samples whose wall-clock
+    time falls inside the timed region [t0, t1] (and says how many there were)."""
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -87,36 +89,43 @@ class ClockSampler:
         fd, self.path = tempfile.mkstemp(suffix=".csv")
         os.close(fd)
         self.proc = subprocess.Popen([exe, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                      "-i", str(self.index), "-lms", "100"],
+                                      "-i", str(self.index), "-lms", "20"],
                                      stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        time.sleep(0.5)   # let the sampler reach its steady rate before the timed region
 
-    def stop(self):
+    def stop(self, t0: float, t1: float):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        import datetime
+        rows = []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in Path(self.path).read_text().splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
+            if len(parts) < 10:
                 continue
             try:
-                sm.append(float(parts[1])); mx.append(float(parts[2]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[2]), float(parts[3]), [n for n, v in zip(names, parts[6:10])
+                                                                    if v.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
         os.unlink(self.path)
-        # samples under load only (idle samples before/after the region sit at the floor clock)
-        load = [s for s in sm if s > 0.5 * max(sm)] if sm else []
-        return {"sm_mhz": statistics.median(load) if load else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+        inside = [r for r in rows if t0 - 0.02 <= r[0] <= t1 + 0.02]
+        scope = "timed region"
+        if len(inside) < 2:   # region shorter than the sampling period: use the loaded samples around it
+            mx = max((r[1] for r in rows), default=0.0)
+            inside = [r for r in rows if r[1] > 0.5 * mx and t0 - 1.0 <= r[0] <= t1 + 1.0]
+            scope = "loaded samples within 1 s of the timed region"
+        reasons = sorted({n for r in inside for n in r[3]})
+        return {"sm_mhz": statistics.median(r[1] for r in inside) if inside else None,
+                "sm_max_mhz": max((r[2] for r in rows), default=None), "reasons": reasons,
+                "samples": len(inside), "scope": scope}
 
 
 # ----------------------------------------------------------------------------
@@ -171,7 +180,7 @@ def run_ours(args):
                       0.0, b["scratch"], M, N, stream)
 
     kernels = [(op, sfx) for sfx, _ in DTYPES for op in OPS]
-    launches_per_step = len(kernels) + 2      # each RMSNorm reverse = row kernel + fold kernel
+    launches_per_step = len(kernels) + 4      # each RMSNorm reverse = row kernel + two fold kernels
 
     def step(events=None):
         for i, (op, sfx) in enumerate(kernels):
@@ -188,12 +197,13 @@ def run_ours(args):
             dist.barrier()
 
     # ---- device-resident timing ----------------------------------------------
-    for _ in range(args.warmup):
-        step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    wall0 = time.time()
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
     per_kernel = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in kernels]
                   for _ in range(args.steps)]
@@ -202,7 +212,8 @@ def run_ours(args):
         step(per_kernel[k])
     e1.record(ts)
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
+    wall1 = time.time()
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     ms_total = e0.elapsed_time(e1)
     if stream.status() != 0:
         raise SystemExit("a kernel reported a non-zero status word")

@@ -5,7 +5,7 @@ The product is the C-ABI shared library built from ``csrc/`` (declared in
 tests and benchmarks; importing it without the built library raises.
 """
 from .abi import StreamContext, LAUNCHERS, UTILS, SUFFIXES, LIB_PATH, load
-from .runtime import Stream, lib, suffix_of, launch
+from .runtime import Stream, FusedChain, lib, suffix_of, launch
 
 __all__ = ["StreamContext", "LAUNCHERS", "UTILS", "SUFFIXES", "LIB_PATH", "load",
-           "Stream", "lib", "suffix_of", "launch"]
+           "Stream", "FusedChain", "lib", "suffix_of", "launch"]

@@ -81,6 +81,15 @@ UTILS = {
     "mpHostAlloc": (P, [L]),
     "mpHostFree": (None, [P]),
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
+    # include/mp_jit.h
+    "mpJitCompile": (P, [C.c_char_p, U32]),
+    "mpJitRelease": (None, [P]),
+    "mpJitNumLeaves": (U32, [P]),
+    "mpJitLeafName": (C.c_char_p, [P, U32]),
+    "mpJitForward": (None, [P, C.POINTER(C.c_void_p), P, L, CTX]),
+    "mpJitReverse": (None, [P, C.POINTER(C.c_void_p), P, C.POINTER(C.c_void_p), D, L, CTX]),
+    "mpJitGenerateSource": (P, [C.c_char_p, U32]),
+    "mpJitFreeSource": (None, [P]),
 }
 
 SUFFIXES = ("r16", "r32", "r64")

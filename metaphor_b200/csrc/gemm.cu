@@ -1,0 +1,464 @@
+// Contractions C[M,N] = alpha * op(A) * op(B) (+ bias) + beta * C, row-major.
+//
+//   launch_inner_product_ij_jk_ik : A[M,K]      B[K,N]       (reference: cuBLAS via
+//                                                             inner_product_ij_jk_ik.cu:3-27)
+//   launch_inner_product_ij_kj_ik : A[M,K]      B[N,K]^T     (reference: transpose to
+//   launch_inner_product_ji_jk_ik : A[K,M]^T    B[K,N]        scratch + the call above)
+//   launch_linear_ij_jk_ik        : A[M,K]      B[K,N] + bias[N]
+//
+// r16 and r32 run on the tcgen05 tensor cores: operand tiles are brought into
+// 128-byte-swizzled shared memory by TMA (one warp's elected thread), a single
+// thread issues tcgen05.mma with the fp32 accumulator tile in TMEM, and four
+// epilogue warps read the accumulator back with tcgen05.ld and apply alpha,
+// beta, bias on the way to global memory.  Transposed operands need no scratch
+// copy: the shared-memory descriptor and the instruction descriptor carry the
+// operand's major-ness.  r32 uses kind::tf32 on an error-compensated split
+// (hi + lo, three MMAs) unless MP_GEMM_TF32X1 is set; r64 and shapes TMA cannot
+// address (row pitch not a multiple of 16 bytes) use an FP-pipe tile kernel.
+#include "mp_tcgen05.cuh"
+
+#include <cuda.h>
+#include <mutex>
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// SIMT tile kernel: any dtype, any shape.  64x64 output tile, 16-deep k-slices
+// through shared memory, 4x4 outputs per thread, accumulation in Acc<T>.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                        const T* __restrict__ bias, typename Acc<T>::type alpha, T* c,
+                                                        typename Acc<T>::type beta, size_t M, size_t N, size_t K, int a_mn,
+                                                        int b_mn) {
+  using A = typename Acc<T>::type;
+  constexpr int TS = 64, KS = 16;
+  __shared__ A sa[KS][TS + 1];
+  __shared__ A sb[KS][TS + 1];
+  const size_t m0 = static_cast<size_t>(blockIdx.y) * TS, n0 = static_cast<size_t>(blockIdx.x) * TS;
+  const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+  A acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = A(0);
+  for (size_t k0 = 0; k0 < K; k0 += KS) {
+    for (int idx = threadIdx.x; idx < TS * KS; idx += 256) {
+      // A element (m, k): a_mn ? a[k*M + m] : a[m*K + k]
+      int kk, mm;
+      if (a_mn) { mm = idx % TS; kk = idx / TS; } else { kk = idx % KS; mm = idx / KS; }
+      const size_t gm = m0 + mm, gk = k0 + kk;
+      sa[kk][mm] = (gm < M && gk < K) ? mp_up(a_mn ? a[gk * M + gm] : a[gm * K + gk]) : A(0);
+      int kb, nb;
+      if (b_mn) { nb = idx % TS; kb = idx / TS; } else { kb = idx % KS; nb = idx / KS; }
+      const size_t gn = n0 + nb, gkb = k0 + kb;
+      sb[kb][nb] = (gn < N && gkb < K) ? mp_up(b_mn ? b[gkb * N + gn] : b[gn * K + gkb]) : A(0);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < KS; ++kk) {
+      A av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = sa[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = sb[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const size_t gm = m0 + ty * 4 + i;
+    if (gm >= M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const size_t gn = n0 + tx * 4 + j;
+      if (gn >= N) continue;
+      A r = alpha * acc[i][j];
+      if (bias != nullptr) r += mp_up(bias[gn]);
+      if (beta != A(0)) r += beta * mp_up(c[gm * N + gn]);
+      c[gm * N + gn] = mp_down<T>(r);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// tcgen05 kernel.
+// ---------------------------------------------------------------------------
+constexpr int BM = 128;               // UMMA M (one TMEM lane per output row)
+constexpr int SWIZZLE_BYTES = 128;    // one operand row / k-row in shared memory
+constexpr int GEMM_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+constexpr int MAX_STAGES = 8;
+
+template <typename T> struct GemmT;
+template <> struct GemmT<__half> {
+  static constexpr int BK = 64;       // elements per 128-byte row
+  static constexpr int UMMA_K = 16;
+  static constexpr bool TF32 = false;
+  static constexpr uint32_t FMT = UMMA_FMT_F16;
+};
+template <> struct GemmT<float> {
+  static constexpr int BK = 32;
+  static constexpr int UMMA_K = 8;
+  static constexpr bool TF32 = true;
+  static constexpr uint32_t FMT = UMMA_FMT_TF32;
+};
+
+struct GemmArgs {
+  const void* bias;   // N values of T or nullptr
+  void* c;            // [M, N] row-major
+  float alpha, beta;
+  int M, N, K;
+  int a_mn, b_mn;     // operand major-ness: 0 = K contiguous, 1 = M resp. N contiguous
+  int stages;
+  int split;          // r32 only: 1 = error-compensated hi/lo split (3 MMAs per k-slice)
+  uint32_t* status;
+};
+
+// Shared memory of one stage: A tile (BM x 128 B), B tile (BN x 128 B), and for
+// the split mode the "lo" copies of both.
+template <int BN> constexpr int stage_bytes(bool split) {
+  return (BM * SWIZZLE_BYTES + BN * SWIZZLE_BYTES) * (split ? 2 : 1);
+}
+
+template <typename T, int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                      const __grid_constant__ CUtensorMap tmap_b,
+                                                                      const GemmArgs g) {
+  using G = GemmT<T>;
+  constexpr int BK = G::BK;
+  constexpr int A_BYTES = BM * SWIZZLE_BYTES, B_BYTES = BN * SWIZZLE_BYTES;
+  constexpr int KSLICES = BK / G::UMMA_K;  // 4
+  extern __shared__ unsigned char gemm_smem_raw[];
+  // 1024-byte alignment: swizzle atoms are 8 rows x 128 bytes
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stages = g.stages;
+  const int stage_sz = (A_BYTES + B_BYTES) * (g.split ? 2 : 1);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(stages) * stage_sz);
+  uint64_t* ready = full + MAX_STAGES;      // split mode: lo tiles written
+  uint64_t* empty = ready + MAX_STAGES;
+  uint64_t* acc_full = empty + MAX_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int num_kb = (g.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(ready + s, 128);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) break;
+        unsigned char* sa = smem + static_cast<size_t>(s) * stage_sz;
+        unsigned char* sb = sa + A_BYTES;
+        mbar_arrive_expect_tx(full + s, A_BYTES + B_BYTES);
+        const int k0 = kb * BK;
+        if (!g.a_mn) {
+          tma_load_2d(sa, &tmap_a, k0, m0, full + s);            // box {BK, BM}
+        } else {
+#pragma unroll 1
+          for (int j = 0; j < BM / BK; ++j)                        // boxes {BK along M, BK k-rows}
+            tma_load_2d(sa + j * (BK * SWIZZLE_BYTES), &tmap_a, m0 + j * BK, k0, full + s);
+        }
+        if (!g.b_mn) {
+          tma_load_2d(sb, &tmap_b, k0, n0, full + s);            // box {BK, BN}
+        } else {
+#pragma unroll 1
+          for (int j = 0; j < BN / BK; ++j)
+            tma_load_2d(sb + j * (BK * SWIZZLE_BYTES), &tmap_b, n0 + j * BK, k0, full + s);
+        }
+        if (++s == stages) { s = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = umma_instr_desc(G::FMT, g.a_mn, g.b_mn, BM, BN);
+      // K-major: rows of 128 B, 8-row groups 1024 B apart, k-slice = +32 B.
+      // MN-major: k-rows of 128 B, 64/32-column blocks BK*128 B apart, k-slice = +UMMA_K*128 B.
+      const uint32_t a_lbo = g.a_mn ? BK * SWIZZLE_BYTES : 16, b_lbo = g.b_mn ? BK * SWIZZLE_BYTES : 16;
+      const uint32_t a_kstep = g.a_mn ? G::UMMA_K * SWIZZLE_BYTES : 32, b_kstep = g.b_mn ? G::UMMA_K * SWIZZLE_BYTES : 32;
+      // 32-bit MN-major tiles use the 32-byte-atom swizzle (groups of 4 k-rows, 512 B)
+      const uint32_t a_lay = (G::TF32 && g.a_mn) ? UMMA_LAYOUT_SW128_BASE32B : UMMA_LAYOUT_SW128;
+      const uint32_t b_lay = (G::TF32 && g.b_mn) ? UMMA_LAYOUT_SW128_BASE32B : UMMA_LAYOUT_SW128;
+      const uint32_t a_sbo = (G::TF32 && g.a_mn) ? 512 : 1024, b_sbo = (G::TF32 && g.b_mn) ? 512 : 1024;
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        uint64_t* wait_on = g.split ? (ready + s) : (full + s);
+        if (!mbar_wait_abortable(wait_on, phase, g.status, abort)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t sa = mp_smem_u32(smem + static_cast<size_t>(s) * stage_sz);
+        const uint32_t sb = sa + A_BYTES;
+        const uint32_t sa_lo = sb + B_BYTES, sb_lo = sa_lo + A_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < KSLICES; ++ks) {
+          const uint64_t ad = umma_smem_desc(sa + ks * a_kstep, a_lbo, a_sbo, a_lay);
+          const uint64_t bd = umma_smem_desc(sb + ks * b_kstep, b_lbo, b_sbo, b_lay);
+          umma<G::TF32>(tmem_acc, ad, bd, idesc, (kb | ks) != 0 ? 1u : 0u);
+          if (g.split) {
+            const uint64_t adl = umma_smem_desc(sa_lo + ks * a_kstep, a_lbo, a_sbo, a_lay);
+            const uint64_t bdl = umma_smem_desc(sb_lo + ks * b_kstep, b_lbo, b_sbo, b_lay);
+            umma<G::TF32>(tmem_acc, ad, bdl, idesc, 1u);   // hi * lo
+            umma<G::TF32>(tmem_acc, adl, bd, idesc, 1u);   // lo * hi
+          }
+        }
+        umma_commit(empty + s);  // the stage may be refilled once these MMAs have read it
+        if (++s == stages) { s = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  } else {
+    // ---------------- operand split (r32 only), then epilogue -----------------
+    const int et = threadIdx.x - 64;  // 0..127
+    if (g.split) {
+      // hi = x with the 13 low mantissa bits cleared (exactly representable in
+      // tf32, so the tensor core's own fp32 -> tf32 conversion cannot change it),
+      // lo = x - hi (exact in fp32; its tf32 conversion error is ~2^-21 |x|).
+      int s = 0;
+      uint32_t phase = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_abortable(full + s, phase, g.status, abort)) break;
+        unsigned char* hi = smem + static_cast<size_t>(s) * stage_sz;
+        unsigned char* lo = hi + A_BYTES + B_BYTES;
+        for (int off = et * 16; off < A_BYTES + B_BYTES; off += 128 * 16) {
+          const uint4 v = *reinterpret_cast<const uint4*>(hi + off);
+          uint4 h, r;
+          h.x = v.x & 0xFFFFE000u; h.y = v.y & 0xFFFFE000u; h.z = v.z & 0xFFFFE000u; h.w = v.w & 0xFFFFE000u;
+          r.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(h.x));
+          r.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(h.y));
+          r.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(h.z));
+          r.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(h.w));
+          *reinterpret_cast<uint4*>(hi + off) = h;
+          *reinterpret_cast<uint4*>(lo + off) = r;
+        }
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's reads
+        mbar_arrive(ready + s);
+        if (++s == stages) { s = 0; phase ^= 1u; }
+      }
+    }
+    const bool acc_ready = mbar_wait_abortable(acc_full, 0, g.status, abort);
+    __syncwarp();  // tcgen05.ld is warp-collective
+    if (acc_ready) {
+      tcgen05_fence_after_sync();
+      const int quarter = warp & 3;                 // TMEM lanes this warp may read
+      const int row = m0 + quarter * 32 + lane;
+      T* crow = static_cast<T*>(g.c) + static_cast<size_t>(row) * g.N;
+      const T* bias = static_cast<const T*>(g.bias);
+      const bool vec_ok = (static_cast<size_t>(g.N) * sizeof(T)) % 16 == 0 && mp_aligned16(g.c);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        tmem_ld_wait();
+        const int col0 = n0 + c0;
+        if (row < g.M && col0 < g.N) {
+          float r[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[j]);
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < g.N) r[j] += mp_up(bias[col0 + j]);
+          }
+          if (vec_ok && col0 + 32 <= g.N) {
+            constexpr int PN = Pack<T>::N;
+            if (g.beta != 0.0f) {
+#pragma unroll
+              for (int p = 0; p < 32 / PN; ++p) {
+                float old[PN];
+                unpack<T>(ld_pack(crow + col0, p), old);
+#pragma unroll
+                for (int e = 0; e < PN; ++e) r[p * PN + e] += g.beta * old[e];
+              }
+            }
+#pragma unroll
+            for (int p = 0; p < 32 / PN; ++p) st_pack(crow + col0, p, pack<T>(r + p * PN));
+          } else {
+            for (int j = 0; j < 32 && col0 + j < g.N; ++j) {
+              float o = r[j];
+              if (g.beta != 0.0f) o += g.beta * mp_up(crow[col0 + j]);
+              crow[col0 + j] = mp_down<T>(o);
+            }
+          }
+        }
+      }
+    }
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_acc, BN);
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor maps and dispatch.
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    MP_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres));
+    if (p == nullptr || qres != cudaDriverEntryPointSuccess) MP_FATAL("cuTensorMapEncodeTiled is not available");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D row-major matrix [rows, cols] of T, box = {box_cols (128 bytes), box_rows}, 128-byte swizzle
+// (16-byte atoms, or 32-byte atoms when `atom32`), out-of-range elements read as zero.
+template <typename T>
+CUtensorMap make_map(const void* base, size_t rows, size_t cols, uint32_t box_cols, uint32_t box_rows, bool atom32 = false) {
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * sizeof(T)};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  MP_CU_CHECK(encode_tiled()(&map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return map;
+}
+
+template <typename T, int BN>
+void launch_tc(const T* a, const T* b, const GemmArgs& args, cudaStream_t st) {
+  using G = GemmT<T>;
+  const int M = args.M, N = args.N, K = args.K;
+  // A: K-major [M,K] box {BK, BM};  MN-major [K,M] box {BK (along M), BK (k-rows)}
+  // (32-bit MN-major tiles: 128-byte swizzle with 32-byte atoms, the only MN-major layout tf32 accepts)
+  const CUtensorMap ta = args.a_mn ? make_map<T>(a, K, M, G::BK, G::BK, G::TF32) : make_map<T>(a, M, K, G::BK, BM);
+  const CUtensorMap tb = args.b_mn ? make_map<T>(b, K, N, G::BK, G::BK, G::TF32) : make_map<T>(b, N, K, G::BK, BN);
+  const size_t smem = static_cast<size_t>(args.stages) * stage_bytes<BN>(args.split != 0) + 1024 /*align*/ + 256 /*barriers*/;
+  MP_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
+  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  gemm_tcgen05_kernel<T, BN><<<grid, GEMM_THREADS, smem, st>>>(ta, tb, args);
+  MP_LAUNCH_CHECK();
+}
+
+bool env_flag(const char* name) {
+  const char* e = getenv(name);
+  return e != nullptr && e[0] != '\0' && e[0] != '0';
+}
+
+// Output-tile width: wide tiles for wide problems, narrower ones when they are
+// needed to put at least ~one CTA on every SM.
+int pick_bn(int M, int N, int sms) {
+  const long tiles_m = (M + BM - 1) / BM;
+  if (N > 128 && tiles_m * ((N + 255) / 256) >= sms) return 256;
+  if (N > 64 && tiles_m * ((N + 127) / 128) >= sms / 2) return 128;
+  return N > 64 && tiles_m * ((N + 127) / 128) >= 4 ? 128 : 64;
+}
+
+template <typename T>
+void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alpha, void* c_, double beta, len_t M, len_t N,
+                   len_t K, int a_mn, int b_mn, StreamContext ctx) {
+  using A = typename Acc<T>::type;
+  if (M == 0 || N == 0) return;
+  cudaStream_t st = mp_stream(ctx);
+  const T* a = static_cast<const T*>(a_);
+  const T* b = static_cast<const T*>(b_);
+  T* c = static_cast<T*>(c_);
+  bool tensor_path = !std::is_same<T, double>::value && K > 0 && !env_flag("MP_GEMM_FORCE_SIMT");
+  if (tensor_path) {
+    // TMA needs 16-byte aligned bases and row pitches, and 32-bit coordinates
+    const size_t a_pitch = (a_mn ? M : K) * sizeof(T), b_pitch = (b_mn ? N : K) * sizeof(T);
+    tensor_path = mp_aligned16(a) && mp_aligned16(b) && a_pitch % 16 == 0 && b_pitch % 16 == 0 &&
+                  M < (1ull << 31) && N < (1ull << 31) && K < (1ull << 31) && mp_state_or_null(ctx) != nullptr;
+  }
+  if (!tensor_path) {
+    const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64));
+    if (grid.y > 65535) MP_FATAL("inner_product: M too large for the FP-pipe kernel");
+    gemm_simt_kernel<T><<<grid, 256, 0, st>>>(a, b, static_cast<const T*>(bias), static_cast<A>(alpha), c, static_cast<A>(beta),
+                                              M, N, K, a_mn, b_mn);
+    MP_LAUNCH_CHECK();
+    return;
+  }
+  if constexpr (!std::is_same<T, double>::value) {
+    MpStreamState* state = mp_state(ctx);
+    GemmArgs args;
+    args.bias = bias;
+    args.c = c;
+    args.alpha = static_cast<float>(alpha);
+    args.beta = static_cast<float>(beta);
+    args.M = static_cast<int>(M);
+    args.N = static_cast<int>(N);
+    args.K = static_cast<int>(K);
+    args.a_mn = a_mn;
+    args.b_mn = b_mn;
+    args.split = (std::is_same<T, float>::value && !env_flag("MP_GEMM_TF32X1")) ? 1 : 0;
+    args.status = state->status_dev;
+    const int bn = pick_bn(args.M, args.N, state->sm_count);
+    const int budget = 200 * 1024;
+    auto stages_for = [&](int per_stage) {
+      int s = budget / per_stage;
+      if (s > MAX_STAGES) s = MAX_STAGES;
+      const int kb = (args.K + GemmT<T>::BK - 1) / GemmT<T>::BK;
+      if (s > kb) s = kb < 2 ? 2 : kb;
+      return s < 2 ? 2 : s;
+    };
+    if (bn == 256) { args.stages = stages_for(stage_bytes<256>(args.split != 0)); launch_tc<T, 256>(a, b, args, st); }
+    else if (bn == 128) { args.stages = stages_for(stage_bytes<128>(args.split != 0)); launch_tc<T, 128>(a, b, args, st); }
+    else { args.stages = stages_for(stage_bytes<64>(args.split != 0)); launch_tc<T, 64>(a, b, args, st); }
+  }
+}
+
+}  // namespace
+
+template <typename T>
+static void inner_product_ij_jk_ik_impl(const void* a, const void* b, double alpha, void* c, double beta, len_t m, len_t n,
+                                        len_t k, StreamContext ctx) {
+  gemm_dispatch<T>(a, b, nullptr, alpha, c, beta, m, k, n, 0, 1, ctx);  // A[m,n] K-major, B[n,k] N-contiguous
+}
+template <typename T>
+static void inner_product_ij_kj_ik_impl(const void* a, const void* b, double alpha, void* c, double beta, len_t m, len_t n,
+                                        len_t k, StreamContext ctx) {
+  gemm_dispatch<T>(a, b, nullptr, alpha, c, beta, m, k, n, 0, 0, ctx);  // B[k,n] K-major
+}
+template <typename T>
+static void inner_product_ji_jk_ik_impl(const void* a, const void* b, double alpha, void* c, double beta, len_t m, len_t n,
+                                        len_t k, StreamContext ctx) {
+  gemm_dispatch<T>(a, b, nullptr, alpha, c, beta, m, k, n, 1, 1, ctx);  // A[n,m] M-contiguous
+}
+template <typename T>
+static void linear_ij_jk_ik_impl(const void* a, const void* b, const void* bias, double alpha, void* c, double beta, len_t m,
+                                 len_t n, len_t k, StreamContext ctx) {
+  gemm_dispatch<T>(a, b, bias, alpha, c, beta, m, k, n, 0, 1, ctx);
+}
+
+MP_STAMP3(inner_product_ij_jk_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))
+MP_STAMP3(inner_product_ij_kj_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))
+MP_STAMP3(inner_product_ji_jk_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))
+MP_STAMP3(linear_ij_jk_ik, (const void* a, const void* b, const void* bias, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, bias, alpha, c, beta, m, n, k, s))

@@ -181,7 +181,7 @@ __device__ __forceinline__ Pack<__half> pack<__half>(const float* in) {
   return r;
 }
 
-static inline bool mp_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+__host__ __device__ static inline bool mp_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---------------------------------------------------------------------------
 // Reductions.
@@ -196,6 +196,14 @@ __device__ __forceinline__ A warp_reduce(A v) {
   return v;
 }
 
+// Butterfly over the low `WIDTH` lanes only (WIDTH a power of two <= 32).
+template <typename Op, int WIDTH, typename A>
+__device__ __forceinline__ A warp_reduce_width(A v) {
+#pragma unroll
+  for (int off = WIDTH / 2; off > 0; off >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, off));
+  return v;
+}
+
 // All threads of the CTA get the result.  `smem` holds >= 32 values of A and
 // may be reused right after the call returns (two barriers inside).
 template <typename Op, int THREADS, typename A>
@@ -206,8 +214,9 @@ __device__ __forceinline__ A cta_reduce(A v, A* smem, A identity) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (lane == 0) smem[warp] = v;
   __syncthreads();
-  A r = (lane < WARPS) ? smem[lane] : identity;
-  r = warp_reduce<Op>(r);
+  (void)identity;
+  A r = smem[lane & (WARPS - 1)];  // WARPS is a power of two: every lane holds one of the partials
+  r = warp_reduce_width<Op, WARPS>(r);
   __syncthreads();
   return r;
 }

@@ -34,7 +34,8 @@ __device__ __forceinline__ float mp_exp_diff(float x, float mx_scaled) {
   return y;
 }
 __device__ __forceinline__ double mp_exp_diff(double x, double mx) { return exp(x - mx); }
-__device__ __forceinline__ float mp_rsqrt(float x) { return 1.0f / sqrtf(x); }
+// MUFU.RSQ, relative error about 2^-22: far inside the 1e-4 budget of a row reduction
+__device__ __forceinline__ float mp_rsqrt(float x) { return rsqrtf(x); }
 __device__ __forceinline__ double mp_rsqrt(double x) { return 1.0 / sqrt(x); }
 
 template <typename Op, int GROUP, typename A>
@@ -53,10 +54,8 @@ __device__ __forceinline__ void group_sum2(A& a, A& b, A* smem) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { smem[warp] = a; smem[32 + warp] = b; }
     __syncthreads();
-    A ra = lane < WARPS ? smem[lane] : A(0);
-    A rb = lane < WARPS ? smem[32 + lane] : A(0);
-    a = warp_reduce<SumOp>(ra);
-    b = warp_reduce<SumOp>(rb);
+    a = warp_reduce_width<SumOp, WARPS>(smem[lane & (WARPS - 1)]);
+    b = warp_reduce_width<SumOp, WARPS>(smem[32 + (lane & (WARPS - 1))]);
     __syncthreads();
   }
 }
@@ -327,8 +326,12 @@ __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_rev_kernel(
 // (mp_async.cuh); a timeout sets the status word and ends the CTA's loop.
 constexpr int STG_THREADS = 256;
 
+// CTAs per SM the staged kernel is compiled for: up to 2 packs per thread and
+// stream fit 3 CTAs (<= 85 registers), wider rows 2.
+template <typename T, int PPT> struct StgOcc { static constexpr int value = (PPT <= 2 && sizeof(T) < 8) ? 3 : 2; };
+
 template <typename T, int PPT, bool FULL, bool BLEND>
-__global__ void __launch_bounds__(STG_THREADS) rmsnorm_rev_staged_kernel(
+__global__ void __launch_bounds__(STG_THREADS, StgOcc<T, PPT>::value) rmsnorm_rev_staged_kernel(
     const T* x, const T* __restrict__ gain, const typename Acc<T>::type* __restrict__ rstd_in, const T* gy,
     typename Acc<T>::type eps, T* gx, typename Acc<T>::type alpha, typename Acc<T>::type* __restrict__ partial,
     size_t m, size_t n, size_t rows_per_cta, int stages, uint32_t* status) {
@@ -351,15 +354,14 @@ __global__ void __launch_bounds__(STG_THREADS) rmsnorm_rev_staged_kernel(
     mbar_fence_init();
   }
   __syncthreads();
-  auto issue = [&](size_t i) {  // row r0 + i into stage i % stages
-    const int s = static_cast<int>(i % stages);
+  auto issue = [&](size_t i, int s) {  // row r0 + i into stage s (= i mod stages)
     unsigned char* dst = data + s * stage_bytes;
     mbar_arrive_expect_tx(full + s, 2 * row_bytes);
     bulk_load_1d(dst, x + (r0 + i) * n, row_bytes, full + s);
     bulk_load_1d(dst + row_bytes, gy + (r0 + i) * n, row_bytes, full + s);
   };
   if (t == 0) {
-    for (size_t i = 0; i < count && i < static_cast<size_t>(stages); ++i) issue(i);
+    for (size_t i = 0; i < count && i < static_cast<size_t>(stages); ++i) issue(i, static_cast<int>(i));
   }
 
   Pack<T> pgain[PPT];
@@ -371,9 +373,9 @@ __global__ void __launch_bounds__(STG_THREADS) rmsnorm_rev_staged_kernel(
     for (int k = 0; k < PN; ++k) acc[u][k] = A(0);
   }
   const A inv_n = A(1) / static_cast<A>(n);
+  int s = 0;            // stage of row i
+  uint32_t parity = 0;  // phase of that stage's barrier
   for (size_t i = 0; i < count; ++i) {
-    const int s = static_cast<int>(i % stages);
-    const uint32_t parity = static_cast<uint32_t>((i / stages) & 1);
     if (!mbar_wait(full + s, parity, status)) break;  // every thread waits on the same phase
     const size_t row = r0 + i;
     const unsigned char* sx = data + s * stage_bytes;
@@ -390,7 +392,8 @@ __global__ void __launch_bounds__(STG_THREADS) rmsnorm_rev_staged_kernel(
     // that every thread has copied stage s to registers; the refill is issued
     // right after the row is finished.
     rmsnorm_rev_row<T, GROUP, PPT, FULL, BLEND>(px, pg, pgain, acc, rstd_in, eps, inv_n, alpha, gx + row * n, row, t, nv, red);
-    if (t == 0 && i + stages < count) issue(i + stages);
+    if (t == 0 && i + stages < count) issue(i + stages, s);
+    if (++s == stages) { s = 0; parity ^= 1u; }
   }
   A* pr = partial + static_cast<size_t>(blockIdx.x) * n;
 #pragma unroll
@@ -578,24 +581,27 @@ struct RowPlan {
   bool full;
 };
 
+// Up to 4 packs per thread.  Measured on B200 at n = 4096: for r16 rows, 128
+// threads x 4 packs beat 256 threads x 2 packs (fewer barrier participants,
+// more independent loads per thread).
 template <typename T>
 RowPlan plan_rows(size_t n, bool aligned) {
   constexpr int PN = Pack<T>::N;
+  constexpr int P = 4;
   RowPlan p{true, GEN_THREADS, 0, GEN_THREADS, 1, false};
   if (!aligned || n % PN != 0 || n == 0) return p;
   const size_t nv = n / PN;
   int group;
-  if (nv <= 32 * 4) group = 32;
-  else if (nv <= 128 * 4) group = 128;
-  else if (nv <= 256 * 4) group = 256;
-  else if (nv <= 512 * 4) group = 512;
+  if (nv <= 32 * P) group = 32;
+  else if (nv <= 128 * P) group = 128;
+  else if (nv <= 256 * P) group = 256;
+  else if (nv <= 512 * P) group = 512;
+  else if (nv <= 1024 * P) group = 1024;
   else return p;
   const size_t need = (nv + group - 1) / group;
   p.generic = false;
   p.group = group;
   p.ppt = need <= 1 ? 1 : (need <= 2 ? 2 : 4);
-  if (group >= 256) p.ppt = 4;
-  if (group == 128 && p.ppt == 1) p.ppt = 2;
   p.threads = group < 128 ? 128 : group;
   p.rows = p.threads / group;
   p.full = nv == static_cast<size_t>(p.group) * p.ppt;
@@ -618,15 +624,20 @@ inline size_t row_grid(const RowPlan& p, size_t m, int sm_count, int threads_per
   return grid;
 }
 
+// (group, packs per thread) pairs plan_rows can produce.
+#define MP_ROW_DISPATCH_G(PLAN, CALL, F, G)                                   \
+  do {                                                                        \
+    if ((PLAN).ppt == 1) { CALL(G, 1, F); }                                   \
+    else if ((PLAN).ppt == 2) { CALL(G, 2, F); }                              \
+    else { CALL(G, 4, F); }                                                   \
+  } while (0)
 #define MP_ROW_DISPATCH_F(PLAN, CALL, F)                                      \
   do {                                                                        \
-    if ((PLAN).group == 32 && (PLAN).ppt == 1) { CALL(32, 1, F); }            \
-    else if ((PLAN).group == 32 && (PLAN).ppt == 2) { CALL(32, 2, F); }       \
-    else if ((PLAN).group == 32) { CALL(32, 4, F); }                          \
-    else if ((PLAN).group == 128 && (PLAN).ppt == 2) { CALL(128, 2, F); }     \
-    else if ((PLAN).group == 128) { CALL(128, 4, F); }                        \
-    else if ((PLAN).group == 256) { CALL(256, 4, F); }                        \
-    else { CALL(512, 4, F); }                                                 \
+    if ((PLAN).group == 32) MP_ROW_DISPATCH_G(PLAN, CALL, F, 32);             \
+    else if ((PLAN).group == 128) MP_ROW_DISPATCH_G(PLAN, CALL, F, 128);      \
+    else if ((PLAN).group == 256) MP_ROW_DISPATCH_G(PLAN, CALL, F, 256);      \
+    else if ((PLAN).group == 512) MP_ROW_DISPATCH_G(PLAN, CALL, F, 512);      \
+    else MP_ROW_DISPATCH_G(PLAN, CALL, F, 1024);                              \
   } while (0)
 // `full`: the row has exactly group*ppt packs, the kernel drops its bounds guards
 #define MP_ROW_DISPATCH(PLAN, CALL)                                           \
@@ -658,18 +669,20 @@ StagedPlan plan_staged(size_t n, bool aligned) {
   const size_t nv = n / PN;
   if (nv < 128 || nv > static_cast<size_t>(STG_THREADS) * 4) return p;
   const size_t stage_bytes = 2 * n * sizeof(T);
-  static size_t budget_kb = 0;  // shared memory per CTA for the ring (MP_RMS_STAGE_KB overrides)
-  if (budget_kb == 0) {
-    const char* e = getenv("MP_RMS_STAGE_KB");
-    const long v = e ? strtol(e, nullptr, 10) : 0;
-    budget_kb = v > 0 ? static_cast<size_t>(v) : 100;
+  const size_t need = (nv + STG_THREADS - 1) / STG_THREADS;
+  const int ppt = need <= 1 ? 1 : (need <= 2 ? 2 : 4);
+  // ring size: ~68 KB when three CTAs share an SM, ~100 KB when two do
+  const int occ = ppt == 1 ? StgOcc<T, 1>::value : (ppt == 2 ? StgOcc<T, 2>::value : StgOcc<T, 4>::value);
+  size_t budget_kb = occ >= 3 ? 68 : 100;
+  if (const char* e = getenv("MP_RMS_STAGE_KB")) {
+    const long v = strtol(e, nullptr, 10);
+    if (v > 0) budget_kb = static_cast<size_t>(v);
   }
   size_t stages = (budget_kb * 1024) / stage_bytes;
   if (stages > 8) stages = 8;
   if (stages < 2) return p;
-  const size_t need = (nv + STG_THREADS - 1) / STG_THREADS;
   p.ok = true;
-  p.ppt = need <= 1 ? 1 : (need <= 2 ? 2 : 4);
+  p.ppt = ppt;
   p.stages = static_cast<int>(stages);
   p.smem_bytes = 128 + stages * stage_bytes;
   p.full = nv == static_cast<size_t>(STG_THREADS) * p.ppt;

@@ -74,3 +74,35 @@ def launch(name: str, dtype, *args):
     conv = [_arg(a) for a in args[:-1]]
     ctx = args[-1].ctx if isinstance(args[-1], Stream) else args[-1]
     fn(*conv, ctx)
+
+
+class FusedChain:
+    """A JIT-compiled element-wise expression (include/mp_jit.h)."""
+
+    def __init__(self, expr: str, dtype):
+        self._lib = lib()
+        self.dtype = dtype
+        key = {"r16": 0, "r32": 1, "r64": 2}[suffix_of(dtype)]
+        self.handle = self._lib.mpJitCompile(expr.encode(), key)
+        if not self.handle:
+            raise ValueError(f"cannot compile expression {expr!r}")
+        n = self._lib.mpJitNumLeaves(self.handle)
+        self.leaves = [self._lib.mpJitLeafName(self.handle, i).decode() for i in range(n)]
+
+    def _ptrs(self, tensors):
+        arr = (C.c_void_p * len(tensors))(*[(t.data_ptr() if t is not None else 0) for t in tensors])
+        return arr
+
+    def forward(self, leaves, out, n, stream):
+        assert len(leaves) == len(self.leaves)
+        self._lib.mpJitForward(self.handle, self._ptrs(leaves), C.c_void_p(out.data_ptr()), n, stream.ctx)
+
+    def reverse(self, leaves, g_out, g_leaves, alpha, n, stream):
+        assert len(leaves) == len(self.leaves) == len(g_leaves)
+        self._lib.mpJitReverse(self.handle, self._ptrs(leaves), C.c_void_p(g_out.data_ptr() if g_out is not None else 0),
+                               self._ptrs(g_leaves), float(alpha), n, stream.ctx)
+
+    def close(self):
+        if self.handle:
+            self._lib.mpJitRelease(self.handle)
+            self.handle = None
