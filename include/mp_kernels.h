@@ -104,6 +104,19 @@ MP_DECL3(rmsnorm_ij_j, const void* x, const void* gain, double eps, void* y, voi
  * the per-CTA partial sums of ggain (deterministic two-stage reduction). */
 MP_DECL3(rmsnorm_ij_j_reverse, const void* x, const void* gain, const void* rstd, const void* gy, double eps, void* gx, void* ggain, double alpha, void* scratch, len_t m, len_t n, StreamContext stream)
 MP_EXTERN_C len_t mpRmsnormReverseScratchBytes(len_t m, len_t n, StreamContext stream);
+/* No counterpart in the reference.  RMSNorm reverse (r32) for callers that are
+ * not allowed to allocate device memory (a plug-in inside a runtime that owns
+ * the whole device through its own pool, a loop where an allocation would stall
+ * the device): same arguments and results as launch_rmsnorm_ij_j_reverse_r32
+ * without `scratch`.  The partial sums live in a fixed array inside the library
+ * (MP_RMSNORM_STATIC_SCRATCH_BYTES per GPU that loads it, held until exit); the
+ * call allocates nothing.  Returns 0, or MP_STATUS_BAD_ARGUMENT with a message
+ * on stderr when one row of partials plus the fold rows does not fit (rows
+ * longer than about 100k columns).  The first call on a device looks up the
+ * array's device address and should come before any stream capture.  Calls
+ * share the array: keep them stream-ordered, overlapping calls race. */
+#define MP_RMSNORM_STATIC_SCRATCH_BYTES (8u << 20)
+MP_EXTERN_C int launch_rmsnorm_ij_j_reverse_static_r32(const void* x, const void* gain, const void* rstd, const void* gy, double eps, void* gx, void* ggain, double alpha, len_t m, len_t n, StreamContext stream);
 
 /* w -= rate * clip(g, clip_lo, clip_hi); argument set of optimizer.zig:170-178 */
 MP_DECL3(sgd, void* w, const void* g, double rate, double clip_lo, double clip_hi, len_t n, StreamContext stream)

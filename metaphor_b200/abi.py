@@ -81,6 +81,7 @@ UTILS = {
     "mpHostAlloc": (P, [L]),
     "mpHostFree": (None, [P]),
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
+    "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),
     # include/mp_jit.h
     "mpJitCompile": (P, [C.c_char_p, U32]),
     "mpJitRelease": (None, [P]),

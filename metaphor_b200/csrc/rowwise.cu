@@ -12,6 +12,7 @@
 #include "mp_async.cuh"
 
 #include <cfloat>
+#include <mutex>
 
 namespace {
 
@@ -862,3 +863,118 @@ MP_STAMP3(softmax_ij_j, (const void* src, void* dst, len_t m, len_t n, StreamCon
 MP_STAMP3(softmax_ij_j_reverse, (const void* y, const void* gy, void* gx, double alpha, len_t m, len_t n, StreamContext ctx), (y, gy, gx, alpha, m, n, ctx))
 MP_STAMP3(rmsnorm_ij_j, (const void* x, const void* gain, double eps, void* y, void* rstd, len_t m, len_t n, StreamContext ctx), (x, gain, eps, y, rstd, m, n, ctx))
 MP_STAMP3(rmsnorm_ij_j_reverse, (const void* x, const void* gain, const void* rstd, const void* gy, double eps, void* gx, void* ggain, double alpha, void* scratch, len_t m, len_t n, StreamContext ctx), (x, gain, rstd, gy, eps, gx, ggain, alpha, scratch, m, n, ctx))
+
+// ---------------------------------------------------------------------------
+// RMSNorm reverse (r32) for callers that may not allocate device memory.
+//
+// Who needs it: a plug-in running inside a host runtime that has handed the
+// whole device to its own memory pool and forbids cudaMalloc, or a
+// latency-critical loop in which an allocation would synchronise the device.
+// Such a caller cannot provide the gain-gradient scratch that
+// launch_rmsnorm_ij_j_reverse_r32 asks for, so this variant keeps the scratch in
+// a fixed array that is part of the library image: every GPU that loads the
+// library holds MP_RMSNORM_STATIC_SCRATCH_BYTES (8 MiB) of it until the process
+// exits.  Nothing here calls cudaMalloc, cudaFree or any allocating routine.
+//
+// The array's name is only a host-side stand-in for the device object, not a
+// device address; the address is fetched once per device with
+// cudaGetSymbolAddress (with that device current) and passed to the kernels.
+// The first call on a device performs that look-up, so it should be made
+// before the stream is put into capture mode.
+//
+// All calls share the one array and it keeps whatever the previous call left
+// there.  Nothing in it has to start at zero: every partial row a launch reads
+// is written earlier in the same launch sequence.  Two calls that overlap on
+// the GPU (different streams) would race on it - keep calls stream-ordered.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_rmsnorm_static_scratch[MP_RMSNORM_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_ptr[64] = {nullptr};
+
+// Device address of the static scratch on the current device (looked up once).
+void* static_scratch_address() {
+  int device = 0;
+  MP_CUDA_CHECK(cudaGetDevice(&device));
+  if (device < 0 || device >= 64) MP_FATAL("device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_ptr[device] == nullptr) {
+    void* ptr = nullptr;
+    MP_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_rmsnorm_static_scratch));
+    g_static_scratch_ptr[device] = ptr;
+  }
+  return g_static_scratch_ptr[device];
+}
+}  // namespace
+
+// Same arguments and results as launch_rmsnorm_ij_j_reverse_r32 minus the
+// scratch pointer.  Returns 0, or MP_STATUS_BAD_ARGUMENT (after printing why)
+// when the row length does not fit the fixed scratch: it must hold at least one
+// partial row per concurrently reduced row plus the 16 rows of the second fold
+// stage, i.e. n <= MP_RMSNORM_STATIC_SCRATCH_BYTES / (4 * 20) = 104857 columns
+// is always accepted.  Any number of rows is accepted (more rows per CTA are
+// used when the scratch would otherwise overflow).
+extern "C" int launch_rmsnorm_ij_j_reverse_static_r32(const void* x_, const void* gain_, const void* rstd_, const void* gy_,
+                                                      double eps, void* gx_, void* ggain_, double alpha, len_t m, len_t n,
+                                                      StreamContext ctx) {
+  using T = float;
+  using A = float;
+  if (n == 0) return 0;
+  const size_t cap_rows = MP_RMSNORM_STATIC_SCRATCH_BYTES / (n * sizeof(A));
+  const T* x = static_cast<const T*>(x_);
+  const T* gain = static_cast<const T*>(gain_);
+  const A* rstd = static_cast<const A*>(rstd_);
+  const T* gy = static_cast<const T*>(gy_);
+  T* gx = static_cast<T*>(gx_);
+  T* ggain = static_cast<T*>(ggain_);
+  const bool aligned = mp_aligned16(x) && mp_aligned16(gain) && mp_aligned16(gy) && mp_aligned16(gx);
+  const RowPlan p = plan_rows<T>(n, aligned);
+  if (cap_rows < static_cast<size_t>(FOLD_SPLITS) + p.rows) {
+    fprintf(stderr,
+            "launch_rmsnorm_ij_j_reverse_static_r32: n = %lu columns does not fit the %u-byte static scratch "
+            "(needs %lu bytes); use launch_rmsnorm_ij_j_reverse_r32 with caller scratch\n",
+            static_cast<unsigned long>(n), static_cast<unsigned>(MP_RMSNORM_STATIC_SCRATCH_BYTES),
+            static_cast<unsigned long>((FOLD_SPLITS + p.rows) * n * sizeof(A)));
+    return static_cast<int>(MP_STATUS_BAD_ARGUMENT);
+  }
+  A* partial = static_cast<A*>(static_scratch_address());
+  cudaStream_t st = mp_stream(ctx);
+  const A a = static_cast<A>(alpha);
+  const A e = static_cast<A>(eps);
+  const bool blend = alpha != 0.0;
+  size_t slots = 0;
+  if (m > 0) {
+    // CTAs (each owning p.rows partial rows) that fit beside the second-stage rows
+    const size_t max_grid = (cap_rows - FOLD_SPLITS) / p.rows;
+    const size_t groups = (m + p.rows - 1) / p.rows;
+    size_t rpc = 32;
+    if ((groups + rpc - 1) / rpc > max_grid) rpc = (groups + max_grid - 1) / max_grid;
+    const unsigned grid = static_cast<unsigned>((groups + rpc - 1) / rpc);
+    slots = static_cast<size_t>(grid) * p.rows;
+    if (p.generic) {
+      rmsnorm_rev_generic<T><<<grid, GEN_THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, blend, partial, m, n, rpc);
+    } else if (blend) {
+#define CALL(G, P, F) rmsnorm_rev_kernel<T, G, P, F, true><<<grid, RowCfg<G>::THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, partial, m, n, rpc)
+      MP_ROW_DISPATCH(p, CALL);
+#undef CALL
+    } else {
+#define CALL(G, P, F) rmsnorm_rev_kernel<T, G, P, F, false><<<grid, RowCfg<G>::THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, partial, m, n, rpc)
+      MP_ROW_DISPATCH(p, CALL);
+#undef CALL
+    }
+    MP_LAUNCH_CHECK();
+  }
+  constexpr int W = 16 / sizeof(A);
+  if (slots >= 128 && n % W == 0) {
+    A* partial2 = partial + slots * n;
+    const dim3 g1(static_cast<unsigned>((n + 32 * W - 1) / (32 * W)), FOLD_SPLITS);
+    rmsnorm_fold_stage1_kernel<A><<<g1, 256, 0, st>>>(partial, partial2, n, slots);
+    MP_LAUNCH_CHECK();
+    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial2, ggain, a, blend, n, FOLD_SPLITS);
+  } else {
+    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial, ggain, a, blend, n, slots);
+  }
+  MP_LAUNCH_CHECK();
+  return 0;
+}
