@@ -39,6 +39,12 @@ UNIT = "GB/s"
 # DRAM bytes per launch from ncu (dram__bytes_read.sum + dram__bytes_write.sum)
 # for the kernels of this step; filled from profiles/ (None = not captured).
 NCU_TRAFFIC_BYTES = {
+    # profiles/rmsnorm_reverse_m32768_n4096.md, captured at 32768 rows and scaled x2 (traffic is linear in rows)
+    "rmsnorm_rev_r32": 2 * (1_073_854_000 + 510_001_152),
+    "rmsnorm_rev_r16": 2 * (537_149_952 + 252_880_128),
+    # profiles/softmax_m32768_n4096.md
+    "softmax_rev_r32": 2 * (1_073_749_000 + 495_847_168),
+    "softmax_fwd_r16": 2 * (268_444_928 + 213_376_768),
 }
 
 
@@ -394,6 +400,60 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_profile_case(spec: str):
+    """`--profile-case OP:DTYPE:ROWS[:COLS]`: three launches of one kernel on a
+    small case, for an ncu capture (no timing, no JSON).  OP is one of
+    softmax_fwd, softmax_rev, rmsnorm_fwd, rmsnorm_rev (rows x cols matrix),
+    chain_fwd, chain_rev (ROWS = element count of selu((a+b)*(c+d))),
+    gemm (ROWS:COLS = M and N = K)."""
+    import torch
+    import metaphor_b200 as mp
+    parts = spec.split(":")
+    op, sfx, m = parts[0], parts[1], int(parts[2])
+    n = int(parts[3]) if len(parts) > 3 else N
+    dt = {"r16": torch.float16, "r32": torch.float32, "r64": torch.float64}[sfx]
+    torch.zeros(1, device="cuda")
+    s = mp.Stream()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    if op in ("chain_fwd", "chain_rev"):
+        leaves = [(torch.rand(m, generator=g, device="cuda") * 2 - 1).to(dt) for _ in range(4)]
+        out = torch.empty_like(leaves[0]); grads = [torch.empty_like(leaves[0]) for _ in range(4)]
+        chain = mp.FusedChain("selu((a+b)*(c+d))", dt)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            if op == "chain_fwd":
+                chain.forward(leaves, out, m, s)
+            else:
+                chain.reverse(leaves, None, grads, 0.0, m, s)
+    elif op == "gemm":
+        a = torch.randn(m, n, generator=g, device="cuda").to(dt); b = torch.randn(n, n, generator=g, device="cuda").to(dt)
+        c = torch.empty(m, n, device="cuda", dtype=dt)
+        torch.cuda.synchronize()
+        for _ in range(3):
+            mp.launch("inner_product_ij_jk_ik", dt, a, b, 1.0, c, 0.0, m, n, n, s)
+    else:
+        x = torch.randn(m, n, generator=g, device="cuda").to(dt); gy = torch.randn(m, n, generator=g, device="cuda").to(dt)
+        y = torch.empty_like(x); gx = torch.empty_like(x)
+        gain = torch.ones(n, device="cuda", dtype=dt); gg = torch.empty_like(gain)
+        scratch = torch.empty(mp.lib().mpRmsnormReverseScratchBytes(m, n, s.ctx), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            if op == "softmax_fwd":
+                mp.launch("softmax_ij_j", dt, x, y, m, n, s)
+            elif op == "softmax_rev":
+                mp.launch("softmax_ij_j_reverse", dt, x, gy, gx, 0.0, m, n, s)
+            elif op == "rmsnorm_fwd":
+                mp.launch("rmsnorm_ij_j", dt, x, gain, EPS, y, None, m, n, s)
+            elif op == "rmsnorm_rev":
+                mp.launch("rmsnorm_ij_j_reverse", dt, x, gain, None, gy, EPS, gx, gg, 0.0, scratch, m, n, s)
+            else:
+                raise SystemExit(f"unknown profile case {op}")
+    s.sync()
+    if s.status() != 0:
+        raise SystemExit("status word set")
+    s.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -402,7 +462,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10, help="upper bound on end-to-end steps (PCIe-bound)")
     ap.add_argument("--cpu-rows", type=int, default=32768, help="rows in the CPU baseline sample")
+    ap.add_argument("--profile-case", default=None, help="OP:DTYPE:ROWS[:COLS], three launches for an ncu capture")
     args = ap.parse_args()
+    if args.profile_case:
+        run_profile_case(args.profile_case)
+        return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
