@@ -136,6 +136,21 @@ MP_DECL3(inner_product_ji_jk_ik, const void* a_data, const void* b_data, const d
  * bias added in the GEMM epilogue. */
 MP_DECL3(linear_ij_jk_ik, const void* a_data, const void* b_data, const void* bias, const double alpha, void* c_data, const double beta, len_t m, len_t n, len_t k, StreamContext stream)
 
+/* Mamba-2 SSD chunked scan (no reference kernel; the op is named by the
+ * project's roadmap only).  Per batch b, head h (group g = h / (heads/ngroups)):
+ *   S_t = exp(dt_t*A_h) S_{t-1} + dt_t * B_t (x) x_t,   y_t = C_t^T S_t,   S_{-1} = 0.
+ * x, y: [batch, seqlen, heads, headdim] of T; dt: [batch, seqlen, heads] r32
+ * (already positive, e.g. after softplus); A: [heads] r32 (negative);
+ * B, C: [batch, seqlen, ngroups, dstate] of T.  fp32 accumulation.
+ * scratch: mpSsdScanScratchBytes(..., reverse) bytes owned by the caller.
+ * Implemented for r16 with dstate = 128, headdim 64 or 128, chunk 128 or 256,
+ * seqlen a multiple of chunk; the r32 / r64 entry points report "not implemented". */
+MP_DECL3(ssd_scan, const void* x, const void* dt, const void* A, const void* B, const void* C, void* y, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
+/* Reverse of the scan: given gy (shape of y) writes (overwrites) gx, gdt (r32),
+ * gA (r32, [heads]), gB, gC.  gB and gC are summed over the heads of a group. */
+MP_DECL3(ssd_scan_reverse, const void* x, const void* dt, const void* A, const void* B, const void* C, const void* gy, void* gx, void* gdt, void* gA, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
+MP_EXTERN_C len_t mpSsdScanScratchBytes(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, uint32_t reverse);
+
 /* Status word values returned by mpGetStatus (mp_device_utils.h). */
 #define MP_STATUS_OK             0u
 #define MP_STATUS_WAIT_TIMEOUT   1u  /* a bounded mbarrier wait gave up    */

@@ -59,6 +59,8 @@ LAUNCHERS = {
     "inner_product_ij_kj_ik": [P, P, D, P, D, L, L, L, CTX],
     "inner_product_ji_jk_ik": [P, P, D, P, D, L, L, L, CTX],
     "linear_ij_jk_ik": [P, P, P, D, P, D, L, L, L, CTX],
+    "ssd_scan": [P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
+    "ssd_scan_reverse": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
 }
 
 # name -> (restype, argtypes)
@@ -81,6 +83,7 @@ UTILS = {
     "mpHostAlloc": (P, [L]),
     "mpHostFree": (None, [P]),
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
+    "mpSsdScanScratchBytes": (L, [L, L, L, L, L, L, L, U32]),
     "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),
     # include/mp_jit.h
     "mpJitCompile": (P, [C.c_char_p, U32]),
