@@ -405,7 +405,7 @@ def run_profile_case(spec: str):
     small case, for an ncu capture (no timing, no JSON).  OP is one of
     softmax_fwd, softmax_rev, rmsnorm_fwd, rmsnorm_rev (rows x cols matrix),
     chain_fwd, chain_rev (ROWS = element count of selu((a+b)*(c+d))),
-    gemm (ROWS:COLS = M and N = K)."""
+    gemm (ROWS:COLS = M and N = K), ssd_fwd, ssd_rev (ROWS:COLS = batch and seqlen)."""
     import torch
     import metaphor_b200 as mp
     parts = spec.split(":")
@@ -425,6 +425,27 @@ def run_profile_case(spec: str):
                 chain.forward(leaves, out, m, s)
             else:
                 chain.reverse(leaves, None, grads, 0.0, m, s)
+    elif op in ("ssd_fwd", "ssd_rev"):
+        # ROWS = batch, COLS = seqlen; heads 32, headdim 64, d_state 128, 1 group, chunk 256
+        import math
+        nb, L, H, P, NS, G, Q = m, n, 32, 64, 128, 1, 256
+        x = torch.randn(nb, L, H, P, generator=g, device="cuda").half()
+        Bm = torch.randn(nb, L, G, NS, generator=g, device="cuda").half()
+        Cm = torch.randn(nb, L, G, NS, generator=g, device="cuda").half()
+        dtv = torch.nn.functional.softplus(torch.randn(nb, L, H, generator=g, device="cuda") - 4)
+        Av = -torch.exp(torch.rand(H, generator=g, device="cuda") * math.log(16))
+        gy = torch.randn(nb, L, H, P, generator=g, device="cuda").half()
+        y = torch.empty_like(x); gx = torch.empty_like(x); gdt = torch.empty_like(dtv); gA = torch.empty_like(Av)
+        gB = torch.empty_like(Bm); gC = torch.empty_like(Cm)
+        dims = (nb, L, H, P, NS, G, Q)
+        rev = op == "ssd_rev"
+        scr = torch.empty(mp.lib().mpSsdScanScratchBytes(*dims, 1 if rev else 0), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            if rev:
+                mp.launch("ssd_scan_reverse", torch.float16, x, dtv, Av, Bm, Cm, gy, gx, gdt, gA, gB, gC, scr, *dims, s)
+            else:
+                mp.launch("ssd_scan", torch.float16, x, dtv, Av, Bm, Cm, y, scr, *dims, s)
     elif op == "gemm":
         a = torch.randn(m, n, generator=g, device="cuda").to(dt); b = torch.randn(n, n, generator=g, device="cuda").to(dt)
         c = torch.empty(m, n, device="cuda", dtype=dt)

@@ -32,9 +32,8 @@
 namespace {
 
 constexpr int SSD_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: transform + epilogue
-constexpr int SSD_STAGES = 4;
+constexpr int SSD_MAX_STAGES = 4;
 constexpr int TILE_BYTES = 128 * 128;  // one operand tile: 128 rows x 128 B, or two 64x64 MN-major boxes
-constexpr int SSD_STAGE_BYTES = 2 * TILE_BYTES;
 constexpr int BOX_BYTES = 64 * 128;    // MN-major box: 64 k-rows x 64 elements
 enum { MODE_SCORES = 0, MODE_STATES = 1, MODE_OUTPUT = 2 };
 
@@ -48,6 +47,9 @@ struct SsdArgs {
   int state_t;            // states stored transposed: [dv x dk] (dk contiguous)
   const float* cum;       // [B, H, nc, Q] inclusive prefix sum of dt*A inside the chunk
   const float* dtt;       // [B, H, nc, Q] dt
+  int stages;             // pipeline depth (2..4)
+  int stage_bytes;        // A tile (16 KB) + the largest B tile of this launch
+  int tmem_cols;          // accumulator columns to allocate (power of two >= tile width)
   __half* g_out;          // SCORES: [(b, c, unit) * Q + i][Q]
   float* s_out;           // STATES: [(b, h, c)][128][d2]
   __half* o_out;          // OUTPUT: row b*L + t, column unit*dv + j (may be null)
@@ -158,20 +160,21 @@ __device__ __forceinline__ Item ssd_item(const SsdArgs& g, int it, int mt, int c
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_constant__ CUtensorMap map_a0,
+__global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_constant__ CUtensorMap map_a0,
                                                                 const __grid_constant__ CUtensorMap map_b0,
                                                                 const __grid_constant__ CUtensorMap map_a1,
                                                                 const __grid_constant__ CUtensorMap map_b1,
                                                                 const SsdArgs g) {
   extern __shared__ unsigned char ssd_smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(ssd_smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + SSD_STAGES * SSD_STAGE_BYTES);
-  uint64_t* ready = full + SSD_STAGES;
-  uint64_t* empty = ready + SSD_STAGES;
-  uint64_t* acc_full = empty + SSD_STAGES;
+  const int STAGES = g.stages, STAGE_BYTES = g.stage_bytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* ready = full + SSD_MAX_STAGES;
+  uint64_t* empty = ready + SSD_MAX_STAGES;
+  uint64_t* acc_full = empty + SSD_MAX_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float* s_cum = reinterpret_cast<float*>(smem + SSD_STAGES * SSD_STAGE_BYTES + 256);  // [nheads][Q]
+  float* s_cum = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + 256);  // [Q] of the head being transformed
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hpg = g.H / g.G;
 
@@ -195,23 +198,23 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
   if (MODE == MODE_SCORES) { head0 = g.scores_head ? unit : unit * hpg; nheads = 1; }
   else if (MODE == MODE_STATES) { head0 = unit; nheads = 1; }
   else { head0 = g.out_head ? unit : unit * hpg; nheads = g.out_head ? 1 : hpg; }
-  float* s_dt = s_cum + nheads * g.Q;
+  float* s_dt = s_cum + g.Q;
+  float* s_colf = s_dt + g.Q;   // 64 column factors of the k-block being transformed
   const int n_items = ssd_num_items<MODE>(g, mt, c, nheads);
   const int tile_n = MODE == MODE_SCORES ? 128 : (MODE == MODE_STATES ? (g.dk == 128 ? g.dv : g.dk) : g.dv);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < SSD_STAGES; ++s) { mbar_init(full + s, 1); mbar_init(ready + s, 128); mbar_init(empty + s, 1); }
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full + s, 1); mbar_init(ready + s, 128); mbar_init(empty + s, 1); }
     mbar_init(acc_full, 1);
     *abort = 0;
     mbar_fence_init();
   }
-  if (warp == 1) tmem_alloc(tmem_slot, 128);
-  if (MODE != MODE_SCORES) {
-    for (int i = threadIdx.x; i < nheads * g.Q; i += SSD_THREADS) {
-      const int hh = i / g.Q, t = i % g.Q;
-      const size_t o = (static_cast<size_t>(b) * g.H + head0 + hh) * g.L + c * g.Q + t;
-      s_cum[i] = g.cum[o];
-      s_dt[i] = g.dtt[o];
+  if (warp == 1) tmem_alloc(tmem_slot, g.tmem_cols);
+  if (MODE != MODE_SCORES) {   // factors of the first head; later heads are reloaded by the transform warps
+    for (int t = threadIdx.x; t < g.Q; t += SSD_THREADS) {
+      const size_t o = (static_cast<size_t>(b) * g.H + head0) * g.L + c * g.Q + t;
+      s_cum[t] = g.cum[o];
+      s_dt[t] = g.dtt[o];
     }
   }
   tcgen05_fence_before_sync();
@@ -229,7 +232,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
       for (int it = 0; it < n_items; ++it) {
         const Item w = ssd_item<MODE>(g, it, mt, c, head0);
         if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) break;
-        unsigned char* sa = smem + s * SSD_STAGE_BYTES;
+        unsigned char* sa = smem + s * STAGE_BYTES;
         unsigned char* sb = sa + TILE_BYTES;
         if (MODE == MODE_SCORES) {
           mbar_arrive_expect_tx(full + s, 2 * TILE_BYTES);
@@ -266,7 +269,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
             }
           }
         }
-        if (++s == SSD_STAGES) { s = 0; phase ^= 1u; }
+        if (++s == STAGES) { s = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
@@ -278,7 +281,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
         uint64_t* wait_on = MODE == MODE_SCORES ? (full + s) : (ready + s);
         if (!mbar_wait_abortable(wait_on, phase, g.status, abort)) { ok = false; break; }
         tcgen05_fence_after_sync();
-        const uint32_t sa = mp_smem_u32(smem + s * SSD_STAGE_BYTES), sb = sa + TILE_BYTES;
+        const uint32_t sa = mp_smem_u32(smem + s * STAGE_BYTES), sb = sa + TILE_BYTES;
         const bool a_mn = MODE == MODE_STATES;
         const bool b_mn = MODE == MODE_STATES || (MODE == MODE_OUTPUT && !(w.off && g.state_t));
         const uint32_t idesc = umma_instr_desc(UMMA_FMT_F16, a_mn ? 1u : 0u, b_mn ? 1u : 0u, 128, tile_n);
@@ -289,7 +292,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
           umma<false>(tmem_acc, ad, bd, idesc, (it | ks) != 0 ? 1u : 0u);
         }
         umma_commit(empty + s);
-        if (++s == SSD_STAGES) { s = 0; phase ^= 1u; }
+        if (++s == STAGES) { s = 0; phase ^= 1u; }
       }
       if (ok && n_items > 0) umma_commit(acc_full);
     }
@@ -298,13 +301,25 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
     const int et = threadIdx.x - 64;  // 0..127 = accumulator row
     if (MODE != MODE_SCORES) {
       int s = 0; uint32_t phase = 0;
+      int cur_head = head0;
       for (int it = 0; it < n_items; ++it) {
         const Item w = ssd_item<MODE>(g, it, mt, c, head0);
+        if (w.head != cur_head) {
+          // next head of the group: swap in its decay / dt factors (only these four warps read them)
+          named_bar_sync(1, 128);
+          for (int t = et; t < g.Q; t += 128) {
+            const size_t o = (static_cast<size_t>(b) * g.H + w.head) * g.L + c * g.Q + t;
+            s_cum[t] = g.cum[o];
+            s_dt[t] = g.dtt[o];
+          }
+          named_bar_sync(1, 128);
+          cur_head = w.head;
+        }
         if (!mbar_wait_abortable(full + s, phase, g.status, abort)) break;
-        unsigned char* sa = smem + s * SSD_STAGE_BYTES;
+        unsigned char* sa = smem + s * STAGE_BYTES;
         unsigned char* sb = sa + TILE_BYTES;
-        const float* cm = s_cum + (w.head - head0) * g.Q;
-        const float* dd = s_dt + (w.head - head0) * g.Q;
+        const float* cm = s_cum;
+        const float* dd = s_dt;
         if (MODE == MODE_STATES) {
           // scale k-row t of the B tile by w_t
           const float last = cm[g.Q - 1];
@@ -331,26 +346,57 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
           unsigned char* row = sa + et * 128;
           const float ci = cm[i];
           if (!w.off) {
-            const float ri = g.anti ? dd[i] : 1.f;
+            // F_ij = mask * exp(+-(cum_i - cum_j)) * (dt_j | dt_i) is split into a column factor
+            // shared by the CTA and a row factor per thread, both relative to a reference
+            // column of this k-block chosen so that the column factors never exceed one:
+            //   causal: ref = last column,  colf_j = exp(cum_ref - cum_j) dt_j,  rowf_i = exp(cum_i - cum_ref)
+            //   anti  : ref = first column, colf_j = exp(cum_j - cum_ref),       rowf_i = exp(cum_ref - cum_i) dt_i
+            // (one exp per column and per row instead of one per element).  Rows inside the
+            // k-block can have a positive row exponent; beyond 60 they take the direct form.
+            const int jref = g.anti ? w.kb * 64 : w.kb * 64 + 63;
+            const float cref = cm[jref];
+            named_bar_sync(2, 128);   // previous item's readers of s_colf are done
+            if (et < 64) {
+              const int j = w.kb * 64 + et;
+              s_colf[et] = g.anti ? ssd_exp(cm[j] - cref) : ssd_exp(cref - cm[j]) * dd[j];
+            }
+            named_bar_sync(2, 128);
+            const float rarg = g.anti ? cref - ci : ci - cref;
+            const bool direct = rarg > 60.f;
+            const float rowf = direct ? 0.f : (g.anti ? ssd_exp(rarg) * dd[i] : ssd_exp(rarg));
+            const bool need_mask = g.anti ? (w.kb * 64 < mt * 128 + 128 && w.kb * 64 + 63 >= mt * 128 && w.kb * 64 < i)
+                                          : (w.kb * 64 + 63 > i);
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const int cp = (q + et) & 7;
-              const int j0 = w.kb * 64 + ((cp ^ (et & 7)) << 3);
+              const int jl = (cp ^ (et & 7)) << 3;      // first column of this chunk inside the k-block
+              const int j0 = w.kb * 64 + jl;
               uint4 v = *reinterpret_cast<uint4*>(row + cp * 16);
               __half2* h2 = reinterpret_cast<__half2*>(&v);
+              const float4 c0 = *reinterpret_cast<const float4*>(s_colf + jl);
+              const float4 c1 = *reinterpret_cast<const float4*>(s_colf + jl + 4);
+              float cf[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+              if (direct) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int j = j0 + e;
+                  cf[e] = g.anti ? ssd_exp(cm[j] - ci) * dd[i] : ssd_exp(ci - cm[j]) * dd[j];
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) cf[e] *= rowf;
+              }
+              if (need_mask) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const int j = j0 + e;
+                  if (g.anti ? (j < i) : (j > i)) cf[e] = 0.f;
+                }
+              }
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
-                const int ja = j0 + 2 * e, jb = ja + 1;
-                float2 f = __half22float2(h2[e]);
-                float fa, fb;
-                if (!g.anti) {
-                  fa = ja <= i ? ssd_exp(ci - cm[ja]) * dd[ja] : 0.f;
-                  fb = jb <= i ? ssd_exp(ci - cm[jb]) * dd[jb] : 0.f;
-                } else {
-                  fa = ja >= i ? ssd_exp(cm[ja] - ci) * ri : 0.f;
-                  fb = jb >= i ? ssd_exp(cm[jb] - ci) * ri : 0.f;
-                }
-                h2[e] = __floats2half2_rn(f.x * fa, f.y * fb);
+                const float2 f = __half22float2(h2[e]);
+                h2[e] = __floats2half2_rn(f.x * cf[2 * e], f.y * cf[2 * e + 1]);
               }
               *reinterpret_cast<uint4*>(row + cp * 16) = v;
             }
@@ -372,7 +418,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
         }
         fence_proxy_async_smem();
         mbar_arrive(ready + s);
-        if (++s == SSD_STAGES) { s = 0; phase ^= 1u; }
+        if (++s == STAGES) { s = 0; phase ^= 1u; }
       }
     }
     const bool acc_ready = n_items > 0 ? mbar_wait_abortable(acc_full, 0, g.status, abort) : true;
@@ -429,7 +475,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 1) ssd_mma_kernel(const __grid_co
   }
   tcgen05_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_acc, 128);
+  if (warp == 1) tmem_dealloc(tmem_acc, g.tmem_cols);
 }
 
 // ---------------------------------------------------------------------------
@@ -567,7 +613,6 @@ void ssd_launch(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap&
 
 // One instance of the chunked operator (scores -> states -> scan -> output).
 void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32_t* status, cudaStream_t st) {
-  const int hpg = d.H / d.G;
   SsdArgs g;
   g.B = d.B; g.L = d.L; g.H = d.H; g.G = d.G; g.Q = d.Q; g.nc = d.nc;
   g.dk = r.dk; g.dv = r.dv; g.anti = r.anti;
@@ -583,7 +628,14 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
   const size_t qcols = static_cast<size_t>(r.q_head ? d.H : d.G) * r.dk;
   const size_t kcols = static_cast<size_t>(r.k_head ? d.H : d.G) * r.dk;
   const size_t vcols = static_cast<size_t>(r.v_head ? d.H : d.G) * r.dv;
-  const size_t base_smem = SSD_STAGES * SSD_STAGE_BYTES + 1024 + 256;
+  // Shared memory per CTA is kept near 50-70 KB so that three or four CTAs share an SM: every CTA has
+  // only a handful of k-blocks, so latency is hidden across CTAs rather than by a deep pipeline.
+  auto configure = [&](int b_tile_bytes, int tile_cols) {
+    g.stage_bytes = TILE_BYTES + b_tile_bytes;
+    g.stages = 2;
+    g.tmem_cols = tile_cols <= 32 ? 32 : (tile_cols <= 64 ? 64 : 128);
+    return static_cast<size_t>(g.stages) * g.stage_bytes + 1024 + 256 + 2 * d.Q * 4 + 64 * 4;
+  };
   const int sunits = r.scores_head ? d.H : d.G;
   const int d2 = r.dk == 128 ? r.dv : r.dk;   // columns of a stored state block ([128][d2])
 
@@ -591,13 +643,15 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
   {
     const CUtensorMap mq = ssd_map(r.q, rows, qcols, 128), mk = ssd_map(r.k, rows, kcols, 128);
     const dim3 grid(d.Q / 128, d.Q / 128, d.B * d.nc * sunits);
-    ssd_launch<MODE_SCORES>(mq, mk, mq, mk, g, grid, base_smem, st);
+    const size_t smem = configure(TILE_BYTES, 128);
+    ssd_launch<MODE_SCORES>(mq, mk, mq, mk, g, grid, smem, st);
   }
   // chunk states: MN-major 64x64 boxes of k and v
   {
     const CUtensorMap mk = ssd_map(r.k, rows, kcols, 64), mv = ssd_map(r.v, rows, vcols, 64);
     const dim3 grid(1, 1, d.B * d.nc * d.H);
-    ssd_launch<MODE_STATES>(mk, mv, mk, mv, g, grid, base_smem + 2 * d.Q * 4, st);
+    const size_t smem = configure((d2 / 64) * BOX_BYTES, d2);
+    ssd_launch<MODE_STATES>(mk, mv, mk, mv, g, grid, smem, st);
   }
   {
     const int E = 128 * d2;
@@ -613,9 +667,9 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
     const size_t srows = static_cast<size_t>(d.B) * d.H * d.nc * 128;
     const CUtensorMap mh = g.state_t ? ssd_map(sc.hs, srows, d2, 128) : ssd_map(sc.hs, srows, d2, 64);
     const int units = r.out_head ? d.H : d.G;
-    const int nheads = r.out_head ? 1 : hpg;
     const dim3 grid(1, d.Q / 128, d.B * d.nc * units);
-    ssd_launch<MODE_OUTPUT>(ms, mv, mq, mh, g, grid, base_smem + static_cast<size_t>(nheads) * 2 * d.Q * 4, st);
+    const size_t smem = configure(g.state_t ? TILE_BYTES : (r.dv / 64) * BOX_BYTES, r.dv);
+    ssd_launch<MODE_OUTPUT>(ms, mv, mq, mh, g, grid, smem, st);
   }
 }
 
@@ -624,7 +678,6 @@ void ssd_check_dims(const SsdDims& d) {
   if (d.Q != 128 && d.Q != 256) MP_FATAL("ssd_scan: chunk must be 128 or 256 (got %d)", d.Q);
   if (d.L % d.Q != 0) MP_FATAL("ssd_scan: seqlen %d is not a multiple of the chunk %d", d.L, d.Q);
   if (d.G <= 0 || d.H % d.G != 0) MP_FATAL("ssd_scan: heads %d not divisible by groups %d", d.H, d.G);
-  if ((d.H / d.G) * d.Q * 8 > 64 * 1024) MP_FATAL("ssd_scan: more than %d heads per group at chunk %d is not supported", 64 * 1024 / (d.Q * 8), d.Q);
 }
 
 SsdDims ssd_dims(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk) {
