@@ -85,6 +85,12 @@ UTILS = {
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
     "mpSsdScanScratchBytes": (L, [L, L, L, L, L, L, L, U32]),
     "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),
+    # include/mp_comm.h
+    "mpCommGetUniqueId": (None, [P]),
+    "mpCommInit": (P, [P, U32, U32]),
+    "mpCommDestroy": (None, [P]),
+    "mpCommWorldSize": (U32, [P]),
+    "mpAllReduceSum": (None, [P, P, L, U32, CTX]),
     # include/mp_jit.h
     "mpJitCompile": (P, [C.c_char_p, U32]),
     "mpJitRelease": (None, [P]),
