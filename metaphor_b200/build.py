@@ -73,7 +73,21 @@ def build(force: bool = False, verbose: bool = True) -> Path:
                        check=True)
         if verbose:
             print(f"built {so}")
+    build_host()
     return so
+
+
+def build_host() -> Path:
+    """C++ mirror of the reference's Zig host layer (host/metaphor.{hpp,cpp}) ->
+    lib/libmp_host.so, linked against libmp_kernels.so in the same directory."""
+    src = ROOT / "host" / "metaphor.cpp"
+    hdr = ROOT / "host" / "metaphor.hpp"
+    out = LIB / "libmp_host.so"
+    newest = max(src.stat().st_mtime, hdr.stat().st_mtime, (LIB / "libmp_kernels.so").stat().st_mtime)
+    if not out.exists() or out.stat().st_mtime < newest:
+        subprocess.run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-o", str(out), str(src),
+                        "-L" + str(LIB), "-lmp_kernels", "-Wl,-rpath,$ORIGIN"], check=True)
+    return out
 
 
 if __name__ == "__main__":

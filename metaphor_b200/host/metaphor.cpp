@@ -1,0 +1,606 @@
+// Implementation of the C++ host mirror (see metaphor.hpp).  Every device
+// action goes through the extern "C" boundary of include/*.h.
+#include "metaphor.hpp"
+
+#include <cassert>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <limits>
+#include <set>
+
+namespace mp {
+
+// 3-entry launcher arrays indexed by the dtype key (file_gen.zig:298-328, root.zig:36-43)
+#define MP_KERNELS(name) {launch_##name##_r16, launch_##name##_r32, launch_##name##_r64}
+namespace kernels {
+using Bin = void (*)(const void*, const void*, void*, len_t, StreamContext);
+using Un = void (*)(const void*, void*, len_t, StreamContext);
+using Sca = void (*)(const void*, double, void*, len_t, StreamContext);
+using UnRev = void (*)(const void*, void*, const void*, len_t, StreamContext);
+using Blend2 = void (*)(const void*, void*, double, len_t, len_t, StreamContext);
+using Gemm = void (*)(const void*, const void*, const double, void*, const double, len_t, len_t, len_t, StreamContext);
+static const Bin addition[3] = MP_KERNELS(addition), subtraction[3] = MP_KERNELS(subtraction),
+                 hadamard[3] = MP_KERNELS(hadamard), hadamard_reverse[3] = MP_KERNELS(hadamard_reverse);
+static const Un negate[3] = MP_KERNELS(negate), relu[3] = MP_KERNELS(relu), selu[3] = MP_KERNELS(selu), copy[3] = MP_KERNELS(copy);
+static const Sca translate[3] = MP_KERNELS(translate), dilate[3] = MP_KERNELS(dilate), dilate_reverse[3] = MP_KERNELS(dilate_reverse);
+static const UnRev relu_reverse[3] = MP_KERNELS(relu_reverse), selu_reverse[3] = MP_KERNELS(selu_reverse);
+static const Blend2 reduce_ij_i[3] = MP_KERNELS(reduce_ij_i), reduce_ij_j[3] = MP_KERNELS(reduce_ij_j),
+                    broadcast_i_ij[3] = MP_KERNELS(broadcast_i_ij), broadcast_j_ij[3] = MP_KERNELS(broadcast_j_ij),
+                    permutate_ij_ji[3] = MP_KERNELS(permutate_ij_ji);
+static const Gemm ip_ij_jk_ik[3] = MP_KERNELS(inner_product_ij_jk_ik), ip_ij_kj_ik[3] = MP_KERNELS(inner_product_ij_kj_ik),
+                  ip_ji_jk_ik[3] = MP_KERNELS(inner_product_ji_jk_ik);
+static void (*const fill[3])(void*, double, len_t, StreamContext) = MP_KERNELS(fill);
+static void (*const sequence[3])(void*, double, double, len_t, StreamContext) = MP_KERNELS(sequence);
+static void (*const linear[3])(const void*, const void*, const void*, const double, void*, const double, len_t, len_t, len_t,
+                               StreamContext) = MP_KERNELS(linear_ij_jk_ik);
+static void (*const softmax[3])(const void*, void*, len_t, len_t, StreamContext) = MP_KERNELS(softmax_ij_j);
+static void (*const softmax_reverse[3])(const void*, const void*, void*, double, len_t, len_t, StreamContext) = MP_KERNELS(softmax_ij_j_reverse);
+static void (*const rmsnorm[3])(const void*, const void*, double, void*, void*, len_t, len_t, StreamContext) = MP_KERNELS(rmsnorm_ij_j);
+static void (*const rmsnorm_reverse[3])(const void*, const void*, const void*, const void*, double, void*, void*, double, void*,
+                                        len_t, len_t, StreamContext) = MP_KERNELS(rmsnorm_ij_j_reverse);
+static void (*const sgd[3])(void*, const void*, double, double, double, len_t, StreamContext) = MP_KERNELS(sgd);
+static void (*const adam[3])(void*, const void*, void*, void*, double, double, double, double, double, len_t, len_t,
+                             StreamContext) = MP_KERNELS(adam);
+}  // namespace kernels
+
+static inline int dkey(Tensor t) { return static_cast<int>(t.dtype()); }   // graph.zig:205-209
+
+[[noreturn]] static void panic(const char* msg) {
+  std::printf("metaphor: %s\n", msg);
+  std::fflush(stdout);
+  std::exit(EXIT_FAILURE);
+}
+
+// ------------------------------ device / stream -------------------------------
+namespace device {
+void init(unsigned n) { mpInitDevice(n); }
+void sync() { mpDeviceSynchronize(); }
+void check() { mpCheckLastError(); }
+size_t total_memory(unsigned n) { return mpDeviceTotalMemory(n); }
+}
+namespace stream {
+Stream init() { return Stream{mpInitStream()}; }
+void deinit(Stream s) { mpDeinitStream(s.context); }
+void sync(Stream s) { mpStreamSynchronize(s.context); }
+}
+
+// ------------------------------ allocator -------------------------------------
+void* TensorAllocator::alloc(size_t bytes, StreamContext ctx) {
+  auto it = free_.find(bytes);
+  if (it != free_.end() && !it->second.empty()) {
+    void* p = it->second.back();
+    it->second.pop_back();
+    return p;
+  }
+  void* p = mpMemAlloc(bytes, ctx);
+  if (p == nullptr) panic("device allocation failed");
+  return p;
+}
+void TensorAllocator::release(void* p, size_t bytes) { free_[bytes].push_back(p); }
+void TensorAllocator::drain(StreamContext ctx) {
+  for (auto& kv : free_)
+    for (void* p : kv.second) mpMemFree(p, ctx);
+  free_.clear();
+}
+size_t TensorAllocator::cached_blocks() const {
+  size_t n = 0;
+  for (const auto& kv : free_) n += kv.second.size();
+  return n;
+}
+
+// ------------------------------ tensor handle ---------------------------------
+void* Tensor::data_ptr() const { return ptr->block_of(cls).data[idx]; }
+void* Tensor::grad_ptr() const { return ptr->block_of(cls).grad[idx]; }
+const std::vector<size_t>& Tensor::sizes() const { return ptr->block_of(cls).sizes[idx]; }
+size_t Tensor::len() const { return ptr->block_of(cls).len[idx]; }
+Dtype Tensor::dtype() const { return ptr->block_of(cls).dtype[idx]; }
+StreamContext Tensor::context() const { return ptr->stream.context; }
+void Tensor::detach() const {
+  assert(cls == Class::hid);
+  ptr->node_block.attached[idx] = false;
+}
+void Tensor::free() const { ptr->free_tensor(*this); }
+
+void Tensor::reverse(ReverseCleanup cleanup) const {
+  if (grad_ptr() == nullptr) {
+    // no loss was applied: the derivative with respect to self is 1 (graph.zig:112-117)
+    enable_gradient(*this);
+    kernels::fill[dkey(*this)](grad_ptr(), 1.0, len(), context());
+  }
+  if (cls != Class::hid) return;
+  ptr->reverse(idx, cleanup);
+}
+
+static std::vector<double> to_host(const void* dptr, size_t n, Dtype dt, StreamContext ctx) {
+  std::vector<double> out(n);
+  if (n == 0 || dptr == nullptr) return out;
+  std::vector<unsigned char> raw(n * dtype_size(dt));
+  mpMemcpyDtoH(raw.data(), dptr, raw.size(), ctx);
+  mpStreamSynchronize(ctx);   // the reference reads without waiting (utils.zig:182-218)
+  for (size_t i = 0; i < n; ++i) {
+    if (dt == Dtype::r32) { float f; std::memcpy(&f, raw.data() + 4 * i, 4); out[i] = f; }
+    else if (dt == Dtype::r64) { double d; std::memcpy(&d, raw.data() + 8 * i, 8); out[i] = d; }
+    else {
+      uint16_t h; std::memcpy(&h, raw.data() + 2 * i, 2);
+      const int s = h >> 15, e = (h >> 10) & 31, m = h & 1023;
+      double v = e == 0 ? std::ldexp(static_cast<double>(m), -24)
+                        : (e == 31 ? (m ? std::numeric_limits<double>::quiet_NaN() : std::numeric_limits<double>::infinity())
+                                   : std::ldexp(static_cast<double>(m + 1024), e - 25));
+      out[i] = s ? -v : v;
+    }
+  }
+  return out;
+}
+std::vector<double> Tensor::native() const { return to_host(data_ptr(), len(), dtype(), context()); }
+std::vector<double> Tensor::native_grad() const { return to_host(grad_ptr(), grad_ptr() ? len() : 0, dtype(), context()); }
+
+// ------------------------------ graph ------------------------------------------
+Graph* Graph::init(GraphConfig cfg) {
+  Graph* g = new Graph();
+  g->mode = cfg.mode;
+  g->stream = cfg.stream;
+  return g;
+}
+
+void Graph::deinit() {
+  reset(ResetGroup::node, ResetComponent::all);
+  reset(ResetGroup::leaf, ResetComponent::all);
+  if (scratch_ != nullptr) mpMemFree(scratch_, stream.context);
+  tensor_allocator.drain(stream.context);
+  mpStreamSynchronize(stream.context);
+  delete this;
+}
+
+Tensor Graph::tensor(const TensorConfig& cfg) {
+  Block& b = block_of(cfg.cls);
+  size_t n = 1;
+  for (size_t s : cfg.sizes) n *= s;
+  if (cfg.sizes.empty()) n = 0;
+  b.data.push_back(n ? tensor_allocator.alloc(n * dtype_size(cfg.dtype), stream.context) : nullptr);
+  b.grad.push_back(nullptr);
+  b.len.push_back(n);
+  b.sizes.push_back(cfg.sizes);
+  b.dtype.push_back(cfg.dtype);
+  b.cls.push_back(cfg.cls);
+  if (cfg.cls == Class::hid) {
+    b.deps.push_back(0);
+    b.attached.push_back(true);
+    b.has_op.push_back(false);
+    b.op_reverse.push_back(nullptr);
+    b.op_args.emplace_back();
+  }
+  return Tensor{this, cfg.cls, b.data.size() - 1};
+}
+
+void Graph::free_gradient(Tensor t) {
+  Block& b = block_of(t.cls);
+  if (b.grad[t.idx] != nullptr) {
+    tensor_allocator.release(b.grad[t.idx], b.len[t.idx] * dtype_size(b.dtype[t.idx]));
+    b.grad[t.idx] = nullptr;
+  }
+}
+
+void Graph::free_tensor(Tensor t) {
+  Block& b = block_of(t.cls);
+  free_gradient(t);
+  if (b.data[t.idx] != nullptr) {
+    tensor_allocator.release(b.data[t.idx], b.len[t.idx] * dtype_size(b.dtype[t.idx]));
+    b.data[t.idx] = nullptr;
+  }
+  b.len[t.idx] = 0;
+}
+
+void Graph::reset(ResetGroup group, ResetComponent component) {
+  Block& b = group == ResetGroup::node ? node_block : leaf_block;
+  const Class c = group == ResetGroup::node ? Class::hid : Class::inp;
+  if (component == ResetComponent::grd) {
+    for (size_t i = 0; i < b.grad.size(); ++i) {
+      free_gradient(Tensor{this, c, i});
+      if (group == ResetGroup::node) b.deps[i] = 0;
+    }
+  } else {
+    mpStreamSynchronize(stream.context);
+    for (size_t i = 0; i < b.data.size(); ++i) free_tensor(Tensor{this, c, i});
+    b = Block();
+  }
+}
+
+void* Graph::scratch(size_t bytes) {
+  if (bytes > scratch_bytes_) {
+    if (scratch_ != nullptr) mpMemFree(scratch_, stream.context);
+    scratch_ = mpMemAlloc(bytes, stream.context);
+    scratch_bytes_ = bytes;
+  }
+  return scratch_;
+}
+
+void enable_gradient(Tensor t) {
+  Graph* g = t.ptr;
+  Graph::Block& b = g->block_of(t.cls);
+  if (b.grad[t.idx] == nullptr && b.len[t.idx] > 0) {
+    b.grad[t.idx] = g->tensor_allocator.alloc(b.len[t.idx] * dtype_size(b.dtype[t.idx]), g->stream.context);
+    kernels::fill[dkey(t)](b.grad[t.idx], 0.0, b.len[t.idx], g->stream.context);   // gradients start at zero
+  }
+}
+
+void attach_op(ReverseFn fn, Tensor out, const std::vector<OpDatum>& args) {
+  assert(out.cls == Class::hid);
+  Graph::Block& nb = out.ptr->node_block;
+  nb.has_op[out.idx] = true;
+  nb.op_reverse[out.idx] = fn;
+  nb.op_args[out.idx] = args;
+  for (size_t i = 0; i + 1 < args.size(); ++i) {   // the last argument is the output
+    if (args[i].kind != OpDatum::tensor_k || args[i].tensor.cls != Class::hid) continue;
+    nb.deps[args[i].tensor.idx] += 1;
+  }
+}
+
+void Graph::reverse(size_t idx, ReverseCleanup cleanup) {
+  assert(mode != Mode::eval);
+  if (node_block.data.empty()) return;
+  std::vector<size_t> node_stack{idx}, free_stack;
+  while (!node_stack.empty()) {
+    const size_t last = node_stack.back();
+    node_stack.pop_back();
+    if (!node_block.has_op[last]) continue;
+    if (cleanup == ReverseCleanup::free) free_stack.push_back(last);
+    const std::vector<OpDatum> args = node_block.op_args[last];
+    node_block.op_reverse[last](args);
+    for (const OpDatum& a : args) {
+      if (a.kind != OpDatum::tensor_k) continue;
+      if (a.tensor.cls != Class::hid || a.tensor.idx == last) continue;
+      if (!node_block.attached[a.tensor.idx]) continue;
+      if (--node_block.deps[a.tensor.idx] == 0) node_stack.push_back(a.tensor.idx);
+    }
+    node_block.has_op[last] = false;   // the dependency is consumed
+    node_block.op_args[last].clear();
+  }
+  if (cleanup == ReverseCleanup::free) {
+    mpStreamSynchronize(stream.context);
+    for (size_t n : free_stack) free_tensor(Tensor{this, Class::hid, n});
+  }
+}
+
+// ------------------------------ algo --------------------------------------------
+namespace algo {
+void fill(Tensor x, double value) { kernels::fill[dkey(x)](x.data_ptr(), value, x.len(), x.context()); }
+void sequence(Tensor x, double init, double step) { kernels::sequence[dkey(x)](x.data_ptr(), init, step, x.len(), x.context()); }
+void copy(Tensor src, Tensor dst) {
+  assert(src.len() == dst.len() && src.dtype() == dst.dtype());
+  kernels::copy[dkey(src)](src.data_ptr(), dst.data_ptr(), src.len(), src.context());
+}
+}
+
+// ------------------------------ ops ----------------------------------------------
+namespace ops {
+
+static Tensor hidden_like(Graph* g, Tensor x) { return g->tensor({Class::hid, x.dtype(), x.sizes()}); }
+static void check_same(Tensor x, Tensor y) {
+  if (x.dtype() != y.dtype() || x.sizes() != y.sizes()) panic("operands differ in dtype or shape");
+}
+
+// --- add / sub / hadamard (addition.zig:27-82, subtraction.zig, hadamard.zig) ---
+static void add_reverse(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[1].tensor, z = a[2].tensor;
+  enable_gradient(x); enable_gradient(y);
+  const int k = dkey(z);
+  kernels::addition[k](z.grad_ptr(), x.grad_ptr(), x.grad_ptr(), x.len(), x.context());   // g_x = g_z + g_x
+  kernels::addition[k](z.grad_ptr(), y.grad_ptr(), y.grad_ptr(), y.len(), y.context());
+}
+Tensor add(Tensor x, Tensor y) {
+  check_same(x, y);
+  Graph* g = x.ptr;
+  Tensor z = hidden_like(g, x);
+  kernels::addition[dkey(z)](x.data_ptr(), y.data_ptr(), z.data_ptr(), z.len(), z.context());
+  if (g->mode == Mode::train) attach_op(add_reverse, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)});
+  return z;
+}
+static void sub_reverse(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[1].tensor, z = a[2].tensor;
+  enable_gradient(x); enable_gradient(y);
+  const int k = dkey(z);
+  kernels::addition[k](z.grad_ptr(), x.grad_ptr(), x.grad_ptr(), x.len(), x.context());
+  kernels::subtraction[k](y.grad_ptr(), z.grad_ptr(), y.grad_ptr(), y.len(), y.context());   // g_y = g_y - g_z
+}
+Tensor sub(Tensor x, Tensor y) {
+  check_same(x, y);
+  Graph* g = x.ptr;
+  Tensor z = hidden_like(g, x);
+  kernels::subtraction[dkey(z)](x.data_ptr(), y.data_ptr(), z.data_ptr(), z.len(), z.context());
+  if (g->mode == Mode::train) attach_op(sub_reverse, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)});
+  return z;
+}
+static void hadamard_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[1].tensor, z = a[2].tensor;
+  enable_gradient(x); enable_gradient(y);
+  const int k = dkey(z);
+  kernels::hadamard_reverse[k](z.grad_ptr(), y.data_ptr(), x.grad_ptr(), x.len(), x.context());   // g_x += g_z*y
+  kernels::hadamard_reverse[k](z.grad_ptr(), x.data_ptr(), y.grad_ptr(), y.len(), y.context());
+}
+Tensor hadamard(Tensor x, Tensor y) {
+  check_same(x, y);
+  Graph* g = x.ptr;
+  Tensor z = hidden_like(g, x);
+  kernels::hadamard[dkey(z)](x.data_ptr(), y.data_ptr(), z.data_ptr(), z.len(), z.context());
+  if (g->mode == Mode::train) attach_op(hadamard_rev, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)});
+  return z;
+}
+
+// --- unary / scalar ops (negate.zig, translate.zig, dilate.zig, relu.zig) ---
+static void negate_reverse(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, z = a[1].tensor;
+  enable_gradient(x);
+  kernels::subtraction[dkey(z)](x.grad_ptr(), z.grad_ptr(), x.grad_ptr(), x.len(), x.context());
+}
+Tensor negate(Tensor x) {
+  Graph* g = x.ptr;
+  Tensor z = hidden_like(g, x);
+  kernels::negate[dkey(z)](x.data_ptr(), z.data_ptr(), z.len(), z.context());
+  if (g->mode == Mode::train) attach_op(negate_reverse, z, {OpDatum::of(x), OpDatum::of(z)});
+  return z;
+}
+static void translate_reverse(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, z = a[2].tensor;
+  enable_gradient(x);
+  kernels::addition[dkey(z)](z.grad_ptr(), x.grad_ptr(), x.grad_ptr(), x.len(), x.context());
+}
+Tensor translate(Tensor x, double value) {
+  Graph* g = x.ptr;
+  Tensor z = hidden_like(g, x);
+  kernels::translate[dkey(z)](x.data_ptr(), value, z.data_ptr(), z.len(), z.context());
+  if (g->mode == Mode::train) attach_op(translate_reverse, z, {OpDatum::of(x), OpDatum::of(value), OpDatum::of(z)});
+  return z;
+}
+static void dilate_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, z = a[2].tensor;
+  enable_gradient(x);
+  kernels::dilate_reverse[dkey(z)](z.grad_ptr(), a[1].scalar, x.grad_ptr(), x.len(), x.context());
+}
+Tensor dilate(Tensor x, double value) {
+  Graph* g = x.ptr;
+  Tensor z = hidden_like(g, x);
+  kernels::dilate[dkey(z)](x.data_ptr(), value, z.data_ptr(), z.len(), z.context());
+  if (g->mode == Mode::train) attach_op(dilate_rev, z, {OpDatum::of(x), OpDatum::of(value), OpDatum::of(z)});
+  return z;
+}
+static void relu_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, z = a[1].tensor;
+  enable_gradient(x);
+  kernels::relu_reverse[dkey(z)](x.data_ptr(), x.grad_ptr(), z.grad_ptr(), x.len(), x.context());
+}
+Tensor relu(Tensor x) {
+  Graph* g = x.ptr;
+  Tensor z = hidden_like(g, x);
+  kernels::relu[dkey(z)](x.data_ptr(), z.data_ptr(), z.len(), z.context());
+  if (g->mode == Mode::train) attach_op(relu_rev, z, {OpDatum::of(x), OpDatum::of(z)});
+  return z;
+}
+static void selu_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, z = a[1].tensor;
+  enable_gradient(x);
+  kernels::selu_reverse[dkey(z)](x.data_ptr(), x.grad_ptr(), z.grad_ptr(), x.len(), x.context());
+}
+Tensor selu(Tensor x) {
+  Graph* g = x.ptr;
+  Tensor z = hidden_like(g, x);
+  kernels::selu[dkey(z)](x.data_ptr(), z.data_ptr(), z.len(), z.context());
+  if (g->mode == Mode::train) attach_op(selu_rev, z, {OpDatum::of(x), OpDatum::of(z)});
+  return z;
+}
+
+// --- reduce / broadcast (reduce.zig:98-182, broadcast.zig:96-183) ---
+static void reduce_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[2].tensor;
+  enable_gradient(x);
+  const auto& s = x.sizes();
+  if (a[1].expr == "ij->i") kernels::broadcast_i_ij[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+  else kernels::broadcast_j_ij[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+}
+Tensor reduce(Tensor x, const std::string& expr) {
+  const auto& s = x.sizes();
+  if (s.size() != 2) panic("reduce needs a rank-2 tensor");
+  Graph* g = x.ptr;
+  Tensor y;
+  if (expr == "ij->i") {
+    y = g->tensor({Class::hid, x.dtype(), {s[0]}});
+    kernels::reduce_ij_i[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
+  } else if (expr == "ij->j") {
+    y = g->tensor({Class::hid, x.dtype(), {s[1]}});
+    kernels::reduce_ij_j[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
+  } else panic("reduce: unknown expression");
+  if (g->mode == Mode::train) attach_op(reduce_rev, y, {OpDatum::of(x), OpDatum::of(expr), OpDatum::of(y)});
+  return y;
+}
+static void broadcast_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[2].tensor;
+  enable_gradient(x);
+  const auto& s = y.sizes();
+  if (a[1].expr == "i->ij") kernels::reduce_ij_i[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+  else kernels::reduce_ij_j[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+}
+Tensor broadcast(Tensor x, const std::vector<size_t>& sizes, const std::string& expr) {
+  if (sizes.size() != 2 || x.sizes().size() != 1) panic("broadcast: rank-1 source and rank-2 target expected");
+  Graph* g = x.ptr;
+  Tensor y = g->tensor({Class::hid, x.dtype(), sizes});
+  if (expr == "i->ij") {
+    if (x.sizes()[0] != sizes[0]) panic("broadcast i->ij: size mismatch");
+    kernels::broadcast_i_ij[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, sizes[0], sizes[1], y.context());
+  } else if (expr == "j->ij") {
+    if (x.sizes()[0] != sizes[1]) panic("broadcast j->ij: size mismatch");
+    kernels::broadcast_j_ij[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, sizes[0], sizes[1], y.context());
+  } else panic("broadcast: unknown expression");
+  if (g->mode == Mode::train) attach_op(broadcast_rev, y, {OpDatum::of(x), OpDatum::of(expr), OpDatum::of(y)});
+  return y;
+}
+
+// --- permutate (permutate.zig:39-104) ---
+static void permutate_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[1].tensor;
+  enable_gradient(x);
+  const auto& s = y.sizes();
+  kernels::permutate_ij_ji[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+}
+Tensor permutate(Tensor x, const std::string& expr) {
+  if (expr != "ij->ji" || x.sizes().size() != 2) panic("permutate: only \"ij->ji\" on rank-2 tensors");
+  Graph* g = x.ptr;
+  const auto& s = x.sizes();
+  Tensor y = g->tensor({Class::hid, x.dtype(), {s[1], s[0]}});
+  kernels::permutate_ij_ji[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
+  if (g->mode == Mode::train) attach_op(permutate_rev, y, {OpDatum::of(x), OpDatum::of(y)});
+  return y;
+}
+
+// --- inner product (inner_product.zig:116-122 expression map, :163-419 variants and reverses) ---
+// Logical shape of the contraction "lhs,rhs->out" as C[m,k] = op(A)[m,n] op(B)[n,k].
+struct Contraction { len_t m, n, k; int kind; };   // kind: 0 = ij,jk  1 = ij,kj  2 = ji,jk
+static Contraction parse_contraction(Tensor x, Tensor y, const std::string& e, std::vector<size_t>& out_sizes) {
+  const auto& xs = x.sizes(); const auto& ys = y.sizes();
+  Contraction c{};
+  if (e == "ij,jk->ik") { c = {xs[0], xs[1], ys[1], 0}; if (xs[1] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {xs[0], ys[1]}; }
+  else if (e == "ij,kj->ik") { c = {xs[0], xs[1], ys[0], 1}; if (xs[1] != ys[1]) panic("inner_product: inner sizes differ"); out_sizes = {xs[0], ys[0]}; }
+  else if (e == "ji,jk->ik") { c = {xs[1], xs[0], ys[1], 2}; if (xs[0] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {xs[1], ys[1]}; }
+  else if (e == "i,ij->j") { c = {1, xs[0], ys[1], 0}; if (xs[0] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {ys[1]}; }
+  else if (e == "ij,j->i") { c = {xs[0], xs[1], 1, 0}; if (xs[1] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {xs[0]}; }
+  else panic("inner_product: unknown expression");
+  return c;
+}
+static void gemm(int key, int kind, const void* a, const void* b, double alpha, void* c, double beta, len_t m, len_t n, len_t k,
+                 StreamContext ctx) {
+  if (kind == 0) kernels::ip_ij_jk_ik[key](a, b, alpha, c, beta, m, n, k, ctx);
+  else if (kind == 1) kernels::ip_ij_kj_ik[key](a, b, alpha, c, beta, m, n, k, ctx);
+  else kernels::ip_ji_jk_ik[key](a, b, alpha, c, beta, m, n, k, ctx);
+}
+static void inner_product_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[1].tensor, z = a[4].tensor;
+  const double scale = a[2].scalar;
+  std::vector<size_t> tmp;
+  const Contraction c = parse_contraction(x, y, a[3].expr, tmp);
+  enable_gradient(x); enable_gradient(y);
+  const int key = dkey(z);
+  StreamContext ctx = z.context();
+  const void* G = z.grad_ptr();
+  // Z = op(X) op(Y):  dX and dY as native transposed-operand contractions, accumulated (beta = 1)
+  if (c.kind == 0) {          // Z = X Y: dX = G Y^T (ij,kj), dY = X^T G (ji,jk)
+    gemm(key, 1, G, y.data_ptr(), scale, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx);
+    gemm(key, 2, x.data_ptr(), G, scale, y.grad_ptr(), 1.0, c.n, c.m, c.k, ctx);
+  } else if (c.kind == 1) {   // Z = X Y^T: dX = G Y (ij,jk), dY = G^T X (ji,jk)
+    gemm(key, 0, G, y.data_ptr(), scale, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx);
+    gemm(key, 2, G, x.data_ptr(), scale, y.grad_ptr(), 1.0, c.k, c.m, c.n, ctx);
+  } else {                    // Z = X^T Y: dX = Y G^T (ij,kj), dY = X G (ij,jk)
+    gemm(key, 1, y.data_ptr(), G, scale, x.grad_ptr(), 1.0, c.n, c.k, c.m, ctx);
+    gemm(key, 0, x.data_ptr(), G, scale, y.grad_ptr(), 1.0, c.n, c.m, c.k, ctx);
+  }
+}
+Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string& expr) {
+  if (x.dtype() != y.dtype()) panic("inner_product: dtypes differ");
+  Graph* g = x.ptr;
+  std::vector<size_t> out_sizes;
+  const Contraction c = parse_contraction(x, y, expr, out_sizes);
+  Tensor z = g->tensor({Class::hid, x.dtype(), out_sizes});
+  gemm(dkey(z), c.kind, x.data_ptr(), y.data_ptr(), scale, z.data_ptr(), 0.0, c.m, c.n, c.k, z.context());
+  if (g->mode == Mode::train)
+    attach_op(inner_product_rev, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(scale), OpDatum::of(expr), OpDatum::of(z)});
+  return z;
+}
+Tensor inner_product(Tensor x, Tensor y, const std::string& expr) { return inner_product_scaled(x, y, 1.0, expr); }
+
+// --- linear: y = x.A + b, bias added in the GEMM epilogue (README.md:81,97) ---
+static void linear_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, A = a[1].tensor, b = a[2].tensor, z = a[4].tensor;
+  std::vector<size_t> tmp;
+  const Contraction c = parse_contraction(x, A, a[3].expr, tmp);
+  enable_gradient(x); enable_gradient(A); enable_gradient(b);
+  const int key = dkey(z);
+  StreamContext ctx = z.context();
+  gemm(key, 1, z.grad_ptr(), A.data_ptr(), 1.0, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx);   // dx = G A^T
+  gemm(key, 2, x.data_ptr(), z.grad_ptr(), 1.0, A.grad_ptr(), 1.0, c.n, c.m, c.k, ctx);   // dA = x^T G
+  kernels::reduce_ij_j[key](z.grad_ptr(), b.grad_ptr(), 1.0, c.m, c.k, ctx);              // db = sum_i G
+}
+Tensor linear(Tensor x, Tensor A, Tensor b, const std::string& expr) {
+  if (expr != "ij,jk->ik" && expr != "i,ij->j") panic("linear: expression must be \"ij,jk->ik\" or \"i,ij->j\"");
+  Graph* g = x.ptr;
+  std::vector<size_t> out_sizes;
+  const Contraction c = parse_contraction(x, A, expr, out_sizes);
+  if (b.len() != c.k) panic("linear: bias length differs from the output width");
+  Tensor z = g->tensor({Class::hid, x.dtype(), out_sizes});
+  kernels::linear[dkey(z)](x.data_ptr(), A.data_ptr(), b.data_ptr(), 1.0, z.data_ptr(), 0.0, c.m, c.n, c.k, z.context());
+  if (g->mode == Mode::train)
+    attach_op(linear_rev, z, {OpDatum::of(x), OpDatum::of(A), OpDatum::of(b), OpDatum::of(expr), OpDatum::of(z)});
+  return z;
+}
+
+// --- row-wise softmax / RMSNorm ("ij|j", expression_parsing.zig:319-340) ---
+static void softmax_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[1].tensor;
+  enable_gradient(x);
+  const auto& s = y.sizes();
+  kernels::softmax_reverse[dkey(y)](y.data_ptr(), y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], y.context());
+}
+Tensor softmax(Tensor x) {
+  if (x.sizes().size() != 2) panic("softmax needs a rank-2 tensor");
+  Graph* g = x.ptr;
+  Tensor y = hidden_like(g, x);
+  kernels::softmax[dkey(y)](x.data_ptr(), y.data_ptr(), x.sizes()[0], x.sizes()[1], y.context());
+  if (g->mode == Mode::train) attach_op(softmax_rev, y, {OpDatum::of(x), OpDatum::of(y)});
+  return y;
+}
+static void rmsnorm_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, gain = a[1].tensor, y = a[3].tensor;
+  enable_gradient(x); enable_gradient(gain);
+  const auto& s = x.sizes();
+  Graph* g = x.ptr;
+  void* scratch = g->scratch(mpRmsnormReverseScratchBytes(s[0], s[1], y.context()));
+  kernels::rmsnorm_reverse[dkey(y)](x.data_ptr(), gain.data_ptr(), nullptr, y.grad_ptr(), a[2].scalar, x.grad_ptr(),
+                                    gain.grad_ptr(), 1.0, scratch, s[0], s[1], y.context());
+}
+Tensor rmsnorm(Tensor x, Tensor gain, double eps) {
+  if (x.sizes().size() != 2 || gain.len() != x.sizes()[1]) panic("rmsnorm: x must be [m,n] and gain [n]");
+  Graph* g = x.ptr;
+  Tensor y = hidden_like(g, x);
+  kernels::rmsnorm[dkey(y)](x.data_ptr(), gain.data_ptr(), eps, y.data_ptr(), nullptr, x.sizes()[0], x.sizes()[1], y.context());
+  if (g->mode == Mode::train) attach_op(rmsnorm_rev, y, {OpDatum::of(x), OpDatum::of(gain), OpDatum::of(eps), OpDatum::of(y)});
+  return y;
+}
+
+}  // namespace ops
+
+// ------------------------------ optimizers ------------------------------------------
+namespace optm {
+ClipRange::ClipRange() : lower(-std::numeric_limits<double>::infinity()), upper(std::numeric_limits<double>::infinity()) {}
+
+// Every weight leaf that has a gradient: w -= rate * clip(g) (optimizer.zig:140-179).
+void SGD::update(Graph* graph) {
+  Graph::Block& b = graph->leaf_block;
+  for (size_t i = 0; i < b.data.size(); ++i) {
+    if (b.cls[i] != Class::wgt || b.grad[i] == nullptr || b.len[i] == 0) continue;
+    kernels::sgd[static_cast<int>(b.dtype[i])](b.data[i], b.grad[i], rate, clip.lower, clip.upper, b.len[i], graph->stream.context);
+  }
+  mpStreamSynchronize(graph->stream.context);   // the reference synchronises each active stream once
+}
+
+void Adam::update(Graph* graph) {
+  Graph::Block& b = graph->leaf_block;
+  ++step;
+  for (size_t i = 0; i < b.data.size(); ++i) {
+    if (b.cls[i] != Class::wgt || b.grad[i] == nullptr || b.len[i] == 0) continue;
+    const int key = static_cast<int>(b.dtype[i]);
+    auto k = std::make_pair(graph, i);
+    auto it = state.find(k);
+    if (it == state.end()) {   // zero-filled on first use, like the reference's Momentum map (optimizer.zig:249-256)
+      const size_t bytes = b.len[i] * dtype_size(b.dtype[i]);
+      void* m = mpMemAlloc(bytes, graph->stream.context);
+      void* v = mpMemAlloc(bytes, graph->stream.context);
+      kernels::fill[key](m, 0.0, b.len[i], graph->stream.context);
+      kernels::fill[key](v, 0.0, b.len[i], graph->stream.context);
+      it = state.emplace(k, std::make_pair(m, v)).first;
+    }
+    kernels::adam[key](b.data[i], b.grad[i], it->second.first, it->second.second, rate, beta1, beta2, eps, grad_scale, step,
+                       b.len[i], graph->stream.context);
+  }
+  mpStreamSynchronize(graph->stream.context);
+}
+}  // namespace optm
+
+}  // namespace mp

@@ -1,0 +1,174 @@
+// C++ mirror of the reference's Zig host layer (src/metaphor.zig facade,
+// src/core/graph.zig, src/core/tensor_allocator.zig, src/ops/*.zig,
+// src/algo/mem.zig, src/optm/optimizer.zig) over the extern "C" device layer of
+// include/*.h.  No Zig toolchain exists where this library is built and tested,
+// so this layer keeps the reference's names, argument meaning and behaviour in
+// C++: the same kernel call sequences, the same reverse walk over dependency
+// counters with .keep / .free clean-up and detach(), the same exact-size tensor
+// cache.  One deliberate difference: a gradient buffer is zero-filled when it is
+// created (the reference allocates it without initialising it, graph.zig:710-722,
+// and then accumulates into it).
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/mp_device_utils.h"
+#include "../../include/mp_kernels.h"
+
+namespace mp {
+
+enum class Dtype : int { r16 = 0, r32 = 1, r64 = 2 };   // scalar.zig:35-40, = dispatch key
+enum class Class { inp, wgt, hid };                     // graph.zig TensorClass
+enum class Mode { train, eval };
+enum class ReverseCleanup { keep, free };               // graph.zig:254
+enum class ResetGroup { node, leaf };
+enum class ResetComponent { all, grd };
+
+inline size_t dtype_size(Dtype d) { return d == Dtype::r16 ? 2 : (d == Dtype::r32 ? 4 : 8); }
+
+struct Stream { StreamContext context; };
+
+namespace device {          // metaphor.zig:13-18
+void init(unsigned device_number);
+void sync();
+void check();
+size_t total_memory(unsigned device_number);
+}
+namespace stream {          // metaphor.zig:20-25
+Stream init();
+void deinit(Stream s);
+void sync(Stream s);
+}
+
+class Graph;
+
+// Handle into a graph (graph.zig:34-183): leaves (inp, wgt) and computed nodes
+// (hid) live in separate blocks, idx indexes the block of `cls`.
+struct Tensor {
+  Graph* ptr = nullptr;
+  Class cls = Class::inp;
+  size_t idx = 0;
+
+  void* data_ptr() const;
+  void* grad_ptr() const;                 // nullptr until a gradient exists
+  bool has_grad() const { return grad_ptr() != nullptr; }
+  const std::vector<size_t>& sizes() const;
+  size_t len() const;                     // 0 after the tensor was freed
+  Dtype dtype() const;
+  StreamContext context() const;
+  void reverse(ReverseCleanup cleanup) const;   // graph.zig:111-121
+  void detach() const;                          // graph.zig:103-105
+  void free() const;
+  std::vector<double> native() const;           // values copied to the host (widened to double)
+  std::vector<double> native_grad() const;
+};
+
+struct TensorConfig { Class cls; Dtype dtype; std::vector<size_t> sizes; };
+struct GraphConfig { Stream stream; Mode mode = Mode::train; };
+
+// Exact-size cache over stream-ordered allocation (tensor_allocator.zig:95-141).
+class TensorAllocator {
+ public:
+  void* alloc(size_t bytes, StreamContext ctx);
+  void release(void* p, size_t bytes);          // back into the cache
+  void drain(StreamContext ctx);                // mpMemFree everything cached
+  size_t cached_blocks() const;
+ private:
+  std::map<size_t, std::vector<void*>> free_;
+};
+
+struct OpDatum {            // graph.zig:776-886 (tensor or scalar or expression operand)
+  enum Kind { tensor_k, scalar_k, expr_k } kind = tensor_k;
+  Tensor tensor;
+  double scalar = 0.0;
+  std::string expr;
+  static OpDatum of(Tensor t) { OpDatum d; d.kind = tensor_k; d.tensor = t; return d; }
+  static OpDatum of(double s) { OpDatum d; d.kind = scalar_k; d.scalar = s; return d; }
+  static OpDatum of(const std::string& e) { OpDatum d; d.kind = expr_k; d.expr = e; return d; }
+};
+using ReverseFn = void (*)(const std::vector<OpDatum>& args);
+
+class Graph {
+ public:
+  static Graph* init(GraphConfig cfg);          // graph.zig:331-348
+  void deinit();                                // graph.zig:350-369
+  Tensor tensor(const TensorConfig& cfg);       // graph.zig:500-520
+  void reset(ResetGroup group, ResetComponent component);   // graph.zig:371-414
+  Mode mode;
+  Stream stream;
+
+  // internal interface used by ops (attach_op / enable_gradient / reverse walk)
+  struct Block {
+    std::vector<void*> data, grad;
+    std::vector<size_t> len;
+    std::vector<std::vector<size_t>> sizes;
+    std::vector<Dtype> dtype;
+    std::vector<Class> cls;
+    // node block only
+    std::vector<int> deps;
+    std::vector<bool> attached, has_op;
+    std::vector<ReverseFn> op_reverse;
+    std::vector<std::vector<OpDatum>> op_args;
+  };
+  Block leaf_block, node_block;
+  TensorAllocator tensor_allocator;
+  Block& block_of(Class c) { return c == Class::hid ? node_block : leaf_block; }
+  void reverse(size_t idx, ReverseCleanup cleanup);          // graph.zig:552-631
+  void free_tensor(Tensor t);
+  void free_gradient(Tensor t);
+  void* scratch(size_t bytes);                                // utils.zig:20-36 grow-only per-stream scratch
+ private:
+  void* scratch_ = nullptr;
+  size_t scratch_bytes_ = 0;
+};
+
+void enable_gradient(Tensor t);                               // graph.zig:710-722 (+ zero fill)
+void attach_op(ReverseFn fn, Tensor out, const std::vector<OpDatum>& args);   // graph.zig:733-757
+
+namespace algo {            // src/algo/mem.zig:24-39
+void fill(Tensor x, double value);
+void sequence(Tensor x, double init, double step);
+void copy(Tensor src, Tensor dst);
+}
+namespace mem = algo;       // README spelling
+
+namespace ops {             // metaphor.zig:44-56 plus the ops the README names
+Tensor add(Tensor x, Tensor y);
+Tensor sub(Tensor x, Tensor y);
+Tensor hadamard(Tensor x, Tensor y);
+Tensor negate(Tensor x);
+Tensor translate(Tensor x, double value);
+Tensor dilate(Tensor x, double value);
+Tensor relu(Tensor x);
+Tensor selu(Tensor x);
+Tensor reduce(Tensor x, const std::string& expr);                       // "ij->i", "ij->j"
+Tensor broadcast(Tensor x, const std::vector<size_t>& sizes, const std::string& expr);   // "i->ij", "j->ij"
+Tensor inner_product(Tensor x, Tensor y, const std::string& expr);      // "ij,jk->ik", "ij,kj->ik", "ji,jk->ik", "i,ij->j", "ij,j->i"
+Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string& expr);
+inline Tensor innerProduct(Tensor x, Tensor y, const std::string& e) { return inner_product(x, y, e); }
+Tensor linear(Tensor x, Tensor A, Tensor b, const std::string& expr);   // "ij,jk->ik", "i,ij->j"
+Tensor permutate(Tensor x, const std::string& expr);                    // "ij->ji"
+Tensor softmax(Tensor x);                                               // over the last axis ("ij|j")
+Tensor rmsnorm(Tensor x, Tensor gain, double eps);
+}
+
+namespace optm {            // src/optm/optimizer.zig:126-180 (SGD); Adam is named in NOTES.md:11
+struct ClipRange { double lower, upper; ClipRange(); ClipRange(double lo, double hi) : lower(lo), upper(hi) {} };
+struct SGD {
+  double rate;
+  ClipRange clip;
+  void update(Graph* graph);
+};
+struct Adam {
+  double rate, beta1 = 0.9, beta2 = 0.999, eps = 1e-8, grad_scale = 1.0;
+  size_t step = 0;
+  std::map<std::pair<Graph*, size_t>, std::pair<void*, void*>> state;   // per (graph, weight): m, v
+  void update(Graph* graph);
+};
+}
+
+}  // namespace mp

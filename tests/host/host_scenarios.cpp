@@ -1,0 +1,209 @@
+// Scenario tests of the C++ host mirror, replaying the reference's example
+// programs (src/examples/subgraphs.zig, src/examples/experimental.zig) and the
+// README feed-forward block (README.md:90-104) on the GPU, with numeric checks
+// against the CPU oracle (liboracle.so; test infrastructure).
+// Usage: host_scenarios [timing-iterations]; exit code 0 = all checks passed.
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <random>
+#include <vector>
+
+#include "../../metaphor_b200/host/metaphor.hpp"
+
+extern "C" {
+void orc_inner_product_f32(const float*, const float*, const float*, double, float*, double, size_t, size_t, size_t, int, int);
+void orc_selu_f32(const float*, float*, size_t);
+void orc_selu_reverse_f32(const float*, float*, const float*, size_t);
+void orc_reduce_ij_j_f32(const float*, float*, double, size_t, size_t);
+void orc_sgd_f32(float*, const float*, double, double, double, size_t);
+void orc_softmax_ij_j_f32(const float*, float*, size_t, size_t);
+void orc_softmax_ij_j_reverse_f32(const float*, const float*, float*, double, size_t, size_t);
+void orc_rmsnorm_ij_j_f32(const float*, const float*, double, float*, float*, size_t, size_t);
+void orc_rmsnorm_ij_j_reverse_f32(const float*, const float*, const float*, double, float*, float*, double, size_t, size_t);
+}
+
+static int failures = 0;
+#define CHECK(cond)                                                        \
+  do {                                                                     \
+    if (!(cond)) { std::printf("CHECK failed: %s (line %d)\n", #cond, __LINE__); ++failures; } \
+  } while (0)
+
+static double rel_err(const std::vector<double>& got, const std::vector<float>& ref) {
+  double mx = 1e-30, err = 0;
+  if (got.size() != ref.size()) return 1e9;
+  for (size_t i = 0; i < ref.size(); ++i) { mx = std::fmax(mx, std::fabs(ref[i])); err = std::fmax(err, std::fabs(got[i] - ref[i])); }
+  return err / mx;
+}
+static void upload(mp::Tensor t, const std::vector<float>& v) {
+  mpMemcpyHtoD(t.data_ptr(), v.data(), v.size() * 4, t.context());
+  mpStreamSynchronize(t.context());
+}
+static std::vector<float> normal(size_t n, unsigned seed, float scale) {
+  std::mt19937 gen(seed);
+  std::normal_distribution<float> d(0.f, scale);
+  std::vector<float> v(n);
+  for (auto& x : v) x = d(gen);
+  return v;
+}
+
+// src/examples/subgraphs.zig:6-150
+static void scenario_subgraphs(mp::Stream stream) {
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  const size_t M = 32;
+  mp::Tensor x = G->tensor({mp::Class::inp, mp::Dtype::r32, {M}});
+  mp::Tensor w1 = G->tensor({mp::Class::wgt, mp::Dtype::r32, {M}});
+  mp::Tensor w2 = G->tensor({mp::Class::wgt, mp::Dtype::r32, {M}});
+  mp::algo::fill(x, 1.0); mp::algo::fill(w1, 1.0); mp::algo::fill(w2, 1.0);
+  mp::Tensor z1 = mp::ops::add(x, w1);
+  mp::Tensor z2 = mp::ops::relu(z1);
+  mp::Tensor z3 = mp::ops::add(z2, w2);
+  mp::Tensor z4 = mp::ops::relu(z3);
+  for (double v : z4.native()) CHECK(v == 3.0);
+  z2.detach();
+  z4.reverse(mp::ReverseCleanup::free);
+  CHECK(z4.len() == 0); CHECK(z3.len() == 0);
+  CHECK(!z4.has_grad()); CHECK(!z3.has_grad());
+  CHECK(z2.len() != 0); CHECK(w2.len() != 0);
+  CHECK(z2.has_grad()); CHECK(w2.has_grad());
+  CHECK(z1.len() != 0); CHECK(w1.len() != 0);
+  CHECK(!z1.has_grad()); CHECK(!w1.has_grad());
+  for (double v : w2.native_grad()) CHECK(v == 1.0);
+  for (double v : z2.native_grad()) CHECK(v == 1.0);
+  CHECK(G->tensor_allocator.cached_blocks() >= 2);   // freed nodes went back to the exact-size cache
+  z2.reverse(mp::ReverseCleanup::keep);
+  CHECK(x.len() != 0); CHECK(z1.len() != 0); CHECK(w1.len() != 0);
+  CHECK(z1.has_grad()); CHECK(w1.has_grad());
+  for (double v : w1.native_grad()) CHECK(v == 1.0);
+  G->reset(mp::ResetGroup::node, mp::ResetComponent::all);
+  G->reset(mp::ResetGroup::leaf, mp::ResetComponent::grd);
+  CHECK(!w1.has_grad()); CHECK(w1.len() == M);
+  mp::device::check();
+  G->deinit();
+}
+
+// src/examples/experimental.zig:19-71 (values derivable by hand)
+static void scenario_experimental(mp::Stream stream) {
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  mp::Tensor x = G->tensor({mp::Class::wgt, mp::Dtype::r32, {3, 2}});
+  mp::Tensor y = G->tensor({mp::Class::wgt, mp::Dtype::r32, {2, 2}});
+  mp::algo::sequence(x, 1.0, 1.0); mp::algo::sequence(y, 1.0, 1.0);
+  mp::Tensor z = mp::ops::inner_product(x, y, "ij,jk->ik");
+  CHECK((z.native() == std::vector<double>{7, 10, 15, 22, 23, 34}));
+  mp::Tensor a = mp::ops::reduce(y, "ij->i");
+  mp::Tensor b = mp::ops::broadcast(a, x.sizes(), "j->ij");
+  CHECK((b.native() == std::vector<double>{3, 7, 3, 7, 3, 7}));
+  mp::Tensor c = mp::ops::reduce(x, "ij->j");
+  mp::Tensor d = mp::ops::broadcast(c, y.sizes(), "i->ij");
+  CHECK((d.native() == std::vector<double>{9, 9, 12, 12}));
+  z.reverse(mp::ReverseCleanup::keep);
+  CHECK((x.native_grad() == std::vector<double>{3, 7, 3, 7, 3, 7}));
+  CHECK((y.native_grad() == std::vector<double>{9, 9, 12, 12}));
+  mp::Tensor t = mp::ops::permutate(x, "ij->ji");
+  CHECK((t.native() == std::vector<double>{1, 3, 5, 2, 4, 6}));
+  G->deinit();
+}
+
+// README feed-forward block: y = selu(linear(x, A, b)); y.reverse(.free); one SGD step.
+static void scenario_feed_forward(mp::Stream stream, int timing_iters) {
+  const size_t m = 32, n = 256, k = 256;
+  const double lr = 1e-2;
+  std::vector<float> hx = normal(m * n, 0, 1.f), hA = normal(n * k, 1, 1.f / 16.f), hb(k, 0.f);
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  mp::Tensor x = G->tensor({mp::Class::inp, mp::Dtype::r32, {m, n}});
+  mp::Tensor A = G->tensor({mp::Class::wgt, mp::Dtype::r32, {n, k}});
+  mp::Tensor b = G->tensor({mp::Class::wgt, mp::Dtype::r32, {k}});
+  upload(x, hx); upload(A, hA); upload(b, hb);
+  mp::Tensor lin = mp::ops::linear(x, A, b, "ij,jk->ik");
+  mp::Tensor y = mp::ops::selu(lin);
+  // oracle: forward
+  std::vector<float> rl(m * k), ry(m * k);
+  orc_inner_product_f32(hx.data(), hA.data(), hb.data(), 1.0, rl.data(), 0.0, m, n, k, 0, 0);
+  orc_selu_f32(rl.data(), ry.data(), m * k);
+  CHECK(rel_err(y.native(), ry) <= 1e-4);
+  y.reverse(mp::ReverseCleanup::free);
+  CHECK(y.len() == 0); CHECK(lin.len() == 0);
+  // oracle: reverse of the sum loss (seed 1), gradients start at zero
+  std::vector<float> seed(m * k, 1.f), gl(m * k, 0.f), gx(m * n, 0.f), gA(n * k, 0.f), gb(k, 0.f);
+  orc_selu_reverse_f32(rl.data(), gl.data(), seed.data(), m * k);
+  orc_inner_product_f32(gl.data(), hA.data(), nullptr, 1.0, gx.data(), 1.0, m, k, n, 0, 1);   // dx = G A^T
+  orc_inner_product_f32(hx.data(), gl.data(), nullptr, 1.0, gA.data(), 1.0, n, m, k, 1, 0);   // dA = x^T G
+  orc_reduce_ij_j_f32(gl.data(), gb.data(), 1.0, m, k);
+  CHECK(rel_err(x.native_grad(), gx) <= 1e-4);
+  CHECK(rel_err(A.native_grad(), gA) <= 1e-4);
+  CHECK(rel_err(b.native_grad(), gb) <= 1e-4);
+  mp::optm::SGD sgd{lr, mp::optm::ClipRange()};
+  sgd.update(G);
+  const double inf = INFINITY;
+  orc_sgd_f32(hA.data(), gA.data(), lr, -inf, inf, n * k);
+  orc_sgd_f32(hb.data(), gb.data(), lr, -inf, inf, k);
+  CHECK(rel_err(A.native(), hA) <= 1e-5);
+  CHECK(rel_err(b.native(), hb) <= 1e-4);
+  // timing of the whole step through the host layer (launch-latency bound: 12.6 MFLOP, 0.6 MB)
+  if (timing_iters > 0) {
+    auto step = [&](bool train) {
+      mp::Tensor l2 = mp::ops::linear(x, A, b, "ij,jk->ik");
+      mp::Tensor y2 = mp::ops::selu(l2);
+      if (train) {
+        G->reset(mp::ResetGroup::leaf, mp::ResetComponent::grd);
+        y2.reverse(mp::ReverseCleanup::free);
+        sgd.update(G);
+      } else {
+        mp::stream::sync(stream);
+        y2.free(); l2.free();
+      }
+    };
+    for (int i = 0; i < 20; ++i) step(true);
+    auto t0 = std::chrono::steady_clock::now();
+    for (int i = 0; i < timing_iters; ++i) step(false);
+    auto t1 = std::chrono::steady_clock::now();
+    for (int i = 0; i < timing_iters; ++i) step(true);
+    auto t2 = std::chrono::steady_clock::now();
+    const double fwd_us = std::chrono::duration<double, std::micro>(t1 - t0).count() / timing_iters;
+    const double all_us = std::chrono::duration<double, std::micro>(t2 - t1).count() / timing_iters;
+    std::printf("FEED_FORWARD_TIMING {\"forward_us\": %.2f, \"forward_reverse_sgd_us\": %.2f, \"forward_launches\": 2, "
+                "\"step_launches\": 13, \"iters\": %d}\n", fwd_us, all_us, timing_iters);
+  }
+  G->deinit();
+}
+
+static void scenario_row_ops(mp::Stream stream) {
+  const size_t m = 48, n = 1024;
+  std::vector<float> hx = normal(m * n, 5, 1.f), hgain = normal(n, 6, 0.02f);
+  for (auto& g : hgain) g += 1.f;
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  mp::Tensor x = G->tensor({mp::Class::wgt, mp::Dtype::r32, {m, n}});
+  mp::Tensor gain = G->tensor({mp::Class::wgt, mp::Dtype::r32, {n}});
+  upload(x, hx); upload(gain, hgain);
+  mp::Tensor y = mp::ops::softmax(mp::ops::rmsnorm(x, gain, 1e-6));
+  std::vector<float> rn(m * n), rstd(m), ry(m * n);
+  orc_rmsnorm_ij_j_f32(hx.data(), hgain.data(), 1e-6, rn.data(), rstd.data(), m, n);
+  orc_softmax_ij_j_f32(rn.data(), ry.data(), m, n);
+  CHECK(rel_err(y.native(), ry) <= 1e-4);
+  y.reverse(mp::ReverseCleanup::keep);
+  std::vector<float> ones(m * n, 1.f), gn(m * n, 0.f), gx(m * n, 0.f), gg(n, 0.f);
+  orc_softmax_ij_j_reverse_f32(ry.data(), ones.data(), gn.data(), 0.0, m, n);
+  orc_rmsnorm_ij_j_reverse_f32(hx.data(), hgain.data(), gn.data(), 1e-6, gx.data(), gg.data(), 0.0, m, n);
+  // gradient of sum(softmax) is zero up to rounding: compare on the scale of the activations
+  const std::vector<double> got = x.native_grad();
+  double err = 0;
+  for (size_t i = 0; i < got.size(); ++i) err = std::fmax(err, std::fabs(got[i] - gx[i]));
+  CHECK(err <= 1e-6);
+  G->deinit();
+}
+
+int main(int argc, char** argv) {
+  const int timing_iters = argc > 1 ? std::atoi(argv[1]) : 0;
+  mp::device::init(0);
+  std::printf("device memory: %zu bytes\n", mp::device::total_memory(0));
+  mp::Stream s = mp::stream::init();
+  scenario_subgraphs(s);
+  scenario_experimental(s);
+  scenario_feed_forward(s, timing_iters);
+  scenario_row_ops(s);
+  mp::stream::deinit(s);
+  std::printf(failures == 0 ? "ALL SCENARIOS PASSED\n" : "%d CHECKS FAILED\n", failures);
+  return failures == 0 ? 0 : 1;
+}
