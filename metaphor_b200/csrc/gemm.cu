@@ -10,7 +10,9 @@
 // 128-byte-swizzled shared memory by TMA (one warp's elected thread), a single
 // thread issues tcgen05.mma with the fp32 accumulator tile in TMEM, and four
 // epilogue warps read the accumulator back with tcgen05.ld and apply alpha,
-// beta, bias on the way to global memory.  Transposed operands need no scratch
+// beta, bias on the way to global memory.  The kernel is persistent (one CTA per
+// SM walking the output tiles) with two TMEM accumulators, so one tile's
+// epilogue overlaps the next tile's main loop.  Transposed operands need no scratch
 // copy: the shared-memory descriptor and the instruction descriptor carry the
 // operand's major-ness.  r32 uses kind::tf32 on an error-compensated split
 // (hi + lo, three MMAs) unless MP_GEMM_TF32X1 is set; r64 and shapes TMA cannot
@@ -90,7 +92,9 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ a,
 // ---------------------------------------------------------------------------
 constexpr int BM = 128;               // UMMA M (one TMEM lane per output row)
 constexpr int SWIZZLE_BYTES = 128;    // one operand row / k-row in shared memory
-constexpr int GEMM_THREADS = 192;     // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+constexpr int GEMM_THREADS = 320;     // warp 0: TMA, warp 1: MMA + TMEM, warps 2-9: epilogue
+constexpr int GEMM_MAX_THREADS = 448; // + warps 10-13: operand split (r32)
+constexpr int EPI_THREADS = 256;      // two epilogue warps per TMEM lane quarter, each takes half of the columns
 constexpr int MAX_STAGES = 8;
 
 template <typename T> struct GemmT;
@@ -124,29 +128,45 @@ template <int BN> constexpr int stage_bytes(bool split) {
   return (BM * SWIZZLE_BYTES + BN * SWIZZLE_BYTES) * (split ? 2 : 1);
 }
 
+// Persistent kernel: grid = min(tiles, SMs); every CTA walks output tiles
+// t = blockIdx.x, blockIdx.x + gridDim.x, ... (consecutive tiles share the B
+// tile, which therefore stays in L2).  The shared-memory ring runs across tile
+// boundaries and there are two TMEM accumulators, so the epilogue of tile i
+// (tcgen05.ld -> registers -> global) overlaps the main loop of tile i+1.
+//   warp 0      TMA producer (one elected thread)
+//   warp 1      MMA issuer (one elected thread), owns the TMEM allocation
+//   warps 2-9   epilogue: warp w reads TMEM lane quarter w % 4 and one half of the tile's columns;
+//               32x32 blocks go registers -> shared staging -> TMA store (coalesced, edge-clipped)
+//   warps 10-13 r32 split mode only: write the hi / lo operand tiles
 template <typename T, int BN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                                                                      const __grid_constant__ CUtensorMap tmap_b,
-                                                                      const GemmArgs g) {
+__global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                          const __grid_constant__ CUtensorMap tmap_b,
+                                                                          const __grid_constant__ CUtensorMap tmap_c,
+                                                                          const GemmArgs g) {
   using G = GemmT<T>;
   constexpr int BK = G::BK;
   constexpr int A_BYTES = BM * SWIZZLE_BYTES, B_BYTES = BN * SWIZZLE_BYTES;
   constexpr int KSLICES = BK / G::UMMA_K;  // 4
+  constexpr int ACC_BUFS = 2;
+  constexpr int EPI_TILE_BYTES = 32 * 32 * sizeof(T);   // per-warp staging block for the TMA store
   extern __shared__ unsigned char gemm_smem_raw[];
   // 1024-byte alignment: swizzle atoms are 8 rows x 128 bytes
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
   const int stages = g.stages;
   const int stage_sz = (A_BYTES + B_BYTES) * (g.split ? 2 : 1);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(stages) * stage_sz);
-  uint64_t* ready = full + MAX_STAGES;      // split mode: lo tiles written
+  uint64_t* ready = full + MAX_STAGES;      // split mode: hi / lo tiles written
   uint64_t* empty = ready + MAX_STAGES;
-  uint64_t* acc_full = empty + MAX_STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  uint64_t* acc_full = empty + MAX_STAGES;  // [2] accumulator complete
+  uint64_t* acc_empty = acc_full + ACC_BUFS;  // [2] accumulator drained by the epilogue
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  unsigned char* epi_stage = smem + static_cast<size_t>(stages) * stage_sz + 256;   // 8 warps x EPI_TILE_BYTES
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int num_kb = (g.K + BK - 1) / BK;
+  const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -154,44 +174,49 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       mbar_init(ready + s, 128);
       mbar_init(empty + s, 1);
     }
-    mbar_init(acc_full, 1);
+    for (int a = 0; a < ACC_BUFS; ++a) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, EPI_THREADS); }
     *abort = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_c);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, BN);
+  if (warp == 1) tmem_alloc(tmem_slot, ACC_BUFS * BN);
   tcgen05_fence_before_sync();
   __syncthreads();
   tcgen05_fence_after_sync();
-  const uint32_t tmem_acc = *tmem_slot;
+  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) break;
-        unsigned char* sa = smem + static_cast<size_t>(s) * stage_sz;
-        unsigned char* sb = sa + A_BYTES;
-        mbar_arrive_expect_tx(full + s, A_BYTES + B_BYTES);
-        const int k0 = kb * BK;
-        if (!g.a_mn) {
-          tma_load_2d(sa, &tmap_a, k0, m0, full + s);            // box {BK, BM}
-        } else {
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) { ok = false; break; }
+          unsigned char* sa = smem + static_cast<size_t>(s) * stage_sz;
+          unsigned char* sb = sa + A_BYTES;
+          mbar_arrive_expect_tx(full + s, A_BYTES + B_BYTES);
+          const int k0 = kb * BK;
+          if (!g.a_mn) {
+            tma_load_2d(sa, &tmap_a, k0, m0, full + s);            // box {BK, BM}
+          } else {
 #pragma unroll 1
-          for (int j = 0; j < BM / BK; ++j)                        // boxes {BK along M, BK k-rows}
-            tma_load_2d(sa + j * (BK * SWIZZLE_BYTES), &tmap_a, m0 + j * BK, k0, full + s);
-        }
-        if (!g.b_mn) {
-          tma_load_2d(sb, &tmap_b, k0, n0, full + s);            // box {BK, BN}
-        } else {
+            for (int j = 0; j < BM / BK; ++j)                        // boxes {BK along M, BK k-rows}
+              tma_load_2d(sa + j * (BK * SWIZZLE_BYTES), &tmap_a, m0 + j * BK, k0, full + s);
+          }
+          if (!g.b_mn) {
+            tma_load_2d(sb, &tmap_b, k0, n0, full + s);            // box {BK, BN}
+          } else {
 #pragma unroll 1
-          for (int j = 0; j < BN / BK; ++j)
-            tma_load_2d(sb + j * (BK * SWIZZLE_BYTES), &tmap_b, n0 + j * BK, k0, full + s);
+            for (int j = 0; j < BN / BK; ++j)
+              tma_load_2d(sb + j * (BK * SWIZZLE_BYTES), &tmap_b, n0 + j * BK, k0, full + s);
+          }
+          if (++s == stages) { s = 0; phase ^= 1u; }
         }
-        if (++s == stages) { s = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
@@ -209,41 +234,51 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        uint64_t* wait_on = g.split ? (ready + s) : (full + s);
-        if (!mbar_wait_abortable(wait_on, phase, g.status, abort)) { ok = false; break; }
+      int local = 0;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const uint32_t use = static_cast<uint32_t>(local >> 1);
+        // the epilogue must have drained this accumulator (passes at once on its first use)
+        if (!mbar_wait_abortable(acc_empty + buf, (use & 1u) ^ 1u, g.status, abort)) { ok = false; break; }
         tcgen05_fence_after_sync();
-        const uint32_t sa = mp_smem_u32(smem + static_cast<size_t>(s) * stage_sz);
-        const uint32_t sb = sa + A_BYTES;
-        const uint32_t sa_lo = sb + B_BYTES, sb_lo = sa_lo + A_BYTES;
+        const uint32_t tmem_acc = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          uint64_t* wait_on = g.split ? (ready + s) : (full + s);
+          if (!mbar_wait_abortable(wait_on, phase, g.status, abort)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+          const uint32_t sa = mp_smem_u32(smem + static_cast<size_t>(s) * stage_sz);
+          const uint32_t sb = sa + A_BYTES;
+          const uint32_t sa_lo = sb + B_BYTES, sb_lo = sa_lo + A_BYTES;
 #pragma unroll
-        for (int ks = 0; ks < KSLICES; ++ks) {
-          const uint64_t ad = umma_smem_desc(sa + ks * a_kstep, a_lbo, a_sbo, a_lay);
-          const uint64_t bd = umma_smem_desc(sb + ks * b_kstep, b_lbo, b_sbo, b_lay);
-          umma<G::TF32>(tmem_acc, ad, bd, idesc, (kb | ks) != 0 ? 1u : 0u);
-          if (g.split) {
-            const uint64_t adl = umma_smem_desc(sa_lo + ks * a_kstep, a_lbo, a_sbo, a_lay);
-            const uint64_t bdl = umma_smem_desc(sb_lo + ks * b_kstep, b_lbo, b_sbo, b_lay);
-            umma<G::TF32>(tmem_acc, ad, bdl, idesc, 1u);   // hi * lo
-            umma<G::TF32>(tmem_acc, adl, bd, idesc, 1u);   // lo * hi
+          for (int ks = 0; ks < KSLICES; ++ks) {
+            const uint64_t ad = umma_smem_desc(sa + ks * a_kstep, a_lbo, a_sbo, a_lay);
+            const uint64_t bd = umma_smem_desc(sb + ks * b_kstep, b_lbo, b_sbo, b_lay);
+            umma<G::TF32>(tmem_acc, ad, bd, idesc, (kb | ks) != 0 ? 1u : 0u);
+            if (g.split) {
+              const uint64_t adl = umma_smem_desc(sa_lo + ks * a_kstep, a_lbo, a_sbo, a_lay);
+              const uint64_t bdl = umma_smem_desc(sb_lo + ks * b_kstep, b_lbo, b_sbo, b_lay);
+              umma<G::TF32>(tmem_acc, ad, bdl, idesc, 1u);   // hi * lo
+              umma<G::TF32>(tmem_acc, adl, bd, idesc, 1u);   // lo * hi
+            }
           }
+          umma_commit(empty + s);  // the stage may be refilled once these MMAs have read it
+          if (++s == stages) { s = 0; phase ^= 1u; }
         }
-        umma_commit(empty + s);  // the stage may be refilled once these MMAs have read it
-        if (++s == stages) { s = 0; phase ^= 1u; }
+        if (ok) umma_commit(acc_full + buf);
       }
-      if (ok) umma_commit(acc_full);
     }
-  } else {
-    // ---------------- operand split (r32 only), then epilogue -----------------
-    const int et = threadIdx.x - 64;  // 0..127
-    if (g.split) {
-      // hi = x with the 13 low mantissa bits cleared (exactly representable in
-      // tf32, so the tensor core's own fp32 -> tf32 conversion cannot change it),
-      // lo = x - hi (exact in fp32; its tf32 conversion error is ~2^-21 |x|).
-      int s = 0;
-      uint32_t phase = 0;
+  } else if (warp >= 10) {
+    // ---------------- r32 split mode: hi / lo operand tiles --------------------
+    // hi = x with the 13 low mantissa bits cleared (exactly representable in
+    // tf32, so the tensor core's own fp32 -> tf32 conversion cannot change it),
+    // lo = x - hi (exact in fp32; its tf32 conversion error is ~2^-21 |x|).
+    const int et = threadIdx.x - 320;  // 0..127
+    int s = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait_abortable(full + s, phase, g.status, abort)) break;
+        if (!mbar_wait_abortable(full + s, phase, g.status, abort)) { ok = false; break; }
         unsigned char* hi = smem + static_cast<size_t>(s) * stage_sz;
         unsigned char* lo = hi + A_BYTES + B_BYTES;
         for (int off = et * 16; off < A_BYTES + B_BYTES; off += 128 * 16) {
@@ -262,30 +297,58 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
         if (++s == stages) { s = 0; phase ^= 1u; }
       }
     }
-    const bool acc_ready = mbar_wait_abortable(acc_full, 0, g.status, abort);
-    __syncwarp();  // tcgen05.ld is warp-collective
-    if (acc_ready) {
+  } else {
+    // ------------------------------ epilogue -----------------------------------
+    const int quarter = warp & 3;                 // TMEM lanes this warp may read
+    const int half = (warp - 2) >> 2;             // which half of the tile's columns
+    const T* bias = static_cast<const T*>(g.bias);
+    const bool vec_ok = (static_cast<size_t>(g.N) * sizeof(T)) % 16 == 0 && mp_aligned16(g.c);
+    const bool use_tma = vec_ok && g.beta == 0.0f;   // overwrite: stage 32x32 blocks and let TMA write them
+    unsigned char* stage = epi_stage + (warp - 2) * EPI_TILE_BYTES;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const uint32_t use = static_cast<uint32_t>(local >> 1);
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const bool acc_ready = mbar_wait_abortable(acc_full + buf, use & 1u, g.status, abort);
+      __syncwarp();  // tcgen05.ld is warp-collective
+      if (!acc_ready) break;
       tcgen05_fence_after_sync();
-      const int quarter = warp & 3;                 // TMEM lanes this warp may read
+      const uint32_t tmem_acc = tmem_base + buf * BN;
       const int row = m0 + quarter * 32 + lane;
       T* crow = static_cast<T*>(g.c) + static_cast<size_t>(row) * g.N;
-      const T* bias = static_cast<const T*>(g.bias);
-      const bool vec_ok = (static_cast<size_t>(g.N) * sizeof(T)) % 16 == 0 && mp_aligned16(g.c);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+        const int col0 = n0 + c0;
+        if (col0 >= g.N) break;   // uniform across the warp
         uint32_t v[32];
         tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
         tmem_ld_wait();
-        const int col0 = n0 + c0;
-        if (row < g.M && col0 < g.N) {
-          float r[32];
+        float r[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[j]);
-          if (bias != nullptr) {
+        for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[j]);
+        if (bias != nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < g.N) r[j] += mp_up(bias[col0 + j]);
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < g.N) r[j] += mp_up(bias[col0 + j]);
+        }
+        if (use_tma) {
+          constexpr int PN = Pack<T>::N;
+          if (lane == 0) bulk_wait_read<0>();   // the previous block's store has finished reading the staging buffer
+          __syncwarp();
+          T* srow = reinterpret_cast<T*>(stage) + lane * 32;
+#pragma unroll
+          for (int p = 0; p < 32 / PN; ++p) {
+            const int pp = (p + lane) % (32 / PN);   // rotate the 16-byte slots across lanes (bank conflicts)
+            st_pack(srow, pp, pack<T>(r + pp * PN));
           }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_c, stage, col0, m0 + quarter * 32);
+            bulk_commit();
+          }
+        } else if (row < g.M) {
           if (vec_ok && col0 + 32 <= g.N) {
             constexpr int PN = Pack<T>::N;
             if (g.beta != 0.0f) {
@@ -308,11 +371,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tcgen05_kernel(const __g
           }
         }
       }
+      // hand the accumulator back to the MMA warp
+      tcgen05_fence_before_sync();
+      mbar_arrive(acc_empty + buf);
     }
+    if (use_tma && lane == 0) bulk_wait_all<0>();   // all of this warp's stores have completed
   }
   tcgen05_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_acc, BN);
+  if (warp == 1) tmem_dealloc(tmem_base, ACC_BUFS * BN);
 }
 
 // ---------------------------------------------------------------------------
@@ -352,19 +419,38 @@ CUtensorMap make_map(const void* base, size_t rows, size_t cols, uint32_t box_co
   return map;
 }
 
+// Row-major [rows, cols] output, box {32 cols, 32 rows}, unswizzled.
+template <typename T>
+CUtensorMap make_store_map(void* base, size_t rows, size_t cols) {
+  CUtensorMap map;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * sizeof(T)};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  MP_CU_CHECK(encode_tiled()(&map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return map;
+}
+
 template <typename T, int BN>
-void launch_tc(const T* a, const T* b, const GemmArgs& args, cudaStream_t st) {
+void launch_tc(const T* a, const T* b, const GemmArgs& args, int sm_count, cudaStream_t st) {
   using G = GemmT<T>;
   const int M = args.M, N = args.N, K = args.K;
   // A: K-major [M,K] box {BK, BM};  MN-major [K,M] box {BK (along M), BK (k-rows)}
   // (32-bit MN-major tiles: 128-byte swizzle with 32-byte atoms, the only MN-major layout tf32 accepts)
   const CUtensorMap ta = args.a_mn ? make_map<T>(a, K, M, G::BK, G::BK, G::TF32) : make_map<T>(a, M, K, G::BK, BM);
   const CUtensorMap tb = args.b_mn ? make_map<T>(b, K, N, G::BK, G::BK, G::TF32) : make_map<T>(b, N, K, G::BK, BN);
-  const size_t smem = static_cast<size_t>(args.stages) * stage_bytes<BN>(args.split != 0) + 1024 /*align*/ + 256 /*barriers*/;
+  // C as a TMA store target: 32 x 32 blocks, no swizzle (only used when the row pitch is a multiple of 16 bytes)
+  CUtensorMap tc = ta;
+  if ((static_cast<size_t>(N) * sizeof(T)) % 16 == 0 && mp_aligned16(args.c)) tc = make_store_map<T>(args.c, M, N);
+  const size_t smem = static_cast<size_t>(args.stages) * stage_bytes<BN>(args.split != 0) + 1024 /*align*/ + 256 /*barriers*/ +
+                      8 * 32 * 32 * sizeof(T) /*epilogue staging*/;
   MP_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
-  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  gemm_tcgen05_kernel<T, BN><<<grid, GEMM_THREADS, smem, st>>>(ta, tb, args);
+  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  const int grid = tiles < sm_count ? tiles : sm_count;   // persistent: one CTA per SM
+  gemm_tcgen05_kernel<T, BN><<<grid, args.split ? GEMM_MAX_THREADS : GEMM_THREADS, smem, st>>>(ta, tb, tc, args);
   MP_LAUNCH_CHECK();
 }
 
@@ -421,17 +507,15 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
     args.split = (std::is_same<T, float>::value && !env_flag("MP_GEMM_TF32X1")) ? 1 : 0;
     args.status = state->status_dev;
     const int bn = pick_bn(args.M, args.N, state->sm_count);
-    const int budget = 200 * 1024;
-    auto stages_for = [&](int per_stage) {
+    const int budget = (200 - 8 * static_cast<int>(sizeof(T))) * 1024;   // ring; the rest is epilogue staging
+    auto stages_for = [&](int per_stage) {   // the ring runs across tiles, so depth is bounded by memory only
       int s = budget / per_stage;
       if (s > MAX_STAGES) s = MAX_STAGES;
-      const int kb = (args.K + GemmT<T>::BK - 1) / GemmT<T>::BK;
-      if (s > kb) s = kb < 2 ? 2 : kb;
       return s < 2 ? 2 : s;
     };
-    if (bn == 256) { args.stages = stages_for(stage_bytes<256>(args.split != 0)); launch_tc<T, 256>(a, b, args, st); }
-    else if (bn == 128) { args.stages = stages_for(stage_bytes<128>(args.split != 0)); launch_tc<T, 128>(a, b, args, st); }
-    else { args.stages = stages_for(stage_bytes<64>(args.split != 0)); launch_tc<T, 64>(a, b, args, st); }
+    if (bn == 256) { args.stages = stages_for(stage_bytes<256>(args.split != 0)); launch_tc<T, 256>(a, b, args, state->sm_count, st); }
+    else if (bn == 128) { args.stages = stages_for(stage_bytes<128>(args.split != 0)); launch_tc<T, 128>(a, b, args, state->sm_count, st); }
+    else { args.stages = stages_for(stage_bytes<64>(args.split != 0)); launch_tc<T, 64>(a, b, args, state->sm_count, st); }
   }
 }
 

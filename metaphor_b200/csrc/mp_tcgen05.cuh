@@ -20,6 +20,15 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       : "memory");
 }
 
+// 2-D tile store shared -> global (bulk async group).  Elements outside the
+// tensor are not written, so edge tiles need no masking.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(mp_smem_u32(smem_src)), "r"(x), "r"(y)
+               : "memory");
+}
+
 // ------------------------------ TMEM ---------------------------------------
 // Executed by ONE full warp.  ncols: power of two in [32, 512].  The base
 // address is written to *smem_slot.
