@@ -58,6 +58,14 @@ MP_EXTERN_C len_t mpWorkspaceBytes(StreamContext);
 /* Number of streaming multiprocessors of the stream's device. */
 MP_EXTERN_C uint32_t mpDeviceSmCount(StreamContext);
 
+/* Events: order work across streams without blocking the host (copy-in ->
+ * compute -> copy-out pipelines).  mpStreamWaitEvent makes all later work on
+ * ctx's stream wait for the work recorded by mpEventRecord. */
+MP_EXTERN_C void* mpEventCreate(void);
+MP_EXTERN_C void mpEventDestroy(void* event);
+MP_EXTERN_C void mpEventRecord(void* event, StreamContext);
+MP_EXTERN_C void mpStreamWaitEvent(StreamContext, void* event);
+
 /* Pinned host memory for the end-to-end copy path (the reference copies from
  * pageable memory, src/core/utils.zig:159-218; pinned buffers let
  * mpMemcpyHtoD / mpMemcpyDtoH run at link speed). */

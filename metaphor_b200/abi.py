@@ -82,6 +82,10 @@ UTILS = {
     "mpDeviceSmCount": (U32, [CTX]),
     "mpHostAlloc": (P, [L]),
     "mpHostFree": (None, [P]),
+    "mpEventCreate": (P, []),
+    "mpEventDestroy": (None, [P]),
+    "mpEventRecord": (None, [P, CTX]),
+    "mpStreamWaitEvent": (None, [CTX, P]),
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
     "mpSsdScanScratchBytes": (L, [L, L, L, L, L, L, L, U32]),
     "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),

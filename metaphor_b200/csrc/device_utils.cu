@@ -155,3 +155,18 @@ extern "C" void* mpHostAlloc(len_t N) {
 }
 
 extern "C" void mpHostFree(void* hptr) { MP_CUDA_CHECK(cudaFreeHost(hptr)); }
+
+// Cross-stream ordering for hosts that pipeline copies and kernels over several
+// streams (the reference only offers whole-stream synchronisation).
+extern "C" void* mpEventCreate(void) {
+  cudaEvent_t ev = nullptr;
+  MP_CUDA_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+  return ev;
+}
+extern "C" void mpEventDestroy(void* event) { MP_CUDA_CHECK(cudaEventDestroy(static_cast<cudaEvent_t>(event))); }
+extern "C" void mpEventRecord(void* event, StreamContext ctx) {
+  MP_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(event), mp_stream(ctx)));
+}
+extern "C" void mpStreamWaitEvent(StreamContext ctx, void* event) {
+  MP_CUDA_CHECK(cudaStreamWaitEvent(mp_stream(ctx), static_cast<cudaEvent_t>(event), 0));
+}
