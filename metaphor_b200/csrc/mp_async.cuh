@@ -55,6 +55,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 
+// Same test, but the warp may be suspended by the hardware for up to `hint_ns`
+// while the phase is incomplete (a waiting warp then stops competing for issue
+// slots with the warps that do the work).
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(done)
+      : "r"(mp_smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+
 // Bounded wait for the phase with the given parity.  Returns false (after
 // setting the status word) if the phase did not complete within the limit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status) {
@@ -63,7 +80,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+      if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
     if (mp_globaltimer_ns() - t0 > MP_WAIT_LIMIT_NS) {
       if (status != nullptr) atomicExch(status, MP_STATUS_WAIT_TIMEOUT);
       return false;

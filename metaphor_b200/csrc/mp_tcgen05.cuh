@@ -132,7 +132,7 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
+      if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
     if (*abort != 0) return false;
     if (mp_globaltimer_ns() - t0 > MP_WAIT_LIMIT_NS) {
       *abort = 1;
