@@ -151,12 +151,23 @@ __device__ __forceinline__ Item ssd_item(const SsdArgs& g, int it, int mt, int c
     const int n_diag = g.anti ? (kq - 2 * mt) : (2 * mt + 2);
     const bool has_state = g.anti ? (c < g.nc - 1) : (c > 0);
     const int per = n_diag + (has_state ? g.dk / 64 : 0);
-    const int hh = it / per, w = it % per;
+    const int hh = g.out_head ? 0 : it / per, w = g.out_head ? it : it % per;   // one head per CTA: no division
     r.head = head0 + hh;
     if (w < n_diag) { r.off = 0; r.kb = g.anti ? (2 * mt + w) : w; }
     else { r.off = 1; r.kb = w - n_diag; }
   }
   return r;
+}
+
+// Column factors of the chunk's Q steps for the head whose cum / dt are in shared memory:
+//   causal: colf_j = exp(cum_ref - cum_j) dt_j, ref = last column of j's 64-column k-block
+//   anti  : colf_j = exp(cum_j - cum_ref),      ref = first column of the k-block
+// (never above one).  Called by the 128 transform threads.
+__device__ __forceinline__ void ssd_fill_colf(const SsdArgs& g, const float* cm, const float* dd, float* colf, int et) {
+  for (int t = et; t < g.Q; t += 128) {
+    const int ref = g.anti ? (t & ~63) : (t | 63);
+    colf[t] = g.anti ? ssd_exp(cm[t] - cm[ref]) : ssd_exp(cm[ref] - cm[t]) * dd[t];
+  }
 }
 
 template <int MODE>
@@ -199,7 +210,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
   else if (MODE == MODE_STATES) { head0 = unit; nheads = 1; }
   else { head0 = g.out_head ? unit : unit * hpg; nheads = g.out_head ? 1 : hpg; }
   float* s_dt = s_cum + g.Q;
-  float* s_colf = s_dt + g.Q;   // 64 column factors of the k-block being transformed
+  float* s_colf = s_dt + g.Q;   // [Q] column factors, each 64-column k-block relative to its own reference column
   const int n_items = ssd_num_items<MODE>(g, mt, c, nheads);
   const int tile_n = MODE == MODE_SCORES ? 128 : (MODE == MODE_STATES ? (g.dk == 128 ? g.dv : g.dk) : g.dv);
 
@@ -299,6 +310,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
   } else {
     // ---------------- operand transforms, then the epilogue --------------------
     const int et = threadIdx.x - 64;  // 0..127 = accumulator row
+    if (MODE == MODE_OUTPUT) { ssd_fill_colf(g, s_cum, s_dt, s_colf, et); named_bar_sync(1, 128); }
     if (MODE != MODE_SCORES) {
       int s = 0; uint32_t phase = 0;
       int cur_head = head0;
@@ -313,6 +325,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
             s_dt[t] = g.dtt[o];
           }
           named_bar_sync(1, 128);
+          if (MODE == MODE_OUTPUT) { ssd_fill_colf(g, s_cum, s_dt, s_colf, et); named_bar_sync(1, 128); }
           cur_head = w.head;
         }
         if (!mbar_wait_abortable(full + s, phase, g.status, abort)) break;
@@ -327,18 +340,20 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
             const int t = w.kb * 64 + (r & 63);
             const float wt = g.anti ? ssd_exp(cm[t]) : ssd_exp(last - cm[t]) * dd[t];
             unsigned char* row = sb + (r >> 6) * BOX_BYTES + (r & 63) * 128;
+            uint4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = *reinterpret_cast<uint4*>(row + ((q + r) & 7) * 16);   // rotated: conflict-free
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              const int cp = (q + r) & 7;   // rotate chunks across threads: conflict-free 16-byte accesses
-              uint4 v = *reinterpret_cast<uint4*>(row + cp * 16);
-              __half2* h2 = reinterpret_cast<__half2*>(&v);
+              __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 float2 f = __half22float2(h2[e]);
                 h2[e] = __floats2half2_rn(f.x * wt, f.y * wt);
               }
-              *reinterpret_cast<uint4*>(row + cp * 16) = v;
             }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(row + ((q + r) & 7) * 16) = v[q];
           }
         } else {
           // row i of the K-major A tile (128 B): element j of the k-block sits in 16-byte chunk (j/8) ^ (i%8)
@@ -355,65 +370,90 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
             // k-block can have a positive row exponent; beyond 60 they take the direct form.
             const int jref = g.anti ? w.kb * 64 : w.kb * 64 + 63;
             const float cref = cm[jref];
-            named_bar_sync(2, 128);   // previous item's readers of s_colf are done
-            if (et < 64) {
-              const int j = w.kb * 64 + et;
-              s_colf[et] = g.anti ? ssd_exp(cm[j] - cref) : ssd_exp(cref - cm[j]) * dd[j];
-            }
-            named_bar_sync(2, 128);
             const float rarg = g.anti ? cref - ci : ci - cref;
             const bool direct = rarg > 60.f;
             const float rowf = direct ? 0.f : (g.anti ? ssd_exp(rarg) * dd[i] : ssd_exp(rarg));
-            const bool need_mask = g.anti ? (w.kb * 64 < mt * 128 + 128 && w.kb * 64 + 63 >= mt * 128 && w.kb * 64 < i)
-                                          : (w.kb * 64 + 63 > i);
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const int cp = (q + et) & 7;
-              const int jl = (cp ^ (et & 7)) << 3;      // first column of this chunk inside the k-block
-              const int j0 = w.kb * 64 + jl;
-              uint4 v = *reinterpret_cast<uint4*>(row + cp * 16);
-              __half2* h2 = reinterpret_cast<__half2*>(&v);
-              const float4 c0 = *reinterpret_cast<const float4*>(s_colf + jl);
-              const float4 c1 = *reinterpret_cast<const float4*>(s_colf + jl + 4);
-              float cf[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-              if (direct) {
+            const float* colf = s_colf + w.kb * 64;
+            const int sw = et & 7;
+            const int iloc = i - w.kb * 64;              // this row relative to the first column of the k-block
+            const int wlo = iloc - lane, whi = wlo + 31; // the warp's 32 consecutive rows
+            if (__any_sync(0xffffffffu, direct)) {
+              // rare: some row of the warp cannot use the factorised form
+#pragma unroll 1
+              for (int jc = 0; jc < 8; ++jc) {
+                uint4 v = *reinterpret_cast<uint4*>(row + ((jc ^ sw) << 4));
+                __half2* h2 = reinterpret_cast<__half2*>(&v);
+                float cf[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                  const int j = j0 + e;
-                  cf[e] = g.anti ? ssd_exp(cm[j] - ci) * dd[i] : ssd_exp(ci - cm[j]) * dd[j];
+                  const int jl = jc * 8 + e, j = w.kb * 64 + jl;
+                  float f = direct ? (g.anti ? ssd_exp(cm[j] - ci) * dd[i] : ssd_exp(ci - cm[j]) * dd[j]) : colf[jl] * rowf;
+                  if (g.anti ? (jl < iloc) : (jl > iloc)) f = 0.f;
+                  cf[e] = f;
                 }
-              } else {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) cf[e] *= rowf;
-              }
-              if (need_mask) {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                  const int j = j0 + e;
-                  if (g.anti ? (j < i) : (j > i)) cf[e] = 0.f;
+                for (int e = 0; e < 4; ++e) {
+                  const float2 f = __half22float2(h2[e]);
+                  h2[e] = __floats2half2_rn(f.x * cf[2 * e], f.y * cf[2 * e + 1]);
                 }
+                *reinterpret_cast<uint4*>(row + ((jc ^ sw) << 4)) = v;
               }
+            } else {
+              // Logical chunk jc (columns 8 jc .. 8 jc + 7) sits at physical chunk jc ^ (row % 8): the eight
+              // rows of a quarter-warp touch eight different chunks, so the accesses are conflict-free and
+              // the column factors are the same for the whole warp.  Four chunks at a time, loads first
+              // (the tile is rewritten in place, which keeps the compiler from hoisting loads over stores).
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 f = __half22float2(h2[e]);
-                h2[e] = __floats2half2_rn(f.x * cf[2 * e], f.y * cf[2 * e + 1]);
+              for (int qb = 0; qb < 8; qb += 4) {
+                uint4 v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) v[q] = *reinterpret_cast<uint4*>(row + (((qb + q) ^ sw) << 4));
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const int jl = (qb + q) * 8;
+                  // mask class of this chunk for the warp's rows (warp-uniform)
+                  const bool all_zero = g.anti ? (jl + 7 < wlo) : (jl > whi);
+                  const bool all_keep = g.anti ? (jl >= whi) : (jl + 7 <= wlo);
+                  if (all_zero) {
+                    v[q] = make_uint4(0u, 0u, 0u, 0u);
+                  } else {
+                    const float4 c0 = *reinterpret_cast<const float4*>(colf + jl);
+                    const float4 c1 = *reinterpret_cast<const float4*>(colf + jl + 4);
+                    float cf[8] = {c0.x * rowf, c0.y * rowf, c0.z * rowf, c0.w * rowf,
+                                   c1.x * rowf, c1.y * rowf, c1.z * rowf, c1.w * rowf};
+                    if (!all_keep) {
+#pragma unroll
+                      for (int e = 0; e < 8; ++e)
+                        if (g.anti ? (jl + e < iloc) : (jl + e > iloc)) cf[e] = 0.f;
+                    }
+                    __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 f = __half22float2(h2[e]);
+                      h2[e] = __floats2half2_rn(f.x * cf[2 * e], f.y * cf[2 * e + 1]);
+                    }
+                  }
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(row + (((qb + q) ^ sw) << 4)) = v[q];
               }
-              *reinterpret_cast<uint4*>(row + cp * 16) = v;
             }
           } else {
             const float fi = g.anti ? ssd_exp(cm[g.Q - 1] - ci) * dd[i] : ssd_exp(ci);
+            uint4 v[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) v[q] = *reinterpret_cast<uint4*>(row + ((q ^ (et & 7)) << 4));
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
-              const int cp = (q + et) & 7;
-              uint4 v = *reinterpret_cast<uint4*>(row + cp * 16);
-              __half2* h2 = reinterpret_cast<__half2*>(&v);
+              __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 float2 f = __half22float2(h2[e]);
                 h2[e] = __floats2half2_rn(f.x * fi, f.y * fi);
               }
-              *reinterpret_cast<uint4*>(row + cp * 16) = v;
             }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(row + ((q ^ (et & 7)) << 4)) = v[q];
           }
         }
         fence_proxy_async_smem();
@@ -634,7 +674,7 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
     g.stage_bytes = TILE_BYTES + b_tile_bytes;
     g.stages = 2;
     g.tmem_cols = tile_cols <= 32 ? 32 : (tile_cols <= 64 ? 64 : 128);
-    return static_cast<size_t>(g.stages) * g.stage_bytes + 1024 + 256 + 2 * d.Q * 4 + 64 * 4;
+    return static_cast<size_t>(g.stages) * g.stage_bytes + 1024 + 256 + 3 * d.Q * 4;
   };
   const int sunits = r.scores_head ? d.H : d.G;
   const int d2 = r.dk == 128 ? r.dv : r.dk;   // columns of a stored state block ([128][d2])
