@@ -31,6 +31,9 @@
 
 namespace {
 
+#ifndef SSD_XF
+#define SSD_XF 2   // chunks per iteration of the (rolled) transform loops: compact code, two loads in flight
+#endif
 constexpr int SSD_THREADS = 192;  // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: transform + epilogue
 constexpr int SSD_MAX_STAGES = 4;
 constexpr int TILE_BYTES = 128 * 128;  // one operand tile: 128 rows x 128 B, or two 64x64 MN-major boxes
@@ -340,20 +343,23 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
             const int t = w.kb * 64 + (r & 63);
             const float wt = g.anti ? ssd_exp(cm[t]) : ssd_exp(last - cm[t]) * dd[t];
             unsigned char* row = sb + (r >> 6) * BOX_BYTES + (r & 63) * 128;
-            uint4 v[8];
+#pragma unroll 1
+            for (int qb = 0; qb < 8; qb += SSD_XF) {
+              uint4 v[SSD_XF];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) v[q] = *reinterpret_cast<uint4*>(row + ((q + r) & 7) * 16);   // rotated: conflict-free
+              for (int q = 0; q < SSD_XF; ++q) v[q] = *reinterpret_cast<uint4*>(row + (((qb + q) ^ (r & 7)) << 4));   // conflict-free
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
+              for (int q = 0; q < SSD_XF; ++q) {
+                __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float2 f = __half22float2(h2[e]);
-                h2[e] = __floats2half2_rn(f.x * wt, f.y * wt);
+                for (int e = 0; e < 4; ++e) {
+                  float2 f = __half22float2(h2[e]);
+                  h2[e] = __floats2half2_rn(f.x * wt, f.y * wt);
+                }
               }
-            }
 #pragma unroll
-            for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(row + ((q + r) & 7) * 16) = v[q];
+              for (int q = 0; q < SSD_XF; ++q) *reinterpret_cast<uint4*>(row + (((qb + q) ^ (r & 7)) << 4)) = v[q];
+            }
           }
         } else {
           // row i of the K-major A tile (128 B): element j of the k-block sits in 16-byte chunk (j/8) ^ (i%8)
@@ -403,13 +409,13 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
               // rows of a quarter-warp touch eight different chunks, so the accesses are conflict-free and
               // the column factors are the same for the whole warp.  Four chunks at a time, loads first
               // (the tile is rewritten in place, which keeps the compiler from hoisting loads over stores).
+#pragma unroll 1
+              for (int qb = 0; qb < 8; qb += SSD_XF) {
+                uint4 v[SSD_XF];
 #pragma unroll
-              for (int qb = 0; qb < 8; qb += 4) {
-                uint4 v[4];
+                for (int q = 0; q < SSD_XF; ++q) v[q] = *reinterpret_cast<uint4*>(row + (((qb + q) ^ sw) << 4));
 #pragma unroll
-                for (int q = 0; q < 4; ++q) v[q] = *reinterpret_cast<uint4*>(row + (((qb + q) ^ sw) << 4));
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
+                for (int q = 0; q < SSD_XF; ++q) {
                   const int jl = (qb + q) * 8;
                   // mask class of this chunk for the warp's rows (warp-uniform)
                   const bool all_zero = g.anti ? (jl + 7 < wlo) : (jl > whi);
@@ -435,25 +441,28 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
                   }
                 }
 #pragma unroll
-                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(row + (((qb + q) ^ sw) << 4)) = v[q];
+                for (int q = 0; q < SSD_XF; ++q) *reinterpret_cast<uint4*>(row + (((qb + q) ^ sw) << 4)) = v[q];
               }
             }
           } else {
             const float fi = g.anti ? ssd_exp(cm[g.Q - 1] - ci) * dd[i] : ssd_exp(ci);
-            uint4 v[8];
+#pragma unroll 1
+            for (int qb = 0; qb < 8; qb += SSD_XF) {
+              uint4 v[SSD_XF];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) v[q] = *reinterpret_cast<uint4*>(row + ((q ^ (et & 7)) << 4));
+              for (int q = 0; q < SSD_XF; ++q) v[q] = *reinterpret_cast<uint4*>(row + (((qb + q) ^ (et & 7)) << 4));
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
+              for (int q = 0; q < SSD_XF; ++q) {
+                __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
 #pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                float2 f = __half22float2(h2[e]);
-                h2[e] = __floats2half2_rn(f.x * fi, f.y * fi);
+                for (int e = 0; e < 4; ++e) {
+                  float2 f = __half22float2(h2[e]);
+                  h2[e] = __floats2half2_rn(f.x * fi, f.y * fi);
+                }
               }
-            }
 #pragma unroll
-            for (int q = 0; q < 8; ++q) *reinterpret_cast<uint4*>(row + ((q ^ (et & 7)) << 4)) = v[q];
+              for (int q = 0; q < SSD_XF; ++q) *reinterpret_cast<uint4*>(row + (((qb + q) ^ (et & 7)) << 4)) = v[q];
+            }
           }
         }
         fence_proxy_async_smem();
