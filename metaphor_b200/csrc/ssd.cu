@@ -341,7 +341,8 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
           const float last = cm[g.Q - 1];
           for (int r = et; r < (tile_n / 64) * 64; r += 128) {
             const int t = w.kb * 64 + (r & 63);
-            const float wt = g.anti ? ssd_exp(cm[t]) : ssd_exp(last - cm[t]) * dd[t];
+            const float wt = g.anti ? ssd_exp(cm[t]) : ssd_exp(last - cm[t]) * dd[t];   // <= 1
+            const __half2 wt2 = __float2half2_rn(wt);
             unsigned char* row = sb + (r >> 6) * BOX_BYTES + (r & 63) * 128;
 #pragma unroll 1
             for (int qb = 0; qb < 8; qb += SSD_XF) {
@@ -352,10 +353,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
               for (int q = 0; q < SSD_XF; ++q) {
                 __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float2 f = __half22float2(h2[e]);
-                  h2[e] = __floats2half2_rn(f.x * wt, f.y * wt);
-                }
+                for (int e = 0; e < 4; ++e) h2[e] = __hmul2(h2[e], wt2);
               }
 #pragma unroll
               for (int q = 0; q < SSD_XF; ++q) *reinterpret_cast<uint4*>(row + (((qb + q) ^ (r & 7)) << 4)) = v[q];
@@ -432,12 +430,10 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
                       for (int e = 0; e < 8; ++e)
                         if (g.anti ? (jl + e < iloc) : (jl + e > iloc)) cf[e] = 0.f;
                     }
+                    // the factor is formed in fp32 and rounded once; the product is a packed half multiply
                     __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                      const float2 f = __half22float2(h2[e]);
-                      h2[e] = __floats2half2_rn(f.x * cf[2 * e], f.y * cf[2 * e + 1]);
-                    }
+                    for (int e = 0; e < 4; ++e) h2[e] = __hmul2(h2[e], __floats2half2_rn(cf[2 * e], cf[2 * e + 1]));
                   }
                 }
 #pragma unroll
@@ -445,7 +441,8 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
               }
             }
           } else {
-            const float fi = g.anti ? ssd_exp(cm[g.Q - 1] - ci) * dd[i] : ssd_exp(ci);
+            const float fi = g.anti ? ssd_exp(cm[g.Q - 1] - ci) * dd[i] : ssd_exp(ci);   // <= 1
+            const __half2 fi2 = __float2half2_rn(fi);
 #pragma unroll 1
             for (int qb = 0; qb < 8; qb += SSD_XF) {
               uint4 v[SSD_XF];
@@ -455,10 +452,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
               for (int q = 0; q < SSD_XF; ++q) {
                 __half2* h2 = reinterpret_cast<__half2*>(&v[q]);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  float2 f = __half22float2(h2[e]);
-                  h2[e] = __floats2half2_rn(f.x * fi, f.y * fi);
-                }
+                for (int e = 0; e < 4; ++e) h2[e] = __hmul2(h2[e], fi2);
               }
 #pragma unroll
               for (int q = 0; q < SSD_XF; ++q) *reinterpret_cast<uint4*>(row + (((qb + q) ^ (et & 7)) << 4)) = v[q];
