@@ -224,13 +224,6 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, g.tmem_cols);
-  if (MODE != MODE_SCORES) {   // factors of the first head; later heads are reloaded by the transform warps
-    for (int t = threadIdx.x; t < g.Q; t += SSD_THREADS) {
-      const size_t o = (static_cast<size_t>(b) * g.H + head0) * g.L + c * g.Q + t;
-      s_cum[t] = g.cum[o];
-      s_dt[t] = g.dtt[o];
-    }
-  }
   tcgen05_fence_before_sync();
   __syncthreads();
   tcgen05_fence_after_sync();
@@ -313,15 +306,15 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
   } else {
     // ---------------- operand transforms, then the epilogue --------------------
     const int et = threadIdx.x - 64;  // 0..127 = accumulator row
-    if (MODE == MODE_OUTPUT) { ssd_fill_colf(g, s_cum, s_dt, s_colf, et); named_bar_sync(1, 128); }
     if (MODE != MODE_SCORES) {
       int s = 0; uint32_t phase = 0;
-      int cur_head = head0;
+      int cur_head = -1;
       for (int it = 0; it < n_items; ++it) {
         const Item w = ssd_item<MODE>(g, it, mt, c, head0);
         if (w.head != cur_head) {
-          // next head of the group: swap in its decay / dt factors (only these four warps read them)
-          named_bar_sync(1, 128);
+          // (next) head: bring in its decay / dt factors; only these four warps read them, and the
+          // TMA producer is already fetching tiles meanwhile
+          if (cur_head >= 0) named_bar_sync(1, 128);
           for (int t = et; t < g.Q; t += 128) {
             const size_t o = (static_cast<size_t>(b) * g.H + w.head) * g.L + c * g.Q + t;
             s_cum[t] = g.cum[o];
@@ -467,9 +460,32 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
     const bool acc_ready = n_items > 0 ? mbar_wait_abortable(acc_full, 0, g.status, abort) : true;
     __syncwarp();
     if (acc_ready) {
+      // The accumulator leaves through shared memory: every thread owns one row in TMEM, which as a
+      // direct store would touch 32 different lines per instruction.  The pipeline stages are idle once
+      // acc_full has fired, so the warp parks its 32 rows there (16-byte chunks XOR-swizzled by row,
+      // conflict-free) and then writes them out with whole rows per instruction.
       tcgen05_fence_after_sync();
       const int quarter = warp & 3;
       const int row = quarter * 32 + lane;   // accumulator row of this thread
+      const int RB = tile_n * (MODE == MODE_STATES ? 4 : 2);   // bytes of one staged row
+      unsigned char* stg_row = smem + row * RB;
+      const int cpr = RB >> 4;             // 16-byte chunks per row: 8, 16 or 32
+      const int rpi = 32 / cpr;            // rows moved per warp instruction
+      const int cc = lane % cpr;
+      // Row dots <z, out> use the fp32 accumulator (u - v cancels downstream, so the rounded output
+      // is not accurate enough): the z tile is parked behind the output tile with coalesced loads.
+      const bool with_dot = MODE == MODE_OUTPUT && g.z != nullptr;
+      unsigned char* zst = smem + 128 * RB;
+      if (with_dot) {
+#pragma unroll 4
+        for (int rr = 0; rr < 32; rr += rpi) {
+          const int lrow = quarter * 32 + rr + lane / cpr;
+          const size_t trow = static_cast<size_t>(r0 + mt * 128 + lrow);
+          *reinterpret_cast<uint4*>(zst + lrow * RB + ((cc ^ (lrow & 7)) << 4)) =
+              *reinterpret_cast<const uint4*>(g.z + trow * g.z_pitch + unit * g.dv + cc * 8);
+        }
+        __syncwarp();
+      }
       float dot = 0.f;
 #pragma unroll 1
       for (int c0 = 0; c0 < tile_n; c0 += 32) {
@@ -481,39 +497,52 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
-        float r[32];
+        if (MODE == MODE_STATES) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = __uint_as_float(v[j]);
-        if (MODE == MODE_SCORES) {
-          const int su = g.scores_head ? g.H : g.G;
-          __half* dst = g.g_out + (static_cast<size_t>((b * g.nc + c) * su + unit) * g.Q + mt * 128 + row) * g.Q + nt * 128 + c0;
-#pragma unroll
-          for (int p = 0; p < 4; ++p) st_pack(dst, p, pack<__half>(r + p * 8));
-        } else if (MODE == MODE_STATES) {
-          float* dst = g.s_out + (static_cast<size_t>((b * g.H + unit) * g.nc + c) * 128 + row) * tile_n + c0;
-#pragma unroll
-          for (int p = 0; p < 8; ++p) *reinterpret_cast<float4*>(dst + p * 4) = make_float4(r[p * 4], r[p * 4 + 1], r[p * 4 + 2], r[p * 4 + 3]);
+          for (int p = 0; p < 8; ++p)
+            *reinterpret_cast<uint4*>(stg_row + (((c0 / 4 + p) ^ (row & 7)) << 4)) = make_uint4(v[p * 4], v[p * 4 + 1], v[p * 4 + 2], v[p * 4 + 3]);
         } else {
-          const size_t trow = static_cast<size_t>(r0 + mt * 128 + row);
-          if (g.z != nullptr) {
-            const __half* zr = g.z + trow * g.z_pitch + unit * g.dv + c0;
 #pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              float zf[8];
-              unpack<__half>(ld_pack(zr, p), zf);
+          for (int p = 0; p < 4; ++p) {
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) dot += zf[e] * r[p * 8 + e];
+            for (int e = 0; e < 4; ++e) {
+              const __half2 h = __floats2half2_rn(__uint_as_float(v[p * 8 + 2 * e]), __uint_as_float(v[p * 8 + 2 * e + 1]));
+              ow[e] = *reinterpret_cast<const uint32_t*>(&h);
             }
-          }
-          if (g.o_out != nullptr) {
-            __half* dst = g.o_out + trow * g.o_pitch + unit * g.dv + c0;
+            *reinterpret_cast<uint4*>(stg_row + (((c0 / 8 + p) ^ (row & 7)) << 4)) = o;
+            if (with_dot) {
+              const uint4 zv = *reinterpret_cast<const uint4*>(zst + row * RB + (((c0 / 8 + p) ^ (row & 7)) << 4));
+              const __half2* z2 = reinterpret_cast<const __half2*>(&zv);
 #pragma unroll
-            for (int p = 0; p < 4; ++p) st_pack(dst, p, pack<__half>(r + p * 8));
+              for (int e = 0; e < 4; ++e) {
+                const float2 zf = __half22float2(z2[e]);
+                dot += zf.x * __uint_as_float(v[p * 8 + 2 * e]) + zf.y * __uint_as_float(v[p * 8 + 2 * e + 1]);
+              }
+            }
           }
         }
       }
-      if (MODE == MODE_OUTPUT && g.z != nullptr && g.dot_out != nullptr)
+      if (with_dot && g.dot_out != nullptr)
         g.dot_out[(static_cast<size_t>(b) * g.H + unit) * g.L + c * g.Q + mt * 128 + row] = dot;
+      __syncwarp();
+#pragma unroll 1
+      for (int rr = 0; rr < 32; rr += rpi) {
+        const int lrow = quarter * 32 + rr + lane / cpr;
+        const uint4 val = *reinterpret_cast<const uint4*>(smem + lrow * RB + ((cc ^ (lrow & 7)) << 4));
+        if (MODE == MODE_SCORES) {
+          const int su = g.scores_head ? g.H : g.G;
+          __half* dst = g.g_out + (static_cast<size_t>((b * g.nc + c) * su + unit) * g.Q + mt * 128 + lrow) * g.Q + nt * 128;
+          *reinterpret_cast<uint4*>(dst + cc * 8) = val;
+        } else if (MODE == MODE_STATES) {
+          float* dst = g.s_out + (static_cast<size_t>((b * g.H + unit) * g.nc + c) * 128 + lrow) * tile_n;
+          *reinterpret_cast<uint4*>(dst + cc * 4) = val;
+        } else {
+          const size_t trow = static_cast<size_t>(r0 + mt * 128 + lrow);
+          if (g.o_out != nullptr) *reinterpret_cast<uint4*>(g.o_out + trow * g.o_pitch + unit * g.dv + cc * 8) = val;
+        }
+      }
     }
   }
   tcgen05_fence_before_sync();
