@@ -151,6 +151,47 @@ MP_DECL3(ssd_scan, const void* x, const void* dt, const void* A, const void* B, 
 MP_DECL3(ssd_scan_reverse, const void* x, const void* dt, const void* A, const void* B, const void* C, const void* gy, void* gx, void* gdt, void* gA, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
 MP_EXTERN_C len_t mpSsdScanScratchBytes(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, uint32_t reverse);
 
+/* ---- operators around the scan in a Mamba-2 language-model step ------------
+ * No counterpart in the reference (its loss layer is a sketch,
+ * src/ops/loss.zig:60-237; the model is named by the project's roadmap only).
+ * "acc" below is the accumulator type of T: r32 for r16 and r32, r64 for r64.
+ * Parameter gradients and per-head parameters use acc; they are ACCUMULATED
+ * (+=), the caller zeroes them once per step.  Pitches are in elements. */
+
+/* out[t,:] = table[ids[t],:]; ids: int32; ids outside [0, vocab) give a zero row */
+MP_DECL3(embedding, const void* table, const void* ids, void* out, len_t n, len_t dim, len_t vocab, StreamContext stream)
+/* gtable[ids[t],:] += gy[t,:]; gtable: acc [vocab, dim] */
+MP_DECL3(embedding_reverse, const void* ids, const void* gy, void* gtable, len_t n, len_t dim, len_t vocab, StreamContext stream)
+/* Depthwise causal convolution + SiLU over x[batch, len, channels] (row pitch
+ * x_pitch): pre = bias[c] + sum_k w[c,k] x[b, l-width+1+k, c] (zero before the
+ * sequence), y = pre*sigmoid(pre).  w: [channels, width] of T, width 2..4;
+ * bias may be NULL. */
+MP_DECL3(causal_conv1d_silu, const void* x, len_t x_pitch, const void* w, const void* bias, void* y, len_t y_pitch, len_t batch, len_t len, len_t channels, len_t width, StreamContext stream)
+/* gx (overwritten), gw += (acc [channels, width]), gbias += (acc [channels], may be NULL) */
+MP_DECL3(causal_conv1d_silu_reverse, const void* x, len_t x_pitch, const void* w, const void* bias, const void* gy, len_t gy_pitch, void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t channels, len_t width, StreamContext stream)
+/* out[r,h] = softplus(raw[r,h] + bias[h]); raw: T with row pitch; bias, out: acc */
+MP_DECL3(softplus_bias, const void* raw, len_t raw_pitch, const void* bias, void* out, len_t rows, len_t heads, StreamContext stream)
+/* graw[r,h] = gdt[r,h]*sigmoid(raw[r,h] + bias[h]) (T, pitched); gbias[h] += sum_r graw (acc, may be NULL) */
+MP_DECL3(softplus_bias_reverse, const void* raw, len_t raw_pitch, const void* bias, const void* gdt, void* graw, len_t graw_pitch, void* gbias, len_t rows, len_t heads, StreamContext stream)
+/* u = (y + D[h]*x) * silu(z); y, x, u: [rows, heads*headdim]; z pitched; D: acc [heads] or NULL */
+MP_DECL3(ssd_gate, const void* y, const void* x, const void* D, const void* z, len_t z_pitch, void* u, len_t rows, len_t heads, len_t headdim, StreamContext stream)
+/* gy = gu*silu(z); gz = gu*(y + D x)*silu'(z) (pitched); gD[h] += sum gy*x (acc, may be NULL).
+ * The skip's share of gx is added afterwards with launch_head_scale_accumulate. */
+MP_DECL3(ssd_gate_reverse, const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gu, void* gy, void* gz, len_t gz_pitch, void* gD, len_t rows, len_t heads, len_t headdim, StreamContext stream)
+/* gx[r,h,:] += D[h]*gy[r,h,:] */
+MP_DECL3(head_scale_accumulate, const void* D, const void* gy, void* gx, len_t rows, len_t heads, len_t headdim, StreamContext stream)
+/* Cross-entropy of logits [m, n] against int32 targets, loss and gradient in one pass:
+ *   loss[i] = logsumexp_j(logits[i,:]) - logits[i,target_i]               (acc [m], may be NULL)
+ *   glogits[i,j] = scale*(softmax(logits[i,:])_j - [j == target_i])       (T, may alias logits, may be NULL)
+ * Rows whose target lies outside [0, n) contribute zero loss and zero gradient. */
+MP_DECL3(cross_entropy, const void* logits, const void* targets, double scale, void* loss, void* glogits, len_t m, len_t n, StreamContext stream)
+/* dst = -exp(src) (the scan's decay parameter A from its logarithm) */
+MP_DECL3(neg_exp, const void* src, void* dst, len_t n, StreamContext stream)
+/* Precision conversion between r16 working copies and r32 master buffers:
+ * dst(r32) = src(r16) + beta*dst;  dst(r16) = round(src(r32)). */
+MP_EXTERN_C void launch_convert_r16_r32(const void* src, void* dst, double beta, len_t n, StreamContext stream);
+MP_EXTERN_C void launch_convert_r32_r16(const void* src, void* dst, len_t n, StreamContext stream);
+
 /* Status word values returned by mpGetStatus (mp_device_utils.h). */
 #define MP_STATUS_OK             0u
 #define MP_STATUS_WAIT_TIMEOUT   1u  /* a bounded mbarrier wait gave up    */

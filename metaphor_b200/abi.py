@@ -61,6 +61,18 @@ LAUNCHERS = {
     "linear_ij_jk_ik": [P, P, P, D, P, D, L, L, L, CTX],
     "ssd_scan": [P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
     "ssd_scan_reverse": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
+    # operators around the scan in a language-model step
+    "embedding": [P, P, P, L, L, L, CTX],
+    "embedding_reverse": [P, P, P, L, L, L, CTX],
+    "causal_conv1d_silu": [P, L, P, P, P, L, L, L, L, L, CTX],
+    "causal_conv1d_silu_reverse": [P, L, P, P, P, L, P, L, P, P, L, L, L, L, CTX],
+    "softplus_bias": [P, L, P, P, L, L, CTX],
+    "softplus_bias_reverse": [P, L, P, P, P, L, P, L, L, CTX],
+    "ssd_gate": [P, P, P, P, L, P, L, L, L, CTX],
+    "ssd_gate_reverse": [P, P, P, P, L, P, P, P, L, P, L, L, L, CTX],
+    "head_scale_accumulate": [P, P, P, L, L, L, CTX],
+    "cross_entropy": [P, P, D, P, P, L, L, CTX],
+    "neg_exp": [P, P, L, CTX],
 }
 
 # name -> (restype, argtypes)
@@ -89,6 +101,8 @@ UTILS = {
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
     "mpSsdScanScratchBytes": (L, [L, L, L, L, L, L, L, U32]),
     "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),
+    "launch_convert_r16_r32": (None, [P, P, D, L, CTX]),
+    "launch_convert_r32_r16": (None, [P, P, L, CTX]),
     # include/mp_comm.h
     "mpCommGetUniqueId": (None, [P]),
     "mpCommInit": (P, [P, U32, U32]),

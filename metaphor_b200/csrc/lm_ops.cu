@@ -1,0 +1,743 @@
+// Operators that sit between the contractions, the RMSNorm and the SSD scan in a
+// Mamba-2 language-model step: token embedding, depthwise causal convolution +
+// SiLU, softplus of the step sizes, D-skip + SiLU gate, cross-entropy (loss and
+// logit gradient in one kernel) and precision conversion between r16 working
+// copies and r32 master buffers.  The reference has none of these (its loss
+// layer is a sketch, src/ops/loss.zig:60-237); they follow its launcher
+// conventions: inputs, scalars, outputs, sizes, StreamContext last.
+//
+// All of them are HBM-bound: every tensor is read once and written once with
+// 16-byte accesses; small parameter gradients (conv taps, biases, D) are reduced
+// inside the CTA and added with one atomic per CTA and element.  Parameter
+// gradients and per-head parameters are kept in the accumulator type (r32 for
+// r16 / r32 tensors, r64 for r64).
+#include "mp_common.cuh"
+
+namespace {
+
+template <typename T, int V>
+struct alignas(sizeof(T) * V) VecT { T v[V]; };
+
+template <typename T, int V>
+__device__ __forceinline__ void load_vec(const T* p, typename Acc<T>::type* out) {
+  const VecT<T, V> x = *reinterpret_cast<const VecT<T, V>*>(p);
+#pragma unroll
+  for (int e = 0; e < V; ++e) out[e] = mp_up(x.v[e]);
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_vec(T* p, const typename Acc<T>::type* in) {
+  VecT<T, V> x;
+#pragma unroll
+  for (int e = 0; e < V; ++e) x.v[e] = mp_down<T>(in[e]);
+  *reinterpret_cast<VecT<T, V>*>(p) = x;
+}
+
+__device__ __forceinline__ float sigmoid_a(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ double sigmoid_a(double x) { return 1.0 / (1.0 + exp(-x)); }
+__device__ __forceinline__ float exp_a(float x) { return __expf(x); }
+__device__ __forceinline__ double exp_a(double x) { return exp(x); }
+__device__ __forceinline__ float log_a(float x) { return __logf(x); }
+__device__ __forceinline__ double log_a(double x) { return log(x); }
+__device__ __forceinline__ float log1p_a(float x) { return log1pf(x); }
+__device__ __forceinline__ double log1p_a(double x) { return log1p(x); }
+
+// true when V-wide accesses at base + k * pitch (+ multiples of V) are aligned
+template <typename T>
+bool vec_ok(const void* p, size_t pitch, size_t width) {
+  constexpr size_t PN = Pack<T>::N;
+  return mp_aligned16(p) && pitch % PN == 0 && width % PN == 0;
+}
+
+// ---------------------------------------------------------------------------
+// embedding: out[t, :] = table[ids[t], :]; ids outside [0, vocab) give a zero row
+// ---------------------------------------------------------------------------
+template <typename T, int V>
+__global__ void __launch_bounds__(256) embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                                        T* __restrict__ out, size_t n, size_t dim, size_t vocab) {
+  const size_t per_row = dim / V;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n * per_row;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = i / per_row, p = i % per_row;
+    const long long id = ids[t];
+    VecT<T, V> x;
+    if (id >= 0 && static_cast<size_t>(id) < vocab) {
+      x = *reinterpret_cast<const VecT<T, V>*>(table + static_cast<size_t>(id) * dim + p * V);
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) x.v[e] = mp_down<T>(0);
+    }
+    *reinterpret_cast<VecT<T, V>*>(out + t * dim + p * V) = x;
+  }
+}
+
+// gtable[ids[t], :] += gy[t, :]   (accumulator-typed table gradient, atomics)
+template <typename T>
+__global__ void __launch_bounds__(256) embedding_reverse_kernel(const int* __restrict__ ids, const T* __restrict__ gy,
+                                                                typename Acc<T>::type* __restrict__ gtable, size_t n,
+                                                                size_t dim, size_t vocab) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n * dim;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = i / dim, j = i % dim;
+    const long long id = ids[t];
+    if (id >= 0 && static_cast<size_t>(id) < vocab) atomicAdd(gtable + static_cast<size_t>(id) * dim + j, mp_up(gy[i]));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// depthwise causal convolution + SiLU over [batch, len, channels] (pitched rows)
+//   pre[b,l,c] = bias[c] + sum_k w[c,k] x[b, l - W + 1 + k, c]   (x = 0 before the sequence)
+//   y = pre * sigmoid(pre)
+// CTA = 32 channel groups x 8 time lanes, every thread walks CONV_LT steps with
+// the last W inputs in registers.
+// ---------------------------------------------------------------------------
+constexpr int CONV_LT = 16;
+constexpr int CONV_TY = 8;
+
+template <typename T, int V, int W>
+__global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_kernel(const T* __restrict__ x, size_t xp, const T* __restrict__ w,
+                                                                  const T* __restrict__ bias, T* __restrict__ y, size_t yp,
+                                                                  int L, int C) {
+  using A = typename Acc<T>::type;
+  const int c0 = (blockIdx.x * 32 + threadIdx.x) * V;
+  if (c0 >= C) return;
+  const int l0 = (blockIdx.y * CONV_TY + threadIdx.y) * CONV_LT;
+  if (l0 >= L) return;
+  const size_t b = blockIdx.z;
+  const T* xb = x + b * L * xp + c0;
+  T* yb = y + b * L * yp + c0;
+  A wk[W][V], bs[V], win[W][V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    bs[e] = bias != nullptr ? mp_up(bias[c0 + e]) : A(0);
+#pragma unroll
+    for (int k = 0; k < W; ++k) wk[k][e] = mp_up(w[static_cast<size_t>(c0 + e) * W + k]);
+  }
+#pragma unroll
+  for (int k = 0; k < W - 1; ++k) {   // win[k + 1] = x[l0 - W + 1 + k]
+    const int l = l0 - W + 1 + k;
+    if (l >= 0) load_vec<T, V>(xb + static_cast<size_t>(l) * xp, win[k + 1]);
+    else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) win[k + 1][e] = A(0);
+    }
+  }
+  const int l1 = min(l0 + CONV_LT, L);
+#pragma unroll 4
+  for (int l = l0; l < l1; ++l) {
+#pragma unroll
+    for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+      for (int e = 0; e < V; ++e) win[k][e] = win[k + 1][e];
+    load_vec<T, V>(xb + static_cast<size_t>(l) * xp, win[W - 1]);
+    A r[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      A acc = bs[e];
+#pragma unroll
+      for (int k = 0; k < W; ++k) acc += wk[k][e] * win[k][e];
+      r[e] = acc * sigmoid_a(acc);
+    }
+    store_vec<T, V>(yb + static_cast<size_t>(l) * yp, r);
+  }
+}
+
+// Reverse: dpre = gy * s * (1 + pre * (1 - s)) with pre recomputed;
+//   gx[l] = sum_k w[k] dpre[l + W - 1 - k];  gw[c,k] += sum_l dpre[l] x[l - W + 1 + k];  gbias[c] += sum_l dpre[l]
+// A thread owns CONV_LT steps and additionally recomputes the W - 1 steps after them.
+template <typename T, int V, int W>
+__global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const T* __restrict__ x, size_t xp,
+                                                                          const T* __restrict__ w, const T* __restrict__ bias,
+                                                                          const T* __restrict__ gy, size_t gyp,
+                                                                          T* __restrict__ gx, size_t gxp,
+                                                                          typename Acc<T>::type* __restrict__ gw,
+                                                                          typename Acc<T>::type* __restrict__ gbias, int L,
+                                                                          int C) {
+  using A = typename Acc<T>::type;
+  __shared__ A red[CONV_TY][32][V * (W + 1) + 1];
+  const int c0 = (blockIdx.x * 32 + threadIdx.x) * V;
+  const int l0 = (blockIdx.y * CONV_TY + threadIdx.y) * CONV_LT;
+  const bool live = c0 < C && l0 < L;
+  A gwk[W][V], gbs[V];
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+    gbs[e] = A(0);
+#pragma unroll
+    for (int k = 0; k < W; ++k) gwk[k][e] = A(0);
+  }
+  if (live) {
+    const size_t b = blockIdx.z;
+    const T* xb = x + b * L * xp + c0;
+    const T* gyb = gy + b * L * gyp + c0;
+    T* gxb = gx + b * L * gxp + c0;
+    A wk[W][V], bs[V], win[W][V], dwin[W][V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      bs[e] = bias != nullptr ? mp_up(bias[c0 + e]) : A(0);
+#pragma unroll
+      for (int k = 0; k < W; ++k) { wk[k][e] = mp_up(w[static_cast<size_t>(c0 + e) * W + k]); dwin[k][e] = A(0); }
+    }
+#pragma unroll
+    for (int k = 0; k < W - 1; ++k) {
+      const int l = l0 - W + 1 + k;
+      if (l >= 0) load_vec<T, V>(xb + static_cast<size_t>(l) * xp, win[k + 1]);
+      else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) win[k + 1][e] = A(0);
+      }
+    }
+    const int own_end = min(l0 + CONV_LT, L);
+    const int last = own_end + W - 1;   // exclusive: own steps plus the look-ahead
+#pragma unroll 2
+    for (int l = l0; l < last; ++l) {
+#pragma unroll
+      for (int k = 0; k < W - 1; ++k)
+#pragma unroll
+        for (int e = 0; e < V; ++e) { win[k][e] = win[k + 1][e]; dwin[k][e] = dwin[k + 1][e]; }
+      A g[V];
+      if (l < L) {
+        load_vec<T, V>(xb + static_cast<size_t>(l) * xp, win[W - 1]);
+        load_vec<T, V>(gyb + static_cast<size_t>(l) * gyp, g);
+      } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) { win[W - 1][e] = A(0); g[e] = A(0); }
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        A pre = bs[e];
+#pragma unroll
+        for (int k = 0; k < W; ++k) pre += wk[k][e] * win[k][e];
+        const A s = sigmoid_a(pre);
+        const A d = g[e] * s * (A(1) + pre * (A(1) - s));
+        dwin[W - 1][e] = d;
+        if (l < own_end) {
+          gbs[e] += d;
+#pragma unroll
+          for (int k = 0; k < W; ++k) gwk[k][e] += d * win[k][e];
+        }
+      }
+      const int m = l - (W - 1);   // gx[m] is complete now: dwin[j] = dpre[m + j]
+      if (m >= l0) {
+        A r[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          A acc = A(0);
+#pragma unroll
+          for (int k = 0; k < W; ++k) acc += wk[k][e] * dwin[W - 1 - k][e];
+          r[e] = acc;
+        }
+        store_vec<T, V>(gxb + static_cast<size_t>(m) * gxp, r);
+      }
+    }
+  }
+  // fold the time lanes of the CTA, then one atomic per (channel, tap)
+#pragma unroll
+  for (int e = 0; e < V; ++e) {
+#pragma unroll
+    for (int k = 0; k < W; ++k) red[threadIdx.y][threadIdx.x][e * (W + 1) + k] = gwk[k][e];
+    red[threadIdx.y][threadIdx.x][e * (W + 1) + W] = gbs[e];
+  }
+  __syncthreads();
+  if (threadIdx.y == 0 && c0 < C) {
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+#pragma unroll
+      for (int k = 0; k <= W; ++k) {
+        A s = A(0);
+#pragma unroll
+        for (int ty = 0; ty < CONV_TY; ++ty) s += red[ty][threadIdx.x][e * (W + 1) + k];
+        if (k < W) atomicAdd(gw + static_cast<size_t>(c0 + e) * W + k, s);
+        else if (gbias != nullptr) atomicAdd(gbias + c0 + e, s);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// dt = softplus(raw + bias[h]) (accumulator-typed output), raw pitched [rows, H]
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) softplus_bias_kernel(const T* __restrict__ raw, size_t rp,
+                                                            const typename Acc<T>::type* __restrict__ bias,
+                                                            typename Acc<T>::type* __restrict__ out, size_t rows, int H) {
+  using A = typename Acc<T>::type;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < rows * H;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = i / H;
+    const int h = static_cast<int>(i % H);
+    const A v = mp_up(raw[r * rp + h]) + bias[h];
+    out[i] = v > A(20) ? v : log1p_a(exp_a(v));
+  }
+}
+
+// graw = gdt * sigmoid(raw + bias);  gbias[h] += sum_rows graw
+template <typename T>
+__global__ void __launch_bounds__(256) softplus_bias_reverse_kernel(const T* __restrict__ raw, size_t rp,
+                                                                    const typename Acc<T>::type* __restrict__ bias,
+                                                                    const typename Acc<T>::type* __restrict__ gdt,
+                                                                    T* __restrict__ graw, size_t gp,
+                                                                    typename Acc<T>::type* __restrict__ gbias, size_t rows,
+                                                                    int H) {
+  using A = typename Acc<T>::type;
+  extern __shared__ unsigned char sp_smem[];
+  A* bins = reinterpret_cast<A*>(sp_smem);
+  for (int h = threadIdx.x; h < H; h += blockDim.x) bins[h] = A(0);
+  __syncthreads();
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < rows * H;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = i / H;
+    const int h = static_cast<int>(i % H);
+    const A v = mp_up(raw[r * rp + h]) + bias[h];
+    const A g = gdt[i] * sigmoid_a(v);
+    graw[r * gp + h] = mp_down<T>(g);
+    atomicAdd(bins + h, g);
+  }
+  __syncthreads();
+  if (gbias != nullptr)
+    for (int h = threadIdx.x; h < H; h += blockDim.x) atomicAdd(gbias + h, bins[h]);
+}
+
+// ---------------------------------------------------------------------------
+// skip + gate around the scan: u = (y + D[h] x) * silu(z);  rows x (H * P), z pitched
+// ---------------------------------------------------------------------------
+template <typename T, int V>
+__global__ void __launch_bounds__(256) ssd_gate_kernel(const T* __restrict__ y, const T* __restrict__ x,
+                                                       const typename Acc<T>::type* __restrict__ D, const T* __restrict__ z,
+                                                       size_t zp, T* __restrict__ u, size_t rows, int H, int P) {
+  using A = typename Acc<T>::type;
+  const size_t width = static_cast<size_t>(H) * P, per_row = width / V;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < rows * per_row;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = i / per_row, c = (i % per_row) * V;
+    A yv[V], xv[V], zv[V], o[V];
+    load_vec<T, V>(y + r * width + c, yv);
+    load_vec<T, V>(x + r * width + c, xv);
+    load_vec<T, V>(z + r * zp + c, zv);
+    const A d = D != nullptr ? D[c / P] : A(0);
+#pragma unroll
+    for (int e = 0; e < V; ++e) o[e] = (yv[e] + d * xv[e]) * zv[e] * sigmoid_a(zv[e]);
+    store_vec<T, V>(u + r * width + c, o);
+  }
+}
+
+// gy = gu * silu(z);  gz = gu * (y + D x) * (s + z s (1 - s));  gD[h] += sum gy * x
+template <typename T, int V>
+__global__ void __launch_bounds__(256) ssd_gate_reverse_kernel(const T* __restrict__ y, const T* __restrict__ x,
+                                                               const typename Acc<T>::type* __restrict__ D,
+                                                               const T* __restrict__ z, size_t zp, const T* __restrict__ gu,
+                                                               T* __restrict__ gy, T* __restrict__ gz, size_t gzp,
+                                                               typename Acc<T>::type* __restrict__ gD, size_t rows, int H,
+                                                               int P) {
+  using A = typename Acc<T>::type;
+  extern __shared__ unsigned char gate_smem[];
+  A* bins = reinterpret_cast<A*>(gate_smem);
+  for (int h = threadIdx.x; h < H; h += blockDim.x) bins[h] = A(0);
+  __syncthreads();
+  const size_t width = static_cast<size_t>(H) * P, per_row = width / V;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < rows * per_row;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t r = i / per_row, c = (i % per_row) * V;
+    A yv[V], xv[V], zv[V], gv[V], oy[V], oz[V];
+    load_vec<T, V>(y + r * width + c, yv);
+    load_vec<T, V>(x + r * width + c, xv);
+    load_vec<T, V>(z + r * zp + c, zv);
+    load_vec<T, V>(gu + r * width + c, gv);
+    const int h = static_cast<int>(c / P);
+    const A d = D != nullptr ? D[h] : A(0);
+    A part = A(0);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const A s = sigmoid_a(zv[e]);
+      oy[e] = gv[e] * zv[e] * s;
+      oz[e] = gv[e] * (yv[e] + d * xv[e]) * (s + zv[e] * s * (A(1) - s));
+      part += oy[e] * xv[e];
+    }
+    store_vec<T, V>(gy + r * width + c, oy);
+    store_vec<T, V>(gz + r * gzp + c, oz);
+    if (gD != nullptr) atomicAdd(bins + h, part);
+  }
+  __syncthreads();
+  if (gD != nullptr)
+    for (int h = threadIdx.x; h < H; h += blockDim.x) atomicAdd(gD + h, bins[h]);
+}
+
+// gx[r, h, :] += D[h] * gy[r, h, :]
+template <typename T, int V>
+__global__ void __launch_bounds__(256) head_scale_accumulate_kernel(const typename Acc<T>::type* __restrict__ D,
+                                                                    const T* __restrict__ gy, T* __restrict__ gx, size_t rows,
+                                                                    int H, int P) {
+  using A = typename Acc<T>::type;
+  const size_t width = static_cast<size_t>(H) * P, per_row = width / V;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < rows * per_row;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t c = (i % per_row) * V;
+    A a[V], g[V];
+    load_vec<T, V>(gx + i * V, a);
+    load_vec<T, V>(gy + i * V, g);
+    const A d = D[c / P];
+#pragma unroll
+    for (int e = 0; e < V; ++e) a[e] += d * g[e];
+    store_vec<T, V>(gx + i * V, a);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// cross-entropy over rows of logits [m, n] with integer targets:
+//   loss_i = log sum_j exp(x_ij) - x_i,target;  glogits_ij = scale * (softmax_ij - [j == target])
+// One CTA per row; the row is parked in shared memory when it fits (one read of
+// the logits, one write of the gradient, which may alias the logits).
+// ---------------------------------------------------------------------------
+constexpr int CE_THREADS = 512;
+
+template <typename T, int V, bool STAGED>
+__global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const T* logits, const int* __restrict__ targets,
+                                                                  typename Acc<T>::type scale,
+                                                                  typename Acc<T>::type* __restrict__ loss, T* glogits,
+                                                                  size_t n) {
+  using A = typename Acc<T>::type;
+  extern __shared__ __align__(16) unsigned char ce_smem[];
+  __shared__ A red[CE_THREADS / 32];
+  __shared__ A bc;
+  T* srow = reinterpret_cast<T*>(ce_smem);
+  const size_t row = blockIdx.x;
+  const T* src = logits + row * n;
+  const size_t nv = n / V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto block_reduce = [&](A v, bool is_max) -> A {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const A other = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? (v > other ? v : other) : v + other;
+    }
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      A t = lane < CE_THREADS / 32 ? red[lane] : (is_max ? A(-INFINITY) : A(0));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const A other = __shfl_xor_sync(0xffffffffu, t, o);
+        t = is_max ? (t > other ? t : other) : t + other;
+      }
+      if (lane == 0) bc = t;
+    }
+    __syncthreads();
+    const A r = bc;
+    __syncthreads();
+    return r;
+  };
+  A mx = A(-INFINITY);
+  for (size_t i = threadIdx.x; i < nv; i += CE_THREADS) {
+    const VecT<T, V> x = *reinterpret_cast<const VecT<T, V>*>(src + i * V);
+    if (STAGED) *reinterpret_cast<VecT<T, V>*>(srow + i * V) = x;
+#pragma unroll
+    for (int e = 0; e < V; ++e) { const A f = mp_up(x.v[e]); mx = f > mx ? f : mx; }
+  }
+  mx = block_reduce(mx, true);   // (the barriers inside also publish the staged row)
+  const T* rd = STAGED ? srow : src;
+  A sum = A(0);
+  for (size_t i = threadIdx.x; i < nv; i += CE_THREADS) {
+    const VecT<T, V> x = *reinterpret_cast<const VecT<T, V>*>(rd + i * V);
+#pragma unroll
+    for (int e = 0; e < V; ++e) sum += exp_a(mp_up(x.v[e]) - mx);
+  }
+  sum = block_reduce(sum, false);
+  const long long tg = targets[row];
+  const bool valid = tg >= 0 && static_cast<size_t>(tg) < n;   // other targets: ignored row (zero loss, zero gradient)
+  if (threadIdx.x == 0 && loss != nullptr) loss[row] = valid ? log_a(sum) + mx - mp_up(rd[valid ? tg : 0]) : A(0);
+  if (glogits != nullptr) {
+    const A inv = scale / sum;
+    T* dst = glogits + row * n;
+    for (size_t i = threadIdx.x; i < nv; i += CE_THREADS) {
+      const VecT<T, V> x = *reinterpret_cast<const VecT<T, V>*>(rd + i * V);
+      VecT<T, V> o;
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        A gval = valid ? exp_a(mp_up(x.v[e]) - mx) * inv : A(0);
+        if (valid && i * V + e == static_cast<size_t>(tg)) gval -= scale;
+        o.v[e] = mp_down<T>(gval);
+      }
+      *reinterpret_cast<VecT<T, V>*>(dst + i * V) = o;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// small element-wise helpers
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) neg_exp_kernel(const T* __restrict__ src, T* __restrict__ dst, size_t n) {
+  using A = typename Acc<T>::type;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    dst[i] = mp_down<T>(-exp_a(static_cast<A>(mp_up(src[i]))));
+}
+
+// dst(r32) = src(r16) + beta * dst
+template <int V>
+__global__ void __launch_bounds__(512) convert_r16_r32_kernel(const __half* __restrict__ src, float* __restrict__ dst, float beta,
+                                                              size_t n) {
+  const size_t nv = n / V;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float a[V], o[V];
+    load_vec<__half, V>(src + i * V, a);
+    if (beta != 0.f) {
+      load_vec<float, V>(dst + i * V, o);
+#pragma unroll
+      for (int e = 0; e < V; ++e) a[e] += beta * o[e];
+    }
+    store_vec<float, V>(dst + i * V, a);
+  }
+}
+template <int V>
+__global__ void __launch_bounds__(512) convert_r32_r16_kernel(const float* __restrict__ src, __half* __restrict__ dst, size_t n) {
+  const size_t nv = n / V;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nv;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float a[V];
+    load_vec<float, V>(src + i * V, a);
+    store_vec<__half, V>(dst + i * V, a);
+  }
+}
+
+inline unsigned grid_for(size_t work_items, int threads) {
+  const size_t g = (work_items + threads - 1) / threads;
+  return static_cast<unsigned>(g < 1 ? 1 : (g > (1u << 30) ? (1u << 30) : g));
+}
+
+// ------------------------------- launch bodies ------------------------------
+template <typename T>
+void embedding_impl(const void* table, const void* ids, void* out, len_t n, len_t dim, len_t vocab, StreamContext ctx) {
+  if (n == 0 || dim == 0) return;
+  constexpr int PN = Pack<T>::N;
+  cudaStream_t st = mp_stream(ctx);
+  if (dim % PN == 0 && mp_aligned16(table) && mp_aligned16(out))
+    embedding_kernel<T, PN><<<grid_for(n * (dim / PN), 256), 256, 0, st>>>(static_cast<const T*>(table), static_cast<const int*>(ids),
+                                                                         static_cast<T*>(out), n, dim, vocab);
+  else
+    embedding_kernel<T, 1><<<grid_for(n * dim, 256), 256, 0, st>>>(static_cast<const T*>(table), static_cast<const int*>(ids),
+                                                                 static_cast<T*>(out), n, dim, vocab);
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T>
+void embedding_reverse_impl(const void* ids, const void* gy, void* gtable, len_t n, len_t dim, len_t vocab, StreamContext ctx) {
+  if (n == 0 || dim == 0) return;
+  using A = typename Acc<T>::type;
+  embedding_reverse_kernel<T><<<grid_for(n * dim, 256), 256, 0, mp_stream(ctx)>>>(static_cast<const int*>(ids), static_cast<const T*>(gy),
+                                                                              static_cast<A*>(gtable), n, dim, vocab);
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T, int V>
+void conv_dispatch(bool reverse, const T* x, size_t xp, const T* w, const T* bias, const T* gy, size_t gyp, T* out, size_t op,
+                   typename Acc<T>::type* gw, typename Acc<T>::type* gbias, len_t batch, len_t len, len_t channels, len_t width,
+                   cudaStream_t st) {
+  const dim3 block(32, CONV_TY);
+  const dim3 grid(static_cast<unsigned>((channels / V + 31) / 32), static_cast<unsigned>((len + CONV_TY * CONV_LT - 1) / (CONV_TY * CONV_LT)),
+                  static_cast<unsigned>(batch));
+  const int L = static_cast<int>(len), C = static_cast<int>(channels);
+#define MP_CONV_CASE(WW)                                                                                              \
+  case WW:                                                                                                            \
+    if (reverse) conv1d_silu_reverse_kernel<T, V, WW><<<grid, block, 0, st>>>(x, xp, w, bias, gy, gyp, out, op, gw, gbias, L, C); \
+    else conv1d_silu_kernel<T, V, WW><<<grid, block, 0, st>>>(x, xp, w, bias, out, op, L, C);                         \
+    break;
+  switch (width) {
+    MP_CONV_CASE(2)
+    MP_CONV_CASE(3)
+    MP_CONV_CASE(4)
+    default: MP_FATAL("causal_conv1d_silu: kernel width %llu is not supported (2, 3 or 4)", static_cast<unsigned long long>(width));
+  }
+#undef MP_CONV_CASE
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T>
+void causal_conv1d_silu_impl(const void* x, len_t x_pitch, const void* w, const void* bias, void* y, len_t y_pitch, len_t batch,
+                             len_t len, len_t channels, len_t width, StreamContext ctx) {
+  if (batch == 0 || len == 0 || channels == 0) return;
+  constexpr int PN = Pack<T>::N;
+  const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(y, y_pitch, channels);
+  if (v) conv_dispatch<T, PN>(false, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias), nullptr, 0,
+                              static_cast<T*>(y), y_pitch, nullptr, nullptr, batch, len, channels, width, mp_stream(ctx));
+  else conv_dispatch<T, 1>(false, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias), nullptr, 0,
+                           static_cast<T*>(y), y_pitch, nullptr, nullptr, batch, len, channels, width, mp_stream(ctx));
+}
+
+template <typename T>
+void causal_conv1d_silu_reverse_impl(const void* x, len_t x_pitch, const void* w, const void* bias, const void* gy, len_t gy_pitch,
+                                     void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t channels,
+                                     len_t width, StreamContext ctx) {
+  if (batch == 0 || len == 0 || channels == 0) return;
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(gy, gy_pitch, channels) && vec_ok<T>(gx, gx_pitch, channels);
+  if (v) conv_dispatch<T, PN>(true, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
+                              static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw), static_cast<A*>(gbias),
+                              batch, len, channels, width, mp_stream(ctx));
+  else conv_dispatch<T, 1>(true, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
+                           static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw), static_cast<A*>(gbias),
+                           batch, len, channels, width, mp_stream(ctx));
+}
+
+template <typename T>
+void softplus_bias_impl(const void* raw, len_t raw_pitch, const void* bias, void* out, len_t rows, len_t heads, StreamContext ctx) {
+  if (rows == 0 || heads == 0) return;
+  using A = typename Acc<T>::type;
+  softplus_bias_kernel<T><<<grid_for(rows * heads, 256), 256, 0, mp_stream(ctx)>>>(static_cast<const T*>(raw), raw_pitch, static_cast<const A*>(bias),
+                                                                               static_cast<A*>(out), rows, static_cast<int>(heads));
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T>
+void softplus_bias_reverse_impl(const void* raw, len_t raw_pitch, const void* bias, const void* gdt, void* graw, len_t graw_pitch,
+                                void* gbias, len_t rows, len_t heads, StreamContext ctx) {
+  if (rows == 0 || heads == 0) return;
+  using A = typename Acc<T>::type;
+  // few, fat CTAs: each one ends with `heads` global atomics
+  const unsigned grid = grid_for((rows * heads + 15) / 16, 256);
+  softplus_bias_reverse_kernel<T><<<grid, 256, heads * sizeof(A), mp_stream(ctx)>>>(
+      static_cast<const T*>(raw), raw_pitch, static_cast<const A*>(bias), static_cast<const A*>(gdt), static_cast<T*>(graw), graw_pitch,
+      static_cast<A*>(gbias), rows, static_cast<int>(heads));
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T>
+void ssd_gate_impl(const void* y, const void* x, const void* D, const void* z, len_t z_pitch, void* u, len_t rows, len_t heads,
+                   len_t headdim, StreamContext ctx) {
+  if (rows == 0 || heads == 0 || headdim == 0) return;
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  const size_t width = heads * headdim;
+  const bool v = headdim % PN == 0 && vec_ok<T>(z, z_pitch, width) && mp_aligned16(y) && mp_aligned16(x) && mp_aligned16(u);
+  cudaStream_t st = mp_stream(ctx);
+  if (v) ssd_gate_kernel<T, PN><<<grid_for(rows * (width / PN), 256), 256, 0, st>>>(static_cast<const T*>(y), static_cast<const T*>(x), static_cast<const A*>(D),
+                                                                                 static_cast<const T*>(z), z_pitch, static_cast<T*>(u), rows,
+                                                                                 static_cast<int>(heads), static_cast<int>(headdim));
+  else ssd_gate_kernel<T, 1><<<grid_for(rows * width, 256), 256, 0, st>>>(static_cast<const T*>(y), static_cast<const T*>(x), static_cast<const A*>(D),
+                                                                        static_cast<const T*>(z), z_pitch, static_cast<T*>(u), rows,
+                                                                        static_cast<int>(heads), static_cast<int>(headdim));
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T>
+void ssd_gate_reverse_impl(const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gu, void* gy, void* gz,
+                           len_t gz_pitch, void* gD, len_t rows, len_t heads, len_t headdim, StreamContext ctx) {
+  if (rows == 0 || heads == 0 || headdim == 0) return;
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  const size_t width = heads * headdim;
+  const bool v = headdim % PN == 0 && vec_ok<T>(z, z_pitch, width) && vec_ok<T>(gz, gz_pitch, width) && mp_aligned16(y) &&
+                 mp_aligned16(x) && mp_aligned16(gu) && mp_aligned16(gy);
+  cudaStream_t st = mp_stream(ctx);
+  const size_t smem = heads * sizeof(A);
+  if (v) ssd_gate_reverse_kernel<T, PN><<<grid_for((rows * (width / PN) + 7) / 8, 256), 256, smem, st>>>(
+        static_cast<const T*>(y), static_cast<const T*>(x), static_cast<const A*>(D), static_cast<const T*>(z), z_pitch, static_cast<const T*>(gu),
+        static_cast<T*>(gy), static_cast<T*>(gz), gz_pitch, static_cast<A*>(gD), rows, static_cast<int>(heads), static_cast<int>(headdim));
+  else ssd_gate_reverse_kernel<T, 1><<<grid_for((rows * width + 7) / 8, 256), 256, smem, st>>>(
+        static_cast<const T*>(y), static_cast<const T*>(x), static_cast<const A*>(D), static_cast<const T*>(z), z_pitch, static_cast<const T*>(gu),
+        static_cast<T*>(gy), static_cast<T*>(gz), gz_pitch, static_cast<A*>(gD), rows, static_cast<int>(heads), static_cast<int>(headdim));
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T>
+void head_scale_accumulate_impl(const void* D, const void* gy, void* gx, len_t rows, len_t heads, len_t headdim, StreamContext ctx) {
+  if (rows == 0 || heads == 0 || headdim == 0) return;
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  const size_t width = heads * headdim;
+  cudaStream_t st = mp_stream(ctx);
+  if (headdim % PN == 0 && mp_aligned16(gy) && mp_aligned16(gx))
+    head_scale_accumulate_kernel<T, PN><<<grid_for(rows * (width / PN), 256), 256, 0, st>>>(static_cast<const A*>(D), static_cast<const T*>(gy),
+                                                                                        static_cast<T*>(gx), rows, static_cast<int>(heads),
+                                                                                        static_cast<int>(headdim));
+  else
+    head_scale_accumulate_kernel<T, 1><<<grid_for(rows * width, 256), 256, 0, st>>>(static_cast<const A*>(D), static_cast<const T*>(gy), static_cast<T*>(gx),
+                                                                                rows, static_cast<int>(heads), static_cast<int>(headdim));
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T, int V>
+void ce_launch(const T* logits, const int* targets, double scale, typename Acc<T>::type* loss, T* glogits, len_t m, len_t n, cudaStream_t st) {
+  using A = typename Acc<T>::type;
+  const size_t row_bytes = n * sizeof(T);
+  if (row_bytes <= 200 * 1024) {
+    MP_CUDA_CHECK(cudaFuncSetAttribute(cross_entropy_kernel<T, V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    cross_entropy_kernel<T, V, true><<<static_cast<unsigned>(m), CE_THREADS, (row_bytes + 15) & ~size_t(15), st>>>(logits, targets, static_cast<A>(scale), loss,
+                                                                                                                 glogits, n);
+  } else {
+    cross_entropy_kernel<T, V, false><<<static_cast<unsigned>(m), CE_THREADS, 0, st>>>(logits, targets, static_cast<A>(scale), loss, glogits, n);
+  }
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T>
+void cross_entropy_impl(const void* logits, const void* targets, double scale, void* loss, void* glogits, len_t m, len_t n, StreamContext ctx) {
+  if (m == 0 || n == 0) return;
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  const bool v = n % PN == 0 && mp_aligned16(logits) && (glogits == nullptr || mp_aligned16(glogits));
+  if (v) ce_launch<T, PN>(static_cast<const T*>(logits), static_cast<const int*>(targets), scale, static_cast<A*>(loss), static_cast<T*>(glogits), m, n, mp_stream(ctx));
+  else ce_launch<T, 1>(static_cast<const T*>(logits), static_cast<const int*>(targets), scale, static_cast<A*>(loss), static_cast<T*>(glogits), m, n, mp_stream(ctx));
+}
+
+template <typename T>
+void neg_exp_impl(const void* src, void* dst, len_t n, StreamContext ctx) {
+  if (n == 0) return;
+  neg_exp_kernel<T><<<grid_for(n, 256), 256, 0, mp_stream(ctx)>>>(static_cast<const T*>(src), static_cast<T*>(dst), n);
+  MP_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+MP_STAMP3(embedding, (const void* table, const void* ids, void* out, len_t n, len_t dim, len_t vocab, StreamContext ctx),
+          (table, ids, out, n, dim, vocab, ctx))
+MP_STAMP3(embedding_reverse, (const void* ids, const void* gy, void* gtable, len_t n, len_t dim, len_t vocab, StreamContext ctx),
+          (ids, gy, gtable, n, dim, vocab, ctx))
+MP_STAMP3(causal_conv1d_silu,
+          (const void* x, len_t x_pitch, const void* w, const void* bias, void* y, len_t y_pitch, len_t batch, len_t len, len_t channels,
+           len_t width, StreamContext ctx),
+          (x, x_pitch, w, bias, y, y_pitch, batch, len, channels, width, ctx))
+MP_STAMP3(causal_conv1d_silu_reverse,
+          (const void* x, len_t x_pitch, const void* w, const void* bias, const void* gy, len_t gy_pitch, void* gx, len_t gx_pitch, void* gw,
+           void* gbias, len_t batch, len_t len, len_t channels, len_t width, StreamContext ctx),
+          (x, x_pitch, w, bias, gy, gy_pitch, gx, gx_pitch, gw, gbias, batch, len, channels, width, ctx))
+MP_STAMP3(softplus_bias, (const void* raw, len_t raw_pitch, const void* bias, void* out, len_t rows, len_t heads, StreamContext ctx),
+          (raw, raw_pitch, bias, out, rows, heads, ctx))
+MP_STAMP3(softplus_bias_reverse,
+          (const void* raw, len_t raw_pitch, const void* bias, const void* gdt, void* graw, len_t graw_pitch, void* gbias, len_t rows,
+           len_t heads, StreamContext ctx),
+          (raw, raw_pitch, bias, gdt, graw, graw_pitch, gbias, rows, heads, ctx))
+MP_STAMP3(ssd_gate,
+          (const void* y, const void* x, const void* D, const void* z, len_t z_pitch, void* u, len_t rows, len_t heads, len_t headdim,
+           StreamContext ctx),
+          (y, x, D, z, z_pitch, u, rows, heads, headdim, ctx))
+MP_STAMP3(ssd_gate_reverse,
+          (const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gu, void* gy, void* gz, len_t gz_pitch,
+           void* gD, len_t rows, len_t heads, len_t headdim, StreamContext ctx),
+          (y, x, D, z, z_pitch, gu, gy, gz, gz_pitch, gD, rows, heads, headdim, ctx))
+MP_STAMP3(head_scale_accumulate, (const void* D, const void* gy, void* gx, len_t rows, len_t heads, len_t headdim, StreamContext ctx),
+          (D, gy, gx, rows, heads, headdim, ctx))
+MP_STAMP3(cross_entropy,
+          (const void* logits, const void* targets, double scale, void* loss, void* glogits, len_t m, len_t n, StreamContext ctx),
+          (logits, targets, scale, loss, glogits, m, n, ctx))
+MP_STAMP3(neg_exp, (const void* src, void* dst, len_t n, StreamContext ctx), (src, dst, n, ctx))
+
+extern "C" void launch_convert_r16_r32(const void* src, void* dst, double beta, len_t n, StreamContext ctx) {
+  if (n == 0) return;
+  cudaStream_t st = mp_stream(ctx);
+  if (n % 8 == 0 && mp_aligned16(src) && (reinterpret_cast<uintptr_t>(dst) & 31u) == 0)
+    convert_r16_r32_kernel<8><<<grid_for(n / 8, 512), 512, 0, st>>>(static_cast<const __half*>(src), static_cast<float*>(dst), static_cast<float>(beta), n);
+  else
+    convert_r16_r32_kernel<1><<<grid_for(n, 512), 512, 0, st>>>(static_cast<const __half*>(src), static_cast<float*>(dst), static_cast<float>(beta), n);
+  MP_LAUNCH_CHECK();
+}
+
+extern "C" void launch_convert_r32_r16(const void* src, void* dst, len_t n, StreamContext ctx) {
+  if (n == 0) return;
+  cudaStream_t st = mp_stream(ctx);
+  if (n % 8 == 0 && mp_aligned16(dst) && (reinterpret_cast<uintptr_t>(src) & 31u) == 0)
+    convert_r32_r16_kernel<8><<<grid_for(n / 8, 512), 512, 0, st>>>(static_cast<const float*>(src), static_cast<__half*>(dst), n);
+  else
+    convert_r32_r16_kernel<1><<<grid_for(n, 512), 512, 0, st>>>(static_cast<const float*>(src), static_cast<__half*>(dst), n);
+  MP_LAUNCH_CHECK();
+}

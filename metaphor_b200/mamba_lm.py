@@ -1,0 +1,308 @@
+"""Host composition of one data-parallel training step of a Mamba-2 language
+model over the C ABI (include/mp_kernels.h): every computation is a ``launch_*``
+call on the library's stream; torch is used for device memory only.
+
+Layer (pre-norm residual block), T = batch * seqlen tokens, r16 activations:
+    xn   = rmsnorm(h, norm_w)
+    zx   = xn @ W_in                      columns [ z | x B C | dt ]
+    x,B,C= silu(causal_conv1d(zx[x B C]))
+    dt   = softplus(zx[dt] + dt_bias);  A = -exp(A_log)
+    y    = ssd_scan(x, dt, A, B, C)
+    u    = (y + D x) * silu(z)
+    h    = h + rmsnorm(u, gnorm_w) @ W_out
+Head: logits = rmsnorm(h, normf_w) @ E^T (tied embedding), mean cross-entropy.
+
+Weights live in one flat r32 master buffer (plus Adam moments); contractions and
+norms read a flat r16 copy refreshed after every step.  Gradients: contractions
+and norm gains write r16 into a flat r16 gradient buffer, everything reduced with
+atomics (embedding rows, conv taps, biases, D, A_log) goes straight to the flat
+r32 gradient, and one conversion folds the r16 part in.  The r32 gradient is what
+the all-reduce and the fused Adam step see.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+
+from .runtime import Stream, launch, lib
+
+
+@dataclass
+class LMConfig:
+    d_model: int = 768
+    n_layer: int = 24
+    expand: int = 2
+    headdim: int = 64
+    d_state: int = 128
+    ngroups: int = 1
+    d_conv: int = 4
+    vocab: int = 50280
+    chunk: int = 256
+    eps: float = 1e-6
+
+    @property
+    def d_inner(self):
+        return self.expand * self.d_model
+
+    @property
+    def heads(self):
+        return self.d_inner // self.headdim
+
+    @property
+    def conv_dim(self):
+        return self.d_inner + 2 * self.ngroups * self.d_state
+
+    @property
+    def d_in_proj(self):
+        return 2 * self.d_inner + 2 * self.ngroups * self.d_state + self.heads
+
+    def param_shapes(self):
+        """(name, shape) in flat-buffer order."""
+        out = [("embedding", (self.vocab, self.d_model))]
+        for i in range(self.n_layer):
+            p = f"layers.{i}."
+            out += [(p + "norm_w", (self.d_model,)), (p + "in_proj", (self.d_model, self.d_in_proj)),
+                    (p + "conv_w", (self.conv_dim, self.d_conv)), (p + "conv_b", (self.conv_dim,)),
+                    (p + "dt_bias", (self.heads,)), (p + "A_log", (self.heads,)), (p + "D", (self.heads,)),
+                    (p + "gnorm_w", (self.d_inner,)), (p + "out_proj", (self.d_inner, self.d_model))]
+        out.append(("normf_w", (self.d_model,)))
+        return out
+
+    def n_params(self):
+        return sum(math.prod(s) for _, s in self.param_shapes())
+
+
+def init_weights(cfg: LMConfig, seed: int = 0):
+    """Random initial weights as float32 numpy arrays (name -> array)."""
+    import numpy as np
+    r = np.random.default_rng(seed)
+    w = {}
+    for name, shape in cfg.param_shapes():
+        leaf = name.split(".")[-1]
+        if leaf in ("norm_w", "gnorm_w", "normf_w", "D"):
+            a = np.ones(shape)
+        elif leaf == "conv_b":
+            a = np.zeros(shape)
+        elif leaf == "conv_w":
+            a = r.uniform(-1.0, 1.0, shape) / math.sqrt(cfg.d_conv)
+        elif leaf == "dt_bias":   # softplus^-1 of step sizes drawn log-uniformly from [1e-3, 1e-1]
+            dt = np.exp(r.uniform(math.log(1e-3), math.log(1e-1), shape))
+            a = dt + np.log(-np.expm1(-dt))
+        elif leaf == "A_log":
+            a = np.log(r.uniform(1.0, 16.0, shape))
+        else:
+            a = r.standard_normal(shape) * 0.02
+        w[name] = a.astype(np.float32)
+    return w
+
+
+ALIGN = 64   # elements: keeps every parameter 128-byte aligned in the r16 copy
+
+
+class MambaLM:
+    def __init__(self, cfg: LMConfig, batch: int, seqlen: int, weights=None, seed: int = 0, stream: Stream | None = None,
+                 loss_scale: float = 1.0):
+        import torch
+        self.cfg, self.batch, self.seqlen = cfg, batch, seqlen
+        self.T = batch * seqlen
+        self.loss_scale = loss_scale
+        self.stream = stream if stream is not None else Stream()
+        self._lib = lib()
+        dev = "cuda"
+        if seqlen % cfg.chunk != 0:
+            raise ValueError("seqlen must be a multiple of the scan chunk")
+        # ---- flat parameter buffers ------------------------------------------------
+        self.offsets, off = {}, 0
+        for name, shape in cfg.param_shapes():
+            self.offsets[name] = (off, shape)
+            off += (math.prod(shape) + ALIGN - 1) // ALIGN * ALIGN
+        self.n_flat = off
+        self.w32 = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.w16 = torch.zeros(off, dtype=torch.float16, device=dev)
+        self.g32 = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.g16 = torch.zeros(off, dtype=torch.float16, device=dev)
+        self.m = torch.zeros(off, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(off, dtype=torch.float32, device=dev)
+        weights = weights if weights is not None else init_weights(cfg, seed)
+        host = torch.zeros(off, dtype=torch.float32)
+        for name, (o, shape) in self.offsets.items():
+            host[o:o + math.prod(shape)] = torch.from_numpy(weights[name]).reshape(-1)
+        self.w32.copy_(host)
+        torch.cuda.synchronize()
+        self._refresh_w16()
+        self.step_count = 0
+        # ---- activations -------------------------------------------------------------
+        T, c = self.T, cfg
+        f16 = lambda *s: torch.empty(*s, dtype=torch.float16, device=dev)
+        f32 = lambda *s: torch.empty(*s, dtype=torch.float32, device=dev)
+        gn = c.ngroups * c.d_state
+        self.ids = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.targets = torch.zeros(T, dtype=torch.int32, device=dev)
+        self.saved = [dict(h_in=f16(T, c.d_model), xn=f16(T, c.d_model), rstd1=f32(T), zx=f16(T, c.d_in_proj), xs=f16(T, c.d_inner),
+                           Bs=f16(T, gn), Cs=f16(T, gn), dt=f32(T, c.heads), A=f32(c.heads), y=f16(T, c.d_inner), u=f16(T, c.d_inner),
+                           un=f16(T, c.d_inner), rstd2=f32(T)) for _ in range(c.n_layer)]
+        self.h = f16(T, c.d_model)
+        self.o = f16(T, c.d_model)
+        self.hn = f16(T, c.d_model)
+        self.rstdf = f32(T)
+        self.logits = f16(T, c.vocab)
+        self.loss_rows = f32(T)
+        self.loss_sum = f32(1)
+        # backward temporaries
+        self.gh = f16(T, c.d_model)
+        self.gt = f16(T, c.d_model)
+        self.gun = f16(T, c.d_inner)
+        self.gu = f16(T, c.d_inner)
+        self.gy = f16(T, c.d_inner)
+        self.gxs = f16(T, c.d_inner)
+        self.gBs = f16(T, gn)
+        self.gCs = f16(T, gn)
+        self.gdt = f32(T, c.heads)
+        self.gA = f32(c.heads)
+        self.gzx = f16(T, c.d_in_proj)
+        dims = (batch, seqlen, c.heads, c.headdim, c.d_state, c.ngroups, c.chunk)
+        self.ssd_dims = dims
+        n_scr = max(self._lib.mpSsdScanScratchBytes(*dims, 0), self._lib.mpSsdScanScratchBytes(*dims, 1))
+        self.ssd_scratch = torch.empty(n_scr, dtype=torch.uint8, device=dev)
+        n_rms = max(self._lib.mpRmsnormReverseScratchBytes(T, c.d_model, self.stream.ctx),
+                    self._lib.mpRmsnormReverseScratchBytes(T, c.d_inner, self.stream.ctx))
+        self.rms_scratch = torch.empty(max(n_rms, 16), dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize()
+
+    # ------------------------------------------------------------------ helpers
+    def _p(self, buf, name, extra=0):
+        """Device address of a parameter (or of its gradient) inside a flat buffer."""
+        return buf.data_ptr() + (self.offsets[name][0] + extra) * buf.element_size()
+
+    def _L(self, name, *args):
+        import torch
+        launch(name, torch.float16, *args, self.stream)
+
+    def _L32(self, name, *args):
+        import torch
+        launch(name, torch.float32, *args, self.stream)
+
+    def _refresh_w16(self):
+        self._lib.launch_convert_r32_r16(C.c_void_p(self.w32.data_ptr()), C.c_void_p(self.w16.data_ptr()), self.n_flat, self.stream.ctx)
+
+    def set_batch(self, ids, targets):
+        """ids, targets: int32 tensors of batch*seqlen tokens, on the host (pinned memory makes the copy
+        asynchronous) or on the device; the copies are ordered on the library's stream."""
+        for dst, src in ((self.ids, ids), (self.targets, targets)):
+            src = src.reshape(-1)
+            assert src.numel() == self.T and src.element_size() == 4
+            if src.is_cuda:   # int32 and r32 are both 4-byte words and the copy kernel is bit-exact
+                self._lib.launch_copy_r32(C.c_void_p(src.data_ptr()), C.c_void_p(dst.data_ptr()), src.numel(), self.stream.ctx)
+            else:
+                self._lib.mpMemcpyHtoD(C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()), src.numel() * 4, self.stream.ctx)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self):
+        c, T, s = self.cfg, self.T, self.stream
+        W = self.w16
+        di, gn, H, P = c.d_inner, c.ngroups * c.d_state, c.heads, c.headdim
+        dip = c.d_in_proj
+        esz = 2
+        self._L("embedding", self._p(W, "embedding"), self.ids, self.h, T, c.d_model, c.vocab)
+        for i, sv in enumerate(self.saved):
+            p = f"layers.{i}."
+            self._L("copy", self.h, sv["h_in"], T * c.d_model)
+            self._L("rmsnorm_ij_j", self.h, self._p(W, p + "norm_w"), c.eps, sv["xn"], sv["rstd1"], T, c.d_model)
+            self._L("inner_product_ij_jk_ik", sv["xn"], self._p(W, p + "in_proj"), 1.0, sv["zx"], 0.0, T, c.d_model, dip)
+            zx = sv["zx"].data_ptr()
+            # conv over the [x | B | C] columns, each segment into its own contiguous tensor
+            for seg_off, seg_w, out in ((0, di, sv["xs"]), (di, gn, sv["Bs"]), (di + gn, gn, sv["Cs"])):
+                self._L("causal_conv1d_silu", zx + (di + seg_off) * esz, dip, self._p(W, p + "conv_w", seg_off * c.d_conv),
+                        self._p(W, p + "conv_b", seg_off), out, seg_w, self.batch, self.seqlen, seg_w, c.d_conv)
+            self._L("softplus_bias", zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), sv["dt"], T, H)
+            self._L32("neg_exp", self._p(self.w32, p + "A_log"), sv["A"], H)
+            self._L("ssd_scan", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], sv["y"], self.ssd_scratch, *self.ssd_dims)
+            self._L("ssd_gate", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, sv["u"], T, H, P)
+            self._L("rmsnorm_ij_j", sv["u"], self._p(W, p + "gnorm_w"), c.eps, sv["un"], sv["rstd2"], T, di)
+            self._L("inner_product_ij_jk_ik", sv["un"], self._p(W, p + "out_proj"), 1.0, self.o, 0.0, T, di, c.d_model)
+            self._L("addition", self.h, self.o, self.h, T * c.d_model)
+        self._L("rmsnorm_ij_j", self.h, self._p(W, "normf_w"), c.eps, self.hn, self.rstdf, T, c.d_model)
+        self._L("inner_product_ij_kj_ik", self.hn, self._p(W, "embedding"), 1.0, self.logits, 0.0, T, c.d_model, c.vocab)
+
+    def loss_and_logit_gradient(self):
+        """Mean cross-entropy (device scalar in loss_sum after the reduce) and, in place of the logits, its
+        gradient times loss_scale."""
+        c, T = self.cfg, self.T
+        self._L("cross_entropy", self.logits, self.targets, self.loss_scale / T, self.loss_rows, self.logits, T, c.vocab)
+        self._L32("reduce_ij_i", self.loss_rows, self.loss_sum, 0.0, 1, T)
+
+    # ------------------------------------------------------------------ backward
+    def backward(self):
+        c, T = self.cfg, self.T
+        W, G16, G32 = self.w16, self.g16, self.g32
+        di, gn, H, P = c.d_inner, c.ngroups * c.d_state, c.heads, c.headdim
+        dip, esz = c.d_in_proj, 2
+        self._L32("fill", G32, 0.0, self.n_flat)
+        self._L("fill", G16, 0.0, self.n_flat)
+        gl = self.logits   # holds d loss / d logits
+        self._L("inner_product_ij_jk_ik", gl, self._p(W, "embedding"), 1.0, self.gt, 0.0, T, c.vocab, c.d_model)
+        self._L("inner_product_ji_jk_ik", gl, self.hn, 1.0, self._p(G16, "embedding"), 0.0, c.vocab, T, c.d_model)
+        self._L("rmsnorm_ij_j_reverse", self.h, self._p(W, "normf_w"), self.rstdf, self.gt, c.eps, self.gh, self._p(G16, "normf_w"),
+                0.0, self.rms_scratch, T, c.d_model)
+        for i in reversed(range(c.n_layer)):
+            sv, p = self.saved[i], f"layers.{i}."
+            zx, gzx = sv["zx"].data_ptr(), self.gzx.data_ptr()
+            # out_proj
+            self._L("inner_product_ij_kj_ik", self.gh, self._p(W, p + "out_proj"), 1.0, self.gun, 0.0, T, c.d_model, di)
+            self._L("inner_product_ji_jk_ik", sv["un"], self.gh, 1.0, self._p(G16, p + "out_proj"), 0.0, di, T, c.d_model)
+            self._L("rmsnorm_ij_j_reverse", sv["u"], self._p(W, p + "gnorm_w"), sv["rstd2"], self.gun, c.eps, self.gu,
+                    self._p(G16, p + "gnorm_w"), 0.0, self.rms_scratch, T, di)
+            self._L("ssd_gate_reverse", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, self.gu, self.gy, gzx, dip,
+                    self._p(G32, p + "D"), T, H, P)
+            self._L("ssd_scan_reverse", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], self.gy, self.gxs, self.gdt, self.gA,
+                    self.gBs, self.gCs, self.ssd_scratch, *self.ssd_dims)
+            self._L("head_scale_accumulate", self._p(self.w32, p + "D"), self.gy, self.gxs, T, H, P)
+            self._L32("hadamard_reverse", self.gA, sv["A"], self._p(G32, p + "A_log"), H)   # dA/dA_log = A
+            self._L("softplus_bias_reverse", zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), self.gdt,
+                    gzx + (di + c.conv_dim) * esz, dip, self._p(G32, p + "dt_bias"), T, H)
+            for seg_off, seg_w, g in ((0, di, self.gxs), (di, gn, self.gBs), (di + gn, gn, self.gCs)):
+                self._L("causal_conv1d_silu_reverse", zx + (di + seg_off) * esz, dip, self._p(W, p + "conv_w", seg_off * c.d_conv),
+                        self._p(W, p + "conv_b", seg_off), g, seg_w, gzx + (di + seg_off) * esz, dip,
+                        self._p(G32, p + "conv_w", seg_off * c.d_conv), self._p(G32, p + "conv_b", seg_off), self.batch, self.seqlen,
+                        seg_w, c.d_conv)
+            # in_proj
+            self._L("inner_product_ij_kj_ik", self.gzx, self._p(W, p + "in_proj"), 1.0, self.gt, 0.0, T, dip, c.d_model)
+            self._L("inner_product_ji_jk_ik", sv["xn"], self.gzx, 1.0, self._p(G16, p + "in_proj"), 0.0, c.d_model, T, dip)
+            # the block's share joins the residual gradient already in gh
+            self._L("rmsnorm_ij_j_reverse", sv["h_in"], self._p(W, p + "norm_w"), sv["rstd1"], self.gt, c.eps, self.gh,
+                    self._p(G16, p + "norm_w"), 1.0, self.rms_scratch, T, c.d_model)
+            # (alpha = 1 would also accumulate the gain gradient; G16 was zero-filled, so that is a plain write)
+        self._L("embedding_reverse", self.ids, self.gh, self._p(G32, "embedding"), T, c.d_model, c.vocab)
+        self._lib.launch_convert_r16_r32(C.c_void_p(G16.data_ptr()), C.c_void_p(G32.data_ptr()), 1.0, self.n_flat, self.stream.ctx)
+
+    # ------------------------------------------------------------------ optimizer
+    def adam_step(self, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, world=1):
+        self.step_count += 1
+        self._L32("adam", self.w32, self.g32, self.m, self.v, lr, beta1, beta2, eps, 1.0 / (self.loss_scale * world), self.step_count,
+                  self.n_flat)
+        self._refresh_w16()
+
+    def train_step(self, comm=None, world=1, **adam):
+        """forward, loss, backward, (all-reduce), Adam.  Returns nothing: the mean loss of the step is read
+        with ``loss()`` after a stream synchronisation."""
+        self.forward()
+        self.loss_and_logit_gradient()
+        self.backward()
+        if comm is not None and world > 1:
+            comm.all_reduce_sum(self.g32, self.stream)
+        self.adam_step(world=world, **adam)
+
+    def loss(self) -> float:
+        self.stream.sync()
+        return float(self.loss_sum.item()) / self.T
+
+    def grad(self, name):
+        """Gradient of a parameter (float32 host array, already divided by loss_scale)."""
+        self.stream.sync()
+        o, shape = self.offsets[name]
+        return (self.g32[o:o + math.prod(shape)].reshape(shape) / self.loss_scale).cpu().numpy()
+
+    def launches_per_step(self) -> int:
+        n = self.cfg.n_layer
+        return 1 + 13 * n + 2 + 2 + 5 + 19 * n + 2 + 2

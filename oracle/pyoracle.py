@@ -234,3 +234,94 @@ def ssd_reverse(x, dt, A, Bm, Cm, gy):
     fn(_p(x), _p(dt), _p(A), _p(Bm), _p(Cm), _p(gy), _p(gx), _p(gdt), _p(gA), _p(gB), _p(gC),
        *(C.c_size_t(v) for v in (nb, L, H, P, N, G)))
     return gx, gdt, gA, gB, gC
+
+
+# ---------------------------------------------------------------------------
+# Operators around the scan in a language-model step (numpy float64, written
+# from the definitions in include/mp_kernels.h; no reference file exists).
+# ---------------------------------------------------------------------------
+def _sigmoid(x):
+    return 1.0 / (1.0 + np.exp(-x))
+
+
+def embedding(table, ids):
+    out = np.zeros((len(ids), table.shape[1]), dtype=np.float64)
+    ok = (ids >= 0) & (ids < table.shape[0])
+    out[ok] = table[ids[ok]]
+    return out
+
+
+def embedding_reverse(ids, gy, vocab):
+    g = np.zeros((vocab, gy.shape[1]), dtype=np.float64)
+    ok = (ids >= 0) & (ids < vocab)
+    np.add.at(g, ids[ok], gy[ok].astype(np.float64))
+    return g
+
+
+def _conv_pre(x, w, bias):
+    nb, L, Cn = x.shape
+    W = w.shape[1]
+    xp = np.concatenate([np.zeros((nb, W - 1, Cn)), x.astype(np.float64)], axis=1)
+    pre = np.zeros((nb, L, Cn)) + (0.0 if bias is None else bias.astype(np.float64))
+    for k in range(W):
+        pre += w[:, k].astype(np.float64) * xp[:, k:k + L, :]
+    return pre, xp
+
+
+def causal_conv1d_silu(x, w, bias):
+    pre, _ = _conv_pre(x, w, bias)
+    return pre * _sigmoid(pre)
+
+
+def causal_conv1d_silu_reverse(x, w, bias, gy):
+    nb, L, Cn = x.shape
+    W = w.shape[1]
+    pre, xp = _conv_pre(x, w, bias)
+    s = _sigmoid(pre)
+    dpre = gy.astype(np.float64) * s * (1.0 + pre * (1.0 - s))
+    dpad = np.concatenate([dpre, np.zeros((nb, W - 1, Cn))], axis=1)
+    gx = np.zeros((nb, L, Cn))
+    gw = np.zeros((Cn, W))
+    for k in range(W):
+        gx += w[:, k].astype(np.float64) * dpad[:, W - 1 - k:W - 1 - k + L, :]
+        gw[:, k] = np.sum(dpre * xp[:, k:k + L, :], axis=(0, 1))
+    return gx, gw, dpre.sum(axis=(0, 1))
+
+
+def softplus_bias(raw, bias):
+    v = raw.astype(np.float64) + bias.astype(np.float64)
+    return np.where(v > 20.0, v, np.log1p(np.exp(np.minimum(v, 20.0))))
+
+
+def softplus_bias_reverse(raw, bias, gdt):
+    g = gdt.astype(np.float64) * _sigmoid(raw.astype(np.float64) + bias.astype(np.float64))
+    return g, g.sum(axis=0)
+
+
+def ssd_gate(y, x, D, z, heads, headdim):
+    d = np.repeat(D.astype(np.float64), headdim)
+    return (y + d * x) * z * _sigmoid(z)
+
+
+def ssd_gate_reverse(y, x, D, z, gu, heads, headdim):
+    d = np.repeat(D.astype(np.float64), headdim)
+    s = _sigmoid(z)
+    gy = gu * z * s
+    gz = gu * (y + d * x) * (s + z * s * (1.0 - s))
+    gD = (gy * x).reshape(-1, heads, headdim).sum(axis=(0, 2))
+    return gy, gz, gD
+
+
+def cross_entropy(logits, targets, scale):
+    x = logits.astype(np.float64)
+    m, n = x.shape
+    mx = x.max(axis=1, keepdims=True)
+    e = np.exp(x - mx)
+    s = e.sum(axis=1, keepdims=True)
+    valid = (targets >= 0) & (targets < n)
+    tg = np.where(valid, targets, 0)
+    loss = np.where(valid, np.log(s[:, 0]) + mx[:, 0] - x[np.arange(m), tg], 0.0)
+    g = e / s
+    g[np.arange(m), tg] -= 1.0
+    g = np.where(valid[:, None], g * scale, 0.0)
+    return loss, g

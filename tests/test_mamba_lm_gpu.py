@@ -1,0 +1,58 @@
+"""Reduced instance of the Mamba-2 language-model training step: loss and every
+parameter gradient of the C-ABI composition (r16 activations) against the
+float64 CPU statement with autograd, then one Adam step against the oracle's
+Adam on the same gradients."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_reduced_lm_step(mp, stream, orc):
+    import torch
+    from metaphor_b200.mamba_lm import LMConfig, MambaLM, init_weights
+    from oracle import lm_oracle
+
+    cfg = LMConfig(d_model=256, n_layer=2, vocab=1024, chunk=128)
+    batch, seqlen = 2, 256
+    w = init_weights(cfg, seed=0)
+    rng = np.random.default_rng(1000)
+    ids = rng.integers(0, cfg.vocab, size=batch * seqlen).astype(np.int32)
+    targets = rng.integers(0, cfg.vocab, size=batch * seqlen).astype(np.int32)
+
+    model = MambaLM(cfg, batch, seqlen, weights=w, stream=stream, loss_scale=256.0)
+    torch.cuda.current_stream().synchronize()
+    model.set_batch(torch.from_numpy(ids), torch.from_numpy(targets))
+    model.forward()
+    model.loss_and_logit_gradient()
+    model.backward()
+    loss = model.loss()
+    assert stream.status() == 0
+
+    # the oracle sees the weights the contractions see: rounded to r16 (per-head parameters stay r32)
+    small = ("dt_bias", "A_log", "D")
+    wt = {k: torch.tensor(v.astype(np.float64) if k.split(".")[-1] in small else v.astype(np.float16).astype(np.float64), requires_grad=True)
+          for k, v in w.items()}
+    ref = lm_oracle.forward_loss(cfg, wt, torch.from_numpy(ids.astype(np.int64)), torch.from_numpy(targets.astype(np.int64)), batch, seqlen)
+    ref.backward()
+    ref_loss = float(ref.detach())
+    assert abs(loss - ref_loss) <= 2e-3 * abs(ref_loss), (loss, ref_loss)
+    worst = {}
+    for name in w:
+        g, r = model.grad(name).astype(np.float64), wt[name].grad.numpy()
+        err = np.max(np.abs(g - r)) / max(np.max(np.abs(r)), 1e-30)
+        worst[name] = err
+    print('loss', loss, ref_loss, 'worst gradient errors', sorted(worst.items(), key=lambda kv: -kv[1])[:5])
+    bad = {k: v for k, v in worst.items() if v > 2e-2}
+    assert not bad, f"gradients outside 2e-2 of the float64 oracle: {bad}"
+
+    # Adam on the flat buffer against the scalar oracle on the same gradient
+    g32 = model.g32.cpu().numpy().copy()
+    w32 = model.w32.cpu().numpy().copy()
+    model.adam_step(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8)
+    stream.sync()
+    mref, vref = np.zeros_like(w32), np.zeros_like(w32)
+    wref, _, _ = orc.adam(w32.copy(), g32, mref, vref, 3e-4, 0.9, 0.95, 1e-8, 1.0 / 256.0, 1)
+    got = model.w32.cpu().numpy()
+    assert np.max(np.abs(got - wref)) <= 1e-6
+    assert np.array_equal(model.w16.cpu().numpy(), got.astype(np.float16))
