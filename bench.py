@@ -442,6 +442,149 @@ def run_reference(args):
     }), flush=True)
 
 
+def run_lm(args):
+    """`--workload lm`: data-parallel training step of the Mamba-2 language model of configs[4]
+    (d_model 768, 24 layers, expand 2, headdim 64, d_state 128, vocab 50280; seq 2048, batch 8 per GPU,
+    fused Adam lr 3e-4 betas 0.9/0.95, all-reduce of the r32 gradient).  A step = forward, cross-entropy,
+    reverse, all-reduce, Adam; `value` = tokens/s over all ranks with the token ids resident on the
+    device, `e2e` = the same step with the ids copied from pinned host memory and the loss read back."""
+    import torch
+    import torch.distributed as dist
+    import metaphor_b200 as mp
+    from metaphor_b200.dist import GradientComm
+    from metaphor_b200.mamba_lm import LMConfig, MambaLM
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    lib = mp.lib()
+    lib.mpInitDevice(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    comm = GradientComm(world, rank) if world > 1 else None
+    cfg = LMConfig(n_layer=args.lm_layers)
+    batch, seqlen = args.lm_batch, 2048
+    model = MambaLM(cfg, batch, seqlen, seed=0, loss_scale=65536.0)
+    stream, ts = model.stream, model.stream.torch_stream()
+    T = batch * seqlen
+    gen = torch.Generator().manual_seed(1000 + rank)
+    tok = torch.randint(0, cfg.vocab, (T + 1,), generator=gen, dtype=torch.int32)
+    ids_h, tgt_h = tok[:-1].contiguous().pin_memory(), tok[1:].contiguous().pin_memory()
+    model.set_batch(ids_h, tgt_h)
+    adam = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8)
+    if not args.lm_no_graph:
+        model.capture()
+
+    def barrier():
+        stream.sync()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(args.warmup):
+        model.train_step(comm=comm, world=world, **adam)
+    barrier()
+    first_loss = None
+    wall0 = time.time()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    phase = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+    e0.record(ts)
+    for k in range(args.steps):
+        last = k == args.steps - 1
+        if last: phase[0].record(ts)
+        if args.lm_no_graph:
+            model.forward()
+            if last: phase[1].record(ts)
+            model.loss_and_logit_gradient()
+            model.backward()
+        else:
+            if last: phase[1].record(ts)
+            model.forward_backward()
+        if last: phase[2].record(ts)
+        if comm is not None:
+            comm.all_reduce_sum(model.g32, stream)
+        if last: phase[3].record(ts)
+        model.adam_step(world=world, **adam)
+        if last: phase[4].record(ts)
+    e1.record(ts)
+    barrier()
+    wall1 = time.time()
+    clocks = sampler.stop(wall0, wall1) if rank == 0 else None
+    if stream.status() != 0:
+        raise SystemExit("a kernel reported a non-zero status word")
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_per_step = float(t.item()) / args.steps
+    value = world * T / (ms_per_step * 1e-3)
+    last_loss = model.loss()
+
+    # end to end: ids from pinned host memory every step, loss read back every step
+    barrier()
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    e0.record(ts)
+    for _ in range(e2e_steps):
+        model.set_batch(ids_h, tgt_h)
+        model.train_step(comm=comm, world=world, **adam)
+        _ = model.loss()
+    e1.record(ts)
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / e2e_steps
+
+    if rank == 0:
+        n_params = cfg.n_params()
+        gemm_params = n_params - 0   # every parameter but the small vectors sits in a contraction; the embedding is tied
+        # model flops per step and GPU: 6 x params x tokens for the contractions + the scan (forward 1x, reverse 2x)
+        Q, H, P, NS = cfg.chunk, cfg.heads, cfg.headdim, cfg.d_state
+        ssd_fwd = (2 * Q * Q * NS) * (T // Q) + (2 * Q * Q * P + 4 * Q * NS * P) * (cfg.heads * T // Q)
+        flops = 6.0 * gemm_params * T + 3.0 * ssd_fwd * cfg.n_layer
+        achieved = flops / (ms_per_step * 1e-3) / 1e12
+        peak = 1381.7
+        try:
+            peak = float(json.loads((Path(__file__).resolve().parent / "MEASURED_PEAKS.json").read_text()).get("bf16_tflops_sustained", peak))
+        except Exception:
+            pass
+        ph = [phase[i].elapsed_time(phase[i + 1]) for i in range(4)]
+        out = {
+            "metric": "Mamba-2 LM training throughput", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations, f32 accumulation and master weights",
+            "data": "synthetic (token ids ~ U[0, 50280), seed 1000 + rank; weights N(0, 0.02), seed 0 on every rank)",
+            "config": {"workload": "configs[4]: Mamba-2 LM d_model 768, %d layers, expand 2, headdim 64, d_state 128, vocab 50280, "
+                                   "seq 2048, batch %d per GPU, cross-entropy, fused Adam lr 3e-4 betas 0.9/0.95, NCCL all-reduce of "
+                                   "the r32 gradient" % (cfg.n_layer, batch),
+                       "assumed": "d_conv 4, tied embedding / LM head, gated RMSNorm before out_proj, D skip, chunk 256, loss scale 65536",
+                       "params": n_params, "tokens_per_gpu_step": T,
+                       "l2": "activations and weights (GBs per step) exceed the 126 MB L2; no flush needed"},
+            "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "peak_kind": "measured sustained bf16 (fp16 runs on the same pipe)",
+                         "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
+                         "algorithmic_flops": flops,
+                         "phases_ms": {"forward" if args.lm_no_graph else "(graph: see next)": round(ph[0], 2),
+                                       "loss+reverse" if args.lm_no_graph else "forward+loss+reverse (one graph launch)": round(ph[1], 2), "all_reduce": round(ph[2], 2),
+                                       "adam+refresh": round(ph[3], 2)}},
+            "cpu_baseline": None,
+            "e2e": {"value": round(world * T / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": 2 * T * 4,
+                    "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
+            "clocks": clocks, "gpu_launches": model.launches_per_step() * args.steps,
+            "loss": {"first_timed_step": first_loss, "last": round(last_loss, 4)},
+        }
+        print(json.dumps(out), flush=True)
+    if comm is not None:
+        comm.close()
+    stream.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_profile_case(spec: str):
     """`--profile-case OP:DTYPE:ROWS[:COLS]`: three launches of one kernel on a
     small case, for an ncu capture (no timing, no JSON).  OP is one of
@@ -525,6 +668,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=10, help="upper bound on end-to-end steps (PCIe-bound)")
     ap.add_argument("--cpu-rows", type=int, default=32768, help="rows in the CPU baseline sample")
+    ap.add_argument("--workload", default="rows", choices=["rows", "lm"],
+                    help="rows = configs[1] (default, the headline line); lm = configs[4] training step, tokens/s")
+    ap.add_argument("--lm-layers", type=int, default=24)
+    ap.add_argument("--lm-batch", type=int, default=8)
+    ap.add_argument("--lm-no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--profile-case", default=None, help="OP:DTYPE:ROWS[:COLS], three launches for an ncu capture")
     args = ap.parse_args()
     if args.profile_case:
@@ -534,6 +682,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "lm":
+        run_lm(args)
     else:
         run_ours(args)
 

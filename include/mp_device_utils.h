@@ -66,6 +66,17 @@ MP_EXTERN_C void mpEventDestroy(void* event);
 MP_EXTERN_C void mpEventRecord(void* event, StreamContext);
 MP_EXTERN_C void mpStreamWaitEvent(StreamContext, void* event);
 
+/* Stream capture into a CUDA graph (the reference launches every kernel from the
+ * host each step, graph.zig:552-631; a training step here is several hundred
+ * launches).  Launcher calls made on ctx's stream between Begin and End are
+ * recorded, not executed; mpGraphLaunch replays them in stream order.  Calls that
+ * synchronise (mpGetStatus, mpStreamSynchronize, mpDeviceSynchronize) are not
+ * allowed inside the captured region. */
+MP_EXTERN_C void mpGraphBeginCapture(StreamContext);
+MP_EXTERN_C void* mpGraphEndCapture(StreamContext);
+MP_EXTERN_C void mpGraphLaunch(void* graph, StreamContext);
+MP_EXTERN_C void mpGraphDestroy(void* graph);
+
 /* Pinned host memory for the end-to-end copy path (the reference copies from
  * pageable memory, src/core/utils.zig:159-218; pinned buffers let
  * mpMemcpyHtoD / mpMemcpyDtoH run at link speed). */

@@ -98,6 +98,10 @@ UTILS = {
     "mpEventDestroy": (None, [P]),
     "mpEventRecord": (None, [P, CTX]),
     "mpStreamWaitEvent": (None, [CTX, P]),
+    "mpGraphBeginCapture": (None, [CTX]),
+    "mpGraphEndCapture": (P, [CTX]),
+    "mpGraphLaunch": (None, [P, CTX]),
+    "mpGraphDestroy": (None, [P]),
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
     "mpSsdScanScratchBytes": (L, [L, L, L, L, L, L, L, U32]),
     "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),

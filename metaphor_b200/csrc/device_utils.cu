@@ -170,3 +170,25 @@ extern "C" void mpEventRecord(void* event, StreamContext ctx) {
 extern "C" void mpStreamWaitEvent(StreamContext ctx, void* event) {
   MP_CUDA_CHECK(cudaStreamWaitEvent(mp_stream(ctx), static_cast<cudaEvent_t>(event), 0));
 }
+
+// Stream capture: a launch-bound sequence of launcher calls (hundreds of kernels per training step)
+// is recorded once and replayed with one call.  Everything the launchers do is stream-ordered and
+// allocation-free, so any sequence of them can be captured; calls that synchronise (mpGetStatus,
+// mpStreamSynchronize, mpMemcpy* from pageable memory) must stay outside the captured region.
+extern "C" void mpGraphBeginCapture(StreamContext ctx) {
+  MP_CUDA_CHECK(cudaStreamBeginCapture(mp_stream(ctx), cudaStreamCaptureModeThreadLocal));
+}
+extern "C" void* mpGraphEndCapture(StreamContext ctx) {
+  cudaGraph_t graph = nullptr;
+  MP_CUDA_CHECK(cudaStreamEndCapture(mp_stream(ctx), &graph));
+  cudaGraphExec_t exec = nullptr;
+  MP_CUDA_CHECK(cudaGraphInstantiate(&exec, graph, 0));
+  MP_CUDA_CHECK(cudaGraphDestroy(graph));
+  return exec;
+}
+extern "C" void mpGraphLaunch(void* exec, StreamContext ctx) {
+  MP_CUDA_CHECK(cudaGraphLaunch(static_cast<cudaGraphExec_t>(exec), mp_stream(ctx)));
+}
+extern "C" void mpGraphDestroy(void* exec) {
+  if (exec != nullptr) MP_CUDA_CHECK(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(exec)));
+}

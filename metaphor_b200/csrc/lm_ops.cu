@@ -87,11 +87,13 @@ __global__ void __launch_bounds__(256) embedding_reverse_kernel(const int* __res
 // depthwise causal convolution + SiLU over [batch, len, channels] (pitched rows)
 //   pre[b,l,c] = bias[c] + sum_k w[c,k] x[b, l - W + 1 + k, c]   (x = 0 before the sequence)
 //   y = pre * sigmoid(pre)
-// CTA = 32 channel groups x 8 time lanes, every thread walks CONV_LT steps with
-// the last W inputs in registers.
+// A thread owns CONV_LT consecutive steps of V channels and loads the CONV_LT + W - 1
+// inputs it needs up front (independent loads; neighbouring threads share them through
+// L1 / L2).  CTA = 32 channel groups x CONV_TY time lanes.
 // ---------------------------------------------------------------------------
-constexpr int CONV_LT = 16;
+constexpr int CONV_LT = 4;
 constexpr int CONV_TY = 8;
+constexpr int CONV_NB = 4;   // reverse: time blocks walked by one CTA (fewer atomics on the tap gradients)
 
 template <typename T, int V, int W>
 __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_kernel(const T* __restrict__ x, size_t xp, const T* __restrict__ w,
@@ -99,13 +101,22 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_kernel(const T* __re
                                                                   int L, int C) {
   using A = typename Acc<T>::type;
   const int c0 = (blockIdx.x * 32 + threadIdx.x) * V;
-  if (c0 >= C) return;
   const int l0 = (blockIdx.y * CONV_TY + threadIdx.y) * CONV_LT;
-  if (l0 >= L) return;
+  if (c0 >= C || l0 >= L) return;
   const size_t b = blockIdx.z;
   const T* xb = x + b * L * xp + c0;
   T* yb = y + b * L * yp + c0;
-  A wk[W][V], bs[V], win[W][V];
+  A xw[CONV_LT + W - 1][V];
+#pragma unroll
+  for (int j = 0; j < CONV_LT + W - 1; ++j) {
+    const int l = l0 - (W - 1) + j;
+    if (l >= 0 && l < L) load_vec<T, V>(xb + static_cast<size_t>(l) * xp, xw[j]);
+    else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) xw[j][e] = A(0);
+    }
+  }
+  A wk[W][V], bs[V];
 #pragma unroll
   for (int e = 0; e < V; ++e) {
     bs[e] = bias != nullptr ? mp_up(bias[c0 + e]) : A(0);
@@ -113,37 +124,24 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_kernel(const T* __re
     for (int k = 0; k < W; ++k) wk[k][e] = mp_up(w[static_cast<size_t>(c0 + e) * W + k]);
   }
 #pragma unroll
-  for (int k = 0; k < W - 1; ++k) {   // win[k + 1] = x[l0 - W + 1 + k]
-    const int l = l0 - W + 1 + k;
-    if (l >= 0) load_vec<T, V>(xb + static_cast<size_t>(l) * xp, win[k + 1]);
-    else {
+  for (int j = 0; j < CONV_LT; ++j) {
+    if (l0 + j < L) {
+      A r[V];
 #pragma unroll
-      for (int e = 0; e < V; ++e) win[k + 1][e] = A(0);
+      for (int e = 0; e < V; ++e) {
+        A acc = bs[e];
+#pragma unroll
+        for (int k = 0; k < W; ++k) acc += wk[k][e] * xw[j + k][e];
+        r[e] = acc * sigmoid_a(acc);
+      }
+      store_vec<T, V>(yb + static_cast<size_t>(l0 + j) * yp, r);
     }
-  }
-  const int l1 = min(l0 + CONV_LT, L);
-#pragma unroll 4
-  for (int l = l0; l < l1; ++l) {
-#pragma unroll
-    for (int k = 0; k < W - 1; ++k)
-#pragma unroll
-      for (int e = 0; e < V; ++e) win[k][e] = win[k + 1][e];
-    load_vec<T, V>(xb + static_cast<size_t>(l) * xp, win[W - 1]);
-    A r[V];
-#pragma unroll
-    for (int e = 0; e < V; ++e) {
-      A acc = bs[e];
-#pragma unroll
-      for (int k = 0; k < W; ++k) acc += wk[k][e] * win[k][e];
-      r[e] = acc * sigmoid_a(acc);
-    }
-    store_vec<T, V>(yb + static_cast<size_t>(l) * yp, r);
   }
 }
 
 // Reverse: dpre = gy * s * (1 + pre * (1 - s)) with pre recomputed;
 //   gx[l] = sum_k w[k] dpre[l + W - 1 - k];  gw[c,k] += sum_l dpre[l] x[l - W + 1 + k];  gbias[c] += sum_l dpre[l]
-// A thread owns CONV_LT steps and additionally recomputes the W - 1 steps after them.
+// A thread owns CONV_LT steps and also recomputes dpre of the W - 1 steps after them.
 template <typename T, int V, int W>
 __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const T* __restrict__ x, size_t xp,
                                                                           const T* __restrict__ w, const T* __restrict__ bias,
@@ -153,79 +151,76 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const
                                                                           typename Acc<T>::type* __restrict__ gbias, int L,
                                                                           int C) {
   using A = typename Acc<T>::type;
+  constexpr int ND = CONV_LT + W - 1;        // dpre values per thread
+  constexpr int NX = CONV_LT + 2 * (W - 1);  // inputs per thread
   __shared__ A red[CONV_TY][32][V * (W + 1) + 1];
   const int c0 = (blockIdx.x * 32 + threadIdx.x) * V;
-  const int l0 = (blockIdx.y * CONV_TY + threadIdx.y) * CONV_LT;
-  const bool live = c0 < C && l0 < L;
-  A gwk[W][V], gbs[V];
+  const bool live_c = c0 < C;
+  A gwk[W][V], gbs[V], wk[W][V], bs[V];
 #pragma unroll
   for (int e = 0; e < V; ++e) {
     gbs[e] = A(0);
+    bs[e] = (live_c && bias != nullptr) ? mp_up(bias[c0 + e]) : A(0);
 #pragma unroll
-    for (int k = 0; k < W; ++k) gwk[k][e] = A(0);
+    for (int k = 0; k < W; ++k) {
+      gwk[k][e] = A(0);
+      wk[k][e] = live_c ? mp_up(w[static_cast<size_t>(c0 + e) * W + k]) : A(0);
+    }
   }
-  if (live) {
-    const size_t b = blockIdx.z;
+  const size_t b = blockIdx.z;
+#pragma unroll 1
+  for (int nb = 0; nb < CONV_NB; ++nb) {
+    const int l0 = ((blockIdx.y * CONV_NB + nb) * CONV_TY + threadIdx.y) * CONV_LT;
+    if (!live_c || l0 >= L) continue;
     const T* xb = x + b * L * xp + c0;
     const T* gyb = gy + b * L * gyp + c0;
     T* gxb = gx + b * L * gxp + c0;
-    A wk[W][V], bs[V], win[W][V], dwin[W][V];
+    A xw[NX][V], dp[ND][V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
-      bs[e] = bias != nullptr ? mp_up(bias[c0 + e]) : A(0);
-#pragma unroll
-      for (int k = 0; k < W; ++k) { wk[k][e] = mp_up(w[static_cast<size_t>(c0 + e) * W + k]); dwin[k][e] = A(0); }
-    }
-#pragma unroll
-    for (int k = 0; k < W - 1; ++k) {
-      const int l = l0 - W + 1 + k;
-      if (l >= 0) load_vec<T, V>(xb + static_cast<size_t>(l) * xp, win[k + 1]);
+    for (int j = 0; j < NX; ++j) {
+      const int l = l0 - (W - 1) + j;
+      if (l >= 0 && l < L) load_vec<T, V>(xb + static_cast<size_t>(l) * xp, xw[j]);
       else {
 #pragma unroll
-        for (int e = 0; e < V; ++e) win[k + 1][e] = A(0);
+        for (int e = 0; e < V; ++e) xw[j][e] = A(0);
       }
     }
-    const int own_end = min(l0 + CONV_LT, L);
-    const int last = own_end + W - 1;   // exclusive: own steps plus the look-ahead
-#pragma unroll 2
-    for (int l = l0; l < last; ++l) {
 #pragma unroll
-      for (int k = 0; k < W - 1; ++k)
+    for (int j = 0; j < ND; ++j) {
+      if (l0 + j < L) load_vec<T, V>(gyb + static_cast<size_t>(l0 + j) * gyp, dp[j]);
+      else {
 #pragma unroll
-        for (int e = 0; e < V; ++e) { win[k][e] = win[k + 1][e]; dwin[k][e] = dwin[k + 1][e]; }
-      A g[V];
-      if (l < L) {
-        load_vec<T, V>(xb + static_cast<size_t>(l) * xp, win[W - 1]);
-        load_vec<T, V>(gyb + static_cast<size_t>(l) * gyp, g);
-      } else {
-#pragma unroll
-        for (int e = 0; e < V; ++e) { win[W - 1][e] = A(0); g[e] = A(0); }
+        for (int e = 0; e < V; ++e) dp[j][e] = A(0);
       }
+    }
+#pragma unroll
+    for (int j = 0; j < ND; ++j) {
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         A pre = bs[e];
 #pragma unroll
-        for (int k = 0; k < W; ++k) pre += wk[k][e] * win[k][e];
-        const A s = sigmoid_a(pre);
-        const A d = g[e] * s * (A(1) + pre * (A(1) - s));
-        dwin[W - 1][e] = d;
-        if (l < own_end) {
-          gbs[e] += d;
+        for (int k = 0; k < W; ++k) pre += wk[k][e] * xw[j + k][e];
+        const A sg = sigmoid_a(pre);
+        dp[j][e] *= sg * (A(1) + pre * (A(1) - sg));   // zero beyond the sequence (gy was loaded as zero)
+        if (j < CONV_LT) {
+          gbs[e] += dp[j][e];
 #pragma unroll
-          for (int k = 0; k < W; ++k) gwk[k][e] += d * win[k][e];
+          for (int k = 0; k < W; ++k) gwk[k][e] += dp[j][e] * xw[j + k][e];
         }
       }
-      const int m = l - (W - 1);   // gx[m] is complete now: dwin[j] = dpre[m + j]
-      if (m >= l0) {
+    }
+#pragma unroll
+    for (int m = 0; m < CONV_LT; ++m) {
+      if (l0 + m < L) {
         A r[V];
 #pragma unroll
         for (int e = 0; e < V; ++e) {
           A acc = A(0);
 #pragma unroll
-          for (int k = 0; k < W; ++k) acc += wk[k][e] * dwin[W - 1 - k][e];
+          for (int k = 0; k < W; ++k) acc += wk[k][e] * dp[m + W - 1 - k][e];
           r[e] = acc;
         }
-        store_vec<T, V>(gxb + static_cast<size_t>(m) * gxp, r);
+        store_vec<T, V>(gxb + static_cast<size_t>(l0 + m) * gxp, r);
       }
     }
   }
@@ -237,16 +232,16 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const
     red[threadIdx.y][threadIdx.x][e * (W + 1) + W] = gbs[e];
   }
   __syncthreads();
-  if (threadIdx.y == 0 && c0 < C) {
+  if (threadIdx.y == 0 && live_c) {
 #pragma unroll
     for (int e = 0; e < V; ++e) {
 #pragma unroll
       for (int k = 0; k <= W; ++k) {
-        A s = A(0);
+        A sum = A(0);
 #pragma unroll
-        for (int ty = 0; ty < CONV_TY; ++ty) s += red[ty][threadIdx.x][e * (W + 1) + k];
-        if (k < W) atomicAdd(gw + static_cast<size_t>(c0 + e) * W + k, s);
-        else if (gbias != nullptr) atomicAdd(gbias + c0 + e, s);
+        for (int ty = 0; ty < CONV_TY; ++ty) sum += red[ty][threadIdx.x][e * (W + 1) + k];
+        if (k < W) atomicAdd(gw + static_cast<size_t>(c0 + e) * W + k, sum);
+        else if (gbias != nullptr) atomicAdd(gbias + c0 + e, sum);
       }
     }
   }
@@ -433,16 +428,25 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const T* logi
   }
   mx = block_reduce(mx, true);   // (the barriers inside also publish the staged row)
   const T* rd = STAGED ? srow : src;
+  const long long tg = targets[row];
+  const bool valid = tg >= 0 && static_cast<size_t>(tg) < n;   // other targets: ignored row (zero loss, zero gradient)
+  // (global memory still holds the logits here: an aliased gradient is only written in the last pass)
+  const A x_target = (threadIdx.x == 0 && valid) ? mp_up(src[tg]) : A(0);
   A sum = A(0);
   for (size_t i = threadIdx.x; i < nv; i += CE_THREADS) {
     const VecT<T, V> x = *reinterpret_cast<const VecT<T, V>*>(rd + i * V);
+    VecT<T, V> ex;
 #pragma unroll
-    for (int e = 0; e < V; ++e) sum += exp_a(mp_up(x.v[e]) - mx);
+    for (int e = 0; e < V; ++e) {
+      const A t = exp_a(mp_up(x.v[e]) - mx);
+      sum += t;
+      ex.v[e] = mp_down<T>(t);
+    }
+    // the parked row now keeps exp(x - max) (at most one, in T): one exponential per element in total
+    if (STAGED) *reinterpret_cast<VecT<T, V>*>(srow + i * V) = ex;
   }
   sum = block_reduce(sum, false);
-  const long long tg = targets[row];
-  const bool valid = tg >= 0 && static_cast<size_t>(tg) < n;   // other targets: ignored row (zero loss, zero gradient)
-  if (threadIdx.x == 0 && loss != nullptr) loss[row] = valid ? log_a(sum) + mx - mp_up(rd[valid ? tg : 0]) : A(0);
+  if (threadIdx.x == 0 && loss != nullptr) loss[row] = valid ? log_a(sum) + mx - x_target : A(0);
   if (glogits != nullptr) {
     const A inv = scale / sum;
     T* dst = glogits + row * n;
@@ -451,7 +455,8 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const T* logi
       VecT<T, V> o;
 #pragma unroll
       for (int e = 0; e < V; ++e) {
-        A gval = valid ? exp_a(mp_up(x.v[e]) - mx) * inv : A(0);
+        A gval = A(0);
+        if (valid) gval = (STAGED ? mp_up(x.v[e]) : exp_a(mp_up(x.v[e]) - mx)) * inv;
         if (valid && i * V + e == static_cast<size_t>(tg)) gval -= scale;
         o.v[e] = mp_down<T>(gval);
       }
@@ -533,7 +538,8 @@ void conv_dispatch(bool reverse, const T* x, size_t xp, const T* w, const T* bia
                    typename Acc<T>::type* gw, typename Acc<T>::type* gbias, len_t batch, len_t len, len_t channels, len_t width,
                    cudaStream_t st) {
   const dim3 block(32, CONV_TY);
-  const dim3 grid(static_cast<unsigned>((channels / V + 31) / 32), static_cast<unsigned>((len + CONV_TY * CONV_LT - 1) / (CONV_TY * CONV_LT)),
+  const size_t steps_per_cta = static_cast<size_t>(CONV_TY) * CONV_LT * (reverse ? CONV_NB : 1);
+  const dim3 grid(static_cast<unsigned>((channels / V + 31) / 32), static_cast<unsigned>((len + steps_per_cta - 1) / steps_per_cta),
                   static_cast<unsigned>(batch));
   const int L = static_cast<int>(len), C = static_cast<int>(channels);
 #define MP_CONV_CASE(WW)                                                                                              \
@@ -571,7 +577,8 @@ void causal_conv1d_silu_reverse_impl(const void* x, len_t x_pitch, const void* w
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(gy, gy_pitch, channels) && vec_ok<T>(gx, gx_pitch, channels);
-  if (v) conv_dispatch<T, PN>(true, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
+  constexpr int RV = PN > 4 ? 4 : PN;   // reverse: at most 4 channels per thread (register footprint)
+  if (v) conv_dispatch<T, RV>(true, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
                               static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw), static_cast<A*>(gbias),
                               batch, len, channels, width, mp_stream(ctx));
   else conv_dispatch<T, 1>(true, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),

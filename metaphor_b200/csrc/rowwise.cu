@@ -650,14 +650,18 @@ inline size_t row_grid(const RowPlan& p, size_t m, int sm_count, int threads_per
 // Row groups each CTA of the RMSNorm reverse kernel walks (its gain-gradient
 // partial costs one scratch row, so more rows per CTA = less scratch traffic,
 // fewer rows = more CTAs in flight).
-inline size_t rms_rev_rows_per_cta() {
-  static size_t r = 0;
-  if (r == 0) {
+// `units` = row groups (register variant) or rows (staged variant) of the call: short matrices take
+// fewer rows per CTA so that at least ~8 CTAs per SM exist.
+inline size_t rms_rev_rows_per_cta(size_t units) {
+  static size_t cap = 0;
+  if (cap == 0) {
     const char* e = getenv("MP_RMS_REV_ROWS");
     long v = e ? strtol(e, nullptr, 10) : 0;
-    r = v > 0 ? static_cast<size_t>(v) : 32;
+    cap = v > 0 ? static_cast<size_t>(v) : 32;
   }
-  return r;
+  size_t r = units / (148 * 8);
+  if (r < 1) r = 1;
+  return r > cap ? cap : r;
 }
 // Staged (bulk-copy) plan of the RMSNorm reverse: rows of n*sizeof(T) bytes,
 // 256 threads, up to 4 packs per thread, at least 2 stages in ~100 KB.
@@ -691,7 +695,8 @@ StagedPlan plan_staged(size_t n, bool aligned) {
 }
 inline size_t rms_rev_grid(const RowPlan& p, size_t m) {
   const size_t groups = (m + p.rows - 1) / p.rows;
-  size_t grid = (groups + rms_rev_rows_per_cta() - 1) / rms_rev_rows_per_cta();
+  const size_t rpc = rms_rev_rows_per_cta(groups);
+  size_t grid = (groups + rpc - 1) / rpc;
   return grid < 1 ? 1 : grid;
 }
 
@@ -773,7 +778,7 @@ static size_t rmsnorm_rev_slots(size_t m, size_t n, int sm_count, bool aligned) 
   const RowPlan p = plan_rows<T>(n, aligned);
   (void)sm_count;
   size_t slots = rms_rev_grid(p, m) * p.rows;
-  const size_t staged = (m + rms_rev_rows_per_cta() - 1) / rms_rev_rows_per_cta();  // one slot per CTA
+  const size_t staged = (m + rms_rev_rows_per_cta(m) - 1) / rms_rev_rows_per_cta(m);  // one slot per CTA
   return slots > staged ? slots : staged;
 }
 
@@ -801,10 +806,11 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
     const RowPlan p = plan_rows<T>(n, aligned);
     const StagedPlan sp = plan_staged<T>(n, aligned);
     unsigned grid = static_cast<unsigned>(rms_rev_grid(p, m));
-    const size_t rpc = rms_rev_rows_per_cta();
+    size_t rpc = rms_rev_rows_per_cta((m + p.rows - 1) / p.rows);
     slots = static_cast<size_t>(grid) * p.rows;
     MpStreamState* state = mp_state_or_null(ctx);  // the staged kernel reports timeouts through the status word
     if (sp.ok && state != nullptr) {
+      rpc = rms_rev_rows_per_cta(m);
       grid = static_cast<unsigned>((m + rpc - 1) / rpc);
       slots = grid;
       uint32_t* status = state->status_dev;

@@ -60,6 +60,8 @@ struct SsdArgs {
   const __half* z;        // OUTPUT: optional row-dot partner, same indexing as o_out
   int z_pitch;
   float* dot_out;         // [B, H, L]
+  float* part_out;        // OUTPUT per group: fp32 partial sums [split][B*L][G*dv] (the heads of a group are
+  int head_splits;        //   divided over head_splits CTAs and folded afterwards); null / 1 otherwise
   uint32_t* status;
 };
 
@@ -211,7 +213,11 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
   int head0, nheads;
   if (MODE == MODE_SCORES) { head0 = g.scores_head ? unit : unit * hpg; nheads = 1; }
   else if (MODE == MODE_STATES) { head0 = unit; nheads = 1; }
-  else { head0 = g.out_head ? unit : unit * hpg; nheads = g.out_head ? 1 : hpg; }
+  else {
+    const int hps = g.out_head ? 1 : hpg / g.head_splits;   // heads per CTA
+    head0 = g.out_head ? unit : unit * hpg + static_cast<int>(blockIdx.x) * hps;
+    nheads = hps;
+  }
   float* s_dt = s_cum + g.Q;
   float* s_colf = s_dt + g.Q;   // [Q] column factors, each 64-column k-block relative to its own reference column
   const int n_items = ssd_num_items<MODE>(g, mt, c, nheads);
@@ -467,7 +473,8 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
       tcgen05_fence_after_sync();
       const int quarter = warp & 3;
       const int row = quarter * 32 + lane;   // accumulator row of this thread
-      const int RB = tile_n * (MODE == MODE_STATES ? 4 : 2);   // bytes of one staged row
+      const bool f32_out = MODE == MODE_STATES || (MODE == MODE_OUTPUT && g.part_out != nullptr);
+      const int RB = tile_n * (f32_out ? 4 : 2);   // bytes of one staged row
       unsigned char* stg_row = smem + row * RB;
       const int cpr = RB >> 4;             // 16-byte chunks per row: 8, 16 or 32
       const int rpi = 32 / cpr;            // rows moved per warp instruction
@@ -497,7 +504,7 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0u;
         }
-        if (MODE == MODE_STATES) {
+        if (f32_out) {
 #pragma unroll
           for (int p = 0; p < 8; ++p)
             *reinterpret_cast<uint4*>(stg_row + (((c0 / 4 + p) ^ (row & 7)) << 4)) = make_uint4(v[p * 4], v[p * 4 + 1], v[p * 4 + 2], v[p * 4 + 3]);
@@ -540,7 +547,12 @@ __global__ void __launch_bounds__(SSD_THREADS, 4) ssd_mma_kernel(const __grid_co
           *reinterpret_cast<uint4*>(dst + cc * 4) = val;
         } else {
           const size_t trow = static_cast<size_t>(r0 + mt * 128 + lrow);
-          if (g.o_out != nullptr) *reinterpret_cast<uint4*>(g.o_out + trow * g.o_pitch + unit * g.dv + cc * 8) = val;
+          if (g.part_out != nullptr) {
+            float* dst = g.part_out + (static_cast<size_t>(blockIdx.x) * g.B * g.L + trow) * g.o_pitch + unit * g.dv;
+            *reinterpret_cast<uint4*>(dst + cc * 4) = val;
+          } else if (g.o_out != nullptr) {
+            *reinterpret_cast<uint4*>(g.o_out + trow * g.o_pitch + unit * g.dv + cc * 8) = val;
+          }
         }
       }
     }
@@ -600,6 +612,23 @@ __global__ void __launch_bounds__(256) ssd_scalar_grads_kernel(const float* __re
   }
 }
 
+// out[i] = sum_s part[s][i] rounded to r16 (fold of the per-group partial outputs), 8 elements per thread
+__global__ void __launch_bounds__(256) ssd_fold_parts_kernel(const float* __restrict__ part, __half* __restrict__ out, size_t n,
+                                                             int splits) {
+  const size_t i = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 8;
+  if (i >= n) return;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int sidx = 0; sidx < splits; ++sidx) {
+    const float4 a = *reinterpret_cast<const float4*>(part + sidx * n + i);
+    const float4 b = *reinterpret_cast<const float4*>(part + sidx * n + i + 4);
+    acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+    acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+  }
+  st_pack(out + i, 0, pack<__half>(acc));
+}
+
 __global__ void ssd_sum_batches_kernel(const float* __restrict__ part, float* __restrict__ gA, int B, int H) {
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   if (h >= H) return;
@@ -642,9 +671,18 @@ CUtensorMap ssd_map(const void* base, size_t rows, size_t cols, uint32_t box_row
 
 struct SsdDims { int B, L, H, P, N, G, Q, nc; };
 
+// CTAs that share the heads of one group when an output is summed over them (gB, gC): with one CTA per
+// group and tile only B * L / 128 * G CTAs would exist, each walking all the group's heads in sequence.
+int ssd_head_splits(const SsdDims& d) {
+  const int hpg = d.H / d.G;
+  for (int sp = 4; sp > 1; --sp)
+    if (hpg % sp == 0) return sp;
+  return 1;
+}
+
 // Scratch layout (bytes, 256-aligned sections).
 struct SsdScratch {
-  float* cum; float* dtt; __half* scores; float* states; __half* hs; float* u; float* v; float* ga_part; __half* y_tmp;
+  float* cum; float* dtt; __half* scores; float* states; __half* hs; float* u; float* v; float* ga_part; float* parts;
   size_t total;
 };
 SsdScratch ssd_carve(void* base, const SsdDims& d, bool reverse) {
@@ -662,7 +700,7 @@ SsdScratch ssd_carve(void* base, const SsdDims& d, bool reverse) {
   s.u = static_cast<float*>(take(reverse ? bhl * 4 : 0));
   s.v = static_cast<float*>(take(reverse ? bhl * 4 : 0));
   s.ga_part = static_cast<float*>(take(reverse ? static_cast<size_t>(d.B) * d.H * 4 : 0));
-  s.y_tmp = nullptr;
+  s.parts = static_cast<float*>(take(reverse ? static_cast<size_t>(ssd_head_splits(d)) * d.B * d.L * d.G * d.N * 4 : 0));
   s.total = off;
   return s;
 }
@@ -696,6 +734,7 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
   g.o_out = r.out; g.o_pitch = (r.out_head ? d.H : d.G) * r.dv;
   g.z = r.z; g.z_pitch = g.o_pitch; g.dot_out = r.dot;
   g.status = status;
+  g.part_out = nullptr; g.head_splits = 1;
   const size_t rows = static_cast<size_t>(d.B) * d.L;
   const size_t qcols = static_cast<size_t>(r.q_head ? d.H : d.G) * r.dk;
   const size_t kcols = static_cast<size_t>(r.k_head ? d.H : d.G) * r.dk;
@@ -739,9 +778,18 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
     const size_t srows = static_cast<size_t>(d.B) * d.H * d.nc * 128;
     const CUtensorMap mh = g.state_t ? ssd_map(sc.hs, srows, d2, 128) : ssd_map(sc.hs, srows, d2, 64);
     const int units = r.out_head ? d.H : d.G;
-    const dim3 grid(1, d.Q / 128, d.B * d.nc * units);
+    const int splits = r.out_head ? 1 : ssd_head_splits(d);
+    g.head_splits = splits;
+    g.part_out = splits > 1 ? sc.parts : nullptr;
+    const dim3 grid(splits, d.Q / 128, d.B * d.nc * units);
     const size_t smem = configure(g.state_t ? TILE_BYTES : (r.dv / 64) * BOX_BYTES, r.dv);
     ssd_launch<MODE_OUTPUT>(ms, mv, mq, mh, g, grid, smem, st);
+    if (splits > 1) {
+      const size_t n = static_cast<size_t>(d.B) * d.L * d.G * r.dv;
+      ssd_fold_parts_kernel<<<static_cast<unsigned>((n / 8 + 255) / 256), 256, 0, st>>>(sc.parts, r.out, n, splits);
+      MP_LAUNCH_CHECK();
+    }
+    g.head_splits = 1; g.part_out = nullptr;
   }
 }
 

@@ -283,12 +283,27 @@ class MambaLM:
                   self.n_flat)
         self._refresh_w16()
 
+    def capture(self):
+        """Record forward + loss + backward once into a CUDA graph; later steps replay it with one call
+        (the step is several hundred launches, which the host cannot issue as fast as the device runs them)."""
+        self.forward(); self.loss_and_logit_gradient(); self.backward()   # first run outside capture: one-time setup
+        self.stream.sync()
+        self._lib.mpGraphBeginCapture(self.stream.ctx)
+        self.forward(); self.loss_and_logit_gradient(); self.backward()
+        self.graph = self._lib.mpGraphEndCapture(self.stream.ctx)
+
+    def forward_backward(self):
+        if getattr(self, "graph", None):
+            self._lib.mpGraphLaunch(self.graph, self.stream.ctx)
+        else:
+            self.forward()
+            self.loss_and_logit_gradient()
+            self.backward()
+
     def train_step(self, comm=None, world=1, **adam):
         """forward, loss, backward, (all-reduce), Adam.  Returns nothing: the mean loss of the step is read
         with ``loss()`` after a stream synchronisation."""
-        self.forward()
-        self.loss_and_logit_gradient()
-        self.backward()
+        self.forward_backward()
         if comm is not None and world > 1:
             comm.all_reduce_sum(self.g32, self.stream)
         self.adam_step(world=world, **adam)
