@@ -32,7 +32,8 @@ __device__ __forceinline__ void store_vec(T* p, const typename Acc<T>::type* in)
   *reinterpret_cast<VecT<T, V>*>(p) = x;
 }
 
-__device__ __forceinline__ float sigmoid_a(float x) { return 1.f / (1.f + __expf(-x)); }
+// ex2 + rcp on the special-function unit (an IEEE division would cost ten instructions per element)
+__device__ __forceinline__ float sigmoid_a(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 __device__ __forceinline__ double sigmoid_a(double x) { return 1.0 / (1.0 + exp(-x)); }
 __device__ __forceinline__ float exp_a(float x) { return __expf(x); }
 __device__ __forceinline__ double exp_a(double x) { return exp(x); }
@@ -141,7 +142,8 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_kernel(const T* __re
 
 // Reverse: dpre = gy * s * (1 + pre * (1 - s)) with pre recomputed;
 //   gx[l] = sum_k w[k] dpre[l + W - 1 - k];  gw[c,k] += sum_l dpre[l] x[l - W + 1 + k];  gbias[c] += sum_l dpre[l]
-// A thread owns CONV_LT steps and also recomputes dpre of the W - 1 steps after them.
+// A thread owns CONV_LT steps; the W - 1 values of dpre after them come from the next time lane of
+// the CTA through shared memory (the last lane recomputes them).
 template <typename T, int V, int W>
 __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const T* __restrict__ x, size_t xp,
                                                                           const T* __restrict__ w, const T* __restrict__ bias,
@@ -151,11 +153,14 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const
                                                                           typename Acc<T>::type* __restrict__ gbias, int L,
                                                                           int C) {
   using A = typename Acc<T>::type;
-  constexpr int ND = CONV_LT + W - 1;        // dpre values per thread
-  constexpr int NX = CONV_LT + 2 * (W - 1);  // inputs per thread
+  constexpr int H = W - 1;                   // look-ahead steps
+  constexpr int ND = CONV_LT + H;            // dpre values a thread needs
   __shared__ A red[CONV_TY][32][V * (W + 1) + 1];
-  const int c0 = (blockIdx.x * 32 + threadIdx.x) * V;
+  __shared__ A halo[CONV_TY][H][32][V];      // first H dpre of every time lane
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int c0 = (blockIdx.x * 32 + tx) * V;
   const bool live_c = c0 < C;
+  const bool last_lane = ty == CONV_TY - 1;
   A gwk[W][V], gbs[V], wk[W][V], bs[V];
 #pragma unroll
   for (int e = 0; e < V; ++e) {
@@ -168,59 +173,84 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const
     }
   }
   const size_t b = blockIdx.z;
+  const T* xb = x + b * L * xp + c0;
+  const T* gyb = gy + b * L * gyp + c0;
+  T* gxb = gx + b * L * gxp + c0;
+  auto dpre_of = [&](const A (*xwin)[V], const A* g, A* out) {   // xwin[k] = x[l - W + 1 + k]
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      A pre = bs[e];
+#pragma unroll
+      for (int k = 0; k < W; ++k) pre += wk[k][e] * xwin[k][e];
+      const A sg = sigmoid_a(pre);
+      out[e] = g[e] * sg * (A(1) + pre * (A(1) - sg));
+    }
+  };
 #pragma unroll 1
   for (int nb = 0; nb < CONV_NB; ++nb) {
-    const int l0 = ((blockIdx.y * CONV_NB + nb) * CONV_TY + threadIdx.y) * CONV_LT;
-    if (!live_c || l0 >= L) continue;
-    const T* xb = x + b * L * xp + c0;
-    const T* gyb = gy + b * L * gyp + c0;
-    T* gxb = gx + b * L * gxp + c0;
-    A xw[NX][V], dp[ND][V];
+    const int l0 = ((blockIdx.y * CONV_NB + nb) * CONV_TY + ty) * CONV_LT;
+    const bool live = live_c && l0 < L;
+    A xw[CONV_LT + 2 * H][V], dp[ND][V];
 #pragma unroll
-    for (int j = 0; j < NX; ++j) {
-      const int l = l0 - (W - 1) + j;
-      if (l >= 0 && l < L) load_vec<T, V>(xb + static_cast<size_t>(l) * xp, xw[j]);
-      else {
+    for (int j = 0; j < ND; ++j)
 #pragma unroll
-        for (int e = 0; e < V; ++e) xw[j][e] = A(0);
+      for (int e = 0; e < V; ++e) dp[j][e] = A(0);
+    if (live) {
+      const int nx = last_lane ? CONV_LT + 2 * H : CONV_LT + H;   // the last lane also recomputes the look-ahead
+#pragma unroll
+      for (int j = 0; j < CONV_LT + 2 * H; ++j) {
+        const int l = l0 - H + j;
+        if (j < nx && l >= 0 && l < L) load_vec<T, V>(xb + static_cast<size_t>(l) * xp, xw[j]);
+        else {
+#pragma unroll
+          for (int e = 0; e < V; ++e) xw[j][e] = A(0);
+        }
       }
-    }
+      const int ng = last_lane ? ND : CONV_LT;
 #pragma unroll
-    for (int j = 0; j < ND; ++j) {
-      if (l0 + j < L) load_vec<T, V>(gyb + static_cast<size_t>(l0 + j) * gyp, dp[j]);
-      else {
+      for (int j = 0; j < ND; ++j)
+        if (j < ng && l0 + j < L) load_vec<T, V>(gyb + static_cast<size_t>(l0 + j) * gyp, dp[j]);   // gy for now
 #pragma unroll
-        for (int e = 0; e < V; ++e) dp[j][e] = A(0);
-      }
-    }
+      for (int j = 0; j < CONV_LT; ++j) {
+        dpre_of(&xw[j], dp[j], dp[j]);      // zero beyond the sequence (gy stayed zero there)
 #pragma unroll
-    for (int j = 0; j < ND; ++j) {
-#pragma unroll
-      for (int e = 0; e < V; ++e) {
-        A pre = bs[e];
-#pragma unroll
-        for (int k = 0; k < W; ++k) pre += wk[k][e] * xw[j + k][e];
-        const A sg = sigmoid_a(pre);
-        dp[j][e] *= sg * (A(1) + pre * (A(1) - sg));   // zero beyond the sequence (gy was loaded as zero)
-        if (j < CONV_LT) {
+        for (int e = 0; e < V; ++e) {
           gbs[e] += dp[j][e];
 #pragma unroll
           for (int k = 0; k < W; ++k) gwk[k][e] += dp[j][e] * xw[j + k][e];
         }
       }
+      if (last_lane) {
+#pragma unroll
+        for (int j = CONV_LT; j < ND; ++j) dpre_of(&xw[j], dp[j], dp[j]);
+      }
     }
 #pragma unroll
-    for (int m = 0; m < CONV_LT; ++m) {
-      if (l0 + m < L) {
-        A r[V];
+    for (int j = 0; j < H; ++j)
 #pragma unroll
-        for (int e = 0; e < V; ++e) {
-          A acc = A(0);
+      for (int e = 0; e < V; ++e) halo[ty][j][tx][e] = dp[j][e];
+    __syncthreads();
+    if (!last_lane) {
 #pragma unroll
-          for (int k = 0; k < W; ++k) acc += wk[k][e] * dp[m + W - 1 - k][e];
-          r[e] = acc;
+      for (int j = 0; j < H; ++j)
+#pragma unroll
+        for (int e = 0; e < V; ++e) dp[CONV_LT + j][e] = halo[ty + 1][j][tx][e];
+    }
+    __syncthreads();
+    if (live) {
+#pragma unroll
+      for (int m = 0; m < CONV_LT; ++m) {
+        if (l0 + m < L) {
+          A r[V];
+#pragma unroll
+          for (int e = 0; e < V; ++e) {
+            A acc = A(0);
+#pragma unroll
+            for (int k = 0; k < W; ++k) acc += wk[k][e] * dp[m + W - 1 - k][e];
+            r[e] = acc;
+          }
+          store_vec<T, V>(gxb + static_cast<size_t>(l0 + m) * gxp, r);
         }
-        store_vec<T, V>(gxb + static_cast<size_t>(l0 + m) * gxp, r);
       }
     }
   }
@@ -228,18 +258,18 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const
 #pragma unroll
   for (int e = 0; e < V; ++e) {
 #pragma unroll
-    for (int k = 0; k < W; ++k) red[threadIdx.y][threadIdx.x][e * (W + 1) + k] = gwk[k][e];
-    red[threadIdx.y][threadIdx.x][e * (W + 1) + W] = gbs[e];
+    for (int k = 0; k < W; ++k) red[ty][tx][e * (W + 1) + k] = gwk[k][e];
+    red[ty][tx][e * (W + 1) + W] = gbs[e];
   }
   __syncthreads();
-  if (threadIdx.y == 0 && live_c) {
+  if (ty == 0 && live_c) {
 #pragma unroll
     for (int e = 0; e < V; ++e) {
 #pragma unroll
       for (int k = 0; k <= W; ++k) {
         A sum = A(0);
 #pragma unroll
-        for (int ty = 0; ty < CONV_TY; ++ty) sum += red[ty][threadIdx.x][e * (W + 1) + k];
+        for (int t2 = 0; t2 < CONV_TY; ++t2) sum += red[t2][tx][e * (W + 1) + k];
         if (k < W) atomicAdd(gw + static_cast<size_t>(c0 + e) * W + k, sum);
         else if (gbias != nullptr) atomicAdd(gbias + c0 + e, sum);
       }
@@ -534,26 +564,37 @@ void embedding_reverse_impl(const void* ids, const void* gy, void* gtable, len_t
 }
 
 template <typename T, int V>
-void conv_dispatch(bool reverse, const T* x, size_t xp, const T* w, const T* bias, const T* gy, size_t gyp, T* out, size_t op,
-                   typename Acc<T>::type* gw, typename Acc<T>::type* gbias, len_t batch, len_t len, len_t channels, len_t width,
-                   cudaStream_t st) {
+void conv_forward_dispatch(const T* x, size_t xp, const T* w, const T* bias, T* y, size_t yp, len_t batch, len_t len, len_t channels,
+                           len_t width, cudaStream_t st) {
   const dim3 block(32, CONV_TY);
-  const size_t steps_per_cta = static_cast<size_t>(CONV_TY) * CONV_LT * (reverse ? CONV_NB : 1);
+  const size_t steps_per_cta = static_cast<size_t>(CONV_TY) * CONV_LT;
   const dim3 grid(static_cast<unsigned>((channels / V + 31) / 32), static_cast<unsigned>((len + steps_per_cta - 1) / steps_per_cta),
                   static_cast<unsigned>(batch));
   const int L = static_cast<int>(len), C = static_cast<int>(channels);
-#define MP_CONV_CASE(WW)                                                                                              \
-  case WW:                                                                                                            \
-    if (reverse) conv1d_silu_reverse_kernel<T, V, WW><<<grid, block, 0, st>>>(x, xp, w, bias, gy, gyp, out, op, gw, gbias, L, C); \
-    else conv1d_silu_kernel<T, V, WW><<<grid, block, 0, st>>>(x, xp, w, bias, out, op, L, C);                         \
-    break;
   switch (width) {
-    MP_CONV_CASE(2)
-    MP_CONV_CASE(3)
-    MP_CONV_CASE(4)
+    case 2: conv1d_silu_kernel<T, V, 2><<<grid, block, 0, st>>>(x, xp, w, bias, y, yp, L, C); break;
+    case 3: conv1d_silu_kernel<T, V, 3><<<grid, block, 0, st>>>(x, xp, w, bias, y, yp, L, C); break;
+    case 4: conv1d_silu_kernel<T, V, 4><<<grid, block, 0, st>>>(x, xp, w, bias, y, yp, L, C); break;
     default: MP_FATAL("causal_conv1d_silu: kernel width %llu is not supported (2, 3 or 4)", static_cast<unsigned long long>(width));
   }
-#undef MP_CONV_CASE
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T, int V>
+void conv_reverse_dispatch(const T* x, size_t xp, const T* w, const T* bias, const T* gy, size_t gyp, T* gx, size_t gxp,
+                           typename Acc<T>::type* gw, typename Acc<T>::type* gbias, len_t batch, len_t len, len_t channels, len_t width,
+                           cudaStream_t st) {
+  const dim3 block(32, CONV_TY);
+  const size_t steps_per_cta = static_cast<size_t>(CONV_TY) * CONV_LT * CONV_NB;
+  const dim3 grid(static_cast<unsigned>((channels / V + 31) / 32), static_cast<unsigned>((len + steps_per_cta - 1) / steps_per_cta),
+                  static_cast<unsigned>(batch));
+  const int L = static_cast<int>(len), C = static_cast<int>(channels);
+  switch (width) {
+    case 2: conv1d_silu_reverse_kernel<T, V, 2><<<grid, block, 0, st>>>(x, xp, w, bias, gy, gyp, gx, gxp, gw, gbias, L, C); break;
+    case 3: conv1d_silu_reverse_kernel<T, V, 3><<<grid, block, 0, st>>>(x, xp, w, bias, gy, gyp, gx, gxp, gw, gbias, L, C); break;
+    case 4: conv1d_silu_reverse_kernel<T, V, 4><<<grid, block, 0, st>>>(x, xp, w, bias, gy, gyp, gx, gxp, gw, gbias, L, C); break;
+    default: MP_FATAL("causal_conv1d_silu_reverse: kernel width %llu is not supported (2, 3 or 4)", static_cast<unsigned long long>(width));
+  }
   MP_LAUNCH_CHECK();
 }
 
@@ -563,10 +604,10 @@ void causal_conv1d_silu_impl(const void* x, len_t x_pitch, const void* w, const 
   if (batch == 0 || len == 0 || channels == 0) return;
   constexpr int PN = Pack<T>::N;
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(y, y_pitch, channels);
-  if (v) conv_dispatch<T, PN>(false, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias), nullptr, 0,
-                              static_cast<T*>(y), y_pitch, nullptr, nullptr, batch, len, channels, width, mp_stream(ctx));
-  else conv_dispatch<T, 1>(false, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias), nullptr, 0,
-                           static_cast<T*>(y), y_pitch, nullptr, nullptr, batch, len, channels, width, mp_stream(ctx));
+  if (v) conv_forward_dispatch<T, PN>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias), static_cast<T*>(y),
+                                      y_pitch, batch, len, channels, width, mp_stream(ctx));
+  else conv_forward_dispatch<T, 1>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias), static_cast<T*>(y),
+                                   y_pitch, batch, len, channels, width, mp_stream(ctx));
 }
 
 template <typename T>
@@ -576,14 +617,14 @@ void causal_conv1d_silu_reverse_impl(const void* x, len_t x_pitch, const void* w
   if (batch == 0 || len == 0 || channels == 0) return;
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
+  constexpr int RV = PN > 4 ? 4 : PN;   // at most 4 channels per thread (register footprint)
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(gy, gy_pitch, channels) && vec_ok<T>(gx, gx_pitch, channels);
-  constexpr int RV = PN > 4 ? 4 : PN;   // reverse: at most 4 channels per thread (register footprint)
-  if (v) conv_dispatch<T, RV>(true, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
-                              static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw), static_cast<A*>(gbias),
-                              batch, len, channels, width, mp_stream(ctx));
-  else conv_dispatch<T, 1>(true, static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
-                           static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw), static_cast<A*>(gbias),
-                           batch, len, channels, width, mp_stream(ctx));
+  if (v) conv_reverse_dispatch<T, RV>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
+                                      static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw),
+                                      static_cast<A*>(gbias), batch, len, channels, width, mp_stream(ctx));
+  else conv_reverse_dispatch<T, 1>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
+                                   static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw),
+                                   static_cast<A*>(gbias), batch, len, channels, width, mp_stream(ctx));
 }
 
 template <typename T>
