@@ -84,6 +84,22 @@ __global__ void __launch_bounds__(256) embedding_reverse_kernel(const int* __res
   }
 }
 
+// The V x W taps (and V biases) of a thread's channels are contiguous in memory: fetch them with the
+// widest aligned vector loads (element-wise loads at a 2 * V * W byte lane stride cost one sector each).
+template <typename T, int N>
+__device__ __forceinline__ void load_contiguous(const T* p, typename Acc<T>::type* out) {
+  constexpr int MAXV = 16 / sizeof(T);
+  constexpr int LOW = N & (-N);                     // largest power of two dividing N
+  constexpr int CH = LOW < MAXV ? LOW : MAXV;
+  if ((reinterpret_cast<uintptr_t>(p) & (CH * sizeof(T) - 1)) == 0) {
+#pragma unroll
+    for (int i = 0; i < N; i += CH) load_vec<T, CH>(p + i, out + i);
+  } else {
+#pragma unroll
+    for (int i = 0; i < N; ++i) out[i] = mp_up(p[i]);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // depthwise causal convolution + SiLU over [batch, len, channels] (pitched rows)
 //   pre[b,l,c] = bias[c] + sum_k w[c,k] x[b, l - W + 1 + k, c]   (x = 0 before the sequence)
@@ -117,12 +133,14 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_kernel(const T* __re
       for (int e = 0; e < V; ++e) xw[j][e] = A(0);
     }
   }
-  A wk[W][V], bs[V];
+  A wk[W][V], bs[V], wflat[V * W];
+  load_contiguous<T, V * W>(w + static_cast<size_t>(c0) * W, wflat);
+  if (bias != nullptr) load_contiguous<T, V>(bias + c0, bs);
 #pragma unroll
   for (int e = 0; e < V; ++e) {
-    bs[e] = bias != nullptr ? mp_up(bias[c0 + e]) : A(0);
+    if (bias == nullptr) bs[e] = A(0);
 #pragma unroll
-    for (int k = 0; k < W; ++k) wk[k][e] = mp_up(w[static_cast<size_t>(c0 + e) * W + k]);
+    for (int k = 0; k < W; ++k) wk[k][e] = wflat[e * W + k];
   }
 #pragma unroll
   for (int j = 0; j < CONV_LT; ++j) {
@@ -161,16 +179,20 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const
   const int c0 = (blockIdx.x * 32 + tx) * V;
   const bool live_c = c0 < C;
   const bool last_lane = ty == CONV_TY - 1;
-  A gwk[W][V], gbs[V], wk[W][V], bs[V];
+  A gwk[W][V], gbs[V], wk[W][V], bs[V], wflat[V * W];
+#pragma unroll
+  for (int i = 0; i < V * W; ++i) wflat[i] = A(0);
+#pragma unroll
+  for (int e = 0; e < V; ++e) bs[e] = A(0);
+  if (live_c) {
+    load_contiguous<T, V * W>(w + static_cast<size_t>(c0) * W, wflat);
+    if (bias != nullptr) load_contiguous<T, V>(bias + c0, bs);
+  }
 #pragma unroll
   for (int e = 0; e < V; ++e) {
     gbs[e] = A(0);
-    bs[e] = (live_c && bias != nullptr) ? mp_up(bias[c0 + e]) : A(0);
 #pragma unroll
-    for (int k = 0; k < W; ++k) {
-      gwk[k][e] = A(0);
-      wk[k][e] = live_c ? mp_up(w[static_cast<size_t>(c0 + e) * W + k]) : A(0);
-    }
+    for (int k = 0; k < W; ++k) { gwk[k][e] = A(0); wk[k][e] = wflat[e * W + k]; }
   }
   const size_t b = blockIdx.z;
   const T* xb = x + b * L * xp + c0;
@@ -617,7 +639,7 @@ void causal_conv1d_silu_reverse_impl(const void* x, len_t x_pitch, const void* w
   if (batch == 0 || len == 0 || channels == 0) return;
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
-  constexpr int RV = PN > 4 ? 4 : PN;   // at most 4 channels per thread (register footprint)
+  constexpr int RV = PN > 4 ? 2 : PN;   // at most 4 channels per thread (register footprint)
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(gy, gy_pitch, channels) && vec_ok<T>(gx, gx_pitch, channels);
   if (v) conv_reverse_dispatch<T, RV>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
                                       static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw),
