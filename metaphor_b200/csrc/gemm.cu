@@ -119,6 +119,8 @@ struct GemmArgs {
   int a_mn, b_mn;     // operand major-ness: 0 = K contiguous, 1 = M resp. N contiguous
   int stages;
   int split;          // r32 only: 1 = error-compensated hi/lo split (3 MMAs per k-slice)
+  int ksplit;         // > 1: the K range of every tile is cut into ksplit work units whose raw fp32
+  float* partial;     //      accumulators go to partial[unit_split][M][N]; a fold kernel finishes C
   uint32_t* status;
 };
 
@@ -167,6 +169,9 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
   const int num_kb = (g.K + BK - 1) / BK;
   const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
+  // work unit u = (tile u % num_tiles, K split u / num_tiles) covering k-blocks [kb0, kb1)
+  const int num_units = num_tiles * g.ksplit;
+  const int kb_per = (num_kb + g.ksplit - 1) / g.ksplit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -193,9 +198,11 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
       int s = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+        const int tile = unit % num_tiles, sp = unit / num_tiles;
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) { ok = false; break; }
           unsigned char* sa = smem + static_cast<size_t>(s) * stage_sz;
           unsigned char* sb = sa + A_BYTES;
@@ -235,14 +242,16 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local) {
+      for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++local) {
         const int buf = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1);
         // the epilogue must have drained this accumulator (passes at once on its first use)
         if (!mbar_wait_abortable(acc_empty + buf, (use & 1u) ^ 1u, g.status, abort)) { ok = false; break; }
         tcgen05_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int sp = unit / num_tiles;
+        const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           uint64_t* wait_on = g.split ? (ready + s) : (full + s);
           if (!mbar_wait_abortable(wait_on, phase, g.status, abort)) { ok = false; break; }
           tcgen05_fence_after_sync();
@@ -253,7 +262,7 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
           for (int ks = 0; ks < KSLICES; ++ks) {
             const uint64_t ad = umma_smem_desc(sa + ks * a_kstep, a_lbo, a_sbo, a_lay);
             const uint64_t bd = umma_smem_desc(sb + ks * b_kstep, b_lbo, b_sbo, b_lay);
-            umma<G::TF32>(tmem_acc, ad, bd, idesc, (kb | ks) != 0 ? 1u : 0u);
+            umma<G::TF32>(tmem_acc, ad, bd, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
             if (g.split) {
               const uint64_t adl = umma_smem_desc(sa_lo + ks * a_kstep, a_lbo, a_sbo, a_lay);
               const uint64_t bdl = umma_smem_desc(sb_lo + ks * b_kstep, b_lbo, b_sbo, b_lay);
@@ -276,8 +285,10 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
     int s = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < num_kb; ++kb) {
+    for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+      const int sp = unit / num_tiles;
+      const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+      for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_abortable(full + s, phase, g.status, abort)) { ok = false; break; }
         unsigned char* hi = smem + static_cast<size_t>(s) * stage_sz;
         unsigned char* lo = hi + A_BYTES + B_BYTES;
@@ -303,10 +314,11 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
     const int half = (warp - 2) >> 2;             // which half of the tile's columns
     const T* bias = static_cast<const T*>(g.bias);
     const bool vec_ok = (static_cast<size_t>(g.N) * sizeof(T)) % 16 == 0 && mp_aligned16(g.c);
-    const bool use_tma = vec_ok && g.beta == 0.0f;   // overwrite: stage 32x32 blocks and let TMA write them
+    const bool use_tma = vec_ok && g.beta == 0.0f && g.ksplit == 1;   // overwrite: stage 32x32 blocks and let TMA write them
     unsigned char* stage = epi_stage + (warp - 2) * EPI_TILE_BYTES;
     int local = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++local) {
+    for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++local) {
+      const int tile = unit % num_tiles, sp = unit / num_tiles;
       const int buf = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
@@ -324,6 +336,18 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
         uint32_t v[32];
         tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
         tmem_ld_wait();
+        if (g.ksplit > 1) {   // raw partial sums; alpha, bias and beta are applied by the fold
+          if (row < g.M) {
+            float* prow = g.partial + (static_cast<size_t>(sp) * g.M + row) * g.N + col0;
+            if ((g.N & 3) == 0 && col0 + 32 <= g.N) {
+#pragma unroll
+              for (int p = 0; p < 8; ++p) *reinterpret_cast<uint4*>(prow + p * 4) = make_uint4(v[p * 4], v[p * 4 + 1], v[p * 4 + 2], v[p * 4 + 3]);
+            } else {
+              for (int j = 0; j < 32 && col0 + j < g.N; ++j) prow[j] = __uint_as_float(v[j]);
+            }
+          }
+          continue;
+        }
         float r[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[j]);
@@ -380,6 +404,32 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
   tcgen05_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, ACC_BUFS * BN);
+}
+
+// C = alpha * sum_s partial[s] + bias + beta * C  (finishes a split-K contraction)
+template <typename T>
+__global__ void __launch_bounds__(256) gemm_fold_kernel(const float* __restrict__ partial, int ksplit, size_t mn, int N, float alpha,
+                                                        const T* __restrict__ bias, float beta, T* __restrict__ c) {
+  const size_t i0 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 4;
+  if (i0 >= mn) return;
+  const bool vec = (mn & 3) == 0;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const int cnt = vec ? 4 : static_cast<int>(mn - i0 < 4 ? mn - i0 : 4);
+  for (int sidx = 0; sidx < ksplit; ++sidx) {
+    const float* p = partial + sidx * mn + i0;
+    if (vec) {
+      const float4 v = *reinterpret_cast<const float4*>(p);
+      acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
+    } else {
+      for (int e = 0; e < cnt; ++e) acc[e] += p[e];
+    }
+  }
+  for (int e = 0; e < cnt; ++e) {
+    float o = alpha * acc[e];
+    if (bias != nullptr) o += mp_up(bias[(i0 + e) % N]);
+    if (beta != 0.0f) o += beta * mp_up(c[i0 + e]);
+    c[i0 + e] = mp_down<T>(o);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -448,10 +498,17 @@ void launch_tc(const T* a, const T* b, const GemmArgs& args, int sm_count, cudaS
                       8 * 32 * 32 * sizeof(T) /*epilogue staging*/;
   MP_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
-  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM);
+  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * args.ksplit;
   const int grid = tiles < sm_count ? tiles : sm_count;   // persistent: one CTA per SM
   gemm_tcgen05_kernel<T, BN><<<grid, args.split ? GEMM_MAX_THREADS : GEMM_THREADS, smem, st>>>(ta, tb, tc, args);
   MP_LAUNCH_CHECK();
+  if (args.ksplit > 1) {
+    const size_t mn = static_cast<size_t>(M) * N;
+    gemm_fold_kernel<T><<<static_cast<unsigned>((mn / 4 + 256) / 256), 256, 0, st>>>(args.partial, args.ksplit, mn, N, args.alpha,
+                                                                                  static_cast<const T*>(args.bias), args.beta,
+                                                                                  static_cast<T*>(args.c));
+    MP_LAUNCH_CHECK();
+  }
 }
 
 bool env_flag(const char* name) {
@@ -466,6 +523,42 @@ int pick_bn(int M, int N, int sms) {
   if (N > 128 && tiles_m * ((N + 255) / 256) >= sms) return 256;
   if (N > 64 && tiles_m * ((N + 127) / 128) >= sms / 2) return 128;
   return N > 64 && tiles_m * ((N + 127) / 128) >= 4 ? 128 : 64;
+}
+
+// Split-K: contractions with few output tiles and a long K (weight gradients: K = tokens) leave SMs
+// idle or run a mostly empty last wave.  Cost model in k-block steps of one CTA:
+//   waves(tiles * ks / SMs) * (k-blocks per unit + fixed cost per unit) * step time(BN)  [+ fold traffic]
+// The unsplit choice of pick_bn stays unless a split is predicted to be at least 15 % faster.
+void pick_split_k(GemmArgs& args, size_t elem, int sms, size_t workspace_bytes, int* bn_io) {
+  const int bk = static_cast<int>(128 / elem);
+  const long num_kb = (args.K + bk - 1) / bk;
+  if (num_kb < 32) return;
+  const double mn_bytes = static_cast<double>(args.M) * args.N * 4.0;
+  auto cost = [&](int bn, int ks) {
+    const long tiles = static_cast<long>((args.M + BM - 1) / BM) * ((args.N + bn - 1) / bn);
+    const long waves = (tiles * ks + sms - 1) / sms;
+    // one k-block step of a CTA at ~1000 TFLOP/s over all SMs (r32: half the rate, three MMAs per slice), in microseconds
+    const double step_us = 2.0 * BM * bn * bk / (1000.0e6 / sms) * (args.split ? 3.0 : 1.0) * (elem == 4 ? 2.0 : 1.0);
+    double t = waves * ((num_kb + ks - 1) / ks + 8.0) * step_us;
+    if (ks > 1) t += 2.0 * ks * mn_bytes / 6.0e6 + 3.0;   // partial write + read at ~6 TB/s, one more launch
+    return t;
+  };
+  const double base = cost(*bn_io, 1);
+  double best = base;
+  int best_bn = *bn_io, best_ks = 1;
+  const int bns[2] = {128, 256};
+  for (int bi = 0; bi < 2; ++bi) {
+    const int bn = bns[bi];
+    if (bn == 256 && args.N <= 128) continue;
+    for (int ks = 2; ks <= 16; ++ks) {
+      if (static_cast<double>(ks) * mn_bytes > static_cast<double>(workspace_bytes)) break;
+      if (num_kb / ks < 8) break;
+      if ((ks - 1) * ((num_kb + ks - 1) / ks) >= num_kb) continue;   // the last unit would be empty
+      const double t = cost(bn, ks);
+      if (t < best) { best = t; best_bn = bn; best_ks = ks; }
+    }
+  }
+  if (best_ks > 1 && best < 0.85 * base) { args.ksplit = best_ks; *bn_io = best_bn; }
 }
 
 template <typename T>
@@ -506,7 +599,10 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
     args.b_mn = b_mn;
     args.split = (std::is_same<T, float>::value && !env_flag("MP_GEMM_TF32X1")) ? 1 : 0;
     args.status = state->status_dev;
-    const int bn = pick_bn(args.M, args.N, state->sm_count);
+    int bn = pick_bn(args.M, args.N, state->sm_count);
+    args.ksplit = 1;
+    args.partial = static_cast<float*>(state->workspace);
+    if (!env_flag("MP_GEMM_NO_SPLITK")) pick_split_k(args, sizeof(T), state->sm_count, state->workspace_bytes, &bn);
     const int budget = (200 - 8 * static_cast<int>(sizeof(T))) * 1024;   // ring; the rest is epilogue staging
     auto stages_for = [&](int per_stage) {   // the ring runs across tiles, so depth is bounded by memory only
       int s = budget / per_stage;
