@@ -97,6 +97,10 @@ constexpr int GEMM_MAX_THREADS = 448; // + warps 10-13: operand split (r32)
 constexpr int EPI_THREADS = 256;      // two epilogue warps per TMEM lane quarter, each takes half of the columns
 constexpr int MAX_STAGES = 8;
 
+// Staging blocks per epilogue warp.  r16: one per 32-column block of the warp's half tile (4 at BN = 256), so
+// a tile's TMA stores are issued back to back and the staging is only waited for at the next tile.
+template <typename T> struct EpiBufs { static constexpr int value = sizeof(T) == 2 ? 4 : 1; };
+
 template <typename T> struct GemmT;
 template <> struct GemmT<__half> {
   static constexpr int BK = 64;       // elements per 128-byte row
@@ -150,7 +154,11 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
   constexpr int A_BYTES = BM * SWIZZLE_BYTES, B_BYTES = BN * SWIZZLE_BYTES;
   constexpr int KSLICES = BK / G::UMMA_K;  // 4
   constexpr int ACC_BUFS = 2;
-  constexpr int EPI_TILE_BYTES = 32 * 32 * sizeof(T);   // per-warp staging block for the TMA store
+  constexpr int EPI_TILE_BYTES = 32 * 32 * sizeof(T);   // one 32 x 32 staging block for the TMA store
+  constexpr int EPI_BUFS = EpiBufs<T>::value;           // staging blocks per warp: no wait between the blocks of a tile
+  // r16, BN >= 128: two 32-column blocks share one [32 rows][64 columns] staging box in the 128-byte swizzle,
+  // written out by one TMA store with full 128-byte rows (64-byte rows halve the store engine's throughput)
+  constexpr bool WIDE_STORE = sizeof(T) == 2 && BN >= 128;
   extern __shared__ unsigned char gemm_smem_raw[];
   // 1024-byte alignment: swizzle atoms are 8 rows x 128 bytes
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -163,7 +171,7 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
   uint64_t* acc_empty = acc_full + ACC_BUFS;  // [2] accumulator drained by the epilogue
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  unsigned char* epi_stage = smem + static_cast<size_t>(stages) * stage_sz + 256;   // 8 warps x EPI_TILE_BYTES
+  unsigned char* epi_stage = smem + static_cast<size_t>(stages) * stage_sz + 1024;   // 8 warps x EPI_BUFS x EPI_TILE_BYTES, 1024-aligned
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (g.K + BK - 1) / BK;
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
     const T* bias = static_cast<const T*>(g.bias);
     const bool vec_ok = (static_cast<size_t>(g.N) * sizeof(T)) % 16 == 0 && mp_aligned16(g.c);
     const bool use_tma = vec_ok && g.beta == 0.0f && g.ksplit == 1;   // overwrite: stage 32x32 blocks and let TMA write them
-    unsigned char* stage = epi_stage + (warp - 2) * EPI_TILE_BYTES;
+    unsigned char* stage_base = epi_stage + (warp - 2) * (EPI_BUFS * EPI_TILE_BYTES);
     int local = 0;
     for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++local) {
       const int tile = unit % num_tiles, sp = unit / num_tiles;
@@ -329,10 +337,12 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
       const uint32_t tmem_acc = tmem_base + buf * BN;
       const int row = m0 + quarter * 32 + lane;
       T* crow = static_cast<T*>(g.c) + static_cast<size_t>(row) * g.N;
+      int blk = 0;
 #pragma unroll 1
-      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32) {
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32, ++blk) {
         const int col0 = n0 + c0;
         if (col0 >= g.N) break;   // uniform across the warp
+        unsigned char* stage = stage_base + (blk % EPI_BUFS) * EPI_TILE_BYTES;
         uint32_t v[32];
         tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
         tmem_ld_wait();
@@ -358,7 +368,28 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
         }
         if (use_tma) {
           constexpr int PN = Pack<T>::N;
-          if (lane == 0) bulk_wait_read<0>();   // the previous block's store has finished reading the staging buffer
+          if constexpr (WIDE_STORE) {
+            if (blk == 0) {   // the previous tile's stores have finished reading the staging boxes
+              if (lane == 0) bulk_wait_read<0>();
+              __syncwarp();
+            }
+            const int in_box = blk & 1;
+            unsigned char* box = stage_base + (blk >> 1) * (2 * EPI_TILE_BYTES);
+#pragma unroll
+            for (int p = 0; p < 4; ++p)   // 16-byte chunk (4 in_box + p) of this lane's 128-byte row, XOR-swizzled
+              *reinterpret_cast<Pack<T>*>(box + lane * 128 + (((4 * in_box + p) ^ (lane & 7)) << 4)) = pack<T>(r + p * PN);
+            if (in_box == 1 || col0 + 32 >= g.N) {   // box complete (columns past N are clipped by the store)
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_2d(&tmap_c, box, col0 - 32 * in_box, m0 + quarter * 32);
+                bulk_commit();
+              }
+            }
+            continue;
+          }
+          // the store that last used this staging block has finished reading it
+          if (lane == 0) { if (EPI_BUFS == 1 || blk < EPI_BUFS) { if (EPI_BUFS == 1 || blk == 0) bulk_wait_read<0>(); } else bulk_wait_read<EPI_BUFS - 1>(); }
           __syncwarp();
           T* srow = reinterpret_cast<T*>(stage) + lane * 32;
 #pragma unroll
@@ -469,17 +500,19 @@ CUtensorMap make_map(const void* base, size_t rows, size_t cols, uint32_t box_co
   return map;
 }
 
-// Row-major [rows, cols] output, box {32 cols, 32 rows}, unswizzled.
+// Row-major [rows, cols] output, box {32 cols, 32 rows} unswizzled, or (wide) {64 cols, 32 rows} of r16 in the
+// 128-byte swizzle.
 template <typename T>
-CUtensorMap make_store_map(void* base, size_t rows, size_t cols) {
+CUtensorMap make_store_map(void* base, size_t rows, size_t cols, bool wide = false) {
   CUtensorMap map;
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {cols * sizeof(T)};
-  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t box[2] = {wide ? 64u : 32u, 32};
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   MP_CU_CHECK(encode_tiled()(&map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+                             wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
   return map;
 }
 
@@ -493,9 +526,9 @@ void launch_tc(const T* a, const T* b, const GemmArgs& args, int sm_count, cudaS
   const CUtensorMap tb = args.b_mn ? make_map<T>(b, K, N, G::BK, G::BK, G::TF32) : make_map<T>(b, N, K, G::BK, BN);
   // C as a TMA store target: 32 x 32 blocks, no swizzle (only used when the row pitch is a multiple of 16 bytes)
   CUtensorMap tc = ta;
-  if ((static_cast<size_t>(N) * sizeof(T)) % 16 == 0 && mp_aligned16(args.c)) tc = make_store_map<T>(args.c, M, N);
-  const size_t smem = static_cast<size_t>(args.stages) * stage_bytes<BN>(args.split != 0) + 1024 /*align*/ + 256 /*barriers*/ +
-                      8 * 32 * 32 * sizeof(T) /*epilogue staging*/;
+  if ((static_cast<size_t>(N) * sizeof(T)) % 16 == 0 && mp_aligned16(args.c)) tc = make_store_map<T>(args.c, M, N, sizeof(T) == 2 && BN >= 128);
+  const size_t smem = static_cast<size_t>(args.stages) * stage_bytes<BN>(args.split != 0) + 1024 /*align*/ + 1024 /*barriers*/ +
+                      8 * EpiBufs<T>::value * 32 * 32 * sizeof(T) /*epilogue staging*/;
   MP_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
   const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * args.ksplit;
@@ -603,7 +636,8 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
     args.ksplit = 1;
     args.partial = static_cast<float*>(state->workspace);
     if (!env_flag("MP_GEMM_NO_SPLITK")) pick_split_k(args, sizeof(T), state->sm_count, state->workspace_bytes, &bn);
-    const int budget = (200 - 8 * static_cast<int>(sizeof(T))) * 1024;   // ring; the rest is epilogue staging
+    // shared memory of the ring: 227 KB per CTA minus alignment slack, barriers and the epilogue staging (r16: 64 KB, r32: 32 KB)
+    const int budget = (sizeof(T) == 2 ? 159 : 168) * 1024;
     auto stages_for = [&](int per_stage) {   // the ring runs across tiles, so depth is bounded by memory only
       int s = budget / per_stage;
       if (s > MAX_STAGES) s = MAX_STAGES;
