@@ -437,6 +437,227 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
   if (warp == 1) tmem_dealloc(tmem_base, ACC_BUFS * BN);
 }
 
+
+// ---------------------------------------------------------------------------
+// CTA-pair kernel (r16): a cluster of two CTAs owns a 256 x 256 output tile.  Rank r loads its 128 rows of
+// A and columns [128 r, 128 r + 128) of B, so every CTA moves 32 KB per 64-deep k-block for a 128 x 256
+// accumulator instead of 48 KB: the single-CTA kernel is bound by the L2 -> shared-memory feed, not by the
+// tensor pipe (measured 1.25-1.7 k cycles per k-block against 0.5 k at the tensor peak).
+//   both ranks  warp 0: TMA producer; warps 2-9: epilogue of the rank's own 128 rows
+//   rank 0      warp 1: issues the pair MMAs, commits to its own barriers
+// Barriers live at the same offsets in both CTAs.  full[s]: rank 0 only, credited by both ranks' loads.
+// empty[s] / acc_full[b]: rank 0 gets the MMA commit, rank 1 a relayed arrival (rank 0's producer thread
+// resp. an epilogue thread forwards it once its own wait has passed).  acc_empty[b]: rank 0 only, one
+// arrival per epilogue warp of both ranks.  Every wait is bounded.
+// ---------------------------------------------------------------------------
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGE_BYTES = BM * SWIZZLE_BYTES + (PAIR_BN / 2) * SWIZZLE_BYTES;   // 32 KB
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                             const __grid_constant__ CUtensorMap tmap_c, const GemmArgs g) {
+  using T = __half;
+  using G = GemmT<T>;
+  constexpr int BK = G::BK, BN = PAIR_BN;
+  constexpr int A_BYTES = BM * SWIZZLE_BYTES, B_BYTES = (BN / 2) * SWIZZLE_BYTES;
+  constexpr int KSLICES = BK / G::UMMA_K;
+  constexpr int ACC_BUFS = 2;
+  constexpr int BOX_BYTES = 32 * 64 * sizeof(T);   // one [32 rows][64 columns] staging box
+  extern __shared__ unsigned char gemm_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
+  const int stages = g.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(stages) * PAIR_STAGE_BYTES);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* acc_full = empty + MAX_STAGES;
+  uint64_t* acc_empty = acc_full + ACC_BUFS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+  volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  unsigned char* epi_stage = smem + static_cast<size_t>(stages) * PAIR_STAGE_BYTES + 1024;   // 8 warps x 2 boxes
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_kb = (g.K + BK - 1) / BK;
+  const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM), tiles_n = (g.N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
+    for (int a = 0; a < ACC_BUFS; ++a) { mbar_init(acc_full + a, 1); mbar_init(acc_empty + a, 16); }
+    *abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_c);
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, ACC_BUFS * BN);
+  tcgen05_fence_before_sync();
+  cluster_sync_all();   // both CTAs' barriers and TMEM exist before anything crosses the pair
+  tcgen05_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (both ranks) ------------------
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 0;
+      long it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m0 = (tile % tiles_m) * 2 * BM + static_cast<int>(rank) * BM;
+        const int n0 = (tile / tiles_m) * BN + static_cast<int>(rank) * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) { ok = false; break; }
+          if (rank == 0) {
+            if (it >= stages) mbar_arrive_cluster(empty + s, 1);   // forward the stage release to rank 1
+            mbar_arrive_expect_tx(full + s, 2 * (A_BYTES + B_BYTES));
+          }
+          unsigned char* sa = smem + static_cast<size_t>(s) * PAIR_STAGE_BYTES;
+          unsigned char* sb = sa + A_BYTES;
+          const int k0 = kb * BK;
+          if (!g.a_mn) {
+            tma_load_2d_pair(sa, &tmap_a, k0, m0, full + s);
+          } else {
+#pragma unroll 1
+            for (int j = 0; j < BM / BK; ++j) tma_load_2d_pair(sa + j * (BK * SWIZZLE_BYTES), &tmap_a, m0 + j * BK, k0, full + s);
+          }
+          if (!g.b_mn) {
+            tma_load_2d_pair(sb, &tmap_b, k0, n0, full + s);
+          } else {
+#pragma unroll 1
+            for (int j = 0; j < (BN / 2) / BK; ++j) tma_load_2d_pair(sb + j * (BK * SWIZZLE_BYTES), &tmap_b, n0 + j * BK, k0, full + s);
+          }
+          if (++s == stages) { s = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer (rank 0) -------------------------
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_instr_desc(G::FMT, g.a_mn, g.b_mn, 2 * BM, BN);
+      const uint32_t a_lbo = g.a_mn ? BK * SWIZZLE_BYTES : 16, b_lbo = g.b_mn ? BK * SWIZZLE_BYTES : 16;
+      const uint32_t a_kstep = g.a_mn ? G::UMMA_K * SWIZZLE_BYTES : 32, b_kstep = g.b_mn ? G::UMMA_K * SWIZZLE_BYTES : 32;
+      int s = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+        const int buf = local & 1;
+        const uint32_t use = static_cast<uint32_t>(local >> 1);
+        if (!mbar_wait_abortable(acc_empty + buf, (use & 1u) ^ 1u, g.status, abort)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t tmem_acc = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_abortable(full + s, phase, g.status, abort)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+          const uint32_t sa = mp_smem_u32(smem + static_cast<size_t>(s) * PAIR_STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < KSLICES; ++ks) {
+            const uint64_t ad = umma_smem_desc(sa + ks * a_kstep, a_lbo, 1024);
+            const uint64_t bd = umma_smem_desc(sb + ks * b_kstep, b_lbo, 1024);
+            umma_pair_f16(tmem_acc, ad, bd, idesc, (kb | ks) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(empty + s);
+          if (++s == stages) { s = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit_pair(acc_full + buf);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue (both ranks) -----------------------
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const T* bias = static_cast<const T*>(g.bias);
+    const bool vec_ok = (static_cast<size_t>(g.N) * sizeof(T)) % 16 == 0 && mp_aligned16(g.c);
+    const bool use_tma = vec_ok && g.beta == 0.0f;
+    unsigned char* stage_base = epi_stage + (warp - 2) * (2 * BOX_BYTES);
+    int local = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+      const int buf = local & 1;
+      const uint32_t use = static_cast<uint32_t>(local >> 1);
+      const int m0 = (tile % tiles_m) * 2 * BM + static_cast<int>(rank) * BM, n0 = (tile / tiles_m) * BN;
+      const bool acc_ready = mbar_wait_abortable(acc_full + buf, use & 1u, g.status, abort);
+      __syncwarp();
+      if (!acc_ready) break;
+      if (rank == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(acc_full + buf, 1);   // forward to rank 1
+      tcgen05_fence_after_sync();
+      const uint32_t tmem_acc = tmem_base + buf * BN;
+      const int row = m0 + quarter * 32 + lane;
+      T* crow = static_cast<T*>(g.c) + static_cast<size_t>(row) * g.N;
+      int blk = 0;
+#pragma unroll 1
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32, ++blk) {
+        const int col0 = n0 + c0;
+        if (col0 >= g.N) break;
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        tmem_ld_wait();
+        float r[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[j]);
+        if (bias != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < g.N) r[j] += mp_up(bias[col0 + j]);
+        }
+        constexpr int PN = Pack<T>::N;
+        if (use_tma) {
+          if (blk == 0) {
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+          }
+          const int in_box = blk & 1;
+          unsigned char* box = stage_base + (blk >> 1) * BOX_BYTES;
+#pragma unroll
+          for (int p = 0; p < 4; ++p)
+            *reinterpret_cast<Pack<T>*>(box + lane * 128 + (((4 * in_box + p) ^ (lane & 7)) << 4)) = pack<T>(r + p * PN);
+          if (in_box == 1 || col0 + 32 >= g.N) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_c, box, col0 - 32 * in_box, m0 + quarter * 32);
+              bulk_commit();
+            }
+          }
+        } else if (row < g.M) {
+          if (vec_ok && col0 + 32 <= g.N) {
+            if (g.beta != 0.0f) {
+#pragma unroll
+              for (int p = 0; p < 32 / PN; ++p) {
+                float old[PN];
+                unpack<T>(ld_pack(crow + col0, p), old);
+#pragma unroll
+                for (int e = 0; e < PN; ++e) r[p * PN + e] += g.beta * old[e];
+              }
+            }
+#pragma unroll
+            for (int p = 0; p < 32 / PN; ++p) st_pack(crow + col0, p, pack<T>(r + p * PN));
+          } else {
+            for (int j = 0; j < 32 && col0 + j < g.N; ++j) {
+              float o = r[j];
+              if (g.beta != 0.0f) o += g.beta * mp_up(crow[col0 + j]);
+              crow[col0 + j] = mp_down<T>(o);
+            }
+          }
+        }
+      }
+      // hand the accumulator back to rank 0's MMA thread: one arrival per warp of either rank
+      tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(acc_empty + buf);
+        else mbar_arrive_cluster(acc_empty + buf, 0);
+      }
+    }
+    if (use_tma && lane == 0) bulk_wait_all<0>();
+  }
+  __syncwarp();         // the cluster barrier below is warp-aligned: lanes that skipped the role loops wait here
+  tcgen05_fence_before_sync();
+  cluster_sync_all();   // neither CTA frees TMEM or leaves while its partner may still read its memory
+  if (warp == 1) tmem_dealloc_pair(tmem_base, ACC_BUFS * BN);
+}
+
 // C = alpha * sum_s partial[s] + bias + beta * C  (finishes a split-K contraction)
 template <typename T>
 __global__ void __launch_bounds__(256) gemm_fold_kernel(const float* __restrict__ partial, int ksplit, size_t mn, int N, float alpha,
@@ -544,6 +765,23 @@ void launch_tc(const T* a, const T* b, const GemmArgs& args, int sm_count, cudaS
   }
 }
 
+void launch_pair(const __half* a, const __half* b, GemmArgs args, int sm_count, cudaStream_t st) {
+  using T = __half;
+  using G = GemmT<T>;
+  const int M = args.M, N = args.N, K = args.K;
+  const CUtensorMap ta = args.a_mn ? make_map<T>(a, K, M, G::BK, G::BK) : make_map<T>(a, M, K, G::BK, BM);
+  const CUtensorMap tb = args.b_mn ? make_map<T>(b, K, N, G::BK, G::BK) : make_map<T>(b, N, K, G::BK, PAIR_BN / 2);
+  CUtensorMap tc = ta;
+  if ((static_cast<size_t>(N) * sizeof(T)) % 16 == 0 && mp_aligned16(args.c)) tc = make_store_map<T>(args.c, M, N, true);
+  args.stages = 5;
+  const size_t smem = static_cast<size_t>(args.stages) * PAIR_STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers*/ + 8 * 2 * 32 * 64 * sizeof(T);
+  MP_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  const int tiles = ((N + PAIR_BN - 1) / PAIR_BN) * ((M + 2 * BM - 1) / (2 * BM));
+  const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
+  gemm_tcgen05_pair_kernel<<<2 * pairs, GEMM_THREADS, smem, st>>>(ta, tb, tc, args);
+  MP_LAUNCH_CHECK();
+}
+
 bool env_flag(const char* name) {
   const char* e = getenv(name);
   return e != nullptr && e[0] != '\0' && e[0] != '0';
@@ -643,6 +881,14 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
       if (s > MAX_STAGES) s = MAX_STAGES;
       return s < 2 ? 2 : s;
     };
+    if constexpr (std::is_same<T, __half>::value) {
+      // CTA pairs for wide problems with enough 256 x 256 tiles to fill the pairs
+      const long pair_tiles = static_cast<long>((args.M + 255) / 256) * ((args.N + 255) / 256);
+      if (args.ksplit == 1 && bn == 256 && pair_tiles >= state->sm_count / 2 && !env_flag("MP_GEMM_NO_PAIRS")) {
+        launch_pair(a, b, args, state->sm_count, st);
+        return;
+      }
+    }
     if (bn == 256) { args.stages = stages_for(stage_bytes<256>(args.split != 0)); launch_tc<T, 256>(a, b, args, state->sm_count, st); }
     else if (bn == 128) { args.stages = stages_for(stage_bytes<128>(args.split != 0)); launch_tc<T, 128>(a, b, args, state->sm_count, st); }
     else { args.stages = stages_for(stage_bytes<64>(args.split != 0)); launch_tc<T, 64>(a, b, args, state->sm_count, st); }
