@@ -585,60 +585,66 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       const uint32_t tmem_acc = tmem_base + buf * BN;
       const int row = m0 + quarter * 32 + lane;
       T* crow = static_cast<T*>(g.c) + static_cast<size_t>(row) * g.N;
-      int blk = 0;
+      // one staging box (64 columns) per iteration: both TMEM loads are in flight before the wait
+      int boxi = 0;
 #pragma unroll 1
-      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32, ++blk) {
+      for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 64, ++boxi) {
         const int col0 = n0 + c0;
         if (col0 >= g.N) break;
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+        uint32_t v[2][32];
+        tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v[0]);
+        tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0 + 32, v[1]);
         tmem_ld_wait();
-        float r[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[j]);
-        if (bias != nullptr) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < g.N) r[j] += mp_up(bias[col0 + j]);
-        }
         constexpr int PN = Pack<T>::N;
-        if (use_tma) {
-          if (blk == 0) {
-            if (lane == 0) bulk_wait_read<0>();
-            __syncwarp();
+        unsigned char* box = stage_base + boxi * BOX_BYTES;
+        if (use_tma && boxi == 0) {   // the previous tile's stores have finished reading the staging boxes
+          if (lane == 0) bulk_wait_read<0>();
+          __syncwarp();
+        }
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+          const int colb = col0 + 32 * hb;
+          if (colb >= g.N) break;
+          float r[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[hb][j]);
+          if (bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (colb + j < g.N) r[j] += mp_up(bias[colb + j]);
           }
-          const int in_box = blk & 1;
-          unsigned char* box = stage_base + (blk >> 1) * BOX_BYTES;
+          if (use_tma) {
 #pragma unroll
-          for (int p = 0; p < 4; ++p)
-            *reinterpret_cast<Pack<T>*>(box + lane * 128 + (((4 * in_box + p) ^ (lane & 7)) << 4)) = pack<T>(r + p * PN);
-          if (in_box == 1 || col0 + 32 >= g.N) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_2d(&tmap_c, box, col0 - 32 * in_box, m0 + quarter * 32);
-              bulk_commit();
-            }
-          }
-        } else if (row < g.M) {
-          if (vec_ok && col0 + 32 <= g.N) {
-            if (g.beta != 0.0f) {
+            for (int p = 0; p < 4; ++p)
+              *reinterpret_cast<Pack<T>*>(box + lane * 128 + (((4 * hb + p) ^ (lane & 7)) << 4)) = pack<T>(r + p * PN);
+          } else if (row < g.M) {
+            if (vec_ok && colb + 32 <= g.N) {
+              if (g.beta != 0.0f) {
 #pragma unroll
-              for (int p = 0; p < 32 / PN; ++p) {
-                float old[PN];
-                unpack<T>(ld_pack(crow + col0, p), old);
+                for (int p = 0; p < 32 / PN; ++p) {
+                  float old[PN];
+                  unpack<T>(ld_pack(crow + colb, p), old);
 #pragma unroll
-                for (int e = 0; e < PN; ++e) r[p * PN + e] += g.beta * old[e];
+                  for (int e = 0; e < PN; ++e) r[p * PN + e] += g.beta * old[e];
+                }
+              }
+#pragma unroll
+              for (int p = 0; p < 32 / PN; ++p) st_pack(crow + colb, p, pack<T>(r + p * PN));
+            } else {
+              for (int j = 0; j < 32 && colb + j < g.N; ++j) {
+                float o = r[j];
+                if (g.beta != 0.0f) o += g.beta * mp_up(crow[colb + j]);
+                crow[colb + j] = mp_down<T>(o);
               }
             }
-#pragma unroll
-            for (int p = 0; p < 32 / PN; ++p) st_pack(crow + col0, p, pack<T>(r + p * PN));
-          } else {
-            for (int j = 0; j < 32 && col0 + j < g.N; ++j) {
-              float o = r[j];
-              if (g.beta != 0.0f) o += g.beta * mp_up(crow[col0 + j]);
-              crow[col0 + j] = mp_down<T>(o);
-            }
+          }
+        }
+        if (use_tma) {   // columns past N are clipped by the store
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmap_c, box, col0, m0 + quarter * 32);
+            bulk_commit();
           }
         }
       }
