@@ -353,7 +353,9 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
 #pragma unroll
               for (int p = 0; p < 8; ++p) *reinterpret_cast<uint4*>(prow + p * 4) = make_uint4(v[p * 4], v[p * 4 + 1], v[p * 4 + 2], v[p * 4 + 3]);
             } else {
-              for (int j = 0; j < 32 && col0 + j < g.N; ++j) prow[j] = __uint_as_float(v[j]);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < g.N) prow[j] = __uint_as_float(v[j]);
             }
           }
           continue;
@@ -391,11 +393,13 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
           // the store that last used this staging block has finished reading it
           if (lane == 0) { if (EPI_BUFS == 1 || blk < EPI_BUFS) { if (EPI_BUFS == 1 || blk == 0) bulk_wait_read<0>(); } else bulk_wait_read<EPI_BUFS - 1>(); }
           __syncwarp();
-          T* srow = reinterpret_cast<T*>(stage) + lane * 32;
+          // r32: 128-byte rows in the 128-byte swizzle (conflict-free); r16 at BN = 64: linear 64-byte rows.
+          // Register indices stay compile-time constants (a lane-dependent slot order would push r[] to local memory).
+          unsigned char* srow = stage + lane * (32 * sizeof(T));
 #pragma unroll
           for (int p = 0; p < 32 / PN; ++p) {
-            const int pp = (p + lane) % (32 / PN);   // rotate the 16-byte slots across lanes (bank conflicts)
-            st_pack(srow, pp, pack<T>(r + pp * PN));
+            const int slot = sizeof(T) == 4 ? (p ^ (lane & 7)) : p;
+            *reinterpret_cast<Pack<T>*>(srow + slot * 16) = pack<T>(r + p * PN);
           }
           fence_proxy_async_smem();
           __syncwarp();
@@ -418,10 +422,13 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
 #pragma unroll
             for (int p = 0; p < 32 / PN; ++p) st_pack(crow + col0, p, pack<T>(r + p * PN));
           } else {
-            for (int j = 0; j < 32 && col0 + j < g.N; ++j) {
-              float o = r[j];
-              if (g.beta != 0.0f) o += g.beta * mp_up(crow[col0 + j]);
-              crow[col0 + j] = mp_down<T>(o);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < g.N) {
+                float o = r[j];
+                if (g.beta != 0.0f) o += g.beta * mp_up(crow[col0 + j]);
+                crow[col0 + j] = mp_down<T>(o);
+              }
             }
           }
         }
@@ -602,9 +609,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
           __syncwarp();
         }
 #pragma unroll
-        for (int hb = 0; hb < 2; ++hb) {
+        for (int hb = 0; hb < 2; ++hb) {   // (no early exit: the register arrays must stay statically indexed)
           const int colb = col0 + 32 * hb;
-          if (colb >= g.N) break;
+          if (colb < g.N) {
           float r[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[hb][j]);
@@ -631,12 +638,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 #pragma unroll
               for (int p = 0; p < 32 / PN; ++p) st_pack(crow + colb, p, pack<T>(r + p * PN));
             } else {
-              for (int j = 0; j < 32 && colb + j < g.N; ++j) {
-                float o = r[j];
-                if (g.beta != 0.0f) o += g.beta * mp_up(crow[colb + j]);
-                crow[colb + j] = mp_down<T>(o);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (colb + j < g.N) {
+                  float o = r[j];
+                  if (g.beta != 0.0f) o += g.beta * mp_up(crow[colb + j]);
+                  crow[colb + j] = mp_down<T>(o);
+                }
               }
             }
+          }
           }
         }
         if (use_tma) {   // columns past N are clipped by the store
@@ -735,10 +746,11 @@ CUtensorMap make_store_map(void* base, size_t rows, size_t cols, bool wide = fal
   const cuuint64_t dims[2] = {cols, rows};
   const cuuint64_t strides[1] = {cols * sizeof(T)};
   const cuuint32_t box[2] = {wide ? 64u : 32u, 32};
+  const bool swizzle = wide || sizeof(T) == 4;   // 128-byte rows: r16 wide boxes and every r32 box
   const cuuint32_t estr[2] = {1, 1};
   const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
   MP_CU_CHECK(encode_tiled()(&map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                             wide ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                             swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
   return map;
 }
