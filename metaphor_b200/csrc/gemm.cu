@@ -487,6 +487,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   const int num_kb = (g.K + BK - 1) / BK;
   const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM), tiles_n = (g.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
+  // work unit u = (tile u % num_tiles, K split u / num_tiles) covering k-blocks [kb0, kb1)
+  const int num_units = num_tiles * g.ksplit;
+  const int kb_per = (num_kb + g.ksplit - 1) / g.ksplit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
@@ -510,10 +513,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       uint32_t phase = 0;
       long it = 0;
       bool ok = true;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int unit = pair; unit < num_units && ok; unit += num_pairs) {
+        const int tile = unit % num_tiles, sp = unit / num_tiles;
         const int m0 = (tile % tiles_m) * 2 * BM + static_cast<int>(rank) * BM;
         const int n0 = (tile / tiles_m) * BN + static_cast<int>(rank) * (BN / 2);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) { ok = false; break; }
           if (rank == 0) {
             if (it >= stages) mbar_arrive_cluster(empty + s, 1);   // forward the stage release to rank 1
@@ -548,13 +553,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
-      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++local) {
+      for (int unit = pair; unit < num_units && ok; unit += num_pairs, ++local) {
         const int buf = local & 1;
         const uint32_t use = static_cast<uint32_t>(local >> 1);
         if (!mbar_wait_abortable(acc_empty + buf, (use & 1u) ^ 1u, g.status, abort)) { ok = false; break; }
         tcgen05_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int sp = unit / num_tiles;
+        const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_abortable(full + s, phase, g.status, abort)) { ok = false; break; }
           tcgen05_fence_after_sync();
           const uint32_t sa = mp_smem_u32(smem + static_cast<size_t>(s) * PAIR_STAGE_BYTES);
@@ -563,7 +570,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
           for (int ks = 0; ks < KSLICES; ++ks) {
             const uint64_t ad = umma_smem_desc(sa + ks * a_kstep, a_lbo, 1024);
             const uint64_t bd = umma_smem_desc(sb + ks * b_kstep, b_lbo, 1024);
-            umma_pair_f16(tmem_acc, ad, bd, idesc, (kb | ks) != 0 ? 1u : 0u);
+            umma_pair_f16(tmem_acc, ad, bd, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
           }
           umma_commit_pair(empty + s);
           if (++s == stages) { s = 0; phase ^= 1u; }
@@ -577,10 +584,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     const int half = (warp - 2) >> 2;
     const T* bias = static_cast<const T*>(g.bias);
     const bool vec_ok = (static_cast<size_t>(g.N) * sizeof(T)) % 16 == 0 && mp_aligned16(g.c);
-    const bool use_tma = vec_ok && g.beta == 0.0f;
+    const bool use_tma = vec_ok && g.beta == 0.0f && g.ksplit == 1;
     unsigned char* stage_base = epi_stage + (warp - 2) * (2 * BOX_BYTES);
     int local = 0;
-    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++local) {
+    for (int unit = pair; unit < num_units; unit += num_pairs, ++local) {
+      const int tile = unit % num_tiles, sp = unit / num_tiles;
       const int buf = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       const int m0 = (tile % tiles_m) * 2 * BM + static_cast<int>(rank) * BM, n0 = (tile / tiles_m) * BN;
@@ -602,6 +610,25 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v[0]);
         tmem_ld_32x32(tmem_acc + (static_cast<uint32_t>(quarter * 32) << 16) + c0 + 32, v[1]);
         tmem_ld_wait();
+        if (g.ksplit > 1) {   // raw partial sums; alpha, bias and beta are applied by the fold
+          if (row < g.M) {
+#pragma unroll
+            for (int hb = 0; hb < 2; ++hb) {
+              const int colb = col0 + 32 * hb;
+              float* prow = g.partial + (static_cast<size_t>(sp) * g.M + row) * g.N + colb;
+              if ((g.N & 3) == 0 && colb + 32 <= g.N) {
+#pragma unroll
+                for (int p = 0; p < 8; ++p)
+                  *reinterpret_cast<uint4*>(prow + p * 4) = make_uint4(v[hb][p * 4], v[hb][p * 4 + 1], v[hb][p * 4 + 2], v[hb][p * 4 + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (colb + j < g.N) prow[j] = __uint_as_float(v[hb][j]);
+              }
+            }
+          }
+          continue;
+        }
         constexpr int PN = Pack<T>::N;
         unsigned char* box = stage_base + boxi * BOX_BYTES;
         if (use_tma && boxi == 0) {   // the previous tile's stores have finished reading the staging boxes
@@ -794,10 +821,17 @@ void launch_pair(const __half* a, const __half* b, GemmArgs args, int sm_count, 
   args.stages = 5;
   const size_t smem = static_cast<size_t>(args.stages) * PAIR_STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers*/ + 8 * 2 * 32 * 64 * sizeof(T);
   MP_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  const int tiles = ((N + PAIR_BN - 1) / PAIR_BN) * ((M + 2 * BM - 1) / (2 * BM));
+  const int tiles = ((N + PAIR_BN - 1) / PAIR_BN) * ((M + 2 * BM - 1) / (2 * BM)) * args.ksplit;
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
   gemm_tcgen05_pair_kernel<<<2 * pairs, GEMM_THREADS, smem, st>>>(ta, tb, tc, args);
   MP_LAUNCH_CHECK();
+  if (args.ksplit > 1) {
+    const size_t mn = static_cast<size_t>(M) * N;
+    gemm_fold_kernel<T><<<static_cast<unsigned>((mn / 4 + 256) / 256), 256, 0, st>>>(args.partial, args.ksplit, mn, N, args.alpha,
+                                                                                  static_cast<const T*>(args.bias), args.beta,
+                                                                                  static_cast<T*>(args.c));
+    MP_LAUNCH_CHECK();
+  }
 }
 
 bool env_flag(const char* name) {
@@ -902,9 +936,29 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
     if constexpr (std::is_same<T, __half>::value) {
       // CTA pairs for wide problems with enough 256 x 256 tiles to fill the pairs
       const long pair_tiles = static_cast<long>((args.M + 255) / 256) * ((args.N + 255) / 256);
-      if (args.ksplit == 1 && bn == 256 && pair_tiles >= state->sm_count / 2 && !env_flag("MP_GEMM_NO_PAIRS")) {
-        launch_pair(a, b, args, state->sm_count, st);
-        return;
+      if (!env_flag("MP_GEMM_NO_PAIRS") && args.M >= 256 && args.N >= 256) {
+        if (args.ksplit == 1 && bn == 256 && pair_tiles >= state->sm_count / 2) {
+          launch_pair(a, b, args, state->sm_count, st);
+          return;
+        }
+        if (args.ksplit > 1) {
+          // long K, few tiles: 256 x 256 pair tiles with the K range cut so that the units fill the pairs about evenly
+          const long num_kb = (args.K + 63) / 64;
+          const int pairs = state->sm_count / 2;
+          int best = 0; double best_cost = 1e30;
+          for (int ks = 1; ks <= 16; ++ks) {
+            if (num_kb / ks < 8 || (ks - 1) * ((num_kb + ks - 1) / ks) >= num_kb) continue;
+            if (static_cast<double>(ks) * args.M * args.N * 4.0 > static_cast<double>(state->workspace_bytes)) break;
+            const long waves = (pair_tiles * ks + pairs - 1) / pairs;
+            const double cost = waves * ((num_kb + ks - 1) / ks + 10.0) + (ks > 1 ? 2.0 * ks * args.M * args.N * 4.0 / 6.0e6 / 0.5 : 0.0);
+            if (cost < best_cost) { best_cost = cost; best = ks; }
+          }
+          if (best >= 1) {
+            args.ksplit = best;
+            launch_pair(a, b, args, state->sm_count, st);
+            return;
+          }
+        }
       }
     }
     if (bn == 256) { args.stages = stages_for(stage_bytes<256>(args.split != 0)); launch_tc<T, 256>(a, b, args, state->sm_count, st); }

@@ -13,7 +13,8 @@ architecture (sm_100a here instead of config.json's sm_89), together with
 checkout; the substituted text exists only in a temporary directory that is
 deleted afterwards.  Nothing but the shared object is written into the repo.
 
-Usage: ``python oracle/build_ref.py [--reference /root/reference]``
+Usage: ``python oracle/build_ref.py [--reference <checkout>]`` (default: the directory named by the
+environment variable MP_REFERENCE_DIR, else a sibling checkout ``../reference``)
 """
 from __future__ import annotations
 
@@ -31,7 +32,10 @@ NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 CUDA_HOME = Path(NVCC).resolve().parent.parent
 
 
-def build(reference: Path = Path("/root/reference"), verbose: bool = True) -> Path | None:
+DEFAULT_REFERENCE = Path(os.environ.get("MP_REFERENCE_DIR", str(Path(__file__).resolve().parents[2] / "reference")))
+
+
+def build(reference: Path = DEFAULT_REFERENCE, verbose: bool = True) -> Path | None:
     src_cuda = reference / "src" / "cuda"
     if not src_cuda.is_dir():
         if verbose:
@@ -83,6 +87,6 @@ def build(reference: Path = Path("/root/reference"), verbose: bool = True) -> Pa
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=str(DEFAULT_REFERENCE))
     args = ap.parse_args()
     sys.exit(0 if build(Path(args.reference)) else 1)

@@ -17,7 +17,7 @@
  *   1. the hand-derivable values of src/examples/experimental.zig:19-69
  *      (tests/test_oracle.py), and
  *   2. outputs of the reference's own CUDA kernels, compiled unmodified from
- *      /root/reference by oracle/build_ref.py into oracle/_ref/ and run on the
+ *      the reference checkout by oracle/build_ref.py into oracle/_ref/ and run on the
  *      GPU (tests/test_reference_kernels.py; fixtures in tests/golden/).
  * For selu, softmax, RMSNorm, SSD, SGD and Adam the reference has neither
  * code nor tests: for those ops parity is unpinned by the reference, and the
