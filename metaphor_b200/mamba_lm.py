@@ -318,6 +318,41 @@ class MambaLM:
         o, shape = self.offsets[name]
         return (self.g32[o:o + math.prod(shape)].reshape(shape) / self.loss_scale).cpu().numpy()
 
+    # ------------------------------------------------------------------ checkpoint
+    def save(self, prefix: str):
+        """Raw-bytes checkpoint in leaf order, one file per tensor named "{prefix}_{idx}" (the naming of the
+        reference's tensor_file.zig:36-40): idx = position in `param_shapes()` for the r32 master weights, then
+        the two Adam moments in the same order, and "{prefix}_state" with the step count."""
+        import math
+        self.stream.sync()
+        n = len(self.offsets)
+        for k, buf in enumerate((self.w32, self.m, self.v)):
+            host = buf.cpu().numpy()
+            for idx, (name, (o, shape)) in enumerate(self.offsets.items()):
+                host[o:o + math.prod(shape)].tofile(f"{prefix}_{k * n + idx}")
+        with open(f"{prefix}_state", "w") as f:
+            f.write(f"{self.step_count}\n")
+
+    def load(self, prefix: str):
+        import math
+        import numpy as np
+        import torch
+        self.stream.sync()
+        n = len(self.offsets)
+        for k, buf in enumerate((self.w32, self.m, self.v)):
+            host = np.zeros(self.n_flat, dtype=np.float32)
+            for idx, (name, (o, shape)) in enumerate(self.offsets.items()):
+                cnt = math.prod(shape)
+                a = np.fromfile(f"{prefix}_{k * n + idx}", dtype=np.float32)
+                if a.size != cnt:
+                    raise ValueError(f"{prefix}_{k * n + idx}: expected {cnt} values for {name}, found {a.size}")
+                host[o:o + cnt] = a
+            buf.copy_(torch.from_numpy(host))
+        torch.cuda.synchronize()
+        with open(f"{prefix}_state") as f:
+            self.step_count = int(f.read().strip())
+        self._refresh_w16()
+
     def launches_per_step(self) -> int:
         n = self.cfg.n_layer
         return 1 + 13 * n + 2 + 2 + 5 + 19 * n + 2 + 2

@@ -56,3 +56,33 @@ def test_reduced_lm_step(mp, stream, orc):
     got = model.w32.cpu().numpy()
     assert np.max(np.abs(got - wref)) <= 1e-6
     assert np.array_equal(model.w16.cpu().numpy(), got.astype(np.float16))
+
+
+def test_checkpoint_resume(mp, stream, tmp_path):
+    """Two steps, save, one more step; a fresh model that loads the checkpoint reproduces that step: the same
+    loss bit for bit (the forward pass is deterministic), the same weights up to the summation order of the
+    atomically reduced parameter gradients."""
+    import torch
+    from metaphor_b200.mamba_lm import LMConfig, MambaLM
+    cfg = LMConfig(d_model=256, n_layer=1, vocab=512, chunk=128)
+    batch, seqlen = 1, 256
+    rng = np.random.default_rng(7)
+    ids = torch.from_numpy(rng.integers(0, cfg.vocab, size=batch * seqlen).astype(np.int32))
+    tgt = torch.from_numpy(rng.integers(0, cfg.vocab, size=batch * seqlen).astype(np.int32))
+    a = MambaLM(cfg, batch, seqlen, seed=3, stream=stream, loss_scale=128.0)
+    torch.cuda.current_stream().synchronize()
+    a.set_batch(ids, tgt)
+    for _ in range(2):
+        a.train_step()
+    prefix = str(tmp_path / "ckpt")
+    a.save(prefix)
+    a.train_step()
+    loss_a, w_a = a.loss(), a.w32.cpu().numpy().copy()
+    b = MambaLM(cfg, batch, seqlen, seed=99, stream=stream, loss_scale=128.0)   # different initial weights
+    torch.cuda.current_stream().synchronize()
+    b.load(prefix)
+    b.set_batch(ids, tgt)
+    b.train_step()
+    assert b.step_count == 3
+    assert b.loss() == loss_a
+    assert np.max(np.abs(b.w32.cpu().numpy() - w_a)) <= 1e-6
