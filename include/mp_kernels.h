@@ -192,6 +192,18 @@ MP_DECL3(neg_exp, const void* src, void* dst, len_t n, StreamContext stream)
 MP_EXTERN_C void launch_convert_r16_r32(const void* src, void* dst, double beta, len_t n, StreamContext stream);
 MP_EXTERN_C void launch_convert_r32_r16(const void* src, void* dst, len_t n, StreamContext stream);
 
+/* Rank-1 losses and the momentum step.  The reference calls kernels of these names (loss.zig:58-136,
+ * optimizer.zig:263-273) but contains no implementation; argument order follows those call sites.
+ *   mse: redux = mean (x-t)^2,                         grad = 2 (x-t)/n
+ *   bce: x = probabilities (sigmoid applied by the host first, loss.zig:117-119),
+ *        redux = -mean [t log p + (1-t) log(1-p)],     grad = (p-t)/n  (w.r.t. the logits)
+ * scratch: n/4096 + 2 accumulator-typed slots (r32 for r16/r32, r64 for r64); redux: one accumulator-typed
+ * value; grad or redux may be NULL. */
+MP_DECL3(mse_loss_i_i, const void* x, void* grad, const void* trg, void* scratch, void* redux, len_t n, StreamContext stream)
+MP_DECL3(bce_loss_i_i, const void* x, void* grad, const void* trg, void* scratch, void* redux, len_t n, StreamContext stream)
+/* m = alpha*m + clip(g, clip_lo, clip_hi);  w -= rate*m */
+MP_DECL3(momentum, void* w, const void* g, void* m, double rate, double alpha, double clip_lo, double clip_hi, len_t n, StreamContext stream)
+
 /* Status word values returned by mpGetStatus (mp_device_utils.h). */
 #define MP_STATUS_OK             0u
 #define MP_STATUS_WAIT_TIMEOUT   1u  /* a bounded mbarrier wait gave up    */

@@ -73,6 +73,9 @@ LAUNCHERS = {
     "head_scale_accumulate": [P, P, P, L, L, L, CTX],
     "cross_entropy": [P, P, D, P, P, L, L, CTX],
     "neg_exp": [P, P, L, CTX],
+    "mse_loss_i_i": [P, P, P, P, P, L, CTX],
+    "bce_loss_i_i": [P, P, P, P, P, L, CTX],
+    "momentum": [P, P, P, D, D, D, D, L, CTX],
 }
 
 # name -> (restype, argtypes)

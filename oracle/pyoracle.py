@@ -325,3 +325,19 @@ def cross_entropy(logits, targets, scale):
     g[np.arange(m), tg] -= 1.0
     g = np.where(valid[:, None], g * scale, 0.0)
     return loss, g
+
+
+def mse_loss(x, t):
+    d = x.astype(np.float64) - t.astype(np.float64)
+    return float(np.mean(d * d)), 2.0 * d / d.size
+
+
+def bce_loss(p, t):
+    p64, t64 = p.astype(np.float64), t.astype(np.float64)
+    pc = np.clip(p64, 1e-12, 1 - 1e-12)
+    return float(-np.mean(t64 * np.log(pc) + (1 - t64) * np.log(1 - pc))), (p64 - t64) / p64.size
+
+
+def momentum(w, g, m, rate, alpha, lo=-np.inf, hi=np.inf):
+    m2 = alpha * m.astype(np.float64) + np.clip(g.astype(np.float64), lo, hi)
+    return w.astype(np.float64) - rate * m2, m2
