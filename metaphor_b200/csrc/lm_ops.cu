@@ -11,7 +11,7 @@
 // inside the CTA and added with one atomic per CTA and element.  Parameter
 // gradients and per-head parameters are kept in the accumulator type (r32 for
 // r16 / r32 tensors, r64 for r64).
-#include "mp_common.cuh"
+#include "mp_async.cuh"
 
 namespace {
 
@@ -441,7 +441,7 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const T* logi
                                                                   typename Acc<T>::type* __restrict__ loss, T* glogits,
                                                                   size_t n) {
   using A = typename Acc<T>::type;
-  extern __shared__ __align__(16) unsigned char ce_smem[];
+  extern __shared__ __align__(128) unsigned char ce_smem[];
   __shared__ A red[CE_THREADS / 32];
   __shared__ A bc;
   T* srow = reinterpret_cast<T*>(ce_smem);
@@ -514,6 +514,107 @@ __global__ void __launch_bounds__(CE_THREADS) cross_entropy_kernel(const T* logi
       }
       *reinterpret_cast<VecT<T, V>*>(dst + i * V) = o;
     }
+  }
+}
+
+// Same computation with the row moved by bulk asynchronous copies: one thread asks for the whole row
+// (global -> shared, completion counted on an mbarrier), the CTA makes its passes over shared memory,
+// writes the gradient in place there and one thread sends it back (shared -> global).  A CTA then has
+// its full row in flight at once instead of what its threads' registers can hold, and two CTAs per SM
+// alternate between moving and computing.  Needs rows that are multiples of 16 bytes.
+constexpr uint32_t CE_BULK_CHUNK = 32768;
+
+template <typename T, int V>
+__global__ void __launch_bounds__(CE_THREADS) cross_entropy_bulk_kernel(const T* logits, const int* __restrict__ targets,
+                                                                       typename Acc<T>::type scale,
+                                                                       typename Acc<T>::type* __restrict__ loss, T* glogits,
+                                                                       size_t n, uint32_t* status) {
+  using A = typename Acc<T>::type;
+  extern __shared__ __align__(128) unsigned char ce_smem[];
+  __shared__ uint64_t bar;
+  __shared__ A red[CE_THREADS / 32];
+  __shared__ A bc;
+  T* srow = reinterpret_cast<T*>(ce_smem);
+  const size_t row = blockIdx.x;
+  const T* src = logits + row * n;
+  const uint32_t row_bytes = static_cast<uint32_t>(n * sizeof(T));
+  const size_t nv = n / V;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    mbar_arrive_expect_tx(&bar, row_bytes);
+    for (uint32_t off = 0; off < row_bytes; off += CE_BULK_CHUNK)
+      bulk_load_1d(ce_smem + off, reinterpret_cast<const unsigned char*>(src) + off,
+                   row_bytes - off < CE_BULK_CHUNK ? row_bytes - off : CE_BULK_CHUNK, &bar);
+  }
+  const long long tg = targets[row];
+  const bool valid = tg >= 0 && static_cast<size_t>(tg) < n;
+  if (!mbar_wait(&bar, 0, status)) return;   // bounded; every thread sees the same outcome
+  auto block_reduce = [&](A v, bool is_max) -> A {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const A other = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? (v > other ? v : other) : v + other;
+    }
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+      A t = lane < CE_THREADS / 32 ? red[lane] : (is_max ? A(-INFINITY) : A(0));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const A other = __shfl_xor_sync(0xffffffffu, t, o);
+        t = is_max ? (t > other ? t : other) : t + other;
+      }
+      if (lane == 0) bc = t;
+    }
+    __syncthreads();
+    const A r = bc;
+    __syncthreads();
+    return r;
+  };
+  A mx = A(-INFINITY);
+  for (size_t i = threadIdx.x; i < nv; i += CE_THREADS) {
+    const VecT<T, V> x = *reinterpret_cast<const VecT<T, V>*>(srow + i * V);
+#pragma unroll
+    for (int e = 0; e < V; ++e) { const A f = mp_up(x.v[e]); mx = f > mx ? f : mx; }
+  }
+  mx = block_reduce(mx, true);
+  const A x_target = (threadIdx.x == 0 && valid) ? mp_up(srow[tg]) : A(0);   // read before the row is overwritten
+  __syncthreads();
+  A sum = A(0);
+  for (size_t i = threadIdx.x; i < nv; i += CE_THREADS) {
+    VecT<T, V> x = *reinterpret_cast<const VecT<T, V>*>(srow + i * V);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const A t = exp_a(mp_up(x.v[e]) - mx);
+      sum += t;
+      x.v[e] = mp_down<T>(t);
+    }
+    *reinterpret_cast<VecT<T, V>*>(srow + i * V) = x;
+  }
+  sum = block_reduce(sum, false);
+  if (threadIdx.x == 0 && loss != nullptr) loss[row] = valid ? log_a(sum) + mx - x_target : A(0);
+  if (glogits == nullptr) return;
+  const A inv = scale / sum;
+  for (size_t i = threadIdx.x; i < nv; i += CE_THREADS) {
+    VecT<T, V> x = *reinterpret_cast<const VecT<T, V>*>(srow + i * V);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      A gval = valid ? mp_up(x.v[e]) * inv : A(0);
+      if (valid && i * V + e == static_cast<size_t>(tg)) gval -= scale;
+      x.v[e] = mp_down<T>(gval);
+    }
+    *reinterpret_cast<VecT<T, V>*>(srow + i * V) = x;
+  }
+  fence_proxy_async_smem();   // generic-proxy writes of the gradient -> visible to the bulk store
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned char* dst = reinterpret_cast<unsigned char*>(glogits + row * n);
+    for (uint32_t off = 0; off < row_bytes; off += CE_BULK_CHUNK)
+      bulk_store_1d(dst + off, ce_smem + off, row_bytes - off < CE_BULK_CHUNK ? row_bytes - off : CE_BULK_CHUNK);
+    bulk_commit();
+    bulk_wait_all<0>();       // shared memory must outlive the copy
   }
 }
 
@@ -727,10 +828,17 @@ void head_scale_accumulate_impl(const void* D, const void* gy, void* gx, len_t r
 }
 
 template <typename T, int V>
-void ce_launch(const T* logits, const int* targets, double scale, typename Acc<T>::type* loss, T* glogits, len_t m, len_t n, cudaStream_t st) {
+void ce_launch(const T* logits, const int* targets, double scale, typename Acc<T>::type* loss, T* glogits, len_t m, len_t n, cudaStream_t st,
+               uint32_t* status) {
   using A = typename Acc<T>::type;
   const size_t row_bytes = n * sizeof(T);
-  if (row_bytes <= 200 * 1024) {
+  if (status != nullptr && row_bytes <= 100 * 1024 + 4096 && row_bytes % 16 == 0 && n % V == 0 && mp_aligned16(logits) &&
+      (glogits == nullptr || mp_aligned16(glogits)) && getenv("MP_CE_NO_BULK") == nullptr) {
+    // (two CTAs per SM need the row below ~110 KB)
+    MP_CUDA_CHECK(cudaFuncSetAttribute(cross_entropy_bulk_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+    cross_entropy_bulk_kernel<T, V><<<static_cast<unsigned>(m), CE_THREADS, (row_bytes + 127) & ~size_t(127), st>>>(
+        logits, targets, static_cast<A>(scale), loss, glogits, n, status);
+  } else if (row_bytes <= 200 * 1024) {
     MP_CUDA_CHECK(cudaFuncSetAttribute(cross_entropy_kernel<T, V, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     cross_entropy_kernel<T, V, true><<<static_cast<unsigned>(m), CE_THREADS, (row_bytes + 15) & ~size_t(15), st>>>(logits, targets, static_cast<A>(scale), loss,
                                                                                                                  glogits, n);
@@ -746,8 +854,10 @@ void cross_entropy_impl(const void* logits, const void* targets, double scale, v
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
   const bool v = n % PN == 0 && mp_aligned16(logits) && (glogits == nullptr || mp_aligned16(glogits));
-  if (v) ce_launch<T, PN>(static_cast<const T*>(logits), static_cast<const int*>(targets), scale, static_cast<A*>(loss), static_cast<T*>(glogits), m, n, mp_stream(ctx));
-  else ce_launch<T, 1>(static_cast<const T*>(logits), static_cast<const int*>(targets), scale, static_cast<A*>(loss), static_cast<T*>(glogits), m, n, mp_stream(ctx));
+  MpStreamState* state = mp_state_or_null(ctx);
+  uint32_t* status = state != nullptr ? state->status_dev : nullptr;   // bounded waits report here
+  if (v) ce_launch<T, PN>(static_cast<const T*>(logits), static_cast<const int*>(targets), scale, static_cast<A*>(loss), static_cast<T*>(glogits), m, n, mp_stream(ctx), status);
+  else ce_launch<T, 1>(static_cast<const T*>(logits), static_cast<const int*>(targets), scale, static_cast<A*>(loss), static_cast<T*>(glogits), m, n, mp_stream(ctx), status);
 }
 
 template <typename T>
