@@ -673,11 +673,22 @@ struct SsdDims { int B, L, H, P, N, G, Q, nc; };
 
 // CTAs that share the heads of one group when an output is summed over them (gB, gC): with one CTA per
 // group and tile only B * L / 128 * G CTAs would exist, each walking all the group's heads in sequence.
+// The split count (a divisor of the heads per group, at most 32) minimises
+//   waves of resident CTAs x (k-blocks per CTA + a fixed cost per CTA)
+// with three CTAs of these launches resident per SM (68 KB of shared memory each) on the 148 SMs of the part.
 int ssd_head_splits(const SsdDims& d) {
   const int hpg = d.H / d.G;
-  for (int sp = 4; sp > 1; --sp)
-    if (hpg % sp == 0) return sp;
-  return 1;
+  const long base = 2L * d.B * d.nc * d.G * (d.Q / 128) / 2 * 1;   // tiles of one split: B * nc * G * (Q / 128)
+  const long slots = 148L * 3;
+  int best = 1;
+  long best_cost = -1;
+  for (int sp = 1; sp <= hpg && sp <= 32; ++sp) {
+    if (hpg % sp != 0) continue;
+    const long waves = (base * sp + slots - 1) / slots;
+    const long cost = waves * (static_cast<long>(hpg / sp) * 5 + 2);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = sp; }
+  }
+  return best;
 }
 
 // Scratch layout (bytes, 256-aligned sections).
