@@ -30,6 +30,7 @@ StreamContext make_context(cudaStream_t stream, bool owns) {
   st->device = device;
   st->sm_count = mp_sm_count_current_device();
   st->owns_stream = owns;
+  st->aux_ready = false;
   st->workspace_bytes = workspace_bytes_from_env();
   MP_CUDA_CHECK(cudaMalloc(&st->workspace, st->workspace_bytes));
   MP_CUDA_CHECK(cudaMalloc(reinterpret_cast<void**>(&st->status_dev), 256));
@@ -123,6 +124,14 @@ extern "C" void mpDeinitStream(StreamContext ctx) {
   cudaStream_t stream = mp_stream(ctx);
   MP_CUDA_CHECK(cudaStreamSynchronize(stream));
   if (st != nullptr) {
+    if (st->aux_ready) {
+      for (int i = 0; i < 3; ++i) {
+        MP_CUDA_CHECK(cudaStreamSynchronize(st->aux_stream[i]));
+        MP_CUDA_CHECK(cudaStreamDestroy(st->aux_stream[i]));
+        MP_CUDA_CHECK(cudaEventDestroy(st->aux_join[i]));
+      }
+      MP_CUDA_CHECK(cudaEventDestroy(st->aux_fork));
+    }
     MP_CUDA_CHECK(cudaFree(st->workspace));
     MP_CUDA_CHECK(cudaFree(st->status_dev));
     MP_CUDA_CHECK(cudaFreeHost(st->status_host));

@@ -67,7 +67,23 @@ struct MpStreamState {
   size_t workspace_bytes;
   uint32_t* status_dev;     // one device word, zero when healthy
   uint32_t* status_host;    // pinned host landing slot for mpGetStatus
+  // Helper streams and events for launchers that run independent kernel chains side by side (forked from and
+  // joined back into `stream`, also under stream capture); created on first use, destroyed with the state.
+  cudaStream_t aux_stream[3];
+  cudaEvent_t aux_fork, aux_join[3];
+  bool aux_ready;
 };
+
+// Creates the helper streams / events of a state on first use.
+static inline void mp_aux_init(MpStreamState* st) {
+  if (st->aux_ready) return;
+  for (int i = 0; i < 3; ++i) {
+    MP_CUDA_CHECK(cudaStreamCreateWithFlags(&st->aux_stream[i], cudaStreamNonBlocking));
+    MP_CUDA_CHECK(cudaEventCreateWithFlags(&st->aux_join[i], cudaEventDisableTiming));
+  }
+  MP_CUDA_CHECK(cudaEventCreateWithFlags(&st->aux_fork, cudaEventDisableTiming));
+  st->aux_ready = true;
+}
 
 static inline cudaStream_t mp_stream(StreamContext ctx) {
   return static_cast<cudaStream_t>(ctx.cuda_stream.ptr);

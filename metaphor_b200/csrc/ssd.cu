@@ -694,6 +694,8 @@ int ssd_head_splits(const SsdDims& d) {
 // Scratch layout (bytes, 256-aligned sections).
 struct SsdScratch {
   float* cum; float* dtt; __half* scores; float* states; __half* hs; float* u; float* v; float* ga_part; float* parts;
+  // reverse: the four operator instances run side by side, each with its own scores / states / partials
+  __half* scores_op[4]; float* states_op[4]; __half* hs_op[4]; float* parts_op[4];
   size_t total;
 };
 SsdScratch ssd_carve(void* base, const SsdDims& d, bool reverse) {
@@ -703,15 +705,21 @@ SsdScratch ssd_carve(void* base, const SsdDims& d, bool reverse) {
   const size_t bhl = static_cast<size_t>(d.B) * d.H * d.L;
   s.cum = static_cast<float*>(take(bhl * 4));
   s.dtt = static_cast<float*>(take(bhl * 4));
-  const size_t score_units = reverse ? d.H : d.G;   // the reverse keeps per-head scores for gB / gC
-  s.scores = static_cast<__half*>(take(static_cast<size_t>(d.B) * d.nc * score_units * d.Q * d.Q * 2));
   const size_t st = static_cast<size_t>(d.B) * d.H * d.nc * 128 * 128;   // upper bound on dk*dv
-  s.states = static_cast<float*>(take(st * 4));
-  s.hs = static_cast<__half*>(take(st * 2));
+  const size_t group_scores = static_cast<size_t>(d.B) * d.nc * d.G * d.Q * d.Q * 2;
+  const size_t head_scores = static_cast<size_t>(d.B) * d.nc * d.H * d.Q * d.Q * 2;   // gB / gC keep per-head scores
+  const size_t parts_bytes = static_cast<size_t>(ssd_head_splits(d)) * d.B * d.L * d.G * d.N * 4;
+  for (int op = 0; op < (reverse ? 4 : 1); ++op) {
+    const bool per_head = reverse && op >= 2;   // operators 2, 3 = gC, gB
+    s.scores_op[op] = static_cast<__half*>(take(per_head ? head_scores : group_scores));
+    s.states_op[op] = static_cast<float*>(take(st * 4));
+    s.hs_op[op] = static_cast<__half*>(take(st * 2));
+    s.parts_op[op] = static_cast<float*>(take(per_head ? parts_bytes : 0));
+  }
+  s.scores = s.scores_op[0]; s.states = s.states_op[0]; s.hs = s.hs_op[0]; s.parts = s.parts_op[0];
   s.u = static_cast<float*>(take(reverse ? bhl * 4 : 0));
   s.v = static_cast<float*>(take(reverse ? bhl * 4 : 0));
   s.ga_part = static_cast<float*>(take(reverse ? static_cast<size_t>(d.B) * d.H * 4 : 0));
-  s.parts = static_cast<float*>(take(reverse ? static_cast<size_t>(ssd_head_splits(d)) * d.B * d.L * d.G * d.N * 4 : 0));
   s.total = off;
   return s;
 }
@@ -871,27 +879,51 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
   ssd_cumsum_kernel<<<d.B * d.H * d.nc, 256, 0, st>>>(static_cast<const float*>(dt), static_cast<const float*>(A), sc.cum, sc.dtt,
                                                      d.B, d.L, d.H, d.Q);
   MP_LAUNCH_CHECK();
+  // The four operator instances are independent of one another: each runs on its own stream (forked from and
+  // joined back into the caller's stream, which also works under stream capture) with its own scratch set, so
+  // that one chain's kernels fill the SM slots another chain's last wave leaves idle.
+  const bool side_by_side = getenv("MP_SSD_SERIAL") == nullptr;
+  cudaStream_t lanes[4] = {st, st, st, st};
+  if (side_by_side) {
+    mp_aux_init(state);
+    MP_CUDA_CHECK(cudaEventRecord(state->aux_fork, st));
+    for (int i = 0; i < 3; ++i) {
+      MP_CUDA_CHECK(cudaStreamWaitEvent(state->aux_stream[i], state->aux_fork, 0));
+      lanes[i + 1] = state->aux_stream[i];
+    }
+  }
+  auto scratch_of = [&](int op) {
+    SsdScratch o = sc;
+    o.scores = sc.scores_op[op]; o.states = sc.states_op[op]; o.hs = sc.hs_op[op]; o.parts = sc.parts_op[op];
+    return o;
+  };
   Roles r;
+  // gx and v_t = <gx_t, x_t>   (the caller's stream)
+  r.q = bh; r.q_head = 0; r.k = ch; r.k_head = 0; r.v = gyh; r.v_head = 1;
+  r.dk = d.N; r.dv = d.P; r.anti = 1; r.scores_head = 0; r.out_head = 1;
+  r.out = static_cast<__half*>(gx); r.z = xh; r.dot = sc.v;
+  ssd_operator(d, r, scratch_of(0), state->status_dev, lanes[0]);
   // u_t = <gy_t, y_t>: the forward operator with the row dot as its only output
   r.q = ch; r.q_head = 0; r.k = bh; r.k_head = 0; r.v = xh; r.v_head = 1;
   r.dk = d.N; r.dv = d.P; r.anti = 0; r.scores_head = 0; r.out_head = 1;
   r.out = nullptr; r.z = gyh; r.dot = sc.u;
-  ssd_operator(d, r, sc, state->status_dev, st);
-  // gx and v_t = <gx_t, x_t>
-  r.q = bh; r.q_head = 0; r.k = ch; r.k_head = 0; r.v = gyh; r.v_head = 1;
-  r.dk = d.N; r.dv = d.P; r.anti = 1; r.scores_head = 0; r.out_head = 1;
-  r.out = static_cast<__half*>(gx); r.z = xh; r.dot = sc.v;
-  ssd_operator(d, r, sc, state->status_dev, st);
+  ssd_operator(d, r, scratch_of(1), state->status_dev, lanes[1]);
   // gC (summed over the heads of each group)
   r.q = gyh; r.q_head = 1; r.k = xh; r.k_head = 1; r.v = bh; r.v_head = 0;
   r.dk = d.P; r.dv = d.N; r.anti = 0; r.scores_head = 1; r.out_head = 0;
   r.out = static_cast<__half*>(gC); r.z = nullptr; r.dot = nullptr;
-  ssd_operator(d, r, sc, state->status_dev, st);
+  ssd_operator(d, r, scratch_of(2), state->status_dev, lanes[2]);
   // gB
   r.q = xh; r.q_head = 1; r.k = gyh; r.k_head = 1; r.v = ch; r.v_head = 0;
   r.dk = d.P; r.dv = d.N; r.anti = 1; r.scores_head = 1; r.out_head = 0;
   r.out = static_cast<__half*>(gB); r.z = nullptr; r.dot = nullptr;
-  ssd_operator(d, r, sc, state->status_dev, st);
+  ssd_operator(d, r, scratch_of(3), state->status_dev, lanes[3]);
+  if (side_by_side) {
+    for (int i = 0; i < 3; ++i) {
+      MP_CUDA_CHECK(cudaEventRecord(state->aux_join[i], state->aux_stream[i]));
+      MP_CUDA_CHECK(cudaStreamWaitEvent(st, state->aux_join[i], 0));
+    }
+  }
   // gdt, gA
   ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, st>>>(sc.u, sc.v, sc.dtt, static_cast<const float*>(A), static_cast<float*>(gdt),
                                                     sc.ga_part, d.B, d.L, d.H);
