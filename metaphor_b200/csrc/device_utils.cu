@@ -125,11 +125,12 @@ extern "C" void mpDeinitStream(StreamContext ctx) {
   MP_CUDA_CHECK(cudaStreamSynchronize(stream));
   if (st != nullptr) {
     if (st->aux_ready) {
-      for (int i = 0; i < 3; ++i) {
+      for (int i = 0; i < 7; ++i) {
         MP_CUDA_CHECK(cudaStreamSynchronize(st->aux_stream[i]));
         MP_CUDA_CHECK(cudaStreamDestroy(st->aux_stream[i]));
         MP_CUDA_CHECK(cudaEventDestroy(st->aux_join[i]));
       }
+      for (int i = 0; i < 4; ++i) MP_CUDA_CHECK(cudaEventDestroy(st->aux_sub_fork[i]));
       MP_CUDA_CHECK(cudaEventDestroy(st->aux_fork));
     }
     MP_CUDA_CHECK(cudaFree(st->workspace));

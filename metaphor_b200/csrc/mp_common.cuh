@@ -69,18 +69,19 @@ struct MpStreamState {
   uint32_t* status_host;    // pinned host landing slot for mpGetStatus
   // Helper streams and events for launchers that run independent kernel chains side by side (forked from and
   // joined back into `stream`, also under stream capture); created on first use, destroyed with the state.
-  cudaStream_t aux_stream[3];
-  cudaEvent_t aux_fork, aux_join[3];
+  cudaStream_t aux_stream[7];          // 0-2: side lanes, 3-6: one sub-lane per lane
+  cudaEvent_t aux_fork, aux_join[7], aux_sub_fork[4];
   bool aux_ready;
 };
 
 // Creates the helper streams / events of a state on first use.
 static inline void mp_aux_init(MpStreamState* st) {
   if (st->aux_ready) return;
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i < 7; ++i) {
     MP_CUDA_CHECK(cudaStreamCreateWithFlags(&st->aux_stream[i], cudaStreamNonBlocking));
     MP_CUDA_CHECK(cudaEventCreateWithFlags(&st->aux_join[i], cudaEventDisableTiming));
   }
+  for (int i = 0; i < 4; ++i) MP_CUDA_CHECK(cudaEventCreateWithFlags(&st->aux_sub_fork[i], cudaEventDisableTiming));
   MP_CUDA_CHECK(cudaEventCreateWithFlags(&st->aux_fork, cudaEventDisableTiming));
   st->aux_ready = true;
 }

@@ -741,7 +741,10 @@ void ssd_launch(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap&
 }
 
 // One instance of the chunked operator (scores -> states -> scan -> output).
-void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32_t* status, cudaStream_t st) {
+// `sub` (may be null): a second stream on which the scores kernel runs beside the states + scan chain; `fork`
+// and `join` are the events that order it against `st`.
+void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32_t* status, cudaStream_t st,
+                  cudaStream_t sub = nullptr, cudaEvent_t fork = nullptr, cudaEvent_t join = nullptr) {
   SsdArgs g;
   g.B = d.B; g.L = d.L; g.H = d.H; g.G = d.G; g.Q = d.Q; g.nc = d.nc;
   g.dk = r.dk; g.dv = r.dv; g.anti = r.anti;
@@ -774,7 +777,14 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
     const CUtensorMap mq = ssd_map(r.q, rows, qcols, 128), mk = ssd_map(r.k, rows, kcols, 128);
     const dim3 grid(d.Q / 128, d.Q / 128, d.B * d.nc * sunits);
     const size_t smem = configure(TILE_BYTES, 128);
-    ssd_launch<MODE_SCORES>(mq, mk, mq, mk, g, grid, smem, st);
+    if (sub != nullptr) {
+      MP_CUDA_CHECK(cudaEventRecord(fork, st));
+      MP_CUDA_CHECK(cudaStreamWaitEvent(sub, fork, 0));
+      ssd_launch<MODE_SCORES>(mq, mk, mq, mk, g, grid, smem, sub);
+      MP_CUDA_CHECK(cudaEventRecord(join, sub));
+    } else {
+      ssd_launch<MODE_SCORES>(mq, mk, mq, mk, g, grid, smem, st);
+    }
   }
   // chunk states: MN-major 64x64 boxes of k and v
   {
@@ -790,6 +800,7 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
     MP_LAUNCH_CHECK();
   }
   // output
+  if (sub != nullptr) MP_CUDA_CHECK(cudaStreamWaitEvent(st, join, 0));
   {
     const CUtensorMap ms = ssd_map(sc.scores, static_cast<size_t>(d.B) * d.nc * sunits * d.Q, d.Q, 128);
     const CUtensorMap mv = ssd_map(r.v, rows, vcols, 64);
@@ -856,7 +867,12 @@ extern "C" void launch_ssd_scan_r16(const void* x, const void* dt, const void* A
   r.v = static_cast<const __half*>(x); r.v_head = 1;
   r.dk = d.N; r.dv = d.P; r.anti = 0; r.scores_head = 0; r.out_head = 1;
   r.out = static_cast<__half*>(y); r.z = nullptr; r.dot = nullptr;
-  ssd_operator(d, r, sc, state->status_dev, st);
+  if (getenv("MP_SSD_SERIAL") == nullptr) {
+    mp_aux_init(state);
+    ssd_operator(d, r, sc, state->status_dev, st, state->aux_stream[3], state->aux_sub_fork[0], state->aux_join[3]);
+  } else {
+    ssd_operator(d, r, sc, state->status_dev, st);
+  }
 }
 
 // Gradients of a loss with upstream gradient gy (same shape as y); every output is overwritten.
@@ -902,22 +918,27 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
   r.q = bh; r.q_head = 0; r.k = ch; r.k_head = 0; r.v = gyh; r.v_head = 1;
   r.dk = d.N; r.dv = d.P; r.anti = 1; r.scores_head = 0; r.out_head = 1;
   r.out = static_cast<__half*>(gx); r.z = xh; r.dot = sc.v;
-  ssd_operator(d, r, scratch_of(0), state->status_dev, lanes[0]);
+  auto run_op = [&](int op) {
+    if (side_by_side) ssd_operator(d, r, scratch_of(op), state->status_dev, lanes[op], state->aux_stream[3 + op],
+                                   state->aux_sub_fork[op], state->aux_join[3 + op]);
+    else ssd_operator(d, r, scratch_of(op), state->status_dev, lanes[op]);
+  };
+  run_op(0);
   // u_t = <gy_t, y_t>: the forward operator with the row dot as its only output
   r.q = ch; r.q_head = 0; r.k = bh; r.k_head = 0; r.v = xh; r.v_head = 1;
   r.dk = d.N; r.dv = d.P; r.anti = 0; r.scores_head = 0; r.out_head = 1;
   r.out = nullptr; r.z = gyh; r.dot = sc.u;
-  ssd_operator(d, r, scratch_of(1), state->status_dev, lanes[1]);
+  run_op(1);
   // gC (summed over the heads of each group)
   r.q = gyh; r.q_head = 1; r.k = xh; r.k_head = 1; r.v = bh; r.v_head = 0;
   r.dk = d.P; r.dv = d.N; r.anti = 0; r.scores_head = 1; r.out_head = 0;
   r.out = static_cast<__half*>(gC); r.z = nullptr; r.dot = nullptr;
-  ssd_operator(d, r, scratch_of(2), state->status_dev, lanes[2]);
+  run_op(2);
   // gB
   r.q = xh; r.q_head = 1; r.k = gyh; r.k_head = 1; r.v = ch; r.v_head = 0;
   r.dk = d.P; r.dv = d.N; r.anti = 1; r.scores_head = 1; r.out_head = 0;
   r.out = static_cast<__half*>(gB); r.z = nullptr; r.dot = nullptr;
-  ssd_operator(d, r, scratch_of(3), state->status_dev, lanes[3]);
+  run_op(3);
   if (side_by_side) {
     for (int i = 0; i < 3; ++i) {
       MP_CUDA_CHECK(cudaEventRecord(state->aux_join[i], state->aux_stream[i]));
