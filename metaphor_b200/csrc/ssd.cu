@@ -763,9 +763,9 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
   const size_t vcols = static_cast<size_t>(r.v_head ? d.H : d.G) * r.dv;
   // Shared memory per CTA is kept near 50-70 KB so that three or four CTAs share an SM: every CTA has
   // only a handful of k-blocks, so latency is hidden across CTAs rather than by a deep pipeline.
-  auto configure = [&](int b_tile_bytes, int tile_cols) {
+  auto configure = [&](int b_tile_bytes, int tile_cols, int stages = 2) {
     g.stage_bytes = TILE_BYTES + b_tile_bytes;
-    g.stages = 2;
+    g.stages = stages;
     g.tmem_cols = tile_cols <= 32 ? 32 : (tile_cols <= 64 ? 64 : 128);
     return static_cast<size_t>(g.stages) * g.stage_bytes + 1024 + 256 + 3 * d.Q * 4;
   };
@@ -776,7 +776,8 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
   {
     const CUtensorMap mq = ssd_map(r.q, rows, qcols, 128), mk = ssd_map(r.k, rows, kcols, 128);
     const dim3 grid(d.Q / 128, d.Q / 128, d.B * d.nc * sunits);
-    const size_t smem = configure(TILE_BYTES, 128);
+    // one k-block per tile when dk = 64 (per-head scores): a single stage, so that four CTAs fit an SM
+    const size_t smem = configure(TILE_BYTES, 128, r.dk / 64 == 1 ? 1 : 2);
     if (sub != nullptr) {
       MP_CUDA_CHECK(cudaEventRecord(fork, st));
       MP_CUDA_CHECK(cudaStreamWaitEvent(sub, fork, 0));
