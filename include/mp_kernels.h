@@ -142,7 +142,9 @@ MP_DECL3(linear_ij_jk_ik, const void* a_data, const void* b_data, const void* bi
  * x, y: [batch, seqlen, heads, headdim] of T; dt: [batch, seqlen, heads] r32
  * (already positive, e.g. after softplus); A: [heads] r32 (negative);
  * B, C: [batch, seqlen, ngroups, dstate] of T.  fp32 accumulation.
- * scratch: mpSsdScanScratchBytes(..., reverse) bytes owned by the caller.
+ * scratch: mpSsdScanScratchBytes(..., reverse) bytes owned by the caller (the reverse holds four
+ * independent sets of intermediates, its operator instances run side by side on helper streams that
+ * the library forks from and joins back into the caller's stream).
  * Implemented for r16 with dstate = 128, headdim 64 or 128, chunk 128 or 256,
  * seqlen a multiple of chunk; the r32 / r64 entry points report "not implemented". */
 MP_DECL3(ssd_scan, const void* x, const void* dt, const void* A, const void* B, const void* C, void* y, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
