@@ -47,3 +47,55 @@ def test_wrapped_torch_stream(mp):
     assert torch.equal(y, torch.relu(x))
     s.close()
     assert float(x.sum()) == float(x.sum())                       # torch's stream is still alive
+
+
+def test_graph_capture_replays_a_launch_sequence(mp):
+    """mpGraphBeginCapture / EndCapture / Launch: three dependent launches recorded once reproduce the eagerly
+    computed result on every replay, also after the inputs change in place."""
+    import numpy as np
+    import torch
+    lib = mp.lib()
+    s = mp.Stream()
+    n = 1 << 16
+    a = torch.randn(n, device="cuda"); b = torch.randn(n, device="cuda")
+    t = torch.empty_like(a); out = torch.empty_like(a)
+    torch.cuda.synchronize()
+
+    def chain():
+        mp.launch("addition", torch.float32, a, b, t, n, s)
+        mp.launch("selu", torch.float32, t, out, n, s)
+        mp.launch("hadamard", torch.float32, out, a, out, n, s)
+
+    chain(); s.sync()
+    want = out.clone()
+    lib.mpGraphBeginCapture(s.ctx)
+    chain()
+    g = lib.mpGraphEndCapture(s.ctx)
+    assert g
+    out.zero_(); torch.cuda.synchronize()
+    lib.mpGraphLaunch(g, s.ctx); s.sync()
+    assert torch.equal(out, want)
+    a.mul_(2.0); torch.cuda.synchronize()          # same buffers, new contents
+    lib.mpGraphLaunch(g, s.ctx); s.sync()
+    ref = torch.nn.functional.selu(a + b) * a
+    assert float((out - ref).abs().max()) < 1e-5
+    assert s.status() == 0
+    lib.mpGraphDestroy(g)
+    s.close()
+
+
+def test_ssd_helper_streams_are_released(mp):
+    """A stream that ran the scan (which forks helper streams) can be closed and re-created."""
+    import torch
+    for _ in range(2):
+        s = mp.Stream()
+        dims = (1, 256, 2, 64, 128, 1, 128)
+        x = torch.randn(1, 256, 2, 64, device="cuda").half(); Bm = torch.randn(1, 256, 1, 128, device="cuda").half()
+        Cm = torch.randn(1, 256, 1, 128, device="cuda").half(); dt = torch.rand(1, 256, 2, device="cuda") * 0.1
+        A = -torch.ones(2, device="cuda"); y = torch.empty_like(x)
+        scr = torch.empty(mp.lib().mpSsdScanScratchBytes(*dims, 0), dtype=torch.uint8, device="cuda")
+        torch.cuda.synchronize()
+        mp.launch("ssd_scan", torch.float16, x, dt, A, Bm, Cm, y, scr, *dims, s)
+        s.sync()
+        assert s.status() == 0 and bool(torch.isfinite(y).all())
+        s.close()
