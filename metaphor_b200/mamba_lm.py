@@ -142,7 +142,9 @@ class MambaLM:
         self.saved = [dict(h_in=f16(T, c.d_model), xn=f16(T, c.d_model), rstd1=f32(T), zx=f16(T, c.d_in_proj), xs=f16(T, c.d_inner),
                            Bs=f16(T, gn), Cs=f16(T, gn), dt=f32(T, c.heads), A=f32(c.heads), y=f16(T, c.d_inner), u=f16(T, c.d_inner),
                            un=f16(T, c.d_inner), rstd2=f32(T)) for _ in range(c.n_layer)]
-        self.h = f16(T, c.d_model)
+        # residual stream: the input of layer i is saved[i]["h_in"], its output is written straight into the next
+        # layer's h_in (the last one into h_out), so nothing is copied
+        self.h_out = f16(T, c.d_model)
         self.o = f16(T, c.d_model)
         self.hn = f16(T, c.d_model)
         self.rstdf = f32(T)
@@ -204,11 +206,11 @@ class MambaLM:
         di, gn, H, P = c.d_inner, c.ngroups * c.d_state, c.heads, c.headdim
         dip = c.d_in_proj
         esz = 2
-        self._L("embedding", self._p(W, "embedding"), self.ids, self.h, T, c.d_model, c.vocab)
+        self._L("embedding", self._p(W, "embedding"), self.ids, self.saved[0]["h_in"], T, c.d_model, c.vocab)
         for i, sv in enumerate(self.saved):
             p = f"layers.{i}."
-            self._L("copy", self.h, sv["h_in"], T * c.d_model)
-            self._L("rmsnorm_ij_j", self.h, self._p(W, p + "norm_w"), c.eps, sv["xn"], sv["rstd1"], T, c.d_model)
+            h_next = self.saved[i + 1]["h_in"] if i + 1 < c.n_layer else self.h_out
+            self._L("rmsnorm_ij_j", sv["h_in"], self._p(W, p + "norm_w"), c.eps, sv["xn"], sv["rstd1"], T, c.d_model)
             self._L("inner_product_ij_jk_ik", sv["xn"], self._p(W, p + "in_proj"), 1.0, sv["zx"], 0.0, T, c.d_model, dip)
             zx = sv["zx"].data_ptr()
             # conv over the [x | B | C] columns, each segment into its own contiguous tensor
@@ -221,8 +223,8 @@ class MambaLM:
             self._L("ssd_gate", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, sv["u"], T, H, P)
             self._L("rmsnorm_ij_j", sv["u"], self._p(W, p + "gnorm_w"), c.eps, sv["un"], sv["rstd2"], T, di)
             self._L("inner_product_ij_jk_ik", sv["un"], self._p(W, p + "out_proj"), 1.0, self.o, 0.0, T, di, c.d_model)
-            self._L("addition", self.h, self.o, self.h, T * c.d_model)
-        self._L("rmsnorm_ij_j", self.h, self._p(W, "normf_w"), c.eps, self.hn, self.rstdf, T, c.d_model)
+            self._L("addition", sv["h_in"], self.o, h_next, T * c.d_model)
+        self._L("rmsnorm_ij_j", self.h_out, self._p(W, "normf_w"), c.eps, self.hn, self.rstdf, T, c.d_model)
         self._L("inner_product_ij_kj_ik", self.hn, self._p(W, "embedding"), 1.0, self.logits, 0.0, T, c.d_model, c.vocab)
 
     def loss_and_logit_gradient(self):
@@ -243,7 +245,7 @@ class MambaLM:
         gl = self.logits   # holds d loss / d logits
         self._L("inner_product_ij_jk_ik", gl, self._p(W, "embedding"), 1.0, self.gt, 0.0, T, c.vocab, c.d_model)
         self._L("inner_product_ji_jk_ik", gl, self.hn, 1.0, self._p(G16, "embedding"), 0.0, c.vocab, T, c.d_model)
-        self._L("rmsnorm_ij_j_reverse", self.h, self._p(W, "normf_w"), self.rstdf, self.gt, c.eps, self.gh, self._p(G16, "normf_w"),
+        self._L("rmsnorm_ij_j_reverse", self.h_out, self._p(W, "normf_w"), self.rstdf, self.gt, c.eps, self.gh, self._p(G16, "normf_w"),
                 0.0, self.rms_scratch, T, c.d_model)
         for i in reversed(range(c.n_layer)):
             sv, p = self.saved[i], f"layers.{i}."
@@ -355,4 +357,4 @@ class MambaLM:
 
     def launches_per_step(self) -> int:
         n = self.cfg.n_layer
-        return 1 + 13 * n + 2 + 2 + 5 + 19 * n + 2 + 2
+        return 1 + 12 * n + 2 + 2 + 5 + 19 * n + 2 + 2
