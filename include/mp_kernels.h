@@ -145,13 +145,17 @@ MP_DECL3(linear_ij_jk_ik, const void* a_data, const void* b_data, const void* bi
  * scratch: mpSsdScanScratchBytes(..., reverse) bytes owned by the caller (the reverse holds four
  * independent sets of intermediates, its operator instances run side by side on helper streams that
  * the library forks from and joins back into the caller's stream).
- * Implemented for r16 with dstate = 128, headdim 64 or 128, chunk 128 or 256,
- * seqlen a multiple of chunk; the r32 / r64 entry points report "not implemented". */
+ * Two implementations: a tensor-core path (r16 with dstate = 128, headdim 64 or 128, chunk 128 or 256,
+ * seqlen a multiple of chunk) and a sequential-recurrence path for every other shape of r16 and for r32 /
+ * r64 storage (dt, A, gdt, gA then have the storage type; `chunk` is ignored).  Scratch: r16 ->
+ * mpSsdScanScratchBytes (either path), r32 / r64 -> mpSsdScanGenericScratchBytes(dtype_key, ...); the
+ * forward of the sequential path needs none. */
 MP_DECL3(ssd_scan, const void* x, const void* dt, const void* A, const void* B, const void* C, void* y, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
 /* Reverse of the scan: given gy (shape of y) writes (overwrites) gx, gdt (r32),
  * gA (r32, [heads]), gB, gC.  gB and gC are summed over the heads of a group. */
 MP_DECL3(ssd_scan_reverse, const void* x, const void* dt, const void* A, const void* B, const void* C, const void* gy, void* gx, void* gdt, void* gA, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
 MP_EXTERN_C len_t mpSsdScanScratchBytes(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, uint32_t reverse);
+MP_EXTERN_C len_t mpSsdScanGenericScratchBytes(uint32_t dtype_key, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, uint32_t reverse);
 
 /* ---- operators around the scan in a Mamba-2 language-model step ------------
  * No counterpart in the reference (its loss layer is a sketch,

@@ -107,6 +107,7 @@ UTILS = {
     "mpGraphDestroy": (None, [P]),
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
     "mpSsdScanScratchBytes": (L, [L, L, L, L, L, L, L, U32]),
+    "mpSsdScanGenericScratchBytes": (L, [U32, L, L, L, L, L, L, U32]),
     "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),
     "launch_convert_r16_r32": (None, [P, P, D, L, CTX]),
     "launch_convert_r32_r16": (None, [P, P, L, CTX]),

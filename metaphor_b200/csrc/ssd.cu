@@ -824,11 +824,11 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
   }
 }
 
-void ssd_check_dims(const SsdDims& d) {
-  if (d.N != 128 || (d.P != 64 && d.P != 128)) MP_FATAL("ssd_scan: the tensor-core path needs d_state = 128 and headdim 64 or 128 (got %d, %d)", d.N, d.P);
-  if (d.Q != 128 && d.Q != 256) MP_FATAL("ssd_scan: chunk must be 128 or 256 (got %d)", d.Q);
-  if (d.L % d.Q != 0) MP_FATAL("ssd_scan: seqlen %d is not a multiple of the chunk %d", d.L, d.Q);
+// Shapes the tensor-core path covers; everything else takes the sequential-recurrence kernels of ssd_generic.cu.
+bool ssd_tensor_path(const SsdDims& d) {
   if (d.G <= 0 || d.H % d.G != 0) MP_FATAL("ssd_scan: heads %d not divisible by groups %d", d.H, d.G);
+  return d.N == 128 && (d.P == 64 || d.P == 128) && (d.Q == 128 || d.Q == 256) && d.L % d.Q == 0 &&
+         getenv("MP_SSD_FORCE_GENERIC") == nullptr;
 }
 
 SsdDims ssd_dims(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk) {
@@ -841,9 +841,20 @@ SsdDims ssd_dims(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t ds
 
 }  // namespace
 
+extern "C" len_t mpSsdScanGenericScratchBytes(uint32_t dtype_key, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate,
+                                              len_t ngroups, uint32_t reverse);
+void mp_ssd_generic_forward_r16(const void* x, const void* dt, const void* A, const void* B, const void* C, void* y, len_t batch, len_t seqlen,
+                                len_t heads, len_t headdim, len_t dstate, len_t ngroups, StreamContext ctx);
+void mp_ssd_generic_reverse_r16(const void* x, const void* dt, const void* A, const void* B, const void* C, const void* gy, void* gx, void* gdt,
+                                void* gA, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim,
+                                len_t dstate, len_t ngroups, StreamContext ctx);
+
+// r16 storage (for r32 / r64 see mpSsdScanGenericScratchBytes)
 extern "C" len_t mpSsdScanScratchBytes(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups,
                                        len_t chunk, uint32_t reverse) {
   const SsdDims d = ssd_dims(batch, seqlen, heads, headdim, dstate, ngroups, chunk);
+  if (batch == 0 || seqlen == 0 || heads == 0) return 256;
+  if (!ssd_tensor_path(d)) return mpSsdScanGenericScratchBytes(0, batch, seqlen, heads, headdim, dstate, ngroups, reverse);
   return ssd_carve(nullptr, d, reverse != 0).total;
 }
 
@@ -854,7 +865,10 @@ extern "C" void launch_ssd_scan_r16(const void* x, const void* dt, const void* A
                                     len_t ngroups, len_t chunk, StreamContext ctx) {
   if (batch == 0 || seqlen == 0 || heads == 0) return;
   const SsdDims d = ssd_dims(batch, seqlen, heads, headdim, dstate, ngroups, chunk);
-  ssd_check_dims(d);
+  if (!ssd_tensor_path(d)) {
+    mp_ssd_generic_forward_r16(x, dt, A, Bm, Cm, y, batch, seqlen, heads, headdim, dstate, ngroups, ctx);
+    return;
+  }
   if (scratch == nullptr) MP_FATAL("ssd_scan: scratch must not be NULL");
   MpStreamState* state = mp_state(ctx);
   cudaStream_t st = mp_stream(ctx);
@@ -884,7 +898,10 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
                                             len_t chunk, StreamContext ctx) {
   if (batch == 0 || seqlen == 0 || heads == 0) return;
   const SsdDims d = ssd_dims(batch, seqlen, heads, headdim, dstate, ngroups, chunk);
-  ssd_check_dims(d);
+  if (!ssd_tensor_path(d)) {
+    mp_ssd_generic_reverse_r16(x, dt, A, Bm, Cm, gy, gx, gdt, gA, gB, gC, scratch, batch, seqlen, heads, headdim, dstate, ngroups, ctx);
+    return;
+  }
   if (scratch == nullptr) MP_FATAL("ssd_scan_reverse: scratch must not be NULL");
   MpStreamState* state = mp_state(ctx);
   cudaStream_t st = mp_stream(ctx);
@@ -953,18 +970,3 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
   ssd_sum_batches_kernel<<<(d.H + 127) / 128, 128, 0, st>>>(sc.ga_part, static_cast<float*>(gA), d.B, d.H);
   MP_LAUNCH_CHECK();
 }
-
-// r32 / r64 storage: not implemented (the benchmark configuration stores x, B, C, y in r16 with r32
-// dt and A); the symbols exist so that the host's three-entry dispatch arrays stay complete.
-#define MP_SSD_UNSUPPORTED(sfx)                                                                                              \
-  extern "C" void launch_ssd_scan_##sfx(const void*, const void*, const void*, const void*, const void*, void*, void*, len_t,  \
-                                        len_t, len_t, len_t, len_t, len_t, len_t, StreamContext) {                             \
-    MP_FATAL("launch_ssd_scan_" #sfx ": only r16 storage is implemented");                                                    \
-  }                                                                                                                            \
-  extern "C" void launch_ssd_scan_reverse_##sfx(const void*, const void*, const void*, const void*, const void*, const void*, \
-                                                void*, void*, void*, void*, void*, void*, len_t, len_t, len_t, len_t, len_t,   \
-                                                len_t, len_t, StreamContext) {                                                 \
-    MP_FATAL("launch_ssd_scan_reverse_" #sfx ": only r16 storage is implemented");                                            \
-  }
-MP_SSD_UNSUPPORTED(r32)
-MP_SSD_UNSUPPORTED(r64)
