@@ -75,3 +75,36 @@ def test_ssd_reverse(mp, stream, orc, dims):
     assert_close(host(gB), rgB.astype(np.float16), TOL, f"gB {dims}")
     assert_close(host(gdt), rgdt, TOL, f"gdt {dims}")
     assert_close(host(gA), rgA, TOL, f"gA {dims}")
+
+
+def test_full_length_against_the_sequential_path(mp, stream):
+    """Benchmark-length sequences (seqlen 8192 = 32 chunks, 32 heads, one batch): the chunked tensor-core path
+    against the sequential-recurrence kernels of the same library, forward and every gradient."""
+    import os
+    import torch
+    dims = (1, 8192, 32, 64, 128, 1, 256)
+    nb, L, H, P, N, G, Q = dims
+    x, dt, A, Bm, Cm, gy = make_inputs(11, nb, L, H, P, N, G)
+    args = [dev(a) for a in (x, dt, A, Bm, Cm)]
+    dgy = dev(gy)
+    lib = mp.lib()
+    out = {}
+    for path in ("tensor", "sequential"):
+        if path == "sequential":
+            os.environ["MP_SSD_FORCE_GENERIC"] = "1"
+        try:
+            n = max(lib.mpSsdScanScratchBytes(*dims, 0), lib.mpSsdScanScratchBytes(*dims, 1))
+            scr = torch.empty(n, dtype=torch.uint8, device="cuda")
+            y = dev(np.full(x.shape, np.nan, np.float16))
+            gx = dev(np.full(x.shape, np.nan, np.float16)); gdt = dev(np.full(dt.shape, np.nan, np.float32))
+            gA = dev(np.full(A.shape, np.nan, np.float32)); gB = dev(np.full(Bm.shape, np.nan, np.float16)); gC = dev(np.full(Cm.shape, np.nan, np.float16))
+            torch.cuda.current_stream().synchronize()
+            mp.launch("ssd_scan", torch.float16, *args, y, scr, *dims, stream)
+            mp.launch("ssd_scan_reverse", torch.float16, *args, dgy, gx, gdt, gA, gB, gC, scr, *dims, stream)
+            stream.sync()
+            assert stream.status() == 0
+            out[path] = [host(t).astype(np.float64) for t in (y, gx, gdt, gA, gB, gC)]
+        finally:
+            os.environ.pop("MP_SSD_FORCE_GENERIC", None)
+    for got, want, name in zip(out["tensor"], out["sequential"], ("y", "gx", "gdt", "gA", "gB", "gC")):
+        assert_close(got, want, 1e-2, f"full-length {name}")
