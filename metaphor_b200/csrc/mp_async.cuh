@@ -1,6 +1,6 @@
 // Asynchronous-copy primitives for sm_100a: shared-memory mbarriers with
 // BOUNDED waits, 1-D bulk copies (cp.async.bulk), tiled TMA loads
-// (cp.async.bulk.tensor, never with cluster multicast) and the proxy fences
+// (cp.async.bulk.tensor, every copy addressed to a single CTA) and the proxy fences
 // that go with them.
 //
 // Every wait gives up after MP_WAIT_LIMIT_NS, records MP_STATUS_WAIT_TIMEOUT in

@@ -1,6 +1,6 @@
 // 5th-generation tensor core (tcgen05) and tiled-TMA primitives for sm_100a,
 // as inline PTX: TMEM allocation, UMMA shared-memory / instruction descriptors,
-// tcgen05.mma / commit / ld, and cp.async.bulk.tensor loads (never multicast).
+// tcgen05.mma / commit / ld, and cp.async.bulk.tensor loads (each addressed to a single CTA).
 #pragma once
 
 #include "mp_async.cuh"
@@ -145,8 +145,8 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
 // ------------------------------ CTA pairs (cta_group::2) ---------------------
 // Two CTAs of a cluster (ranks 0 and 1) work on one 256-row tile: each holds its 128 rows of A and one
 // half of B's columns in its own shared memory and its 128 accumulator rows in its own TMEM; the MMA is
-// issued by one thread of rank 0 and reads both CTAs' shared memory at the same offsets.  Nothing here
-// uses cluster multicast.
+// issued by one thread of rank 0 and reads both CTAs' shared memory at the same offsets.  Every copy and
+// every barrier arrival below is addressed to exactly one CTA.
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
