@@ -356,5 +356,11 @@ class MambaLM:
         self._refresh_w16()
 
     def launches_per_step(self) -> int:
+        """Kernels of this library launched per training step (a launcher call is several kernels: the scan
+        forward 5, its reverse 22, an RMSNorm reverse 3, a split-K contraction 2)."""
         n = self.cfg.n_layer
-        return 1 + 12 * n + 2 + 2 + 5 + 19 * n + 2 + 2
+        forward = 16 * n + 3          # per layer: 2 norms, 2 contractions, 3 convs, softplus, neg_exp, scan (5), gate, add
+        loss = 2
+        reverse = 41 * n + 9          # per layer: 4 contractions (2 split-K), 2 norm reverses, gate, scan (22), skip, A_log, softplus, 3 convs
+        update = 3                    # gradient conversion, Adam, r16 refresh
+        return forward + loss + reverse + update
