@@ -210,6 +210,25 @@ MP_DECL3(bce_loss_i_i, const void* x, void* grad, const void* trg, void* scratch
 /* m = alpha*m + clip(g, clip_lo, clip_hi);  w -= rate*m */
 MP_DECL3(momentum, void* w, const void* g, void* m, double rate, double alpha, double clip_lo, double clip_hi, len_t n, StreamContext stream)
 
+/* Roadmap operators of the reference beyond rank 2 (NOTES.md:3-5 "General Permutation", NOTES.md:18
+ * "_ij,_jk->_ik"); the reference holds the expression grammar (expression_parsing.zig:205-255, :257-317)
+ * but no kernels.
+ *
+ * permutate: dst = permute(src) + alpha*dst for any rank <= MAX_DIMS.  `sizes` are the source sizes and
+ * `perm[i]` is the position of source dimension i in the output (the `perm` array that `permutateSizes`
+ * derives from "ijk->kij": lhs index i sits at rhs position perm[i]); both are HOST arrays of `rank`
+ * entries, read before the call returns.  Bit-exact when alpha = 0.  permutate_ij_ji is the instance
+ * sizes = {row, col}, perm = {1, 0}. */
+MP_DECL3(permutate, const void* src, void* dst, double alpha, const len_t* sizes, const len_t* perm, len_t rank, StreamContext stream)
+/* Batched contractions over densely packed operands, one (m,n)x(n,k) product per batch entry:
+ *   bij,bjk->bik : C[b,m,k] = alpha*A[b,m,n]*B[b,n,k]   + beta*C
+ *   bij,bkj->bik : C[b,m,k] = alpha*A[b,m,n]*B[b,k,n]^T + beta*C
+ *   bji,bjk->bik : C[b,m,k] = alpha*A[b,n,m]^T*B[b,n,k] + beta*C
+ * Same tcgen05 kernel as the rank-2 forms over 3-D tensor maps (work unit = batch entry x output tile). */
+MP_DECL3(inner_product_bij_bjk_bik, const void* a_data, const void* b_data, const double alpha, void* c_data, const double beta, len_t batch, len_t m, len_t n, len_t k, StreamContext stream)
+MP_DECL3(inner_product_bij_bkj_bik, const void* a_data, const void* b_data, const double alpha, void* c_data, const double beta, len_t batch, len_t m, len_t n, len_t k, StreamContext stream)
+MP_DECL3(inner_product_bji_bjk_bik, const void* a_data, const void* b_data, const double alpha, void* c_data, const double beta, len_t batch, len_t m, len_t n, len_t k, StreamContext stream)
+
 /* Status word values returned by mpGetStatus (mp_device_utils.h). */
 #define MP_STATUS_OK             0u
 #define MP_STATUS_WAIT_TIMEOUT   1u  /* a bounded mbarrier wait gave up    */

@@ -76,6 +76,11 @@ LAUNCHERS = {
     "mse_loss_i_i": [P, P, P, P, P, L, CTX],
     "bce_loss_i_i": [P, P, P, P, P, L, CTX],
     "momentum": [P, P, P, D, D, D, D, L, CTX],
+    # beyond rank 2: sizes / perm are host arrays of len_t
+    "permutate": [P, P, D, P, P, L, CTX],
+    "inner_product_bij_bjk_bik": [P, P, D, P, D, L, L, L, L, CTX],
+    "inner_product_bij_bkj_bik": [P, P, D, P, D, L, L, L, L, CTX],
+    "inner_product_bji_bjk_bik": [P, P, D, P, D, L, L, L, L, CTX],
 }
 
 # name -> (restype, argtypes)

@@ -35,6 +35,9 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ a,
                                                         int b_mn) {
   using A = typename Acc<T>::type;
   constexpr int TS = 64, KS = 16;
+  a += static_cast<size_t>(blockIdx.z) * M * K;   // batch entries are densely packed
+  b += static_cast<size_t>(blockIdx.z) * K * N;
+  c += static_cast<size_t>(blockIdx.z) * M * N;
   __shared__ A sa[KS][TS + 1];
   __shared__ A sb[KS][TS + 1];
   const size_t m0 = static_cast<size_t>(blockIdx.y) * TS, n0 = static_cast<size_t>(blockIdx.x) * TS;
@@ -125,6 +128,7 @@ struct GemmArgs {
   int split;          // r32 only: 1 = error-compensated hi/lo split (3 MMAs per k-slice)
   int ksplit;         // > 1: the K range of every tile is cut into ksplit work units whose raw fp32
   float* partial;     //      accumulators go to partial[unit_split][M][N]; a fold kernel finishes C
+  int batch;          // > 1: densely packed [batch, M, K] x [batch, K, N] -> [batch, M, N] over 3-D tensor maps (ksplit = 1)
   uint32_t* status;
 };
 
@@ -178,8 +182,10 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
   const int tiles_m = (g.M + BM - 1) / BM, tiles_n = (g.N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   // work unit u = (tile u % num_tiles, K split u / num_tiles) covering k-blocks [kb0, kb1)
-  const int num_units = num_tiles * g.ksplit;
+  // batched: unit = batch entry * num_tiles + tile (ksplit is 1)
+  const int num_units = num_tiles * g.ksplit * g.batch;
   const int kb_per = (num_kb + g.ksplit - 1) / g.ksplit;
+  const bool batched = g.batch > 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -207,7 +213,8 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
       uint32_t phase = 0;
       bool ok = true;
       for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
-        const int tile = unit % num_tiles, sp = unit / num_tiles;
+        const int bz = batched ? unit / num_tiles : 0;
+        const int tile = batched ? unit - bz * num_tiles : unit % num_tiles, sp = batched ? 0 : unit / num_tiles;
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
         const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -216,19 +223,34 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
           unsigned char* sb = sa + A_BYTES;
           mbar_arrive_expect_tx(full + s, A_BYTES + B_BYTES);
           const int k0 = kb * BK;
-          if (!g.a_mn) {
-            tma_load_2d(sa, &tmap_a, k0, m0, full + s);            // box {BK, BM}
-          } else {
+          if (batched) {   // the same boxes over 3-D maps
+            if (!g.a_mn) {
+              tma_load_3d(sa, &tmap_a, k0, m0, bz, full + s);
+            } else {
 #pragma unroll 1
-            for (int j = 0; j < BM / BK; ++j)                        // boxes {BK along M, BK k-rows}
-              tma_load_2d(sa + j * (BK * SWIZZLE_BYTES), &tmap_a, m0 + j * BK, k0, full + s);
-          }
-          if (!g.b_mn) {
-            tma_load_2d(sb, &tmap_b, k0, n0, full + s);            // box {BK, BN}
-          } else {
+              for (int j = 0; j < BM / BK; ++j) tma_load_3d(sa + j * (BK * SWIZZLE_BYTES), &tmap_a, m0 + j * BK, k0, bz, full + s);
+            }
+            if (!g.b_mn) {
+              tma_load_3d(sb, &tmap_b, k0, n0, bz, full + s);
+            } else {
 #pragma unroll 1
-            for (int j = 0; j < BN / BK; ++j)
-              tma_load_2d(sb + j * (BK * SWIZZLE_BYTES), &tmap_b, n0 + j * BK, k0, full + s);
+              for (int j = 0; j < BN / BK; ++j) tma_load_3d(sb + j * (BK * SWIZZLE_BYTES), &tmap_b, n0 + j * BK, k0, bz, full + s);
+            }
+          } else {
+            if (!g.a_mn) {
+              tma_load_2d(sa, &tmap_a, k0, m0, full + s);            // box {BK, BM}
+            } else {
+#pragma unroll 1
+              for (int j = 0; j < BM / BK; ++j)                        // boxes {BK along M, BK k-rows}
+                tma_load_2d(sa + j * (BK * SWIZZLE_BYTES), &tmap_a, m0 + j * BK, k0, full + s);
+            }
+            if (!g.b_mn) {
+              tma_load_2d(sb, &tmap_b, k0, n0, full + s);            // box {BK, BN}
+            } else {
+#pragma unroll 1
+              for (int j = 0; j < BN / BK; ++j)
+                tma_load_2d(sb + j * (BK * SWIZZLE_BYTES), &tmap_b, n0 + j * BK, k0, full + s);
+            }
           }
           if (++s == stages) { s = 0; phase ^= 1u; }
         }
@@ -257,7 +279,7 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
         if (!mbar_wait_abortable(acc_empty + buf, (use & 1u) ^ 1u, g.status, abort)) { ok = false; break; }
         tcgen05_fence_after_sync();
         const uint32_t tmem_acc = tmem_base + buf * BN;
-        const int sp = unit / num_tiles;
+        const int sp = batched ? 0 : unit / num_tiles;
         const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
           uint64_t* wait_on = g.split ? (ready + s) : (full + s);
@@ -294,7 +316,7 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
     uint32_t phase = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
-      const int sp = unit / num_tiles;
+      const int sp = batched ? 0 : unit / num_tiles;
       const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait_abortable(full + s, phase, g.status, abort)) { ok = false; break; }
@@ -326,7 +348,8 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
     unsigned char* stage_base = epi_stage + (warp - 2) * (EPI_BUFS * EPI_TILE_BYTES);
     int local = 0;
     for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++local) {
-      const int tile = unit % num_tiles, sp = unit / num_tiles;
+      const int bz = batched ? unit / num_tiles : 0;
+      const int tile = batched ? unit - bz * num_tiles : unit % num_tiles, sp = batched ? 0 : unit / num_tiles;
       const int buf = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
@@ -336,7 +359,7 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
       tcgen05_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + buf * BN;
       const int row = m0 + quarter * 32 + lane;
-      T* crow = static_cast<T*>(g.c) + static_cast<size_t>(row) * g.N;
+      T* crow = static_cast<T*>(g.c) + (static_cast<size_t>(bz) * g.M + row) * g.N;
       int blk = 0;
 #pragma unroll 1
       for (int c0 = half * (BN / 2); c0 < (half + 1) * (BN / 2); c0 += 32, ++blk) {
@@ -384,7 +407,8 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
               fence_proxy_async_smem();
               __syncwarp();
               if (lane == 0) {
-                tma_store_2d(&tmap_c, box, col0 - 32 * in_box, m0 + quarter * 32);
+                if (batched) tma_store_3d(&tmap_c, box, col0 - 32 * in_box, m0 + quarter * 32, bz);
+                else tma_store_2d(&tmap_c, box, col0 - 32 * in_box, m0 + quarter * 32);
                 bulk_commit();
               }
             }
@@ -404,7 +428,8 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            tma_store_2d(&tmap_c, stage, col0, m0 + quarter * 32);
+            if (batched) tma_store_3d(&tmap_c, stage, col0, m0 + quarter * 32, bz);
+            else tma_store_2d(&tmap_c, stage, col0, m0 + quarter * 32);
             bulk_commit();
           }
         } else if (row < g.M) {
@@ -750,15 +775,17 @@ EncodeTiledFn encode_tiled() {
 
 // 2-D row-major matrix [rows, cols] of T, box = {box_cols (128 bytes), box_rows}, 128-byte swizzle
 // (16-byte atoms, or 32-byte atoms when `atom32`), out-of-range elements read as zero.
+// batch > 1: [batch, rows, cols] densely packed as a 3-D tensor, boxes one batch entry deep.
 template <typename T>
-CUtensorMap make_map(const void* base, size_t rows, size_t cols, uint32_t box_cols, uint32_t box_rows, bool atom32 = false) {
+CUtensorMap make_map(const void* base, size_t rows, size_t cols, uint32_t box_cols, uint32_t box_rows, bool atom32 = false,
+                     size_t batch = 1) {
   CUtensorMap map;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * sizeof(T)};
-  const cuuint32_t box[2] = {box_cols, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
+  const cuuint64_t dims[3] = {cols, rows, batch};
+  const cuuint64_t strides[2] = {cols * sizeof(T), rows * cols * sizeof(T)};
+  const cuuint32_t box[3] = {box_cols, box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  MP_CU_CHECK(encode_tiled()(&map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  MP_CU_CHECK(encode_tiled()(&map, dt, batch > 1 ? 3 : 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
@@ -768,15 +795,15 @@ CUtensorMap make_map(const void* base, size_t rows, size_t cols, uint32_t box_co
 // Row-major [rows, cols] output, box {32 cols, 32 rows} unswizzled, or (wide) {64 cols, 32 rows} of r16 in the
 // 128-byte swizzle.
 template <typename T>
-CUtensorMap make_store_map(void* base, size_t rows, size_t cols, bool wide = false) {
+CUtensorMap make_store_map(void* base, size_t rows, size_t cols, bool wide = false, size_t batch = 1) {
   CUtensorMap map;
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {cols * sizeof(T)};
-  const cuuint32_t box[2] = {wide ? 64u : 32u, 32};
+  const cuuint64_t dims[3] = {cols, rows, batch};
+  const cuuint64_t strides[2] = {cols * sizeof(T), rows * cols * sizeof(T)};
+  const cuuint32_t box[3] = {wide ? 64u : 32u, 32, 1};
   const bool swizzle = wide || sizeof(T) == 4;   // 128-byte rows: r16 wide boxes and every r32 box
-  const cuuint32_t estr[2] = {1, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = sizeof(T) == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-  MP_CU_CHECK(encode_tiled()(&map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  MP_CU_CHECK(encode_tiled()(&map, dt, batch > 1 ? 3 : 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                              swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
   return map;
@@ -788,17 +815,18 @@ void launch_tc(const T* a, const T* b, const GemmArgs& args, int sm_count, cudaS
   const int M = args.M, N = args.N, K = args.K;
   // A: K-major [M,K] box {BK, BM};  MN-major [K,M] box {BK (along M), BK (k-rows)}
   // (32-bit MN-major tiles: 128-byte swizzle with 32-byte atoms, the only MN-major layout tf32 accepts)
-  const CUtensorMap ta = args.a_mn ? make_map<T>(a, K, M, G::BK, G::BK, G::TF32) : make_map<T>(a, M, K, G::BK, BM);
-  const CUtensorMap tb = args.b_mn ? make_map<T>(b, K, N, G::BK, G::BK, G::TF32) : make_map<T>(b, N, K, G::BK, BN);
+  const size_t nb = static_cast<size_t>(args.batch);
+  const CUtensorMap ta = args.a_mn ? make_map<T>(a, K, M, G::BK, G::BK, G::TF32, nb) : make_map<T>(a, M, K, G::BK, BM, false, nb);
+  const CUtensorMap tb = args.b_mn ? make_map<T>(b, K, N, G::BK, G::BK, G::TF32, nb) : make_map<T>(b, N, K, G::BK, BN, false, nb);
   // C as a TMA store target: 32 x 32 blocks, no swizzle (only used when the row pitch is a multiple of 16 bytes)
   CUtensorMap tc = ta;
-  if ((static_cast<size_t>(N) * sizeof(T)) % 16 == 0 && mp_aligned16(args.c)) tc = make_store_map<T>(args.c, M, N, sizeof(T) == 2 && BN >= 128);
+  if ((static_cast<size_t>(N) * sizeof(T)) % 16 == 0 && mp_aligned16(args.c)) tc = make_store_map<T>(args.c, M, N, sizeof(T) == 2 && BN >= 128, nb);
   const size_t smem = static_cast<size_t>(args.stages) * stage_bytes<BN>(args.split != 0) + 1024 /*align*/ + 1024 /*barriers*/ +
                       8 * EpiBufs<T>::value * 32 * 32 * sizeof(T) /*epilogue staging*/;
   MP_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_kernel<T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(smem)));
-  const int tiles = ((N + BN - 1) / BN) * ((M + BM - 1) / BM) * args.ksplit;
-  const int grid = tiles < sm_count ? tiles : sm_count;   // persistent: one CTA per SM
+  const long tiles = static_cast<long>((N + BN - 1) / BN) * ((M + BM - 1) / BM) * args.ksplit * args.batch;
+  const int grid = tiles < sm_count ? static_cast<int>(tiles) : sm_count;   // persistent: one CTA per SM
   gemm_tcgen05_kernel<T, BN><<<grid, args.split ? GEMM_MAX_THREADS : GEMM_THREADS, smem, st>>>(ta, tb, tc, args);
   MP_LAUNCH_CHECK();
   if (args.ksplit > 1) {
@@ -841,8 +869,8 @@ bool env_flag(const char* name) {
 
 // Output-tile width: wide tiles for wide problems, narrower ones when they are
 // needed to put at least ~one CTA on every SM.
-int pick_bn(int M, int N, int sms) {
-  const long tiles_m = (M + BM - 1) / BM;
+int pick_bn(int M, int N, int sms, int batch = 1) {
+  const long tiles_m = static_cast<long>((M + BM - 1) / BM) * batch;
   if (N > 128 && tiles_m * ((N + 255) / 256) >= sms) return 256;
   if (N > 64 && tiles_m * ((N + 127) / 128) >= sms / 2) return 128;
   return N > 64 && tiles_m * ((N + 127) / 128) >= 4 ? 128 : 64;
@@ -886,9 +914,9 @@ void pick_split_k(GemmArgs& args, size_t elem, int sms, size_t workspace_bytes, 
 
 template <typename T>
 void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alpha, void* c_, double beta, len_t M, len_t N,
-                   len_t K, int a_mn, int b_mn, StreamContext ctx) {
+                   len_t K, int a_mn, int b_mn, StreamContext ctx, len_t batch = 1) {
   using A = typename Acc<T>::type;
-  if (M == 0 || N == 0) return;
+  if (M == 0 || N == 0 || batch == 0) return;
   cudaStream_t st = mp_stream(ctx);
   const T* a = static_cast<const T*>(a_);
   const T* b = static_cast<const T*>(b_);
@@ -899,13 +927,21 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
     const size_t a_pitch = (a_mn ? M : K) * sizeof(T), b_pitch = (b_mn ? N : K) * sizeof(T);
     tensor_path = mp_aligned16(a) && mp_aligned16(b) && a_pitch % 16 == 0 && b_pitch % 16 == 0 &&
                   M < (1ull << 31) && N < (1ull << 31) && K < (1ull << 31) && mp_state_or_null(ctx) != nullptr;
+    if (batch > 1) {
+      // 3-D maps: the batch pitch must keep 16-byte alignment, and the work-unit count stays in 32 bits
+      const double units = static_cast<double>((M + BM - 1) / BM) * static_cast<double>((N + 63) / 64) * static_cast<double>(batch);
+      tensor_path = tensor_path && (M * K * sizeof(T)) % 16 == 0 && (K * N * sizeof(T)) % 16 == 0 && units < 2.0e9;
+    }
   }
   if (!tensor_path) {
-    const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64));
-    if (grid.y > 65535) MP_FATAL("inner_product: M too large for the FP-pipe kernel");
-    gemm_simt_kernel<T><<<grid, 256, 0, st>>>(a, b, static_cast<const T*>(bias), static_cast<A>(alpha), c, static_cast<A>(beta),
-                                              M, N, K, a_mn, b_mn);
-    MP_LAUNCH_CHECK();
+    if ((M + 63) / 64 > 65535) MP_FATAL("inner_product: M too large for the FP-pipe kernel");
+    for (len_t b0 = 0; b0 < batch; b0 += 65535) {   // grid.z carries the batch index
+      const len_t nb = batch - b0 < 65535 ? batch - b0 : 65535;
+      const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64), static_cast<unsigned>(nb));
+      gemm_simt_kernel<T><<<grid, 256, 0, st>>>(a + b0 * M * K, b + b0 * K * N, static_cast<const T*>(bias), static_cast<A>(alpha),
+                                                c + b0 * M * N, static_cast<A>(beta), M, N, K, a_mn, b_mn);
+      MP_LAUNCH_CHECK();
+    }
     return;
   }
   if constexpr (!std::is_same<T, double>::value) {
@@ -922,10 +958,11 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
     args.b_mn = b_mn;
     args.split = (std::is_same<T, float>::value && !env_flag("MP_GEMM_TF32X1")) ? 1 : 0;
     args.status = state->status_dev;
-    int bn = pick_bn(args.M, args.N, state->sm_count);
+    args.batch = static_cast<int>(batch);
+    int bn = pick_bn(args.M, args.N, state->sm_count, args.batch);
     args.ksplit = 1;
     args.partial = static_cast<float*>(state->workspace);
-    if (!env_flag("MP_GEMM_NO_SPLITK")) pick_split_k(args, sizeof(T), state->sm_count, state->workspace_bytes, &bn);
+    if (batch == 1 && !env_flag("MP_GEMM_NO_SPLITK")) pick_split_k(args, sizeof(T), state->sm_count, state->workspace_bytes, &bn);
     // shared memory of the ring: 227 KB per CTA minus alignment slack, barriers and the epilogue staging (r16: 64 KB, r32: 32 KB)
     const int budget = (sizeof(T) == 2 ? 159 : 168) * 1024;
     auto stages_for = [&](int per_stage) {   // the ring runs across tiles, so depth is bounded by memory only
@@ -936,7 +973,7 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
     if constexpr (std::is_same<T, __half>::value) {
       // CTA pairs for wide problems with enough 256 x 256 tiles to fill the pairs
       const long pair_tiles = static_cast<long>((args.M + 255) / 256) * ((args.N + 255) / 256);
-      if (!env_flag("MP_GEMM_NO_PAIRS") && args.M >= 256 && args.N >= 256) {
+      if (batch == 1 && !env_flag("MP_GEMM_NO_PAIRS") && args.M >= 256 && args.N >= 256) {
         if (args.ksplit == 1 && bn == 256 && pair_tiles >= state->sm_count / 2) {
           launch_pair(a, b, args, state->sm_count, st);
           return;
@@ -990,6 +1027,26 @@ static void linear_ij_jk_ik_impl(const void* a, const void* b, const void* bias,
   gemm_dispatch<T>(a, b, bias, alpha, c, beta, m, k, n, 0, 1, ctx);
 }
 
+// Batched forms ("_ij,_jk->_ik" of the reference's roadmap, NOTES.md:18): densely packed [batch, ., .] operands.
+template <typename T>
+static void inner_product_bij_bjk_bik_impl(const void* a, const void* b, double alpha, void* c, double beta, len_t batch, len_t m,
+                                           len_t n, len_t k, StreamContext ctx) {
+  gemm_dispatch<T>(a, b, nullptr, alpha, c, beta, m, k, n, 0, 1, ctx, batch);
+}
+template <typename T>
+static void inner_product_bij_bkj_bik_impl(const void* a, const void* b, double alpha, void* c, double beta, len_t batch, len_t m,
+                                           len_t n, len_t k, StreamContext ctx) {
+  gemm_dispatch<T>(a, b, nullptr, alpha, c, beta, m, k, n, 0, 0, ctx, batch);
+}
+template <typename T>
+static void inner_product_bji_bjk_bik_impl(const void* a, const void* b, double alpha, void* c, double beta, len_t batch, len_t m,
+                                           len_t n, len_t k, StreamContext ctx) {
+  gemm_dispatch<T>(a, b, nullptr, alpha, c, beta, m, k, n, 1, 1, ctx, batch);
+}
+
+MP_STAMP3(inner_product_bij_bjk_bik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t batch, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, batch, m, n, k, s))
+MP_STAMP3(inner_product_bij_bkj_bik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t batch, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, batch, m, n, k, s))
+MP_STAMP3(inner_product_bji_bjk_bik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t batch, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, batch, m, n, k, s))
 MP_STAMP3(inner_product_ij_jk_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))
 MP_STAMP3(inner_product_ij_kj_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))
 MP_STAMP3(inner_product_ji_jk_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))

@@ -29,6 +29,21 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
                : "memory");
 }
 
+// 3-D forms (x, y as above, z = batch index): the tile in shared memory has the 2-D layout.
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* map, int x, int y, int z, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(
+          mp_smem_u32(smem_dst)),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(mp_smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* smem_src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(map)),
+               "r"(mp_smem_u32(smem_src)), "r"(x), "r"(y), "r"(z)
+               : "memory");
+}
+
 // ------------------------------ TMEM ---------------------------------------
 // Executed by ONE full warp.  ncols: power of two in [32, 512].  The base
 // address is written to *smem_slot.

@@ -9,6 +9,7 @@
 #include <cstring>
 #include <limits>
 #include <set>
+#include <string>
 
 namespace mp {
 
@@ -31,6 +32,10 @@ static const Blend2 reduce_ij_i[3] = MP_KERNELS(reduce_ij_i), reduce_ij_j[3] = M
                     permutate_ij_ji[3] = MP_KERNELS(permutate_ij_ji);
 static const Gemm ip_ij_jk_ik[3] = MP_KERNELS(inner_product_ij_jk_ik), ip_ij_kj_ik[3] = MP_KERNELS(inner_product_ij_kj_ik),
                   ip_ji_jk_ik[3] = MP_KERNELS(inner_product_ji_jk_ik);
+using GemmB = void (*)(const void*, const void*, const double, void*, const double, len_t, len_t, len_t, len_t, StreamContext);
+static const GemmB ip_bij_bjk_bik[3] = MP_KERNELS(inner_product_bij_bjk_bik), ip_bij_bkj_bik[3] = MP_KERNELS(inner_product_bij_bkj_bik),
+                   ip_bji_bjk_bik[3] = MP_KERNELS(inner_product_bji_bjk_bik);
+static void (*const permutate[3])(const void*, void*, double, const len_t*, const len_t*, len_t, StreamContext) = MP_KERNELS(permutate);
 static void (*const fill[3])(void*, double, len_t, StreamContext) = MP_KERNELS(fill);
 static void (*const sequence[3])(void*, double, double, len_t, StreamContext) = MP_KERNELS(sequence);
 static void (*const linear[3])(const void*, const void*, const void*, const double, void*, const double, len_t, len_t, len_t,
@@ -41,6 +46,7 @@ static void (*const rmsnorm[3])(const void*, const void*, double, void*, void*, 
 static void (*const rmsnorm_reverse[3])(const void*, const void*, const void*, const void*, double, void*, void*, double, void*,
                                         len_t, len_t, StreamContext) = MP_KERNELS(rmsnorm_ij_j_reverse);
 static void (*const sgd[3])(void*, const void*, double, double, double, len_t, StreamContext) = MP_KERNELS(sgd);
+static void (*const momentum[3])(void*, const void*, void*, double, double, double, double, len_t, StreamContext) = MP_KERNELS(momentum);
 static void (*const adam[3])(void*, const void*, void*, void*, double, double, double, double, double, len_t, len_t,
                              StreamContext) = MP_KERNELS(adam);
 }  // namespace kernels
@@ -190,6 +196,44 @@ void Graph::free_tensor(Tensor t) {
     b.data[t.idx] = nullptr;
   }
   b.len[t.idx] = 0;
+}
+
+static std::string weight_path(const std::string& dir, const std::string& prefix, size_t k) {
+  return dir + "/" + prefix + "_" + std::to_string(k);
+}
+void Graph::save(const std::string& dir, const std::string& prefix) {
+  std::vector<unsigned char> host;
+  size_t k = 0;
+  for (size_t i = 0; i < leaf_block.data.size(); ++i) {
+    if (leaf_block.cls[i] != Class::wgt) continue;
+    const size_t bytes = leaf_block.len[i] * dtype_size(leaf_block.dtype[i]);
+    if (bytes == 0) panic("Graph.save: a weight has no data");
+    host.resize(bytes);
+    mpMemcpyDtoH(host.data(), leaf_block.data[i], bytes, stream.context);
+    mpStreamSynchronize(stream.context);
+    std::FILE* f = std::fopen(weight_path(dir, prefix, k).c_str(), "wb");
+    if (f == nullptr || std::fwrite(host.data(), 1, bytes, f) != bytes) panic("Failed to save tensor data.");
+    std::fclose(f);
+    ++k;
+  }
+}
+void Graph::load(const std::string& dir, const std::string& prefix) {
+  std::vector<unsigned char> host;
+  size_t k = 0;
+  for (size_t i = 0; i < leaf_block.data.size(); ++i) {
+    if (leaf_block.cls[i] != Class::wgt) continue;
+    const size_t bytes = leaf_block.len[i] * dtype_size(leaf_block.dtype[i]);
+    if (bytes == 0) panic("Graph.load: a weight has no data");
+    host.resize(bytes + 1);
+    std::FILE* f = std::fopen(weight_path(dir, prefix, k).c_str(), "rb");
+    if (f == nullptr) panic("Failed to load tensor data.");
+    const size_t got = std::fread(host.data(), 1, bytes + 1, f);   // one byte more: a longer file is also a mismatch
+    std::fclose(f);
+    if (got != bytes) panic("Failed to load tensor data (wrong byte count).");
+    mpMemcpyHtoD(leaf_block.data[i], host.data(), bytes, stream.context);
+    mpStreamSynchronize(stream.context);
+    ++k;
+  }
 }
 
 void Graph::reset(ResetGroup group, ResetComponent component) {
@@ -435,39 +479,100 @@ Tensor broadcast(Tensor x, const std::vector<size_t>& sizes, const std::string& 
   return y;
 }
 
-// --- permutate (permutate.zig:39-104) ---
+// --- permutate (permutate.zig:39-104; grammar expression_parsing.zig:205-255) ---
+// "ijk->kij": both sides lower-case letters, each used once, the right side a permutation of the left.
+// perm[i] = position of the i-th left letter on the right (`permutateSizes`).
+std::vector<size_t> permutation_of(const std::string& expr) {
+  const size_t arrow = expr.find("->");
+  if (arrow == std::string::npos) panic("permutate: expression has no \"->\"");
+  const std::string lhs = expr.substr(0, arrow), rhs = expr.substr(arrow + 2);
+  if (lhs.empty() || lhs.size() != rhs.size()) panic("permutate: both sides must name the same indices");
+  std::vector<size_t> perm(lhs.size());
+  for (size_t i = 0; i < lhs.size(); ++i) {
+    if (lhs[i] < 'a' || lhs[i] > 'z' || rhs[i] < 'a' || rhs[i] > 'z') panic("permutate: tensor indices must be lower case characters");
+    if (lhs.find(lhs[i]) != i || rhs.find(rhs[i]) != i) panic("permutate: an index appears twice");
+    const size_t j = rhs.find(lhs[i]);
+    if (j == std::string::npos) panic("permutate: left and right operands must be permutations of each other");
+    perm[i] = j;
+  }
+  return perm;
+}
+static void launch_permutate(Tensor src_t, const void* src, void* dst, double alpha, const std::vector<size_t>& sizes,
+                             const std::vector<size_t>& perm) {
+  len_t sz[8], pm[8];
+  if (sizes.size() > 6) panic("permutate: rank above 6");
+  for (size_t i = 0; i < sizes.size(); ++i) { sz[i] = sizes[i]; pm[i] = perm[i]; }
+  kernels::permutate[dkey(src_t)](src, dst, alpha, sz, pm, sizes.size(), src_t.context());
+}
+// the gradient flows back through the inverse permutation (for "ij->ji" that is the permutation itself, the
+// only case permutate.zig:62-72 handles), accumulated into x.grad
 static void permutate_rev(const std::vector<OpDatum>& a) {
   Tensor x = a[0].tensor, y = a[1].tensor;
   enable_gradient(x);
-  const auto& s = y.sizes();
-  kernels::permutate_ij_ji[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+  const std::vector<size_t> perm = permutation_of(a[2].expr);
+  if (perm.size() == 2 && perm[0] == 1) {
+    const auto& s = y.sizes();
+    kernels::permutate_ij_ji[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+    return;
+  }
+  std::vector<size_t> inverse(perm.size());
+  for (size_t i = 0; i < perm.size(); ++i) inverse[perm[i]] = i;
+  launch_permutate(y, y.grad_ptr(), x.grad_ptr(), 1.0, y.sizes(), inverse);
 }
 Tensor permutate(Tensor x, const std::string& expr) {
-  if (expr != "ij->ji" || x.sizes().size() != 2) panic("permutate: only \"ij->ji\" on rank-2 tensors");
-  Graph* g = x.ptr;
+  const std::vector<size_t> perm = permutation_of(expr);
   const auto& s = x.sizes();
-  Tensor y = g->tensor({Class::hid, x.dtype(), {s[1], s[0]}});
-  kernels::permutate_ij_ji[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
-  if (g->mode == Mode::train) attach_op(permutate_rev, y, {OpDatum::of(x), OpDatum::of(y)});
+  if (perm.size() != s.size()) panic("permutate: the expression's rank differs from the tensor's");
+  Graph* g = x.ptr;
+  std::vector<size_t> out(s.size());
+  for (size_t i = 0; i < s.size(); ++i) out[perm[i]] = s[i];
+  Tensor y = g->tensor({Class::hid, x.dtype(), out});
+  if (perm.size() == 2 && perm[0] == 1) kernels::permutate_ij_ji[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
+  else launch_permutate(x, x.data_ptr(), y.data_ptr(), 0.0, s, perm);
+  if (g->mode == Mode::train) attach_op(permutate_rev, y, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(expr)});
   return y;
 }
 
 // --- inner product (inner_product.zig:116-122 expression map, :163-419 variants and reverses) ---
 // Logical shape of the contraction "lhs,rhs->out" as C[m,k] = op(A)[m,n] op(B)[n,k].
-struct Contraction { len_t m, n, k; int kind; };   // kind: 0 = ij,jk  1 = ij,kj  2 = ji,jk
-static Contraction parse_contraction(Tensor x, Tensor y, const std::string& e, std::vector<size_t>& out_sizes) {
+struct Contraction { len_t m, n, k; int kind; len_t batch; };   // kind: 0 = ij,jk  1 = ij,kj  2 = ji,jk;  batch 0 = rank-2 form
+// A leading index shared by all three operands is a batch index ("bij,bjk->bik"); written as '_' it is optional
+// ("_ij,_jk->_ik", NOTES.md:18): present for rank-3 operands, absent for rank-2 ones.
+static Contraction parse_contraction(Tensor x, Tensor y, const std::string& expr, std::vector<size_t>& out_sizes) {
   const auto& xs = x.sizes(); const auto& ys = y.sizes();
+  std::string e = expr;
+  len_t batch = 0;
+  size_t o = 0;   // offset of the matrix dimensions in the operands' sizes
+  const size_t comma = e.find(','), arrow = e.find("->");
+  if (comma != std::string::npos && arrow != std::string::npos && comma == 3 && arrow == 7 && e.size() == 12 && e[0] == e[4] &&
+      e[0] == e[9] && e.find(e[0], 1) == 4) {
+    const bool optional = e[0] == '_';
+    e = e.substr(1, 2) + "," + e.substr(5, 2) + "->" + e.substr(10, 2);
+    if (!(optional && xs.size() == 2 && ys.size() == 2)) {
+      if (xs.size() != 3 || ys.size() != 3) panic("inner_product: a batched expression needs rank-3 operands");
+      if (xs[0] != ys[0]) panic("inner_product: batch sizes differ");
+      batch = xs[0];
+      o = 1;
+    }
+  }
   Contraction c{};
-  if (e == "ij,jk->ik") { c = {xs[0], xs[1], ys[1], 0}; if (xs[1] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {xs[0], ys[1]}; }
-  else if (e == "ij,kj->ik") { c = {xs[0], xs[1], ys[0], 1}; if (xs[1] != ys[1]) panic("inner_product: inner sizes differ"); out_sizes = {xs[0], ys[0]}; }
-  else if (e == "ji,jk->ik") { c = {xs[1], xs[0], ys[1], 2}; if (xs[0] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {xs[1], ys[1]}; }
-  else if (e == "i,ij->j") { c = {1, xs[0], ys[1], 0}; if (xs[0] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {ys[1]}; }
-  else if (e == "ij,j->i") { c = {xs[0], xs[1], 1, 0}; if (xs[1] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {xs[0]}; }
+  if (e == "ij,jk->ik") { c = {xs[o], xs[o + 1], ys[o + 1], 0, batch}; if (xs[o + 1] != ys[o]) panic("inner_product: inner sizes differ"); out_sizes = {xs[o], ys[o + 1]}; }
+  else if (e == "ij,kj->ik") { c = {xs[o], xs[o + 1], ys[o], 1, batch}; if (xs[o + 1] != ys[o + 1]) panic("inner_product: inner sizes differ"); out_sizes = {xs[o], ys[o]}; }
+  else if (e == "ji,jk->ik") { c = {xs[o + 1], xs[o], ys[o + 1], 2, batch}; if (xs[o] != ys[o]) panic("inner_product: inner sizes differ"); out_sizes = {xs[o + 1], ys[o + 1]}; }
+  else if (o == 0 && e == "i,ij->j") { c = {1, xs[0], ys[1], 0, 0}; if (xs[0] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {ys[1]}; }
+  else if (o == 0 && e == "ij,j->i") { c = {xs[0], xs[1], 1, 0, 0}; if (xs[1] != ys[0]) panic("inner_product: inner sizes differ"); out_sizes = {xs[0]}; }
   else panic("inner_product: unknown expression");
+  if (o == 1) out_sizes.insert(out_sizes.begin(), static_cast<size_t>(batch));
   return c;
 }
 static void gemm(int key, int kind, const void* a, const void* b, double alpha, void* c, double beta, len_t m, len_t n, len_t k,
-                 StreamContext ctx) {
+                 StreamContext ctx, len_t batch = 0) {
+  if (batch != 0) {
+    if (kind == 0) kernels::ip_bij_bjk_bik[key](a, b, alpha, c, beta, batch, m, n, k, ctx);
+    else if (kind == 1) kernels::ip_bij_bkj_bik[key](a, b, alpha, c, beta, batch, m, n, k, ctx);
+    else kernels::ip_bji_bjk_bik[key](a, b, alpha, c, beta, batch, m, n, k, ctx);
+    return;
+  }
   if (kind == 0) kernels::ip_ij_jk_ik[key](a, b, alpha, c, beta, m, n, k, ctx);
   else if (kind == 1) kernels::ip_ij_kj_ik[key](a, b, alpha, c, beta, m, n, k, ctx);
   else kernels::ip_ji_jk_ik[key](a, b, alpha, c, beta, m, n, k, ctx);
@@ -483,14 +588,14 @@ static void inner_product_rev(const std::vector<OpDatum>& a) {
   const void* G = z.grad_ptr();
   // Z = op(X) op(Y):  dX and dY as native transposed-operand contractions, accumulated (beta = 1)
   if (c.kind == 0) {          // Z = X Y: dX = G Y^T (ij,kj), dY = X^T G (ji,jk)
-    gemm(key, 1, G, y.data_ptr(), scale, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx);
-    gemm(key, 2, x.data_ptr(), G, scale, y.grad_ptr(), 1.0, c.n, c.m, c.k, ctx);
+    gemm(key, 1, G, y.data_ptr(), scale, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx, c.batch);
+    gemm(key, 2, x.data_ptr(), G, scale, y.grad_ptr(), 1.0, c.n, c.m, c.k, ctx, c.batch);
   } else if (c.kind == 1) {   // Z = X Y^T: dX = G Y (ij,jk), dY = G^T X (ji,jk)
-    gemm(key, 0, G, y.data_ptr(), scale, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx);
-    gemm(key, 2, G, x.data_ptr(), scale, y.grad_ptr(), 1.0, c.k, c.m, c.n, ctx);
+    gemm(key, 0, G, y.data_ptr(), scale, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx, c.batch);
+    gemm(key, 2, G, x.data_ptr(), scale, y.grad_ptr(), 1.0, c.k, c.m, c.n, ctx, c.batch);
   } else {                    // Z = X^T Y: dX = Y G^T (ij,kj), dY = X G (ij,jk)
-    gemm(key, 1, y.data_ptr(), G, scale, x.grad_ptr(), 1.0, c.n, c.k, c.m, ctx);
-    gemm(key, 0, x.data_ptr(), G, scale, y.grad_ptr(), 1.0, c.n, c.m, c.k, ctx);
+    gemm(key, 1, y.data_ptr(), G, scale, x.grad_ptr(), 1.0, c.n, c.k, c.m, ctx, c.batch);
+    gemm(key, 0, x.data_ptr(), G, scale, y.grad_ptr(), 1.0, c.n, c.m, c.k, ctx, c.batch);
   }
 }
 Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string& expr) {
@@ -499,7 +604,7 @@ Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string&
   std::vector<size_t> out_sizes;
   const Contraction c = parse_contraction(x, y, expr, out_sizes);
   Tensor z = g->tensor({Class::hid, x.dtype(), out_sizes});
-  gemm(dkey(z), c.kind, x.data_ptr(), y.data_ptr(), scale, z.data_ptr(), 0.0, c.m, c.n, c.k, z.context());
+  gemm(dkey(z), c.kind, x.data_ptr(), y.data_ptr(), scale, z.data_ptr(), 0.0, c.m, c.n, c.k, z.context(), c.batch);
   if (g->mode == Mode::train)
     attach_op(inner_product_rev, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(scale), OpDatum::of(expr), OpDatum::of(z)});
   return z;
@@ -578,6 +683,28 @@ void SGD::update(Graph* graph) {
     kernels::sgd[static_cast<int>(b.dtype[i])](b.data[i], b.grad[i], rate, clip.lower, clip.upper, b.len[i], graph->stream.context);
   }
   mpStreamSynchronize(graph->stream.context);   // the reference synchronises each active stream once
+}
+
+void Momentum::update(Graph* graph) {
+  if (!(alpha > 0.0 && alpha < 1.0)) panic("Momentum: alpha must lie in (0, 1)");
+  Graph::Block& b = graph->leaf_block;
+  for (size_t i = 0; i < b.data.size(); ++i) {
+    if (b.cls[i] != Class::wgt || b.grad[i] == nullptr || b.len[i] == 0) continue;
+    const int key = static_cast<int>(b.dtype[i]);
+    auto k = std::make_pair(graph, i);
+    auto it = state.find(k);
+    if (it == state.end()) {   // optimizer.zig:249-256: allocated and zero-filled on first use
+      void* m = mpMemAlloc(b.len[i] * dtype_size(b.dtype[i]), graph->stream.context);
+      kernels::fill[key](m, 0.0, b.len[i], graph->stream.context);
+      it = state.emplace(k, m).first;
+    }
+    kernels::momentum[key](b.data[i], b.grad[i], it->second, rate, alpha, clip.lower, clip.upper, b.len[i], graph->stream.context);
+  }
+  mpStreamSynchronize(graph->stream.context);
+}
+void Momentum::deinit(Stream stream) {   // optimizer.zig:211-218
+  for (auto& kv : state) mpMemFree(kv.second, stream.context);
+  state.clear();
 }
 
 void Adam::update(Graph* graph) {

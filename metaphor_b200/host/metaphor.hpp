@@ -98,6 +98,10 @@ class Graph {
   void deinit();                                // graph.zig:350-369
   Tensor tensor(const TensorConfig& cfg);       // graph.zig:500-520
   void reset(ResetGroup group, ResetComponent component);   // graph.zig:371-414
+  // Weights as raw bytes, one file "<dir>/<prefix>_<k>" per weight, k counting the weights in leaf order
+  // (graph.zig:633-703, tensor_file.zig:36-40,56-86).  load panics when a file's size differs from the tensor's.
+  void save(const std::string& dir, const std::string& prefix);
+  void load(const std::string& dir, const std::string& prefix);
   Mode mode;
   Stream stream;
 
@@ -147,11 +151,13 @@ Tensor relu(Tensor x);
 Tensor selu(Tensor x);
 Tensor reduce(Tensor x, const std::string& expr);                       // "ij->i", "ij->j"
 Tensor broadcast(Tensor x, const std::vector<size_t>& sizes, const std::string& expr);   // "i->ij", "j->ij"
-Tensor inner_product(Tensor x, Tensor y, const std::string& expr);      // "ij,jk->ik", "ij,kj->ik", "ji,jk->ik", "i,ij->j", "ij,j->i"
+Tensor inner_product(Tensor x, Tensor y, const std::string& expr);      // "ij,jk->ik", "ij,kj->ik", "ji,jk->ik", "i,ij->j", "ij,j->i";
+                                                                        // batched "bij,bjk->bik" (and the kj / ji forms), "_ij,_jk->_ik" = optional batch
 Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string& expr);
 inline Tensor innerProduct(Tensor x, Tensor y, const std::string& e) { return inner_product(x, y, e); }
 Tensor linear(Tensor x, Tensor A, Tensor b, const std::string& expr);   // "ij,jk->ik", "i,ij->j"
-Tensor permutate(Tensor x, const std::string& expr);                    // "ij->ji"
+Tensor permutate(Tensor x, const std::string& expr);                    // any permutation up to rank 6: "ij->ji", "ijk->kij", ...
+std::vector<size_t> permutation_of(const std::string& expr);            // perm[i] = position of the i-th left index on the right
 Tensor softmax(Tensor x);                                               // over the last axis ("ij|j")
 Tensor rmsnorm(Tensor x, Tensor gain, double eps);
 }
@@ -162,6 +168,13 @@ struct SGD {
   double rate;
   ClipRange clip;
   void update(Graph* graph);
+};
+struct Momentum {           // optimizer.zig:182-275: m = alpha*m + clip(g); w -= rate*m; state per (graph, weight), zero on first use
+  double rate, alpha = 0.90;
+  ClipRange clip;
+  std::map<std::pair<Graph*, size_t>, void*> state;
+  void update(Graph* graph);
+  void deinit(Stream stream);
 };
 struct Adam {
   double rate, beta1 = 0.9, beta2 = 0.999, eps = 1e-8, grad_scale = 1.0;

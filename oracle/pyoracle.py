@@ -147,6 +147,23 @@ def permutate_ij_ji(src, dst=None, alpha=0.0):
     _call("orc_permutate_ij_ji", src, src, dst, float(alpha), row, col); return dst
 
 
+def permutate(src, perm, dst=None, alpha=0.0):
+    """dst = permute(src) + alpha*dst; perm[i] = output position of source dimension i."""
+    perm = [int(q) for q in perm]
+    out_shape = [0] * src.ndim
+    for i, q in enumerate(perm):
+        out_shape[q] = src.shape[i]
+    if dst is None:
+        dst = np.zeros(out_shape, dtype=src.dtype)
+    assert list(dst.shape) == out_shape
+    sizes = (C.c_size_t * src.ndim)(*src.shape)
+    pm = (C.c_size_t * src.ndim)(*perm)
+    fn = getattr(lib(), f"orc_permutate_{_sfx(src)}")
+    fn.restype = None
+    fn(_p(src), _p(dst), C.c_double(alpha), sizes, pm, C.c_size_t(src.ndim))
+    return dst
+
+
 def reduce_ij_i(src, dst=None, alpha=0.0):
     m, n = src.shape
     if dst is None:
@@ -184,6 +201,15 @@ def inner_product(a, b, alpha=1.0, c=None, beta=0.0, ta=False, tb=False, bias=No
     fn(_p(a), _p(b), _p(bias), C.c_double(alpha), _p(c), C.c_double(beta),
        C.c_size_t(m), C.c_size_t(n), C.c_size_t(k), C.c_int(int(ta)), C.c_int(int(tb)))
     return c
+
+
+def inner_product_batched(a, b, alpha=1.0, c=None, beta=0.0, ta=False, tb=False):
+    """One rank-2 contraction (orc_inner_product) per leading batch entry."""
+    outs = []
+    for q in range(a.shape[0]):
+        cq = None if c is None else np.ascontiguousarray(c[q])
+        outs.append(inner_product(np.ascontiguousarray(a[q]), np.ascontiguousarray(b[q]), alpha, cq, beta, ta=ta, tb=tb))
+    return np.stack(outs) if outs else np.zeros((0,) + ((a.shape[2] if ta else a.shape[1]), (b.shape[1] if tb else b.shape[2])), a.dtype)
 
 
 # ---- row-wise ----------------------------------------------------------------

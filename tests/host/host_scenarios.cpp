@@ -2,13 +2,14 @@
 // programs (src/examples/subgraphs.zig, src/examples/experimental.zig) and the
 // README feed-forward block (README.md:90-104) on the GPU, with numeric checks
 // against the CPU oracle (liboracle.so; test infrastructure).
-// Usage: host_scenarios [timing-iterations]; exit code 0 = all checks passed.
+// Usage: host_scenarios [timing-iterations [directory for weight files]]; exit code 0 = all checks passed.
 #include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <random>
+#include <string>
 #include <vector>
 
 #include "../../metaphor_b200/host/metaphor.hpp"
@@ -23,6 +24,8 @@ void orc_softmax_ij_j_f32(const float*, float*, size_t, size_t);
 void orc_softmax_ij_j_reverse_f32(const float*, const float*, float*, double, size_t, size_t);
 void orc_rmsnorm_ij_j_f32(const float*, const float*, double, float*, float*, size_t, size_t);
 void orc_rmsnorm_ij_j_reverse_f32(const float*, const float*, const float*, double, float*, float*, double, size_t, size_t);
+void orc_momentum_f32(float*, const float*, float*, double, double, double, double, size_t);
+void orc_permutate_f32(const float*, float*, double, const size_t*, const size_t*, size_t);
 }
 
 static int failures = 0;
@@ -194,6 +197,93 @@ static void scenario_row_ops(mp::Stream stream) {
   G->deinit();
 }
 
+// Rank-3 operators of the reference's roadmap (NOTES.md:3-5 general permutation, NOTES.md:18 "_ij,_jk->_ik")
+static void scenario_rank3(mp::Stream stream) {
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  // y = permute(x, "ijk->kij"), loss = sum(y o w): x.grad is w carried back through the inverse permutation
+  const size_t sizes[3] = {2, 3, 4};
+  mp::Tensor x = G->tensor({mp::Class::wgt, mp::Dtype::r32, {2, 3, 4}});
+  mp::Tensor w = G->tensor({mp::Class::wgt, mp::Dtype::r32, {4, 2, 3}});
+  mp::algo::sequence(x, 1.0, 1.0); mp::algo::sequence(w, 0.5, 0.25);
+  CHECK((mp::ops::permutation_of("ijk->kij") == std::vector<size_t>{1, 2, 0}));
+  mp::Tensor y = mp::ops::permutate(x, "ijk->kij");
+  CHECK((y.sizes() == std::vector<size_t>{4, 2, 3}));
+  std::vector<float> hx(24), hw(24), ref(24), gref(24, 0.f);
+  for (int i = 0; i < 24; ++i) { hx[i] = 1.f + i; hw[i] = 0.5f + 0.25f * i; }
+  const size_t perm[3] = {1, 2, 0}, out_sizes[3] = {4, 2, 3}, inverse[3] = {2, 0, 1};
+  orc_permutate_f32(hx.data(), ref.data(), 0.0, sizes, perm, 3);
+  CHECK(rel_err(y.native(), ref) == 0.0);
+  mp::Tensor z = mp::ops::hadamard(y, w);
+  z.reverse(mp::ReverseCleanup::keep);
+  orc_permutate_f32(hw.data(), gref.data(), 1.0, out_sizes, inverse, 3);   // accumulated into a zeroed gradient
+  CHECK(rel_err(x.native_grad(), gref) == 0.0);
+
+  // batched contraction and its reverse, every entry against the rank-2 oracle
+  const size_t nb = 3, m = 5, n = 7, k = 4;
+  std::vector<float> ha = normal(nb * m * n, 21, 1.f), hb = normal(nb * n * k, 22, 0.4f);
+  mp::Tensor a = G->tensor({mp::Class::wgt, mp::Dtype::r32, {nb, m, n}});
+  mp::Tensor b = G->tensor({mp::Class::wgt, mp::Dtype::r32, {nb, n, k}});
+  upload(a, ha); upload(b, hb);
+  mp::Tensor c = mp::ops::inner_product(a, b, "bij,bjk->bik");
+  CHECK((c.sizes() == std::vector<size_t>{nb, m, k}));
+  std::vector<float> rc(nb * m * k), ga(nb * m * n, 0.f), gb(nb * n * k, 0.f), ones(m * k, 1.f);
+  for (size_t q = 0; q < nb; ++q) {
+    orc_inner_product_f32(&ha[q * m * n], &hb[q * n * k], nullptr, 1.0, &rc[q * m * k], 0.0, m, n, k, 0, 0);
+    orc_inner_product_f32(ones.data(), &hb[q * n * k], nullptr, 1.0, &ga[q * m * n], 1.0, m, k, n, 0, 1);   // dA = G B^T
+    orc_inner_product_f32(&ha[q * m * n], ones.data(), nullptr, 1.0, &gb[q * n * k], 1.0, n, m, k, 1, 0);   // dB = A^T G
+  }
+  CHECK(rel_err(c.native(), rc) <= 1e-4);
+  c.reverse(mp::ReverseCleanup::keep);
+  CHECK(rel_err(a.native_grad(), ga) <= 1e-4);
+  CHECK(rel_err(b.native_grad(), gb) <= 1e-4);
+  // the optional batch index: rank-3 operands take the batched kernel, rank-2 operands the plain one
+  mp::Tensor c3 = mp::ops::inner_product(a, b, "_ij,_jk->_ik");
+  CHECK(rel_err(c3.native(), rc) <= 1e-4);
+  mp::Tensor x2 = G->tensor({mp::Class::inp, mp::Dtype::r32, {3, 2}});
+  mp::Tensor y2 = G->tensor({mp::Class::inp, mp::Dtype::r32, {2, 2}});
+  mp::algo::sequence(x2, 1.0, 1.0); mp::algo::sequence(y2, 1.0, 1.0);
+  CHECK((mp::ops::inner_product(x2, y2, "_ij,_jk->_ik").native() == std::vector<double>{7, 10, 15, 22, 23, 34}));
+  mp::device::check();
+  G->deinit();
+}
+
+// Momentum steps (optimizer.zig:182-275) and weight files (graph.zig:633-703): train two steps, save, perturb,
+// load, and compare with the oracle's two steps
+static void scenario_momentum_and_weight_files(mp::Stream stream, const char* dir) {
+  const size_t m = 6, n = 10;
+  std::vector<float> hw = normal(m * n, 31, 1.f), hx = normal(m * n, 32, 1.f), mom(m * n, 0.f);
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  mp::Tensor x = G->tensor({mp::Class::inp, mp::Dtype::r32, {m, n}});
+  mp::Tensor w = G->tensor({mp::Class::wgt, mp::Dtype::r32, {m, n}});
+  mp::Tensor bias = G->tensor({mp::Class::wgt, mp::Dtype::r64, {n}});   // a second weight of another dtype: file index 1
+  upload(x, hx); upload(w, hw); mp::algo::sequence(bias, 0.0, 0.5);
+  mp::optm::Momentum opt{0.1, 0.9, mp::optm::ClipRange(-0.5, 0.5), {}};
+  for (int step = 0; step < 2; ++step) {
+    mp::Tensor z = mp::ops::hadamard(x, w);       // d(sum z)/dw = x
+    z.reverse(mp::ReverseCleanup::free);
+    opt.update(G);
+    orc_momentum_f32(hw.data(), hx.data(), mom.data(), 0.1, 0.9, -0.5, 0.5, m * n);
+    G->reset(mp::ResetGroup::leaf, mp::ResetComponent::grd);
+    G->reset(mp::ResetGroup::node, mp::ResetComponent::all);
+  }
+  CHECK(rel_err(w.native(), hw) <= 1e-6);
+  G->save(dir, "scenario");
+  const std::vector<double> saved = w.native(), saved_bias = bias.native();
+  mp::algo::fill(w, -7.0); mp::algo::fill(bias, 3.0);
+  G->load(dir, "scenario");
+  CHECK(w.native() == saved);
+  CHECK(bias.native() == saved_bias);
+  std::FILE* f = std::fopen((std::string(dir) + "/scenario_0").c_str(), "rb");
+  CHECK(f != nullptr);
+  if (f) { std::fseek(f, 0, SEEK_END); CHECK(std::ftell(f) == static_cast<long>(m * n * 4)); std::fclose(f); }
+  f = std::fopen((std::string(dir) + "/scenario_1").c_str(), "rb");
+  CHECK(f != nullptr);
+  if (f) { std::fseek(f, 0, SEEK_END); CHECK(std::ftell(f) == static_cast<long>(n * 8)); std::fclose(f); }
+  opt.deinit(stream);
+  mp::device::check();
+  G->deinit();
+}
+
 int main(int argc, char** argv) {
   const int timing_iters = argc > 1 ? std::atoi(argv[1]) : 0;
   mp::device::init(0);
@@ -203,6 +293,8 @@ int main(int argc, char** argv) {
   scenario_experimental(s);
   scenario_feed_forward(s, timing_iters);
   scenario_row_ops(s);
+  scenario_rank3(s);
+  scenario_momentum_and_weight_files(s, argc > 2 ? argv[2] : "/tmp");
   mp::stream::deinit(s);
   std::printf(failures == 0 ? "ALL SCENARIOS PASSED\n" : "%d CHECKS FAILED\n", failures);
   return failures == 0 ? 0 : 1;

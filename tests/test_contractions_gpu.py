@@ -53,6 +53,48 @@ def test_linear_adds_bias_in_the_epilogue(mp, stream, orc, sfx, shape):
     assert_close(host(c), narrow(ref, sfx), TOL_RED[sfx], f"linear {sfx} {shape}")
 
 
+BATCHED = [("inner_product_bij_bjk_bik", False, False), ("inner_product_bij_bkj_bik", False, True),
+           ("inner_product_bji_bjk_bik", True, False)]
+# (batch, m, n, k): tiles cut at the edges of every batch entry, one entry, odd pitches (FP-pipe kernel), deep n
+BATCHED_SHAPES = [(3, 129, 72, 200), (1, 64, 64, 64), (5, 7, 3, 5), (16, 128, 64, 128), (4, 100, 1000, 24), (2, 300, 40, 264),
+                  (6, 33, 8, 8)]
+
+
+@pytest.mark.parametrize("sfx", DTYPES)
+@pytest.mark.parametrize("shape", BATCHED_SHAPES)
+@pytest.mark.parametrize("variant", BATCHED, ids=[v[0][-11:] for v in BATCHED])
+def test_batched_inner_product_variants(mp, stream, orc, sfx, shape, variant):
+    name, ta, tb = variant
+    nb, m, n, k = shape
+    a = rng_normal(20, (nb, n, m) if ta else (nb, m, n), sfx)
+    b = rng_normal(21, (nb, k, n) if tb else (nb, n, k), sfx, scale=1.0 / np.sqrt(n))
+    c = dev(np.full((nb, m, k), np.nan, a.dtype))        # beta = 0 must not read the fresh output
+    run(mp, stream, name, sfx, dev(a), dev(b), 1.0, c, 0.0, nb, m, n, k)
+    ref = orc.inner_product_batched(wide(a), wide(b), ta=ta, tb=tb)
+    assert_close(host(c), narrow(ref, sfx), TOL_RED[sfx], f"{name} {sfx} {shape}")
+    c0 = rng_normal(22, (nb, m, k), sfx)
+    c = dev(c0)
+    run(mp, stream, name, sfx, dev(a), dev(b), 0.5, c, 1.0, nb, m, n, k)
+    ref = orc.inner_product_batched(wide(a), wide(b), 0.5, wide(c0).copy(), 1.0, ta=ta, tb=tb)
+    assert_close(host(c), narrow(ref, sfx), TOL_RED[sfx], f"{name} accumulate {sfx} {shape}")
+    assert stream.status() == 0
+
+
+@pytest.mark.parametrize("sfx", ["r16", "r32"])
+def test_batched_entries_equal_the_rank2_contraction(mp, stream, sfx):
+    # every batch entry is bit-identical to the rank-2 launcher run on that entry alone (same kernel, same tile walk),
+    # at a size the oracle does not reach
+    import torch
+    nb, m, n, k = 12, 512, 256, 384
+    dt = {"r16": torch.float16, "r32": torch.float32}[sfx]
+    a = torch.randn(nb, m, n, device="cuda").to(dt); b = (torch.randn(nb, n, k, device="cuda") / 16).to(dt)
+    c = torch.empty(nb, m, k, device="cuda", dtype=dt); c1 = torch.empty(m, k, device="cuda", dtype=dt)
+    run(mp, stream, "inner_product_bij_bjk_bik", sfx, a, b, 1.0, c, 0.0, nb, m, n, k)
+    for q in (0, 5, 11):
+        run(mp, stream, "inner_product_ij_jk_ik", sfx, a[q], b[q], 1.0, c1, 0.0, m, n, k)
+        assert torch.equal(c[q], c1)
+
+
 def test_experimental_example_through_the_abi(mp, stream):
     # src/examples/experimental.zig: x = sequence(1,1)[3,2], y = sequence(1,1)[2,2]; z = x.y; reverse with seed 1
     import torch

@@ -29,7 +29,7 @@ def test_host_layer_and_scenarios_compile(mp, orc, tmp_path):
 @pytest.mark.gpu
 def test_reference_examples_and_feed_forward_block(mp, orc, tmp_path):
     exe = build_scenarios(tmp_path, orc)
-    res = subprocess.run([str(exe), "200"], capture_output=True, text=True, timeout=300)
+    res = subprocess.run([str(exe), "200", str(tmp_path)], capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert "ALL SCENARIOS PASSED" in res.stdout
     m = re.search(r"FEED_FORWARD_TIMING (\{.*\})", res.stdout)

@@ -78,6 +78,31 @@ def test_rank2_against_numpy(orc):
     assert np.array_equal(orc.permutate_ij_ji(s, bad, 0.0), s.T)
 
 
+def inverse_axes(perm):
+    """numpy `axes` of the permutation whose source dimension i lands at output position perm[i]."""
+    axes = [0] * len(perm)
+    for i, q in enumerate(perm):
+        axes[q] = i
+    return axes
+
+
+def test_general_permutation_against_numpy_and_the_rank2_instance(orc):
+    import itertools
+    r = np.random.default_rng(11)
+    s = r.standard_normal((37, 53))
+    assert np.array_equal(orc.permutate(s, [1, 0]), orc.permutate_ij_ji(s))          # pinned rank-2 instance
+    for shape in [(3, 4, 5), (2, 1, 7, 3), (2, 3, 2, 3, 2, 3)]:
+        x = r.standard_normal(shape).astype(np.float32)
+        perms = list(itertools.permutations(range(len(shape))))
+        for perm in perms[:: max(1, len(perms) // 24)]:
+            ref = np.transpose(x, inverse_axes(perm))
+            assert np.array_equal(orc.permutate(x, perm), ref), (shape, perm)
+    x = r.standard_normal((3, 4, 5)); d0 = r.standard_normal((5, 3, 4))
+    assert np.allclose(orc.permutate(x, [1, 2, 0], d0.copy(), 0.5), np.transpose(x, (2, 0, 1)) + 0.5 * d0)
+    bad = np.full((5, 3, 4), np.nan)
+    assert np.array_equal(orc.permutate(x, [1, 2, 0], bad, 0.0), np.transpose(x, (2, 0, 1)))
+
+
 def test_contractions_against_numpy(orc):
     r = np.random.default_rng(2)
     a = r.standard_normal((5, 7)); b = r.standard_normal((7, 3)); c0 = r.standard_normal((5, 3)); bias = r.standard_normal(3)
@@ -160,3 +185,25 @@ def test_ssd_oracle_against_torch_autograd(orc, G):
     gx, gdt, gA, gB, gC = orc.ssd_reverse(n(x), n(dt), n(A), n(Bm), n(Cm), n(gy))
     for got, ref, name in [(gx, x.grad, "gx"), (gdt, dt.grad, "gdt"), (gA, A.grad, "gA"), (gB, Bm.grad, "gB"), (gC, Cm.grad, "gC")]:
         assert rel_err(got, n(ref)) < 1e-12, name
+
+
+def test_batched_contractions_against_numpy(orc):
+    r = np.random.default_rng(12)
+    a = r.standard_normal((4, 5, 7)); b = r.standard_normal((4, 7, 3)); c0 = r.standard_normal((4, 5, 3))
+    assert np.allclose(orc.inner_product_batched(a, b), a @ b)
+    assert np.allclose(orc.inner_product_batched(a, b, 0.5, c0.copy(), 2.0), 0.5 * a @ b + 2 * c0)
+    assert np.allclose(orc.inner_product_batched(a, np.ascontiguousarray(b.transpose(0, 2, 1)), tb=True), a @ b)
+    assert np.allclose(orc.inner_product_batched(np.ascontiguousarray(a.transpose(0, 2, 1)), b, ta=True), a @ b)
+
+
+def test_c_and_numpy_momentum_agree(orc):
+    import ctypes as C
+    r = np.random.default_rng(13)
+    w = r.standard_normal(100); g = r.standard_normal(100); m = r.standard_normal(100)
+    w_ref, m_ref = orc.momentum(w, g, m, 0.1, 0.9, -0.5, 0.5)
+    fn = orc.lib().orc_momentum_f64
+    fn.restype = None
+    wc, mc = w.copy(), m.copy()
+    fn(C.c_void_p(wc.ctypes.data), C.c_void_p(g.ctypes.data), C.c_void_p(mc.ctypes.data), C.c_double(0.1), C.c_double(0.9),
+       C.c_double(-0.5), C.c_double(0.5), C.c_size_t(100))
+    assert np.allclose(wc, w_ref, rtol=0, atol=1e-15) and np.allclose(mc, m_ref, rtol=0, atol=1e-15)
