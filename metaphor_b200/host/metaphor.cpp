@@ -507,9 +507,9 @@ static void launch_permutate(Tensor src_t, const void* src, void* dst, double al
 // the gradient flows back through the inverse permutation (for "ij->ji" that is the permutation itself, the
 // only case permutate.zig:62-72 handles), accumulated into x.grad
 static void permutate_rev(const std::vector<OpDatum>& a) {
-  Tensor x = a[0].tensor, y = a[1].tensor;
+  Tensor x = a[0].tensor, y = a[2].tensor;   // the output is the last argument (attach_op counts the others as dependencies)
   enable_gradient(x);
-  const std::vector<size_t> perm = permutation_of(a[2].expr);
+  const std::vector<size_t> perm = permutation_of(a[1].expr);
   if (perm.size() == 2 && perm[0] == 1) {
     const auto& s = y.sizes();
     kernels::permutate_ij_ji[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
@@ -529,7 +529,7 @@ Tensor permutate(Tensor x, const std::string& expr) {
   Tensor y = g->tensor({Class::hid, x.dtype(), out});
   if (perm.size() == 2 && perm[0] == 1) kernels::permutate_ij_ji[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
   else launch_permutate(x, x.data_ptr(), y.data_ptr(), 0.0, s, perm);
-  if (g->mode == Mode::train) attach_op(permutate_rev, y, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(expr)});
+  if (g->mode == Mode::train) attach_op(permutate_rev, y, {OpDatum::of(x), OpDatum::of(expr), OpDatum::of(y)});
   return y;
 }
 

@@ -25,10 +25,11 @@ def out_shape(shape, perm):
 
 
 # shapes exercising: odd extents (scalar paths), 16-byte friendly extents (vector paths), size-1 dimensions,
-# merges of neighbouring dimensions, tiles cut at both edges, long rows cut into pieces
+# merges of neighbouring dimensions, tiles cut at both edges, long rows cut into pieces, kept rows of 4 / 8 bytes
+# (moved as wider elements)
 CASES = [((3, 4, 5), None), ((2, 1, 7, 3), None), ((8, 16, 24), None), ((5, 130, 66), None), ((2, 3, 4, 5, 6), "some"),
          ((2, 3, 2, 3, 2, 3), "some"), ((4, 8, 8, 8, 8, 16), "some"), ((1, 1, 1), None), ((7,), None), ((3, 70000), None),
-         ((2, 300, 8), None)]
+         ((2, 300, 8), None), ((33, 65, 2), None), ((17, 40, 4), None), ((3, 5, 7, 2), None), ((8, 100, 3, 16), None), ((6, 9, 200), None)]
 
 
 @pytest.mark.parametrize("sfx", DTYPES)
