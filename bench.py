@@ -585,12 +585,15 @@ def run_lm(args):
         dist.destroy_process_group()
 
 
-def run_profile_case(spec: str):
+def run_profile_case(spec: str, timed: bool = False):
     """`--profile-case OP:DTYPE:ROWS[:COLS]`: three launches of one kernel on a
     small case, for an ncu capture (no timing, no JSON).  OP is one of
     softmax_fwd, softmax_rev, rmsnorm_fwd, rmsnorm_rev (rows x cols matrix),
     chain_fwd, chain_rev (ROWS = element count of selu((a+b)*(c+d))),
-    gemm (ROWS:COLS = M and N = K), ssd_fwd, ssd_rev (ROWS:COLS = batch and seqlen)."""
+    gemm (ROWS:COLS = M and N = K), ssd_fwd, ssd_rev (ROWS:COLS = batch and seqlen),
+    bmm (ROWS:COLS = batch entries and M = N = K), permute_heads / permute_reverse (ROWS:COLS = batch and seqlen of a
+    [batch, seqlen, 32, 128] tensor: "blhd->bhld" resp. "blhd->dhlb").  With `--profile-time` the case is then launched
+    20 more times between CUDA events and one JSON line with the mean launch time is printed."""
     import torch
     import metaphor_b200 as mp
     parts = spec.split(":")
@@ -600,6 +603,8 @@ def run_profile_case(spec: str):
     torch.zeros(1, device="cuda")
     s = mp.Stream()
     g = torch.Generator(device="cuda").manual_seed(0)
+    once = None          # one launch of the case (set by the branches that support --profile-time)
+    work = None          # (amount, unit) per launch
     if op in ("chain_fwd", "chain_rev"):
         leaves = [(torch.rand(m, generator=g, device="cuda") * 2 - 1).to(dt) for _ in range(4)]
         out = torch.empty_like(leaves[0]); grads = [torch.empty_like(leaves[0]) for _ in range(4)]
@@ -610,6 +615,25 @@ def run_profile_case(spec: str):
                 chain.forward(leaves, out, m, s)
             else:
                 chain.reverse(leaves, None, grads, 0.0, m, s)
+    elif op == "bmm":
+        a = torch.randn(m, n, n, generator=g, device="cuda").to(dt); b = (torch.randn(m, n, n, generator=g, device="cuda") / 32).to(dt)
+        c = torch.empty(m, n, n, device="cuda", dtype=dt)
+        once = lambda: mp.launch("inner_product_bij_bjk_bik", dt, a, b, 1.0, c, 0.0, m, n, n, n, s)
+        work = (2.0 * m * n * n * n / 1e12, "TFLOP")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            once()
+    elif op in ("permute_heads", "permute_reverse"):
+        import ctypes
+        shape = (m, n, 32, 128)
+        perm = (0, 2, 1, 3) if op == "permute_heads" else (3, 2, 1, 0)
+        x = torch.randn(shape, generator=g, device="cuda").to(dt); y = torch.empty_like(x)
+        sizes = (ctypes.c_ulong * 4)(*shape); pm = (ctypes.c_ulong * 4)(*perm)
+        once = lambda: mp.launch("permutate", dt, x, y, 0.0, sizes, pm, 4, s)
+        work = (2.0 * x.numel() * x.element_size() / 1e9, "GB")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            once()
     elif op in ("ssd_fwd", "ssd_rev"):
         # ROWS = batch, COLS = seqlen; heads 32, headdim 64, d_state 128, 1 group, chunk 256
         import math
@@ -634,9 +658,11 @@ def run_profile_case(spec: str):
     elif op == "gemm":
         a = torch.randn(m, n, generator=g, device="cuda").to(dt); b = torch.randn(n, n, generator=g, device="cuda").to(dt)
         c = torch.empty(m, n, device="cuda", dtype=dt)
+        once = lambda: mp.launch("inner_product_ij_jk_ik", dt, a, b, 1.0, c, 0.0, m, n, n, s)
+        work = (2.0 * m * n * n / 1e12, "TFLOP")
         torch.cuda.synchronize()
         for _ in range(3):
-            mp.launch("inner_product_ij_jk_ik", dt, a, b, 1.0, c, 0.0, m, n, n, s)
+            once()
     else:
         x = torch.randn(m, n, generator=g, device="cuda").to(dt); gy = torch.randn(m, n, generator=g, device="cuda").to(dt)
         y = torch.empty_like(x); gx = torch.empty_like(x)
@@ -655,6 +681,19 @@ def run_profile_case(spec: str):
             else:
                 raise SystemExit(f"unknown profile case {op}")
     s.sync()
+    if timed:
+        if once is None:
+            raise SystemExit(f"--profile-time is not available for {op}")
+        ts = s.torch_stream()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(ts)
+        for _ in range(20):
+            once()
+        e1.record(ts)
+        s.sync()
+        us = e0.elapsed_time(e1) / 20 * 1e3
+        print(json.dumps({"case": spec, "us_per_launch": round(us, 2), "per_launch": work[0], "unit": work[1],
+                          "rate": round(work[0] / (us * 1e-6), 1), "rate_unit": work[1] + "/s"}))
     if s.status() != 0:
         raise SystemExit("status word set")
     s.close()
@@ -674,9 +713,10 @@ def main():
     ap.add_argument("--lm-batch", type=int, default=8)
     ap.add_argument("--lm-no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--profile-case", default=None, help="OP:DTYPE:ROWS[:COLS], three launches for an ncu capture")
+    ap.add_argument("--profile-time", action="store_true", help="with --profile-case: also time 20 launches with CUDA events")
     args = ap.parse_args()
     if args.profile_case:
-        run_profile_case(args.profile_case)
+        run_profile_case(args.profile_case, args.profile_time)
         return
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -299,6 +299,124 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const
   }
 }
 
+// Reverse for r16 rows that allow 16-byte accesses: a CTA stages a tile of 64 channels x 64 steps (plus the
+// W - 1 steps before it of x and after it of gy) in shared memory with 16-byte loads, then every thread walks
+// 16 steps of one channel with the windows of x and dpre in registers (one shared-memory read of x and of gy per
+// step, no barrier inside the walk), and the gx tile leaves through shared memory with 16-byte stores.  The
+// W - 1 look-ahead values of dpre are recomputed by the lane that needs them.  Tap / bias gradients accumulate
+// in registers over the CTA's time tiles and end in one atomic per (CTA, channel, tap).
+constexpr int CT_C = 64;            // channels per tile
+constexpr int CT_L = 64;            // steps per tile
+constexpr int CT_LANES = 4;         // time lanes: 256 threads = 64 channels x 4 lanes
+constexpr int CT_STEPS = CT_L / CT_LANES;
+
+template <int W>
+__global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __half* __restrict__ x, size_t xp,
+                                                                        const __half* __restrict__ w, const __half* __restrict__ bias,
+                                                                        const __half* __restrict__ gy, size_t gyp,
+                                                                        __half* __restrict__ gx, size_t gxp, float* __restrict__ gw,
+                                                                        float* __restrict__ gbias, int L, int C, int tiles_per_cta) {
+  constexpr int H = W - 1;
+  __shared__ __align__(16) __half xs[CT_L + 2 * H][CT_C];    // row r = step l0 - H + r
+  __shared__ __align__(16) __half gys[CT_L + H][CT_C];       // row r = step l0 + r
+  __shared__ __align__(16) __half gxs[CT_L][CT_C];
+  __shared__ float red[CT_LANES][CT_C][W + 1];
+  const int tid = threadIdx.x;
+  const int c = tid % CT_C, lane = tid / CT_C;
+  const int cbase = blockIdx.x * CT_C;
+  const bool live_c = cbase + c < C;
+  const size_t b = blockIdx.z;
+  const __half* xb = x + b * L * xp + cbase;
+  const __half* gyb = gy + b * L * gyp + cbase;
+  __half* gxb = gx + b * L * gxp + cbase;
+  float wk[W], bs = 0.f, gwk[W], gbs = 0.f;
+#pragma unroll
+  for (int k = 0; k < W; ++k) { wk[k] = live_c ? __half2float(w[static_cast<size_t>(cbase + c) * W + k]) : 0.f; gwk[k] = 0.f; }
+  if (live_c && bias != nullptr) bs = __half2float(bias[cbase + c]);
+  constexpr int PPR = CT_C / 8;   // 16-byte packs per tile row
+  const int packs_live = min(PPR, (C - cbase) / 8);   // C is a multiple of 8 on this path
+
+  for (int t = 0; t < tiles_per_cta; ++t) {
+    const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
+    if (l0 >= L) break;
+    // ---- stage x and gy (zero outside the sequence and beyond the last channel) ----
+    for (int v = tid; v < (CT_L + 2 * H) * PPR; v += 256) {
+      const int r = v / PPR, pk = v % PPR;
+      const int l = l0 - H + r;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (l >= 0 && l < L && pk < packs_live) val = *reinterpret_cast<const uint4*>(xb + static_cast<size_t>(l) * xp + pk * 8);
+      *reinterpret_cast<uint4*>(&xs[r][pk * 8]) = val;
+    }
+    for (int v = tid; v < (CT_L + H) * PPR; v += 256) {
+      const int r = v / PPR, pk = v % PPR;
+      const int l = l0 + r;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (l < L && pk < packs_live) val = *reinterpret_cast<const uint4*>(gyb + static_cast<size_t>(l) * gyp + pk * 8);
+      *reinterpret_cast<uint4*>(&gys[r][pk * 8]) = val;
+    }
+    __syncthreads();
+    // ---- walk CT_STEPS (+ H look-ahead) steps of one channel ----
+    {
+      const int s0 = lane * CT_STEPS;
+      float xw[W], d[W];   // xw[k] = x at step s + k - H (tile row s + k); d[k] = dpre at step s - k
+#pragma unroll
+      for (int k = 0; k < W; ++k) d[k] = 0.f;
+#pragma unroll
+      for (int k = 0; k < H; ++k) xw[k + 1] = __half2float(xs[s0 + k][c]);
+#pragma unroll
+      for (int j = 0; j < CT_STEPS + H; ++j) {
+        const int s = s0 + j;
+#pragma unroll
+        for (int k = 0; k < H; ++k) xw[k] = xw[k + 1];
+        xw[H] = __half2float(xs[s + H][c]);
+        float pre = bs;
+#pragma unroll
+        for (int k = 0; k < W; ++k) pre += wk[k] * xw[k];
+        const float sg = sigmoid_a(pre);
+        const float dp = __half2float(gys[s][c]) * sg * (1.f + pre * (1.f - sg));
+#pragma unroll
+        for (int k = H; k > 0; --k) d[k] = d[k - 1];
+        d[0] = dp;
+        if (j < CT_STEPS) {   // own steps only: the look-ahead belongs to the next lane / tile
+          gbs += dp;
+#pragma unroll
+          for (int k = 0; k < W; ++k) gwk[k] += dp * xw[k];
+        }
+        if (j >= H) {         // gx at step s - H = sum_k w[k] dpre[s - k]
+          float acc = 0.f;
+#pragma unroll
+          for (int k = 0; k < W; ++k) acc += wk[k] * d[k];
+          gxs[s - H][c] = __float2half_rn(acc);
+        }
+      }
+    }
+    __syncthreads();
+    // ---- gx tile -> global ----
+    for (int v = tid; v < CT_L * PPR; v += 256) {
+      const int r = v / PPR, pk = v % PPR;
+      const int l = l0 + r;
+      if (l < L && pk < packs_live) *reinterpret_cast<uint4*>(gxb + static_cast<size_t>(l) * gxp + pk * 8) = *reinterpret_cast<const uint4*>(&gxs[r][pk * 8]);
+    }
+    // the next tile's staging overwrites xs / gys only (all threads are past the walk) and gxs is rewritten
+    // after the next barrier pair, so no further barrier is needed here
+  }
+  // ---- fold the time lanes, one atomic per (channel, tap) ----
+#pragma unroll
+  for (int k = 0; k < W; ++k) red[lane][c][k] = gwk[k];
+  red[lane][c][W] = gbs;
+  __syncthreads();
+  if (lane == 0 && live_c) {
+#pragma unroll
+    for (int k = 0; k <= W; ++k) {
+      float sum = 0.f;
+#pragma unroll
+      for (int q = 0; q < CT_LANES; ++q) sum += red[q][c][k];
+      if (k < W) atomicAdd(gw + static_cast<size_t>(cbase + c) * W + k, sum);
+      else if (gbias != nullptr) atomicAdd(gbias + cbase + c, sum);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // dt = softplus(raw + bias[h]) (accumulator-typed output), raw pitched [rows, H]
 // ---------------------------------------------------------------------------
@@ -742,6 +860,27 @@ void causal_conv1d_silu_reverse_impl(const void* x, len_t x_pitch, const void* w
   constexpr int PN = Pack<T>::N;
   constexpr int RV = PN > 4 ? 2 : PN;   // at most 4 channels per thread (register footprint)
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(gy, gy_pitch, channels) && vec_ok<T>(gx, gx_pitch, channels);
+  if constexpr (std::is_same<T, __half>::value) {
+    if (v && width >= 2 && width <= 4 && !getenv("MP_CONV_NO_TILES")) {
+      // time tiles per CTA: as many as keep about four CTAs per SM (fewer atomics on the tap gradients)
+      const unsigned cblocks = static_cast<unsigned>((channels + CT_C - 1) / CT_C);
+      const size_t ltiles = (len + CT_L - 1) / CT_L;
+      size_t per = 8;
+      while (per > 1 && cblocks * ((ltiles + per - 1) / per) * batch < 4ull * mp_sm_count(ctx)) per >>= 1;
+      const dim3 grid(cblocks, static_cast<unsigned>((ltiles + per - 1) / per), static_cast<unsigned>(batch));
+      const int L = static_cast<int>(len), C = static_cast<int>(channels), tp = static_cast<int>(per);
+      cudaStream_t st = mp_stream(ctx);
+      const __half* xh = static_cast<const __half*>(x); const __half* wh = static_cast<const __half*>(w);
+      const __half* bh = static_cast<const __half*>(bias); const __half* gyh = static_cast<const __half*>(gy);
+      __half* gxh = static_cast<__half*>(gx);
+      float* gwf = static_cast<float*>(gw); float* gbf = static_cast<float*>(gbias);
+      if (width == 4) conv1d_silu_reverse_tiled_kernel<4><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, gyh, gy_pitch, gxh, gx_pitch, gwf, gbf, L, C, tp);
+      else if (width == 3) conv1d_silu_reverse_tiled_kernel<3><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, gyh, gy_pitch, gxh, gx_pitch, gwf, gbf, L, C, tp);
+      else conv1d_silu_reverse_tiled_kernel<2><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, gyh, gy_pitch, gxh, gx_pitch, gwf, gbf, L, C, tp);
+      MP_LAUNCH_CHECK();
+      return;
+    }
+  }
   if (v) conv_reverse_dispatch<T, RV>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
                                       static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw),
                                       static_cast<A*>(gbias), batch, len, channels, width, mp_stream(ctx));

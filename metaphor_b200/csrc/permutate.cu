@@ -21,7 +21,7 @@ namespace {
 
 constexpr int PERM_THREADS = 256;
 
-constexpr int PERM_DIMS = MAX_DIMS + 2;    // two dimensions may be split in two for locality
+constexpr int PERM_DIMS = MAX_DIMS;
 struct PermDims {
   int rank;                                // number of (batch / outer) dimensions listed below
   unsigned long long size[PERM_DIMS];      // slowest first (the order rows are visited in)
@@ -240,33 +240,10 @@ static void permutate_run(const T* src, T* dst, double alpha, const size_t* n, c
     for (int i = 1; i < m - 1; ++i)   // insertion sort by output stride, descending
       for (int j = i; j > 0 && ds[order[j]] > ds[order[j - 1]]; --j) { const int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t; }
     const size_t inner = n[m - 1], rows = total / inner;
-    // Short rows that change places: visiting rows in output order reads 'inner'-sized chunks at a large stride.
-    // Split A (the outer dimension running fastest in the output) and B (running fastest in the source) into
-    // blocks of up to 32 and visit (..., A_hi, B_hi, B_lo, A_lo): neighbouring lane groups then cover a
-    // 32 x 32 block of rows whose reads and writes both fall into runs of 32 rows.
-    int ia = -1, ib = -1;
-    for (int i = 0; i < m - 1; ++i) {
-      if (ia < 0 || ds[i] < ds[ia]) ia = i;
-      if (ib < 0 || ss[i] < ss[ib]) ib = i;
-    }
-    auto block_of = [](size_t extent) { size_t f = 32; while (f > 1 && extent % f != 0) f >>= 1; return f; };
-    const size_t fa = ia >= 0 ? block_of(n[ia]) : 1, fb = ib >= 0 ? block_of(n[ib]) : 1;
-    if (m - 1 >= 2 && ia != ib && inner * sizeof(T) <= 2048 && fa >= 4 && fb >= 4) {
-      int k = 0;
-      for (int i = 0; i < m - 1; ++i) {
-        const int j = order[i];
-        if (j == ia || j == ib) continue;
-        o.size[k] = n[j]; o.sstride[k] = ss[j]; o.dstride[k] = ds[j]; ++k;
-      }
-      o.size[k] = n[ia] / fa; o.sstride[k] = ss[ia] * fa; o.dstride[k] = ds[ia] * fa; ++k;
-      o.size[k] = n[ib] / fb; o.sstride[k] = ss[ib] * fb; o.dstride[k] = ds[ib] * fb; ++k;
-      o.size[k] = fb; o.sstride[k] = ss[ib]; o.dstride[k] = ds[ib]; ++k;
-      o.size[k] = fa; o.sstride[k] = ss[ia]; o.dstride[k] = ds[ia]; ++k;
-      o.rank = k;
-    } else {
-      o.rank = m - 1;
-      for (int i = 0; i < m - 1; ++i) { o.size[i] = n[order[i]]; o.sstride[i] = ss[order[i]]; o.dstride[i] = ds[order[i]]; }
-    }
+    // rows are visited in output order (a blocked order over the fastest output / source dimensions was
+    // measured slower: 2.9 instead of 4.2 TB/s on [8, 2048, 32, 128] r16 "blhd->bhld")
+    o.rank = m - 1;
+    for (int i = 0; i < m - 1; ++i) { o.size[i] = n[order[i]]; o.sstride[i] = ss[order[i]]; o.dstride[i] = ds[order[i]]; }
     const bool vec = aligned && inner % PN == 0;
     const size_t units = vec ? inner / PN : inner;
     // long rows are cut into pieces of 256 units (8 per lane) so that a few long rows still fill the machine
