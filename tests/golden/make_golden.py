@@ -49,6 +49,16 @@ def build() -> dict:
     dt = np.log1p(np.exp(r.standard_normal((1, 8, 2)) - 1.0)); Ah = -np.exp(r.uniform(0, 1, 2))
     g["ssd_x"], g["ssd_B"], g["ssd_C"], g["ssd_dt"], g["ssd_A"] = xs, Bm, Cm, dt, Ah
     g["ssd_y"] = orc.ssd_forward(xs.copy(), dt.copy(), Ah.copy(), Bm.copy(), Cm.copy())
+    # rank-3 operators (appended, so the arrays above keep their values)
+    px = r.standard_normal((3, 4, 5))
+    g["perm_x"] = px
+    g["perm_kij"] = orc.permutate(px.copy(), [1, 2, 0])            # "ijk->kij"
+    ba = r.standard_normal((3, 5, 7)); bb = r.standard_normal((3, 7, 4))
+    g["bmm_a"], g["bmm_b"] = ba, bb
+    g["bmm_c"] = orc.inner_product_batched(ba.copy(), bb.copy())
+    mw = r.standard_normal(32); mg = r.standard_normal(32); mm = r.standard_normal(32)
+    g["mom_w0"], g["mom_g"], g["mom_m0"] = mw, mg, mm
+    g["mom_w1"], g["mom_m1"] = orc.momentum(mw.copy(), mg.copy(), mm.copy(), 0.1, 0.9, -0.5, 0.5)
     return g
 
 

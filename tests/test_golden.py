@@ -38,3 +38,9 @@ def test_golden_known_answers():
             S = np.exp(dt[0, t, h] * A[h]) * S + dt[0, t, h] * np.outer(Bm[0, t, 0], xs[0, t, h])
             y[0, t, h] = Cm[0, t, 0] @ S
     np.testing.assert_allclose(g["ssd_y"], y, rtol=1e-10, atol=1e-12)
+    # "ijk->kij": out[k, i, j] = x[i, j, k]
+    np.testing.assert_array_equal(g["perm_kij"], np.transpose(g["perm_x"], (2, 0, 1)))
+    np.testing.assert_allclose(g["bmm_c"], np.einsum("bij,bjk->bik", g["bmm_a"], g["bmm_b"]), rtol=1e-12)
+    m1 = 0.9 * g["mom_m0"] + np.clip(g["mom_g"], -0.5, 0.5)
+    np.testing.assert_allclose(g["mom_m1"], m1, rtol=1e-14)
+    np.testing.assert_allclose(g["mom_w1"], g["mom_w0"] - 0.1 * m1, rtol=1e-14)

@@ -47,3 +47,17 @@ def test_flat_ops_against_golden(mp, stream):
     run(mp, stream, "cross_entropy", "r32", lg, tg, 0.25, loss, lg, 5, 33)
     assert_close(host(loss), G["ce_loss"], 1e-5, "cross-entropy loss")
     assert_close(host(lg), G["ce_glogits"], 1e-5, "cross-entropy gradient")
+
+
+def test_rank3_ops_against_golden(mp, stream):
+    import ctypes as C
+    x = dev(G["perm_x"].astype(np.float32)); out = dev(np.zeros((5, 3, 4), np.float32))
+    run(mp, stream, "permutate", "r32", x, out, 0.0, (C.c_ulong * 3)(3, 4, 5), (C.c_ulong * 3)(1, 2, 0), 3)
+    assert np.array_equal(host(out), G["perm_kij"].astype(np.float32))
+    a = dev(G["bmm_a"].astype(np.float32)); b = dev(G["bmm_b"].astype(np.float32)); c = dev(np.zeros((3, 5, 4), np.float32))
+    run(mp, stream, "inner_product_bij_bjk_bik", "r32", a, b, 1.0, c, 0.0, 3, 5, 7, 4)
+    assert_close(host(c), G["bmm_c"], 1e-4, "batched inner product")
+    w = dev(G["mom_w0"].astype(np.float32)); g = dev(G["mom_g"].astype(np.float32)); m = dev(G["mom_m0"].astype(np.float32))
+    run(mp, stream, "momentum", "r32", w, g, m, 0.1, 0.9, -0.5, 0.5, 32)
+    assert_close(host(w), G["mom_w1"], 1e-6, "momentum w")
+    assert_close(host(m), G["mom_m1"], 1e-6, "momentum m")
