@@ -310,6 +310,63 @@ constexpr int CT_L = 64;            // steps per tile
 constexpr int CT_LANES = 4;         // time lanes: 256 threads = 64 channels x 4 lanes
 constexpr int CT_STEPS = CT_L / CT_LANES;
 
+// Forward with the same staging: x tile (+ W - 1 rows before it) in, y tile out, 16 steps per thread.
+template <int W>
+__global__ void __launch_bounds__(256) conv1d_silu_tiled_kernel(const __half* __restrict__ x, size_t xp, const __half* __restrict__ w,
+                                                                const __half* __restrict__ bias, __half* __restrict__ y, size_t yp,
+                                                                int L, int C, int tiles_per_cta) {
+  constexpr int H = W - 1;
+  __shared__ __align__(16) __half xs[CT_L + H][CT_C];    // row r = step l0 - H + r
+  __shared__ __align__(16) __half ys[CT_L][CT_C];
+  const int tid = threadIdx.x;
+  const int c = tid % CT_C, lane = tid / CT_C;
+  const int cbase = blockIdx.x * CT_C;
+  const bool live_c = cbase + c < C;
+  const size_t b = blockIdx.z;
+  const __half* xb = x + b * L * xp + cbase;
+  __half* yb = y + b * L * yp + cbase;
+  float wk[W], bs = 0.f;
+#pragma unroll
+  for (int k = 0; k < W; ++k) wk[k] = live_c ? __half2float(w[static_cast<size_t>(cbase + c) * W + k]) : 0.f;
+  if (live_c && bias != nullptr) bs = __half2float(bias[cbase + c]);
+  constexpr int PPR = CT_C / 8;
+  const int packs_live = min(PPR, (C - cbase) / 8);
+  for (int t = 0; t < tiles_per_cta; ++t) {
+    const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
+    if (l0 >= L) break;
+    for (int v = tid; v < (CT_L + H) * PPR; v += 256) {
+      const int r = v / PPR, pk = v % PPR;
+      const int l = l0 - H + r;
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (l >= 0 && l < L && pk < packs_live) val = *reinterpret_cast<const uint4*>(xb + static_cast<size_t>(l) * xp + pk * 8);
+      *reinterpret_cast<uint4*>(&xs[r][pk * 8]) = val;
+    }
+    __syncthreads();
+    {
+      const int s0 = lane * CT_STEPS;
+      float xw[W];
+#pragma unroll
+      for (int k = 0; k < H; ++k) xw[k + 1] = __half2float(xs[s0 + k][c]);
+#pragma unroll
+      for (int j = 0; j < CT_STEPS; ++j) {
+#pragma unroll
+        for (int k = 0; k < H; ++k) xw[k] = xw[k + 1];
+        xw[H] = __half2float(xs[s0 + j + H][c]);
+        float pre = bs;
+#pragma unroll
+        for (int k = 0; k < W; ++k) pre += wk[k] * xw[k];
+        ys[s0 + j][c] = __float2half_rn(pre * sigmoid_a(pre));
+      }
+    }
+    __syncthreads();
+    for (int v = tid; v < CT_L * PPR; v += 256) {
+      const int r = v / PPR, pk = v % PPR;
+      const int l = l0 + r;
+      if (l < L && pk < packs_live) *reinterpret_cast<uint4*>(yb + static_cast<size_t>(l) * yp + pk * 8) = *reinterpret_cast<const uint4*>(&ys[r][pk * 8]);
+    }
+  }
+}
+
 template <int W>
 __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __half* __restrict__ x, size_t xp,
                                                                         const __half* __restrict__ w, const __half* __restrict__ bias,
@@ -845,6 +902,24 @@ void causal_conv1d_silu_impl(const void* x, len_t x_pitch, const void* w, const 
   if (batch == 0 || len == 0 || channels == 0) return;
   constexpr int PN = Pack<T>::N;
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(y, y_pitch, channels);
+  if constexpr (std::is_same<T, __half>::value) {
+    if (v && width >= 2 && width <= 4 && !getenv("MP_CONV_NO_TILES")) {
+      const unsigned cblocks = static_cast<unsigned>((channels + CT_C - 1) / CT_C);
+      const size_t ltiles = (len + CT_L - 1) / CT_L;
+      const size_t per = ltiles >= 2 ? 2 : 1;   // time tiles per CTA (measured best of 1, 2, 4, 8 at 1536 and 128 channels)
+      const dim3 grid(cblocks, static_cast<unsigned>((ltiles + per - 1) / per), static_cast<unsigned>(batch));
+      const int L = static_cast<int>(len), C = static_cast<int>(channels), tp = static_cast<int>(per);
+      cudaStream_t st = mp_stream(ctx);
+      const __half* xh = static_cast<const __half*>(x); const __half* wh = static_cast<const __half*>(w);
+      const __half* bh = static_cast<const __half*>(bias);
+      __half* yh = static_cast<__half*>(y);
+      if (width == 4) conv1d_silu_tiled_kernel<4><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, yh, y_pitch, L, C, tp);
+      else if (width == 3) conv1d_silu_tiled_kernel<3><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, yh, y_pitch, L, C, tp);
+      else conv1d_silu_tiled_kernel<2><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, yh, y_pitch, L, C, tp);
+      MP_LAUNCH_CHECK();
+      return;
+    }
+  }
   if (v) conv_forward_dispatch<T, PN>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias), static_cast<T*>(y),
                                       y_pitch, batch, len, channels, width, mp_stream(ctx));
   else conv_forward_dispatch<T, 1>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias), static_cast<T*>(y),
@@ -862,11 +937,9 @@ void causal_conv1d_silu_reverse_impl(const void* x, len_t x_pitch, const void* w
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(gy, gy_pitch, channels) && vec_ok<T>(gx, gx_pitch, channels);
   if constexpr (std::is_same<T, __half>::value) {
     if (v && width >= 2 && width <= 4 && !getenv("MP_CONV_NO_TILES")) {
-      // time tiles per CTA: as many as keep about four CTAs per SM (fewer atomics on the tap gradients)
       const unsigned cblocks = static_cast<unsigned>((channels + CT_C - 1) / CT_C);
       const size_t ltiles = (len + CT_L - 1) / CT_L;
-      size_t per = 8;
-      while (per > 1 && cblocks * ((ltiles + per - 1) / per) * batch < 4ull * mp_sm_count(ctx)) per >>= 1;
+      const size_t per = ltiles >= 2 ? 2 : 1;   // time tiles per CTA (measured best of 1, 2, 4, 8 at 1536 and 128 channels)
       const dim3 grid(cblocks, static_cast<unsigned>((ltiles + per - 1) / per), static_cast<unsigned>(batch));
       const int L = static_cast<int>(len), C = static_cast<int>(channels), tp = static_cast<int>(per);
       cudaStream_t st = mp_stream(ctx);
