@@ -36,23 +36,27 @@ template <typename T, typename I, bool VEC, bool BLEND>
 __global__ void __launch_bounds__(PERM_THREADS) permute_rows_kernel(const T* __restrict__ src, T* dst, typename Acc<T>::type alpha,
                                                                     const PermDims o, I pieces, I segs, size_t inner_units,
                                                                     unsigned seg_units, int group_log2) {
-  // a row of `inner_units` units (16-byte packs when VEC, else elements) is cut into `segs` pieces of `seg_units`
+  // A row of `inner_units` units (16-byte packs when VEC, else elements) is cut into `segs` pieces of `seg_units`.
+  // A warp takes 32 consecutive pieces: every lane decodes ONE piece (the index arithmetic costs more than the
+  // copy of a short row), then the warp walks the 32 pieces with 2^group_log2 lanes per piece, the offsets
+  // handed around by shuffles; two steps are in flight at a time.
   constexpr int PN = Pack<T>::N;
-  const unsigned group_mask = (1u << group_log2) - 1u;
-  const size_t tid = static_cast<size_t>(blockIdx.x) * PERM_THREADS + threadIdx.x;
-  const size_t groups = (static_cast<size_t>(gridDim.x) * PERM_THREADS) >> group_log2;
-  const unsigned sub = static_cast<unsigned>(tid) & group_mask;
-  // two pieces per trip: both loads are issued before either store
-  for (size_t piece = tid >> group_log2; piece < pieces; piece += 2 * groups) {
-    size_t soff[2], doff[2], u0[2], u1[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const size_t pc = piece + h * groups;
-      I rem = static_cast<I>(pc < pieces ? pc : piece);
+  constexpr int UNIT = VEC ? PN : 1;
+  const int lane = threadIdx.x & 31;
+  const int group = 1 << group_log2;
+  const int sub = lane & (group - 1);
+  const int per_step = 32 >> group_log2;   // pieces per step
+  const size_t warp = (static_cast<size_t>(blockIdx.x) * PERM_THREADS + threadIdx.x) >> 5;
+  const size_t warps = (static_cast<size_t>(gridDim.x) * PERM_THREADS) >> 5;
+  for (size_t base = warp * 32; base < pieces; base += warps * 32) {
+    const size_t piece = base + lane;
+    size_t my_s = 0, my_d = 0;     // first unit of the piece on both sides
+    unsigned my_len = 0;           // units in the piece (0: past the end)
+    if (piece < pieces) {
+      I rem = static_cast<I>(piece);
       const I row = rem / segs;
-      u0[h] = static_cast<size_t>(rem - row * segs) * seg_units;
-      u1[h] = u0[h] + seg_units < inner_units ? u0[h] + seg_units : inner_units;
-      if (pc >= pieces) u1[h] = u0[h];   // nothing to do
+      const size_t u0 = static_cast<size_t>(rem - row * segs) * seg_units;
+      my_len = static_cast<unsigned>(u0 + seg_units < inner_units ? seg_units : inner_units - u0);
       rem = row;
       size_t so = 0, dof = 0;
 #pragma unroll
@@ -66,41 +70,52 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_rows_kernel(const T* __r
           rem = q;
         }
       }
-      soff[h] = so;
-      doff[h] = dof;
+      my_s = so / UNIT + u0;       // every stride is a multiple of the row length, hence of UNIT
+      my_d = dof / UNIT + u0;
     }
-    const size_t len0 = u1[0] - u0[0], len1 = u1[1] - u0[1];
-    const size_t len = len0 > len1 ? len0 : len1;
-    for (size_t u = sub; u < len; u += group_mask + 1u) {
-      const bool on0 = u < len0, on1 = u < len1;
-      if constexpr (VEC) {
-        Pack<T> p0, p1;
-        if (on0) p0 = ld_pack_stream(src, soff[0] / PN + u0[0] + u);
-        if (on1) p1 = ld_pack_stream(src, soff[1] / PN + u0[1] + u);
-        if constexpr (BLEND) {
-          if (on0) {
-            const Pack<T> old = ld_pack_stream(dst, doff[0] / PN + u0[0] + u);
+    for (int t = 0; t < 32; t += 2 * per_step) {
+      size_t so[2], dof[2];
+      unsigned len[2];
 #pragma unroll
-            for (int e = 0; e < PN; ++e) p0.v[e] = mp_down<T>(mp_up(p0.v[e]) + alpha * mp_up(old.v[e]));
-          }
-          if (on1) {
-            const Pack<T> old = ld_pack_stream(dst, doff[1] / PN + u0[1] + u);
+      for (int h = 0; h < 2; ++h) {
+        const int from = (t + h * per_step + (lane >> group_log2)) & 31;
+        so[h] = __shfl_sync(0xffffffffu, my_s, from);
+        dof[h] = __shfl_sync(0xffffffffu, my_d, from);
+        len[h] = __shfl_sync(0xffffffffu, my_len, from);
+        if (t + h * per_step >= 32) len[h] = 0;   // one lane per piece: a single step covers all 32
+      }
+      const unsigned longest = len[0] > len[1] ? len[0] : len[1];
+      for (unsigned u = sub; u < longest; u += group) {
+        const bool on0 = u < len[0], on1 = u < len[1];
+        if constexpr (VEC) {
+          Pack<T> p0, p1;
+          if (on0) p0 = ld_pack_stream(src, so[0] + u);
+          if (on1) p1 = ld_pack_stream(src, so[1] + u);
+          if constexpr (BLEND) {
+            if (on0) {
+              const Pack<T> old = ld_pack_stream(dst, dof[0] + u);
 #pragma unroll
-            for (int e = 0; e < PN; ++e) p1.v[e] = mp_down<T>(mp_up(p1.v[e]) + alpha * mp_up(old.v[e]));
+              for (int e = 0; e < PN; ++e) p0.v[e] = mp_down<T>(mp_up(p0.v[e]) + alpha * mp_up(old.v[e]));
+            }
+            if (on1) {
+              const Pack<T> old = ld_pack_stream(dst, dof[1] + u);
+#pragma unroll
+              for (int e = 0; e < PN; ++e) p1.v[e] = mp_down<T>(mp_up(p1.v[e]) + alpha * mp_up(old.v[e]));
+            }
           }
+          if (on0) st_pack_stream(dst, dof[0] + u, p0);
+          if (on1) st_pack_stream(dst, dof[1] + u, p1);
+        } else {
+          T v0 = T(), v1 = T();
+          if (on0) v0 = src[so[0] + u];
+          if (on1) v1 = src[so[1] + u];
+          if constexpr (BLEND) {
+            if (on0) v0 = mp_down<T>(mp_up(v0) + alpha * mp_up(dst[dof[0] + u]));
+            if (on1) v1 = mp_down<T>(mp_up(v1) + alpha * mp_up(dst[dof[1] + u]));
+          }
+          if (on0) dst[dof[0] + u] = v0;
+          if (on1) dst[dof[1] + u] = v1;
         }
-        if (on0) st_pack_stream(dst, doff[0] / PN + u0[0] + u, p0);
-        if (on1) st_pack_stream(dst, doff[1] / PN + u0[1] + u, p1);
-      } else {
-        T v0 = T(), v1 = T();
-        if (on0) v0 = src[soff[0] + u0[0] + u];
-        if (on1) v1 = src[soff[1] + u0[1] + u];
-        if constexpr (BLEND) {
-          if (on0) v0 = mp_down<T>(mp_up(v0) + alpha * mp_up(dst[doff[0] + u0[0] + u]));
-          if (on1) v1 = mp_down<T>(mp_up(v1) + alpha * mp_up(dst[doff[1] + u0[1] + u]));
-        }
-        if (on0) dst[doff[0] + u0[0] + u] = v0;
-        if (on1) dst[doff[1] + u0[1] + u] = v1;
       }
     }
   }
@@ -199,6 +214,77 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
   }
 }
 
+// r16 tiles with 16-byte accesses on both sides: two neighbouring output-innermost rows (d, d + 1) travel through
+// shared memory as one 32-bit word per source column, which halves the shared-memory instructions of the
+// 2-byte version and removes its sub-word bank conflicts (rows of TILE / 2 + 1 words: conflict-free both ways).
+template <bool BLEND>
+__global__ void __launch_bounds__(PERM_THREADS) permute_tiles_h2_kernel(const __half* __restrict__ src, __half* dst, float alpha,
+                                                                        const PermDims batch, size_t n_s, size_t n_d, size_t s_pitch,
+                                                                        size_t d_pitch, unsigned tiles_s, unsigned tiles_d,
+                                                                        const PermSplit sp) {
+  constexpr int TILE = 128, PN = 8, VPR = TILE / PN;
+  __shared__ uint32_t tile[TILE][TILE / 2 + 1];   // tile[s][d / 2] = (value at d, value at d + 1)
+  size_t rem = blockIdx.x;
+  const size_t s0 = (rem % tiles_s) * TILE;
+  rem /= tiles_s;
+  const size_t d0 = (rem % tiles_d) * TILE;
+  rem /= tiles_d;
+  size_t sbase = 0, dbase = 0;
+#pragma unroll
+  for (int k = PERM_DIMS - 1; k >= 0; --k) {
+    if (k < batch.rank) {
+      const size_t c = rem % batch.size[k];
+      rem /= batch.size[k];
+      sbase += c * batch.sstride[k];
+      dbase += c * batch.dstride[k];
+    }
+  }
+  auto src_row = [&](size_t id) -> size_t {
+    if (sp.d_lo == 0) return id * s_pitch;
+    const unsigned hi = static_cast<unsigned>(id) / sp.d_lo;
+    return static_cast<size_t>(static_cast<unsigned>(id) - hi * sp.d_lo) * s_pitch + hi * sp.s_pitch_hi;
+  };
+  auto dst_row = [&](size_t is) -> size_t {
+    if (sp.s_lo == 0) return is * d_pitch;
+    const unsigned hi = static_cast<unsigned>(is) / sp.s_lo;
+    return static_cast<size_t>(static_cast<unsigned>(is) - hi * sp.s_lo) * d_pitch + hi * sp.d_pitch_hi;
+  };
+  const int tid = threadIdx.x;
+  for (int v = tid; v < (TILE / 2) * VPR; v += PERM_THREADS) {
+    // a warp covers 8 row pairs x 4 packs: 64 contiguous bytes per source row (whole sectors) and 32 distinct banks
+    // per shared-memory store (bank = 8 * pack + pair with rows of 65 words)
+    const int g = v >> 5, l = v & 31;
+    const int td = ((g >> 2) * 8 + (l >> 2)) * 2, ts = ((g & 3) * 4 + (l & 3)) * PN;
+    if (d0 + td < n_d && s0 + ts < n_s) {   // n_d and n_s are multiples of 8: the pair and the pack are whole
+      union { uint4 u; unsigned short h[8]; } a, b;
+      a.u = *reinterpret_cast<const uint4*>(src + sbase + src_row(d0 + td) + s0 + ts);
+      b.u = *reinterpret_cast<const uint4*>(src + sbase + src_row(d0 + td + 1) + s0 + ts);
+#pragma unroll
+      for (int e = 0; e < PN; ++e) tile[ts + e][td >> 1] = static_cast<uint32_t>(a.h[e]) | (static_cast<uint32_t>(b.h[e]) << 16);
+    }
+  }
+  __syncthreads();
+  for (int v = tid; v < TILE * VPR; v += PERM_THREADS) {
+    const int ts = v / VPR, td = (v % VPR) * PN;
+    if (s0 + ts < n_s && d0 + td < n_d) {
+      __half* out = dst + dbase + dst_row(s0 + ts) + d0 + td;
+      union { uint4 u; uint32_t w[4]; __half2 h2[4]; } p;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) p.w[e] = tile[ts][(td >> 1) + e];
+      if constexpr (BLEND) {
+        union { uint4 u; __half2 h2[4]; } old;
+        old.u = *reinterpret_cast<const uint4*>(out);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 x = __half22float2(p.h2[e]), y = __half22float2(old.h2[e]);
+          p.h2[e] = __floats2half2_rn(x.x + alpha * y.x, x.y + alpha * y.y);
+        }
+      }
+      *reinterpret_cast<uint4*>(out) = p.u;
+    }
+  }
+}
+
 template <typename T, typename I, bool VEC>
 void rows_launch(const T* src, T* dst, double alpha, const PermDims& o, size_t pieces, size_t segs, size_t units, unsigned seg_units,
                  int glog, unsigned grid, cudaStream_t st) {
@@ -253,7 +339,7 @@ static void permutate_run(const T* src, T* dst, double alpha, const size_t* n, c
     const size_t piece_units = units < SEG_UNITS ? units : SEG_UNITS;
     int glog = 0;
     while (glog < 5 && (1ull << glog) < piece_units) ++glog;
-    const size_t threads = ((pieces + 1) / 2) << glog;   // a lane group takes two pieces per trip
+    const size_t threads = ((pieces + 31) / 32) * 32;    // a warp takes 32 pieces per trip
     size_t blocks = (threads + PERM_THREADS - 1) / PERM_THREADS;
     const size_t cap = static_cast<size_t>(mp_sm_count(ctx)) * 32;   // grid-stride beyond this
     if (blocks > cap) blocks = cap;
@@ -308,6 +394,14 @@ static void permutate_run(const T* src, T* dst, double alpha, const size_t* n, c
   const bool vs = aligned && n[d] % PN == 0;
   const unsigned grid = static_cast<unsigned>(blocks);
   const unsigned ts = static_cast<unsigned>(tiles_s), td = static_cast<unsigned>(tiles_d);
+  if constexpr (std::is_same<T, __half>::value) {
+    if (vl && vs) {
+      if (alpha == 0.0) permute_tiles_h2_kernel<false><<<grid, PERM_THREADS, 0, st>>>(src, dst, 0.f, b, n_s, n_d, s_pitch, d_pitch, ts, td, sp);
+      else permute_tiles_h2_kernel<true><<<grid, PERM_THREADS, 0, st>>>(src, dst, static_cast<float>(alpha), b, n_s, n_d, s_pitch, d_pitch, ts, td, sp);
+      MP_LAUNCH_CHECK();
+      return;
+    }
+  }
   if (vl && vs) tiles_launch<T, true, true>(src, dst, alpha, b, n_s, n_d, s_pitch, d_pitch, ts, td, sp, grid, st);
   else if (vl) tiles_launch<T, true, false>(src, dst, alpha, b, n_s, n_d, s_pitch, d_pitch, ts, td, sp, grid, st);
   else if (vs) tiles_launch<T, false, true>(src, dst, alpha, b, n_s, n_d, s_pitch, d_pitch, ts, td, sp, grid, st);
