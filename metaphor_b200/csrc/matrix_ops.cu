@@ -322,6 +322,13 @@ static void permutate_ij_ji_impl(const void* src_, void* dst_, double alpha, len
   const dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
   const bool vl = (col % PN == 0) && mp_aligned16(src);
   const bool vs = (row % PN == 0) && mp_aligned16(dst);
+  if constexpr (std::is_same<T, __half>::value) {
+    if (vl && vs) {   // the general permutation's r16 tile kernel (row pairs as 32-bit words) is faster: 4.65 vs 4.1 TB/s
+      const len_t sizes[2] = {row, col}, perm[2] = {1, 0};
+      launch_permutate_r16(src_, dst_, alpha, sizes, perm, 2, ctx);
+      return;
+    }
+  }
   cudaStream_t st = mp_stream(ctx);
   if (vl && vs) transpose_dispatch<T, true, true>(src, dst, alpha, row, col, grid, st);
   else if (vl) transpose_dispatch<T, true, false>(src, dst, alpha, row, col, grid, st);

@@ -170,6 +170,7 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
     return static_cast<size_t>(static_cast<unsigned>(is) - hi * sp.s_lo) * d_pitch + hi * sp.d_pitch_hi;
   };
   if constexpr (VL) {
+#pragma unroll
     for (int v = tid; v < TILE * VPR; v += PERM_THREADS) {
       const int td = v / VPR, ts = (v % VPR) * PN;
       if (d0 + td < n_d && s0 + ts < n_s) {
@@ -186,6 +187,7 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
   }
   __syncthreads();
   if constexpr (VS) {
+#pragma unroll
     for (int v = tid; v < TILE * VPR; v += PERM_THREADS) {
       const int ts = v / VPR, td = (v % VPR) * PN;
       if (s0 + ts < n_s && d0 + td < n_d) {
@@ -250,7 +252,8 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_h2_kernel(const __
     return static_cast<size_t>(static_cast<unsigned>(is) - hi * sp.s_lo) * d_pitch + hi * sp.d_pitch_hi;
   };
   const int tid = threadIdx.x;
-  for (int v = tid; v < (TILE / 2) * VPR; v += PERM_THREADS) {
+#pragma unroll
+  for (int v = tid; v < (TILE / 2) * VPR; v += PERM_THREADS) {   // 4 trips: all 8 loads of a thread are issued up front
     // a warp covers 8 row pairs x 4 packs: 64 contiguous bytes per source row (whole sectors) and 32 distinct banks
     // per shared-memory store (bank = 8 * pack + pair with rows of 65 words)
     const int g = v >> 5, l = v & 31;
@@ -264,6 +267,7 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_h2_kernel(const __
     }
   }
   __syncthreads();
+#pragma unroll
   for (int v = tid; v < TILE * VPR; v += PERM_THREADS) {
     const int ts = v / VPR, td = (v % VPR) * PN;
     if (s0 + ts < n_s && d0 + td < n_d) {
