@@ -24,7 +24,8 @@ using Blend2 = void (*)(const void*, void*, double, len_t, len_t, StreamContext)
 using Gemm = void (*)(const void*, const void*, const double, void*, const double, len_t, len_t, len_t, StreamContext);
 static const Bin addition[3] = MP_KERNELS(addition), subtraction[3] = MP_KERNELS(subtraction),
                  hadamard[3] = MP_KERNELS(hadamard), hadamard_reverse[3] = MP_KERNELS(hadamard_reverse);
-static const Un negate[3] = MP_KERNELS(negate), relu[3] = MP_KERNELS(relu), selu[3] = MP_KERNELS(selu), copy[3] = MP_KERNELS(copy);
+static const Un negate[3] = MP_KERNELS(negate), relu[3] = MP_KERNELS(relu), selu[3] = MP_KERNELS(selu), copy[3] = MP_KERNELS(copy),
+                stepwise[3] = MP_KERNELS(stepwise);
 static const Sca translate[3] = MP_KERNELS(translate), dilate[3] = MP_KERNELS(dilate), dilate_reverse[3] = MP_KERNELS(dilate_reverse);
 static const UnRev relu_reverse[3] = MP_KERNELS(relu_reverse), selu_reverse[3] = MP_KERNELS(selu_reverse);
 static const Blend2 reduce_ij_i[3] = MP_KERNELS(reduce_ij_i), reduce_ij_j[3] = MP_KERNELS(reduce_ij_j),
@@ -175,6 +176,7 @@ Tensor Graph::tensor(const TensorConfig& cfg) {
     b.attached.push_back(true);
     b.has_op.push_back(false);
     b.op_reverse.push_back(nullptr);
+    b.op_derive.push_back(nullptr);
     b.op_args.emplace_back();
   }
   return Tensor{this, cfg.cls, b.data.size() - 1};
@@ -269,16 +271,40 @@ void enable_gradient(Tensor t) {
   }
 }
 
-void attach_op(ReverseFn fn, Tensor out, const std::vector<OpDatum>& args) {
+void attach_op(ReverseFn fn, Tensor out, const std::vector<OpDatum>& args, DeriveFn derive_fn) {
   assert(out.cls == Class::hid);
   Graph::Block& nb = out.ptr->node_block;
   nb.has_op[out.idx] = true;
   nb.op_reverse[out.idx] = fn;
+  nb.op_derive[out.idx] = derive_fn;
   nb.op_args[out.idx] = args;
   for (size_t i = 0; i + 1 < args.size(); ++i) {   // the last argument is the output
     if (args[i].kind != OpDatum::tensor_k || args[i].tensor.cls != Class::hid) continue;
     nb.deps[args[i].tensor.idx] += 1;
   }
+}
+
+std::optional<OpDatum> derive(Tensor x, Tensor wrt) {
+  if (x.cls != Class::hid) return x.same(wrt) ? std::optional<OpDatum>(OpDatum::of(1.0)) : std::nullopt;
+  Graph::Block& nb = x.ptr->node_block;
+  if (!nb.has_op[x.idx]) return std::nullopt;
+  if (nb.op_derive[x.idx] == nullptr) panic("derive: an operator on the path has no element-wise derivative");
+  return nb.op_derive[x.idx](nb.op_args[x.idx], wrt);
+}
+
+std::optional<Tensor> Tensor::derive(Tensor wrt) const {
+  if (ptr->mode == Mode::eval) return std::nullopt;
+  auto constant = [&](double value) {
+    Tensor dx = wrt.ptr->tensor({Class::hid, dtype(), sizes()});
+    algo::fill(dx, value);
+    return dx;
+  };
+  if (same(wrt)) return constant(1.0);
+  if (cls != Class::hid) return std::nullopt;
+  const std::optional<OpDatum> d = mp::derive(*this, wrt);
+  if (!d) return std::nullopt;
+  if (d->kind == OpDatum::scalar_k) return constant(d->scalar);   // constant-valued tensor
+  return d->tensor;
 }
 
 void Graph::reverse(size_t idx, ReverseCleanup cleanup) {
@@ -325,6 +351,12 @@ static void check_same(Tensor x, Tensor y) {
   if (x.dtype() != y.dtype() || x.sizes() != y.sizes()) panic("operands differ in dtype or shape");
 }
 
+// forward-mode derivatives, defined after the ops they compose
+static std::optional<OpDatum> add_derive(const std::vector<OpDatum>&, Tensor), sub_derive(const std::vector<OpDatum>&, Tensor),
+    hadamard_derive(const std::vector<OpDatum>&, Tensor), negate_derive(const std::vector<OpDatum>&, Tensor),
+    translate_derive(const std::vector<OpDatum>&, Tensor), dilate_derive(const std::vector<OpDatum>&, Tensor),
+    relu_derive(const std::vector<OpDatum>&, Tensor), selu_derive(const std::vector<OpDatum>&, Tensor);
+
 // --- add / sub / hadamard (addition.zig:27-82, subtraction.zig, hadamard.zig) ---
 static void add_reverse(const std::vector<OpDatum>& a) {
   Tensor x = a[0].tensor, y = a[1].tensor, z = a[2].tensor;
@@ -338,7 +370,7 @@ Tensor add(Tensor x, Tensor y) {
   Graph* g = x.ptr;
   Tensor z = hidden_like(g, x);
   kernels::addition[dkey(z)](x.data_ptr(), y.data_ptr(), z.data_ptr(), z.len(), z.context());
-  if (g->mode == Mode::train) attach_op(add_reverse, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)});
+  if (g->mode == Mode::train) attach_op(add_reverse, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)}, add_derive);
   return z;
 }
 static void sub_reverse(const std::vector<OpDatum>& a) {
@@ -353,7 +385,7 @@ Tensor sub(Tensor x, Tensor y) {
   Graph* g = x.ptr;
   Tensor z = hidden_like(g, x);
   kernels::subtraction[dkey(z)](x.data_ptr(), y.data_ptr(), z.data_ptr(), z.len(), z.context());
-  if (g->mode == Mode::train) attach_op(sub_reverse, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)});
+  if (g->mode == Mode::train) attach_op(sub_reverse, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)}, sub_derive);
   return z;
 }
 static void hadamard_rev(const std::vector<OpDatum>& a) {
@@ -368,7 +400,7 @@ Tensor hadamard(Tensor x, Tensor y) {
   Graph* g = x.ptr;
   Tensor z = hidden_like(g, x);
   kernels::hadamard[dkey(z)](x.data_ptr(), y.data_ptr(), z.data_ptr(), z.len(), z.context());
-  if (g->mode == Mode::train) attach_op(hadamard_rev, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)});
+  if (g->mode == Mode::train) attach_op(hadamard_rev, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(z)}, hadamard_derive);
   return z;
 }
 
@@ -382,7 +414,7 @@ Tensor negate(Tensor x) {
   Graph* g = x.ptr;
   Tensor z = hidden_like(g, x);
   kernels::negate[dkey(z)](x.data_ptr(), z.data_ptr(), z.len(), z.context());
-  if (g->mode == Mode::train) attach_op(negate_reverse, z, {OpDatum::of(x), OpDatum::of(z)});
+  if (g->mode == Mode::train) attach_op(negate_reverse, z, {OpDatum::of(x), OpDatum::of(z)}, negate_derive);
   return z;
 }
 static void translate_reverse(const std::vector<OpDatum>& a) {
@@ -394,7 +426,7 @@ Tensor translate(Tensor x, double value) {
   Graph* g = x.ptr;
   Tensor z = hidden_like(g, x);
   kernels::translate[dkey(z)](x.data_ptr(), value, z.data_ptr(), z.len(), z.context());
-  if (g->mode == Mode::train) attach_op(translate_reverse, z, {OpDatum::of(x), OpDatum::of(value), OpDatum::of(z)});
+  if (g->mode == Mode::train) attach_op(translate_reverse, z, {OpDatum::of(x), OpDatum::of(value), OpDatum::of(z)}, translate_derive);
   return z;
 }
 static void dilate_rev(const std::vector<OpDatum>& a) {
@@ -406,7 +438,7 @@ Tensor dilate(Tensor x, double value) {
   Graph* g = x.ptr;
   Tensor z = hidden_like(g, x);
   kernels::dilate[dkey(z)](x.data_ptr(), value, z.data_ptr(), z.len(), z.context());
-  if (g->mode == Mode::train) attach_op(dilate_rev, z, {OpDatum::of(x), OpDatum::of(value), OpDatum::of(z)});
+  if (g->mode == Mode::train) attach_op(dilate_rev, z, {OpDatum::of(x), OpDatum::of(value), OpDatum::of(z)}, dilate_derive);
   return z;
 }
 static void relu_rev(const std::vector<OpDatum>& a) {
@@ -418,7 +450,7 @@ Tensor relu(Tensor x) {
   Graph* g = x.ptr;
   Tensor z = hidden_like(g, x);
   kernels::relu[dkey(z)](x.data_ptr(), z.data_ptr(), z.len(), z.context());
-  if (g->mode == Mode::train) attach_op(relu_rev, z, {OpDatum::of(x), OpDatum::of(z)});
+  if (g->mode == Mode::train) attach_op(relu_rev, z, {OpDatum::of(x), OpDatum::of(z)}, relu_derive);
   return z;
 }
 static void selu_rev(const std::vector<OpDatum>& a) {
@@ -430,8 +462,74 @@ Tensor selu(Tensor x) {
   Graph* g = x.ptr;
   Tensor z = hidden_like(g, x);
   kernels::selu[dkey(z)](x.data_ptr(), z.data_ptr(), z.len(), z.context());
-  if (g->mode == Mode::train) attach_op(selu_rev, z, {OpDatum::of(x), OpDatum::of(z)});
+  if (g->mode == Mode::train) attach_op(selu_rev, z, {OpDatum::of(x), OpDatum::of(z)}, selu_derive);
   return z;
+}
+
+// --- forward-mode derivatives of the element-wise ops (the `derive` of addition.zig:84-116, subtraction.zig:85-124,
+// hadamard.zig:85-160, negate.zig:55-61, translate.zig:60-62, dilate.zig:60-67, relu.zig:56-58).  The value algebra
+// is the reference's: a derivative is nothing (no dependence), a scalar (constant) or a tensor; scalars 0 and 1 are
+// folded away.  relu's derivative here applies the chain rule (the reference returns step(x) alone).
+using Deriv = std::optional<OpDatum>;
+static bool is_scalar(const Deriv& d) { return d && d->kind == OpDatum::scalar_k; }
+static Deriv d_negate(Graph* g, const Deriv& d) {
+  (void)g;
+  if (!d) return d;
+  if (is_scalar(d)) return OpDatum::of(-d->scalar);
+  return OpDatum::of(negate(d->tensor));
+}
+static Deriv d_add(const Deriv& a, const Deriv& b) {
+  if (!a) return b;
+  if (!b) return a;
+  if (is_scalar(a) && is_scalar(b)) return OpDatum::of(a->scalar + b->scalar);
+  if (is_scalar(a)) return a->scalar == 0.0 ? b : Deriv(OpDatum::of(translate(b->tensor, a->scalar)));
+  if (is_scalar(b)) return b->scalar == 0.0 ? a : Deriv(OpDatum::of(translate(a->tensor, b->scalar)));
+  return OpDatum::of(add(a->tensor, b->tensor));
+}
+// d * t for a derivative d and a tensor factor t
+static Deriv d_times(const Deriv& d, Tensor t) {
+  if (!d) return d;
+  if (is_scalar(d)) {
+    if (d->scalar == 0.0) return std::nullopt;
+    if (d->scalar == 1.0) return OpDatum::of(t);
+    return OpDatum::of(dilate(t, d->scalar));
+  }
+  return OpDatum::of(hadamard(t, d->tensor));
+}
+static Deriv add_derive(const std::vector<OpDatum>& a, Tensor wrt) { return d_add(derive(a[0].tensor, wrt), derive(a[1].tensor, wrt)); }
+static Deriv sub_derive(const std::vector<OpDatum>& a, Tensor wrt) {
+  return d_add(derive(a[0].tensor, wrt), d_negate(wrt.ptr, derive(a[1].tensor, wrt)));
+}
+static Deriv hadamard_derive(const std::vector<OpDatum>& a, Tensor wrt) {
+  Tensor x = a[0].tensor, y = a[1].tensor;
+  if (x.same(wrt) && y.same(wrt)) return OpDatum::of(dilate(x, 2.0));   // power rule (hadamard.zig:87-90)
+  return d_add(d_times(derive(x, wrt), y), d_times(derive(y, wrt), x));  // x'y + xy'
+}
+static Deriv negate_derive(const std::vector<OpDatum>& a, Tensor wrt) { return d_negate(wrt.ptr, derive(a[0].tensor, wrt)); }
+static Deriv translate_derive(const std::vector<OpDatum>& a, Tensor wrt) { return derive(a[0].tensor, wrt); }
+static Deriv dilate_derive(const std::vector<OpDatum>& a, Tensor wrt) {
+  const Deriv d = derive(a[0].tensor, wrt);
+  if (!d) return d;
+  if (is_scalar(d)) return OpDatum::of(d->scalar * a[1].scalar);
+  return OpDatum::of(dilate(d->tensor, a[1].scalar));
+}
+static Deriv relu_derive(const std::vector<OpDatum>& a, Tensor wrt) {
+  Tensor x = a[0].tensor;
+  const Deriv d = derive(x, wrt);
+  if (!d) return d;
+  Tensor step = hidden_like(x.ptr, x);
+  kernels::stepwise[dkey(x)](x.data_ptr(), step.data_ptr(), x.len(), x.context());   // 1 where x >= 0 (stepwise.zig:21)
+  return d_times(d, step);
+}
+static Deriv selu_derive(const std::vector<OpDatum>& a, Tensor wrt) {
+  Tensor x = a[0].tensor;
+  const Deriv d = derive(x, wrt);
+  if (!d) return d;
+  // selu'(x) through the reverse kernel: slope = 0 + 1 * selu'(x)
+  Tensor slope = hidden_like(x.ptr, x), ones = hidden_like(x.ptr, x);
+  algo::fill(slope, 0.0); algo::fill(ones, 1.0);
+  kernels::selu_reverse[dkey(x)](x.data_ptr(), slope.data_ptr(), ones.data_ptr(), x.len(), x.context());
+  return d_times(d, slope);
 }
 
 // --- reduce / broadcast (reduce.zig:98-182, broadcast.zig:96-183) ---
@@ -519,6 +617,13 @@ static void permutate_rev(const std::vector<OpDatum>& a) {
   for (size_t i = 0; i < perm.size(); ++i) inverse[perm[i]] = i;
   launch_permutate(y, y.grad_ptr(), x.grad_ptr(), 1.0, y.sizes(), inverse);
 }
+// every output element is one input element: the element-wise derivative is the permuted derivative of the input
+// (permutate.zig:71-73 panics here)
+static std::optional<OpDatum> permutate_derive(const std::vector<OpDatum>& a, Tensor wrt) {
+  const std::optional<OpDatum> d = derive(a[0].tensor, wrt);
+  if (!d || d->kind == OpDatum::scalar_k) return d;
+  return OpDatum::of(permutate(d->tensor, a[1].expr));
+}
 Tensor permutate(Tensor x, const std::string& expr) {
   const std::vector<size_t> perm = permutation_of(expr);
   const auto& s = x.sizes();
@@ -529,7 +634,7 @@ Tensor permutate(Tensor x, const std::string& expr) {
   Tensor y = g->tensor({Class::hid, x.dtype(), out});
   if (perm.size() == 2 && perm[0] == 1) kernels::permutate_ij_ji[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
   else launch_permutate(x, x.data_ptr(), y.data_ptr(), 0.0, s, perm);
-  if (g->mode == Mode::train) attach_op(permutate_rev, y, {OpDatum::of(x), OpDatum::of(expr), OpDatum::of(y)});
+  if (g->mode == Mode::train) attach_op(permutate_rev, y, {OpDatum::of(x), OpDatum::of(expr), OpDatum::of(y)}, permutate_derive);
   return y;
 }
 

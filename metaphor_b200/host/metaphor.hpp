@@ -13,6 +13,7 @@
 #include <cstddef>
 #include <cstdint>
 #include <map>
+#include <optional>
 #include <string>
 #include <vector>
 
@@ -63,6 +64,10 @@ struct Tensor {
   void reverse(ReverseCleanup cleanup) const;   // graph.zig:111-121
   void detach() const;                          // graph.zig:103-105
   void free() const;
+  // Forward-mode derivative d self / d wrt of an element-wise expression, as a new tensor of self's shape
+  // (graph.zig:123-148); nullopt when self does not depend on wrt or the graph is in eval mode.
+  std::optional<Tensor> derive(Tensor wrt) const;
+  bool same(Tensor o) const { return ptr == o.ptr && cls == o.cls && idx == o.idx; }
   std::vector<double> native() const;           // values copied to the host (widened to double)
   std::vector<double> native_grad() const;
 };
@@ -91,6 +96,9 @@ struct OpDatum {            // graph.zig:776-886 (tensor or scalar or expression
   static OpDatum of(const std::string& e) { OpDatum d; d.kind = expr_k; d.expr = e; return d; }
 };
 using ReverseFn = void (*)(const std::vector<OpDatum>& args);
+// Element-wise derivative of an op's output w.r.t. `wrt`: a scalar (the same value everywhere), a tensor, or
+// nullopt = no dependence (the `?OpDatum` of graph.zig:802-807).
+using DeriveFn = std::optional<OpDatum> (*)(const std::vector<OpDatum>& args, Tensor wrt);
 
 class Graph {
  public:
@@ -116,6 +124,7 @@ class Graph {
     std::vector<int> deps;
     std::vector<bool> attached, has_op;
     std::vector<ReverseFn> op_reverse;
+    std::vector<DeriveFn> op_derive;
     std::vector<std::vector<OpDatum>> op_args;
   };
   Block leaf_block, node_block;
@@ -131,7 +140,8 @@ class Graph {
 };
 
 void enable_gradient(Tensor t);                               // graph.zig:710-722 (+ zero fill)
-void attach_op(ReverseFn fn, Tensor out, const std::vector<OpDatum>& args);   // graph.zig:733-757
+void attach_op(ReverseFn fn, Tensor out, const std::vector<OpDatum>& args, DeriveFn derive = nullptr);   // graph.zig:733-757
+std::optional<OpDatum> derive(Tensor x, Tensor wrt);          // graph.zig:762-771: what op.derive functions call
 
 namespace algo {            // src/algo/mem.zig:24-39
 void fill(Tensor x, double value);

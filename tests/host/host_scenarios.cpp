@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <optional>
 #include <random>
 #include <string>
 #include <vector>
@@ -284,6 +285,55 @@ static void scenario_momentum_and_weight_files(mp::Stream stream, const char* di
   G->deinit();
 }
 
+// Forward-mode `derive` (graph.zig:123-148, the per-op derive functions): hand-derivable values, and agreement with
+// the reverse pass (for an element-wise f, reverse with a seed of ones leaves f'(x) in x.grad)
+static void scenario_derive(mp::Stream stream) {
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  mp::Tensor x = G->tensor({mp::Class::wgt, mp::Dtype::r32, {6}});
+  mp::Tensor y = G->tensor({mp::Class::inp, mp::Dtype::r32, {6}});
+  mp::algo::sequence(x, -2.5, 1.0);    // -2.5 -1.5 -0.5 0.5 1.5 2.5
+  mp::algo::sequence(y, 1.0, 1.0);     // 1 .. 6
+  // f = x*x + 3x - relu(x):  f' = 2x + 3 - step(x)
+  mp::Tensor f = mp::ops::sub(mp::ops::add(mp::ops::hadamard(x, x), mp::ops::dilate(x, 3.0)), mp::ops::relu(x));
+  std::optional<mp::Tensor> df = f.derive(x);
+  CHECK(df.has_value());
+  if (df) CHECK((df->native() == std::vector<double>{-2, 0, 2, 3, 5, 7}));
+  f.reverse(mp::ReverseCleanup::keep);
+  if (df) CHECK(df->native() == x.native_grad());
+  // constants: d(x + y)/dx = 1 everywhere, d(-(x + 4))/dx = -1, no dependence -> nothing
+  std::optional<mp::Tensor> d1 = mp::ops::add(x, y).derive(x);
+  CHECK(d1 && d1->native() == std::vector<double>(6, 1.0));
+  std::optional<mp::Tensor> d2 = mp::ops::negate(mp::ops::translate(x, 4.0)).derive(x);
+  CHECK(d2 && d2->native() == std::vector<double>(6, -1.0));
+  CHECK(!mp::ops::dilate(y, 2.0).derive(x).has_value());
+  CHECK(x.derive(x) && x.derive(x)->native() == std::vector<double>(6, 1.0));
+  // chain rule through relu and a product with a constant tensor: d(relu(2x) * y)/dx = 2 step(2x) y
+  std::optional<mp::Tensor> d3 = mp::ops::hadamard(mp::ops::relu(mp::ops::dilate(x, 2.0)), y).derive(x);
+  CHECK(d3 && d3->native() == (std::vector<double>{0, 0, 0, 8, 10, 12}));
+  // selu'(x) = lambda (x > 0), lambda alpha e^x otherwise
+  std::optional<mp::Tensor> d4 = mp::ops::selu(x).derive(x);
+  CHECK(d4.has_value());
+  if (d4) {
+    const double lam = 1.0507009873554805, al = 1.6732632423543772;
+    const std::vector<double> got = d4->native();
+    const double xs[6] = {-2.5, -1.5, -0.5, 0.5, 1.5, 2.5};
+    for (int i = 0; i < 6; ++i) CHECK(std::fabs(got[i] - (xs[i] > 0 ? lam : lam * al * std::exp(xs[i]))) <= 1e-6);
+  }
+  // through a permutation: d permute(x2*x2)/dx2 = permute(2 x2)
+  mp::Tensor x2 = G->tensor({mp::Class::wgt, mp::Dtype::r32, {2, 3}});
+  mp::algo::sequence(x2, 1.0, 1.0);    // [[1 2 3] [4 5 6]]
+  std::optional<mp::Tensor> d5 = mp::ops::permutate(mp::ops::hadamard(x2, x2), "ij->ji").derive(x2);
+  CHECK(d5 && d5->sizes() == (std::vector<size_t>{3, 2}) && d5->native() == (std::vector<double>{2, 8, 4, 10, 6, 12}));
+  // eval mode: no derivative
+  mp::Graph* E = mp::Graph::init({stream, mp::Mode::eval});
+  mp::Tensor xe = E->tensor({mp::Class::wgt, mp::Dtype::r32, {4}});
+  mp::algo::fill(xe, 1.0);
+  CHECK(!mp::ops::dilate(xe, 2.0).derive(xe).has_value());
+  mp::device::check();
+  E->deinit();
+  G->deinit();
+}
+
 int main(int argc, char** argv) {
   const int timing_iters = argc > 1 ? std::atoi(argv[1]) : 0;
   mp::device::init(0);
@@ -294,6 +344,7 @@ int main(int argc, char** argv) {
   scenario_feed_forward(s, timing_iters);
   scenario_row_ops(s);
   scenario_rank3(s);
+  scenario_derive(s);
   scenario_momentum_and_weight_files(s, argc > 2 ? argv[2] : "/tmp");
   mp::stream::deinit(s);
   std::printf(failures == 0 ? "ALL SCENARIOS PASSED\n" : "%d CHECKS FAILED\n", failures);
