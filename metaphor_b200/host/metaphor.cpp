@@ -532,47 +532,100 @@ static Deriv selu_derive(const std::vector<OpDatum>& a, Tensor wrt) {
   return d_times(d, slope);
 }
 
-// --- reduce / broadcast (reduce.zig:98-182, broadcast.zig:96-183) ---
+// --- reduce / broadcast (reduce.zig:98-182, broadcast.zig:96-183; grammar expression_parsing.zig:343-380) ---
+// "ijk->ik" sums over the indices missing on the right; the broadcast "ik->ijk" is its transpose (NOTES.md:27-35).
+// Any rank up to 6: trailing reduced indices are a row sum, leading ones a column sum of the flattened matrix
+// (the reference's rank-2 kernels); any other pattern first moves the reduced indices to the end with the general
+// permutation (through the stream's scratch buffer).
+struct ReducePlan {
+  std::vector<size_t> sizes, perm, moved_sizes, inverse, out_sizes;   // perm: kept indices in output order, then the reduced ones
+  bool trailing = false, leading = false;
+  size_t kept = 1, red = 1;
+};
+static ReducePlan plan_reduce(const std::string& expr, const std::vector<size_t>& sizes, const char* who) {
+  const size_t arrow = expr.find("->");
+  if (arrow == std::string::npos) panic("reduce / broadcast: expression has no \"->\"");
+  const std::string lhs = expr.substr(0, arrow), rhs = expr.substr(arrow + 2);
+  if (lhs.size() != sizes.size() || lhs.size() > 6 || lhs.empty()) { std::printf("%s: ", who); panic("the expression's rank differs from the tensor's"); }
+  if (rhs.size() > lhs.size()) { std::printf("%s: ", who); panic("found extra indices in the expression"); }
+  ReducePlan p;
+  p.sizes = sizes;
+  p.perm.assign(lhs.size(), 0);
+  p.out_sizes.assign(rhs.size(), 0);
+  size_t n_red = 0;
+  for (size_t i = 0; i < lhs.size(); ++i) {
+    if (lhs[i] < 'a' || lhs[i] > 'z' || lhs.find(lhs[i]) != i) panic("reduce / broadcast: indices must be distinct lower case characters");
+    const size_t j = rhs.find(lhs[i]);
+    if (j == std::string::npos) { p.perm[i] = rhs.size() + n_red++; p.red *= sizes[i]; }
+    else { p.perm[i] = j; p.out_sizes[j] = sizes[i]; p.kept *= sizes[i]; }
+  }
+  for (size_t j = 0; j < rhs.size(); ++j)
+    if (lhs.find(rhs[j]) == std::string::npos || rhs.find(rhs[j]) != j) panic("reduce / broadcast: the short side must be a subset of the long side");
+  if (p.out_sizes.empty()) p.out_sizes = {1};   // full reduction
+  p.trailing = true;
+  for (size_t i = 0; i < lhs.size(); ++i) p.trailing = p.trailing && p.perm[i] == i;
+  p.leading = !p.trailing;
+  for (size_t i = 0; i < lhs.size(); ++i)   // reduced indices first, kept ones in order behind them
+    p.leading = p.leading && p.perm[i] == (i < n_red ? rhs.size() + i : i - n_red);
+  p.moved_sizes.assign(lhs.size(), 0);
+  p.inverse.assign(lhs.size(), 0);
+  for (size_t i = 0; i < lhs.size(); ++i) { p.moved_sizes[p.perm[i]] = sizes[i]; p.inverse[p.perm[i]] = i; }
+  return p;
+}
+static void call_permutate(int key, const void* src, void* dst, double alpha, const std::vector<size_t>& sizes,
+                           const std::vector<size_t>& perm, StreamContext ctx) {
+  len_t sz[8], pm[8];
+  for (size_t i = 0; i < sizes.size(); ++i) { sz[i] = sizes[i]; pm[i] = perm[i]; }
+  kernels::permutate[key](src, dst, alpha, sz, pm, sizes.size(), ctx);
+}
+// small = sum over the reduced indices of big (+ alpha * small)
+static void run_reduce(Graph* g, int key, size_t elem, const ReducePlan& p, const void* big, void* small, double alpha, StreamContext ctx) {
+  if (p.trailing) { kernels::reduce_ij_i[key](big, small, alpha, p.kept, p.red, ctx); return; }
+  if (p.leading) { kernels::reduce_ij_j[key](big, small, alpha, p.red, p.kept, ctx); return; }
+  void* tmp = g->scratch(p.kept * p.red * elem);
+  call_permutate(key, big, tmp, 0.0, p.sizes, p.perm, ctx);
+  kernels::reduce_ij_i[key](tmp, small, alpha, p.kept, p.red, ctx);
+}
+// big = small repeated along the reduced indices (+ alpha * big)
+static void run_broadcast(Graph* g, int key, size_t elem, const ReducePlan& p, const void* small, void* big, double alpha, StreamContext ctx) {
+  if (p.trailing) { kernels::broadcast_i_ij[key](small, big, alpha, p.kept, p.red, ctx); return; }
+  if (p.leading) { kernels::broadcast_j_ij[key](small, big, alpha, p.red, p.kept, ctx); return; }
+  void* tmp = g->scratch(p.kept * p.red * elem);
+  kernels::broadcast_i_ij[key](small, tmp, 0.0, p.kept, p.red, ctx);
+  call_permutate(key, tmp, big, alpha, p.moved_sizes, p.inverse, ctx);
+}
 static void reduce_rev(const std::vector<OpDatum>& a) {
   Tensor x = a[0].tensor, y = a[2].tensor;
   enable_gradient(x);
-  const auto& s = x.sizes();
-  if (a[1].expr == "ij->i") kernels::broadcast_i_ij[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
-  else kernels::broadcast_j_ij[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+  const ReducePlan p = plan_reduce(a[1].expr, x.sizes(), "reduce");
+  run_broadcast(x.ptr, dkey(y), dtype_size(y.dtype()), p, y.grad_ptr(), x.grad_ptr(), 1.0, x.context());
 }
 Tensor reduce(Tensor x, const std::string& expr) {
-  const auto& s = x.sizes();
-  if (s.size() != 2) panic("reduce needs a rank-2 tensor");
   Graph* g = x.ptr;
-  Tensor y;
-  if (expr == "ij->i") {
-    y = g->tensor({Class::hid, x.dtype(), {s[0]}});
-    kernels::reduce_ij_i[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
-  } else if (expr == "ij->j") {
-    y = g->tensor({Class::hid, x.dtype(), {s[1]}});
-    kernels::reduce_ij_j[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, s[0], s[1], y.context());
-  } else panic("reduce: unknown expression");
+  const ReducePlan p = plan_reduce(expr, x.sizes(), "reduce");
+  Tensor y = g->tensor({Class::hid, x.dtype(), p.out_sizes});
+  run_reduce(g, dkey(y), dtype_size(y.dtype()), p, x.data_ptr(), y.data_ptr(), 0.0, y.context());
   if (g->mode == Mode::train) attach_op(reduce_rev, y, {OpDatum::of(x), OpDatum::of(expr), OpDatum::of(y)});
   return y;
+}
+// "i->ij": the plan is the one of the opposite reduction "ij->i" over the target's sizes
+static std::string flipped(const std::string& expr) {
+  const size_t arrow = expr.find("->");
+  if (arrow == std::string::npos) panic("broadcast: expression has no \"->\"");
+  return expr.substr(arrow + 2) + "->" + expr.substr(0, arrow);
 }
 static void broadcast_rev(const std::vector<OpDatum>& a) {
   Tensor x = a[0].tensor, y = a[2].tensor;
   enable_gradient(x);
-  const auto& s = y.sizes();
-  if (a[1].expr == "i->ij") kernels::reduce_ij_i[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
-  else kernels::reduce_ij_j[dkey(y)](y.grad_ptr(), x.grad_ptr(), 1.0, s[0], s[1], x.context());
+  const ReducePlan p = plan_reduce(flipped(a[1].expr), y.sizes(), "broadcast");
+  run_reduce(x.ptr, dkey(y), dtype_size(y.dtype()), p, y.grad_ptr(), x.grad_ptr(), 1.0, x.context());
 }
 Tensor broadcast(Tensor x, const std::vector<size_t>& sizes, const std::string& expr) {
-  if (sizes.size() != 2 || x.sizes().size() != 1) panic("broadcast: rank-1 source and rank-2 target expected");
   Graph* g = x.ptr;
+  const ReducePlan p = plan_reduce(flipped(expr), sizes, "broadcast");
+  if (x.sizes() != p.out_sizes) panic("broadcast: the source's sizes differ from the target's sizes at its indices");
   Tensor y = g->tensor({Class::hid, x.dtype(), sizes});
-  if (expr == "i->ij") {
-    if (x.sizes()[0] != sizes[0]) panic("broadcast i->ij: size mismatch");
-    kernels::broadcast_i_ij[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, sizes[0], sizes[1], y.context());
-  } else if (expr == "j->ij") {
-    if (x.sizes()[0] != sizes[1]) panic("broadcast j->ij: size mismatch");
-    kernels::broadcast_j_ij[dkey(y)](x.data_ptr(), y.data_ptr(), 0.0, sizes[0], sizes[1], y.context());
-  } else panic("broadcast: unknown expression");
+  run_broadcast(g, dkey(y), dtype_size(y.dtype()), p, x.data_ptr(), y.data_ptr(), 0.0, y.context());
   if (g->mode == Mode::train) attach_op(broadcast_rev, y, {OpDatum::of(x), OpDatum::of(expr), OpDatum::of(y)});
   return y;
 }

@@ -159,8 +159,8 @@ Tensor translate(Tensor x, double value);
 Tensor dilate(Tensor x, double value);
 Tensor relu(Tensor x);
 Tensor selu(Tensor x);
-Tensor reduce(Tensor x, const std::string& expr);                       // "ij->i", "ij->j"
-Tensor broadcast(Tensor x, const std::vector<size_t>& sizes, const std::string& expr);   // "i->ij", "j->ij"
+Tensor reduce(Tensor x, const std::string& expr);                       // "ij->i", "ij->j", and any rank <= 6: "ijk->ik", "ijk->j", ...
+Tensor broadcast(Tensor x, const std::vector<size_t>& sizes, const std::string& expr);   // "i->ij", "j->ij", "ik->ijk", ...
 Tensor inner_product(Tensor x, Tensor y, const std::string& expr);      // "ij,jk->ik", "ij,kj->ik", "ji,jk->ik", "i,ij->j", "ij,j->i";
                                                                         // batched "bij,bjk->bik" (and the kj / ji forms), "_ij,_jk->_ik" = optional batch
 Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string& expr);

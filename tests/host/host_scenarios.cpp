@@ -334,6 +334,51 @@ static void scenario_derive(mp::Stream stream) {
   G->deinit();
 }
 
+// Rank-3 reduce / broadcast (NOTES.md:27-35): "ijk->ik" sums over j, its reverse broadcasts the gradient back
+static void scenario_rank3_reduce(mp::Stream stream) {
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  const size_t I = 2, J = 3, K = 4;
+  mp::Tensor x = G->tensor({mp::Class::wgt, mp::Dtype::r32, {I, J, K}});
+  mp::algo::sequence(x, 1.0, 1.0);     // x[i,j,k] = 1 + (i*J + j)*K + k
+  auto at = [&](size_t i, size_t j, size_t k) { return 1.0 + (i * J + j) * K + k; };
+  struct Case { const char* expr; std::vector<size_t> out; };
+  const Case cases[] = {{"ijk->ij", {I, J}}, {"ijk->jk", {J, K}}, {"ijk->ik", {I, K}}, {"ijk->j", {J}}, {"ijk->ki", {K, I}},
+                        {"ijk->k", {K}}, {"ijk->i", {I}}};
+  for (const Case& c : cases) {
+    mp::Tensor y = mp::ops::reduce(x, c.expr);
+    CHECK(y.sizes() == c.out);
+    const std::string rhs = std::string(c.expr).substr(5);
+    std::vector<double> want(y.len(), 0.0);
+    for (size_t i = 0; i < I; ++i) for (size_t j = 0; j < J; ++j) for (size_t k = 0; k < K; ++k) {
+      size_t o = 0;
+      for (char ch : rhs) o = o * (ch == 'i' ? I : ch == 'j' ? J : K) + (ch == 'i' ? i : ch == 'j' ? j : k);
+      want[o] += at(i, j, k);
+    }
+    CHECK(y.native() == want);
+  }
+  // reverse of "ijk->ik" weighted by w[i,k]: x.grad[i,j,k] = w[i,k]
+  mp::Tensor w = G->tensor({mp::Class::inp, mp::Dtype::r32, {I, K}});
+  mp::algo::sequence(w, 0.5, 0.5);
+  mp::Tensor z = mp::ops::hadamard(mp::ops::reduce(x, "ijk->ik"), w);
+  z.reverse(mp::ReverseCleanup::keep);
+  std::vector<double> gwant(I * J * K);
+  for (size_t i = 0; i < I; ++i) for (size_t j = 0; j < J; ++j) for (size_t k = 0; k < K; ++k) gwant[(i * J + j) * K + k] = 0.5 + 0.5 * (i * K + k);
+  CHECK(x.native_grad() == gwant);
+  // broadcast "ik->ijk" equals that gradient pattern; its reverse sums over j
+  mp::Tensor v = G->tensor({mp::Class::wgt, mp::Dtype::r32, {I, K}});
+  mp::algo::sequence(v, 0.5, 0.5);
+  mp::Tensor b = mp::ops::broadcast(v, {I, J, K}, "ik->ijk");
+  CHECK(b.native() == gwant);
+  mp::Tensor b2 = mp::ops::broadcast(v, {K, J, I}, "ik->kji");   // target order differs from the source order
+  std::vector<double> want2(I * J * K);
+  for (size_t k = 0; k < K; ++k) for (size_t j = 0; j < J; ++j) for (size_t i = 0; i < I; ++i) want2[(k * J + j) * I + i] = 0.5 + 0.5 * (i * K + k);
+  CHECK(b2.native() == want2);
+  b.reverse(mp::ReverseCleanup::keep);
+  CHECK(v.native_grad() == std::vector<double>(I * K, static_cast<double>(J)));
+  mp::device::check();
+  G->deinit();
+}
+
 int main(int argc, char** argv) {
   const int timing_iters = argc > 1 ? std::atoi(argv[1]) : 0;
   mp::device::init(0);
@@ -345,6 +390,7 @@ int main(int argc, char** argv) {
   scenario_row_ops(s);
   scenario_rank3(s);
   scenario_derive(s);
+  scenario_rank3_reduce(s);
   scenario_momentum_and_weight_files(s, argc > 2 ? argv[2] : "/tmp");
   mp::stream::deinit(s);
   std::printf(failures == 0 ? "ALL SCENARIOS PASSED\n" : "%d CHECKS FAILED\n", failures);
