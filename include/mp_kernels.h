@@ -175,6 +175,13 @@ MP_DECL3(embedding_reverse, const void* ids, const void* gy, void* gtable, len_t
 MP_DECL3(causal_conv1d_silu, const void* x, len_t x_pitch, const void* w, const void* bias, void* y, len_t y_pitch, len_t batch, len_t len, len_t channels, len_t width, StreamContext stream)
 /* gx (overwritten), gw += (acc [channels, width]), gbias += (acc [channels], may be NULL) */
 MP_DECL3(causal_conv1d_silu_reverse, const void* x, len_t x_pitch, const void* w, const void* bias, const void* gy, len_t gy_pitch, void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t channels, len_t width, StreamContext stream)
+/* The same convolution over sum(seg_channels) consecutive channels of x, cut into nseg <= 4 consecutive segments whose
+ * outputs (reverse: incoming gradients) live in buffers of their own: ys[i] / gys[i] with row pitch pitches[i] hold
+ * seg_channels[i] channels.  w, bias, gx, gw, gbias are indexed by the channel of x.  ys / gys / pitches / seg_channels
+ * are HOST arrays, read before the call returns.  One launch for r16 with 16-byte-aligned rows (x, B and C of a Mamba-2
+ * block are neighbouring column ranges of one projection), otherwise one launch per segment. */
+MP_DECL3(causal_conv1d_silu_segments, const void* x, len_t x_pitch, const void* w, const void* bias, void* const* ys, const len_t* y_pitches, const len_t* seg_channels, len_t nseg, len_t batch, len_t len, len_t width, StreamContext stream)
+MP_DECL3(causal_conv1d_silu_segments_reverse, const void* x, len_t x_pitch, const void* w, const void* bias, const void* const* gys, const len_t* gy_pitches, const len_t* seg_channels, len_t nseg, void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t width, StreamContext stream)
 /* out[r,h] = softplus(raw[r,h] + bias[h]); raw: T with row pitch; bias, out: acc */
 MP_DECL3(softplus_bias, const void* raw, len_t raw_pitch, const void* bias, void* out, len_t rows, len_t heads, StreamContext stream)
 /* graw[r,h] = gdt[r,h]*sigmoid(raw[r,h] + bias[h]) (T, pitched); gbias[h] += sum_r graw (acc, may be NULL) */

@@ -66,6 +66,8 @@ LAUNCHERS = {
     "embedding_reverse": [P, P, P, L, L, L, CTX],
     "causal_conv1d_silu": [P, L, P, P, P, L, L, L, L, L, CTX],
     "causal_conv1d_silu_reverse": [P, L, P, P, P, L, P, L, P, P, L, L, L, L, CTX],
+    "causal_conv1d_silu_segments": [P, L, P, P, P, P, P, L, L, L, L, CTX],
+    "causal_conv1d_silu_segments_reverse": [P, L, P, P, P, P, P, L, P, L, P, P, L, L, L, CTX],
     "softplus_bias": [P, L, P, P, L, L, CTX],
     "softplus_bias_reverse": [P, L, P, P, P, L, P, L, L, CTX],
     "ssd_gate": [P, P, P, P, L, P, L, L, L, CTX],

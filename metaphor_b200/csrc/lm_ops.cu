@@ -310,21 +310,45 @@ constexpr int CT_L = 64;            // steps per tile
 constexpr int CT_LANES = 4;         // time lanes: 256 threads = 64 channels x 4 lanes
 constexpr int CT_STEPS = CT_L / CT_LANES;
 
+// The channels of one convolution may be cut into up to CONV_MAX_SEGS consecutive segments whose outputs
+// (forward: y; reverse: the incoming gy) live in buffers of their own: one launch then serves what would be
+// one launch per segment (x / B / C of a Mamba-2 block share one convolution over neighbouring columns).
+constexpr int CONV_MAX_SEGS = 4;
+struct ConvSegs {
+  int nseg;
+  int blk_begin[CONV_MAX_SEGS + 1];   // first channel block (of CT_C channels) of every segment
+  int ch_begin[CONV_MAX_SEGS];        // first channel
+  int ch_count[CONV_MAX_SEGS];        // channels (a multiple of 8)
+  const void* ptr[CONV_MAX_SEGS];     // the segment's own buffer (y resp. gy), channel 0 of the segment at column 0
+  unsigned long long pitch[CONV_MAX_SEGS];
+};
+__device__ __forceinline__ int conv_segment_of(const ConvSegs& sg, int block) {
+  int s = 0;
+#pragma unroll
+  for (int i = 1; i < CONV_MAX_SEGS; ++i)
+    if (i < sg.nseg && block >= sg.blk_begin[i]) s = i;
+  return s;
+}
+
 // Forward with the same staging: x tile (+ W - 1 rows before it) in, y tile out, 16 steps per thread.
 template <int W>
 __global__ void __launch_bounds__(256) conv1d_silu_tiled_kernel(const __half* __restrict__ x, size_t xp, const __half* __restrict__ w,
-                                                                const __half* __restrict__ bias, __half* __restrict__ y, size_t yp,
-                                                                int L, int C, int tiles_per_cta) {
+                                                                const __half* __restrict__ bias, const ConvSegs sg, int L,
+                                                                int tiles_per_cta) {
   constexpr int H = W - 1;
   __shared__ __align__(16) __half xs[CT_L + H][CT_C];    // row r = step l0 - H + r
   __shared__ __align__(16) __half ys[CT_L][CT_C];
   const int tid = threadIdx.x;
   const int c = tid % CT_C, lane = tid / CT_C;
-  const int cbase = blockIdx.x * CT_C;
+  const int seg = conv_segment_of(sg, blockIdx.x);
+  const int local = (blockIdx.x - sg.blk_begin[seg]) * CT_C;   // first channel of the tile inside its segment
+  const int cbase = sg.ch_begin[seg] + local;                  // ... and in x / w / bias
+  const int C = sg.ch_begin[seg] + sg.ch_count[seg];           // channels past the segment's end belong to the next tile row
   const bool live_c = cbase + c < C;
   const size_t b = blockIdx.z;
+  const size_t yp = sg.pitch[seg];
   const __half* xb = x + b * L * xp + cbase;
-  __half* yb = y + b * L * yp + cbase;
+  __half* yb = static_cast<__half*>(const_cast<void*>(sg.ptr[seg])) + b * L * yp + local;
   float wk[W], bs = 0.f;
 #pragma unroll
   for (int k = 0; k < W; ++k) wk[k] = live_c ? __half2float(w[static_cast<size_t>(cbase + c) * W + k]) : 0.f;
@@ -370,9 +394,9 @@ __global__ void __launch_bounds__(256) conv1d_silu_tiled_kernel(const __half* __
 template <int W>
 __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __half* __restrict__ x, size_t xp,
                                                                         const __half* __restrict__ w, const __half* __restrict__ bias,
-                                                                        const __half* __restrict__ gy, size_t gyp,
-                                                                        __half* __restrict__ gx, size_t gxp, float* __restrict__ gw,
-                                                                        float* __restrict__ gbias, int L, int C, int tiles_per_cta) {
+                                                                        const ConvSegs sg, __half* __restrict__ gx, size_t gxp,
+                                                                        float* __restrict__ gw, float* __restrict__ gbias, int L,
+                                                                        int tiles_per_cta) {
   constexpr int H = W - 1;
   __shared__ __align__(16) __half xs[CT_L + 2 * H][CT_C];    // row r = step l0 - H + r
   __shared__ __align__(16) __half gys[CT_L + H][CT_C];       // row r = step l0 + r
@@ -380,11 +404,15 @@ __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __
   __shared__ float red[CT_LANES][CT_C][W + 1];
   const int tid = threadIdx.x;
   const int c = tid % CT_C, lane = tid / CT_C;
-  const int cbase = blockIdx.x * CT_C;
+  const int seg = conv_segment_of(sg, blockIdx.x);
+  const int local = (blockIdx.x - sg.blk_begin[seg]) * CT_C;
+  const int cbase = sg.ch_begin[seg] + local;
+  const int C = sg.ch_begin[seg] + sg.ch_count[seg];
   const bool live_c = cbase + c < C;
   const size_t b = blockIdx.z;
+  const size_t gyp = sg.pitch[seg];
   const __half* xb = x + b * L * xp + cbase;
-  const __half* gyb = gy + b * L * gyp + cbase;
+  const __half* gyb = static_cast<const __half*>(sg.ptr[seg]) + b * L * gyp + local;
   __half* gxb = gx + b * L * gxp + cbase;
   float wk[W], bs = 0.f, gwk[W], gbs = 0.f;
 #pragma unroll
@@ -896,6 +924,60 @@ void conv_reverse_dispatch(const T* x, size_t xp, const T* w, const T* bias, con
   MP_LAUNCH_CHECK();
 }
 
+// Segment table for the tiled r16 kernels; false when a segment does not allow 16-byte accesses.
+static bool conv_make_segs(ConvSegs& sg, const void* const* bufs, const len_t* pitches, const len_t* counts, len_t nseg) {
+  if (nseg == 0 || nseg > CONV_MAX_SEGS) return false;
+  sg.nseg = static_cast<int>(nseg);
+  int blk = 0, ch = 0;
+  for (int i = 0; i < sg.nseg; ++i) {
+    if (!vec_ok<__half>(bufs[i], pitches[i], counts[i]) || counts[i] == 0) return false;
+    sg.blk_begin[i] = blk;
+    sg.ch_begin[i] = ch;
+    sg.ch_count[i] = static_cast<int>(counts[i]);
+    sg.ptr[i] = bufs[i];
+    sg.pitch[i] = pitches[i];
+    blk += static_cast<int>((counts[i] + CT_C - 1) / CT_C);
+    ch += static_cast<int>(counts[i]);
+  }
+  for (int i = sg.nseg; i <= CONV_MAX_SEGS; ++i) sg.blk_begin[i] = blk;
+  return true;
+}
+static dim3 conv_tiled_grid(const ConvSegs& sg, len_t len, len_t batch, int* tiles_per_cta) {
+  const size_t ltiles = (len + CT_L - 1) / CT_L;
+  const size_t per = ltiles >= 2 ? 2 : 1;   // time tiles per CTA (measured best of 1, 2, 4, 8 at 1536 and 128 channels)
+  *tiles_per_cta = static_cast<int>(per);
+  return dim3(static_cast<unsigned>(sg.blk_begin[sg.nseg]), static_cast<unsigned>((ltiles + per - 1) / per), static_cast<unsigned>(batch));
+}
+static bool conv_tiles_enabled(len_t width) { return width >= 2 && width <= 4 && !getenv("MP_CONV_NO_TILES"); }
+static void conv_tiled_forward(const void* x, len_t x_pitch, const void* w, const void* bias, const ConvSegs& sg, len_t batch, len_t len,
+                               len_t width, StreamContext ctx) {
+  int tp = 1;
+  const dim3 grid = conv_tiled_grid(sg, len, batch, &tp);
+  const int L = static_cast<int>(len);
+  cudaStream_t st = mp_stream(ctx);
+  const __half* xh = static_cast<const __half*>(x); const __half* wh = static_cast<const __half*>(w);
+  const __half* bh = static_cast<const __half*>(bias);
+  if (width == 4) conv1d_silu_tiled_kernel<4><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
+  else if (width == 3) conv1d_silu_tiled_kernel<3><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
+  else conv1d_silu_tiled_kernel<2><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
+  MP_LAUNCH_CHECK();
+}
+static void conv_tiled_reverse(const void* x, len_t x_pitch, const void* w, const void* bias, const ConvSegs& sg, void* gx, len_t gx_pitch,
+                               void* gw, void* gbias, len_t batch, len_t len, len_t width, StreamContext ctx) {
+  int tp = 1;
+  const dim3 grid = conv_tiled_grid(sg, len, batch, &tp);
+  const int L = static_cast<int>(len);
+  cudaStream_t st = mp_stream(ctx);
+  const __half* xh = static_cast<const __half*>(x); const __half* wh = static_cast<const __half*>(w);
+  const __half* bh = static_cast<const __half*>(bias);
+  __half* gxh = static_cast<__half*>(gx);
+  float* gwf = static_cast<float*>(gw); float* gbf = static_cast<float*>(gbias);
+  if (width == 4) conv1d_silu_reverse_tiled_kernel<4><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
+  else if (width == 3) conv1d_silu_reverse_tiled_kernel<3><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
+  else conv1d_silu_reverse_tiled_kernel<2><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
+  MP_LAUNCH_CHECK();
+}
+
 template <typename T>
 void causal_conv1d_silu_impl(const void* x, len_t x_pitch, const void* w, const void* bias, void* y, len_t y_pitch, len_t batch,
                              len_t len, len_t channels, len_t width, StreamContext ctx) {
@@ -903,20 +985,10 @@ void causal_conv1d_silu_impl(const void* x, len_t x_pitch, const void* w, const 
   constexpr int PN = Pack<T>::N;
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(y, y_pitch, channels);
   if constexpr (std::is_same<T, __half>::value) {
-    if (v && width >= 2 && width <= 4 && !getenv("MP_CONV_NO_TILES")) {
-      const unsigned cblocks = static_cast<unsigned>((channels + CT_C - 1) / CT_C);
-      const size_t ltiles = (len + CT_L - 1) / CT_L;
-      const size_t per = ltiles >= 2 ? 2 : 1;   // time tiles per CTA (measured best of 1, 2, 4, 8 at 1536 and 128 channels)
-      const dim3 grid(cblocks, static_cast<unsigned>((ltiles + per - 1) / per), static_cast<unsigned>(batch));
-      const int L = static_cast<int>(len), C = static_cast<int>(channels), tp = static_cast<int>(per);
-      cudaStream_t st = mp_stream(ctx);
-      const __half* xh = static_cast<const __half*>(x); const __half* wh = static_cast<const __half*>(w);
-      const __half* bh = static_cast<const __half*>(bias);
-      __half* yh = static_cast<__half*>(y);
-      if (width == 4) conv1d_silu_tiled_kernel<4><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, yh, y_pitch, L, C, tp);
-      else if (width == 3) conv1d_silu_tiled_kernel<3><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, yh, y_pitch, L, C, tp);
-      else conv1d_silu_tiled_kernel<2><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, yh, y_pitch, L, C, tp);
-      MP_LAUNCH_CHECK();
+    ConvSegs sg;
+    const void* bufs[1] = {y};
+    if (v && conv_tiles_enabled(width) && conv_make_segs(sg, bufs, &y_pitch, &channels, 1)) {
+      conv_tiled_forward(x, x_pitch, w, bias, sg, batch, len, width, ctx);
       return;
     }
   }
@@ -936,21 +1008,10 @@ void causal_conv1d_silu_reverse_impl(const void* x, len_t x_pitch, const void* w
   constexpr int RV = PN > 4 ? 2 : PN;   // at most 4 channels per thread (register footprint)
   const bool v = vec_ok<T>(x, x_pitch, channels) && vec_ok<T>(gy, gy_pitch, channels) && vec_ok<T>(gx, gx_pitch, channels);
   if constexpr (std::is_same<T, __half>::value) {
-    if (v && width >= 2 && width <= 4 && !getenv("MP_CONV_NO_TILES")) {
-      const unsigned cblocks = static_cast<unsigned>((channels + CT_C - 1) / CT_C);
-      const size_t ltiles = (len + CT_L - 1) / CT_L;
-      const size_t per = ltiles >= 2 ? 2 : 1;   // time tiles per CTA (measured best of 1, 2, 4, 8 at 1536 and 128 channels)
-      const dim3 grid(cblocks, static_cast<unsigned>((ltiles + per - 1) / per), static_cast<unsigned>(batch));
-      const int L = static_cast<int>(len), C = static_cast<int>(channels), tp = static_cast<int>(per);
-      cudaStream_t st = mp_stream(ctx);
-      const __half* xh = static_cast<const __half*>(x); const __half* wh = static_cast<const __half*>(w);
-      const __half* bh = static_cast<const __half*>(bias); const __half* gyh = static_cast<const __half*>(gy);
-      __half* gxh = static_cast<__half*>(gx);
-      float* gwf = static_cast<float*>(gw); float* gbf = static_cast<float*>(gbias);
-      if (width == 4) conv1d_silu_reverse_tiled_kernel<4><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, gyh, gy_pitch, gxh, gx_pitch, gwf, gbf, L, C, tp);
-      else if (width == 3) conv1d_silu_reverse_tiled_kernel<3><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, gyh, gy_pitch, gxh, gx_pitch, gwf, gbf, L, C, tp);
-      else conv1d_silu_reverse_tiled_kernel<2><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, gyh, gy_pitch, gxh, gx_pitch, gwf, gbf, L, C, tp);
-      MP_LAUNCH_CHECK();
+    ConvSegs sg;
+    const void* bufs[1] = {gy};
+    if (v && conv_tiles_enabled(width) && conv_make_segs(sg, bufs, &gy_pitch, &channels, 1)) {
+      conv_tiled_reverse(x, x_pitch, w, bias, sg, gx, gx_pitch, gw, gbias, batch, len, width, ctx);
       return;
     }
   }
@@ -960,6 +1021,58 @@ void causal_conv1d_silu_reverse_impl(const void* x, len_t x_pitch, const void* w
   else conv_reverse_dispatch<T, 1>(static_cast<const T*>(x), x_pitch, static_cast<const T*>(w), static_cast<const T*>(bias),
                                    static_cast<const T*>(gy), gy_pitch, static_cast<T*>(gx), gx_pitch, static_cast<A*>(gw),
                                    static_cast<A*>(gbias), batch, len, channels, width, mp_stream(ctx));
+}
+
+// Segmented forms: the convolution covers sum(seg_channels) consecutive channels of x (w, bias, gx, gw, gbias are indexed
+// by that channel), segment i writes y (reads gy) in its own buffer ys[i] / gys[i] with pitch pitches[i].  One launch on
+// the tiled r16 path, otherwise one launch per segment.
+template <typename T>
+void causal_conv1d_silu_segments_impl(const void* x, len_t x_pitch, const void* w, const void* bias, void* const* ys, const len_t* y_pitches,
+                                      const len_t* seg_channels, len_t nseg, len_t batch, len_t len, len_t width, StreamContext ctx) {
+  if (batch == 0 || len == 0 || nseg == 0) return;
+  if (ys == nullptr || y_pitches == nullptr || seg_channels == nullptr) MP_FATAL("causal_conv1d_silu_segments: the segment arrays are host arrays of nseg entries");
+  len_t total = 0;
+  for (len_t i = 0; i < nseg; ++i) total += seg_channels[i];
+  if constexpr (std::is_same<T, __half>::value) {
+    ConvSegs sg;
+    if (vec_ok<T>(x, x_pitch, total) && conv_tiles_enabled(width) &&
+        conv_make_segs(sg, const_cast<const void* const*>(ys), y_pitches, seg_channels, nseg)) {
+      conv_tiled_forward(x, x_pitch, w, bias, sg, batch, len, width, ctx);
+      return;
+    }
+  }
+  len_t c0 = 0;
+  for (len_t i = 0; i < nseg; ++i) {
+    causal_conv1d_silu_impl<T>(static_cast<const T*>(x) + c0, x_pitch, static_cast<const T*>(w) + c0 * width,
+                               bias ? static_cast<const T*>(bias) + c0 : nullptr, ys[i], y_pitches[i], batch, len, seg_channels[i], width, ctx);
+    c0 += seg_channels[i];
+  }
+}
+template <typename T>
+void causal_conv1d_silu_segments_reverse_impl(const void* x, len_t x_pitch, const void* w, const void* bias, const void* const* gys,
+                                              const len_t* gy_pitches, const len_t* seg_channels, len_t nseg, void* gx, len_t gx_pitch,
+                                              void* gw, void* gbias, len_t batch, len_t len, len_t width, StreamContext ctx) {
+  if (batch == 0 || len == 0 || nseg == 0) return;
+  using A = typename Acc<T>::type;
+  if (gys == nullptr || gy_pitches == nullptr || seg_channels == nullptr) MP_FATAL("causal_conv1d_silu_segments_reverse: the segment arrays are host arrays of nseg entries");
+  len_t total = 0;
+  for (len_t i = 0; i < nseg; ++i) total += seg_channels[i];
+  if constexpr (std::is_same<T, __half>::value) {
+    ConvSegs sg;
+    if (vec_ok<T>(x, x_pitch, total) && vec_ok<T>(gx, gx_pitch, total) && conv_tiles_enabled(width) &&
+        conv_make_segs(sg, gys, gy_pitches, seg_channels, nseg)) {
+      conv_tiled_reverse(x, x_pitch, w, bias, sg, gx, gx_pitch, gw, gbias, batch, len, width, ctx);
+      return;
+    }
+  }
+  len_t c0 = 0;
+  for (len_t i = 0; i < nseg; ++i) {
+    causal_conv1d_silu_reverse_impl<T>(static_cast<const T*>(x) + c0, x_pitch, static_cast<const T*>(w) + c0 * width,
+                                       bias ? static_cast<const T*>(bias) + c0 : nullptr, gys[i], gy_pitches[i], static_cast<T*>(gx) + c0, gx_pitch,
+                                       static_cast<A*>(gw) + c0 * width, gbias ? static_cast<A*>(gbias) + c0 : nullptr, batch, len,
+                                       seg_channels[i], width, ctx);
+    c0 += seg_channels[i];
+  }
 }
 
 template <typename T>
@@ -1093,6 +1206,15 @@ MP_STAMP3(causal_conv1d_silu_reverse,
           (const void* x, len_t x_pitch, const void* w, const void* bias, const void* gy, len_t gy_pitch, void* gx, len_t gx_pitch, void* gw,
            void* gbias, len_t batch, len_t len, len_t channels, len_t width, StreamContext ctx),
           (x, x_pitch, w, bias, gy, gy_pitch, gx, gx_pitch, gw, gbias, batch, len, channels, width, ctx))
+MP_STAMP3(causal_conv1d_silu_segments,
+          (const void* x, len_t x_pitch, const void* w, const void* bias, void* const* ys, const len_t* y_pitches, const len_t* seg_channels,
+           len_t nseg, len_t batch, len_t len, len_t width, StreamContext ctx),
+          (x, x_pitch, w, bias, ys, y_pitches, seg_channels, nseg, batch, len, width, ctx))
+MP_STAMP3(causal_conv1d_silu_segments_reverse,
+          (const void* x, len_t x_pitch, const void* w, const void* bias, const void* const* gys, const len_t* gy_pitches,
+           const len_t* seg_channels, len_t nseg, void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t width,
+           StreamContext ctx),
+          (x, x_pitch, w, bias, gys, gy_pitches, seg_channels, nseg, gx, gx_pitch, gw, gbias, batch, len, width, ctx))
 MP_STAMP3(softplus_bias, (const void* raw, len_t raw_pitch, const void* bias, void* out, len_t rows, len_t heads, StreamContext ctx),
           (raw, raw_pitch, bias, out, rows, heads, ctx))
 MP_STAMP3(softplus_bias_reverse,

@@ -204,6 +204,7 @@ class MambaLM:
         c, T, s = self.cfg, self.T, self.stream
         W = self.w16
         di, gn, H, P = c.d_inner, c.ngroups * c.d_state, c.heads, c.headdim
+        seg_widths = (C.c_ulong * 3)(di, gn, gn)   # channels (= row pitch) of the conv's x, B and C outputs
         dip = c.d_in_proj
         esz = 2
         self._L("embedding", self._p(W, "embedding"), self.ids, self.saved[0]["h_in"], T, c.d_model, c.vocab)
@@ -213,10 +214,10 @@ class MambaLM:
             self._L("rmsnorm_ij_j", sv["h_in"], self._p(W, p + "norm_w"), c.eps, sv["xn"], sv["rstd1"], T, c.d_model)
             self._L("inner_product_ij_jk_ik", sv["xn"], self._p(W, p + "in_proj"), 1.0, sv["zx"], 0.0, T, c.d_model, dip)
             zx = sv["zx"].data_ptr()
-            # conv over the [x | B | C] columns, each segment into its own contiguous tensor
-            for seg_off, seg_w, out in ((0, di, sv["xs"]), (di, gn, sv["Bs"]), (di + gn, gn, sv["Cs"])):
-                self._L("causal_conv1d_silu", zx + (di + seg_off) * esz, dip, self._p(W, p + "conv_w", seg_off * c.d_conv),
-                        self._p(W, p + "conv_b", seg_off), out, seg_w, self.batch, self.seqlen, seg_w, c.d_conv)
+            # one conv over the [x | B | C] columns, each segment into its own contiguous tensor
+            self._L("causal_conv1d_silu_segments", zx + di * esz, dip, self._p(W, p + "conv_w"), self._p(W, p + "conv_b"),
+                    (C.c_void_p * 3)(sv["xs"].data_ptr(), sv["Bs"].data_ptr(), sv["Cs"].data_ptr()), seg_widths, seg_widths, 3,
+                    self.batch, self.seqlen, c.d_conv)
             self._L("softplus_bias", zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), sv["dt"], T, H)
             self._L32("neg_exp", self._p(self.w32, p + "A_log"), sv["A"], H)
             self._L("ssd_scan", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], sv["y"], self.ssd_scratch, *self.ssd_dims)
@@ -239,6 +240,7 @@ class MambaLM:
         c, T = self.cfg, self.T
         W, G16, G32 = self.w16, self.g16, self.g32
         di, gn, H, P = c.d_inner, c.ngroups * c.d_state, c.heads, c.headdim
+        seg_widths = (C.c_ulong * 3)(di, gn, gn)   # channels (= row pitch) of the conv's x, B and C outputs
         dip, esz = c.d_in_proj, 2
         self._L32("fill", G32, 0.0, self.n_flat)
         self._L("fill", G16, 0.0, self.n_flat)
@@ -263,11 +265,9 @@ class MambaLM:
             self._L32("hadamard_reverse", self.gA, sv["A"], self._p(G32, p + "A_log"), H)   # dA/dA_log = A
             self._L("softplus_bias_reverse", zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), self.gdt,
                     gzx + (di + c.conv_dim) * esz, dip, self._p(G32, p + "dt_bias"), T, H)
-            for seg_off, seg_w, g in ((0, di, self.gxs), (di, gn, self.gBs), (di + gn, gn, self.gCs)):
-                self._L("causal_conv1d_silu_reverse", zx + (di + seg_off) * esz, dip, self._p(W, p + "conv_w", seg_off * c.d_conv),
-                        self._p(W, p + "conv_b", seg_off), g, seg_w, gzx + (di + seg_off) * esz, dip,
-                        self._p(G32, p + "conv_w", seg_off * c.d_conv), self._p(G32, p + "conv_b", seg_off), self.batch, self.seqlen,
-                        seg_w, c.d_conv)
+            self._L("causal_conv1d_silu_segments_reverse", zx + di * esz, dip, self._p(W, p + "conv_w"), self._p(W, p + "conv_b"),
+                    (C.c_void_p * 3)(self.gxs.data_ptr(), self.gBs.data_ptr(), self.gCs.data_ptr()), seg_widths, seg_widths, 3,
+                    gzx + di * esz, dip, self._p(G32, p + "conv_w"), self._p(G32, p + "conv_b"), self.batch, self.seqlen, c.d_conv)
             # in_proj
             self._L("inner_product_ij_kj_ik", self.gzx, self._p(W, p + "in_proj"), 1.0, self.gt, 0.0, T, dip, c.d_model)
             self._L("inner_product_ji_jk_ik", sv["xn"], self.gzx, 1.0, self._p(G16, p + "in_proj"), 0.0, c.d_model, T, dip)
@@ -359,8 +359,8 @@ class MambaLM:
         """Kernels of this library launched per training step (a launcher call is several kernels: the scan
         forward 5, its reverse 22, an RMSNorm reverse 3, a split-K contraction 2)."""
         n = self.cfg.n_layer
-        forward = 16 * n + 3          # per layer: 2 norms, 2 contractions, 3 convs, softplus, neg_exp, scan (5), gate, add
+        forward = 14 * n + 3          # per layer: 2 norms, 2 contractions, conv, softplus, neg_exp, scan (5), gate, add
         loss = 2
-        reverse = 41 * n + 9          # per layer: 4 contractions (2 split-K), 2 norm reverses, gate, scan (22), skip, A_log, softplus, 3 convs
+        reverse = 39 * n + 9          # per layer: 4 contractions (2 split-K), 2 norm reverses, gate, scan (22), skip, A_log, softplus, conv
         update = 3                    # gradient conversion, Adam, r16 refresh
         return forward + loss + reverse + update

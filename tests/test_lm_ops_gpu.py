@@ -68,6 +68,56 @@ def test_causal_conv1d_silu(mp, stream, orc, sfx, nb, L, Cn, W, pitch):
     assert_close(host(gb), gb0.astype(np.float64) + rgb, ptol, "conv gbias")
 
 
+# (batch, len, segment widths, taps, pitch of the wide input row): tile-aligned segments, segments ending inside a
+# 64-channel tile, widths that rule out 16-byte accesses (one launch per segment)
+SEG_CASES = [(2, 200, (128, 64, 64), 4, 320), (1, 70, (72, 8, 40), 4, 136), (2, 33, (24, 16), 3, 40), (1, 9, (5, 3, 7), 2, 20)]
+
+
+@pytest.mark.parametrize("sfx", DTYPES)
+@pytest.mark.parametrize("nb,L,widths,W,pitch", SEG_CASES)
+def test_causal_conv1d_silu_segments(mp, stream, orc, sfx, nb, L, widths, W, pitch):
+    import ctypes as C
+    rng = np.random.default_rng(11)
+    Cn = sum(widths)
+    off = pitch - Cn
+    xfull = draw(rng, (nb, L, pitch), sfx)
+    w = draw(rng, (Cn, W), sfx, 0.5)
+    bias = draw(rng, (Cn,), sfx, 0.1)
+    x = xfull[:, :, off:]
+    dx, dw, db = dev(xfull), dev(w), dev(bias)
+    esz = xfull.itemsize
+    ys = [dev(np.full((nb, L, cw), np.nan, NP_OF[sfx])) for cw in widths]
+    ptrs = (C.c_void_p * len(widths))(*[t.data_ptr() for t in ys])
+    cw = (C.c_ulong * len(widths))(*widths)
+    run(mp, stream, "causal_conv1d_silu_segments", sfx, dx.data_ptr() + off * esz, pitch, dw, db, ptrs, cw, cw, len(widths), nb, L, W)
+    ref = orc.causal_conv1d_silu(x.astype(np.float64), w.astype(np.float64), bias.astype(np.float64))
+    c0 = 0
+    for t, cwid in zip(ys, widths):
+        assert_close(host(t), ref[:, :, c0:c0 + cwid], TOL[sfx], f"segment forward at channel {c0}")
+        # the same segment through the plain launcher: identical bits
+        single = dev(np.zeros((nb, L, cwid), NP_OF[sfx]))
+        run(mp, stream, "causal_conv1d_silu", sfx, dx.data_ptr() + (off + c0) * esz, pitch, dw.data_ptr() + c0 * W * esz,
+            db.data_ptr() + c0 * esz, single, cwid, nb, L, cwid, W)
+        assert np.array_equal(host(t), host(single))
+        c0 += cwid
+    gys_np = [draw(rng, (nb, L, cwid), sfx) for cwid in widths]
+    gys = [dev(g) for g in gys_np]
+    gptrs = (C.c_void_p * len(widths))(*[t.data_ptr() for t in gys])
+    gxfull = dev(np.full((nb, L, pitch), 3, NP_OF[sfx]))
+    gw0 = rng.standard_normal((Cn, W)).astype(ACC[sfx]); gb0 = rng.standard_normal((Cn,)).astype(ACC[sfx])
+    gw, gb = dev(gw0.copy()), dev(gb0.copy())
+    run(mp, stream, "causal_conv1d_silu_segments_reverse", sfx, dx.data_ptr() + off * esz, pitch, dw, db, gptrs, cw, cw, len(widths),
+        gxfull.data_ptr() + off * esz, pitch, gw, gb, nb, L, W)
+    gy = np.concatenate(gys_np, axis=2)
+    rgx, rgw, rgb = orc.causal_conv1d_silu_reverse(x.astype(np.float64), w.astype(np.float64), bias.astype(np.float64), gy.astype(np.float64))
+    got = host(gxfull)
+    assert_close(got[:, :, off:], rgx, TOL[sfx], "segments gx")
+    assert np.all(got[:, :, :off] == 3), "columns outside the slice were written"
+    ptol = 1e-4 if sfx != "r64" else 1e-11
+    assert_close(host(gw), gw0.astype(np.float64) + rgw, ptol, "segments gw")
+    assert_close(host(gb), gb0.astype(np.float64) + rgb, ptol, "segments gbias")
+
+
 @pytest.mark.parametrize("sfx", DTYPES)
 @pytest.mark.parametrize("rows,H,pitch", [(1000, 24, 40), (3, 5, 5)])
 def test_softplus_bias(mp, stream, orc, sfx, rows, H, pitch):
