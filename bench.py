@@ -466,7 +466,7 @@ def run_lm(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     comm = GradientComm(world, rank) if world > 1 else None
-    cfg = LMConfig(n_layer=args.lm_layers)
+    cfg = LMConfig(n_layer=args.lm_layers, chunk=args.lm_chunk)
     batch, seqlen = args.lm_batch, 2048
     model = MambaLM(cfg, batch, seqlen, seed=0, loss_scale=65536.0)
     stream, ts = model.stream, model.stream.torch_stream()
@@ -563,7 +563,7 @@ def run_lm(args):
             "config": {"workload": "configs[4]: Mamba-2 LM d_model 768, %d layers, expand 2, headdim 64, d_state 128, vocab 50280, "
                                    "seq 2048, batch %d per GPU, cross-entropy, fused Adam lr 3e-4 betas 0.9/0.95, NCCL all-reduce of "
                                    "the r32 gradient" % (cfg.n_layer, batch),
-                       "assumed": "d_conv 4, tied embedding / LM head, gated RMSNorm before out_proj, D skip, chunk 256, loss scale 65536",
+                       "assumed": f"d_conv 4, tied embedding / LM head, gated RMSNorm before out_proj, D skip, chunk {cfg.chunk}, loss scale 65536",
                        "params": n_params, "tokens_per_gpu_step": T,
                        "l2": "activations and weights (GBs per step) exceed the 126 MB L2; no flush needed"},
             "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "peak_kind": "measured sustained bf16 (fp16 runs on the same pipe)",
@@ -713,6 +713,7 @@ def main():
     ap.add_argument("--lm-layers", type=int, default=24)
     ap.add_argument("--lm-batch", type=int, default=8)
     ap.add_argument("--lm-no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--lm-chunk", type=int, default=256, help="scan chunk of the LM workload (128 or 256)")
     ap.add_argument("--profile-case", default=None, help="OP:DTYPE:ROWS[:COLS], three launches for an ncu capture")
     ap.add_argument("--profile-time", action="store_true", help="with --profile-case: also time 20 launches with CUDA events")
     args = ap.parse_args()
