@@ -609,6 +609,22 @@ RowPlan plan_rows(size_t n, bool aligned) {
   return p;
 }
 
+// Plan of the RMSNorm reverse (register variant).  One warp per row with four packs per lane keeps 32 r16 values
+// of x, gy, their products and the gain-gradient sums per lane: 226 registers, two CTAs per SM.  Rows of 65..128
+// r16 packs therefore take 128 threads with one pack each (about 50 registers; a quarter of the partial rows).
+template <typename T>
+RowPlan plan_rows_rev(size_t n, bool aligned) {
+  RowPlan p = plan_rows<T>(n, aligned);
+  if (!p.generic && sizeof(T) == 2 && p.group == 32 && p.ppt == 4 && getenv("MP_RMS_REV_WARP_ROWS") == nullptr) {
+    p.group = 128;
+    p.ppt = 1;
+    p.threads = 128;
+    p.rows = 1;
+    p.full = n / Pack<T>::N == 128;
+  }
+  return p;
+}
+
 // Streaming row kernels launch one CTA per row group (measured faster on B200
 // than persistent CTAs looping in lock-step).  `threads_per_sm` != 0 asks for a
 // persistent grid instead (kernels that carry per-CTA state across rows).
@@ -775,7 +791,7 @@ static void rmsnorm_ij_j_impl(const void* x_, const void* gain_, double eps, voi
 // scratch is sized for the larger of the two possible plans.
 template <typename T>
 static size_t rmsnorm_rev_slots(size_t m, size_t n, int sm_count, bool aligned) {
-  const RowPlan p = plan_rows<T>(n, aligned);
+  const RowPlan p = plan_rows_rev<T>(n, aligned);
   (void)sm_count;
   size_t slots = rms_rev_grid(p, m) * p.rows;
   const size_t staged = (m + rms_rev_rows_per_cta(m) - 1) / rms_rev_rows_per_cta(m);  // one slot per CTA
@@ -803,7 +819,7 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
   if (m > 0) {
     if (scratch == nullptr) MP_FATAL("rmsnorm_ij_j_reverse: scratch must not be NULL");
     const bool aligned = mp_aligned16(x) && mp_aligned16(gain) && mp_aligned16(gy) && mp_aligned16(gx);
-    const RowPlan p = plan_rows<T>(n, aligned);
+    const RowPlan p = plan_rows_rev<T>(n, aligned);
     const StagedPlan sp = plan_staged<T>(n, aligned);
     unsigned grid = static_cast<unsigned>(rms_rev_grid(p, m));
     size_t rpc = rms_rev_rows_per_cta((m + p.rows - 1) / p.rows);

@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 
 # (m, n): warp-per-row, CTA-per-row in every group size, ragged n (generic path), long rows
 SHAPES = [(1, 1), (7, 8), (33, 128), (65, 512), (40, 1024), (19, 2048), (300, 4096), (9, 8192), (5, 16384),
-          (11, 50280), (13, 1000), (6, 4099), (3, 40000)]
+          (11, 50280), (13, 1000), (6, 4099), (3, 40000), (70, 768), (37, 520), (300, 1024)]
 DTYPES = ["r16", "r32", "r64"]
 
 
