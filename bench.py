@@ -593,7 +593,8 @@ def run_profile_case(spec: str, timed: bool = False):
     chain_fwd, chain_rev (ROWS = element count of selu((a+b)*(c+d))),
     gemm (ROWS:COLS = M and N = K), ssd_fwd, ssd_rev (ROWS:COLS = batch and seqlen),
     bmm (ROWS:COLS = batch entries and M = N = K), permute_heads / permute_reverse (ROWS:COLS = batch and seqlen of a
-    [batch, seqlen, 32, 128] tensor: "blhd->bhld" resp. "blhd->dhlb").  With `--profile-time` the case is then launched
+    [batch, seqlen, 32, 128] tensor: "blhd->bhld" resp. "blhd->dhlb"), conv_fwd / conv_rev (ROWS:COLS = batch and seqlen; the
+    segmented causal convolution over the 1792 [x | B | C] columns of a Mamba-2 block).  With `--profile-time` the case is then launched
     20 more times between CUDA events and one JSON line with the mean launch time is printed."""
     import torch
     import metaphor_b200 as mp
@@ -621,6 +622,27 @@ def run_profile_case(spec: str, timed: bool = False):
         c = torch.empty(m, n, n, device="cuda", dtype=dt)
         once = lambda: mp.launch("inner_product_bij_bjk_bik", dt, a, b, 1.0, c, 0.0, m, n, n, n, s)
         work = (2.0 * m * n * n * n / 1e12, "TFLOP")
+        torch.cuda.synchronize()
+        for _ in range(3):
+            once()
+    elif op in ("conv_fwd", "conv_rev"):
+        # ROWS = batch, COLS = seqlen; the [x | B | C] columns (1536 + 128 + 128) of a 3352-wide projection row, 4 taps
+        import ctypes
+        widths, dip, di, W = (1536, 128, 128), 3352, 1536, 4
+        Cn = sum(widths)
+        zx = torch.randn(m * n, dip, generator=g, device="cuda").to(dt); gzx = torch.empty_like(zx)
+        w = torch.randn(Cn, W, generator=g, device="cuda").to(dt); bias = torch.randn(Cn, generator=g, device="cuda").to(dt)
+        outs = [torch.randn(m * n, cw, generator=g, device="cuda").to(dt) for cw in widths]
+        gw = torch.zeros(Cn, W, device="cuda"); gb = torch.zeros(Cn, device="cuda")
+        ptrs = (ctypes.c_void_p * 3)(*[t.data_ptr() for t in outs]); cw = (ctypes.c_ulong * 3)(*widths)
+        esz = zx.element_size()
+        if op == "conv_fwd":
+            once = lambda: mp.launch("causal_conv1d_silu_segments", dt, zx.data_ptr() + di * esz, dip, w, bias, ptrs, cw, cw, 3, m, n, W, s)
+            work = (2.0 * m * n * Cn * esz / 1e9, "GB")
+        else:
+            once = lambda: mp.launch("causal_conv1d_silu_segments_reverse", dt, zx.data_ptr() + di * esz, dip, w, bias, ptrs, cw, cw, 3,
+                                     gzx.data_ptr() + di * esz, dip, gw, gb, m, n, W, s)
+            work = (3.0 * m * n * Cn * esz / 1e9, "GB")
         torch.cuda.synchronize()
         for _ in range(3):
             once()

@@ -310,6 +310,13 @@ constexpr int CT_L = 64;            // steps per tile
 constexpr int CT_LANES = 4;         // time lanes: 256 threads = 64 channels x 4 lanes
 constexpr int CT_STEPS = CT_L / CT_LANES;
 
+// 16-byte asynchronous global -> shared copies (LDGSTS); `valid == false` writes 16 zero bytes without touching global memory.
+__device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(mp_smem_u32(smem_dst)), "l"(gmem_src), "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 // The channels of one convolution may be cut into up to CONV_MAX_SEGS consecutive segments whose outputs
 // (forward: y; reverse: the incoming gy) live in buffers of their own: one launch then serves what would be
 // one launch per segment (x / B / C of a Mamba-2 block share one convolution over neighbouring columns).
@@ -336,7 +343,7 @@ __global__ void __launch_bounds__(256) conv1d_silu_tiled_kernel(const __half* __
                                                                 const __half* __restrict__ bias, const ConvSegs sg, int L,
                                                                 int tiles_per_cta) {
   constexpr int H = W - 1;
-  __shared__ __align__(16) __half xs[CT_L + H][CT_C];    // row r = step l0 - H + r
+  __shared__ __align__(16) __half xs[2][CT_L + H][CT_C];    // two tiles in turn; row r = step l0 - H + r
   __shared__ __align__(16) __half ys[CT_L][CT_C];
   const int tid = threadIdx.x;
   const int c = tid % CT_C, lane = tid / CT_C;
@@ -355,27 +362,35 @@ __global__ void __launch_bounds__(256) conv1d_silu_tiled_kernel(const __half* __
   if (live_c && bias != nullptr) bs = __half2float(bias[cbase + c]);
   constexpr int PPR = CT_C / 8;
   const int packs_live = min(PPR, (C - cbase) / 8);
-  for (int t = 0; t < tiles_per_cta; ++t) {
+  // tile t + 1 is fetched (asynchronous copies, zero-filled outside the sequence / the segment) while tile t is computed
+  auto stage = [&](int t) {
     const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
-    if (l0 >= L) break;
     for (int v = tid; v < (CT_L + H) * PPR; v += 256) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 - H + r;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (l >= 0 && l < L && pk < packs_live) val = *reinterpret_cast<const uint4*>(xb + static_cast<size_t>(l) * xp + pk * 8);
-      *reinterpret_cast<uint4*>(&xs[r][pk * 8]) = val;
+      const bool ok = l >= 0 && l < L && pk < packs_live;
+      cp_async_16_zfill(&xs[t & 1][r][pk * 8], ok ? xb + static_cast<size_t>(l) * xp + pk * 8 : xb, ok);
     }
+    cp_async_commit();
+  };
+  stage(0);
+  for (int t = 0; t < tiles_per_cta; ++t) {
+    const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
+    if (l0 >= L) break;
+    const bool more = t + 1 < tiles_per_cta && l0 + CT_L < L;
+    if (more) { stage(t + 1); cp_async_wait<1>(); } else cp_async_wait<0>();
     __syncthreads();
     {
+      const __half (*xt)[CT_C] = xs[t & 1];
       const int s0 = lane * CT_STEPS;
       float xw[W];
 #pragma unroll
-      for (int k = 0; k < H; ++k) xw[k + 1] = __half2float(xs[s0 + k][c]);
+      for (int k = 0; k < H; ++k) xw[k + 1] = __half2float(xt[s0 + k][c]);
 #pragma unroll
       for (int j = 0; j < CT_STEPS; ++j) {
 #pragma unroll
         for (int k = 0; k < H; ++k) xw[k] = xw[k + 1];
-        xw[H] = __half2float(xs[s0 + j + H][c]);
+        xw[H] = __half2float(xt[s0 + j + H][c]);
         float pre = bs;
 #pragma unroll
         for (int k = 0; k < W; ++k) pre += wk[k] * xw[k];
@@ -398,8 +413,8 @@ __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __
                                                                         float* __restrict__ gw, float* __restrict__ gbias, int L,
                                                                         int tiles_per_cta) {
   constexpr int H = W - 1;
-  __shared__ __align__(16) __half xs[CT_L + 2 * H][CT_C];    // row r = step l0 - H + r
-  __shared__ __align__(16) __half gys[CT_L + H][CT_C];       // row r = step l0 + r
+  __shared__ __align__(16) __half xs[2][CT_L + 2 * H][CT_C];    // two tiles in turn; row r = step l0 - H + r
+  __shared__ __align__(16) __half gys[2][CT_L + H][CT_C];       // row r = step l0 + r
   __shared__ __align__(16) __half gxs[CT_L][CT_C];
   __shared__ float red[CT_LANES][CT_C][W + 1];
   const int tid = threadIdx.x;
@@ -421,44 +436,52 @@ __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __
   constexpr int PPR = CT_C / 8;   // 16-byte packs per tile row
   const int packs_live = min(PPR, (C - cbase) / 8);   // C is a multiple of 8 on this path
 
-  for (int t = 0; t < tiles_per_cta; ++t) {
+  // ---- stage x and gy of tile t (zero outside the sequence and beyond the last channel) with asynchronous copies:
+  //      tile t + 1 is in flight while tile t is walked ----
+  auto stage = [&](int t) {
     const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
-    if (l0 >= L) break;
-    // ---- stage x and gy (zero outside the sequence and beyond the last channel) ----
     for (int v = tid; v < (CT_L + 2 * H) * PPR; v += 256) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 - H + r;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (l >= 0 && l < L && pk < packs_live) val = *reinterpret_cast<const uint4*>(xb + static_cast<size_t>(l) * xp + pk * 8);
-      *reinterpret_cast<uint4*>(&xs[r][pk * 8]) = val;
+      const bool ok = l >= 0 && l < L && pk < packs_live;
+      cp_async_16_zfill(&xs[t & 1][r][pk * 8], ok ? xb + static_cast<size_t>(l) * xp + pk * 8 : xb, ok);
     }
     for (int v = tid; v < (CT_L + H) * PPR; v += 256) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 + r;
-      uint4 val = make_uint4(0, 0, 0, 0);
-      if (l < L && pk < packs_live) val = *reinterpret_cast<const uint4*>(gyb + static_cast<size_t>(l) * gyp + pk * 8);
-      *reinterpret_cast<uint4*>(&gys[r][pk * 8]) = val;
+      const bool ok = l < L && pk < packs_live;
+      cp_async_16_zfill(&gys[t & 1][r][pk * 8], ok ? gyb + static_cast<size_t>(l) * gyp + pk * 8 : gyb, ok);
     }
+    cp_async_commit();
+  };
+  stage(0);
+  for (int t = 0; t < tiles_per_cta; ++t) {
+    const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
+    if (l0 >= L) break;
+    const bool more = t + 1 < tiles_per_cta && l0 + CT_L < L;
+    if (more) { stage(t + 1); cp_async_wait<1>(); } else cp_async_wait<0>();
     __syncthreads();
     // ---- walk CT_STEPS (+ H look-ahead) steps of one channel ----
     {
+      const __half (*xt)[CT_C] = xs[t & 1];
+      const __half (*gt)[CT_C] = gys[t & 1];
       const int s0 = lane * CT_STEPS;
       float xw[W], d[W];   // xw[k] = x at step s + k - H (tile row s + k); d[k] = dpre at step s - k
 #pragma unroll
       for (int k = 0; k < W; ++k) d[k] = 0.f;
 #pragma unroll
-      for (int k = 0; k < H; ++k) xw[k + 1] = __half2float(xs[s0 + k][c]);
+      for (int k = 0; k < H; ++k) xw[k + 1] = __half2float(xt[s0 + k][c]);
 #pragma unroll
       for (int j = 0; j < CT_STEPS + H; ++j) {
         const int s = s0 + j;
 #pragma unroll
         for (int k = 0; k < H; ++k) xw[k] = xw[k + 1];
-        xw[H] = __half2float(xs[s + H][c]);
+        xw[H] = __half2float(xt[s + H][c]);
         float pre = bs;
 #pragma unroll
         for (int k = 0; k < W; ++k) pre += wk[k] * xw[k];
         const float sg = sigmoid_a(pre);
-        const float dp = __half2float(gys[s][c]) * sg * (1.f + pre * (1.f - sg));
+        const float dp = __half2float(gt[s][c]) * sg * (1.f + pre * (1.f - sg));
 #pragma unroll
         for (int k = H; k > 0; --k) d[k] = d[k - 1];
         d[0] = dp;
@@ -482,8 +505,8 @@ __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __
       const int l = l0 + r;
       if (l < L && pk < packs_live) *reinterpret_cast<uint4*>(gxb + static_cast<size_t>(l) * gxp + pk * 8) = *reinterpret_cast<const uint4*>(&gxs[r][pk * 8]);
     }
-    // the next tile's staging overwrites xs / gys only (all threads are past the walk) and gxs is rewritten
-    // after the next barrier pair, so no further barrier is needed here
+    // the staging of tile t + 2 (issued in the next trip) overwrites this tile's buffers: all threads are past the walk;
+    // gxs is rewritten after the next barrier pair, so no further barrier is needed here
   }
   // ---- fold the time lanes, one atomic per (channel, tap) ----
 #pragma unroll
@@ -944,7 +967,8 @@ static bool conv_make_segs(ConvSegs& sg, const void* const* bufs, const len_t* p
 }
 static dim3 conv_tiled_grid(const ConvSegs& sg, len_t len, len_t batch, int* tiles_per_cta) {
   const size_t ltiles = (len + CT_L - 1) / CT_L;
-  const size_t per = ltiles >= 2 ? 2 : 1;   // time tiles per CTA (measured best of 1, 2, 4, 8 at 1536 and 128 channels)
+  size_t per = ltiles >= 2 ? 2 : 1;   // time tiles per CTA (measured best of 1, 2, 4, 8 at 1536 and 128 channels)
+  if (const char* e = getenv("MP_CONV_TILES_PER_CTA")) { const long v = strtol(e, nullptr, 10); if (v >= 1 && v <= 64) per = static_cast<size_t>(v); }
   *tiles_per_cta = static_cast<int>(per);
   return dim3(static_cast<unsigned>(sg.blk_begin[sg.nseg]), static_cast<unsigned>((ltiles + per - 1) / per), static_cast<unsigned>(batch));
 }
