@@ -119,7 +119,7 @@ def test_causal_conv1d_silu_segments(mp, stream, orc, sfx, nb, L, widths, W, pit
 
 
 @pytest.mark.parametrize("sfx", DTYPES)
-@pytest.mark.parametrize("rows,H,pitch", [(1000, 24, 40), (3, 5, 5)])
+@pytest.mark.parametrize("rows,H,pitch", [(1000, 24, 40), (3, 5, 5), (70, 300, 304), (50, 256, 256), (4099, 32, 32)])
 def test_softplus_bias(mp, stream, orc, sfx, rows, H, pitch):
     rng = np.random.default_rng(2)
     rawfull = draw(rng, (rows, pitch), sfx, 3.0)
