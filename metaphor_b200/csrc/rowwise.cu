@@ -612,6 +612,7 @@ RowPlan plan_rows(size_t n, bool aligned) {
 // Plan of the RMSNorm reverse (register variant).  One warp per row with four packs per lane keeps 32 r16 values
 // of x, gy, their products and the gain-gradient sums per lane: 226 registers, two CTAs per SM.  Rows of 65..128
 // r16 packs therefore take 128 threads with one pack each (about 50 registers; a quarter of the partial rows).
+// (The forward keeps one warp per row at that width: 14.5 against 17.0 us on [16384, 768].)
 template <typename T>
 RowPlan plan_rows_rev(size_t n, bool aligned) {
   RowPlan p = plan_rows<T>(n, aligned);
