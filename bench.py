@@ -1,22 +1,32 @@
 #!/usr/bin/env python
-"""Benchmark of the row-reduction hot path (softmax and RMSNorm, forward and
-reverse, r32 and r16, X = [65536, 4096]) through the C ABI.
-
-One "step" = one pass over one batch: for each dtype, softmax forward, softmax
-reverse, RMSNorm forward, RMSNorm reverse (gradients overwritten, alpha = 0;
-rstd recomputed in the reverse).  Metric: algorithmic HBM GB/s = the bytes each
-kernel must read and write once, summed over the step, divided by the time.
+"""Benchmark of the device layer behind mp.ops / mp.optm.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Under torchrun (N > 1) every rank runs the same per-GPU workload on its own
-rows (weak scaling, no collective on the data path); the time is the maximum
-over ranks, the value the sum of all ranks' bytes over that time.
+Headline (default): the data-parallel training step of the Mamba-2 language
+model of configs[4] - forward, cross-entropy, reverse, NCCL all-reduce of the r32
+gradient (N > 1), fused Adam - in tokens/s over all ranks.  One process per GPU
+(torchrun for N > 1), weak scaling: every rank runs batch 8 x seq 2048 of its
+own token stream.  At N = 1 the same JSON line carries `per_config`: the other
+four configs (README feed-forward block, row reductions, fused chain, SSD scan)
+and the contraction shapes of the model, each with its roofline fraction, a
+CPU-oracle baseline and, where the reference has kernels for it, the
+reference's own CUDA kernels timed in the same run (`ref_cuda`).
+
+`--impl reference` times the float64 CPU oracle of the same training step
+(oracle/lm_oracle.py, full model width, a short batch; tokens/s is
+size-normalised): the reference has no CPU implementation and no kernels for
+most of this step, so the oracle port is the reference arm.
+
+`--workload rows` runs configs[1] alone (the former default line);
+`--profile-case OP:DTYPE:SIZES [--profile-time]` launches a single case three
+times for an ncu capture and optionally times it (see bench_cases.build_case).
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import shutil
 import statistics
@@ -135,7 +145,8 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------
-def run_ours(args):
+def run_rows(args, standalone=True):
+    """configs[1] alone: the record printed by `--workload rows`, and the C2 entry of `per_config`."""
     import torch
     import torch.distributed as dist
     import metaphor_b200 as mp
@@ -148,7 +159,7 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     lib = mp.lib()
     lib.mpInitDevice(local_rank)
-    if world > 1:
+    if world > 1 and standalone:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     stream = mp.Stream()
     ts = stream.torch_stream()
@@ -253,6 +264,7 @@ def run_ours(args):
     cpu = None
     if rank == 0 and world == 1:
         cpu = cpu_baseline(sample_rows=args.cpu_rows)
+    out = None
 
     if rank == 0:
         out = {
@@ -266,11 +278,16 @@ def run_ours(args):
                        "bytes_per_step_per_gpu": STEP_BYTES, "io": "r32 and r16 storage, fp32 arithmetic"},
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "clocks": clocks,
             "gpu_launches": launches_per_step * args.steps,
+            "ref_cuda": "no reference kernel (the reference has neither softmax nor RMSNorm)",
         }
-        print(json.dumps(out), flush=True)
+        if standalone:
+            print(json.dumps(out), flush=True)
+    del bufs
+    torch.cuda.empty_cache()
     stream.close()
-    if world > 1:
+    if world > 1 and standalone:
         dist.destroy_process_group()
+    return out if rank == 0 else None
 
 
 E2E_CHUNKS = 8
@@ -412,8 +429,8 @@ def cpu_baseline(sample_rows: int):
                       f"{threads} host threads over disjoint row ranges, mean of {repeats} passes of {dt:.2f} s"}
 
 
-def run_reference(args):
-    """Reference arm.  The reference has no CPU (or any) implementation of
+def run_reference_rows(args):
+    """Reference arm of `--workload rows`.  The reference has no CPU (or any) implementation of
     softmax / RMSNorm, so this times the CPU oracle port of the step on all host
     threads, one bounded row sample per step."""
     rank = int(os.environ.get("RANK", "0"))
@@ -443,12 +460,111 @@ def run_reference(args):
     }), flush=True)
 
 
+# ----------------------------------------------------------------------------
+# configs[4]: the data-parallel Mamba-2 LM training step (the headline)
+# ----------------------------------------------------------------------------
+LM_METRIC = "Mamba-2 LM training throughput (data-parallel step: forward, cross-entropy, reverse, gradient all-reduce, fused Adam)"
+LM_SEQ = 2048
+ADAM = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8)
+ORACLE_BATCH, ORACLE_SEQ = 1, 64     # the CPU oracle's sample of the step: full model width, 64 tokens
+
+
+def lm_workload_text(n_layer, batch):
+    return ("configs[4]: Mamba-2 LM d_model 768, %d layers, expand 2, headdim 64, d_state 128, ngroups 1, RMSNorm, vocab 50280, "
+            "seq 2048, batch %d per GPU, cross-entropy, fused Adam lr 3e-4 betas 0.9/0.95, NCCL all-reduce of the r32 gradient"
+            % (n_layer, batch))
+
+
+# launcher -> DRAM bytes per call from ncu (dram__bytes_read.sum + dram__bytes_write.sum), with the commit
+# the capture was taken at; a launcher that is not listed reports traffic null
+LM_NCU_TRAFFIC = {}
+
+
+def lm_launcher_work(label, cfg, batch, seqlen):
+    """Algorithmic work of ONE call of a launcher of the step: ({"flops": F} | {"bytes": B}, bound)."""
+    import re
+    from bench_cases import ssd_bytes, ssd_flops
+    T = batch * seqlen
+    dims = (batch, seqlen, cfg.heads, cfg.headdim, cfg.d_state, cfg.ngroups)
+    if label.startswith("ssd_scan_reverse"):
+        return {"flops": ssd_flops(*dims, cfg.chunk, True), "bytes": ssd_bytes(*dims, True)}, "both"
+    if label.startswith("ssd_scan"):
+        return {"flops": ssd_flops(*dims, cfg.chunk, False), "bytes": ssd_bytes(*dims, False)}, "both"
+    m = re.match(r"inner_product_\w+\[(\d+)x(\d+)x(\d+)\]", label)
+    if m:
+        a, b, c = (int(v) for v in m.groups())
+        return {"flops": 2.0 * a * b * c}, "tensor"
+    if label.startswith("cross_entropy"):
+        return {"bytes": 2 * T * cfg.vocab * 2}, "hbm"
+    if label.startswith("adam"):
+        return {"bytes": 28 * cfg.n_params()}, "hbm"
+    return None, None
+
+
+def lm_oracle_sample(steps, warmup, threads=None):
+    """The float64 CPU oracle of the training step (oracle/lm_oracle.py: sequential-recurrence scan, torch autograd,
+    Adam) at the full model width on ORACLE_BATCH x ORACLE_SEQ tokens.  Returns (seconds per step, tokens per step,
+    threads, first loss)."""
+    import numpy as np
+    import torch
+    from metaphor_b200.mamba_lm import LMConfig, init_weights
+    from oracle import lm_oracle
+    threads = threads or (os.cpu_count() or 1)
+    torch.set_num_threads(threads)
+    cfg = LMConfig()
+    w = {k: torch.from_numpy(v).double().requires_grad_() for k, v in init_weights(cfg, 0).items()}
+    m = {k: torch.zeros_like(v) for k, v in w.items()}
+    v2 = {k: torch.zeros_like(v) for k, v in w.items()}
+    T = ORACLE_BATCH * ORACLE_SEQ
+    tok = torch.from_numpy(np.random.default_rng(1000).integers(0, cfg.vocab, T + 1))
+    ids, tgt = tok[:-1], tok[1:]
+    times, first = [], None
+    for k in range(warmup + steps):
+        t0 = time.perf_counter()
+        loss = lm_oracle.forward_loss(cfg, w, ids, tgt, ORACLE_BATCH, ORACLE_SEQ)
+        loss.backward()
+        with torch.no_grad():
+            b1, b2, step = ADAM["beta1"], ADAM["beta2"], k + 1
+            for name, p in w.items():
+                g = p.grad
+                m[name].mul_(b1).add_(g, alpha=1 - b1)
+                v2[name].mul_(b2).addcmul_(g, g, value=1 - b2)
+                p.addcdiv_(m[name] / (1 - b1 ** step), (v2[name] / (1 - b2 ** step)).sqrt_().add_(ADAM["eps"]), value=-ADAM["lr"])
+                p.grad = None
+        dt = time.perf_counter() - t0
+        if first is None:
+            first = float(loss.detach())
+        if k >= warmup:
+            times.append(dt)
+    return statistics.mean(times), T, threads, first
+
+
+def run_reference_lm(args):
+    """Reference arm of the headline: the CPU oracle of the same training step on the box's host cores."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    steps = max(1, min(args.steps, 8))          # ~2-4 s per step: bounded so that the arm ends within minutes
+    warmup = 1 if args.warmup > 0 else 0
+    dt, T, threads, first = lm_oracle_sample(steps, warmup)
+    value = round(T / dt, 2)
+    sample = (f"each step = the full-width model (24 layers, vocab 50280) on {ORACLE_BATCH} x {ORACLE_SEQ} tokens instead of 8 x 2048 "
+              f"(tokens/s is size-normalised), float64 oracle port: sequential-recurrence scan, torch autograd, Adam; {threads} host threads; "
+              f"{steps} timed steps (of the {args.steps} asked for) after {warmup} warm-up; the reference itself has no CPU code and no kernels for most of this step")
+    print(json.dumps({
+        "impl": "reference", "metric": LM_METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(dt * 1e3, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f64", "data": "synthetic (token ids ~ U[0, 50280), seed 1000; weights N(0, 0.02), seed 0)",
+        "config": {"workload": lm_workload_text(24, 8), "tokens_sampled_per_step": T},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "loss": {"first_step": round(first, 4)},
+    }), flush=True)
+
+
 def run_lm(args):
-    """`--workload lm`: data-parallel training step of the Mamba-2 language model of configs[4]
-    (d_model 768, 24 layers, expand 2, headdim 64, d_state 128, vocab 50280; seq 2048, batch 8 per GPU,
-    fused Adam lr 3e-4 betas 0.9/0.95, all-reduce of the r32 gradient).  A step = forward, cross-entropy,
-    reverse, all-reduce, Adam; `value` = tokens/s over all ranks with the token ids resident on the
-    device, `e2e` = the same step with the ids copied from pinned host memory and the loss read back."""
+    """The headline line.  A step = forward, cross-entropy, reverse, all-reduce, Adam; `value` = tokens/s over all
+    ranks with the token ids resident on the device, `e2e` = the same step with the ids copied from pinned host
+    memory and the loss read back every step."""
     import torch
     import torch.distributed as dist
     import metaphor_b200 as mp
@@ -467,7 +583,7 @@ def run_lm(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     comm = GradientComm(world, rank) if world > 1 else None
     cfg = LMConfig(n_layer=args.lm_layers, chunk=args.lm_chunk)
-    batch, seqlen = args.lm_batch, 2048
+    batch, seqlen = args.lm_batch, LM_SEQ
     model = MambaLM(cfg, batch, seqlen, seed=0, loss_scale=65536.0)
     stream, ts = model.stream, model.stream.torch_stream()
     T = batch * seqlen
@@ -475,9 +591,9 @@ def run_lm(args):
     tok = torch.randint(0, cfg.vocab, (T + 1,), generator=gen, dtype=torch.int32)
     ids_h, tgt_h = tok[:-1].contiguous().pin_memory(), tok[1:].contiguous().pin_memory()
     model.set_batch(ids_h, tgt_h)
-    adam = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8)
     if not args.lm_no_graph:
         model.capture()
+    losses = torch.zeros(args.steps + 1, dtype=torch.float32, device="cuda")   # summed loss of every timed step
 
     def barrier():
         stream.sync()
@@ -485,46 +601,45 @@ def run_lm(args):
         if world > 1:
             dist.barrier()
 
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     for _ in range(args.warmup):
-        model.train_step(comm=comm, world=world, **adam)
+        model.train_step(comm=comm, world=world, **ADAM)
     barrier()
-    first_loss = None
     wall0 = time.time()
     e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-    phase = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
     e0.record(ts)
     for k in range(args.steps):
-        last = k == args.steps - 1
-        if last: phase[0].record(ts)
-        if args.lm_no_graph:
-            model.forward()
-            if last: phase[1].record(ts)
-            model.loss_and_logit_gradient()
-            model.backward()
-        else:
-            if last: phase[1].record(ts)
-            model.forward_backward()
-        if last: phase[2].record(ts)
-        if comm is not None:
-            comm.all_reduce_sum(model.g32, stream)
-        if last: phase[3].record(ts)
-        model.adam_step(world=world, **adam)
-        if last: phase[4].record(ts)
+        model.train_step(comm=comm, world=world, **ADAM)
+        # the step's summed loss, kept on the device (one 4-byte copy kernel; read after the timed region)
+        lib.launch_copy_r32(model.loss_sum.data_ptr(), losses.data_ptr() + 4 * k, 1, stream.ctx)
     e1.record(ts)
     barrier()
     wall1 = time.time()
     clocks = sampler.stop(wall0, wall1) if rank == 0 else None
     if stream.status() != 0:
         raise SystemExit("a kernel reported a non-zero status word")
-    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms_per_step = float(t.item()) / args.steps
+    ms_per_step = max_over_ranks(e0.elapsed_time(e1)) / args.steps
     value = world * T / (ms_per_step * 1e-3)
-    last_loss = model.loss()
+    loss_host = (losses.cpu() / T).tolist()
+
+    # every rank must hold the same weights after the same number of all-reduced steps
+    wsum = torch.zeros(1, dtype=torch.float32, device="cuda")
+    mp.launch("reduce_ij_i", torch.float32, model.w32, wsum, 0.0, 1, model.n_flat, stream)
+    stream.sync()
+    sums = [torch.zeros_like(wsum) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(sums, wsum)
+    else:
+        sums = [wsum]
+    checksums = [float(x.item()) for x in sums]
 
     # end to end: ids from pinned host memory every step, loss read back every step
     barrier()
@@ -532,191 +647,138 @@ def run_lm(args):
     e0.record(ts)
     for _ in range(e2e_steps):
         model.set_batch(ids_h, tgt_h)
-        model.train_step(comm=comm, world=world, **adam)
+        model.train_step(comm=comm, world=world, **ADAM)
         _ = model.loss()
     e1.record(ts)
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], device="cuda", dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
 
+    # one more step issued launcher by launcher with an event pair around each: the share of every launcher
+    prof = model.profile_step(comm=comm, world=world, **ADAM)
+    barrier()
+    graph_kernels = int(lib.mpGraphKernelNodes(model.graph)) if getattr(model, "graph", None) else None
+    n_params = cfg.n_params()
+
+    out = None
     if rank == 0:
-        n_params = cfg.n_params()
-        gemm_params = n_params - 0   # every parameter but the small vectors sits in a contraction; the embedding is tied
-        # model flops per step and GPU: 6 x params x tokens for the contractions + the scan (forward 1x, reverse 2x)
+        from bench_cases import peaks, rate_record
+        hbm, burst, sustained, peak_kind = peaks()
         Q, H, P, NS = cfg.chunk, cfg.heads, cfg.headdim, cfg.d_state
         ssd_fwd = (2 * Q * Q * NS) * (T // Q) + (2 * Q * Q * P + 4 * Q * NS * P) * (cfg.heads * T // Q)
-        flops = 6.0 * gemm_params * T + 3.0 * ssd_fwd * cfg.n_layer
-        achieved = flops / (ms_per_step * 1e-3) / 1e12
-        peak = 1381.7
-        try:
-            peak = float(json.loads((Path(__file__).resolve().parent / "MEASURED_PEAKS.json").read_text()).get("bf16_tflops_sustained", peak))
-        except Exception:
-            pass
-        ph = [phase[i].elapsed_time(phase[i + 1]) for i in range(4)]
+        flops = 6.0 * n_params * T + 3.0 * ssd_fwd * cfg.n_layer
+        total_prof = sum(r["ms"] for r in prof.values())
+        top = sorted(prof.items(), key=lambda kv: -kv[1]["ms"])
+        dom, dom_rec = top[0]
+        work, bound = lm_launcher_work(dom, cfg, batch, seqlen)
+        per_call_ms = dom_rec["ms"] / dom_rec["calls"]
+        roofline = {"kernel": dom, "calls_per_step": dom_rec["calls"], "share_of_step": round(dom_rec["ms"] / total_prof, 4),
+                    "us_per_call": round(per_call_ms * 1e3, 1), "traffic": LM_NCU_TRAFFIC.get(dom),
+                    "timing": "CUDA events around every call of the launcher in one step issued without graph replay, same process, right after the timed region"}
+        if work is not None:
+            rr = rate_record(per_call_ms, work, bound, tensor_peak=sustained)
+            if bound == "hbm":
+                roofline.update({"bound": "hbm", "achieved": rr["GB/s"], "peak": hbm, "unit": "GB/s", "frac": rr["frac"]})
+            else:
+                roofline.update({"bound": "tensor", "achieved": rr["TFLOP/s"], "peak": sustained, "unit": "TFLOP/s",
+                                 "frac": round(rr["TFLOP/s"] / sustained, 4)})
+                if bound == "both":
+                    roofline["note"] = ("the scan sits at the ridge: roofline time = max(HBM, tensor) = %.1f us, fraction of that %.4f"
+                                        % (rr["roofline_us"], rr["frac"]))
+            roofline["peak_kind"] = peak_kind + (" sustained bf16 (fp16 runs on the same pipe)" if bound != "hbm" else " copy bandwidth")
+            roofline.update({k: v for k, v in rr.items() if k.startswith("algorithmic")})
+        roofline["step_model_flops"] = {"achieved_TFLOP/s": round(flops / (ms_per_step * 1e-3) / 1e12, 1), "flops": flops,
+                                        "frac_of_sustained_peak": round(flops / (ms_per_step * 1e-3) / 1e12 / sustained, 4)}
+        roofline["launchers_ms"] = {k: {"ms": round(v["ms"], 3), "calls": v["calls"]} for k, v in top[:14]}
         out = {
-            "metric": "Mamba-2 LM training throughput", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+            "metric": LM_METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations, f32 accumulation and master weights",
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations / f32 accumulate, master weights and optimizer state",
             "data": "synthetic (token ids ~ U[0, 50280), seed 1000 + rank; weights N(0, 0.02), seed 0 on every rank)",
-            "config": {"workload": "configs[4]: Mamba-2 LM d_model 768, %d layers, expand 2, headdim 64, d_state 128, vocab 50280, "
-                                   "seq 2048, batch %d per GPU, cross-entropy, fused Adam lr 3e-4 betas 0.9/0.95, NCCL all-reduce of "
-                                   "the r32 gradient" % (cfg.n_layer, batch),
-                       "assumed": f"d_conv 4, tied embedding / LM head, gated RMSNorm before out_proj, D skip, chunk {cfg.chunk}, loss scale 65536",
-                       "params": n_params, "tokens_per_gpu_step": T,
+            "config": {"workload": lm_workload_text(cfg.n_layer, batch),
+                       "assumed": f"d_conv 4, tied embedding / LM head, gated RMSNorm before out_proj, D skip, chunk {cfg.chunk}, static loss scale 65536",
+                       "params": n_params, "tokens_per_gpu_step": T, "graph_replay": not args.lm_no_graph,
+                       "all_reduce": ("none (one rank)" if world == 1 else model.all_reduce_description()),
                        "l2": "activations and weights (GBs per step) exceed the 126 MB L2; no flush needed"},
-            "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peak, "peak_kind": "measured sustained bf16 (fp16 runs on the same pipe)",
-                         "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
-                         "algorithmic_flops": flops,
-                         "phases_ms": {"forward" if args.lm_no_graph else "(graph: see next)": round(ph[0], 2),
-                                       "loss+reverse" if args.lm_no_graph else "forward+loss+reverse (one graph launch)": round(ph[1], 2), "all_reduce": round(ph[2], 2),
-                                       "adam+refresh": round(ph[3], 2)}},
-            "cpu_baseline": None,
+            "roofline": roofline, "cpu_baseline": None,
             "e2e": {"value": round(world * T / (e2e_ms * 1e-3), 1), "unit": "tokens/s", "h2d_bytes_per_step": 2 * T * 4,
-                    "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps},
-            "clocks": clocks, "gpu_launches": model.launches_per_step() * args.steps,
-            "loss": {"first_timed_step": first_loss, "last": round(last_loss, 4)},
+                    "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
+                    "path": "MambaLM.set_batch (mpMemcpyHtoD from pinned memory) + train_step + loss() (mpMemcpyDtoH + stream sync) every step"},
+            "clocks": clocks,
+            "gpu_launches": (graph_kernels + 3 if graph_kernels else model.launches_per_step()) * args.steps,
+            "gpu_launches_per_step": {"graph_kernel_nodes (forward + loss + reverse)": graph_kernels,
+                                      "outside the graph": "Adam, r16 weight refresh, loss copy" + (", NCCL all-reduce" if world > 1 else "")},
+            "loss": {"first_timed_step": round(loss_host[0], 4), "last_timed_step": round(loss_host[args.steps - 1], 4),
+                     "expected_at_init": round(math.log(cfg.vocab), 4),
+                     "note": "one fixed random batch per rank is repeated, so the loss falls as the model memorises it"},
+            "weights_checksum": {"per_rank": checksums, "all_equal": len(set(checksums)) == 1,
+                                 "meaning": "sum of the r32 master weights after the last step; equal on all ranks only if every step's gradient was all-reduced"},
         }
-        print(json.dumps(out), flush=True)
     if comm is not None:
         comm.close()
-    stream.close()
+    model.release()
+    del model
+    torch.cuda.empty_cache()
+    if rank == 0:
+        if world == 1 and not args.no_per_config:
+            out["cpu_baseline"] = lm_cpu_baseline()
+            out["per_config"] = run_per_config(args, mp)
+        else:
+            out["per_config"] = "reported at N = 1 only (rank 0 of a single-GPU run)"
+        print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
+def lm_cpu_baseline():
+    dt, T, threads, first = lm_oracle_sample(steps=2, warmup=1)
+    return {"value": round(T / dt, 2), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"full-width model on {ORACLE_BATCH} x {ORACLE_SEQ} tokens (tokens/s is size-normalised), float64 oracle: sequential-recurrence scan, "
+                      f"torch autograd, Adam; mean of 2 steps of {dt:.2f} s after 1 warm-up", "first_loss": round(first, 4)}
+
+
+def run_per_config(args, mp):
+    """The other four configs and the contraction shapes, one after another on a fresh stream."""
+    import torch
+    import bench_cases as bc
+    out = {}
+    s = mp.Stream()
+    flush = bc.Flusher(mp, s)
+    ref = bc.ref_cuda_or_none()
+    try:
+        out["C1_feed_forward_block"] = bc.config_feed_forward(mp, s, ref)
+        rows_args = argparse.Namespace(**vars(args)); rows_args.steps = 5; rows_args.warmup = 3; rows_args.e2e_steps = 2; rows_args.cpu_rows = 16384
+        out["C2_row_reductions"] = run_rows(rows_args, standalone=False)
+        torch.cuda.empty_cache()
+        out["C3_fused_chain"] = bc.config_chain(mp, s, flush, ref=ref)
+        torch.cuda.empty_cache()
+        out["C4_ssd_scan"] = bc.config_ssd(mp, s, flush)
+        torch.cuda.empty_cache()
+        out["einsum_lm_shapes"] = bc.config_einsum(mp, s, flush, ref=ref)
+    finally:
+        if isinstance(ref, bc.RefCuda):
+            ref.close()
+        s.close()
+    return out
+
+
 def run_profile_case(spec: str, timed: bool = False):
-    """`--profile-case OP:DTYPE:ROWS[:COLS]`: three launches of one kernel on a
-    small case, for an ncu capture (no timing, no JSON).  OP is one of
-    softmax_fwd, softmax_rev, rmsnorm_fwd, rmsnorm_rev (rows x cols matrix),
-    chain_fwd, chain_rev (ROWS = element count of selu((a+b)*(c+d))),
-    gemm (ROWS:COLS = M and N = K), ssd_fwd, ssd_rev (ROWS:COLS = batch and seqlen),
-    bmm (ROWS:COLS = batch entries and M = N = K), permute_heads / permute_reverse (ROWS:COLS = batch and seqlen of a
-    [batch, seqlen, 32, 128] tensor: "blhd->bhld" resp. "blhd->dhlb"), conv_fwd / conv_rev (ROWS:COLS = batch and seqlen; the
-    segmented causal convolution over the 1792 [x | B | C] columns of a Mamba-2 block).  With `--profile-time` the case is then launched
-    20 more times between CUDA events and one JSON line with the mean launch time is printed."""
+    """`--profile-case OP:DTYPE:SIZES`: three launches of one case on a small size, for an ncu capture; with
+    `--profile-time` the case is then timed (CUDA events, L2 flushed between launches when the inputs fit it) and one
+    JSON line is printed.  Grammar: bench_cases.build_case."""
     import torch
     import metaphor_b200 as mp
-    parts = spec.split(":")
-    op, sfx, m = parts[0], parts[1], int(parts[2])
-    n = int(parts[3]) if len(parts) > 3 else N
-    dt = {"r16": torch.float16, "r32": torch.float32, "r64": torch.float64}[sfx]
+    import bench_cases as bc
     torch.zeros(1, device="cuda")
     s = mp.Stream()
-    g = torch.Generator(device="cuda").manual_seed(0)
-    once = None          # one launch of the case (set by the branches that support --profile-time)
-    work = None          # (amount, unit) per launch
-    if op in ("chain_fwd", "chain_rev"):
-        leaves = [(torch.rand(m, generator=g, device="cuda") * 2 - 1).to(dt) for _ in range(4)]
-        out = torch.empty_like(leaves[0]); grads = [torch.empty_like(leaves[0]) for _ in range(4)]
-        chain = mp.FusedChain("selu((a+b)*(c+d))", dt)
-        torch.cuda.synchronize()
-        for _ in range(3):
-            if op == "chain_fwd":
-                chain.forward(leaves, out, m, s)
-            else:
-                chain.reverse(leaves, None, grads, 0.0, m, s)
-    elif op == "bmm":
-        a = torch.randn(m, n, n, generator=g, device="cuda").to(dt); b = (torch.randn(m, n, n, generator=g, device="cuda") / 32).to(dt)
-        c = torch.empty(m, n, n, device="cuda", dtype=dt)
-        once = lambda: mp.launch("inner_product_bij_bjk_bik", dt, a, b, 1.0, c, 0.0, m, n, n, n, s)
-        work = (2.0 * m * n * n * n / 1e12, "TFLOP")
-        torch.cuda.synchronize()
-        for _ in range(3):
-            once()
-    elif op in ("conv_fwd", "conv_rev"):
-        # ROWS = batch, COLS = seqlen; the [x | B | C] columns (1536 + 128 + 128) of a 3352-wide projection row, 4 taps
-        import ctypes
-        widths, dip, di, W = (1536, 128, 128), 3352, 1536, 4
-        Cn = sum(widths)
-        zx = torch.randn(m * n, dip, generator=g, device="cuda").to(dt); gzx = torch.empty_like(zx)
-        w = torch.randn(Cn, W, generator=g, device="cuda").to(dt); bias = torch.randn(Cn, generator=g, device="cuda").to(dt)
-        outs = [torch.randn(m * n, cw, generator=g, device="cuda").to(dt) for cw in widths]
-        gw = torch.zeros(Cn, W, device="cuda"); gb = torch.zeros(Cn, device="cuda")
-        ptrs = (ctypes.c_void_p * 3)(*[t.data_ptr() for t in outs]); cw = (ctypes.c_ulong * 3)(*widths)
-        esz = zx.element_size()
-        if op == "conv_fwd":
-            once = lambda: mp.launch("causal_conv1d_silu_segments", dt, zx.data_ptr() + di * esz, dip, w, bias, ptrs, cw, cw, 3, m, n, W, s)
-            work = (2.0 * m * n * Cn * esz / 1e9, "GB")
-        else:
-            once = lambda: mp.launch("causal_conv1d_silu_segments_reverse", dt, zx.data_ptr() + di * esz, dip, w, bias, ptrs, cw, cw, 3,
-                                     gzx.data_ptr() + di * esz, dip, gw, gb, m, n, W, s)
-            work = (3.0 * m * n * Cn * esz / 1e9, "GB")
-        torch.cuda.synchronize()
-        for _ in range(3):
-            once()
-    elif op in ("permute_heads", "permute_reverse"):
-        import ctypes
-        shape = (m, n, 32, 128)
-        perm = (0, 2, 1, 3) if op == "permute_heads" else (3, 2, 1, 0)
-        x = torch.randn(shape, generator=g, device="cuda").to(dt); y = torch.empty_like(x)
-        sizes = (ctypes.c_ulong * 4)(*shape); pm = (ctypes.c_ulong * 4)(*perm)
-        once = lambda: mp.launch("permutate", dt, x, y, 0.0, sizes, pm, 4, s)
-        work = (2.0 * x.numel() * x.element_size() / 1e9, "GB")
-        torch.cuda.synchronize()
-        for _ in range(3):
-            once()
-    elif op in ("ssd_fwd", "ssd_rev"):
-        # ROWS = batch, COLS = seqlen; heads 32, headdim 64, d_state 128, 1 group, chunk 256
-        import math
-        nb, L, H, P, NS, G, Q = m, n, 32, 64, 128, 1, 256
-        x = torch.randn(nb, L, H, P, generator=g, device="cuda").half()
-        Bm = torch.randn(nb, L, G, NS, generator=g, device="cuda").half()
-        Cm = torch.randn(nb, L, G, NS, generator=g, device="cuda").half()
-        dtv = torch.nn.functional.softplus(torch.randn(nb, L, H, generator=g, device="cuda") - 4)
-        Av = -torch.exp(torch.rand(H, generator=g, device="cuda") * math.log(16))
-        gy = torch.randn(nb, L, H, P, generator=g, device="cuda").half()
-        y = torch.empty_like(x); gx = torch.empty_like(x); gdt = torch.empty_like(dtv); gA = torch.empty_like(Av)
-        gB = torch.empty_like(Bm); gC = torch.empty_like(Cm)
-        dims = (nb, L, H, P, NS, G, Q)
-        rev = op == "ssd_rev"
-        scr = torch.empty(mp.lib().mpSsdScanScratchBytes(*dims, 1 if rev else 0), dtype=torch.uint8, device="cuda")
-        torch.cuda.synchronize()
-        for _ in range(3):
-            if rev:
-                mp.launch("ssd_scan_reverse", torch.float16, x, dtv, Av, Bm, Cm, gy, gx, gdt, gA, gB, gC, scr, *dims, s)
-            else:
-                mp.launch("ssd_scan", torch.float16, x, dtv, Av, Bm, Cm, y, scr, *dims, s)
-    elif op == "gemm":
-        a = torch.randn(m, n, generator=g, device="cuda").to(dt); b = torch.randn(n, n, generator=g, device="cuda").to(dt)
-        c = torch.empty(m, n, device="cuda", dtype=dt)
-        once = lambda: mp.launch("inner_product_ij_jk_ik", dt, a, b, 1.0, c, 0.0, m, n, n, s)
-        work = (2.0 * m * n * n / 1e12, "TFLOP")
-        torch.cuda.synchronize()
-        for _ in range(3):
-            once()
-    else:
-        x = torch.randn(m, n, generator=g, device="cuda").to(dt); gy = torch.randn(m, n, generator=g, device="cuda").to(dt)
-        y = torch.empty_like(x); gx = torch.empty_like(x)
-        gain = torch.ones(n, device="cuda", dtype=dt); gg = torch.empty_like(gain)
-        scratch = torch.empty(mp.lib().mpRmsnormReverseScratchBytes(m, n, s.ctx), dtype=torch.uint8, device="cuda")
-        torch.cuda.synchronize()
-        for _ in range(3):
-            if op == "softmax_fwd":
-                mp.launch("softmax_ij_j", dt, x, y, m, n, s)
-            elif op == "softmax_rev":
-                mp.launch("softmax_ij_j_reverse", dt, x, gy, gx, 0.0, m, n, s)
-            elif op == "rmsnorm_fwd":
-                mp.launch("rmsnorm_ij_j", dt, x, gain, EPS, y, None, m, n, s)
-            elif op == "rmsnorm_rev":
-                mp.launch("rmsnorm_ij_j_reverse", dt, x, gain, None, gy, EPS, gx, gg, 0.0, scratch, m, n, s)
-            else:
-                raise SystemExit(f"unknown profile case {op}")
+    case = bc.build_case(mp, s, spec)
+    torch.cuda.synchronize()
+    for _ in range(3):
+        case.once()
     s.sync()
     if timed:
-        if once is None:
-            raise SystemExit(f"--profile-time is not available for {op}")
-        ts = s.torch_stream()
-        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-        e0.record(ts)
-        for _ in range(20):
-            once()
-        e1.record(ts)
-        s.sync()
-        us = e0.elapsed_time(e1) / 20 * 1e3
-        print(json.dumps({"case": spec, "us_per_launch": round(us, 2), "per_launch": work[0], "unit": work[1],
-                          "rate": round(work[0] / (us * 1e-6), 1), "rate_unit": work[1] + "/s"}))
+        rec = case.measure(s, bc.Flusher(mp, s), iters=20)
+        rec["case"] = spec
+        print(json.dumps(rec))
     if s.status() != 0:
         raise SystemExit("status word set")
     s.close()
@@ -728,15 +790,16 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--e2e-steps", type=int, default=10, help="upper bound on end-to-end steps (PCIe-bound)")
-    ap.add_argument("--cpu-rows", type=int, default=32768, help="rows in the CPU baseline sample")
-    ap.add_argument("--workload", default="rows", choices=["rows", "lm"],
-                    help="rows = configs[1] (default, the headline line); lm = configs[4] training step, tokens/s")
+    ap.add_argument("--e2e-steps", type=int, default=10, help="upper bound on end-to-end steps")
+    ap.add_argument("--cpu-rows", type=int, default=32768, help="rows in the CPU baseline sample of --workload rows")
+    ap.add_argument("--workload", default="lm", choices=["lm", "rows"],
+                    help="lm = configs[4] training step, tokens/s (default, the headline line); rows = configs[1] alone")
+    ap.add_argument("--no-per-config", action="store_true", help="skip the per_config block (and the CPU baseline) of the headline line")
     ap.add_argument("--lm-layers", type=int, default=24)
     ap.add_argument("--lm-batch", type=int, default=8)
     ap.add_argument("--lm-no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
     ap.add_argument("--lm-chunk", type=int, default=256, help="scan chunk of the LM workload (128 or 256)")
-    ap.add_argument("--profile-case", default=None, help="OP:DTYPE:ROWS[:COLS], three launches for an ncu capture")
+    ap.add_argument("--profile-case", default=None, help="OP:DTYPE:SIZES, three launches for an ncu capture")
     ap.add_argument("--profile-time", action="store_true", help="with --profile-case: also time 20 launches with CUDA events")
     args = ap.parse_args()
     if args.profile_case:
@@ -745,11 +808,11 @@ def main():
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
     if args.impl == "reference":
-        run_reference(args)
+        (run_reference_lm if args.workload == "lm" else run_reference_rows)(args)
     elif args.workload == "lm":
         run_lm(args)
     else:
-        run_ours(args)
+        run_rows(args)
 
 
 if __name__ == "__main__":

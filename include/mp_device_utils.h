@@ -76,6 +76,9 @@ MP_EXTERN_C void mpGraphBeginCapture(StreamContext);
 MP_EXTERN_C void* mpGraphEndCapture(StreamContext);
 MP_EXTERN_C void mpGraphLaunch(void* graph, StreamContext);
 MP_EXTERN_C void mpGraphDestroy(void* graph);
+/* Number of kernel launches a graph returned by mpGraphEndCapture replays (0 for an unknown handle).
+ * No counterpart in the reference. */
+MP_EXTERN_C len_t mpGraphKernelNodes(void* graph);
 
 /* Pinned host memory for the end-to-end copy path (the reference copies from
  * pageable memory, src/core/utils.zig:159-218; pinned buffers let

@@ -112,6 +112,7 @@ UTILS = {
     "mpGraphEndCapture": (P, [CTX]),
     "mpGraphLaunch": (None, [P, CTX]),
     "mpGraphDestroy": (None, [P]),
+    "mpGraphKernelNodes": (L, [P]),
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
     "mpSsdScanScratchBytes": (L, [L, L, L, L, L, L, L, U32]),
     "mpSsdScanGenericScratchBytes": (L, [U32, L, L, L, L, L, L, U32]),

@@ -3,7 +3,9 @@
 // caller can observe are listed beside each function.
 #include "mp_common.cuh"
 
+#include <map>
 #include <mutex>
+#include <vector>
 
 namespace {
 
@@ -185,20 +187,48 @@ extern "C" void mpStreamWaitEvent(StreamContext ctx, void* event) {
 // is recorded once and replayed with one call.  Everything the launchers do is stream-ordered and
 // allocation-free, so any sequence of them can be captured; calls that synchronise (mpGetStatus,
 // mpStreamSynchronize, mpMemcpy* from pageable memory) must stay outside the captured region.
+namespace {
+std::mutex g_graph_mutex;
+std::map<void*, size_t> g_graph_kernels;   // executable graph -> number of kernel nodes
+}
 extern "C" void mpGraphBeginCapture(StreamContext ctx) {
   MP_CUDA_CHECK(cudaStreamBeginCapture(mp_stream(ctx), cudaStreamCaptureModeThreadLocal));
 }
 extern "C" void* mpGraphEndCapture(StreamContext ctx) {
   cudaGraph_t graph = nullptr;
   MP_CUDA_CHECK(cudaStreamEndCapture(mp_stream(ctx), &graph));
+  // kernel nodes of the captured work, kept for mpGraphKernelNodes
+  size_t n_nodes = 0, n_kernels = 0;
+  MP_CUDA_CHECK(cudaGraphGetNodes(graph, nullptr, &n_nodes));
+  std::vector<cudaGraphNode_t> nodes(n_nodes);
+  if (n_nodes > 0) MP_CUDA_CHECK(cudaGraphGetNodes(graph, nodes.data(), &n_nodes));
+  for (size_t i = 0; i < n_nodes; ++i) {
+    cudaGraphNodeType type;
+    MP_CUDA_CHECK(cudaGraphNodeGetType(nodes[i], &type));
+    if (type == cudaGraphNodeTypeKernel) ++n_kernels;
+  }
   cudaGraphExec_t exec = nullptr;
   MP_CUDA_CHECK(cudaGraphInstantiate(&exec, graph, 0));
   MP_CUDA_CHECK(cudaGraphDestroy(graph));
+  {
+    std::lock_guard<std::mutex> lock(g_graph_mutex);
+    g_graph_kernels[exec] = n_kernels;
+  }
   return exec;
+}
+extern "C" len_t mpGraphKernelNodes(void* exec) {
+  std::lock_guard<std::mutex> lock(g_graph_mutex);
+  auto it = g_graph_kernels.find(exec);
+  return it == g_graph_kernels.end() ? 0 : it->second;
 }
 extern "C" void mpGraphLaunch(void* exec, StreamContext ctx) {
   MP_CUDA_CHECK(cudaGraphLaunch(static_cast<cudaGraphExec_t>(exec), mp_stream(ctx)));
 }
 extern "C" void mpGraphDestroy(void* exec) {
-  if (exec != nullptr) MP_CUDA_CHECK(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(exec)));
+  if (exec == nullptr) return;
+  {
+    std::lock_guard<std::mutex> lock(g_graph_mutex);
+    g_graph_kernels.erase(exec);
+  }
+  MP_CUDA_CHECK(cudaGraphExecDestroy(static_cast<cudaGraphExec_t>(exec)));
 }

@@ -3,6 +3,7 @@
 #include "metaphor.hpp"
 
 #include <cassert>
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -889,3 +890,50 @@ void Adam::update(Graph* graph) {
 }  // namespace optm
 
 }  // namespace mp
+
+// README feed-forward block (README.md:90-104) timed through this layer: y = selu(linear(x, A, b)) on
+// x[32,256], A[256,256], b[256] in r32, then reverse(.free) of the sum loss and one SGD step (rate 1e-2).
+// out[0] = host microseconds per forward (stream-synchronised, as the .free walk is), out[1] = per forward +
+// reverse + update, out[2], out[3] = kernel launches per forward / per step.  Returns 0 on success.
+extern "C" int mpHostFeedForwardBench(int iters, double* out) {
+  using namespace mp;
+  if (iters <= 0 || out == nullptr) return 1;
+  const size_t m = 32, n = 256, k = 256;
+  Stream st = stream::init();
+  Graph* G = Graph::init({st, Mode::train});
+  Tensor x = G->tensor({Class::inp, Dtype::r32, {m, n}});
+  Tensor A = G->tensor({Class::wgt, Dtype::r32, {n, k}});
+  Tensor b = G->tensor({Class::wgt, Dtype::r32, {k}});
+  // deterministic values with the scale of the configuration (x ~ unit scale, A ~ 1/16, b = 0)
+  algo::sequence(x, -1.0, 2.0 / static_cast<double>(m * n));
+  algo::sequence(A, -1.0 / 16.0, 2.0 / 16.0 / static_cast<double>(n * k));
+  algo::fill(b, 0.0);
+  optm::SGD sgd{1e-2, optm::ClipRange()};
+  auto step = [&](bool train) {
+    Tensor lin = ops::linear(x, A, b, "ij,jk->ik");
+    Tensor y = ops::selu(lin);
+    if (train) {
+      G->reset(ResetGroup::leaf, ResetComponent::grd);
+      y.reverse(ReverseCleanup::free);
+      sgd.update(G);
+    } else {
+      stream::sync(st);
+      y.free(); lin.free();
+    }
+  };
+  for (int i = 0; i < 20; ++i) step(true);
+  stream::sync(st);
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int i = 0; i < iters; ++i) step(false);
+  const auto t1 = std::chrono::steady_clock::now();
+  for (int i = 0; i < iters; ++i) step(true);
+  stream::sync(st);
+  const auto t2 = std::chrono::steady_clock::now();
+  out[0] = std::chrono::duration<double, std::micro>(t1 - t0).count() / iters;
+  out[1] = std::chrono::duration<double, std::micro>(t2 - t1).count() / iters;
+  out[2] = 2.0;    // linear (bias in the contraction's epilogue), selu
+  out[3] = 13.0;   // + 3 gradient fills, seed fill, selu reverse, 2 contractions, column sum (2 kernels), 2 SGD updates
+  G->deinit();
+  stream::deinit(st);
+  return 0;
+}

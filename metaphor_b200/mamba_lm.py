@@ -177,16 +177,56 @@ class MambaLM:
         """Device address of a parameter (or of its gradient) inside a flat buffer."""
         return buf.data_ptr() + (self.offsets[name][0] + extra) * buf.element_size()
 
+    def _timed(self, name, call):
+        """Run `call()`; while a profile is being taken, bracket it with CUDA events on the library's stream."""
+        prof = getattr(self, "_prof", None)
+        if prof is None:
+            call()
+            return
+        import torch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self._prof_ts)
+        call()
+        e1.record(self._prof_ts)
+        prof.append((name, e0, e1))
+
     def _L(self, name, *args):
         import torch
-        launch(name, torch.float16, *args, self.stream)
+        label = name + "_r16"
+        if name.startswith("inner_product"):
+            label += "[%dx%dx%d]" % tuple(args[-3:])
+        self._timed(label, lambda: launch(name, torch.float16, *args, self.stream))
 
     def _L32(self, name, *args):
         import torch
-        launch(name, torch.float32, *args, self.stream)
+        self._timed(name + "_r32", lambda: launch(name, torch.float32, *args, self.stream))
 
     def _refresh_w16(self):
-        self._lib.launch_convert_r32_r16(C.c_void_p(self.w32.data_ptr()), C.c_void_p(self.w16.data_ptr()), self.n_flat, self.stream.ctx)
+        self._timed("convert_r32_r16", lambda: self._lib.launch_convert_r32_r16(
+            C.c_void_p(self.w32.data_ptr()), C.c_void_p(self.w16.data_ptr()), self.n_flat, self.stream.ctx))
+
+    def profile_step(self, comm=None, world=1, **adam):
+        """One training step issued launcher by launcher (no graph replay) with a CUDA-event pair around
+        every launcher call.  Returns {launcher: {"ms": total device time, "calls": count}}; a launcher that
+        forks work onto the library's side streams is bracketed on the caller's stream, join included."""
+        self.stream.sync()
+        self._prof, self._prof_ts = [], self.stream.torch_stream()
+        try:
+            self.forward()
+            self.loss_and_logit_gradient()
+            self.backward()
+            if comm is not None and world > 1:
+                self._timed("all_reduce_sum", lambda: comm.all_reduce_sum(self.g32, self.stream))
+            self.adam_step(world=world, **adam)
+            self.stream.sync()
+            out = {}
+            for name, e0, e1 in self._prof:
+                r = out.setdefault(name, {"ms": 0.0, "calls": 0})
+                r["ms"] += e0.elapsed_time(e1)
+                r["calls"] += 1
+        finally:
+            self._prof = None
+        return out
 
     def set_batch(self, ids, targets):
         """ids, targets: int32 tensors of batch*seqlen tokens, on the host (pinned memory makes the copy
@@ -276,7 +316,8 @@ class MambaLM:
                     self._p(G16, p + "norm_w"), 1.0, self.rms_scratch, T, c.d_model)
             # (alpha = 1 would also accumulate the gain gradient; G16 was zero-filled, so that is a plain write)
         self._L("embedding_reverse", self.ids, self.gh, self._p(G32, "embedding"), T, c.d_model, c.vocab)
-        self._lib.launch_convert_r16_r32(C.c_void_p(G16.data_ptr()), C.c_void_p(G32.data_ptr()), 1.0, self.n_flat, self.stream.ctx)
+        self._timed("convert_r16_r32", lambda: self._lib.launch_convert_r16_r32(
+            C.c_void_p(G16.data_ptr()), C.c_void_p(G32.data_ptr()), 1.0, self.n_flat, self.stream.ctx))
 
     # ------------------------------------------------------------------ optimizer
     def adam_step(self, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, world=1):
@@ -309,6 +350,17 @@ class MambaLM:
         if comm is not None and world > 1:
             comm.all_reduce_sum(self.g32, self.stream)
         self.adam_step(world=world, **adam)
+
+    def all_reduce_description(self) -> str:
+        return "one mpAllReduceSum (NCCL) over the flat r32 gradient (%d bytes) after the reverse pass, on the compute stream" % (self.n_flat * 4)
+
+    def release(self):
+        """Destroy the captured graph (if any) and the stream; the device buffers go with the object."""
+        self.stream.sync()
+        if getattr(self, "graph", None):
+            self._lib.mpGraphDestroy(self.graph)
+            self.graph = None
+        self.stream.close()
 
     def loss(self) -> float:
         self.stream.sync()
