@@ -598,10 +598,11 @@ __global__ void __launch_bounds__(256) ssd_boundary_dot_kernel(const __half* __r
 }
 
 // One CTA per (b, h); one thread per step of a chunk (Q <= 256), chunks walked from the last to the first.
+// `halves` = 2: u and v are the sums of two arrays, the second `B*H*L` elements after the first.
 __global__ void __launch_bounds__(256) ssd_scalar_grads_kernel(const float* __restrict__ u, const float* __restrict__ v,
                                                                const float* __restrict__ dtt, const float* __restrict__ A,
                                                                const float* __restrict__ pin, float* __restrict__ gdt,
-                                                               float* __restrict__ gA_part, int B, int L, int H, int Q) {
+                                                               float* __restrict__ gA_part, int B, int L, int H, int Q, int halves) {
   __shared__ float warp_tot[8];
   __shared__ float total_s;
   __shared__ float ga_red[8];
@@ -614,7 +615,13 @@ __global__ void __launch_bounds__(256) ssd_scalar_grads_kernel(const float* __re
     const int j = static_cast<int>(threadIdx.x);           // thread 0 holds the latest step of the chunk
     const int t = c * Q + (Q - 1 - j);
     const bool in = j < Q;
-    const float d = in ? u[base + t] - v[base + t] : 0.f;
+    const size_t hs = static_cast<size_t>(B) * H * L;
+    float ut = 0.f, vt = 0.f;
+    if (in) {
+      ut = u[base + t]; vt = v[base + t];
+      if (halves == 2) { ut += u[hs + base + t]; vt += v[hs + base + t]; }
+    }
+    const float d = ut - vt;
     float s = d;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -634,7 +641,7 @@ __global__ void __launch_bounds__(256) ssd_scalar_grads_kernel(const float* __re
     if (in) {
       const float ga = right + within + resid * (static_cast<float>(j + 1) / static_cast<float>(Q));
       const float dtv = dtt[base + t];
-      gdt[(static_cast<size_t>(b) * L + t) * H + h] = v[base + t] / dtv + Ah * ga;
+      gdt[(static_cast<size_t>(b) * L + t) * H + h] = vt / dtv + Ah * ga;
       ga_acc += dtv * ga;
     }
     __syncthreads();
@@ -887,12 +894,53 @@ void mp_ssd_generic_reverse_r16(const void* x, const void* dt, const void* A, co
                                 void* gA, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim,
                                 len_t dstate, len_t ngroups, StreamContext ctx);
 
+// chunk-walk kernels (ssd_walk.cu)
+bool mp_ssd_walk_supported(int L, int H, int P, int N, int G);
+void mp_ssd_walk_cumsum(const float* dt, const float* A, float* cum, float* dtt, float* colf_c, float* colf_a, int B, int L, int H,
+                        cudaStream_t st);
+void mp_ssd_walk(int anti, const __half* q, const __half* k, const __half* v, const float* cum, const float* dtt, const float* colf, __half* out,
+                 const __half* z, float* dot_out, __half* hs_out, int B, int L, int H, int G, uint32_t* status, cudaStream_t st);
+
+void mp_ssd_group_grads(const __half* gy, const __half* x, const __half* Bm, const __half* Cm, const __half* hs_causal, const __half* hs_anti,
+                        const float* cum, const float* dtt, const float* colf_c, __half* gB, __half* gC, int B, int L, int H, int G,
+                        uint32_t* status, cudaStream_t st);
+
+namespace {
+// Scratch of the walk path: prefix sums and dt in [B,H,L] order; for the reverse also the states every 128-step
+// chunk receives from its predecessors and from its successors (r16 [B,H,L/128][128][64]).
+struct WalkScratch { float* cum; float* dtt; float* colf_c; float* colf_a; __half* hs_causal; __half* hs_anti; float* pin; float* u; float* v; float* ga_part; size_t total; };
+WalkScratch walk_carve(void* base, const SsdDims& d, bool reverse, size_t off0) {
+  WalkScratch w;
+  size_t off = off0;
+  auto take = [&](size_t bytes) { void* p = base ? static_cast<unsigned char*>(base) + off : nullptr; off += (bytes + 255) & ~size_t(255); return p; };
+  const size_t bhl = static_cast<size_t>(d.B) * d.H * d.L;
+  w.cum = static_cast<float*>(take(bhl * 4));
+  w.dtt = static_cast<float*>(take(bhl * 4));
+  w.colf_c = static_cast<float*>(take(bhl * 4));
+  w.colf_a = static_cast<float*>(take(reverse ? bhl * 4 : 0));
+  const size_t st = static_cast<size_t>(d.B) * d.H * (d.L / 128) * 128 * 64 * 2;
+  w.hs_causal = static_cast<__half*>(take(reverse ? st : 0));
+  w.hs_anti = static_cast<__half*>(take(reverse ? st : 0));
+  w.pin = static_cast<float*>(take(reverse ? static_cast<size_t>(d.B) * d.H * (d.L / 128) * 4 : 0));
+  w.u = static_cast<float*>(take(reverse ? 2 * bhl * 4 : 0));     // one array per half of the columns
+  w.v = static_cast<float*>(take(reverse ? 2 * bhl * 4 : 0));
+  w.ga_part = static_cast<float*>(take(reverse ? static_cast<size_t>(d.B) * d.H * 4 : 0));
+  w.total = off;
+  return w;
+}
+}  // namespace
+
 // r16 storage (for r32 / r64 see mpSsdScanGenericScratchBytes)
 extern "C" len_t mpSsdScanScratchBytes(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups,
                                        len_t chunk, uint32_t reverse) {
   const SsdDims d = ssd_dims(batch, seqlen, heads, headdim, dstate, ngroups, chunk);
   if (batch == 0 || seqlen == 0 || heads == 0) return 256;
   if (!ssd_tensor_path(d)) return mpSsdScanGenericScratchBytes(0, batch, seqlen, heads, headdim, dstate, ngroups, reverse);
+  if (mp_ssd_walk_supported(d.L, d.H, d.P, d.N, d.G)) {
+    if (reverse != 0) return walk_carve(nullptr, d, true, 0).total;
+    const size_t a = walk_carve(nullptr, d, false, 0).total, b = ssd_carve(nullptr, d, false).total;   // either forward path
+    return a > b ? a : b;
+  }
   return ssd_carve(nullptr, d, reverse != 0).total;
 }
 
@@ -910,6 +958,15 @@ extern "C" void launch_ssd_scan_r16(const void* x, const void* dt, const void* A
   if (scratch == nullptr) MP_FATAL("ssd_scan: scratch must not be NULL");
   MpStreamState* state = mp_state(ctx);
   cudaStream_t st = mp_stream(ctx);
+  // The forward pass runs the three-phase path by default (measured faster than the chunk walk at 8 x 8192 x 32 and
+  // 8 x 2048 x 24); MP_SSD_WALK_FORWARD selects the walk, which needs no state scratch.
+  if (mp_ssd_walk_supported(d.L, d.H, d.P, d.N, d.G) && getenv("MP_SSD_WALK_FORWARD") != nullptr) {
+    const WalkScratch w = walk_carve(scratch, d, false, 0);
+    mp_ssd_walk_cumsum(static_cast<const float*>(dt), static_cast<const float*>(A), w.cum, w.dtt, w.colf_c, nullptr, d.B, d.L, d.H, st);
+    mp_ssd_walk(0, static_cast<const __half*>(Cm), static_cast<const __half*>(Bm), static_cast<const __half*>(x), w.cum, w.dtt, w.colf_c,
+                static_cast<__half*>(y), nullptr, nullptr, nullptr, d.B, d.L, d.H, d.G, state->status_dev, st);
+    return;
+  }
   const SsdScratch sc = ssd_carve(scratch, d, false);
   ssd_cumsum_kernel<<<d.B * d.H * d.nc, 256, 0, st>>>(static_cast<const float*>(dt), static_cast<const float*>(A), sc.cum, sc.dtt,
                                                      d.B, d.L, d.H, d.Q);
@@ -943,11 +1000,42 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
   if (scratch == nullptr) MP_FATAL("ssd_scan_reverse: scratch must not be NULL");
   MpStreamState* state = mp_state(ctx);
   cudaStream_t st = mp_stream(ctx);
-  const SsdScratch sc = ssd_carve(scratch, d, true);
   const __half* xh = static_cast<const __half*>(x);
   const __half* bh = static_cast<const __half*>(Bm);
   const __half* ch = static_cast<const __half*>(Cm);
   const __half* gyh = static_cast<const __half*>(gy);
+  if (mp_ssd_walk_supported(d.L, d.H, d.P, d.N, d.G)) {
+    // Two chunk walks side by side (anti-causal: gx and the row dots <gx, x>; causal: the row dots <gy, y>), both
+    // leaving the states every 128-step chunk receives; then gB / gC from those states, and gdt / gA.
+    const WalkScratch w = walk_carve(scratch, d, true, 0);
+    const bool side = getenv("MP_SSD_SERIAL") == nullptr;
+    cudaStream_t lane1 = st;
+    mp_ssd_walk_cumsum(static_cast<const float*>(dt), static_cast<const float*>(A), w.cum, w.dtt, w.colf_c, w.colf_a, d.B, d.L, d.H, st);
+    if (side) {
+      mp_aux_init(state);
+      lane1 = state->aux_stream[0];
+      MP_CUDA_CHECK(cudaEventRecord(state->aux_fork, st));
+      MP_CUDA_CHECK(cudaStreamWaitEvent(lane1, state->aux_fork, 0));
+    }
+    mp_ssd_walk(1, bh, ch, gyh, w.cum, w.dtt, w.colf_a, static_cast<__half*>(gx), xh, w.v, w.hs_anti, d.B, d.L, d.H, d.G, state->status_dev, st);
+    mp_ssd_walk(0, ch, bh, xh, w.cum, w.dtt, w.colf_c, nullptr, gyh, w.u, w.hs_causal, d.B, d.L, d.H, d.G, state->status_dev, lane1);
+    if (side) {
+      MP_CUDA_CHECK(cudaEventRecord(state->aux_join[0], lane1));
+      MP_CUDA_CHECK(cudaStreamWaitEvent(st, state->aux_join[0], 0));
+    }
+    mp_ssd_group_grads(gyh, xh, bh, ch, w.hs_causal, w.hs_anti, w.cum, w.dtt, w.colf_c, static_cast<__half*>(gB), static_cast<__half*>(gC),
+                       d.B, d.L, d.H, d.G, state->status_dev, st);
+    const int wnc = d.L / 128;
+    ssd_boundary_dot_kernel<<<d.B * d.H * wnc, 256, 0, st>>>(w.hs_anti, w.hs_causal, w.pin, wnc, d.N * d.P);
+    MP_LAUNCH_CHECK();
+    ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, st>>>(w.u, w.v, w.dtt, static_cast<const float*>(A), w.pin, static_cast<float*>(gdt), w.ga_part,
+                                                      d.B, d.L, d.H, 128, 2);
+    MP_LAUNCH_CHECK();
+    ssd_sum_batches_kernel<<<(d.H + 127) / 128, 128, 0, st>>>(w.ga_part, static_cast<float*>(gA), d.B, d.H);
+    MP_LAUNCH_CHECK();
+    return;
+  }
+  const SsdScratch sc = ssd_carve(scratch, d, true);
   ssd_cumsum_kernel<<<d.B * d.H * d.nc, 256, 0, st>>>(static_cast<const float*>(dt), static_cast<const float*>(A), sc.cum, sc.dtt,
                                                      d.B, d.L, d.H, d.Q);
   MP_LAUNCH_CHECK();
@@ -1003,11 +1091,11 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
   }
   // gdt, gA
   // (operator 0 = gx: anti-causal states of C gy^T; operator 1 = u: causal states of B x^T; both [B,H,nc][N][P])
-  ssd_boundary_dot_kernel<<<d.B * d.H * d.nc, 256, 0, st>>>(sc.hs_op[0], sc.hs_op[1], sc.pin, d.nc, d.N * d.P);
-  MP_LAUNCH_CHECK();
-  ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, st>>>(sc.u, sc.v, sc.dtt, static_cast<const float*>(A), sc.pin, static_cast<float*>(gdt),
-                                                    sc.ga_part, d.B, d.L, d.H, d.Q);
-  MP_LAUNCH_CHECK();
+    ssd_boundary_dot_kernel<<<d.B * d.H * d.nc, 256, 0, st>>>(sc.hs_op[0], sc.hs_op[1], sc.pin, d.nc, d.N * d.P);
+    MP_LAUNCH_CHECK();
+    ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, st>>>(sc.u, sc.v, sc.dtt, static_cast<const float*>(A), sc.pin, static_cast<float*>(gdt),
+                                                      sc.ga_part, d.B, d.L, d.H, d.Q, 1);
+    MP_LAUNCH_CHECK();
   ssd_sum_batches_kernel<<<(d.H + 127) / 128, 128, 0, st>>>(sc.ga_part, static_cast<float*>(gA), d.B, d.H);
   MP_LAUNCH_CHECK();
 }

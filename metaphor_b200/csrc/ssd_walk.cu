@@ -1,0 +1,905 @@
+// Mamba-2 SSD scan as a chunk walk: one CTA per (batch, head) goes through the
+// sequence 128 steps at a time and keeps the carried state on chip, so no chunk
+// state is written to or scanned from global memory.  The same kernel evaluates
+// the operator in both directions,
+//     out_i = r_i * sum_j mask(i,j) * decay(i,j) * c_j * <q_i, k_j> * v_j
+//   causal      : j <= i, decay = exp(cum_i - cum_j), c_j = dt_j, r_i = 1       (chunks first to last)
+//   anti-causal : j >= i, decay = exp(cum_j - cum_i), c_j = 1,    r_i = dt_i    (chunks last to first)
+// with cum the inclusive prefix sum of dt*A inside the 128-step chunk:
+//   forward pass   y  = causal(q, k, v) = (C, B, x)
+//   reverse pass   gx = anti(q, k, v)   = (B, C, gy),   v_t = <gx_t, x_t>
+//                  u_t = <gy_t, y_t> from a second causal walk that keeps the row dots and drops y.
+// Per chunk (all on the 5th-generation tensor core, operands in 128-byte
+// swizzled shared memory, fp32 accumulators in TMEM):
+//   G   = q k^T                         128 x 128, K = 128   -> TMEM
+//   P   = G o F  (mask, decay, c_j)     TMEM -> registers -> r16 operand tile in shared memory
+//   Yd  = P v                           128 x 64,  K = 128
+//   Yo  = q H                           128 x 64,  K = 128   (H = state received by the chunk, r16 copy in smem)
+//   S   = k^T (w o v)                   128 x 64,  K = 128   (w_j = decay of step j to the chunk's far end)
+//   out = r o (Yd + f o Yo),  H' = D H + S   (H in fp32 registers of the eight worker warps)
+// Warp 0 feeds the two-stage ring by TMA, one thread of warp 1 issues the MMAs, warps 2-9
+// (two warps per TMEM lane quarter, one per half of the columns) do the element-wise parts.
+// The chunk length of the walk is fixed (128); the `chunk` argument of the public launcher
+// only selects the evaluation order of a result that does not depend on it.
+#include "mp_tcgen05.cuh"
+
+#include <cuda.h>
+#include <mutex>
+
+namespace {
+
+constexpr int WQ = 128;                       // steps per chunk
+constexpr int WN = 128;                       // state size (columns of q and k)
+constexpr int WP = 64;                        // head size (columns of v)
+constexpr int W_THREADS = 320;
+constexpr int W_TILE_QK = 2 * WQ * 128;       // [2 k-blocks][128 rows][128 B]
+constexpr int W_TILE_V = WQ * 128;            // [128 rows][128 B]
+constexpr int W_STAGE = 2 * W_TILE_QK + W_TILE_V;
+constexpr int W_OFF_P = 2 * W_STAGE;
+constexpr int W_OFF_H = W_OFF_P + W_TILE_QK;
+constexpr int W_OFF_VS = W_OFF_H + W_TILE_V;
+constexpr int W_OFF_TAIL = W_OFF_VS + W_TILE_V;   // 229376
+constexpr int W_TAIL_BYTES = 2048;
+constexpr int W_SMEM_BYTES = W_OFF_TAIL + W_TAIL_BYTES + 1024;   // + alignment slack = 232448 (the per-CTA maximum)
+// TMEM columns
+constexpr uint32_t TC_G = 0, TC_S = 128, TC_Y = 192, TC_COLS = 512;   // Yd / Yo of chunk parity p at TC_Y + p * 128 (+ 64)
+
+enum { B_FULL0 = 0, B_FULL1, B_EMPTY0, B_EMPTY1, B_GFULL, B_PREADY, B_VSREADY, B_HREADY, B_YFULL, B_SFULL, B_SCAL, B_COUNT };
+
+struct WalkArgs {
+  int B, L, H, G, nc;
+  const float* cum;        // [B, H, L] inclusive prefix sums of dt*A inside each 128-step chunk
+  const float* dtt;        // [B, H, L] dt
+  const float* colf;       // [B, H, L] column factor of every step relative to the far end of its 32-step piece
+  __half* out;             // [B*L, H*64] or null
+  const __half* z;         // dot partner, same indexing as out, or null
+  float* dot_out;          // [2][B, H, L] row dots <z, out> from the fp32 accumulators, one array per half of the columns, or null
+  long long* prof;         // debug: per-phase clock sums of CTA 0 (null in normal use)
+  __half* hs_out;          // [B, H, nc][128][64]: state every chunk receives, or null
+  uint32_t* status;
+};
+
+__device__ __forceinline__ float w_exp(float x) { return __expf(x); }
+
+// One arrival per warp: every lane has made its shared-memory writes visible to the asynchronous proxy (and
+// finished its TMEM reads) before lane 0 arrives for the warp.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+  fence_proxy_async_smem();
+  tcgen05_fence_before_sync();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+}
+
+// The hand-offs of the walk sit on its critical path: poll without a suspend hint first (a suspended warp
+// wakes up hundreds of cycles after the phase completes), then fall back to the bounded, abortable wait.
+__device__ __forceinline__ bool walk_wait(uint64_t* bar, uint32_t parity, uint32_t* status, volatile int* abort) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(mp_smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return mbar_wait_abortable(bar, parity, status, abort);
+}
+
+template <int ANTI>
+__global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                               const __grid_constant__ CUtensorMap map_k,
+                                                               const __grid_constant__ CUtensorMap map_v,
+                                                               const __grid_constant__ CUtensorMap map_hs, const WalkArgs g) {
+  extern __shared__ unsigned char walk_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(walk_smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sP = smem + W_OFF_P;
+  unsigned char* sH = smem + W_OFF_H;
+  unsigned char* sVs = smem + W_OFF_VS;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + W_OFF_TAIL);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + W_OFF_TAIL + 112);
+  volatile int* abort = reinterpret_cast<volatile int*>(smem + W_OFF_TAIL + 116);
+  float* s_cum = reinterpret_cast<float*>(smem + W_OFF_TAIL + 128);   // [128]
+  float* s_colf = s_cum + WQ;                                         // [128]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.x % g.H, b = blockIdx.x / g.H;
+  const int grp = h / (g.H / g.G);
+  const int nc = g.nc;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bars + B_FULL0, 1); mbar_init(bars + B_FULL1, 1);
+    mbar_init(bars + B_EMPTY0, 1); mbar_init(bars + B_EMPTY1, 1);
+    mbar_init(bars + B_GFULL, 1); mbar_init(bars + B_YFULL, 1); mbar_init(bars + B_SFULL, 1);
+    mbar_init(bars + B_PREADY, 8); mbar_init(bars + B_VSREADY, 8); mbar_init(bars + B_HREADY, 8);
+    mbar_init(bars + B_SCAL, 4);
+    *abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TC_COLS);
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      for (int k = 0; k < nc; ++k) {
+        const int c = ANTI ? nc - 1 - k : k;
+        const int s = k & 1;
+        if (!walk_wait(bars + B_EMPTY0 + s, ((k >> 1) & 1) ^ 1u, g.status, abort)) break;
+        unsigned char* st = smem + s * W_STAGE;
+        const int row0 = b * g.L + c * WQ;
+        mbar_arrive_expect_tx(bars + B_FULL0 + s, W_STAGE);
+        tma_load_2d(st, &map_q, grp * WN, row0, bars + B_FULL0 + s);
+        tma_load_2d(st + WQ * 128, &map_q, grp * WN + 64, row0, bars + B_FULL0 + s);
+        tma_load_2d(st + W_TILE_QK, &map_k, grp * WN, row0, bars + B_FULL0 + s);
+        tma_load_2d(st + W_TILE_QK + WQ * 128, &map_k, grp * WN + 64, row0, bars + B_FULL0 + s);
+        tma_load_2d(st + 2 * W_TILE_QK, &map_v, h * WP, row0, bars + B_FULL0 + s);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    // Order per chunk k: Yd(k) as soon as its P tile is written, Yo(k) as soon as the state the chunk
+    // receives is in shared memory, S(k), then the scores of chunk k+1.
+    if (lane == 0) {
+      const uint32_t id_g = umma_instr_desc(UMMA_FMT_F16, 0u, 0u, 128, 128);   // q (K-major) x k (K-major)
+      const uint32_t id_y = umma_instr_desc(UMMA_FMT_F16, 0u, 1u, 128, 64);    // K-major A x MN-major B
+      const uint32_t id_s = umma_instr_desc(UMMA_FMT_F16, 1u, 1u, 128, 64);    // k^T (MN-major A) x MN-major B
+      const uint32_t sp = mp_smem_u32(sP), sh = mp_smem_u32(sH), svs = mp_smem_u32(sVs);
+      auto issue_g = [&](int s) {
+        const uint32_t sq = mp_smem_u32(smem + s * W_STAGE), sk = sq + W_TILE_QK;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t o = (ks >> 2) * (WQ * 128) + (ks & 3) * 32;
+          umma<false>(tmem + TC_G, umma_smem_desc(sq + o, 16, 1024), umma_smem_desc(sk + o, 16, 1024), id_g, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(bars + B_GFULL);
+      };
+      const bool prof = g.prof != nullptr && blockIdx.x == 0;
+      long long pt[5] = {0, 0, 0, 0, 0};
+      long long tlast = prof ? clock64() : 0;
+      auto stamp = [&](int i) { if (prof) { const long long t = clock64(); pt[i] += t - tlast; tlast = t; } };
+      bool ok = walk_wait(bars + B_FULL0, 0, g.status, abort);
+      if (ok) { tcgen05_fence_after_sync(); issue_g(0); }
+      for (int k = 0; ok && k < nc; ++k) {
+        const int s = k & 1;
+        const uint32_t sq = mp_smem_u32(smem + s * W_STAGE), sk = sq + W_TILE_QK, sv = sk + W_TILE_QK;
+        const uint32_t ty = tmem + TC_Y + (k & 1) * 128;
+        stamp(0);
+        if (!walk_wait(bars + B_PREADY, k & 1, g.status, abort)) { ok = false; break; }
+        stamp(1);
+        tcgen05_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t o = (ks >> 2) * (WQ * 128) + (ks & 3) * 32;
+          umma<false>(ty, umma_smem_desc(sp + o, 16, 1024), umma_smem_desc(sv + ks * 2048, W_TILE_V, 1024), id_y, ks != 0 ? 1u : 0u);
+        }
+        if (k > 0) {
+          stamp(0);
+          if (!walk_wait(bars + B_HREADY, (k - 1) & 1, g.status, abort)) { ok = false; break; }
+          stamp(2);
+          tcgen05_fence_after_sync();
+          if (g.hs_out != nullptr) {   // the state this chunk receives, straight from its operand tile
+            const int c = ANTI ? nc - 1 - k : k;
+            tma_store_2d(&map_hs, sH, 0, static_cast<int>(((static_cast<size_t>(b) * g.H + h) * nc + c) * WN));
+            bulk_commit();
+          }
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t o = (ks >> 2) * (WQ * 128) + (ks & 3) * 32;
+            umma<false>(ty + 64, umma_smem_desc(sq + o, 16, 1024), umma_smem_desc(sh + ks * 2048, W_TILE_V, 1024), id_y, ks != 0 ? 1u : 0u);
+          }
+        }
+        if (g.hs_out != nullptr && k > 0) bulk_wait_read<0>();   // the workers rewrite the state tile after this phase
+        umma_commit(bars + B_YFULL);
+        // scores of the next chunk (its stage was released by S(k-1); the workers are past G(k))
+        if (k + 1 < nc) {
+          const int s1 = (k + 1) & 1;
+          stamp(0);
+          if (!walk_wait(bars + B_FULL0 + s1, ((k + 1) >> 1) & 1, g.status, abort)) { ok = false; break; }
+          stamp(4);
+          tcgen05_fence_after_sync();
+          issue_g(s1);
+        }
+        stamp(0);
+        if (!walk_wait(bars + B_VSREADY, k & 1, g.status, abort)) { ok = false; break; }
+        stamp(3);
+        tcgen05_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          umma<false>(tmem + TC_S, umma_smem_desc(sk + ks * 2048, WQ * 128, 1024), umma_smem_desc(svs + ks * 2048, W_TILE_V, 1024), id_s,
+                      ks != 0 ? 1u : 0u);
+        umma_commit(bars + B_SFULL);
+        umma_commit(bars + B_EMPTY0 + s);
+      }
+      if (g.hs_out != nullptr) bulk_wait_all<0>();
+      if (prof) {
+#pragma unroll
+        for (int i = 0; i < 5; ++i) g.prof[8 + i] = pt[i];
+      }
+    }
+  } else {
+    // ------------------------------ workers -----------------------------------
+    // Software pipeline: in iteration k the warps write the P tile of chunk k+1, fold S(k) into the carried
+    // state, scale the values of chunk k+1 and only then read chunk k's accumulators, so that every MMA of
+    // chunk k+1 is in flight while chunk k's epilogue runs.
+    const int quarter = warp & 3;              // TMEM lane quarter this warp may read
+    const int ch = (warp - 2) >> 2;            // column half
+    const int r = quarter * 32 + lane;         // row of every 128-row tile
+    const size_t bh = static_cast<size_t>(b) * g.H + h;
+    const float* cum_g = g.cum + bh * g.L;
+    const float* dt_g = g.dtt + bh * g.L;
+    const float* colf_g = g.colf + bh * g.L;
+    const uint32_t tl = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int pitch = g.H * WP;
+    float state[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) state[e] = 0.f;
+    const int c_first = ANTI ? nc - 1 : 0;
+    if (g.hs_out != nullptr) {   // the first chunk of the walk receives nothing
+      uint4* dst = reinterpret_cast<uint4*>(g.hs_out + ((bh * nc + c_first) * WN + r) * WP + ch * 32);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    bool ok = true;
+    const bool prof = g.prof != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
+    long long pt[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    long long tlast = prof ? clock64() : 0;
+    auto stamp = [&](int i) { if (prof) { const long long t = clock64(); pt[i] += t - tlast; tlast = t; } };
+
+    // values of the walk's scalars: chunk in hand (cur) and the one after it (nxt)
+    float cum_cur = 0.f, dt_cur = 0.f, last_cur = 0.f;
+    float cum_nxt = cum_g[c_first * WQ + r], dt_nxt = dt_g[c_first * WQ + r], colf_nxt = colf_g[c_first * WQ + r];
+    float last_nxt = 0.f;
+
+    // publish the scalars of chunk kk (held in *_nxt) to shared memory and fetch those of the chunk after it
+    auto publish = [&](int kk) -> bool {
+      if (ch == 0) {
+        s_cum[r] = cum_nxt; s_colf[r] = colf_nxt;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + B_SCAL);
+      }
+      if (!walk_wait(bars + B_SCAL, kk & 1, g.status, abort)) return false;
+      last_nxt = s_cum[WQ - 1];
+      return true;
+    };
+    // w o v of the chunk whose scalars are in *_nxt
+    auto scale_values = [&](int kk) -> bool {
+      const int s = kk & 1;
+      if (!walk_wait(bars + B_FULL0 + s, (kk >> 1) & 1, g.status, abort)) return false;
+      const float wt = ANTI ? w_exp(cum_nxt) : w_exp(last_nxt - cum_nxt) * dt_nxt;
+      const __half2 wt2 = __float2half2_rn(wt);
+      const unsigned char* src = smem + s * W_STAGE + 2 * W_TILE_QK + r * 128;
+      unsigned char* dst = sVs + r * 128;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int off = ((ch * 4 + q4) ^ (r & 7)) << 4;
+        uint4 v = *reinterpret_cast<const uint4*>(src + off);
+        __half2* h2 = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h2[e] = __hmul2(h2[e], wt2);
+        *reinterpret_cast<uint4*>(dst + off) = v;
+      }
+      warp_arrive(bars + B_VSREADY, lane);
+      return true;
+    };
+    // P = G o F of chunk index cc (k-th of the walk: kk), scalars in *_nxt
+    auto transform = [&](int kk, int cc) -> bool {
+      if (!walk_wait(bars + B_GFULL, kk & 1, g.status, abort)) return false;
+      tcgen05_fence_after_sync();
+#pragma unroll 1
+      for (int pp = 0; pp < 2; ++pp) {
+        const int pc = ch * 2 + pp;              // 32-column piece of the chunk
+        const int j0 = pc * 32;
+        unsigned char* prow = sP + ch * (WQ * 128) + r * 128;
+        const bool zero = ANTI ? (pc < quarter) : (pc > quarter);   // warp-uniform: the whole piece is masked
+        if (zero) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(prow + (((pp * 4 + q4) ^ (r & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+          continue;
+        }
+        uint32_t v[32];
+        tmem_ld_32x32(tl + TC_G + j0, v);
+        const int ref = ANTI ? j0 : j0 + 31;
+        const float rarg = ANTI ? s_cum[ref] - cum_nxt : cum_nxt - s_cum[ref];   // <= 0 off the diagonal piece
+        const bool diag = pc == quarter;
+        const bool direct = diag && rarg > 40.f;    // factorised form would overflow: rare, take the exact exponent per element
+        const float rowf = w_exp(direct ? 0.f : rarg);
+        tmem_ld_wait();
+        float f[32];
+        if (__any_sync(0xffffffffu, direct)) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int j = j0 + e;
+            const float cj = cum_g[cc * WQ + j];
+            f[e] = direct ? (ANTI ? w_exp(cj - cum_nxt) : w_exp(cum_nxt - cj) * dt_g[cc * WQ + j]) : s_colf[j] * rowf;
+          }
+        } else {
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 cf = *reinterpret_cast<const float4*>(s_colf + j0 + e4 * 4);
+            f[e4 * 4] = cf.x * rowf; f[e4 * 4 + 1] = cf.y * rowf; f[e4 * 4 + 2] = cf.z * rowf; f[e4 * 4 + 3] = cf.w * rowf;
+          }
+        }
+        if (diag) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e)
+            if (ANTI ? (e < lane) : (e > lane)) f[e] = 0.f;
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 o;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i0 = q4 * 8 + 2 * e;
+            const __half2 hv = __floats2half2_rn(__uint_as_float(v[i0]) * f[i0], __uint_as_float(v[i0 + 1]) * f[i0 + 1]);
+            ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+          }
+          *reinterpret_cast<uint4*>(prow + (((pp * 4 + q4) ^ (r & 7)) << 4)) = o;
+        }
+      }
+      warp_arrive(bars + B_PREADY, lane);
+      return true;
+    };
+    // scalars two chunks ahead, so that their loads are never waited for
+    float cum_pre = 0.f, dt_pre = 0.f, colf_pre = 0.f;
+    auto prefetch = [&](int kk) {   // scalars of the walk's kk-th chunk into *_pre (kk < nc)
+      const int cn = ANTI ? nc - 1 - kk : kk;
+      cum_pre = cum_g[cn * WQ + r]; dt_pre = dt_g[cn * WQ + r]; colf_pre = colf_g[cn * WQ + r];
+    };
+    if (nc > 1) prefetch(1);
+
+    // ---- prologue: chunk 0 up to its P tile ----------------------------------------
+    ok = publish(0) && scale_values(0) && transform(0, c_first);
+    for (int k = 0; ok && k < nc; ++k) {
+      const int c = ANTI ? nc - 1 - k : k;
+      const uint32_t par = k & 1;
+      const bool more = k + 1 < nc;
+      cum_cur = cum_nxt; dt_cur = dt_nxt; last_cur = last_nxt;
+      if (more) {
+        cum_nxt = cum_pre; dt_nxt = dt_pre; colf_nxt = colf_pre;
+        if (k + 2 < nc) prefetch(k + 2);
+      }
+      // Yd(k) has consumed the P tile, and every warp is past the shared scalars of chunk k
+      uint4 zc[4];
+      if (g.z != nullptr) {
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const size_t zrow = static_cast<size_t>(b) * g.L + c * WQ + quarter * 32 + it * 8 + (lane >> 2);
+          zc[it] = *reinterpret_cast<const uint4*>(g.z + zrow * pitch + h * WP + ch * 32 + (lane & 3) * 8);
+        }
+      }
+      stamp(0);
+      if (!walk_wait(bars + B_YFULL, par, g.status, abort)) { ok = false; break; }
+      stamp(1);
+      if (more) {
+        if (!publish(k + 1)) { ok = false; break; }
+        stamp(2);
+        if (!transform(k + 1, ANTI ? c - 1 : c + 1)) { ok = false; break; }
+        stamp(3);
+      }
+      // ---- H' = D H + S ---------------------------------------------------------------
+      if (!walk_wait(bars + B_SFULL, par, g.status, abort)) { ok = false; break; }
+      stamp(4);
+      tcgen05_fence_after_sync();
+      if (more) {
+        uint32_t sv[32];
+        tmem_ld_32x32(tl + TC_S + ch * 32, sv);
+        const float D = w_exp(last_cur);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) state[e] = D * state[e] + __uint_as_float(sv[e]);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 pk;
+          uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const __half2 hv = __floats2half2_rn(state[q4 * 8 + 2 * e], state[q4 * 8 + 2 * e + 1]);
+            ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+          }
+          *reinterpret_cast<uint4*>(sH + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4)) = pk;
+        }
+        warp_arrive(bars + B_HREADY, lane);
+        stamp(5);
+      }
+      // ---- out = r o (Yd + f o Yo) of chunk k -------------------------------------------
+      // staging = this warp's own positions of the scaled-value tile (S(k), its last reader, has completed, and the
+      // warp refills exactly these positions for chunk k+1 right after the epilogue)
+      unsigned char* stg = sVs;
+      uint4 zv[4];
+      if (g.z != nullptr) {
+        // the dot partner's rows arrive with whole-row loads (issued at the top of the iteration) and change
+        // hands through the warp's own positions of the staging tile
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int lr = quarter * 32 + it * 8 + (lane >> 2), cc = ch * 4 + (lane & 3);
+          *reinterpret_cast<uint4*>(stg + lr * 128 + ((cc ^ (lr & 7)) << 4)) = zc[it];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) zv[q4] = *reinterpret_cast<const uint4*>(stg + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4));
+        __syncwarp();
+      }
+      tcgen05_fence_after_sync();
+      {
+        uint32_t yd[32], yo[32];
+        const uint32_t ty = tl + TC_Y + (k & 1) * 128 + ch * 32;
+        tmem_ld_32x32(ty, yd);
+        if (k > 0) tmem_ld_32x32(ty + 64, yo);
+        const float fo = k > 0 ? (ANTI ? w_exp(last_cur - cum_cur) : w_exp(cum_cur)) : 0.f;
+        const float ro = ANTI ? dt_cur : 1.f;
+        tmem_ld_wait();
+        if (k == 0) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) yo[e] = 0u;
+        }
+        float o[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = ro * (__uint_as_float(yd[e]) + fo * __uint_as_float(yo[e]));
+        if (g.out != nullptr) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 pk;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __half2 hv = __floats2half2_rn(o[q4 * 8 + 2 * e], o[q4 * 8 + 2 * e + 1]);
+              ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            *reinterpret_cast<uint4*>(stg + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4)) = pk;
+          }
+          __syncwarp();
+          // whole 64-byte row pieces per store instruction
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int lr = quarter * 32 + it * 8 + (lane >> 2), cc = ch * 4 + (lane & 3);
+            const uint4 val = *reinterpret_cast<const uint4*>(stg + lr * 128 + ((cc ^ (lr & 7)) << 4));
+            const size_t orow = static_cast<size_t>(b) * g.L + c * WQ + lr;
+            *reinterpret_cast<uint4*>(g.out + orow * pitch + h * WP + cc * 8) = val;
+          }
+          __syncwarp();
+        }
+        if (g.z != nullptr) {
+          float dot = 0.f;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const __half2* z2 = reinterpret_cast<const __half2*>(&zv[q4]);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 zf = __half22float2(z2[e]);
+              dot += zf.x * o[q4 * 8 + 2 * e] + zf.y * o[q4 * 8 + 2 * e + 1];
+            }
+          }
+          g.dot_out[static_cast<size_t>(ch) * g.B * g.H * g.L + bh * g.L + c * WQ + r] = dot;
+        }
+      }
+      stamp(6);
+      if (more && !scale_values(k + 1)) { ok = false; break; }
+    }
+    stamp(7);
+    if (prof) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) g.prof[i] = pt[i];
+    }
+    (void)ok;
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, TC_COLS);
+}
+
+// ---------------------------------------------------------------------------
+// Gradients of B and C (summed over the heads of a group).  One CTA per (batch, 128-step chunk, group)
+// walks the group's heads; per head h
+//     Sc  = gy_h x_h^T                       128 x 128, K = 64      -> TMEM
+//     acc += Sc o L_h                        in registers (L_h = causal mask * exp(cum_i - cum_j) * dt_j)
+//     gC += (e_h o gy_h) Hc_h^T,  gB += (w_h o x_h) Ha_h^T          128 x 128, K = 64, accumulated over the heads in TMEM
+// (Hc_h / Ha_h = the state the chunk receives from its predecessors / successors, left by the two walks;
+//  e_i = exp(cum_i), w_j = exp(cum_last - cum_j) dt_j; the row factors are multiplied into the operand
+//  tiles in place once the score MMA has read them).  After the last head the summed scores go to shared memory once
+// and serve both products, as a K-major operand for gC += acc B and as an MN-major one for gB += acc^T C.
+// No per-head score tile and no per-head partial output ever reaches global memory.
+// ---------------------------------------------------------------------------
+constexpr int GG_TILE = WQ * 128;                 // [128 rows][128 B]
+constexpr int GG_STAGE = 4 * GG_TILE;             // gy, x, Hc, Ha
+constexpr int GG_OFF_ACC = 2 * GG_STAGE;          // summed scores, [2 k-blocks][128 rows][128 B]
+constexpr int GG_OFF_TAIL = GG_OFF_ACC + 2 * GG_TILE;
+constexpr int GG_SMEM_BYTES = GG_OFF_TAIL + 4096 + 1024;
+constexpr uint32_t GT_SC = 0, GT_C = 256, GT_B = 384;   // score buffers at 0 / 128
+enum { GB_FULL0 = 0, GB_FULL1, GB_EMPTY0, GB_EMPTY1, GB_SC0, GB_SC1, GB_SCALED, GB_SCAL, GB_GG, GB_BCFULL, GB_ACC, GB_OUT, GB_COUNT };
+
+struct GroupArgs {
+  int B, L, H, G, nc;
+  const float* cum; const float* dtt; const float* colf;   // [B, H, L], causal column factors
+  uint32_t* status;
+};
+
+__global__ void __launch_bounds__(W_THREADS, 1) ssd_group_grads_kernel(const __grid_constant__ CUtensorMap map_gy,
+                                                                      const __grid_constant__ CUtensorMap map_x,
+                                                                      const __grid_constant__ CUtensorMap map_hc,
+                                                                      const __grid_constant__ CUtensorMap map_ha,
+                                                                      const __grid_constant__ CUtensorMap map_b,
+                                                                      const __grid_constant__ CUtensorMap map_c,
+                                                                      const __grid_constant__ CUtensorMap map_gb,
+                                                                      const __grid_constant__ CUtensorMap map_gc, const GroupArgs g) {
+  extern __shared__ unsigned char walk_smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(walk_smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* sGG = smem + GG_OFF_ACC;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + GG_OFF_TAIL);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + GG_OFF_TAIL + 112);
+  volatile int* abort = reinterpret_cast<volatile int*>(smem + GG_OFF_TAIL + 116);
+  float* s_cum = reinterpret_cast<float*>(smem + GG_OFF_TAIL + 128);   // [2][128]
+  float* s_colf = s_cum + 2 * WQ;                                      // [2][128]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int hpg = g.H / g.G;
+  const int grp = blockIdx.x % g.G;
+  const int c = (blockIdx.x / g.G) % g.nc;
+  const int b = blockIdx.x / (g.G * g.nc);
+  const int row0 = b * g.L + c * WQ;
+  const int nh = hpg;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bars + GB_FULL0, 1); mbar_init(bars + GB_FULL1, 1);
+    mbar_init(bars + GB_EMPTY0, 1); mbar_init(bars + GB_EMPTY1, 1);
+    mbar_init(bars + GB_SC0, 1); mbar_init(bars + GB_SC1, 1);
+    mbar_init(bars + GB_SCALED, 8); mbar_init(bars + GB_SCAL, 8); mbar_init(bars + GB_GG, 8);
+    mbar_init(bars + GB_BCFULL, 1); mbar_init(bars + GB_ACC, 1); mbar_init(bars + GB_OUT, 8);
+    *abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TC_COLS);
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  tcgen05_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA: loads, then the output stores -------------
+    if (lane == 0) {
+      bool ok = true;
+      for (int hi = 0; hi < nh; ++hi) {
+        const int h = grp * hpg + hi, s = hi & 1;
+        if (!walk_wait(bars + GB_EMPTY0 + s, ((hi >> 1) & 1) ^ 1u, g.status, abort)) { ok = false; break; }
+        unsigned char* st = smem + s * GG_STAGE;
+        const int srow = ((b * g.H + h) * g.nc + c) * WN;
+        mbar_arrive_expect_tx(bars + GB_FULL0 + s, GG_STAGE);
+        tma_load_2d(st, &map_gy, h * WP, row0, bars + GB_FULL0 + s);
+        tma_load_2d(st + GG_TILE, &map_x, h * WP, row0, bars + GB_FULL0 + s);
+        tma_load_2d(st + 2 * GG_TILE, &map_hc, 0, srow, bars + GB_FULL0 + s);
+        tma_load_2d(st + 3 * GG_TILE, &map_ha, 0, srow, bars + GB_FULL0 + s);
+      }
+      // B and C of the chunk take the place of the two stages once their last MMAs have completed
+      for (int s = 0; ok && s < 2; ++s) {
+        const int uses = (nh + 1 - s) / 2;       // heads that went through stage s
+        if (uses > 0 && !walk_wait(bars + GB_EMPTY0 + s, (uses - 1) & 1, g.status, abort)) { ok = false; break; }
+      }
+      if (ok) {
+        mbar_arrive_expect_tx(bars + GB_BCFULL, 4 * GG_TILE);
+        tma_load_2d(smem, &map_b, grp * WN, row0, bars + GB_BCFULL);
+        tma_load_2d(smem + GG_TILE, &map_b, grp * WN + 64, row0, bars + GB_BCFULL);
+        tma_load_2d(smem + GG_STAGE, &map_c, grp * WN, row0, bars + GB_BCFULL);
+        tma_load_2d(smem + GG_STAGE + GG_TILE, &map_c, grp * WN + 64, row0, bars + GB_BCFULL);
+        if (walk_wait(bars + GB_OUT, 0, g.status, abort)) {
+          // staged outputs: gC behind the B tiles of stage 0, gB behind the C tiles of stage 1
+          tma_store_2d(&map_gc, smem + 2 * GG_TILE, grp * WN, row0);
+          tma_store_2d(&map_gc, smem + 3 * GG_TILE, grp * WN + 64, row0);
+          tma_store_2d(&map_gb, smem + GG_STAGE + 2 * GG_TILE, grp * WN, row0);
+          tma_store_2d(&map_gb, smem + GG_STAGE + 3 * GG_TILE, grp * WN + 64, row0);
+          bulk_commit();
+          bulk_wait_all<0>();
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (lane == 0) {
+      const uint32_t id_kk = umma_instr_desc(UMMA_FMT_F16, 0u, 0u, 128, 128);   // K-major x K-major
+      const uint32_t id_kn = umma_instr_desc(UMMA_FMT_F16, 0u, 1u, 128, 128);   // K-major A x MN-major B
+      const uint32_t id_nn = umma_instr_desc(UMMA_FMT_F16, 1u, 1u, 128, 128);   // MN-major A x MN-major B
+      auto issue_score = [&](int hi) {
+        const uint32_t st = mp_smem_u32(smem + (hi & 1) * GG_STAGE);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma<false>(tmem + GT_SC + (hi & 1) * 128, umma_smem_desc(st + ks * 32, 16, 1024), umma_smem_desc(st + GG_TILE + ks * 32, 16, 1024),
+                      id_kk, ks != 0 ? 1u : 0u);
+        umma_commit(bars + GB_SC0 + (hi & 1));
+      };
+      bool ok = walk_wait(bars + GB_FULL0, 0, g.status, abort);
+      if (ok) { tcgen05_fence_after_sync(); issue_score(0); }
+      for (int hi = 0; ok && hi < nh; ++hi) {
+        const int s = hi & 1;
+        if (hi + 1 < nh) {   // the next head's scores run while the workers transform this head's
+          if (!walk_wait(bars + GB_FULL0 + ((hi + 1) & 1), ((hi + 1) >> 1) & 1, g.status, abort)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+          issue_score(hi + 1);
+        }
+        if (!walk_wait(bars + GB_SCALED, hi & 1, g.status, abort)) { ok = false; break; }
+        tcgen05_fence_after_sync();
+        const uint32_t st = mp_smem_u32(smem + s * GG_STAGE);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma<false>(tmem + GT_C, umma_smem_desc(st + ks * 32, 16, 1024), umma_smem_desc(st + 2 * GG_TILE + ks * 32, 16, 1024), id_kk,
+                      (hi | ks) != 0 ? 1u : 0u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma<false>(tmem + GT_B, umma_smem_desc(st + GG_TILE + ks * 32, 16, 1024), umma_smem_desc(st + 3 * GG_TILE + ks * 32, 16, 1024), id_kk,
+                      (hi | ks) != 0 ? 1u : 0u);
+        umma_commit(bars + GB_EMPTY0 + s);
+      }
+      // summed scores x B and (summed scores)^T x C
+      if (ok) ok = walk_wait(bars + GB_GG, 0, g.status, abort) && walk_wait(bars + GB_BCFULL, 0, g.status, abort);
+      if (ok) {
+        tcgen05_fence_after_sync();
+        const uint32_t sg = mp_smem_u32(sGG), sb = mp_smem_u32(smem), sc = mp_smem_u32(smem + GG_STAGE);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)     // K = step j: A K-major over the two 64-column blocks, B rows j (MN-major, two 64-column blocks)
+          umma<false>(tmem + GT_C, umma_smem_desc(sg + (ks >> 2) * GG_TILE + (ks & 3) * 32, 16, 1024), umma_smem_desc(sb + ks * 2048, GG_TILE, 1024),
+                      id_kn, 1u);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)     // K = step i: A = transposed view of the same tile (MN-major), C rows i
+          umma<false>(tmem + GT_B, umma_smem_desc(sg + ks * 2048, GG_TILE, 1024), umma_smem_desc(sc + ks * 2048, GG_TILE, 1024), id_nn, 1u);
+        umma_commit(bars + GB_ACC);
+      }
+    }
+  } else {
+    // ------------------------------ workers -----------------------------------
+    const int quarter = warp & 3;
+    const int ch = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;
+    const uint32_t tl = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    float acc[64];
+#pragma unroll
+    for (int e = 0; e < 64; ++e) acc[e] = 0.f;
+    auto scal_ptr = [&](const float* base, int hi) { return base + (static_cast<size_t>(b) * g.H + grp * hpg + hi) * g.L + c * WQ + r; };
+    float cum_n = *scal_ptr(g.cum, 0), dt_n = *scal_ptr(g.dtt, 0), colf_n = *scal_ptr(g.colf, 0);
+    float cum_p = 0.f, dt_p = 0.f, colf_p = 0.f;
+    if (nh > 1) { cum_p = *scal_ptr(g.cum, 1); dt_p = *scal_ptr(g.dtt, 1); colf_p = *scal_ptr(g.colf, 1); }
+    bool ok = true;
+    for (int hi = 0; hi < nh; ++hi) {
+      const int s = hi & 1;
+      const float cum_r = cum_n, dt_r = dt_n;
+      float* cumb = s_cum + s * WQ;
+      float* colfb = s_colf + s * WQ;
+      // every warp arrives: the phase also tells the writers of the other buffer that all warps are done with it
+      if (ch == 0) { cumb[r] = cum_n; colfb[r] = colf_n; }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bars + GB_SCAL);
+      cum_n = cum_p; dt_n = dt_p; colf_n = colf_p;
+      if (hi + 2 < nh) { cum_p = *scal_ptr(g.cum, hi + 2); dt_p = *scal_ptr(g.dtt, hi + 2); colf_p = *scal_ptr(g.colf, hi + 2); }
+      if (!walk_wait(bars + GB_SCAL, hi & 1, g.status, abort)) { ok = false; break; }
+      const float cum_last = cumb[WQ - 1];
+      // ---- acc += Sc o L ------------------------------------------------------------
+      if (!walk_wait(bars + GB_SC0 + s, (hi >> 1) & 1, g.status, abort)) { ok = false; break; }
+      tcgen05_fence_after_sync();
+#pragma unroll
+      for (int pp = 0; pp < 2; ++pp) {
+        const int pc = ch * 2 + pp;
+        const int j0 = pc * 32;
+        if (pc > quarter) continue;                 // above the diagonal for every row of the warp
+        uint32_t v[32];
+        tmem_ld_32x32(tl + GT_SC + s * 128 + j0, v);
+        const float rarg = cum_r - cumb[j0 + 31];
+        const bool diag = pc == quarter;
+        const bool direct = diag && rarg > 40.f;
+        const float rowf = w_exp(direct ? 0.f : rarg);
+        tmem_ld_wait();
+        if (__any_sync(0xffffffffu, direct)) {
+          const float* cg = scal_ptr(g.cum, hi) - r;
+          const float* dg = scal_ptr(g.dtt, hi) - r;
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const float f = direct ? w_exp(cum_r - cg[j0 + e]) * dg[j0 + e] : colfb[j0 + e] * rowf;
+            if (!diag || e <= lane) acc[pp * 32 + e] += __uint_as_float(v[e]) * f;
+          }
+        } else {
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            const float4 cf = *reinterpret_cast<const float4*>(colfb + j0 + e4 * 4);
+            const float f4[4] = {cf.x * rowf, cf.y * rowf, cf.z * rowf, cf.w * rowf};
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (!diag || e4 * 4 + e <= lane) acc[pp * 32 + e4 * 4 + e] += __uint_as_float(v[e4 * 4 + e]) * f4[e];
+          }
+        }
+      }
+      // ---- row factors into the operand tiles, in place (the score MMA has read them) ----
+      {
+        const __half2 e2 = __float2half2_rn(w_exp(cum_r));
+        const __half2 w2 = __float2half2_rn(w_exp(cum_last - cum_r) * dt_r);
+        unsigned char* gyrow = smem + s * GG_STAGE + r * 128;
+        unsigned char* xrow = gyrow + GG_TILE;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int off = ((ch * 4 + q4) ^ (r & 7)) << 4;
+          uint4 a = *reinterpret_cast<const uint4*>(gyrow + off);
+          uint4 x4 = *reinterpret_cast<const uint4*>(xrow + off);
+          __half2* ha = reinterpret_cast<__half2*>(&a);
+          __half2* hx = reinterpret_cast<__half2*>(&x4);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { ha[e] = __hmul2(ha[e], e2); hx[e] = __hmul2(hx[e], w2); }
+          *reinterpret_cast<uint4*>(gyrow + off) = a;
+          *reinterpret_cast<uint4*>(xrow + off) = x4;
+        }
+      }
+      warp_arrive(bars + GB_SCALED, lane);
+    }
+    if (ok) {
+      // ---- summed scores -> r16 operand tile ------------------------------------------
+      unsigned char* prow = sGG + ch * GG_TILE + r * 128;
+#pragma unroll
+      for (int q8 = 0; q8 < 8; ++q8) {
+        uint4 pk;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __half2 hv = __floats2half2_rn(acc[q8 * 8 + 2 * e], acc[q8 * 8 + 2 * e + 1]);
+          ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+        }
+        *reinterpret_cast<uint4*>(prow + ((q8 ^ (r & 7)) << 4)) = pk;
+      }
+      warp_arrive(bars + GB_GG, lane);
+      // ---- outputs ---------------------------------------------------------------------
+      if (walk_wait(bars + GB_ACC, 0, g.status, abort)) {
+        tcgen05_fence_after_sync();
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {   // 0: gC (staged behind B in stage 0), 1: gB (behind C in stage 1)
+          unsigned char* stg = smem + which * GG_STAGE + 2 * GG_TILE + ch * GG_TILE + r * 128;
+#pragma unroll
+          for (int pp = 0; pp < 2; ++pp) {
+            uint32_t v[32];
+            tmem_ld_32x32(tl + (which ? GT_B : GT_C) + ch * 64 + pp * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 pk;
+              uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const __half2 hv = __floats2half2_rn(__uint_as_float(v[q4 * 8 + 2 * e]), __uint_as_float(v[q4 * 8 + 2 * e + 1]));
+                ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+              }
+              *reinterpret_cast<uint4*>(stg + (((pp * 4 + q4) ^ (r & 7)) << 4)) = pk;
+            }
+          }
+        }
+        warp_arrive(bars + GB_OUT, lane);
+      }
+    }
+  }
+  tcgen05_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, TC_COLS);
+}
+
+// dt*A prefix sums inside every 128-step chunk, dt, and the column factors of both walk directions, all in
+// [B, H, L] order.  One CTA per (b, h, chunk).  Column factor of step t relative to the far end of its 32-step
+// piece: causal exp(cum[t | 31] - cum[t]) dt[t], anti-causal exp(cum[t] - cum[t & ~31]); both are at most one (dt).
+__global__ void __launch_bounds__(WQ) ssd_walk_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A, float* __restrict__ cum,
+                                                             float* __restrict__ dtt, float* __restrict__ colf_c, float* __restrict__ colf_a,
+                                                             int L, int H) {
+  __shared__ float warp_tot[4];
+  const int nc = L / WQ;
+  const int c = blockIdx.x % nc, h = (blockIdx.x / nc) % H, b = blockIdx.x / (nc * H);
+  const int t = threadIdx.x;
+  const float d = dt[(static_cast<size_t>(b) * L + c * WQ + t) * H + h];
+  float v = d * A[h];
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const float n = __shfl_up_sync(0xffffffffu, v, off);
+    if ((t & 31) >= off) v += n;
+  }
+  if ((t & 31) == 31) warp_tot[t >> 5] = v;
+  __syncthreads();
+  float base = 0.f;
+  for (int w = 0; w < (t >> 5); ++w) base += warp_tot[w];
+  const float cv = v + base;
+  const float c_hi = __shfl_sync(0xffffffffu, cv, 31), c_lo = __shfl_sync(0xffffffffu, cv, 0);
+  const size_t o = (static_cast<size_t>(b) * H + h) * L + c * WQ + t;
+  cum[o] = cv;
+  dtt[o] = d;
+  colf_c[o] = w_exp(c_hi - cv) * d;
+  if (colf_a != nullptr) colf_a[o] = w_exp(cv - c_lo);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn walk_encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, []() {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    MP_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (p == nullptr || q != cudaDriverEntryPointSuccess) MP_FATAL("cuTensorMapEncodeTiled is not available");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// r16 matrix [rows, cols] (row-major), box {64 columns, 128 rows}, 128-byte swizzle
+CUtensorMap walk_map(const void* base, size_t rows, size_t cols) {
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * sizeof(__half)};
+  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t es[2] = {1, 1};
+  MP_CU_CHECK(walk_encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, es,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+  return m;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// Interface to the launchers in ssd.cu.
+// ---------------------------------------------------------------------------
+bool mp_ssd_walk_supported(int L, int H, int P, int N, int G) {
+  return P == WP && N == WN && L % WQ == 0 && L > 0 && G > 0 && H % G == 0 && getenv("MP_SSD_NO_WALK") == nullptr;
+}
+
+void mp_ssd_walk_cumsum(const float* dt, const float* A, float* cum, float* dtt, float* colf_c, float* colf_a, int B, int L, int H,
+                        cudaStream_t st) {
+  ssd_walk_cumsum_kernel<<<B * H * (L / WQ), WQ, 0, st>>>(dt, A, cum, dtt, colf_c, colf_a, L, H);
+  MP_LAUNCH_CHECK();
+}
+
+// One walk.  q, k: [B*L, G*128]; v, z, out: [B*L, H*64]; cum, dtt, colf (of the walk's direction): [B, H, L] from mp_ssd_walk_cumsum.
+void mp_ssd_walk(int anti, const __half* q, const __half* k, const __half* v, const float* cum, const float* dtt, const float* colf, __half* out,
+                 const __half* z,
+                 float* dot_out, __half* hs_out, int B, int L, int H, int G, uint32_t* status, cudaStream_t st) {
+  WalkArgs g;
+  g.B = B; g.L = L; g.H = H; g.G = G; g.nc = L / WQ;
+  g.cum = cum; g.dtt = dtt; g.colf = colf; g.out = out; g.z = z; g.dot_out = dot_out; g.hs_out = hs_out; g.status = status;
+  g.prof = nullptr;
+  static long long* prof_buf = nullptr;
+  const bool prof = getenv("MP_SSD_WALK_PROF") != nullptr;
+  if (prof) {
+    if (prof_buf == nullptr) MP_CUDA_CHECK(cudaMalloc(&prof_buf, 16 * sizeof(long long)));
+    MP_CUDA_CHECK(cudaMemsetAsync(prof_buf, 0, 16 * sizeof(long long), st));
+    g.prof = prof_buf;
+  }
+  const size_t rows = static_cast<size_t>(B) * L;
+  const CUtensorMap mq = walk_map(q, rows, static_cast<size_t>(G) * WN), mk = walk_map(k, rows, static_cast<size_t>(G) * WN);
+  const CUtensorMap mv = walk_map(v, rows, static_cast<size_t>(H) * WP);
+  const CUtensorMap mh = hs_out != nullptr ? walk_map(hs_out, static_cast<size_t>(B) * H * g.nc * WN, WP) : mv;
+  if (anti) {
+    MP_CUDA_CHECK(cudaFuncSetAttribute(ssd_walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES));
+    ssd_walk_kernel<1><<<B * H, W_THREADS, W_SMEM_BYTES, st>>>(mq, mk, mv, mh, g);
+  } else {
+    MP_CUDA_CHECK(cudaFuncSetAttribute(ssd_walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES));
+    ssd_walk_kernel<0><<<B * H, W_THREADS, W_SMEM_BYTES, st>>>(mq, mk, mv, mh, g);
+  }
+  MP_LAUNCH_CHECK();
+  if (prof) {   // debug only: synchronises
+    long long hbuf[16];
+    MP_CUDA_CHECK(cudaStreamSynchronize(st));
+    MP_CUDA_CHECK(cudaMemcpy(hbuf, prof_buf, sizeof(hbuf), cudaMemcpyDeviceToHost));
+    printf("walk prof (clocks, CTA 0, %d chunks) worker: top %lld | wait y %lld | publish %lld | transform %lld | wait s %lld | state %lld | scale %lld | epilogue %lld"
+           " || mma: issue %lld | wait p %lld | wait h %lld | wait vs %lld | wait full %lld\n",
+           g.nc, hbuf[0], hbuf[1], hbuf[2], hbuf[3], hbuf[4], hbuf[5], hbuf[6], hbuf[7], hbuf[8], hbuf[9], hbuf[10], hbuf[11], hbuf[12]);
+    fflush(stdout);
+  }
+}
+
+// gB, gC [B*L, G*128] from gy, x [B*L, H*64], Bm, Cm [B*L, G*128] and the states left by the two walks
+// (hs_causal, hs_anti: [B, H, L/128][128][64]).
+void mp_ssd_group_grads(const __half* gy, const __half* x, const __half* Bm, const __half* Cm, const __half* hs_causal, const __half* hs_anti,
+                        const float* cum, const float* dtt, const float* colf_c, __half* gB, __half* gC, int B, int L, int H, int G,
+                        uint32_t* status, cudaStream_t st) {
+  GroupArgs g;
+  g.B = B; g.L = L; g.H = H; g.G = G; g.nc = L / WQ;
+  g.cum = cum; g.dtt = dtt; g.colf = colf_c; g.status = status;
+  const size_t rows = static_cast<size_t>(B) * L;
+  const size_t srows = static_cast<size_t>(B) * H * g.nc * WN;
+  const CUtensorMap mgy = walk_map(gy, rows, static_cast<size_t>(H) * WP), mx = walk_map(x, rows, static_cast<size_t>(H) * WP);
+  const CUtensorMap mhc = walk_map(hs_causal, srows, WP), mha = walk_map(hs_anti, srows, WP);
+  const CUtensorMap mb = walk_map(Bm, rows, static_cast<size_t>(G) * WN), mc = walk_map(Cm, rows, static_cast<size_t>(G) * WN);
+  const CUtensorMap mgb = walk_map(gB, rows, static_cast<size_t>(G) * WN), mgc = walk_map(gC, rows, static_cast<size_t>(G) * WN);
+  MP_CUDA_CHECK(cudaFuncSetAttribute(ssd_group_grads_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GG_SMEM_BYTES));
+  ssd_group_grads_kernel<<<B * g.nc * G, W_THREADS, GG_SMEM_BYTES, st>>>(mgy, mx, mhc, mha, mb, mc, mgb, mgc, g);
+  MP_LAUNCH_CHECK();
+}
