@@ -496,8 +496,6 @@ def lm_launcher_work(label, cfg, batch, seqlen):
         return {"flops": 2.0 * a * b * c}, "tensor"
     if label.startswith("cross_entropy"):
         return {"bytes": 2 * T * cfg.vocab * 2}, "hbm"
-    if label.startswith("adam"):
-        return {"bytes": 28 * cfg.n_params()}, "hbm"
     return None, None
 
 
@@ -592,7 +590,7 @@ def run_lm(args):
     ids_h, tgt_h = tok[:-1].contiguous().pin_memory(), tok[1:].contiguous().pin_memory()
     model.set_batch(ids_h, tgt_h)
     if not args.lm_no_graph:
-        model.capture()
+        model.capture(comm=comm, world=world, **ADAM)
     losses = torch.zeros(args.steps + 1, dtype=torch.float32, device="cuda")   # summed loss of every timed step
 
     def barrier():
@@ -695,7 +693,7 @@ def run_lm(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 activations / f32 accumulate, master weights and optimizer state",
             "data": "synthetic (token ids ~ U[0, 50280), seed 1000 + rank; weights N(0, 0.02), seed 0 on every rank)",
             "config": {"workload": lm_workload_text(cfg.n_layer, batch),
-                       "assumed": f"d_conv 4, tied embedding / LM head, gated RMSNorm before out_proj, D skip, chunk {cfg.chunk}, static loss scale 65536",
+                       "assumed": f"d_conv 4, tied embedding / LM head, gated RMSNorm before out_proj, D skip, scan chunk argument {cfg.chunk}, static loss scale 65536",
                        "params": n_params, "tokens_per_gpu_step": T, "graph_replay": not args.lm_no_graph,
                        "all_reduce": ("none (one rank)" if world == 1 else model.all_reduce_description()),
                        "l2": "activations and weights (GBs per step) exceed the 126 MB L2; no flush needed"},
@@ -704,9 +702,10 @@ def run_lm(args):
                     "d2h_bytes_per_step": 4, "ms_per_step": round(e2e_ms, 3), "steps": e2e_steps,
                     "path": "MambaLM.set_batch (mpMemcpyHtoD from pinned memory) + train_step + loss() (mpMemcpyDtoH + stream sync) every step"},
             "clocks": clocks,
-            "gpu_launches": (graph_kernels + 3 if graph_kernels else model.launches_per_step()) * args.steps,
-            "gpu_launches_per_step": {"graph_kernel_nodes (forward + loss + reverse)": graph_kernels,
-                                      "outside the graph": "Adam, r16 weight refresh, loss copy" + (", NCCL all-reduce" if world > 1 else "")},
+            "gpu_launches": ((graph_kernels or 0) + 1) * args.steps,
+            "gpu_launches_per_step": {"graph_kernel_nodes": graph_kernels,
+                                      "graph": "the whole step: forward, loss, reverse, per-bucket gradient folding" + (", NCCL all-reduces" if world > 1 else "") + ", mixed-precision Adam",
+                                      "outside the graph": "one 4-byte copy of the step's loss"},
             "loss": {"first_timed_step": round(loss_host[0], 4), "last_timed_step": round(loss_host[args.steps - 1], 4),
                      "expected_at_init": round(math.log(cfg.vocab), 4),
                      "note": "one fixed random batch per rank is repeated, so the loss falls as the model memorises it"},

@@ -50,6 +50,16 @@ MP_EXTERN_C StreamContext mpWrapStream(void* cuda_stream);
  * spinning forever. */
 MP_EXTERN_C uint32_t mpGetStatus(StreamContext);
 
+/* Limit, in microseconds, after which a kernel's bounded wait (on a shared-memory barrier fed by an asynchronous
+ * copy or by the tensor core) gives up, records MP_STATUS_WAIT_TIMEOUT and lets the kernel end; 0 = the built-in
+ * 2 s.  Applies to kernels launched on the stream after the call.  The environment variable MP_SPIN_LIMIT_US sets
+ * the initial value of every stream.  (The reference's kernels have no waits; its error path is print-and-exit,
+ * src/cuda/kernel_header.h:64-98.) */
+MP_EXTERN_C void mpSetWaitLimit(StreamContext, len_t microseconds);
+/* Launches a one-CTA kernel whose wait can never be satisfied: it returns after the stream's wait limit with
+ * MP_STATUS_WAIT_TIMEOUT in the status word.  A check of the time-out path that faults nothing. */
+MP_EXTERN_C void mpSelfTestWaitTimeout(StreamContext);
+
 /* Bytes of library-owned workspace attached to the stream (split-K partials,
  * column-reduce partials, tensor-map staging).  Allocated once in
  * mpInitStream / mpWrapStream, never inside a launcher. */

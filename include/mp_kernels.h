@@ -204,6 +204,15 @@ MP_DECL3(neg_exp, const void* src, void* dst, len_t n, StreamContext stream)
  * dst(r32) = src(r16) + beta*dst;  dst(r16) = round(src(r32)). */
 MP_EXTERN_C void launch_convert_r16_r32(const void* src, void* dst, double beta, len_t n, StreamContext stream);
 MP_EXTERN_C void launch_convert_r32_r16(const void* src, void* dst, len_t n, StreamContext stream);
+/* Mixed-precision Adam over a flat parameter bucket (the reference names Adam only in NOTES.md:11; its update loop
+ * over the weights is optimizer.zig:140-179).  `tick` = 16 bytes of zero-initialised device memory holding
+ * {1/(1-beta1^t), 1/(1-beta2^t), t, non-finite flag}; launch_adam_tick advances t on the stream, so a step replayed
+ * from a captured graph uses its own step number.  launch_adam_mixed_r32: g = (g32 + g16) * grad_scale (g16 may be
+ * NULL), Adam update of w32 / m / v, and w16 = round(w32) in the same pass.  Elements whose gradient is not finite are
+ * left unchanged and the flag (4th word of `tick`) is set. */
+MP_EXTERN_C void launch_adam_tick(void* tick, double beta1, double beta2, StreamContext stream);
+MP_EXTERN_C void launch_adam_mixed_r32(void* w32, void* w16, const void* g32, const void* g16, void* m, void* v, double lr, double beta1,
+                                       double beta2, double eps, double grad_scale, void* tick, len_t n, StreamContext stream);
 
 /* Rank-1 losses and the momentum step.  The reference calls kernels of these names (loss.zig:58-136,
  * optimizer.zig:263-273) but contains no implementation; argument order follows those call sites.

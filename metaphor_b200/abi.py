@@ -100,6 +100,8 @@ UTILS = {
     "mpDeviceTotalMemory": (L, [U32]),
     "mpWrapStream": (CTX, [P]),
     "mpGetStatus": (U32, [CTX]),
+    "mpSetWaitLimit": (None, [CTX, L]),
+    "mpSelfTestWaitTimeout": (None, [CTX]),
     "mpWorkspaceBytes": (L, [CTX]),
     "mpDeviceSmCount": (U32, [CTX]),
     "mpHostAlloc": (P, [L]),
@@ -119,12 +121,19 @@ UTILS = {
     "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),
     "launch_convert_r16_r32": (None, [P, P, D, L, CTX]),
     "launch_convert_r32_r16": (None, [P, P, L, CTX]),
+    "launch_adam_tick": (None, [P, D, D, CTX]),
+    "launch_adam_mixed_r32": (None, [P, P, P, P, P, P, D, D, D, D, D, P, L, CTX]),
     # include/mp_comm.h
     "mpCommGetUniqueId": (None, [P]),
     "mpCommInit": (P, [P, U32, U32]),
     "mpCommDestroy": (None, [P]),
     "mpCommWorldSize": (U32, [P]),
     "mpAllReduceSum": (None, [P, P, L, U32, CTX]),
+    "mpCommInitStatus": (C.c_int32, [P, U32, U32, C.POINTER(C.c_void_p)]),
+    "mpAllReduceSumStatus": (C.c_int32, [P, P, L, U32, CTX]),
+    "mpCommPoll": (C.c_int32, [P, CTX, U32]),
+    "mpCommAbort": (None, [P]),
+    "mpSetFailPoint": (None, [C.c_char_p, C.c_int32]),
     # include/mp_jit.h
     "mpJitCompile": (P, [C.c_char_p, U32]),
     "mpJitRelease": (None, [P]),

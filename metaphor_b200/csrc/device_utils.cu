@@ -1,7 +1,7 @@
 // mp* device utilities: the host-visible lifecycle / memory / copy calls.
 // Replaces the reference's src/cuda/device_utils.cu:4-99.  Differences that a
 // caller can observe are listed beside each function.
-#include "mp_common.cuh"
+#include "mp_async.cuh"
 
 #include <map>
 #include <mutex>
@@ -39,6 +39,11 @@ StreamContext make_context(cudaStream_t stream, bool owns) {
   MP_CUDA_CHECK(cudaMemsetAsync(st->status_dev, 0, 256, stream));
   MP_CUDA_CHECK(cudaMallocHost(reinterpret_cast<void**>(&st->status_host), 256));
   st->status_host[0] = 0;
+  if (const char* lim = getenv("MP_SPIN_LIMIT_US")) {     // wait limit of the bounded waits, bytes 8..15 of the status block
+    const unsigned long long ns = strtoull(lim, nullptr, 10) * 1000ull;
+    MP_CUDA_CHECK(cudaMemcpyAsync(st->status_dev + 2, &ns, sizeof(ns), cudaMemcpyHostToDevice, stream));
+    MP_CUDA_CHECK(cudaStreamSynchronize(stream));
+  }
   StreamContext ctx;
   ctx.cuda_stream.ptr = reinterpret_cast<void*>(stream);
   ctx.blas_handle.ptr = reinterpret_cast<void*>(st);
@@ -154,6 +159,35 @@ extern "C" uint32_t mpGetStatus(StreamContext ctx) {
   MP_CUDA_CHECK(cudaMemsetAsync(st->status_dev, 0, sizeof(uint32_t), st->stream));
   MP_CUDA_CHECK(cudaStreamSynchronize(st->stream));
   return st->status_host[0];
+}
+
+// Limit of every bounded wait of kernels launched on this stream from now on (stream-ordered); 0 restores the default.
+extern "C" void mpSetWaitLimit(StreamContext ctx, len_t microseconds) {
+  MpStreamState* st = mp_state(ctx);
+  unsigned long long* slot = reinterpret_cast<unsigned long long*>(st->status_host + 2);
+  MP_CUDA_CHECK(cudaStreamSynchronize(st->stream));     // the pinned slot may still feed an earlier copy
+  *slot = static_cast<unsigned long long>(microseconds) * 1000ull;
+  MP_CUDA_CHECK(cudaMemcpyAsync(st->status_dev + 2, slot, sizeof(*slot), cudaMemcpyHostToDevice, st->stream));
+}
+
+namespace {
+// One CTA waits for a phase of a shared-memory barrier that nothing completes: the bounded wait runs out, records
+// MP_STATUS_WAIT_TIMEOUT in the stream's status word and the kernel returns normally.
+__global__ void wait_timeout_selftest_kernel(uint32_t* status) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    (void)mbar_wait(&bar, 0, status);
+  }
+}
+}  // namespace
+
+// Exercises the time-out path of the bounded waits without any fault: returns after the wait limit of the stream.
+extern "C" void mpSelfTestWaitTimeout(StreamContext ctx) {
+  MpStreamState* st = mp_state(ctx);
+  wait_timeout_selftest_kernel<<<1, 32, 0, st->stream>>>(st->status_dev);
+  MP_LAUNCH_CHECK();
 }
 
 extern "C" len_t mpWorkspaceBytes(StreamContext ctx) { return mp_state(ctx)->workspace_bytes; }

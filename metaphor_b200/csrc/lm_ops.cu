@@ -916,6 +916,49 @@ __global__ void __launch_bounds__(512) convert_r32_r16_kernel(const float* __res
   }
 }
 
+// Mixed-precision Adam over a flat bucket (see launch_adam_mixed_r32).  The step-dependent bias corrections come
+// from device memory, so a captured graph can replay the call for every step.
+struct AdamTick { float inv_bc1, inv_bc2; uint32_t step, nonfinite; };
+__global__ void adam_tick_kernel(AdamTick* t, float beta1, float beta2) {
+  const uint32_t step = t->step + 1;
+  t->step = step;
+  t->inv_bc1 = 1.f / (1.f - powf(beta1, static_cast<float>(step)));
+  t->inv_bc2 = 1.f / (1.f - powf(beta2, static_cast<float>(step)));
+}
+template <int V>
+__global__ void __launch_bounds__(512) adam_mixed_kernel(float* __restrict__ w32, __half* __restrict__ w16, const float* __restrict__ g32,
+                                                         const __half* __restrict__ g16, float* __restrict__ m, float* __restrict__ v,
+                                                         float lr, float b1, float b2, float eps, float gscale, AdamTick* tick, size_t n) {
+  const float ib1 = tick->inv_bc1, ib2 = tick->inv_bc2;
+  const size_t nv = n / V;
+  bool bad = false;
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nv; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float w[V], g[V], mm[V], vv[V], h[V];
+    load_vec<float, V>(w32 + i * V, w);
+    load_vec<float, V>(g32 + i * V, g);
+    load_vec<float, V>(m + i * V, mm);
+    load_vec<float, V>(v + i * V, vv);
+    if (g16 != nullptr) {
+      load_vec<__half, V>(g16 + i * V, h);
+#pragma unroll
+      for (int e = 0; e < V; ++e) g[e] += h[e];
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const float gs = g[e] * gscale;
+      if (!isfinite(gs)) { bad = true; continue; }      // an overflowed gradient leaves this element untouched
+      mm[e] = b1 * mm[e] + (1.f - b1) * gs;
+      vv[e] = b2 * vv[e] + (1.f - b2) * gs * gs;
+      w[e] -= lr * (mm[e] * ib1) / (sqrtf(vv[e] * ib2) + eps);
+    }
+    store_vec<float, V>(w32 + i * V, w);
+    store_vec<float, V>(m + i * V, mm);
+    store_vec<float, V>(v + i * V, vv);
+    store_vec<__half, V>(w16 + i * V, w);
+  }
+  if (bad) tick->nonfinite = 1u;
+}
+
 inline unsigned grid_for(size_t work_items, int threads) {
   const size_t g = (work_items + threads - 1) / threads;
   return static_cast<unsigned>(g < 1 ? 1 : (g > (1u << 30) ? (1u << 30) : g));
@@ -1321,5 +1364,37 @@ extern "C" void launch_convert_r32_r16(const void* src, void* dst, len_t n, Stre
     convert_r32_r16_kernel<8><<<grid_for(n / 8, 512), 512, 0, st>>>(static_cast<const float*>(src), static_cast<__half*>(dst), n);
   else
     convert_r32_r16_kernel<1><<<grid_for(n, 512), 512, 0, st>>>(static_cast<const float*>(src), static_cast<__half*>(dst), n);
+  MP_LAUNCH_CHECK();
+}
+
+// ---- mixed-precision optimizer step of the language-model composition ---------------------------------------
+// tick: 16 bytes of device memory, zero-filled once by the caller: {1/(1-b1^t), 1/(1-b2^t), t, non-finite flag}.
+// launch_adam_tick advances t and refreshes the two corrections; it runs on the stream like any launcher (one
+// thread), so a step that is replayed from a captured graph still sees its own step number.
+extern "C" void launch_adam_tick(void* tick, double beta1, double beta2, StreamContext ctx) {
+  adam_tick_kernel<<<1, 1, 0, mp_stream(ctx)>>>(static_cast<AdamTick*>(tick), static_cast<float>(beta1), static_cast<float>(beta2));
+  MP_LAUNCH_CHECK();
+}
+
+// One pass over a flat parameter bucket: g = (g32 + g16) * grad_scale (g16 may be NULL), Adam update of the r32 master
+// weights and moments with the corrections in `tick`, and the refreshed r16 working copy w16 = round(w32).  Elements
+// whose gradient is not finite are left unchanged and the flag in `tick` is set (a static loss scale can overflow).
+extern "C" void launch_adam_mixed_r32(void* w32, void* w16, const void* g32, const void* g16, void* m, void* v, double lr, double beta1,
+                                      double beta2, double eps, double grad_scale, void* tick, len_t n, StreamContext ctx) {
+  if (n == 0) return;
+  cudaStream_t st = mp_stream(ctx);
+  const bool vec = n % 8 == 0 && mp_aligned16(w16) && (g16 == nullptr || mp_aligned16(g16)) &&
+                   ((reinterpret_cast<uintptr_t>(w32) | reinterpret_cast<uintptr_t>(g32) | reinterpret_cast<uintptr_t>(m) |
+                     reinterpret_cast<uintptr_t>(v)) & 31u) == 0;
+  if (vec)
+    adam_mixed_kernel<8><<<grid_for(n / 8, 512), 512, 0, st>>>(static_cast<float*>(w32), static_cast<__half*>(w16), static_cast<const float*>(g32),
+                                                             static_cast<const __half*>(g16), static_cast<float*>(m), static_cast<float*>(v),
+                                                             static_cast<float>(lr), static_cast<float>(beta1), static_cast<float>(beta2),
+                                                             static_cast<float>(eps), static_cast<float>(grad_scale), static_cast<AdamTick*>(tick), n);
+  else
+    adam_mixed_kernel<1><<<grid_for(n, 512), 512, 0, st>>>(static_cast<float*>(w32), static_cast<__half*>(w16), static_cast<const float*>(g32),
+                                                         static_cast<const __half*>(g16), static_cast<float*>(m), static_cast<float*>(v),
+                                                         static_cast<float>(lr), static_cast<float>(beta1), static_cast<float>(beta2),
+                                                         static_cast<float>(eps), static_cast<float>(grad_scale), static_cast<AdamTick*>(tick), n);
   MP_LAUNCH_CHECK();
 }

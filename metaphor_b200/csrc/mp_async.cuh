@@ -11,7 +11,7 @@
 #include "mp_common.cuh"
 
 #ifndef MP_WAIT_LIMIT_NS
-#define MP_WAIT_LIMIT_NS 2000000000ull  // 2 s
+#define MP_WAIT_LIMIT_NS 2000000000ull  // 2 s: the limit when the stream's state carries none
 #endif
 
 __device__ __forceinline__ uint32_t mp_smem_u32(const void* p) {
@@ -22,6 +22,14 @@ __device__ __forceinline__ uint64_t mp_globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
+}
+
+// The stream's status block: word 0 = status, bytes 8..15 = wait limit in nanoseconds (0 = the default above),
+// set by mpSetWaitLimit or the MP_SPIN_LIMIT_US environment variable.  Read only on the slow path of a wait.
+__device__ __forceinline__ uint64_t mp_wait_limit_ns(const uint32_t* status) {
+  if (status == nullptr) return MP_WAIT_LIMIT_NS;
+  const uint64_t v = *reinterpret_cast<const volatile uint64_t*>(status + 2);
+  return v != 0 ? v : MP_WAIT_LIMIT_NS;
 }
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
@@ -77,11 +85,12 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t* status) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = mp_globaltimer_ns();
+  const uint64_t limit = mp_wait_limit_ns(status);
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i)
       if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
-    if (mp_globaltimer_ns() - t0 > MP_WAIT_LIMIT_NS) {
+    if (mp_globaltimer_ns() - t0 > limit) {
       if (status != nullptr) atomicExch(status, MP_STATUS_WAIT_TIMEOUT);
       return false;
     }

@@ -144,12 +144,13 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, uint32_t* status, volatile int* abort) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = mp_globaltimer_ns();
+  const uint64_t limit = mp_wait_limit_ns(status);
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 32; ++i)
       if (mbar_try_wait_suspend(bar, parity, 20000u)) return true;
     if (*abort != 0) return false;
-    if (mp_globaltimer_ns() - t0 > MP_WAIT_LIMIT_NS) {
+    if (mp_globaltimer_ns() - t0 > limit) {
       *abort = 1;
       if (status != nullptr) atomicExch(status, MP_STATUS_WAIT_TIMEOUT);
       return false;

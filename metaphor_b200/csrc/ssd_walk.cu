@@ -54,7 +54,6 @@ struct WalkArgs {
   __half* out;             // [B*L, H*64] or null
   const __half* z;         // dot partner, same indexing as out, or null
   float* dot_out;          // [2][B, H, L] row dots <z, out> from the fp32 accumulators, one array per half of the columns, or null
-  long long* prof;         // debug: per-phase clock sums of CTA 0 (null in normal use)
   __half* hs_out;          // [B, H, nc][128][64]: state every chunk receives, or null
   uint32_t* status;
 };
@@ -156,19 +155,13 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
         }
         umma_commit(bars + B_GFULL);
       };
-      const bool prof = g.prof != nullptr && blockIdx.x == 0;
-      long long pt[5] = {0, 0, 0, 0, 0};
-      long long tlast = prof ? clock64() : 0;
-      auto stamp = [&](int i) { if (prof) { const long long t = clock64(); pt[i] += t - tlast; tlast = t; } };
       bool ok = walk_wait(bars + B_FULL0, 0, g.status, abort);
       if (ok) { tcgen05_fence_after_sync(); issue_g(0); }
       for (int k = 0; ok && k < nc; ++k) {
         const int s = k & 1;
         const uint32_t sq = mp_smem_u32(smem + s * W_STAGE), sk = sq + W_TILE_QK, sv = sk + W_TILE_QK;
         const uint32_t ty = tmem + TC_Y + (k & 1) * 128;
-        stamp(0);
         if (!walk_wait(bars + B_PREADY, k & 1, g.status, abort)) { ok = false; break; }
-        stamp(1);
         tcgen05_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
@@ -176,9 +169,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
           umma<false>(ty, umma_smem_desc(sp + o, 16, 1024), umma_smem_desc(sv + ks * 2048, W_TILE_V, 1024), id_y, ks != 0 ? 1u : 0u);
         }
         if (k > 0) {
-          stamp(0);
           if (!walk_wait(bars + B_HREADY, (k - 1) & 1, g.status, abort)) { ok = false; break; }
-          stamp(2);
           tcgen05_fence_after_sync();
           if (g.hs_out != nullptr) {   // the state this chunk receives, straight from its operand tile
             const int c = ANTI ? nc - 1 - k : k;
@@ -196,15 +187,11 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
         // scores of the next chunk (its stage was released by S(k-1); the workers are past G(k))
         if (k + 1 < nc) {
           const int s1 = (k + 1) & 1;
-          stamp(0);
           if (!walk_wait(bars + B_FULL0 + s1, ((k + 1) >> 1) & 1, g.status, abort)) { ok = false; break; }
-          stamp(4);
           tcgen05_fence_after_sync();
           issue_g(s1);
         }
-        stamp(0);
         if (!walk_wait(bars + B_VSREADY, k & 1, g.status, abort)) { ok = false; break; }
-        stamp(3);
         tcgen05_fence_after_sync();
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)
@@ -214,10 +201,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
         umma_commit(bars + B_EMPTY0 + s);
       }
       if (g.hs_out != nullptr) bulk_wait_all<0>();
-      if (prof) {
-#pragma unroll
-        for (int i = 0; i < 5; ++i) g.prof[8 + i] = pt[i];
-      }
     }
   } else {
     // ------------------------------ workers -----------------------------------
@@ -243,10 +226,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
       for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(0u, 0u, 0u, 0u);
     }
     bool ok = true;
-    const bool prof = g.prof != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
-    long long pt[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long tlast = prof ? clock64() : 0;
-    auto stamp = [&](int i) { if (prof) { const long long t = clock64(); pt[i] += t - tlast; tlast = t; } };
 
     // values of the walk's scalars: chunk in hand (cur) and the one after it (nxt)
     float cum_cur = 0.f, dt_cur = 0.f, last_cur = 0.f;
@@ -371,18 +350,13 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
           zc[it] = *reinterpret_cast<const uint4*>(g.z + zrow * pitch + h * WP + ch * 32 + (lane & 3) * 8);
         }
       }
-      stamp(0);
       if (!walk_wait(bars + B_YFULL, par, g.status, abort)) { ok = false; break; }
-      stamp(1);
       if (more) {
         if (!publish(k + 1)) { ok = false; break; }
-        stamp(2);
         if (!transform(k + 1, ANTI ? c - 1 : c + 1)) { ok = false; break; }
-        stamp(3);
       }
       // ---- H' = D H + S ---------------------------------------------------------------
       if (!walk_wait(bars + B_SFULL, par, g.status, abort)) { ok = false; break; }
-      stamp(4);
       tcgen05_fence_after_sync();
       if (more) {
         uint32_t sv[32];
@@ -403,7 +377,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
           *reinterpret_cast<uint4*>(sH + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4)) = pk;
         }
         warp_arrive(bars + B_HREADY, lane);
-        stamp(5);
       }
       // ---- out = r o (Yd + f o Yo) of chunk k -------------------------------------------
       // staging = this warp's own positions of the scaled-value tile (S(k), its last reader, has completed, and the
@@ -476,13 +449,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
           g.dot_out[static_cast<size_t>(ch) * g.B * g.H * g.L + bh * g.L + c * WQ + r] = dot;
         }
       }
-      stamp(6);
       if (more && !scale_values(k + 1)) { ok = false; break; }
-    }
-    stamp(7);
-    if (prof) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) g.prof[i] = pt[i];
     }
     (void)ok;
   }
@@ -854,14 +821,6 @@ void mp_ssd_walk(int anti, const __half* q, const __half* k, const __half* v, co
   WalkArgs g;
   g.B = B; g.L = L; g.H = H; g.G = G; g.nc = L / WQ;
   g.cum = cum; g.dtt = dtt; g.colf = colf; g.out = out; g.z = z; g.dot_out = dot_out; g.hs_out = hs_out; g.status = status;
-  g.prof = nullptr;
-  static long long* prof_buf = nullptr;
-  const bool prof = getenv("MP_SSD_WALK_PROF") != nullptr;
-  if (prof) {
-    if (prof_buf == nullptr) MP_CUDA_CHECK(cudaMalloc(&prof_buf, 16 * sizeof(long long)));
-    MP_CUDA_CHECK(cudaMemsetAsync(prof_buf, 0, 16 * sizeof(long long), st));
-    g.prof = prof_buf;
-  }
   const size_t rows = static_cast<size_t>(B) * L;
   const CUtensorMap mq = walk_map(q, rows, static_cast<size_t>(G) * WN), mk = walk_map(k, rows, static_cast<size_t>(G) * WN);
   const CUtensorMap mv = walk_map(v, rows, static_cast<size_t>(H) * WP);
@@ -874,15 +833,6 @@ void mp_ssd_walk(int anti, const __half* q, const __half* k, const __half* v, co
     ssd_walk_kernel<0><<<B * H, W_THREADS, W_SMEM_BYTES, st>>>(mq, mk, mv, mh, g);
   }
   MP_LAUNCH_CHECK();
-  if (prof) {   // debug only: synchronises
-    long long hbuf[16];
-    MP_CUDA_CHECK(cudaStreamSynchronize(st));
-    MP_CUDA_CHECK(cudaMemcpy(hbuf, prof_buf, sizeof(hbuf), cudaMemcpyDeviceToHost));
-    printf("walk prof (clocks, CTA 0, %d chunks) worker: top %lld | wait y %lld | publish %lld | transform %lld | wait s %lld | state %lld | scale %lld | epilogue %lld"
-           " || mma: issue %lld | wait p %lld | wait h %lld | wait vs %lld | wait full %lld\n",
-           g.nc, hbuf[0], hbuf[1], hbuf[2], hbuf[3], hbuf[4], hbuf[5], hbuf[6], hbuf[7], hbuf[8], hbuf[9], hbuf[10], hbuf[11], hbuf[12]);
-    fflush(stdout);
-  }
 }
 
 // gB, gC [B*L, G*128] from gy, x [B*L, H*64], Bm, Cm [B*L, G*128] and the states left by the two walks

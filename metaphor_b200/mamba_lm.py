@@ -13,11 +13,19 @@ Layer (pre-norm residual block), T = batch * seqlen tokens, r16 activations:
 Head: logits = rmsnorm(h, normf_w) @ E^T (tied embedding), mean cross-entropy.
 
 Weights live in one flat r32 master buffer (plus Adam moments); contractions and
-norms read a flat r16 copy refreshed after every step.  Gradients: contractions
-and norm gains write r16 into a flat r16 gradient buffer, everything reduced with
-atomics (embedding rows, conv taps, biases, D, A_log) goes straight to the flat
-r32 gradient, and one conversion folds the r16 part in.  The r32 gradient is what
-the all-reduce and the fused Adam step see.
+norms read a flat r16 copy.  Gradients: contractions and norm gains write r16
+into a flat r16 gradient buffer, everything reduced with atomics (embedding rows,
+conv taps, biases, D, A_log) goes straight to the flat r32 gradient.
+
+The update is bucketed and overlapped with the reverse pass: the flat buffers are
+in layer order, so as soon as the reverse of a group of layers has finished, a
+second stream folds that bucket's r16 gradients into the r32 ones, all-reduces
+the bucket (data-parallel runs) and applies the mixed-precision Adam step, which
+also writes the bucket's refreshed r16 weights - while the first stream is
+already in the reverse of the layers below.  Only the embedding bucket, whose
+gradient is complete last, is exposed.  The whole step (forward, loss, reverse,
+all-reduces, updates) is one stream-ordered sequence and can be captured into
+one CUDA graph: the step number Adam needs lives in device memory.
 """
 from __future__ import annotations
 
@@ -102,11 +110,16 @@ ALIGN = 64   # elements: keeps every parameter 128-byte aligned in the r16 copy
 
 class MambaLM:
     def __init__(self, cfg: LMConfig, batch: int, seqlen: int, weights=None, seed: int = 0, stream: Stream | None = None,
-                 loss_scale: float = 1.0):
+                 loss_scale: float | None = None, bucket_layers: int = 4):
+        """loss_scale multiplies the logit gradient before it is stored in r16 (the mean cross-entropy puts a factor
+        1/T on it, which at realistic T drops typical entries into the r16 subnormal range).  Default: the largest
+        power of two not above T, so that scale/T is in (1/2, 1].  The scale is static; Adam skips elements whose
+        gradient overflowed and `nonfinite_gradients()` reports it."""
         import torch
         self.cfg, self.batch, self.seqlen = cfg, batch, seqlen
         self.T = batch * seqlen
-        self.loss_scale = loss_scale
+        self.loss_scale = float(loss_scale) if loss_scale is not None else float(2 ** int(math.floor(math.log2(max(self.T, 1)))))
+        self._own_stream = stream is None
         self.stream = stream if stream is not None else Stream()
         self._lib = lib()
         dev = "cuda"
@@ -132,6 +145,22 @@ class MambaLM:
         torch.cuda.synchronize()
         self._refresh_w16()
         self.step_count = 0
+        self.tick = torch.zeros(4, dtype=torch.float32, device=dev)   # Adam's step number and bias corrections (launch_adam_tick)
+        # ---- update buckets, in the order the reverse pass completes them ------------------------------
+        # (lo, hi, first layer of the group or -1 for the embedding): layer groups from the top (the final norm's gain
+        # sits right behind the last layer), then the embedding
+        self.buckets = []
+        hi = off
+        top = cfg.n_layer
+        while top > 0:
+            first = max(0, top - max(1, bucket_layers))
+            lo = self.offsets[f"layers.{first}.norm_w"][0]
+            self.buckets.append((lo, hi, first))
+            hi, top = lo, first
+        self.buckets.append((0, hi, -1))
+        self.side = Stream()                      # carries gradient folding, all-reduce and Adam of finished buckets
+        self._ev_bucket = [self._lib.mpEventCreate() for _ in self.buckets]
+        self._ev_join = self._lib.mpEventCreate()
         # ---- activations -------------------------------------------------------------
         T, c = self.T, cfg
         f16 = lambda *s: torch.empty(*s, dtype=torch.float16, device=dev)
@@ -177,18 +206,19 @@ class MambaLM:
         """Device address of a parameter (or of its gradient) inside a flat buffer."""
         return buf.data_ptr() + (self.offsets[name][0] + extra) * buf.element_size()
 
-    def _timed(self, name, call):
-        """Run `call()`; while a profile is being taken, bracket it with CUDA events on the library's stream."""
+    def _timed(self, name, call, side=False):
+        """Run `call()`; while a profile is being taken, bracket it with CUDA events on the stream it is issued to."""
         prof = getattr(self, "_prof", None)
         if prof is None:
             call()
             return
         import torch
+        ts = self._prof_side_ts if side else self._prof_ts
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(self._prof_ts)
+        e0.record(ts)
         call()
-        e1.record(self._prof_ts)
-        prof.append((name, e0, e1))
+        e1.record(ts)
+        prof.append((name + (" (update stream)" if side else ""), e0, e1))
 
     def _L(self, name, *args):
         import torch
@@ -208,17 +238,13 @@ class MambaLM:
     def profile_step(self, comm=None, world=1, **adam):
         """One training step issued launcher by launcher (no graph replay) with a CUDA-event pair around
         every launcher call.  Returns {launcher: {"ms": total device time, "calls": count}}; a launcher that
-        forks work onto the library's side streams is bracketed on the caller's stream, join included."""
-        self.stream.sync()
-        self._prof, self._prof_ts = [], self.stream.torch_stream()
+        forks work onto the library's side streams is bracketed on the caller's stream, join included, and the
+        bucket updates are bracketed on the update stream (they overlap the reverse pass)."""
+        self.stream.sync(); self.side.sync()
+        self._prof, self._prof_ts, self._prof_side_ts = [], self.stream.torch_stream(), self.side.torch_stream()
         try:
-            self.forward()
-            self.loss_and_logit_gradient()
-            self.backward()
-            if comm is not None and world > 1:
-                self._timed("all_reduce_sum", lambda: comm.all_reduce_sum(self.g32, self.stream))
-            self.adam_step(world=world, **adam)
-            self.stream.sync()
+            self._issue_step(comm, world, **adam)
+            self.stream.sync(); self.side.sync()
             out = {}
             for name, e0, e1 in self._prof:
                 r = out.setdefault(name, {"ms": 0.0, "calls": 0})
@@ -276,7 +302,26 @@ class MambaLM:
         self._L32("reduce_ij_i", self.loss_rows, self.loss_sum, 0.0, 1, T)
 
     # ------------------------------------------------------------------ backward
-    def backward(self):
+    def _update_bucket(self, k, comm, world, adam):
+        """Bucket k's gradients are complete on the main stream: hand them to the update stream."""
+        lo, hi, _ = self.buckets[k]
+        n = hi - lo
+        side = self.side
+        self._lib.mpEventRecord(self._ev_bucket[k], self.stream.ctx)
+        self._lib.mpStreamWaitEvent(side.ctx, self._ev_bucket[k])
+        P = lambda buf: C.c_void_p(buf.data_ptr() + lo * buf.element_size())
+        g16 = P(self.g16)
+        if comm is not None and world > 1:
+            self._timed("convert_r16_r32", lambda: self._lib.launch_convert_r16_r32(g16, P(self.g32), 1.0, n, side.ctx), side=True)
+            self._timed("all_reduce_sum", lambda: comm.all_reduce_sum(self.g32[lo:hi], side), side=True)
+            g16 = C.c_void_p(0)
+        self._timed("adam_mixed_r32", lambda: self._lib.launch_adam_mixed_r32(
+            P(self.w32), P(self.w16), P(self.g32), g16, P(self.m), P(self.v), adam["lr"], adam["beta1"], adam["beta2"], adam["eps"],
+            1.0 / (self.loss_scale * world), C.c_void_p(self.tick.data_ptr()), n, side.ctx), side=True)
+
+    def backward(self, update=None):
+        """Reverse pass.  `update` = (comm, world, adam) applies every bucket's update as soon as its gradients are
+        complete; None leaves the gradients in g16 / g32 (use `fold_gradients()` to read them)."""
         c, T = self.cfg, self.T
         W, G16, G32 = self.w16, self.g16, self.g32
         di, gn, H, P = c.d_inner, c.ngroups * c.d_state, c.heads, c.headdim
@@ -289,6 +334,7 @@ class MambaLM:
         self._L("inner_product_ji_jk_ik", gl, self.hn, 1.0, self._p(G16, "embedding"), 0.0, c.vocab, T, c.d_model)
         self._L("rmsnorm_ij_j_reverse", self.h_out, self._p(W, "normf_w"), self.rstdf, self.gt, c.eps, self.gh, self._p(G16, "normf_w"),
                 0.0, self.rms_scratch, T, c.d_model)
+        group_first = {first: k for k, (_, _, first) in enumerate(self.buckets)}
         for i in reversed(range(c.n_layer)):
             sv, p = self.saved[i], f"layers.{i}."
             zx, gzx = sv["zx"].data_ptr(), self.gzx.data_ptr()
@@ -315,55 +361,93 @@ class MambaLM:
             self._L("rmsnorm_ij_j_reverse", sv["h_in"], self._p(W, p + "norm_w"), sv["rstd1"], self.gt, c.eps, self.gh,
                     self._p(G16, p + "norm_w"), 1.0, self.rms_scratch, T, c.d_model)
             # (alpha = 1 would also accumulate the gain gradient; G16 was zero-filled, so that is a plain write)
+            if update is not None and i in group_first:
+                self._update_bucket(group_first[i], *update)
         self._L("embedding_reverse", self.ids, self.gh, self._p(G32, "embedding"), T, c.d_model, c.vocab)
+        if update is not None:
+            self._update_bucket(len(self.buckets) - 1, *update)
+            # the next step's forward reads the refreshed weights
+            self._lib.mpEventRecord(self._ev_join, self.side.ctx)
+            self._lib.mpStreamWaitEvent(self.stream.ctx, self._ev_join)
+
+    def fold_gradients(self):
+        """g32 += g16 over the whole flat buffer (only for a reverse pass run without updates)."""
         self._timed("convert_r16_r32", lambda: self._lib.launch_convert_r16_r32(
-            C.c_void_p(G16.data_ptr()), C.c_void_p(G32.data_ptr()), 1.0, self.n_flat, self.stream.ctx))
+            C.c_void_p(self.g16.data_ptr()), C.c_void_p(self.g32.data_ptr()), 1.0, self.n_flat, self.stream.ctx))
 
-    # ------------------------------------------------------------------ optimizer
-    def adam_step(self, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, world=1):
+    # ------------------------------------------------------------------ the step
+    def _issue_step(self, comm, world, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8):
+        adam = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps)
+        self._timed("adam_tick", lambda: self._lib.launch_adam_tick(C.c_void_p(self.tick.data_ptr()), beta1, beta2, self.stream.ctx))
+        self.forward()
+        self.loss_and_logit_gradient()
+        self.backward(update=(comm, world, adam))
+
+    def capture(self, comm=None, world=1, **adam):
+        """Record the whole step (forward, loss, reverse with the bucketed all-reduces and updates on the second
+        stream) once into a CUDA graph; `train_step` then replays it with one call (the step is over a thousand
+        launches, which the host cannot issue as fast as the device runs them).  The captured sequence is first run
+        once for real - it is a training step like any other - so that every one-time set-up has happened."""
+        self._issue_step(comm, world, **adam)
         self.step_count += 1
-        self._L32("adam", self.w32, self.g32, self.m, self.v, lr, beta1, beta2, eps, 1.0 / (self.loss_scale * world), self.step_count,
-                  self.n_flat)
-        self._refresh_w16()
-
-    def capture(self):
-        """Record forward + loss + backward once into a CUDA graph; later steps replay it with one call
-        (the step is several hundred launches, which the host cannot issue as fast as the device runs them)."""
-        self.forward(); self.loss_and_logit_gradient(); self.backward()   # first run outside capture: one-time setup
-        self.stream.sync()
+        self.stream.sync(); self.side.sync()
         self._lib.mpGraphBeginCapture(self.stream.ctx)
-        self.forward(); self.loss_and_logit_gradient(); self.backward()
+        self._issue_step(comm, world, **adam)
         self.graph = self._lib.mpGraphEndCapture(self.stream.ctx)
-
-    def forward_backward(self):
-        if getattr(self, "graph", None):
-            self._lib.mpGraphLaunch(self.graph, self.stream.ctx)
-        else:
-            self.forward()
-            self.loss_and_logit_gradient()
-            self.backward()
+        self._graph_key = (id(comm), world, tuple(sorted(adam.items())))
 
     def train_step(self, comm=None, world=1, **adam):
-        """forward, loss, backward, (all-reduce), Adam.  Returns nothing: the mean loss of the step is read
+        """forward, loss, reverse, (all-reduce), Adam.  Returns nothing: the mean loss of the step is read
         with ``loss()`` after a stream synchronisation."""
-        self.forward_backward()
-        if comm is not None and world > 1:
-            comm.all_reduce_sum(self.g32, self.stream)
-        self.adam_step(world=world, **adam)
+        self.step_count += 1
+        if getattr(self, "graph", None):
+            if self._graph_key != (id(comm), world, tuple(sorted(adam.items()))):
+                raise ValueError("train_step called with other arguments than the step was captured with")
+            self._lib.mpGraphLaunch(self.graph, self.stream.ctx)
+        else:
+            self._issue_step(comm, world, **adam)
+
+    def adam_step(self, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, world=1):
+        """Whole-buffer update from the folded r32 gradient (after `forward_backward`), on the main stream."""
+        self.step_count += 1
+        self._timed("adam_tick", lambda: self._lib.launch_adam_tick(C.c_void_p(self.tick.data_ptr()), beta1, beta2, self.stream.ctx))
+        self._timed("adam_mixed_r32", lambda: self._lib.launch_adam_mixed_r32(
+            C.c_void_p(self.w32.data_ptr()), C.c_void_p(self.w16.data_ptr()), C.c_void_p(self.g32.data_ptr()), C.c_void_p(0),
+            C.c_void_p(self.m.data_ptr()), C.c_void_p(self.v.data_ptr()), lr, beta1, beta2, eps, 1.0 / (self.loss_scale * world),
+            C.c_void_p(self.tick.data_ptr()), self.n_flat, self.stream.ctx))
+
+    def forward_backward(self):
+        """Gradients only (no update): forward, loss, reverse, then the r16 gradients folded into g32."""
+        self.forward()
+        self.loss_and_logit_gradient()
+        self.backward()
+        self.fold_gradients()
+
+    def nonfinite_gradients(self) -> bool:
+        """True if any Adam update so far met a gradient that was not finite (and skipped that element)."""
+        self.stream.sync(); self.side.sync()
+        import torch
+        return bool(self.tick.view(torch.int32)[3].item() != 0)
 
     def all_reduce_description(self) -> str:
-        return "one mpAllReduceSum (NCCL) over the flat r32 gradient (%d bytes) after the reverse pass, on the compute stream" % (self.n_flat * 4)
+        sizes = ", ".join("%.0f MB" % ((hi - lo) * 4 / 1e6) for lo, hi, _ in self.buckets)
+        return ("%d buckets in the order the reverse pass completes them (%s); each is folded to r32, all-reduced with mpAllReduceSum (NCCL) "
+                "and updated on a second stream while the reverse pass continues; only the last (embedding) bucket is exposed" % (len(self.buckets), sizes))
 
     def release(self):
         """Destroy the captured graph (if any) and the stream; the device buffers go with the object."""
-        self.stream.sync()
+        self.stream.sync(); self.side.sync()
         if getattr(self, "graph", None):
             self._lib.mpGraphDestroy(self.graph)
             self.graph = None
-        self.stream.close()
+        for e in self._ev_bucket + [self._ev_join]:
+            self._lib.mpEventDestroy(e)
+        self.side.close()
+        if self._own_stream:
+            self.stream.close()
 
     def loss(self) -> float:
-        self.stream.sync()
+        self.stream.sync()   # the step's last main-stream operation waits for the update stream
         return float(self.loss_sum.item()) / self.T
 
     def grad(self, name):
@@ -377,22 +461,41 @@ class MambaLM:
         """Raw-bytes checkpoint in leaf order, one file per tensor named "{prefix}_{idx}" (the naming of the
         reference's tensor_file.zig:36-40): idx = position in `param_shapes()` for the r32 master weights, then
         the two Adam moments in the same order, and "{prefix}_state" with the step count."""
+        import hashlib
         import math
-        self.stream.sync()
+        import os
+        self.stream.sync(); self.side.sync()
         n = len(self.offsets)
+
+        def write_atomically(path, writer):      # a crash leaves either the old file or the new one, never a torn one
+            tmp = path + ".tmp"
+            writer(tmp)
+            os.replace(tmp, path)
         for k, buf in enumerate((self.w32, self.m, self.v)):
             host = buf.cpu().numpy()
             for idx, (name, (o, shape)) in enumerate(self.offsets.items()):
-                host[o:o + math.prod(shape)].tofile(f"{prefix}_{k * n + idx}")
-        with open(f"{prefix}_state", "w") as f:
-            f.write(f"{self.step_count}\n")
+                write_atomically(f"{prefix}_{k * n + idx}", lambda t, a=host[o:o + math.prod(shape)]: a.tofile(t))
+        layout = hashlib.sha256(repr(self.cfg.param_shapes()).encode()).hexdigest()
+
+        def write_state(t):
+            with open(t, "w") as f:
+                f.write(f"{self.step_count}\n{n}\n{layout}\n")
+        write_atomically(f"{prefix}_state", write_state)    # written last: its presence marks a complete checkpoint
 
     def load(self, prefix: str):
+        import hashlib
         import math
         import numpy as np
         import torch
-        self.stream.sync()
+        self.stream.sync(); self.side.sync()
         n = len(self.offsets)
+        with open(f"{prefix}_state") as f:
+            fields = f.read().split()
+        step = int(fields[0])
+        if len(fields) >= 3:     # tensor count and layout hash of the configuration the checkpoint was written with
+            layout = hashlib.sha256(repr(self.cfg.param_shapes()).encode()).hexdigest()
+            if int(fields[1]) != n or fields[2] != layout:
+                raise ValueError(f"{prefix}_state was written for another parameter layout")
         for k, buf in enumerate((self.w32, self.m, self.v)):
             host = np.zeros(self.n_flat, dtype=np.float32)
             for idx, (name, (o, shape)) in enumerate(self.offsets.items()):
@@ -403,16 +506,12 @@ class MambaLM:
                 host[o:o + cnt] = a
             buf.copy_(torch.from_numpy(host))
         torch.cuda.synchronize()
-        with open(f"{prefix}_state") as f:
-            self.step_count = int(f.read().strip())
+        self.step_count = step
+        self.tick.zero_()
+        self.tick.view(torch.int32)[2] = step     # Adam's step number continues where the checkpoint left off
+        torch.cuda.synchronize()
         self._refresh_w16()
 
     def launches_per_step(self) -> int:
-        """Kernels of this library launched per training step (a launcher call is several kernels: the scan
-        forward 5, its reverse 22, an RMSNorm reverse 3, a split-K contraction 2)."""
-        n = self.cfg.n_layer
-        forward = 14 * n + 3          # per layer: 2 norms, 2 contractions, conv, softplus, neg_exp, scan (5), gate, add
-        loss = 2
-        reverse = 39 * n + 9          # per layer: 4 contractions (2 split-K), 2 norm reverses, gate, scan (22), skip, A_log, softplus, conv
-        update = 3                    # gradient conversion, Adam, r16 refresh
-        return forward + loss + reverse + update
+        """Kernel launches of one training step: the kernel nodes of the captured graph (0 before `capture`)."""
+        return int(self._lib.mpGraphKernelNodes(self.graph)) if getattr(self, "graph", None) else 0

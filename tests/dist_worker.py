@@ -4,7 +4,11 @@ MODE cpu: gloo ranks exercise the host logic of the data-parallel path - row
 sharding, the unique-id exchange, "sum of shard gradients = full-batch
 gradient", optimizer step with grad_scale = 1/world - with the CPU oracle doing
 the arithmetic.  MODE gpu: the same step with the library's kernels and its
-NCCL all-reduce (mpAllReduceSum).  Exit code 0 = all checks passed."""
+NCCL all-reduce (mpAllReduceSum).  MODE fail_init / leave: failure detection
+among CPU ranks - a rank whose communicator creation fails (host fail point),
+and a rank that leaves between two steps; the survivors must notice on the host
+(status codes, heartbeat, bounded collective) and never hang.  Exit code 0 = all
+checks passed."""
 import os
 import sys
 from pathlib import Path
@@ -28,10 +32,84 @@ def inputs():
     return x, gy, gain
 
 
+def failure_modes(mode, rank, world):
+    import datetime
+    import metaphor_b200 as mp
+    from metaphor_b200.dist import ERROR, TIMEOUT, CommFailure, GradientComm, Heartbeat
+    lib = mp.lib()
+    dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=20))
+    store = dist.distributed_c10d._get_default_store()
+    if mode == "fail_init":
+        # rank 1's communicator creation fails; every rank learns of it before any collective is started
+        if rank == 1:
+            lib.mpSetFailPoint(b"mpCommInit", 1)
+        try:
+            comm = GradientComm(world, rank, host_fake=True)
+            mine = 0
+        except CommFailure as e:
+            assert e.status == ERROR and rank == 1
+            comm, mine = None, e.status
+        status = torch.tensor([mine], dtype=torch.int32)
+        gathered = [torch.zeros_like(status) for _ in range(world)]
+        dist.all_gather(gathered, status)
+        failed = [r for r, t in enumerate(gathered) if int(t) != 0]
+        assert failed == [1], failed
+        # the fail point is spent: a second attempt on rank 1 succeeds (the recovery path rebuilds the communicator)
+        if rank == 1:
+            comm = GradientComm(world, rank, host_fake=True)
+        t = torch.full((8,), float(rank + 1))
+        comm.all_reduce_sum(t)
+        assert float(t[0]) == world * (world + 1) / 2
+        # bad handles and arguments are reported, not dereferenced
+        import ctypes as C
+        assert lib.mpAllReduceSumStatus(None, None, 0, 1, mp.abi.StreamContext()) == 4
+        out = C.c_void_p(0)
+        assert lib.mpCommInitStatus(None, 2, 5, C.byref(out)) == 5
+        lib.mpSetFailPoint(b"mpAllReduceSum", 1)
+        try:
+            comm.all_reduce_sum(torch.zeros(4))
+            raise AssertionError("the fail point did not fire")
+        except CommFailure as e:
+            assert e.status == ERROR
+        lib.mpSetFailPoint(None, 0)
+        comm.close()
+        dist.barrier()
+    else:
+        # two steps; rank 1 leaves after the first, with nothing in flight
+        comm = GradientComm(world, rank, host_fake=True, timeout_s=2.0)
+        hb = Heartbeat(store, world, rank, timeout_s=1.5)
+        hb.post(1)
+        assert hb.missing(1) == []
+        t = torch.full((1024,), float(rank + 1))
+        comm.all_reduce_sum(t)
+        assert float(t[0]) == world * (world + 1) / 2
+        if rank == 1:
+            comm.close()
+            print(f"rank {rank}/{world} ok", flush=True)
+            os._exit(0)                              # gone without a word, between steps
+        hb.post(2)
+        gone = hb.missing(2)                         # noticed on the host before the next launch
+        assert gone == [1], gone
+        # and a collective started anyway ends with a status within the time-out instead of hanging
+        import time
+        t0 = time.monotonic()
+        try:
+            comm.all_reduce_sum(torch.ones(1024))
+            raise AssertionError("the collective towards a rank that left did not fail")
+        except CommFailure as e:
+            assert e.status in (ERROR, TIMEOUT)
+        assert time.monotonic() - t0 < 10.0
+        comm.close()
+    print(f"rank {rank}/{world} ok", flush=True)
+    os._exit(0)      # no collective shutdown: a peer may be gone
+
+
 def main():
     mode = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if mode in ("fail_init", "leave"):
+        return failure_modes(mode, rank, world)
     from oracle import pyoracle as orc
     x, gy, gain = inputs()
     lo, hi = shard_range(M, world, rank)

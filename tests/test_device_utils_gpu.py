@@ -99,3 +99,27 @@ def test_ssd_helper_streams_are_released(mp):
         s.sync()
         assert s.status() == 0 and bool(torch.isfinite(y).all())
         s.close()
+
+
+def test_a_wait_that_cannot_be_satisfied_times_out_and_reports(mp):
+    """The bounded waits' time-out path, exercised without a fault: with a 1 ms limit a kernel that waits for a
+    barrier phase nobody completes returns by itself, the status word reads MP_STATUS_WAIT_TIMEOUT, and the stream
+    stays usable."""
+    import time
+    import torch
+    torch.zeros(1, device="cuda")
+    lib = mp.lib()
+    with mp.Stream() as s:
+        lib.mpSetWaitLimit(s.ctx, 1000)
+        t0 = time.monotonic()
+        lib.mpSelfTestWaitTimeout(s.ctx)
+        s.sync()
+        assert time.monotonic() - t0 < 1.0           # far below the default 2 s: the run-time limit was used
+        assert s.status() == 1                       # MP_STATUS_WAIT_TIMEOUT
+        assert s.status() == 0                       # reading clears it
+        lib.mpSetWaitLimit(s.ctx, 0)
+        x = torch.arange(1024, dtype=torch.float32, device="cuda"); y = torch.empty_like(x)
+        torch.cuda.synchronize()
+        mp.launch("copy", torch.float32, x, y, 1024, s)
+        s.sync()
+        assert torch.equal(x, y) and s.status() == 0

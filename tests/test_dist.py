@@ -24,7 +24,15 @@ def test_shard_range_partitions_exactly():
         shard_range(10, 2, 2)
 
 
-def run_ranks(mode, nproc, port):
+def free_port() -> int:
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def run_ranks(mode, nproc, port=None):
+    port = port or free_port()
     env = dict(os.environ)
     env["PYTHONPATH"] = str(ROOT) + os.pathsep + env.get("PYTHONPATH", "")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
@@ -33,7 +41,7 @@ def run_ranks(mode, nproc, port):
 
 
 def test_two_gloo_ranks_reproduce_the_full_batch_step(orc):
-    res = run_ranks("cpu", 2, 29541)
+    res = run_ranks("cpu", 2)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     assert res.stdout.count(" ok") == 2
 
@@ -43,6 +51,17 @@ def test_nccl_all_reduce_and_data_parallel_step_on_two_gpus(mp, orc):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    res = run_ranks("gpu", 2, 29542)
+    res = run_ranks("gpu", 2)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     assert res.stdout.count(" ok") == 2
+
+
+def test_a_rank_whose_communicator_creation_fails_is_noticed_by_all(mp):
+    res = run_ranks("fail_init", 2)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert res.stdout.count(" ok") == 2
+
+
+def test_a_rank_that_leaves_between_steps_is_noticed_without_hanging(mp):
+    res = run_ranks("leave", 2)
+    assert res.stdout.count(" ok") == 2, res.stdout[-2000:] + res.stderr[-4000:]

@@ -26,6 +26,7 @@ def test_reduced_lm_step(mp, stream, orc):
     model.forward()
     model.loss_and_logit_gradient()
     model.backward()
+    model.fold_gradients()
     loss = model.loss()
     assert stream.status() == 0
 
@@ -36,15 +37,18 @@ def test_reduced_lm_step(mp, stream, orc):
     ref = lm_oracle.forward_loss(cfg, wt, torch.from_numpy(ids.astype(np.int64)), torch.from_numpy(targets.astype(np.int64)), batch, seqlen)
     ref.backward()
     ref_loss = float(ref.detach())
-    assert abs(loss - ref_loss) <= 2e-3 * abs(ref_loss), (loss, ref_loss)
+    assert abs(loss - ref_loss) <= 1e-2 * abs(ref_loss), (loss, ref_loss)   # r16 activations: the r16 tolerance
+    assert abs(loss - ref_loss) <= 2e-3 * abs(ref_loss), ("loss is usually within 2e-3", loss, ref_loss)
     worst = {}
     for name in w:
         g, r = model.grad(name).astype(np.float64), wt[name].grad.numpy()
         err = np.max(np.abs(g - r)) / max(np.max(np.abs(r)), 1e-30)
         worst[name] = err
-    print('loss', loss, ref_loss, 'worst gradient errors', sorted(worst.items(), key=lambda kv: -kv[1])[:5])
-    bad = {k: v for k, v in worst.items() if v > 2e-2}
-    assert not bad, f"gradients outside 2e-2 of the float64 oracle: {bad}"
+    print('loss', loss, ref_loss, 'gradient errors (max |got - ref| / max |ref|), worst first:')
+    for k, v in sorted(worst.items(), key=lambda kv: -kv[1]):
+        print(f"  {k:28s} {v:.3e}")
+    bad = {k: v for k, v in worst.items() if v > 1e-2}
+    assert not bad, f"gradients outside 1e-2 (the r16 tolerance) of the float64 oracle: {bad}"
 
     # Adam on the flat buffer against the scalar oracle on the same gradient
     g32 = model.g32.cpu().numpy().copy()
@@ -56,6 +60,36 @@ def test_reduced_lm_step(mp, stream, orc):
     got = model.w32.cpu().numpy()
     assert np.max(np.abs(got - wref)) <= 1e-6
     assert np.array_equal(model.w16.cpu().numpy(), got.astype(np.float16))
+    assert not model.nonfinite_gradients()
+
+
+def test_default_loss_scale_and_overflow_flag(mp, stream):
+    """Default arguments at a realistic token count: the default loss scale keeps the r16 logit gradient out of the
+    subnormal range (every weight gets a non-zero update), and a gradient that overflows is skipped and reported."""
+    import torch
+    from metaphor_b200.mamba_lm import LMConfig, MambaLM
+    cfg = LMConfig(d_model=256, n_layer=1, vocab=4096, chunk=128)
+    batch, seqlen = 8, 2048                      # T = 16384: 1/T = 6.1e-5 is already the smallest normal r16 number
+    model = MambaLM(cfg, batch, seqlen, seed=0, stream=stream)
+    assert model.loss_scale == 16384.0
+    g = torch.Generator().manual_seed(5)
+    tok = torch.randint(0, cfg.vocab, (batch * seqlen + 1,), generator=g, dtype=torch.int32)
+    torch.cuda.current_stream().synchronize()
+    model.set_batch(tok[:-1].contiguous(), tok[1:].contiguous())
+    model.forward_backward()
+    stream.sync()
+    emb = model.grad("embedding")
+    assert np.isfinite(emb).all()
+    used = np.unique(tok.numpy())
+    assert (np.abs(emb[used]).max(axis=1) > 0).mean() > 0.99      # rows of tokens that occur all carry gradient
+    w_before = model.w32.cpu().numpy().copy()
+    model.g32[7] = float("inf")
+    torch.cuda.synchronize()
+    model.adam_step()
+    assert model.nonfinite_gradients()
+    w_after = model.w32.cpu().numpy()
+    assert w_after[7] == w_before[7] and np.isfinite(w_after).all()
+    model.release()
 
 
 def test_checkpoint_resume(mp, stream, tmp_path):

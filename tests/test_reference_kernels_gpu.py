@@ -112,3 +112,25 @@ def test_rank2_reference_vs_oracle_vs_ours(mp, stream, orc, ref, sfx, shape):
     ours(mp, stream, "broadcast_i_ij", sfx, dev(vi), o_ours, 0.0, m, n)
     assert np.array_equal(host(o_ref), np.broadcast_to(vi[:, None], shape))
     assert np.array_equal(host(o_ours), host(o_ref))
+
+
+# The reference's contraction launcher (cuBLAS H/S/Dgemm behind launch_inner_product_ij_jk_ik,
+# src/cuda/nvcc_src/inner_product_ij_jk_ik.cu:12-26 and gemm_dispatch.cuh:24,59,95): the oracle's triple loop
+# against it, and this library against it.  r16: the reference computes and accumulates in fp16, so it is
+# compared at the r16 tolerance; ours is additionally held to the fp64 oracle.
+@pytest.mark.parametrize("sfx", ["r16", "r32", "r64"])
+@pytest.mark.parametrize("shape", [(32, 256, 256), (128, 128, 128), (37, 53, 29), (256, 768, 512)])
+@pytest.mark.parametrize("alpha_beta", [(1.0, 0.0), (0.5, 1.0)])
+def test_inner_product_reference_vs_oracle_vs_ours(mp, stream, orc, ref, sfx, shape, alpha_beta):
+    m, n, k = shape      # a [m, n], b [n, k], c [m, k] (the reference's argument order)
+    alpha, beta = alpha_beta
+    a = rng_normal(21, (m, n), sfx); b = rng_normal(22, (n, k), sfx, scale=1.0 / np.sqrt(n))
+    c0 = rng_normal(23, (m, k), sfx) if beta else np.zeros((m, k), a.dtype)
+    o_ref = dev(c0); o_ours = dev(c0)
+    ref.launch("inner_product_ij_jk_ik", sfx, dev(a), dev(b), alpha, o_ref, beta, m, n, k)
+    ours(mp, stream, "inner_product_ij_jk_ik", sfx, dev(a), dev(b), alpha, o_ours, beta, m, n, k)
+    want = narrow(orc.inner_product(wide(a), wide(b), alpha, wide(c0).copy(), beta), sfx)
+    tol = TOL_RED[sfx]
+    assert_close(want, host(o_ref), tol, f"oracle vs reference inner_product {sfx} {shape} alpha,beta={alpha_beta}")
+    assert_close(host(o_ours), host(o_ref), tol, f"ours vs reference inner_product {sfx} {shape} alpha,beta={alpha_beta}")
+    assert_close(host(o_ours), want, tol, f"ours vs oracle inner_product {sfx} {shape} alpha,beta={alpha_beta}")
