@@ -582,7 +582,7 @@ def run_lm(args):
     comm = GradientComm(world, rank) if world > 1 else None
     cfg = LMConfig(n_layer=args.lm_layers, chunk=args.lm_chunk)
     batch, seqlen = args.lm_batch, LM_SEQ
-    model = MambaLM(cfg, batch, seqlen, seed=0, loss_scale=65536.0)
+    model = MambaLM(cfg, batch, seqlen, seed=0, loss_scale=65536.0, overlap=not args.lm_no_overlap)
     stream, ts = model.stream, model.stream.torch_stream()
     T = batch * seqlen
     gen = torch.Generator().manual_seed(1000 + rank)
@@ -654,7 +654,7 @@ def run_lm(args):
     # one more step issued launcher by launcher with an event pair around each: the share of every launcher
     prof = model.profile_step(comm=comm, world=world, **ADAM)
     barrier()
-    graph_kernels = int(lib.mpGraphKernelNodes(model.graph)) if getattr(model, "graph", None) else None
+    graph_kernels = model.launches_per_step(world) or None
     n_params = cfg.n_params()
 
     out = None
@@ -703,9 +703,10 @@ def run_lm(args):
                     "path": "MambaLM.set_batch (mpMemcpyHtoD from pinned memory) + train_step + loss() (mpMemcpyDtoH + stream sync) every step"},
             "clocks": clocks,
             "gpu_launches": ((graph_kernels or 0) + 1) * args.steps,
-            "gpu_launches_per_step": {"graph_kernel_nodes": graph_kernels,
-                                      "graph": "the whole step: forward, loss, reverse, per-bucket gradient folding" + (", NCCL all-reduces" if world > 1 else "") + ", mixed-precision Adam",
-                                      "outside the graph": "one 4-byte copy of the step's loss"},
+            "gpu_launches_per_step": {"kernels of this library": graph_kernels,
+                                      "how": "kernel nodes of the %d captured graphs (forward, loss, reverse, cut at the update buckets) + the live launches of the bucket updates "
+                                             "(mixed-precision Adam; gradient folding before an all-reduce)%s + one 4-byte copy of the step's loss"
+                                             % (len(model.buckets), "; NCCL's all-reduce kernels are not counted" if world > 1 else "")},
             "loss": {"first_timed_step": round(loss_host[0], 4), "last_timed_step": round(loss_host[args.steps - 1], 4),
                      "expected_at_init": round(math.log(cfg.vocab), 4),
                      "note": "one fixed random batch per rank is repeated, so the loss falls as the model memorises it"},
@@ -797,6 +798,7 @@ def main():
     ap.add_argument("--lm-layers", type=int, default=24)
     ap.add_argument("--lm-batch", type=int, default=8)
     ap.add_argument("--lm-no-graph", action="store_true", help="issue every launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--lm-no-overlap", action="store_true", help="run the bucket updates (all-reduce, Adam) on the main stream instead of a second one")
     ap.add_argument("--lm-chunk", type=int, default=256, help="scan chunk of the LM workload (128 or 256)")
     ap.add_argument("--profile-case", default=None, help="OP:DTYPE:SIZES, three launches for an ncu capture")
     ap.add_argument("--profile-time", action="store_true", help="with --profile-case: also time 20 launches with CUDA events")

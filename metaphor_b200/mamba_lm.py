@@ -23,9 +23,10 @@ second stream folds that bucket's r16 gradients into the r32 ones, all-reduces
 the bucket (data-parallel runs) and applies the mixed-precision Adam step, which
 also writes the bucket's refreshed r16 weights - while the first stream is
 already in the reverse of the layers below.  Only the embedding bucket, whose
-gradient is complete last, is exposed.  The whole step (forward, loss, reverse,
-all-reduces, updates) is one stream-ordered sequence and can be captured into
-one CUDA graph: the step number Adam needs lives in device memory.
+gradient is complete last, is exposed.  For replay the main-stream work is captured
+as one CUDA graph per bucket (cut where a bucket's gradients are complete); the
+bucket updates - and with them every NCCL call - are issued live between the
+graph launches, on the second stream.
 """
 from __future__ import annotations
 
@@ -110,7 +111,7 @@ ALIGN = 64   # elements: keeps every parameter 128-byte aligned in the r16 copy
 
 class MambaLM:
     def __init__(self, cfg: LMConfig, batch: int, seqlen: int, weights=None, seed: int = 0, stream: Stream | None = None,
-                 loss_scale: float | None = None, bucket_layers: int = 4):
+                 loss_scale: float | None = None, bucket_layers: int = 4, overlap: bool = True):
         """loss_scale multiplies the logit gradient before it is stored in r16 (the mean cross-entropy puts a factor
         1/T on it, which at realistic T drops typical entries into the r16 subnormal range).  Default: the largest
         power of two not above T, so that scale/T is in (1/2, 1].  The scale is static; Adam skips elements whose
@@ -158,6 +159,7 @@ class MambaLM:
             self.buckets.append((lo, hi, first))
             hi, top = lo, first
         self.buckets.append((0, hi, -1))
+        self.overlap = overlap                    # False: the bucket updates run on the main stream, between the reverse kernels
         self.side = Stream()                      # carries gradient folding, all-reduce and Adam of finished buckets
         self._ev_bucket = [self._lib.mpEventCreate() for _ in self.buckets]
         self._ev_join = self._lib.mpEventCreate()
@@ -306,9 +308,10 @@ class MambaLM:
         """Bucket k's gradients are complete on the main stream: hand them to the update stream."""
         lo, hi, _ = self.buckets[k]
         n = hi - lo
-        side = self.side
-        self._lib.mpEventRecord(self._ev_bucket[k], self.stream.ctx)
-        self._lib.mpStreamWaitEvent(side.ctx, self._ev_bucket[k])
+        side = self.side if self.overlap else self.stream
+        if self.overlap:
+            self._lib.mpEventRecord(self._ev_bucket[k], self.stream.ctx)
+            self._lib.mpStreamWaitEvent(side.ctx, self._ev_bucket[k])
         P = lambda buf: C.c_void_p(buf.data_ptr() + lo * buf.element_size())
         g16 = P(self.g16)
         if comm is not None and world > 1:
@@ -319,9 +322,10 @@ class MambaLM:
             P(self.w32), P(self.w16), P(self.g32), g16, P(self.m), P(self.v), adam["lr"], adam["beta1"], adam["beta2"], adam["eps"],
             1.0 / (self.loss_scale * world), C.c_void_p(self.tick.data_ptr()), n, side.ctx), side=True)
 
-    def backward(self, update=None):
-        """Reverse pass.  `update` = (comm, world, adam) applies every bucket's update as soon as its gradients are
-        complete; None leaves the gradients in g16 / g32 (use `fold_gradients()` to read them)."""
+    def backward(self, at_bucket=None):
+        """Reverse pass.  `at_bucket(k)` is called on the host right after the last launch that writes a gradient of
+        bucket k (the update of that bucket, or a cut of the graph capture); None leaves the gradients in g16 / g32
+        (use `fold_gradients()` to read them)."""
         c, T = self.cfg, self.T
         W, G16, G32 = self.w16, self.g16, self.g32
         di, gn, H, P = c.d_inner, c.ngroups * c.d_state, c.heads, c.headdim
@@ -361,14 +365,11 @@ class MambaLM:
             self._L("rmsnorm_ij_j_reverse", sv["h_in"], self._p(W, p + "norm_w"), sv["rstd1"], self.gt, c.eps, self.gh,
                     self._p(G16, p + "norm_w"), 1.0, self.rms_scratch, T, c.d_model)
             # (alpha = 1 would also accumulate the gain gradient; G16 was zero-filled, so that is a plain write)
-            if update is not None and i in group_first:
-                self._update_bucket(group_first[i], *update)
+            if at_bucket is not None and i in group_first:
+                at_bucket(group_first[i])
         self._L("embedding_reverse", self.ids, self.gh, self._p(G32, "embedding"), T, c.d_model, c.vocab)
-        if update is not None:
-            self._update_bucket(len(self.buckets) - 1, *update)
-            # the next step's forward reads the refreshed weights
-            self._lib.mpEventRecord(self._ev_join, self.side.ctx)
-            self._lib.mpStreamWaitEvent(self.stream.ctx, self._ev_join)
+        if at_bucket is not None:
+            at_bucket(len(self.buckets) - 1)
 
     def fold_gradients(self):
         """g32 += g16 over the whole flat buffer (only for a reverse pass run without updates)."""
@@ -376,36 +377,58 @@ class MambaLM:
             C.c_void_p(self.g16.data_ptr()), C.c_void_p(self.g32.data_ptr()), 1.0, self.n_flat, self.stream.ctx))
 
     # ------------------------------------------------------------------ the step
-    def _issue_step(self, comm, world, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8):
-        adam = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps)
+    def _issue_main(self, at_bucket, beta1, beta2):
+        """The main-stream sequence of a step, with the host callback at every completed bucket."""
         self._timed("adam_tick", lambda: self._lib.launch_adam_tick(C.c_void_p(self.tick.data_ptr()), beta1, beta2, self.stream.ctx))
         self.forward()
         self.loss_and_logit_gradient()
-        self.backward(update=(comm, world, adam))
+        self.backward(at_bucket)
 
-    def capture(self, comm=None, world=1, **adam):
-        """Record the whole step (forward, loss, reverse with the bucketed all-reduces and updates on the second
-        stream) once into a CUDA graph; `train_step` then replays it with one call (the step is over a thousand
-        launches, which the host cannot issue as fast as the device runs them).  The captured sequence is first run
-        once for real - it is a training step like any other - so that every one-time set-up has happened."""
-        self._issue_step(comm, world, **adam)
+    def _join_updates(self):
+        # the next step's forward reads the refreshed weights
+        if not self.overlap:
+            return
+        self._lib.mpEventRecord(self._ev_join, self.side.ctx)
+        self._lib.mpStreamWaitEvent(self.stream.ctx, self._ev_join)
+
+    def _issue_step(self, comm, world, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8):
+        adam = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps)
+        self._issue_main(lambda k: self._update_bucket(k, comm, world, adam), beta1, beta2)
+        self._join_updates()
+
+    def capture(self, comm=None, world=1, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8):
+        """Record the main-stream work of a step as one CUDA graph per update bucket (the step is over nine hundred
+        launches, which the host cannot issue as fast as the device runs them); `train_step` then launches the
+        graphs one after another and issues each bucket's update - gradient folding, all-reduce, Adam - live on the
+        second stream right behind the graph that completes the bucket.  No collective is ever part of a graph.
+        The sequence is first run once for real (a training step like any other), so that every one-time set-up
+        has happened before the capture."""
+        self._issue_step(comm, world, lr=lr, beta1=beta1, beta2=beta2, eps=eps)
         self.step_count += 1
         self.stream.sync(); self.side.sync()
-        self._lib.mpGraphBeginCapture(self.stream.ctx)
-        self._issue_step(comm, world, **adam)
-        self.graph = self._lib.mpGraphEndCapture(self.stream.ctx)
-        self._graph_key = (id(comm), world, tuple(sorted(adam.items())))
+        graphs = []
+        last = len(self.buckets) - 1
 
-    def train_step(self, comm=None, world=1, **adam):
+        def cut(k):
+            graphs.append(self._lib.mpGraphEndCapture(self.stream.ctx))
+            if k < last:
+                self._lib.mpGraphBeginCapture(self.stream.ctx)
+        self._lib.mpGraphBeginCapture(self.stream.ctx)
+        self._issue_main(cut, beta1, beta2)
+        self.graphs = graphs
+
+    def train_step(self, comm=None, world=1, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8):
         """forward, loss, reverse, (all-reduce), Adam.  Returns nothing: the mean loss of the step is read
         with ``loss()`` after a stream synchronisation."""
         self.step_count += 1
-        if getattr(self, "graph", None):
-            if self._graph_key != (id(comm), world, tuple(sorted(adam.items()))):
-                raise ValueError("train_step called with other arguments than the step was captured with")
-            self._lib.mpGraphLaunch(self.graph, self.stream.ctx)
+        if getattr(self, "graphs", None):
+            adam = dict(lr=lr, beta1=beta1, beta2=beta2, eps=eps)
+            for k, graph in enumerate(self.graphs):
+                self._lib.mpGraphLaunch(graph, self.stream.ctx)
+                self._update_bucket(k, comm, world, adam)
+            self._join_updates()
         else:
-            self._issue_step(comm, world, **adam)
+            self._issue_step(comm, world, lr=lr, beta1=beta1, beta2=beta2, eps=eps)
 
     def adam_step(self, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, world=1):
         """Whole-buffer update from the folded r32 gradient (after `forward_backward`), on the main stream."""
@@ -437,9 +460,9 @@ class MambaLM:
     def release(self):
         """Destroy the captured graph (if any) and the stream; the device buffers go with the object."""
         self.stream.sync(); self.side.sync()
-        if getattr(self, "graph", None):
-            self._lib.mpGraphDestroy(self.graph)
-            self.graph = None
+        for graph in getattr(self, "graphs", None) or []:
+            self._lib.mpGraphDestroy(graph)
+        self.graphs = None
         for e in self._ev_bucket + [self._ev_join]:
             self._lib.mpEventDestroy(e)
         self.side.close()
@@ -512,6 +535,10 @@ class MambaLM:
         torch.cuda.synchronize()
         self._refresh_w16()
 
-    def launches_per_step(self) -> int:
-        """Kernel launches of one training step: the kernel nodes of the captured graph (0 before `capture`)."""
-        return int(self._lib.mpGraphKernelNodes(self.graph)) if getattr(self, "graph", None) else 0
+    def launches_per_step(self, world: int = 1) -> int:
+        """Kernel launches of one training step: the kernel nodes of the captured graphs plus the live launches of the
+        bucket updates (0 before `capture`).  NCCL's own kernels are not counted."""
+        graphs = getattr(self, "graphs", None)
+        if not graphs:
+            return 0
+        return sum(int(self._lib.mpGraphKernelNodes(g)) for g in graphs) + (2 if world > 1 else 1) * len(self.buckets)
