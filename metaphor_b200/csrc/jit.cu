@@ -20,6 +20,7 @@
 #include <string.h>
 
 #include <map>
+#include <tuple>
 #include <mutex>
 #include <sstream>
 #include <string>
@@ -391,7 +392,7 @@ struct JitProgram {
 constexpr uint64_t JIT_MAGIC = 0x4d504a4954505247ull;
 
 std::mutex g_jit_mutex;
-std::map<std::pair<std::string, int>, JitProgram*> g_jit_cache;
+std::map<std::tuple<std::string, int, int>, JitProgram*> g_jit_cache;   // (expression, dtype key, device)
 
 JitProgram* as_program(void* h) {
   JitProgram* p = static_cast<JitProgram*>(h);
@@ -421,7 +422,12 @@ extern "C" void mpJitFreeSource(char* s) { free(s); }
 extern "C" void* mpJitCompile(const char* expr_text, uint32_t dtype_key) {
   if (dtype_key > 2) { printf("mpJitCompile: bad dtype key %u\n", dtype_key); return nullptr; }
   std::lock_guard<std::mutex> lock(g_jit_mutex);
-  const auto key = std::make_pair(std::string(expr_text), static_cast<int>(dtype_key));
+  // A loaded module belongs to the context of the device it was loaded on: the device is part of the key, so a
+  // process that works on several devices gets one module per device.
+  int device = -1;
+  MP_CUDA_CHECK(cudaFree(nullptr));  // make sure the primary context exists and is current
+  MP_CUDA_CHECK(cudaGetDevice(&device));
+  const auto key = std::make_tuple(std::string(expr_text), static_cast<int>(dtype_key), device);
   auto it = g_jit_cache.find(key);
   if (it != g_jit_cache.end()) { it->second->refs++; return it->second; }
 

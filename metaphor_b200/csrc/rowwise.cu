@@ -294,18 +294,35 @@ __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_rev_kernel(
     for (int k = 0; k < PN; ++k) acc[u][k] = A(0);
   }
   const A inv_n = A(1) / static_cast<A>(n);
-  for (size_t i = 0; i < rows_per_cta; ++i) {
-    const size_t row = (static_cast<size_t>(blockIdx.x) * rows_per_cta + i) * ROWS + g;
-    if (row >= m) break;
-    Pack<T> px[PPT], pg[PPT];
+  // The next row's packs are requested before the current row is reduced: a narrow row is a few hundred bytes per
+  // thread group, and with one row in flight per group the kernel waits on memory latency, not bandwidth.
+  Pack<T> px[PPT], pg[PPT], nx[PPT], ng[PPT];
+  const size_t row0 = static_cast<size_t>(blockIdx.x) * rows_per_cta * ROWS + g;
+  if (row0 < m) {
 #pragma unroll
     for (int u = 0; u < PPT; ++u) {
       if (MP_PACK_VALID(u)) {
-        px[u] = ld_pack_stream(x + row * n, MP_PACK_INDEX(u));
-        pg[u] = ld_pack_stream(gy + row * n, MP_PACK_INDEX(u));
+        px[u] = ld_pack_stream(x + row0 * n, MP_PACK_INDEX(u));
+        pg[u] = ld_pack_stream(gy + row0 * n, MP_PACK_INDEX(u));
+      }
+    }
+  }
+  for (size_t i = 0; i < rows_per_cta; ++i) {
+    const size_t row = (static_cast<size_t>(blockIdx.x) * rows_per_cta + i) * ROWS + g;
+    if (row >= m) break;
+    const size_t next = row + ROWS;
+    if (i + 1 < rows_per_cta && next < m) {
+#pragma unroll
+      for (int u = 0; u < PPT; ++u) {
+        if (MP_PACK_VALID(u)) {
+          nx[u] = ld_pack_stream(x + next * n, MP_PACK_INDEX(u));
+          ng[u] = ld_pack_stream(gy + next * n, MP_PACK_INDEX(u));
+        }
       }
     }
     rmsnorm_rev_row<T, GROUP, PPT, FULL, BLEND>(px, pg, pgain, acc, rstd_in, eps, inv_n, alpha, gx + row * n, row, t, nv, red);
+#pragma unroll
+    for (int u = 0; u < PPT; ++u) { px[u] = nx[u]; pg[u] = ng[u]; }
   }
   A* pr = partial + (static_cast<size_t>(blockIdx.x) * ROWS + g) * n;
 #pragma unroll
@@ -669,14 +686,13 @@ inline size_t row_grid(const RowPlan& p, size_t m, int sm_count, int threads_per
 // fewer rows = more CTAs in flight).
 // `units` = row groups (register variant) or rows (staged variant) of the call: short matrices take
 // fewer rows per CTA so that at least ~8 CTAs per SM exist.
-inline size_t rms_rev_rows_per_cta(size_t units) {
-  static size_t cap = 0;
-  if (cap == 0) {
+inline size_t rms_rev_rows_per_cta(size_t units, int sm_count) {
+  static const size_t cap = []() {      // initialised once, thread-safely (launchers may be called from any host thread)
     const char* e = getenv("MP_RMS_REV_ROWS");
-    long v = e ? strtol(e, nullptr, 10) : 0;
-    cap = v > 0 ? static_cast<size_t>(v) : 32;
-  }
-  size_t r = units / (148 * 8);
+    const long v = e ? strtol(e, nullptr, 10) : 0;
+    return v > 0 ? static_cast<size_t>(v) : static_cast<size_t>(32);
+  }();
+  size_t r = units / (static_cast<size_t>(sm_count > 0 ? sm_count : 148) * 8);
   if (r < 1) r = 1;
   return r > cap ? cap : r;
 }
@@ -710,9 +726,9 @@ StagedPlan plan_staged(size_t n, bool aligned) {
   p.full = nv == static_cast<size_t>(STG_THREADS) * p.ppt;
   return p;
 }
-inline size_t rms_rev_grid(const RowPlan& p, size_t m) {
+inline size_t rms_rev_grid(const RowPlan& p, size_t m, int sm_count) {
   const size_t groups = (m + p.rows - 1) / p.rows;
-  const size_t rpc = rms_rev_rows_per_cta(groups);
+  const size_t rpc = rms_rev_rows_per_cta(groups, sm_count);
   size_t grid = (groups + rpc - 1) / rpc;
   return grid < 1 ? 1 : grid;
 }
@@ -793,9 +809,8 @@ static void rmsnorm_ij_j_impl(const void* x_, const void* gain_, double eps, voi
 template <typename T>
 static size_t rmsnorm_rev_slots(size_t m, size_t n, int sm_count, bool aligned) {
   const RowPlan p = plan_rows_rev<T>(n, aligned);
-  (void)sm_count;
-  size_t slots = rms_rev_grid(p, m) * p.rows;
-  const size_t staged = (m + rms_rev_rows_per_cta(m) - 1) / rms_rev_rows_per_cta(m);  // one slot per CTA
+  size_t slots = rms_rev_grid(p, m, sm_count) * p.rows;
+  const size_t staged = (m + rms_rev_rows_per_cta(m, sm_count) - 1) / rms_rev_rows_per_cta(m, sm_count);  // one slot per CTA
   return slots > staged ? slots : staged;
 }
 
@@ -822,12 +837,13 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
     const bool aligned = mp_aligned16(x) && mp_aligned16(gain) && mp_aligned16(gy) && mp_aligned16(gx);
     const RowPlan p = plan_rows_rev<T>(n, aligned);
     const StagedPlan sp = plan_staged<T>(n, aligned);
-    unsigned grid = static_cast<unsigned>(rms_rev_grid(p, m));
-    size_t rpc = rms_rev_rows_per_cta((m + p.rows - 1) / p.rows);
+    const int sms = mp_sm_count(ctx);
+    unsigned grid = static_cast<unsigned>(rms_rev_grid(p, m, sms));
+    size_t rpc = rms_rev_rows_per_cta((m + p.rows - 1) / p.rows, sms);
     slots = static_cast<size_t>(grid) * p.rows;
     MpStreamState* state = mp_state_or_null(ctx);  // the staged kernel reports timeouts through the status word
     if (sp.ok && state != nullptr) {
-      rpc = rms_rev_rows_per_cta(m);
+      rpc = rms_rev_rows_per_cta(m, sms);
       grid = static_cast<unsigned>((m + rpc - 1) / rpc);
       slots = grid;
       uint32_t* status = state->status_dev;
@@ -944,6 +960,15 @@ extern "C" int launch_rmsnorm_ij_j_reverse_static_r32(const void* x_, const void
   using T = float;
   using A = float;
   if (n == 0) return 0;
+  if (MpStreamState* state = mp_state_or_null(ctx)) {
+    // the scratch array is per device: the stream must belong to the device that is current in this thread
+    int current = -1;
+    MP_CUDA_CHECK(cudaGetDevice(&current));
+    if (state->device != current) {
+      fprintf(stderr, "launch_rmsnorm_ij_j_reverse_static_r32: the stream belongs to device %d, device %d is current\n", state->device, current);
+      return static_cast<int>(MP_STATUS_BAD_ARGUMENT);
+    }
+  }
   const size_t cap_rows = MP_RMSNORM_STATIC_SCRATCH_BYTES / (n * sizeof(A));
   const T* x = static_cast<const T*>(x_);
   const T* gain = static_cast<const T*>(gain_);

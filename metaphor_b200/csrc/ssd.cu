@@ -719,11 +719,22 @@ struct SsdDims { int B, L, H, P, N, G, Q, nc; };
 // group and tile only B * L / 128 * G CTAs would exist, each walking all the group's heads in sequence.
 // The split count (a divisor of the heads per group, at most 32) minimises
 //   waves of resident CTAs x (k-blocks per CTA + a fixed cost per CTA)
-// with three CTAs of these launches resident per SM (68 KB of shared memory each) on the 148 SMs of the part.
-int ssd_head_splits(const SsdDims& d) {
+// with three CTAs of these launches resident per SM (68 KB of shared memory each).
+// SM count of the current device; 148 (a B200) where no device can be queried, so that scratch sizes can be computed
+// on a machine without a GPU.
+int ssd_sm_count() {
+  int device = 0, n = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) {
+    (void)cudaGetLastError();
+    return 148;
+  }
+  return n;
+}
+
+int ssd_head_splits(const SsdDims& d, int sm_count) {
   const int hpg = d.H / d.G;
   const long base = 2L * d.B * d.nc * d.G * (d.Q / 128) / 2 * 1;   // tiles of one split: B * nc * G * (Q / 128)
-  const long slots = 148L * 3;
+  const long slots = static_cast<long>(sm_count > 0 ? sm_count : 148) * 3;
   int best = 1;
   long best_cost = -1;
   for (int sp = 1; sp <= hpg && sp <= 32; ++sp) {
@@ -752,7 +763,7 @@ SsdScratch ssd_carve(void* base, const SsdDims& d, bool reverse) {
   const size_t st = static_cast<size_t>(d.B) * d.H * d.nc * 128 * 128;   // upper bound on dk*dv
   const size_t group_scores = static_cast<size_t>(d.B) * d.nc * d.G * d.Q * d.Q * 2;
   const size_t head_scores = static_cast<size_t>(d.B) * d.nc * d.H * d.Q * d.Q * 2;   // gB / gC keep per-head scores
-  const size_t parts_bytes = static_cast<size_t>(ssd_head_splits(d)) * d.B * d.L * d.G * d.N * 4;
+  const size_t parts_bytes = static_cast<size_t>(ssd_head_splits(d, ssd_sm_count())) * d.B * d.L * d.G * d.N * 4;
   for (int op = 0; op < (reverse ? 4 : 1); ++op) {
     const bool per_head = reverse && op >= 2;   // operators 2, 3 = gC, gB
     s.scores_op[op] = static_cast<__half*>(take(per_head ? head_scores : group_scores));
@@ -854,7 +865,7 @@ void ssd_operator(const SsdDims& d, const Roles& r, const SsdScratch& sc, uint32
     const size_t srows = static_cast<size_t>(d.B) * d.H * d.nc * 128;
     const CUtensorMap mh = g.state_t ? ssd_map(sc.hs, srows, d2, 128) : ssd_map(sc.hs, srows, d2, 64);
     const int units = r.out_head ? d.H : d.G;
-    const int splits = r.out_head ? 1 : ssd_head_splits(d);
+    const int splits = r.out_head ? 1 : ssd_head_splits(d, ssd_sm_count());
     g.head_splits = splits;
     g.part_out = splits > 1 ? sc.parts : nullptr;
     const dim3 grid(splits, d.Q / 128, d.B * d.nc * units);

@@ -778,18 +778,34 @@ static void linear_rev(const std::vector<OpDatum>& a) {
   enable_gradient(x); enable_gradient(A); enable_gradient(b);
   const int key = dkey(z);
   StreamContext ctx = z.context();
+  if (a[3].expr == "ij,j->i") {
+    // y = M v + b with M = x [m,n], v = A [n]: dM = G v^T, dv = M^T G, db = G (one bias entry per output row)
+    gemm(key, 1, z.grad_ptr(), A.data_ptr(), 1.0, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx);
+    gemm(key, 2, x.data_ptr(), z.grad_ptr(), 1.0, A.grad_ptr(), 1.0, c.n, c.m, c.k, ctx);
+    kernels::addition[key](z.grad_ptr(), b.grad_ptr(), b.grad_ptr(), c.m, ctx);
+    return;
+  }
   gemm(key, 1, z.grad_ptr(), A.data_ptr(), 1.0, x.grad_ptr(), 1.0, c.m, c.k, c.n, ctx);   // dx = G A^T
   gemm(key, 2, x.data_ptr(), z.grad_ptr(), 1.0, A.grad_ptr(), 1.0, c.n, c.m, c.k, ctx);   // dA = x^T G
   kernels::reduce_ij_j[key](z.grad_ptr(), b.grad_ptr(), 1.0, c.m, c.k, ctx);              // db = sum_i G
 }
+// "ij,jk->ik" and "i,ij->j": y = x.A + b with b along the output columns.  "ij,j->i" (README.md:81, called as
+// linear(A, x, b, ...)): y = A.x + b with one bias entry per output row, so the first operand is the matrix.
 Tensor linear(Tensor x, Tensor A, Tensor b, const std::string& expr) {
-  if (expr != "ij,jk->ik" && expr != "i,ij->j") panic("linear: expression must be \"ij,jk->ik\" or \"i,ij->j\"");
+  if (expr != "ij,jk->ik" && expr != "i,ij->j" && expr != "ij,j->i")
+    panic("linear: expression must be \"ij,jk->ik\", \"i,ij->j\" or \"ij,j->i\"");
   Graph* g = x.ptr;
   std::vector<size_t> out_sizes;
   const Contraction c = parse_contraction(x, A, expr, out_sizes);
-  if (b.len() != c.k) panic("linear: bias length differs from the output width");
+  const bool mat_vec = expr == "ij,j->i";
+  if (b.len() != (mat_vec ? c.m : c.k)) panic("linear: bias length differs from the output length");
   Tensor z = g->tensor({Class::hid, x.dtype(), out_sizes});
-  kernels::linear[dkey(z)](x.data_ptr(), A.data_ptr(), b.data_ptr(), 1.0, z.data_ptr(), 0.0, c.m, c.n, c.k, z.context());
+  if (mat_vec) {
+    gemm(dkey(z), 0, x.data_ptr(), A.data_ptr(), 1.0, z.data_ptr(), 0.0, c.m, c.n, c.k, z.context());
+    kernels::addition[dkey(z)](z.data_ptr(), b.data_ptr(), z.data_ptr(), c.m, z.context());
+  } else {
+    kernels::linear[dkey(z)](x.data_ptr(), A.data_ptr(), b.data_ptr(), 1.0, z.data_ptr(), 0.0, c.m, c.n, c.k, z.context());
+  }
   if (g->mode == Mode::train)
     attach_op(linear_rev, z, {OpDatum::of(x), OpDatum::of(A), OpDatum::of(b), OpDatum::of(expr), OpDatum::of(z)});
   return z;

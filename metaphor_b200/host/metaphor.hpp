@@ -165,7 +165,7 @@ Tensor inner_product(Tensor x, Tensor y, const std::string& expr);      // "ij,j
                                                                         // batched "bij,bjk->bik" (and the kj / ji forms), "_ij,_jk->_ik" = optional batch
 Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string& expr);
 inline Tensor innerProduct(Tensor x, Tensor y, const std::string& e) { return inner_product(x, y, e); }
-Tensor linear(Tensor x, Tensor A, Tensor b, const std::string& expr);   // "ij,jk->ik", "i,ij->j"
+Tensor linear(Tensor x, Tensor A, Tensor b, const std::string& expr);   // "ij,jk->ik", "i,ij->j"; "ij,j->i" = matrix first: linear(A, x, b, ...)
 Tensor permutate(Tensor x, const std::string& expr);                    // any permutation up to rank 6: "ij->ji", "ijk->kij", ...
 std::vector<size_t> permutation_of(const std::string& expr);            // perm[i] = position of the i-th left index on the right
 Tensor softmax(Tensor x);                                               // over the last axis ("ij|j")

@@ -173,6 +173,34 @@ static void scenario_feed_forward(mp::Stream stream, int timing_iters) {
   G->deinit();
 }
 
+// README.md:78-81: y = A.x ("ij,j->i") and y = A.x + b through linear(A, x, b, "ij,j->i"), forward and reverse.
+static void scenario_matrix_vector(mp::Stream stream) {
+  const size_t m = 48, n = 200;
+  std::vector<float> hA = normal(m * n, 11, 0.1f), hx = normal(n, 12, 1.f), hb = normal(m, 13, 1.f);
+  mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+  mp::Tensor A = G->tensor({mp::Class::wgt, mp::Dtype::r32, {m, n}});
+  mp::Tensor x = G->tensor({mp::Class::inp, mp::Dtype::r32, {n}});
+  mp::Tensor b = G->tensor({mp::Class::wgt, mp::Dtype::r32, {m}});
+  upload(A, hA); upload(x, hx); upload(b, hb);
+  mp::Tensor y0 = mp::ops::innerProduct(A, x, "ij,j->i");
+  mp::Tensor y = mp::ops::linear(A, x, b, "ij,j->i");
+  std::vector<float> r0(m), r1(m);
+  orc_inner_product_f32(hA.data(), hx.data(), nullptr, 1.0, r0.data(), 0.0, m, n, 1, 0, 0);
+  for (size_t i = 0; i < m; ++i) r1[i] = r0[i] + hb[i];
+  CHECK(y0.sizes() == std::vector<size_t>{m});
+  CHECK(rel_err(y0.native(), r0) <= 1e-4);
+  CHECK(rel_err(y.native(), r1) <= 1e-4);
+  y.reverse(mp::ReverseCleanup::keep);
+  // sum loss: G = 1, dA = 1 x^T, dx = A^T 1, db = 1
+  std::vector<float> gA(m * n), gx(n, 0.f), gb(m, 1.f);
+  for (size_t i = 0; i < m; ++i)
+    for (size_t j = 0; j < n; ++j) { gA[i * n + j] = hx[j]; gx[j] += hA[i * n + j]; }
+  CHECK(rel_err(A.native_grad(), gA) <= 1e-4);
+  CHECK(rel_err(x.native_grad(), gx) <= 1e-4);
+  CHECK(rel_err(b.native_grad(), gb) <= 1e-5);
+  G->deinit();
+}
+
 static void scenario_row_ops(mp::Stream stream) {
   const size_t m = 48, n = 1024;
   std::vector<float> hx = normal(m * n, 5, 1.f), hgain = normal(n, 6, 0.02f);
@@ -387,6 +415,7 @@ int main(int argc, char** argv) {
   scenario_subgraphs(s);
   scenario_experimental(s);
   scenario_feed_forward(s, timing_iters);
+  scenario_matrix_vector(s);
   scenario_row_ops(s);
   scenario_rank3(s);
   scenario_derive(s);
