@@ -969,9 +969,9 @@ extern "C" void launch_ssd_scan_r16(const void* x, const void* dt, const void* A
   if (scratch == nullptr) MP_FATAL("ssd_scan: scratch must not be NULL");
   MpStreamState* state = mp_state(ctx);
   cudaStream_t st = mp_stream(ctx);
-  // The forward pass runs the three-phase path by default (measured faster than the chunk walk at 8 x 8192 x 32 and
-  // 8 x 2048 x 24); MP_SSD_WALK_FORWARD selects the walk, which needs no state scratch.
-  if (mp_ssd_walk_supported(d.L, d.H, d.P, d.N, d.G) && getenv("MP_SSD_WALK_FORWARD") != nullptr) {
+  // The chunk walk (no chunk state in global memory) where it applies; MP_SSD_LEGACY_FORWARD selects the three-phase
+  // path (scores, chunk states, scan, output as separate kernels), which also serves head size 128.
+  if (mp_ssd_walk_supported(d.L, d.H, d.P, d.N, d.G) && getenv("MP_SSD_LEGACY_FORWARD") == nullptr) {
     const WalkScratch w = walk_carve(scratch, d, false, 0);
     mp_ssd_walk_cumsum(static_cast<const float*>(dt), static_cast<const float*>(A), w.cum, w.dtt, w.colf_c, nullptr, d.B, d.L, d.H, st);
     mp_ssd_walk(0, static_cast<const __half*>(Cm), static_cast<const __half*>(Bm), static_cast<const __half*>(x), w.cum, w.dtt, w.colf_c,
@@ -1033,17 +1033,24 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
     if (side) {
       MP_CUDA_CHECK(cudaEventRecord(state->aux_join[0], lane1));
       MP_CUDA_CHECK(cudaStreamWaitEvent(st, state->aux_join[0], 0));
+      // gdt / gA need both walks (u, v, states) but not gB / gC: they run beside the group-gradient kernel
+      MP_CUDA_CHECK(cudaEventRecord(state->aux_sub_fork[0], st));
+      MP_CUDA_CHECK(cudaStreamWaitEvent(lane1, state->aux_sub_fork[0], 0));
     }
     mp_ssd_group_grads(gyh, xh, bh, ch, w.hs_causal, w.hs_anti, w.cum, w.dtt, w.colf_c, static_cast<__half*>(gB), static_cast<__half*>(gC),
                        d.B, d.L, d.H, d.G, state->status_dev, st);
     const int wnc = d.L / 128;
-    ssd_boundary_dot_kernel<<<d.B * d.H * wnc, 256, 0, st>>>(w.hs_anti, w.hs_causal, w.pin, wnc, d.N * d.P);
+    ssd_boundary_dot_kernel<<<d.B * d.H * wnc, 256, 0, lane1>>>(w.hs_anti, w.hs_causal, w.pin, wnc, d.N * d.P);
     MP_LAUNCH_CHECK();
-    ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, st>>>(w.u, w.v, w.dtt, static_cast<const float*>(A), w.pin, static_cast<float*>(gdt), w.ga_part,
-                                                      d.B, d.L, d.H, 128, 2);
+    ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, lane1>>>(w.u, w.v, w.dtt, static_cast<const float*>(A), w.pin, static_cast<float*>(gdt), w.ga_part,
+                                                         d.B, d.L, d.H, 128, 2);
     MP_LAUNCH_CHECK();
-    ssd_sum_batches_kernel<<<(d.H + 127) / 128, 128, 0, st>>>(w.ga_part, static_cast<float*>(gA), d.B, d.H);
+    ssd_sum_batches_kernel<<<(d.H + 127) / 128, 128, 0, lane1>>>(w.ga_part, static_cast<float*>(gA), d.B, d.H);
     MP_LAUNCH_CHECK();
+    if (side) {
+      MP_CUDA_CHECK(cudaEventRecord(state->aux_join[1], lane1));
+      MP_CUDA_CHECK(cudaStreamWaitEvent(st, state->aux_join[1], 0));
+    }
     return;
   }
   const SsdScratch sc = ssd_carve(scratch, d, true);

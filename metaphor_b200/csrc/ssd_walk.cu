@@ -31,7 +31,7 @@ namespace {
 constexpr int WQ = 128;                       // steps per chunk
 constexpr int WN = 128;                       // state size (columns of q and k)
 constexpr int WP = 64;                        // head size (columns of v)
-constexpr int W_THREADS = 320;
+constexpr int W_THREADS = 320;        // warps 0-1 control (TMA, MMA), warps 2-9 workers
 constexpr int W_TILE_QK = 2 * WQ * 128;       // [2 k-blocks][128 rows][128 B]
 constexpr int W_TILE_V = WQ * 128;            // [128 rows][128 B]
 constexpr int W_STAGE = 2 * W_TILE_QK + W_TILE_V;
@@ -50,7 +50,7 @@ struct WalkArgs {
   int B, L, H, G, nc;
   const float* cum;        // [B, H, L] inclusive prefix sums of dt*A inside each 128-step chunk
   const float* dtt;        // [B, H, L] dt
-  const float* colf;       // [B, H, L] column factor of every step relative to the far end of its 32-step piece
+  const float* colf;       // [B, H, L] column factor of every step relative to the far end of its 8-step piece
   __half* out;             // [B*L, H*64] or null
   const __half* z;         // dot partner, same indexing as out, or null
   float* dot_out;          // [2][B, H, L] row dots <z, out> from the fp32 accumulators, one array per half of the columns, or null
@@ -85,7 +85,9 @@ __device__ __forceinline__ bool walk_wait(uint64_t* bar, uint32_t parity, uint32
   return mbar_wait_abortable(bar, parity, status, abort);
 }
 
-template <int ANTI>
+// DOT: the row dots <z, out> are wanted (the reverse pass); a template parameter, so that the forward pass does not
+// carry the registers of the dot partner's rows.
+template <int ANTI, bool DOT>
 __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v,
@@ -100,6 +102,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
   volatile int* abort = reinterpret_cast<volatile int*>(smem + W_OFF_TAIL + 116);
   float* s_cum = reinterpret_cast<float*>(smem + W_OFF_TAIL + 128);   // [128]
   float* s_colf = s_cum + WQ;                                         // [128]
+  float* s_dt = s_colf + WQ;                                          // [128]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x % g.H, b = blockIdx.x / g.H;
   const int grp = h / (g.H / g.G);
@@ -119,6 +122,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
   __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
+
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -225,181 +229,147 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(0u, 0u, 0u, 0u);
     }
-    bool ok = true;
-
-    // values of the walk's scalars: chunk in hand (cur) and the one after it (nxt)
+    // scalars of the walk: chunk in hand (cur), the one after it (nxt), and one more in flight (pre), so that
+    // their loads are never waited for
     float cum_cur = 0.f, dt_cur = 0.f, last_cur = 0.f;
     float cum_nxt = cum_g[c_first * WQ + r], dt_nxt = dt_g[c_first * WQ + r], colf_nxt = colf_g[c_first * WQ + r];
     float last_nxt = 0.f;
-
-    // publish the scalars of chunk kk (held in *_nxt) to shared memory and fetch those of the chunk after it
-    auto publish = [&](int kk) -> bool {
-      if (ch == 0) {
-        s_cum[r] = cum_nxt; s_colf[r] = colf_nxt;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bars + B_SCAL);
-      }
-      if (!walk_wait(bars + B_SCAL, kk & 1, g.status, abort)) return false;
-      last_nxt = s_cum[WQ - 1];
-      return true;
-    };
-    // w o v of the chunk whose scalars are in *_nxt
-    auto scale_values = [&](int kk) -> bool {
-      const int s = kk & 1;
-      if (!walk_wait(bars + B_FULL0 + s, (kk >> 1) & 1, g.status, abort)) return false;
-      const float wt = ANTI ? w_exp(cum_nxt) : w_exp(last_nxt - cum_nxt) * dt_nxt;
-      const __half2 wt2 = __float2half2_rn(wt);
-      const unsigned char* src = smem + s * W_STAGE + 2 * W_TILE_QK + r * 128;
-      unsigned char* dst = sVs + r * 128;
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) {
-        const int off = ((ch * 4 + q4) ^ (r & 7)) << 4;
-        uint4 v = *reinterpret_cast<const uint4*>(src + off);
-        __half2* h2 = reinterpret_cast<__half2*>(&v);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) h2[e] = __hmul2(h2[e], wt2);
-        *reinterpret_cast<uint4*>(dst + off) = v;
-      }
-      warp_arrive(bars + B_VSREADY, lane);
-      return true;
-    };
-    // P = G o F of chunk index cc (k-th of the walk: kk), scalars in *_nxt
-    auto transform = [&](int kk, int cc) -> bool {
-      if (!walk_wait(bars + B_GFULL, kk & 1, g.status, abort)) return false;
-      tcgen05_fence_after_sync();
-#pragma unroll 1
-      for (int pp = 0; pp < 2; ++pp) {
-        const int pc = ch * 2 + pp;              // 32-column piece of the chunk
-        const int j0 = pc * 32;
-        unsigned char* prow = sP + ch * (WQ * 128) + r * 128;
-        const bool zero = ANTI ? (pc < quarter) : (pc > quarter);   // warp-uniform: the whole piece is masked
-        if (zero) {
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(prow + (((pp * 4 + q4) ^ (r & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
-          continue;
-        }
-        uint32_t v[32];
-        tmem_ld_32x32(tl + TC_G + j0, v);
-        const int ref = ANTI ? j0 : j0 + 31;
-        const float rarg = ANTI ? s_cum[ref] - cum_nxt : cum_nxt - s_cum[ref];   // <= 0 off the diagonal piece
-        const bool diag = pc == quarter;
-        const bool direct = diag && rarg > 40.f;    // factorised form would overflow: rare, take the exact exponent per element
-        const float rowf = w_exp(direct ? 0.f : rarg);
-        tmem_ld_wait();
-        float f[32];
-        if (__any_sync(0xffffffffu, direct)) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int j = j0 + e;
-            const float cj = cum_g[cc * WQ + j];
-            f[e] = direct ? (ANTI ? w_exp(cj - cum_nxt) : w_exp(cum_nxt - cj) * dt_g[cc * WQ + j]) : s_colf[j] * rowf;
-          }
-        } else {
-#pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) {
-            const float4 cf = *reinterpret_cast<const float4*>(s_colf + j0 + e4 * 4);
-            f[e4 * 4] = cf.x * rowf; f[e4 * 4 + 1] = cf.y * rowf; f[e4 * 4 + 2] = cf.z * rowf; f[e4 * 4 + 3] = cf.w * rowf;
-          }
-        }
-        if (diag) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (ANTI ? (e < lane) : (e > lane)) f[e] = 0.f;
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 o;
-          uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i0 = q4 * 8 + 2 * e;
-            const __half2 hv = __floats2half2_rn(__uint_as_float(v[i0]) * f[i0], __uint_as_float(v[i0 + 1]) * f[i0 + 1]);
-            ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
-          }
-          *reinterpret_cast<uint4*>(prow + (((pp * 4 + q4) ^ (r & 7)) << 4)) = o;
-        }
-      }
-      warp_arrive(bars + B_PREADY, lane);
-      return true;
-    };
-    // scalars two chunks ahead, so that their loads are never waited for
     float cum_pre = 0.f, dt_pre = 0.f, colf_pre = 0.f;
-    auto prefetch = [&](int kk) {   // scalars of the walk's kk-th chunk into *_pre (kk < nc)
-      const int cn = ANTI ? nc - 1 - kk : kk;
-      cum_pre = cum_g[cn * WQ + r]; dt_pre = dt_g[cn * WQ + r]; colf_pre = colf_g[cn * WQ + r];
-    };
-    if (nc > 1) prefetch(1);
+    if (nc > 1) {
+      const int c1 = ANTI ? nc - 2 : 1;
+      cum_pre = cum_g[c1 * WQ + r]; dt_pre = dt_g[c1 * WQ + r]; colf_pre = colf_g[c1 * WQ + r];
+    }
 
-    // ---- prologue: chunk 0 up to its P tile ----------------------------------------
-    ok = publish(0) && scale_values(0) && transform(0, c_first);
-    for (int k = 0; ok && k < nc; ++k) {
-      const int c = ANTI ? nc - 1 - k : k;
-      const uint32_t par = k & 1;
+    // Iteration k finishes chunk k and prepares chunk k+1; k = -1 is the lead-in that only prepares chunk 0.
+#pragma unroll 1
+    for (int k = -1; k < nc; ++k) {
+      const bool cur = k >= 0;
       const bool more = k + 1 < nc;
-      cum_cur = cum_nxt; dt_cur = dt_nxt; last_cur = last_nxt;
-      if (more) {
-        cum_nxt = cum_pre; dt_nxt = dt_pre; colf_nxt = colf_pre;
-        if (k + 2 < nc) prefetch(k + 2);
-      }
-      // Yd(k) has consumed the P tile, and every warp is past the shared scalars of chunk k
+      const int c = ANTI ? nc - 1 - k : k;                 // chunk in hand (meaningless in the lead-in)
+      const uint32_t par = static_cast<uint32_t>(k) & 1u;
+      const uint32_t parn = static_cast<uint32_t>(k + 1) & 1u;
       uint4 zc[4];
-      if (g.z != nullptr) {
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const size_t zrow = static_cast<size_t>(b) * g.L + c * WQ + quarter * 32 + it * 8 + (lane >> 2);
-          zc[it] = *reinterpret_cast<const uint4*>(g.z + zrow * pitch + h * WP + ch * 32 + (lane & 3) * 8);
-        }
-      }
-      if (!walk_wait(bars + B_YFULL, par, g.status, abort)) { ok = false; break; }
-      if (more) {
-        if (!publish(k + 1)) { ok = false; break; }
-        if (!transform(k + 1, ANTI ? c - 1 : c + 1)) { ok = false; break; }
-      }
-      // ---- H' = D H + S ---------------------------------------------------------------
-      if (!walk_wait(bars + B_SFULL, par, g.status, abort)) { ok = false; break; }
-      tcgen05_fence_after_sync();
-      if (more) {
-        uint32_t sv[32];
-        tmem_ld_32x32(tl + TC_S + ch * 32, sv);
-        const float D = w_exp(last_cur);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) state[e] = D * state[e] + __uint_as_float(sv[e]);
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 pk;
-          uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const __half2 hv = __floats2half2_rn(state[q4 * 8 + 2 * e], state[q4 * 8 + 2 * e + 1]);
-            ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+      if (cur) {
+        cum_cur = cum_nxt; dt_cur = dt_nxt; last_cur = last_nxt;
+        if (more) {
+          cum_nxt = cum_pre; dt_nxt = dt_pre; colf_nxt = colf_pre;
+          if (k + 2 < nc) {
+            const int c2 = ANTI ? nc - 3 - k : k + 2;
+            cum_pre = cum_g[c2 * WQ + r]; dt_pre = dt_g[c2 * WQ + r]; colf_pre = colf_g[c2 * WQ + r];
           }
-          *reinterpret_cast<uint4*>(sH + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4)) = pk;
         }
-        warp_arrive(bars + B_HREADY, lane);
+        // Yd(k) has consumed the P tile, and every warp is past the shared scalars of chunk k
+        if (!walk_wait(bars + B_YFULL, par, g.status, abort)) break;
       }
-      // ---- out = r o (Yd + f o Yo) of chunk k -------------------------------------------
-      // staging = this warp's own positions of the scaled-value tile (S(k), its last reader, has completed, and the
-      // warp refills exactly these positions for chunk k+1 right after the epilogue)
-      unsigned char* stg = sVs;
-      uint4 zv[4];
-      if (g.z != nullptr) {
-        // the dot partner's rows arrive with whole-row loads (issued at the top of the iteration) and change
-        // hands through the warp's own positions of the staging tile
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int lr = quarter * 32 + it * 8 + (lane >> 2), cc = ch * 4 + (lane & 3);
-          *reinterpret_cast<uint4*>(stg + lr * 128 + ((cc ^ (lr & 7)) << 4)) = zc[it];
+      if (more) {
+        // ---- scalars of chunk k+1 into shared memory ------------------------------------------
+        if (ch == 0) {
+          s_cum[r] = cum_nxt; s_colf[r] = colf_nxt; s_dt[r] = dt_nxt;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + B_SCAL);
         }
-        __syncwarp();
+        if (!walk_wait(bars + B_SCAL, parn, g.status, abort)) break;
+        last_nxt = s_cum[WQ - 1];
+        // ---- P = G o F of chunk k+1 ----------------------------------------------------------------
+        if (!walk_wait(bars + B_GFULL, parn, g.status, abort)) break;
+        tcgen05_fence_after_sync();
+#pragma unroll 1
+        for (int pp = 0; pp < 2; ++pp) {
+          const int pc = ch * 2 + pp;              // 32-column piece of the chunk
+          const int j0 = pc * 32;
+          unsigned char* prow = sP + ch * (WQ * 128) + r * 128;
+          const bool zero = ANTI ? (pc < quarter) : (pc > quarter);   // warp-uniform: the whole piece is masked
+          if (zero) {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) zv[q4] = *reinterpret_cast<const uint4*>(stg + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4));
-        __syncwarp();
+            for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(prow + (((pp * 4 + q4) ^ (r & 7)) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+            continue;
+          }
+          uint32_t v[32];
+          tmem_ld_32x32(tl + TC_G + j0, v);
+          // F = row factor x column factor, both relative to the far end of the 8-column sub-piece, so that neither
+          // leaves the fp32 range unless eight steps decay by more than e^-80; there (rare, and only on the
+          // diagonal sub-piece) the exponent is taken per element.
+          const bool diag = pc == quarter;
+          tmem_ld_wait();
+#pragma unroll
+          for (int sp = 0; sp < 4; ++sp) {
+            const int jb = j0 + sp * 8;
+            const float cref = s_cum[ANTI ? jb : jb + 7];
+            const float rarg = ANTI ? cref - cum_nxt : cum_nxt - cref;   // <= 0 off the diagonal
+            const bool direct = rarg > 80.f;
+            const float rowf = w_exp(direct ? 0.f : rarg);
+            const float4 c0 = *reinterpret_cast<const float4*>(s_colf + jb);
+            const float4 c1 = *reinterpret_cast<const float4*>(s_colf + jb + 4);
+            float f[8] = {c0.x * rowf, c0.y * rowf, c0.z * rowf, c0.w * rowf, c1.x * rowf, c1.y * rowf, c1.z * rowf, c1.w * rowf};
+            if (direct) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const float cj = s_cum[jb + e];
+                f[e] = ANTI ? w_exp(fminf(cj - cum_nxt, 0.f)) : w_exp(fminf(cum_nxt - cj, 0.f)) * s_dt[jb + e];
+              }
+            }
+            if (diag) {
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                if (ANTI ? (sp * 8 + e < lane) : (sp * 8 + e > lane)) f[e] = 0.f;
+            }
+            uint4 o;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __half2 hv = __floats2half2_rn(__uint_as_float(v[sp * 8 + 2 * e]) * f[2 * e], __uint_as_float(v[sp * 8 + 2 * e + 1]) * f[2 * e + 1]);
+              ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            *reinterpret_cast<uint4*>(prow + (((pp * 4 + sp) ^ (r & 7)) << 4)) = o;
+          }
+        }
+        warp_arrive(bars + B_PREADY, lane);
       }
-      tcgen05_fence_after_sync();
-      {
+      if (cur) {
+        if (DOT) {    // the dot partner's rows of chunk k, whole 64-byte row pieces per load
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const size_t zrow = static_cast<size_t>(b) * g.L + c * WQ + quarter * 32 + it * 8 + (lane >> 2);
+            zc[it] = *reinterpret_cast<const uint4*>(g.z + zrow * pitch + h * WP + ch * 32 + (lane & 3) * 8);
+          }
+        }
+        // ---- H' = D H + S ---------------------------------------------------------------
+        if (!walk_wait(bars + B_SFULL, par, g.status, abort)) break;
+        tcgen05_fence_after_sync();
+        if (more) {
+          uint32_t sv[32];
+          tmem_ld_32x32(tl + TC_S + ch * 32, sv);
+          const float D = w_exp(last_cur);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) state[e] = D * state[e] + __uint_as_float(sv[e]);
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            uint4 pk;
+            uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const __half2 hv = __floats2half2_rn(state[q4 * 8 + 2 * e], state[q4 * 8 + 2 * e + 1]);
+              ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+            }
+            *reinterpret_cast<uint4*>(sH + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4)) = pk;
+          }
+          warp_arrive(bars + B_HREADY, lane);
+        }
+        // ---- out = r o (Yd + f o Yo) of chunk k -------------------------------------------
+        // staging = this warp's own positions of the scaled-value tile (S(k), its last reader, has completed, and the
+        // warp refills exactly these positions for chunk k+1 right after the epilogue)
+        unsigned char* stg = sVs;
+        if (DOT) {
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int lr = quarter * 32 + it * 8 + (lane >> 2), cc = ch * 4 + (lane & 3);
+            *reinterpret_cast<uint4*>(stg + lr * 128 + ((cc ^ (lr & 7)) << 4)) = zc[it];
+          }
+          __syncwarp();
+        }
         uint32_t yd[32], yo[32];
-        const uint32_t ty = tl + TC_Y + (k & 1) * 128 + ch * 32;
+        const uint32_t ty = tl + TC_Y + par * 128 + ch * 32;
         tmem_ld_32x32(ty, yd);
         if (k > 0) tmem_ld_32x32(ty + 64, yo);
         const float fo = k > 0 ? (ANTI ? w_exp(last_cur - cum_cur) : w_exp(cum_cur)) : 0.f;
@@ -412,6 +382,22 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
         float o[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) o[e] = ro * (__uint_as_float(yd[e]) + fo * __uint_as_float(yo[e]));
+        tcgen05_fence_before_sync();
+        if (DOT) {   // this thread's row of z comes back from the staging positions before the output overwrites them
+          float dot = 0.f;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint4 zq = *reinterpret_cast<const uint4*>(stg + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4));
+            const __half2* z2 = reinterpret_cast<const __half2*>(&zq);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 zf = __half22float2(z2[e]);
+              dot += zf.x * o[q4 * 8 + 2 * e] + zf.y * o[q4 * 8 + 2 * e + 1];
+            }
+          }
+          g.dot_out[static_cast<size_t>(ch) * g.B * g.H * g.L + bh * g.L + c * WQ + r] = dot;
+          __syncwarp();
+        }
         if (g.out != nullptr) {
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
@@ -435,23 +421,27 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
           }
           __syncwarp();
         }
-        if (g.z != nullptr) {
-          float dot = 0.f;
-#pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const __half2* z2 = reinterpret_cast<const __half2*>(&zv[q4]);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 zf = __half22float2(z2[e]);
-              dot += zf.x * o[q4 * 8 + 2 * e] + zf.y * o[q4 * 8 + 2 * e + 1];
-            }
-          }
-          g.dot_out[static_cast<size_t>(ch) * g.B * g.H * g.L + bh * g.L + c * WQ + r] = dot;
-        }
       }
-      if (more && !scale_values(k + 1)) { ok = false; break; }
+      if (more) {
+        // ---- w o v of chunk k+1 -> operand of its state update ------------------------------------
+        const int s1 = (k + 1) & 1;
+        if (!walk_wait(bars + B_FULL0 + s1, static_cast<uint32_t>((k + 1) >> 1) & 1u, g.status, abort)) break;
+        const float wt = ANTI ? w_exp(cum_nxt) : w_exp(last_nxt - cum_nxt) * dt_nxt;
+        const __half2 wt2 = __float2half2_rn(wt);
+        const unsigned char* src = smem + s1 * W_STAGE + 2 * W_TILE_QK + r * 128;
+        unsigned char* dst = sVs + r * 128;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const int off = ((ch * 4 + q4) ^ (r & 7)) << 4;
+          uint4 v = *reinterpret_cast<const uint4*>(src + off);
+          __half2* h2 = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) h2[e] = __hmul2(h2[e], wt2);
+          *reinterpret_cast<uint4*>(dst + off) = v;
+        }
+        warp_arrive(bars + B_VSREADY, lane);
+      }
     }
-    (void)ok;
   }
   tcgen05_fence_before_sync();
   __syncthreads();
@@ -500,6 +490,7 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_group_grads_kernel(const __g
   volatile int* abort = reinterpret_cast<volatile int*>(smem + GG_OFF_TAIL + 116);
   float* s_cum = reinterpret_cast<float*>(smem + GG_OFF_TAIL + 128);   // [2][128]
   float* s_colf = s_cum + 2 * WQ;                                      // [2][128]
+  float* s_dt = s_colf + 2 * WQ;                                       // [2][128]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hpg = g.H / g.G;
   const int grp = blockIdx.x % g.G;
@@ -630,8 +621,9 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_group_grads_kernel(const __g
       const float cum_r = cum_n, dt_r = dt_n;
       float* cumb = s_cum + s * WQ;
       float* colfb = s_colf + s * WQ;
+      float* dtb = s_dt + s * WQ;
       // every warp arrives: the phase also tells the writers of the other buffer that all warps are done with it
-      if (ch == 0) { cumb[r] = cum_n; colfb[r] = colf_n; }
+      if (ch == 0) { cumb[r] = cum_n; colfb[r] = colf_n; dtb[r] = dt_n; }
       __syncwarp();
       if (lane == 0) mbar_arrive(bars + GB_SCAL);
       cum_n = cum_p; dt_n = dt_p; colf_n = colf_p;
@@ -648,28 +640,24 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_group_grads_kernel(const __g
         if (pc > quarter) continue;                 // above the diagonal for every row of the warp
         uint32_t v[32];
         tmem_ld_32x32(tl + GT_SC + s * 128 + j0, v);
-        const float rarg = cum_r - cumb[j0 + 31];
         const bool diag = pc == quarter;
-        const bool direct = diag && rarg > 40.f;
-        const float rowf = w_exp(direct ? 0.f : rarg);
         tmem_ld_wait();
-        if (__any_sync(0xffffffffu, direct)) {
-          const float* cg = scal_ptr(g.cum, hi) - r;
-          const float* dg = scal_ptr(g.dtt, hi) - r;
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const float f = direct ? w_exp(cum_r - cg[j0 + e]) * dg[j0 + e] : colfb[j0 + e] * rowf;
-            if (!diag || e <= lane) acc[pp * 32 + e] += __uint_as_float(v[e]) * f;
+        for (int sp = 0; sp < 4; ++sp) {      // factors relative to the last column of each 8-column sub-piece (see the walk kernel)
+          const int jb = j0 + sp * 8;
+          const float rarg = cum_r - cumb[jb + 7];
+          const bool direct = rarg > 80.f;
+          const float rowf = w_exp(direct ? 0.f : rarg);
+          const float4 c0 = *reinterpret_cast<const float4*>(colfb + jb);
+          const float4 c1 = *reinterpret_cast<const float4*>(colfb + jb + 4);
+          float f[8] = {c0.x * rowf, c0.y * rowf, c0.z * rowf, c0.w * rowf, c1.x * rowf, c1.y * rowf, c1.z * rowf, c1.w * rowf};
+          if (direct) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f[e] = w_exp(fminf(cum_r - cumb[jb + e], 0.f)) * dtb[jb + e];
           }
-        } else {
 #pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) {
-            const float4 cf = *reinterpret_cast<const float4*>(colfb + j0 + e4 * 4);
-            const float f4[4] = {cf.x * rowf, cf.y * rowf, cf.z * rowf, cf.w * rowf};
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (!diag || e4 * 4 + e <= lane) acc[pp * 32 + e4 * 4 + e] += __uint_as_float(v[e4 * 4 + e]) * f4[e];
-          }
+          for (int e = 0; e < 8; ++e)
+            if (!diag || sp * 8 + e <= lane) acc[pp * 32 + sp * 8 + e] += __uint_as_float(v[sp * 8 + e]) * f[e];
         }
       }
       // ---- row factors into the operand tiles, in place (the score MMA has read them) ----
@@ -742,8 +730,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_group_grads_kernel(const __g
 }
 
 // dt*A prefix sums inside every 128-step chunk, dt, and the column factors of both walk directions, all in
-// [B, H, L] order.  One CTA per (b, h, chunk).  Column factor of step t relative to the far end of its 32-step
-// piece: causal exp(cum[t | 31] - cum[t]) dt[t], anti-causal exp(cum[t] - cum[t & ~31]); both are at most one (dt).
+// [B, H, L] order.  One CTA per (b, h, chunk).  Column factor of step t relative to the far end of its 8-step
+// piece: causal exp(cum[t | 7] - cum[t]) dt[t], anti-causal exp(cum[t] - cum[t & ~7]); both are at most one (dt).
 __global__ void __launch_bounds__(WQ) ssd_walk_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A, float* __restrict__ cum,
                                                              float* __restrict__ dtt, float* __restrict__ colf_c, float* __restrict__ colf_a,
                                                              int L, int H) {
@@ -763,7 +751,7 @@ __global__ void __launch_bounds__(WQ) ssd_walk_cumsum_kernel(const float* __rest
   float base = 0.f;
   for (int w = 0; w < (t >> 5); ++w) base += warp_tot[w];
   const float cv = v + base;
-  const float c_hi = __shfl_sync(0xffffffffu, cv, 31), c_lo = __shfl_sync(0xffffffffu, cv, 0);
+  const float c_hi = __shfl_sync(0xffffffffu, cv, (t & 31) | 7), c_lo = __shfl_sync(0xffffffffu, cv, (t & 31) & ~7);
   const size_t o = (static_cast<size_t>(b) * H + h) * L + c * WQ + t;
   cum[o] = cv;
   dtt[o] = d;
@@ -825,12 +813,16 @@ void mp_ssd_walk(int anti, const __half* q, const __half* k, const __half* v, co
   const CUtensorMap mq = walk_map(q, rows, static_cast<size_t>(G) * WN), mk = walk_map(k, rows, static_cast<size_t>(G) * WN);
   const CUtensorMap mv = walk_map(v, rows, static_cast<size_t>(H) * WP);
   const CUtensorMap mh = hs_out != nullptr ? walk_map(hs_out, static_cast<size_t>(B) * H * g.nc * WN, WP) : mv;
+  auto launch = [&](auto kernel) {
+    MP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES));
+    kernel<<<B * H, W_THREADS, W_SMEM_BYTES, st>>>(mq, mk, mv, mh, g);
+  };
+  const bool dot = z != nullptr && dot_out != nullptr;
+  if (!dot) { g.z = nullptr; g.dot_out = nullptr; }
   if (anti) {
-    MP_CUDA_CHECK(cudaFuncSetAttribute(ssd_walk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES));
-    ssd_walk_kernel<1><<<B * H, W_THREADS, W_SMEM_BYTES, st>>>(mq, mk, mv, mh, g);
+    if (dot) launch(ssd_walk_kernel<1, true>); else launch(ssd_walk_kernel<1, false>);
   } else {
-    MP_CUDA_CHECK(cudaFuncSetAttribute(ssd_walk_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES));
-    ssd_walk_kernel<0><<<B * H, W_THREADS, W_SMEM_BYTES, st>>>(mq, mk, mv, mh, g);
+    if (dot) launch(ssd_walk_kernel<0, true>); else launch(ssd_walk_kernel<0, false>);
   }
   MP_LAUNCH_CHECK();
 }
