@@ -723,7 +723,7 @@ def run_lm(args):
             out["cpu_baseline"] = lm_cpu_baseline()
             out["per_config"] = run_per_config(args, mp)
         else:
-            out["per_config"] = "reported at N = 1 only (rank 0 of a single-GPU run)"
+            out["per_config"] = "skipped (--no-per-config)" if world == 1 else "reported at N = 1 only (rank 0 of a single-GPU run)"
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
