@@ -475,9 +475,22 @@ def lm_workload_text(n_layer, batch):
             % (n_layer, batch))
 
 
-# launcher -> DRAM bytes per call from ncu (dram__bytes_read.sum + dram__bytes_write.sum), with the commit
-# the capture was taken at; a launcher that is not listed reports traffic null
-LM_NCU_TRAFFIC = {}
+# launcher -> DRAM bytes of one call from ncu (dram__bytes_read.sum + dram__bytes_write.sum over the launcher's tensor-core
+# kernels: both chunk walks and the group-gradient kernel; the prefix-sum and scalar-gradient kernels were not captured),
+# taken at batch 4 x seqlen 4096 x 32 heads (profiles/ssd_walk_and_group_gradients_b4_l4096_h32.md).  Every CTA walks one
+# (batch, head) sequence, so traffic grows in proportion to batch x seqlen x heads and is scaled to the step's shape.
+# A launcher that is not listed reports traffic null.
+LM_NCU_TRAFFIC = {
+    "ssd_scan_reverse_r16": {"bytes": 247.2e6 + 194.5e6 + 286.7e6, "units": 4 * 4096 * 32},
+    "ssd_scan_r16": {"bytes": 81.9e6 + 29.9e6, "units": 4 * 4096 * 32},
+}
+
+
+def lm_ncu_traffic(label, cfg, batch, seqlen):
+    rec = LM_NCU_TRAFFIC.get(label)
+    if rec is None:
+        return None
+    return int(rec["bytes"] * (batch * seqlen * cfg.heads) / rec["units"])
 
 
 def lm_launcher_work(label, cfg, batch, seqlen):
@@ -670,7 +683,7 @@ def run_lm(args):
         work, bound = lm_launcher_work(dom, cfg, batch, seqlen)
         per_call_ms = dom_rec["ms"] / dom_rec["calls"]
         roofline = {"kernel": dom, "calls_per_step": dom_rec["calls"], "share_of_step": round(dom_rec["ms"] / total_prof, 4),
-                    "us_per_call": round(per_call_ms * 1e3, 1), "traffic": LM_NCU_TRAFFIC.get(dom),
+                    "us_per_call": round(per_call_ms * 1e3, 1), "traffic": lm_ncu_traffic(dom, cfg, batch, seqlen),
                     "timing": "CUDA events around every call of the launcher in one step issued without graph replay, same process, right after the timed region"}
         if work is not None:
             rr = rate_record(per_call_ms, work, bound, tensor_peak=sustained)
