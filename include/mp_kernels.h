@@ -191,6 +191,15 @@ MP_DECL3(ssd_gate, const void* y, const void* x, const void* D, const void* z, l
 /* gy = gu*silu(z); gz = gu*(y + D x)*silu'(z) (pitched); gD[h] += sum gy*x (acc, may be NULL).
  * The skip's share of gx is added afterwards with launch_head_scale_accumulate. */
 MP_DECL3(ssd_gate_reverse, const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gu, void* gy, void* gz, len_t gz_pitch, void* gD, len_t rows, len_t heads, len_t headdim, StreamContext stream)
+/* Gate and RMSNorm in one pass: with u = (y + D[h]*x) * silu(z) (never written),
+ *   out = u * rstd * gain, rstd[r] = 1/sqrt(mean_j u[r,j]^2 + eps)   (rstd: acc [rows], may be NULL) */
+MP_DECL3(ssd_gate_rmsnorm, const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gain, double eps, void* out, void* rstd, len_t rows, len_t heads, len_t headdim, StreamContext stream)
+/* Reverse of launch_ssd_gate_rmsnorm: u is recomputed from y, x, z; gout is d loss / d out.
+ *   gy = gu*silu(z); gz = gu*(y + D x)*silu'(z) (pitched) with gu the RMSNorm reverse of gout;
+ *   gD[h] += sum gy*x (acc, may be NULL); ggain = alpha*ggain + sum_r gout*u*rstd (T [heads*headdim], may be NULL).
+ * scratch: caller-owned, mpSsdGateRmsnormReverseScratchBytes(rows, heads, headdim, ctx) bytes. */
+MP_DECL3(ssd_gate_rmsnorm_reverse, const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gain, const void* rstd, const void* gout, void* gy, void* gz, len_t gz_pitch, void* gD, void* ggain, double alpha, void* scratch, len_t rows, len_t heads, len_t headdim, StreamContext stream)
+MP_EXTERN_C len_t mpSsdGateRmsnormReverseScratchBytes(len_t rows, len_t heads, len_t headdim, StreamContext stream);
 /* gx[r,h,:] += D[h]*gy[r,h,:] */
 MP_DECL3(head_scale_accumulate, const void* D, const void* gy, void* gx, len_t rows, len_t heads, len_t headdim, StreamContext stream)
 /* Cross-entropy of logits [m, n] against int32 targets, loss and gradient in one pass:

@@ -72,6 +72,8 @@ LAUNCHERS = {
     "softplus_bias_reverse": [P, L, P, P, P, L, P, L, L, CTX],
     "ssd_gate": [P, P, P, P, L, P, L, L, L, CTX],
     "ssd_gate_reverse": [P, P, P, P, L, P, P, P, L, P, L, L, L, CTX],
+    "ssd_gate_rmsnorm": [P, P, P, P, L, P, D, P, P, L, L, L, CTX],
+    "ssd_gate_rmsnorm_reverse": [P, P, P, P, L, P, P, P, P, P, L, P, P, D, P, L, L, L, CTX],
     "head_scale_accumulate": [P, P, P, L, L, L, CTX],
     "cross_entropy": [P, P, D, P, P, L, L, CTX],
     "neg_exp": [P, P, L, CTX],
@@ -116,6 +118,7 @@ UTILS = {
     "mpGraphDestroy": (None, [P]),
     "mpGraphKernelNodes": (L, [P]),
     "mpRmsnormReverseScratchBytes": (L, [L, L, CTX]),
+    "mpSsdGateRmsnormReverseScratchBytes": (L, [L, L, L, CTX]),
     "mpSsdScanScratchBytes": (L, [L, L, L, L, L, L, L, U32]),
     "mpSsdScanGenericScratchBytes": (L, [U32, L, L, L, L, L, L, U32]),
     "launch_rmsnorm_ij_j_reverse_static_r32": (C.c_int, [P, P, P, P, D, P, P, D, L, L, CTX]),

@@ -666,6 +666,410 @@ __global__ void __launch_bounds__(256) ssd_gate_reverse_kernel(const T* __restri
     for (int h = threadIdx.x; h < H; h += blockDim.x) atomicAdd(gD + h, bins[h]);
 }
 
+// ---------------------------------------------------------------------------
+// Gate + RMSNorm in one pass (the block's "gated norm"): with u = (y + D[h] x) * silu(z),
+//   out = u * rstd * gain,  rstd = 1 / sqrt(mean_j u_j^2 + eps)
+// u is never written: the reverse recomputes it from y, x and z.  One warp per row; with NP > 0 the row's
+// packs stay in registers between the reduction and the output pass (NP packs of V elements per lane, row
+// width = 32 * NP * V), with NP = 0 the second pass reads the row again (any width, V = 1 for unaligned rows).
+// ---------------------------------------------------------------------------
+constexpr int GN_THREADS = 256;   // 8 rows in flight per CTA
+
+template <typename PackT>
+__device__ __forceinline__ void gn_opaque(PackT& v) {
+  if constexpr (sizeof(PackT) % 4 == 0) {
+    uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int i = 0; i < static_cast<int>(sizeof(PackT) / 4); ++i) asm volatile("" : "+r"(w[i]));
+  }
+}
+
+template <typename T, int V>
+__device__ __forceinline__ void gn_load3(const T* __restrict__ y, const T* __restrict__ x, const T* __restrict__ z, size_t off, size_t zoff,
+                                         typename Acc<T>::type* yv, typename Acc<T>::type* xv, typename Acc<T>::type* zv) {
+  load_vec<T, V>(y + off, yv);
+  load_vec<T, V>(x + off, xv);
+  load_vec<T, V>(z + zoff, zv);
+}
+
+template <typename T, int V, int NP>
+__global__ void __launch_bounds__(GN_THREADS) gate_rmsnorm_kernel(const T* __restrict__ y, const T* __restrict__ x,
+                                                                  const typename Acc<T>::type* __restrict__ D, const T* __restrict__ z,
+                                                                  size_t zp, const T* __restrict__ gain, typename Acc<T>::type eps,
+                                                                  T* __restrict__ out, typename Acc<T>::type* __restrict__ rstd,
+                                                                  size_t rows, int H, int P) {
+  using A = typename Acc<T>::type;
+  const int lane = threadIdx.x & 31;
+  const size_t width = static_cast<size_t>(H) * P;
+  const int packs = NP > 0 ? NP : static_cast<int>((width / V + 31) / 32);
+  const size_t warps = static_cast<size_t>(gridDim.x) * (GN_THREADS / 32);
+  for (size_t r = blockIdx.x * static_cast<size_t>(GN_THREADS / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
+    A u[NP > 0 ? NP : 1][V];
+    A sum = A(0);
+#pragma unroll
+    for (int p = 0; p < packs; ++p) {
+      const size_t c = (static_cast<size_t>(p) * 32 + lane) * V;
+      if (NP > 0 || c < width) {
+        A yv[V], xv[V], zv[V];
+        gn_load3<T, V>(y, x, z, r * width + c, r * zp + c, yv, xv, zv);
+        const A d = D != nullptr ? D[c / P] : A(0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const A t = (yv[e] + d * xv[e]) * zv[e] * sigmoid_a(zv[e]);
+          if (NP > 0) u[NP > 0 ? p : 0][e] = t;
+          sum += t * t;
+        }
+      }
+    }
+    sum = warp_reduce<SumOp>(sum);
+    const A rs = A(1) / sqrt(sum / static_cast<A>(width) + eps);
+    if (lane == 0 && rstd != nullptr) rstd[r] = rs;
+#pragma unroll
+    for (int p = 0; p < packs; ++p) {
+      const size_t c = (static_cast<size_t>(p) * 32 + lane) * V;
+      if (NP > 0 || c < width) {
+        A gv[V], o[V];
+        load_vec<T, V>(gain + c, gv);
+        if (NP > 0) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) o[e] = u[NP > 0 ? p : 0][e] * rs * gv[e];
+        } else {
+          A yv[V], xv[V], zv[V];
+          gn_load3<T, V>(y, x, z, r * width + c, r * zp + c, yv, xv, zv);
+          const A d = D != nullptr ? D[c / P] : A(0);
+#pragma unroll
+          for (int e = 0; e < V; ++e) o[e] = (yv[e] + d * xv[e]) * zv[e] * sigmoid_a(zv[e]) * rs * gv[e];
+        }
+        store_vec<T, V>(out + r * width + c, o);
+      }
+    }
+  }
+}
+
+// Reverse of the gated norm.  Per row, with u as above, xh = u * rstd, gxh = gout * gain, m = mean_j gxh_j xh_j:
+//   gu = rstd * (gxh - xh * m);  gy = gu * silu(z);  gz = gu * (y + D x) * silu'(z);  gD[h] += sum gy * x
+//   ggain_j = sum over rows of gout_j * xh_j: every CTA leaves one partial row in `partial` (folded afterwards).
+// The per-column and per-head sums of a lane's packs are kept in registers over all rows of the warp (NP > 0)
+// or added to shared memory row by row (NP = 0).  Shared memory: width + H accumulators.
+template <typename T, int V, int NP>
+__global__ void __launch_bounds__(GN_THREADS) gate_rmsnorm_reverse_kernel(
+    const T* __restrict__ y, const T* __restrict__ x, const typename Acc<T>::type* __restrict__ D, const T* __restrict__ z, size_t zp,
+    const T* __restrict__ gain, const typename Acc<T>::type* __restrict__ rstd, const T* __restrict__ gout, T* __restrict__ gy,
+    T* __restrict__ gz, size_t gzp, typename Acc<T>::type* __restrict__ gD, typename Acc<T>::type* __restrict__ partial, size_t rows,
+    int H, int P) {
+  using A = typename Acc<T>::type;
+  extern __shared__ unsigned char gn_smem[];
+  A* cols = reinterpret_cast<A*>(gn_smem);
+  const size_t width = static_cast<size_t>(H) * P;
+  A* bins = cols + width;
+  for (size_t i = threadIdx.x; i < width + H; i += GN_THREADS) cols[i] = A(0);
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int packs = NP > 0 ? NP : static_cast<int>((width / V + 31) / 32);
+  const size_t warps = static_cast<size_t>(gridDim.x) * (GN_THREADS / 32);
+  A gacc[NP > 0 ? NP : 1][V];
+  A dacc[NP > 0 ? NP : 1];
+#pragma unroll
+  for (int p = 0; p < (NP > 0 ? NP : 1); ++p) {
+    dacc[p] = A(0);
+#pragma unroll
+    for (int e = 0; e < V; ++e) gacc[p][e] = A(0);
+  }
+  for (size_t r = blockIdx.x * static_cast<size_t>(GN_THREADS / 32) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const A rs = rstd[r];
+    // pass 1: dot = sum gxh * xh, and the gain-gradient terms; the raw packs stay in registers for pass 2
+    VecT<T, V> ry[NP > 0 ? NP : 1], rx[NP > 0 ? NP : 1], rz[NP > 0 ? NP : 1], rg[NP > 0 ? NP : 1];
+    A dot = A(0);
+    if (NP > 0) {
+#pragma unroll
+      for (int p = 0; p < NP; ++p) {   // all loads of the row first
+        const size_t c = (static_cast<size_t>(p) * 32 + lane) * V;
+        ry[p] = *reinterpret_cast<const VecT<T, V>*>(y + r * width + c);
+        rx[p] = *reinterpret_cast<const VecT<T, V>*>(x + r * width + c);
+        rz[p] = *reinterpret_cast<const VecT<T, V>*>(z + r * zp + c);
+        rg[p] = *reinterpret_cast<const VecT<T, V>*>(gout + r * width + c);
+      }
+    }
+#pragma unroll
+    for (int p = 0; p < packs; ++p) {
+      const size_t c = (static_cast<size_t>(p) * 32 + lane) * V;
+      if (NP > 0 || c < width) {
+        const int q = NP > 0 ? p : 0;
+        if (NP == 0) {
+          ry[0] = *reinterpret_cast<const VecT<T, V>*>(y + r * width + c);
+          rx[0] = *reinterpret_cast<const VecT<T, V>*>(x + r * width + c);
+          rz[0] = *reinterpret_cast<const VecT<T, V>*>(z + r * zp + c);
+          rg[0] = *reinterpret_cast<const VecT<T, V>*>(gout + r * width + c);
+        }
+        A gn[V];
+        load_vec<T, V>(gain + c, gn);
+        const A d = D != nullptr ? D[c / P] : A(0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const A zz = mp_up(rz[q].v[e]), gv = mp_up(rg[q].v[e]);
+          const A xh = (mp_up(ry[q].v[e]) + d * mp_up(rx[q].v[e])) * zz * sigmoid_a(zz) * rs;
+          dot += gv * gn[e] * xh;
+          if (NP > 0) gacc[q][e] += gv * xh;
+          else atomicAdd(cols + c + e, gv * xh);
+        }
+      }
+    }
+    dot = warp_reduce<SumOp>(dot);
+    const A m = dot / static_cast<A>(width);
+    if (NP > 0) {
+      // pass 2 decodes the packs again: without this fence the compiler keeps pass 1's converted values alive
+      // (four times the registers of the packs) and spills
+#pragma unroll
+      for (int p = 0; p < (NP > 0 ? NP : 1); ++p) { gn_opaque(ry[p]); gn_opaque(rx[p]); gn_opaque(rz[p]); gn_opaque(rg[p]); }
+    }
+#pragma unroll
+    for (int p = 0; p < packs; ++p) {
+      const size_t c = (static_cast<size_t>(p) * 32 + lane) * V;
+      if (NP > 0 || c < width) {
+        const int q = NP > 0 ? p : 0;
+        if (NP == 0) {
+          ry[0] = *reinterpret_cast<const VecT<T, V>*>(y + r * width + c);
+          rx[0] = *reinterpret_cast<const VecT<T, V>*>(x + r * width + c);
+          rz[0] = *reinterpret_cast<const VecT<T, V>*>(z + r * zp + c);
+          rg[0] = *reinterpret_cast<const VecT<T, V>*>(gout + r * width + c);
+        }
+        A gn[V], oy[V], oz[V];
+        load_vec<T, V>(gain + c, gn);
+        const A d = D != nullptr ? D[c / P] : A(0);
+        A part = A(0);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const A zz = mp_up(rz[q].v[e]), xv = mp_up(rx[q].v[e]);
+          const A s = sigmoid_a(zz);
+          const A ww = mp_up(ry[q].v[e]) + d * xv;
+          const A xh = ww * zz * s * rs;
+          const A gu = rs * (mp_up(rg[q].v[e]) * gn[e] - xh * m);
+          oy[e] = gu * zz * s;
+          oz[e] = gu * ww * (s + zz * s * (A(1) - s));
+          part += oy[e] * xv;
+        }
+        if (NP > 0) dacc[q] += part;
+        else if (gD != nullptr) atomicAdd(bins + c / P, part);
+        store_vec<T, V>(gy + r * width + c, oy);
+        store_vec<T, V>(gz + r * gzp + c, oz);
+      }
+    }
+  }
+  if (NP > 0) {
+#pragma unroll
+    for (int p = 0; p < (NP > 0 ? NP : 1); ++p) {
+      const size_t c = (static_cast<size_t>(p) * 32 + lane) * V;
+#pragma unroll
+      for (int e = 0; e < V; ++e) atomicAdd(cols + c + e, gacc[p][e]);
+      if (gD != nullptr) atomicAdd(bins + c / P, dacc[p]);
+    }
+  }
+  __syncthreads();
+  for (size_t i = threadIdx.x; i < width; i += GN_THREADS) partial[blockIdx.x * width + i] = cols[i];
+  if (gD != nullptr)
+    for (int h = threadIdx.x; h < H; h += GN_THREADS) atomicAdd(gD + h, bins[h]);
+}
+
+// r16 rows of 512 * NP elements: TWO warps per row (half the registers per lane, twice the warps in flight: the
+// one-warp kernels above run 8 - 16 warps per SM and wait on their own loads), the row sums meet in shared memory
+// behind a 64-thread named barrier.  Pack p of warp w of the pair covers columns ((2 p + w) * 32 + lane) * 8 ...
+__device__ __forceinline__ void gn_pair_sync(int pair) { asm volatile("bar.sync %0, 64;" ::"r"(pair + 1) : "memory"); }
+
+template <int NP>
+__global__ void __launch_bounds__(GN_THREADS) gate_rmsnorm_h2_kernel(const __half* __restrict__ y, const __half* __restrict__ x,
+                                                                     const float* __restrict__ D, const __half* __restrict__ z, size_t zp,
+                                                                     const __half* __restrict__ gain, float eps, __half* __restrict__ out,
+                                                                     float* __restrict__ rstd, size_t rows, int P) {
+  __shared__ float slot[2][GN_THREADS / 64][2];
+  constexpr size_t width = static_cast<size_t>(NP) * 512;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, pair = warp >> 1, wsub = warp & 1;
+  const size_t pairs = static_cast<size_t>(gridDim.x) * (GN_THREADS / 64);
+  int parity = 0;
+  for (size_t r = blockIdx.x * static_cast<size_t>(GN_THREADS / 64) + pair; r < rows; r += pairs, parity ^= 1) {
+    uint4 ry[NP], rx[NP], rz[NP];
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const size_t c = (static_cast<size_t>(2 * p + wsub) * 32 + lane) * 8;
+      ry[p] = *reinterpret_cast<const uint4*>(y + r * width + c);
+      rx[p] = *reinterpret_cast<const uint4*>(x + r * width + c);
+      rz[p] = *reinterpret_cast<const uint4*>(z + r * zp + c);
+    }
+    float t[NP][8];
+    float sum = 0.f;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const size_t c = (static_cast<size_t>(2 * p + wsub) * 32 + lane) * 8;
+      const float d = D != nullptr ? D[c / P] : 0.f;
+      const __half2* hy = reinterpret_cast<const __half2*>(&ry[p]);
+      const __half2* hx = reinterpret_cast<const __half2*>(&rx[p]);
+      const __half2* hz = reinterpret_cast<const __half2*>(&rz[p]);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 fy = __half22float2(hy[q]), fx = __half22float2(hx[q]), fz = __half22float2(hz[q]);
+        t[p][2 * q] = (fy.x + d * fx.x) * fz.x * sigmoid_a(fz.x);
+        t[p][2 * q + 1] = (fy.y + d * fx.y) * fz.y * sigmoid_a(fz.y);
+        sum += t[p][2 * q] * t[p][2 * q] + t[p][2 * q + 1] * t[p][2 * q + 1];
+      }
+    }
+    sum = warp_reduce<SumOp>(sum);
+    if (lane == 0) slot[parity][pair][wsub] = sum;
+    gn_pair_sync(pair);
+    sum = slot[parity][pair][0] + slot[parity][pair][1];
+    const float rs = rsqrtf(sum * (1.f / static_cast<float>(width)) + eps);
+    if (lane == 0 && wsub == 0 && rstd != nullptr) rstd[r] = rs;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const size_t c = (static_cast<size_t>(2 * p + wsub) * 32 + lane) * 8;
+      const uint4 rg = *reinterpret_cast<const uint4*>(gain + c);
+      const __half2* hg = reinterpret_cast<const __half2*>(&rg);
+      uint4 o;
+      __half2* ho = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 fg = __half22float2(hg[q]);
+        ho[q] = __floats2half2_rn(t[p][2 * q] * rs * fg.x, t[p][2 * q + 1] * rs * fg.y);
+      }
+      *reinterpret_cast<uint4*>(out + r * width + c) = o;
+    }
+  }
+}
+
+// Reverse, same layout.  The outputs are linear in the row mean m, which is only known after the row has been read:
+//   gy = a1 - m b1,  gz = a2 - m b2,  with a1 = rstd gxh zs, b1 = rstd xh zs, a2 = rstd gxh w ds, b2 = rstd xh w ds
+// (w = y + D x, zs = silu(z), ds = silu'(z)).  The first pass leaves a1, b1, a2, b2 as packed halves in registers (the
+// size of the raw inputs) and the second pass is two packed multiply-adds per pair of elements instead of a second
+// evaluation of the gate.  gD uses sum(gy x) = sum(a1 x) - m sum(b1 x) in fp32.
+template <int NP>
+__global__ void __launch_bounds__(GN_THREADS) gate_rmsnorm_reverse_h2_kernel(
+    const __half* __restrict__ y, const __half* __restrict__ x, const float* __restrict__ D, const __half* __restrict__ z, size_t zp,
+    const __half* __restrict__ gain, const float* __restrict__ rstd, const __half* __restrict__ gout, __half* __restrict__ gy,
+    __half* __restrict__ gz, size_t gzp, float* __restrict__ gD, float* __restrict__ partial, size_t rows, int H, int P) {
+  extern __shared__ unsigned char gn_smem[];
+  float* cols = reinterpret_cast<float*>(gn_smem);
+  constexpr size_t width = static_cast<size_t>(NP) * 512;
+  float* bins = cols + width;
+  __shared__ float slot[2][GN_THREADS / 64][2];
+  for (size_t i = threadIdx.x; i < width + H; i += GN_THREADS) cols[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, pair = warp >> 1, wsub = warp & 1;
+  const size_t pairs = static_cast<size_t>(gridDim.x) * (GN_THREADS / 64);
+  float gacc[NP][8], dacc[NP];
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    dacc[p] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) gacc[p][e] = 0.f;
+  }
+  int parity = 0;
+  for (size_t r = blockIdx.x * static_cast<size_t>(GN_THREADS / 64) + pair; r < rows; r += pairs, parity ^= 1) {
+    const float rs = rstd[r];
+    uint4 ry[NP], rx[NP], rz[NP], rg[NP];
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const size_t c = (static_cast<size_t>(2 * p + wsub) * 32 + lane) * 8;
+      ry[p] = *reinterpret_cast<const uint4*>(y + r * width + c);
+      rx[p] = *reinterpret_cast<const uint4*>(x + r * width + c);
+      rz[p] = *reinterpret_cast<const uint4*>(z + r * zp + c);
+      rg[p] = *reinterpret_cast<const uint4*>(gout + r * width + c);
+    }
+    __half2 a1[NP][4], b1[NP][4], a2[NP][4], b2[NP][4];
+    float pa[NP], pb[NP];
+    float dot = 0.f;
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const size_t c = (static_cast<size_t>(2 * p + wsub) * 32 + lane) * 8;
+      const float d = D != nullptr ? D[c / P] : 0.f;
+      const uint4 rn = *reinterpret_cast<const uint4*>(gain + c);
+      const __half2* hy = reinterpret_cast<const __half2*>(&ry[p]);
+      const __half2* hx = reinterpret_cast<const __half2*>(&rx[p]);
+      const __half2* hz = reinterpret_cast<const __half2*>(&rz[p]);
+      const __half2* hg = reinterpret_cast<const __half2*>(&rg[p]);
+      const __half2* hn = reinterpret_cast<const __half2*>(&rn);
+      pa[p] = 0.f;
+      pb[p] = 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 fy = __half22float2(hy[q]), fx = __half22float2(hx[q]), fz = __half22float2(hz[q]);
+        const float2 fg = __half22float2(hg[q]), fn = __half22float2(hn[q]);
+        float A1[2], B1[2], A2[2], B2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float yy = e ? fy.y : fy.x, xx = e ? fx.y : fx.x, zz = e ? fz.y : fz.x, gg = e ? fg.y : fg.x, nn = e ? fn.y : fn.x;
+          const float sg = sigmoid_a(zz);
+          const float zs = zz * sg;
+          const float w = yy + d * xx;
+          const float xh = w * zs * rs;
+          const float gxh = gg * nn;
+          dot += gxh * xh;
+          gacc[p][2 * q + e] += gg * xh;
+          const float wds = w * (sg + zs * (1.f - sg));
+          const float t1 = rs * gxh, t2 = rs * xh;
+          A1[e] = t1 * zs; B1[e] = t2 * zs; A2[e] = t1 * wds; B2[e] = t2 * wds;
+          pa[p] += A1[e] * xx;
+          pb[p] += B1[e] * xx;
+        }
+        a1[p][q] = __floats2half2_rn(A1[0], A1[1]);
+        b1[p][q] = __floats2half2_rn(B1[0], B1[1]);
+        a2[p][q] = __floats2half2_rn(A2[0], A2[1]);
+        b2[p][q] = __floats2half2_rn(B2[0], B2[1]);
+      }
+    }
+    dot = warp_reduce<SumOp>(dot);
+    if (lane == 0) slot[parity][pair][wsub] = dot;
+    gn_pair_sync(pair);
+    const float m = (slot[parity][pair][0] + slot[parity][pair][1]) * (1.f / static_cast<float>(width));
+    const __half2 nm = __float2half2_rn(-m);
+#pragma unroll
+    for (int p = 0; p < NP; ++p) {
+      const size_t c = (static_cast<size_t>(2 * p + wsub) * 32 + lane) * 8;
+      uint4 oy, oz;
+      __half2* hy = reinterpret_cast<__half2*>(&oy);
+      __half2* hz = reinterpret_cast<__half2*>(&oz);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        hy[q] = __hfma2(nm, b1[p][q], a1[p][q]);
+        hz[q] = __hfma2(nm, b2[p][q], a2[p][q]);
+      }
+      *reinterpret_cast<uint4*>(gy + r * width + c) = oy;
+      *reinterpret_cast<uint4*>(gz + r * gzp + c) = oz;
+      dacc[p] += pa[p] - m * pb[p];
+    }
+  }
+#pragma unroll
+  for (int p = 0; p < NP; ++p) {
+    const size_t c = (static_cast<size_t>(2 * p + wsub) * 32 + lane) * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) atomicAdd(cols + c + e, gacc[p][e]);
+    if (gD != nullptr) atomicAdd(bins + c / P, dacc[p]);
+  }
+  __syncthreads();
+  for (size_t i = threadIdx.x; i < width; i += GN_THREADS) partial[blockIdx.x * width + i] = cols[i];
+  if (gD != nullptr)
+    for (int h = threadIdx.x; h < H; h += GN_THREADS) atomicAdd(gD + h, bins[h]);
+}
+
+// ggain = alpha * ggain + sum over the CTAs' partial rows (fixed order)
+template <typename T>
+__global__ void __launch_bounds__(256) gate_rmsnorm_fold_kernel(const typename Acc<T>::type* __restrict__ partial, int nrows, size_t width,
+                                                                typename Acc<T>::type alpha, T* __restrict__ ggain) {
+  using A = typename Acc<T>::type;
+  __shared__ A part[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const size_t c = blockIdx.x * static_cast<size_t>(32) + cx;
+  A sum = A(0);
+  if (c < width)
+    for (int r = ry; r < nrows; r += 8) sum += partial[static_cast<size_t>(r) * width + c];
+  part[ry][cx] = sum;
+  __syncthreads();
+  if (ry == 0 && c < width) {
+    A t = A(0);
+#pragma unroll
+    for (int q = 0; q < 8; ++q) t += part[q][cx];
+    if (alpha != A(0)) t += alpha * mp_up(ggain[c]);
+    ggain[c] = mp_down<T>(t);
+  }
+}
+
 // gx[r, h, :] += D[h] * gy[r, h, :]
 template <typename T, int V>
 __global__ void __launch_bounds__(256) head_scale_accumulate_kernel(const typename Acc<T>::type* __restrict__ D,
@@ -1246,6 +1650,137 @@ void ssd_gate_reverse_impl(const void* y, const void* x, const void* D, const vo
   MP_LAUNCH_CHECK();
 }
 
+inline unsigned gate_rmsnorm_grid(size_t rows, int sms) {
+  const size_t want = (rows + GN_THREADS / 32 - 1) / (GN_THREADS / 32);
+  const size_t cap = 2 * static_cast<size_t>(sms);   // one partial row of gain gradients per CTA
+  return static_cast<unsigned>(want < 1 ? 1 : (want < cap ? want : cap));
+}
+
+// packs per lane when the whole row fits the register plan (0: it does not)
+template <typename T>
+int gate_rmsnorm_packs(size_t width, bool aligned) {
+  constexpr size_t PN = Pack<T>::N;
+  if (!aligned || width % (32 * PN) != 0) return 0;
+  const size_t np = width / (32 * PN);
+  return np <= (sizeof(T) == 2 ? 6 : 8) ? static_cast<int>(np) : 0;   // r16 beyond 6 packs: the register plan spills
+}
+
+template <typename T>
+void ssd_gate_rmsnorm_impl(const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gain, double eps, void* out,
+                           void* rstd, len_t rows, len_t heads, len_t headdim, StreamContext ctx) {
+  if (rows == 0 || heads == 0 || headdim == 0) return;
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  const size_t width = heads * headdim;
+  const bool v = headdim % PN == 0 && vec_ok<T>(z, z_pitch, width) && mp_aligned16(y) && mp_aligned16(x) && mp_aligned16(out) && mp_aligned16(gain);
+  cudaStream_t st = mp_stream(ctx);
+  if constexpr (std::is_same<T, __half>::value) {
+    if (v && width % 512 == 0 && width / 512 <= 4 && headdim % 8 == 0 && getenv("MP_GATED_NORM_ONE_WARP") == nullptr) {
+      const unsigned g2 = grid_for(rows * 64, GN_THREADS);
+#define GN_FWD2(NPV)                                                                                                                 \
+  gate_rmsnorm_h2_kernel<NPV><<<g2, GN_THREADS, 0, st>>>(static_cast<const __half*>(y), static_cast<const __half*>(x),               \
+                                                         static_cast<const float*>(D), static_cast<const __half*>(z), z_pitch,      \
+                                                         static_cast<const __half*>(gain), static_cast<float>(eps),                 \
+                                                         static_cast<__half*>(out), static_cast<float*>(rstd), rows, static_cast<int>(headdim))
+      switch (width / 512) {
+        case 1: GN_FWD2(1); break;
+        case 2: GN_FWD2(2); break;
+        case 3: GN_FWD2(3); break;
+        default: GN_FWD2(4); break;
+      }
+#undef GN_FWD2
+      MP_LAUNCH_CHECK();
+      return;
+    }
+  }
+  const unsigned grid = grid_for(rows * 32, GN_THREADS);
+#define GN_FWD(VV, NPV)                                                                                                              \
+  gate_rmsnorm_kernel<T, VV, NPV><<<grid, GN_THREADS, 0, st>>>(static_cast<const T*>(y), static_cast<const T*>(x), static_cast<const A*>(D), \
+                                                               static_cast<const T*>(z), z_pitch, static_cast<const T*>(gain), static_cast<A>(eps), \
+                                                               static_cast<T*>(out), static_cast<A*>(rstd), rows, static_cast<int>(heads),   \
+                                                               static_cast<int>(headdim))
+  switch (gate_rmsnorm_packs<T>(width, v)) {
+    case 1: GN_FWD(PN, 1); break;
+    case 2: GN_FWD(PN, 2); break;
+    case 3: GN_FWD(PN, 3); break;
+    case 4: GN_FWD(PN, 4); break;
+    case 5: GN_FWD(PN, 5); break;
+    case 6: GN_FWD(PN, 6); break;
+    case 7: GN_FWD(PN, 7); break;
+    case 8: GN_FWD(PN, 8); break;
+    default:
+      if (v) GN_FWD(PN, 0);
+      else GN_FWD(1, 0);
+  }
+#undef GN_FWD
+  MP_LAUNCH_CHECK();
+}
+
+template <typename T>
+void ssd_gate_rmsnorm_reverse_impl(const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gain, const void* rstd,
+                                   const void* gout, void* gy, void* gz, len_t gz_pitch, void* gD, void* ggain, double alpha, void* scratch,
+                                   len_t rows, len_t heads, len_t headdim, StreamContext ctx) {
+  if (rows == 0 || heads == 0 || headdim == 0) return;
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  const size_t width = heads * headdim;
+  const bool v = headdim % PN == 0 && vec_ok<T>(z, z_pitch, width) && vec_ok<T>(gz, gz_pitch, width) && mp_aligned16(y) && mp_aligned16(x) &&
+                 mp_aligned16(gout) && mp_aligned16(gy) && mp_aligned16(gain);
+  cudaStream_t st = mp_stream(ctx);
+  const unsigned grid = gate_rmsnorm_grid(rows, mp_sm_count(ctx));
+  const size_t smem = (width + heads) * sizeof(A);
+  if (smem > 200 * 1024) MP_FATAL("ssd_gate_rmsnorm_reverse: row too wide for the shared-memory accumulators");
+  bool launched = false;
+  if constexpr (std::is_same<T, __half>::value) {
+    if (v && width % 512 == 0 && width / 512 <= 4 && headdim % 8 == 0 && getenv("MP_GATED_NORM_ONE_WARP") == nullptr) {
+#define GN_REV2(NPV)                                                                                                                 \
+  gate_rmsnorm_reverse_h2_kernel<NPV><<<grid, GN_THREADS, smem, st>>>(                                                               \
+      static_cast<const __half*>(y), static_cast<const __half*>(x), static_cast<const float*>(D), static_cast<const __half*>(z), z_pitch, \
+      static_cast<const __half*>(gain), static_cast<const float*>(rstd), static_cast<const __half*>(gout), static_cast<__half*>(gy),   \
+      static_cast<__half*>(gz), gz_pitch, static_cast<float*>(gD), static_cast<float*>(scratch), rows, static_cast<int>(heads),        \
+      static_cast<int>(headdim))
+      switch (width / 512) {
+        case 1: GN_REV2(1); break;
+        case 2: GN_REV2(2); break;
+        case 3: GN_REV2(3); break;
+        default: GN_REV2(4); break;
+      }
+#undef GN_REV2
+      launched = true;
+    }
+  }
+#define GN_REV(VV, NPV)                                                                                                              \
+  do {                                                                                                                               \
+    if (smem > 48 * 1024)                                                                                                            \
+      MP_CUDA_CHECK(cudaFuncSetAttribute(gate_rmsnorm_reverse_kernel<T, VV, NPV>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
+                                         static_cast<int>(smem)));                                                                   \
+    gate_rmsnorm_reverse_kernel<T, VV, NPV><<<grid, GN_THREADS, smem, st>>>(                                                         \
+        static_cast<const T*>(y), static_cast<const T*>(x), static_cast<const A*>(D), static_cast<const T*>(z), z_pitch,             \
+        static_cast<const T*>(gain), static_cast<const A*>(rstd), static_cast<const T*>(gout), static_cast<T*>(gy), static_cast<T*>(gz), \
+        gz_pitch, static_cast<A*>(gD), static_cast<A*>(scratch), rows, static_cast<int>(heads), static_cast<int>(headdim));          \
+  } while (0)
+  if (!launched) switch (gate_rmsnorm_packs<T>(width, v)) {
+    case 1: GN_REV(PN, 1); break;
+    case 2: GN_REV(PN, 2); break;
+    case 3: GN_REV(PN, 3); break;
+    case 4: GN_REV(PN, 4); break;
+    case 5: GN_REV(PN, 5); break;
+    case 6: GN_REV(PN, 6); break;
+    case 7: GN_REV(PN, 7); break;
+    case 8: GN_REV(PN, 8); break;
+    default:
+      if (v) GN_REV(PN, 0);
+      else GN_REV(1, 0);
+  }
+#undef GN_REV
+  MP_LAUNCH_CHECK();
+  if (ggain != nullptr) {
+    gate_rmsnorm_fold_kernel<T><<<static_cast<unsigned>((width + 31) / 32), 256, 0, st>>>(static_cast<const A*>(scratch), static_cast<int>(grid), width,
+                                                                                          static_cast<A>(alpha), static_cast<T*>(ggain));
+    MP_LAUNCH_CHECK();
+  }
+}
+
 template <typename T>
 void head_scale_accumulate_impl(const void* D, const void* gy, void* gx, len_t rows, len_t heads, len_t headdim, StreamContext ctx) {
   if (rows == 0 || heads == 0 || headdim == 0) return;
@@ -1340,6 +1875,18 @@ MP_STAMP3(ssd_gate_reverse,
           (const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gu, void* gy, void* gz, len_t gz_pitch,
            void* gD, len_t rows, len_t heads, len_t headdim, StreamContext ctx),
           (y, x, D, z, z_pitch, gu, gy, gz, gz_pitch, gD, rows, heads, headdim, ctx))
+MP_STAMP3(ssd_gate_rmsnorm,
+          (const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gain, double eps, void* out, void* rstd,
+           len_t rows, len_t heads, len_t headdim, StreamContext ctx),
+          (y, x, D, z, z_pitch, gain, eps, out, rstd, rows, heads, headdim, ctx))
+MP_STAMP3(ssd_gate_rmsnorm_reverse,
+          (const void* y, const void* x, const void* D, const void* z, len_t z_pitch, const void* gain, const void* rstd, const void* gout,
+           void* gy, void* gz, len_t gz_pitch, void* gD, void* ggain, double alpha, void* scratch, len_t rows, len_t heads, len_t headdim,
+           StreamContext ctx),
+          (y, x, D, z, z_pitch, gain, rstd, gout, gy, gz, gz_pitch, gD, ggain, alpha, scratch, rows, heads, headdim, ctx))
+extern "C" len_t mpSsdGateRmsnormReverseScratchBytes(len_t rows, len_t heads, len_t headdim, StreamContext ctx) {
+  return static_cast<len_t>(gate_rmsnorm_grid(rows, mp_sm_count(ctx))) * heads * headdim * sizeof(double);
+}
 MP_STAMP3(head_scale_accumulate, (const void* D, const void* gy, void* gx, len_t rows, len_t heads, len_t headdim, StreamContext ctx),
           (D, gy, gx, rows, heads, headdim, ctx))
 MP_STAMP3(cross_entropy,

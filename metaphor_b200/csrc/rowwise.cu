@@ -334,6 +334,113 @@ __global__ void __launch_bounds__(RowCfg<GROUP>::THREADS) rmsnorm_rev_kernel(
   }
 }
 
+// Warp-per-row variant for narrow rows (n = 32 * NP packs, NP <= 8): a row lives in one warp's registers, the two
+// row sums are warp shuffles (no CTA barrier per row), the next row's packs are requested before the current row is
+// reduced, and the gain-gradient sums stay in registers over all rows of the warp.  The four warps of a CTA meet in
+// shared memory once, so the call leaves gridDim.x partial rows (at most three per SM) instead of one per row group.
+constexpr int WROW_THREADS = 128;
+
+template <typename P>
+__device__ __forceinline__ void pack_fence(P& v) {
+  static_assert(sizeof(P) == 16, "16-byte packs");
+  uint32_t* w = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) asm volatile("" : "+r"(w[i]));
+}
+
+template <typename T, int NP, bool BLEND>
+__global__ void __launch_bounds__(WROW_THREADS, 3) rmsnorm_rev_warp_kernel(
+    const T* x, const T* __restrict__ gain, const typename Acc<T>::type* __restrict__ rstd_in, const T* gy,
+    typename Acc<T>::type eps, T* gx, typename Acc<T>::type alpha, typename Acc<T>::type* __restrict__ partial, size_t m) {
+  using A = typename Acc<T>::type;
+  constexpr int PN = Pack<T>::N;
+  constexpr size_t n = static_cast<size_t>(NP) * 32 * PN;
+  __shared__ A cols[NP * 32 * PN];
+  for (int i = threadIdx.x; i < NP * 32 * PN; i += WROW_THREADS) cols[i] = A(0);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  Pack<T> pgain[NP];
+  A acc[NP][PN];
+#pragma unroll
+  for (int u = 0; u < NP; ++u) {
+    pgain[u] = ld_pack(gain, u * 32 + lane);
+#pragma unroll
+    for (int k = 0; k < PN; ++k) acc[u][k] = A(0);
+  }
+  const A inv_n = A(1) / static_cast<A>(n);
+  const size_t stride = static_cast<size_t>(gridDim.x) * (WROW_THREADS / 32);
+  size_t row = static_cast<size_t>(blockIdx.x) * (WROW_THREADS / 32) + warp;
+  Pack<T> px[NP], pg[NP], nx[NP], ng[NP];
+  if (row < m) {
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      px[u] = ld_pack_stream(x + row * n, u * 32 + lane);
+      pg[u] = ld_pack_stream(gy + row * n, u * 32 + lane);
+    }
+  }
+  for (; row < m; row += stride) {
+    const size_t next = row + stride;
+    if (next < m) {
+#pragma unroll
+      for (int u = 0; u < NP; ++u) {
+        nx[u] = ld_pack_stream(x + next * n, u * 32 + lane);
+        ng[u] = ld_pack_stream(gy + next * n, u * 32 + lane);
+      }
+    }
+    Pack<T> po[BLEND ? NP : 1];
+    if constexpr (BLEND) {
+#pragma unroll
+      for (int u = 0; u < NP; ++u) po[u] = ld_pack_stream(gx + row * n, u * 32 + lane);
+    }
+    A ss = A(0), dot = A(0);
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      A fx[PN], fg[PN], fgain[PN];
+      unpack<T>(px[u], fx);
+      unpack<T>(pg[u], fg);
+      unpack<T>(pgain[u], fgain);
+#pragma unroll
+      for (int k = 0; k < PN; ++k) {
+        ss += fx[k] * fx[k];
+        dot += fg[k] * fgain[k] * fx[k];
+      }
+    }
+    ss = warp_reduce<SumOp>(ss);
+    dot = warp_reduce<SumOp>(dot);
+    const A rstd = rstd_in != nullptr ? rstd_in[row] : mp_rsqrt(ss * inv_n + eps);
+    const A coef = rstd * rstd * rstd * dot * inv_n;
+    // the packs are decoded again below: without the fence the compiler keeps the first pass's converted values
+    // alive (r16: four registers per pack become eight) and spills
+#pragma unroll
+    for (int u = 0; u < NP; ++u) { pack_fence(px[u]); pack_fence(pg[u]); pack_fence(pgain[u]); }
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      A fx[PN], fg[PN], fgain[PN], fo[PN], r[PN];
+      unpack<T>(px[u], fx);
+      unpack<T>(pg[u], fg);
+      unpack<T>(pgain[u], fgain);
+      if constexpr (BLEND) unpack<T>(po[u], fo);
+#pragma unroll
+      for (int k = 0; k < PN; ++k) {
+        r[k] = rstd * fg[k] * fgain[k] - fx[k] * coef;
+        if constexpr (BLEND) r[k] += alpha * fo[k];
+        acc[u][k] += fg[k] * fx[k] * rstd;
+      }
+      st_pack_stream(gx + row * n, u * 32 + lane, pack<T>(r));
+    }
+#pragma unroll
+    for (int u = 0; u < NP; ++u) { px[u] = nx[u]; pg[u] = ng[u]; }
+  }
+#pragma unroll
+  for (int u = 0; u < NP; ++u) {
+#pragma unroll
+    for (int k = 0; k < PN; ++k) atomicAdd(cols + (u * 32 + lane) * PN + k, acc[u][k]);
+  }
+  __syncthreads();
+  A* pr = partial + static_cast<size_t>(blockIdx.x) * n;
+  for (int i = threadIdx.x; i < NP * 32 * PN; i += WROW_THREADS) pr[i] = cols[i];
+}
+
 // Shared-memory staged variant of the RMSNorm reverse kernel: the rows of x and
 // gy that a CTA will need are fetched ahead of time by 1-D bulk async copies
 // (TMA unit) into a ring of `stages` buffers, each guarded by an mbarrier, so
@@ -726,6 +833,18 @@ StagedPlan plan_staged(size_t n, bool aligned) {
   p.full = nv == static_cast<size_t>(STG_THREADS) * p.ppt;
   return p;
 }
+// Warp-per-row plan of the RMSNorm reverse: packs per lane (0: the row does not fit it)
+template <typename T>
+int rms_rev_warp_packs(size_t n, bool aligned) {
+  constexpr size_t PN = Pack<T>::N;
+  if (!aligned || n % (32 * PN) != 0 || getenv("MP_RMS_REV_NO_WARP") != nullptr) return 0;
+  const size_t np = n / (32 * PN);
+  return np <= (sizeof(T) == 4 ? 5 : 4) ? static_cast<int>(np) : 0;   // wider rows spill the register plan
+}
+inline size_t rms_rev_warp_grid(size_t m, int sm_count) {
+  const size_t want = (m + WROW_THREADS / 32 - 1) / (WROW_THREADS / 32), cap = 3 * static_cast<size_t>(sm_count > 0 ? sm_count : 148);
+  return want < 1 ? 1 : (want < cap ? want : cap);
+}
 inline size_t rms_rev_grid(const RowPlan& p, size_t m, int sm_count) {
   const size_t groups = (m + p.rows - 1) / p.rows;
   const size_t rpc = rms_rev_rows_per_cta(groups, sm_count);
@@ -811,7 +930,9 @@ static size_t rmsnorm_rev_slots(size_t m, size_t n, int sm_count, bool aligned) 
   const RowPlan p = plan_rows_rev<T>(n, aligned);
   size_t slots = rms_rev_grid(p, m, sm_count) * p.rows;
   const size_t staged = (m + rms_rev_rows_per_cta(m, sm_count) - 1) / rms_rev_rows_per_cta(m, sm_count);  // one slot per CTA
-  return slots > staged ? slots : staged;
+  if (staged > slots) slots = staged;
+  const size_t warp_rows = rms_rev_warp_grid(m, sm_count);
+  return slots > warp_rows ? slots : warp_rows;
 }
 
 template <typename T>
@@ -842,7 +963,24 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
     size_t rpc = rms_rev_rows_per_cta((m + p.rows - 1) / p.rows, sms);
     slots = static_cast<size_t>(grid) * p.rows;
     MpStreamState* state = mp_state_or_null(ctx);  // the staged kernel reports timeouts through the status word
-    if (sp.ok && state != nullptr) {
+    const int wnp = rms_rev_warp_packs<T>(n, aligned);
+    if (wnp > 0) {
+      grid = static_cast<unsigned>(rms_rev_warp_grid(m, sms));
+      slots = grid;
+#define WROW(NPV)                                                                                                          \
+  do {                                                                                                                     \
+    if (blend) rmsnorm_rev_warp_kernel<T, NPV, true><<<grid, WROW_THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, partial, m);   \
+    else rmsnorm_rev_warp_kernel<T, NPV, false><<<grid, WROW_THREADS, 0, st>>>(x, gain, rstd, gy, e, gx, a, partial, m);        \
+  } while (0)
+      switch (wnp) {
+        case 1: WROW(1); break;
+        case 2: WROW(2); break;
+        case 3: WROW(3); break;
+        case 4: WROW(4); break;
+        default: WROW(5); break;
+      }
+#undef WROW
+    } else if (sp.ok && state != nullptr) {
       rpc = rms_rev_rows_per_cta(m, sms);
       grid = static_cast<unsigned>((m + rpc - 1) / rpc);
       slots = grid;
@@ -874,7 +1012,7 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
     MP_LAUNCH_CHECK();
   }
   constexpr int W = 16 / sizeof(A);
-  if (slots >= 128 && n % W == 0 && mp_aligned16(partial)) {
+  if (slots >= 512 && n % W == 0 && mp_aligned16(partial)) {   // (a few hundred rows: one launch is cheaper than two)
     A* partial2 = partial + slots * n;  // FOLD_SPLITS rows after the per-CTA partials
     const dim3 g1(static_cast<unsigned>((n + 32 * W - 1) / (32 * W)), FOLD_SPLITS);
     rmsnorm_fold_stage1_kernel<A><<<g1, 256, 0, st>>>(partial, partial2, n, slots);

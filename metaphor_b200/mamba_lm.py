@@ -171,7 +171,7 @@ class MambaLM:
         self.ids = torch.zeros(T, dtype=torch.int32, device=dev)
         self.targets = torch.zeros(T, dtype=torch.int32, device=dev)
         self.saved = [dict(h_in=f16(T, c.d_model), xn=f16(T, c.d_model), rstd1=f32(T), zx=f16(T, c.d_in_proj), xs=f16(T, c.d_inner),
-                           Bs=f16(T, gn), Cs=f16(T, gn), dt=f32(T, c.heads), A=f32(c.heads), y=f16(T, c.d_inner), u=f16(T, c.d_inner),
+                           Bs=f16(T, gn), Cs=f16(T, gn), dt=f32(T, c.heads), A=f32(c.heads), y=f16(T, c.d_inner),
                            un=f16(T, c.d_inner), rstd2=f32(T)) for _ in range(c.n_layer)]
         # residual stream: the input of layer i is saved[i]["h_in"], its output is written straight into the next
         # layer's h_in (the last one into h_out), so nothing is copied
@@ -186,7 +186,6 @@ class MambaLM:
         self.gh = f16(T, c.d_model)
         self.gt = f16(T, c.d_model)
         self.gun = f16(T, c.d_inner)
-        self.gu = f16(T, c.d_inner)
         self.gy = f16(T, c.d_inner)
         self.gxs = f16(T, c.d_inner)
         self.gBs = f16(T, gn)
@@ -199,7 +198,7 @@ class MambaLM:
         n_scr = max(self._lib.mpSsdScanScratchBytes(*dims, 0), self._lib.mpSsdScanScratchBytes(*dims, 1))
         self.ssd_scratch = torch.empty(n_scr, dtype=torch.uint8, device=dev)
         n_rms = max(self._lib.mpRmsnormReverseScratchBytes(T, c.d_model, self.stream.ctx),
-                    self._lib.mpRmsnormReverseScratchBytes(T, c.d_inner, self.stream.ctx))
+                    self._lib.mpSsdGateRmsnormReverseScratchBytes(T, c.heads, c.headdim, self.stream.ctx))
         self.rms_scratch = torch.empty(max(n_rms, 16), dtype=torch.uint8, device=dev)
         torch.cuda.synchronize()
 
@@ -289,8 +288,9 @@ class MambaLM:
             self._L("softplus_bias", zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), sv["dt"], T, H)
             self._L32("neg_exp", self._p(self.w32, p + "A_log"), sv["A"], H)
             self._L("ssd_scan", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], sv["y"], self.ssd_scratch, *self.ssd_dims)
-            self._L("ssd_gate", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, sv["u"], T, H, P)
-            self._L("rmsnorm_ij_j", sv["u"], self._p(W, p + "gnorm_w"), c.eps, sv["un"], sv["rstd2"], T, di)
+            # skip, gate and the gated norm in one pass; the gated activation itself is never stored
+            self._L("ssd_gate_rmsnorm", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, self._p(W, p + "gnorm_w"), c.eps, sv["un"],
+                    sv["rstd2"], T, H, P)
             self._L("inner_product_ij_jk_ik", sv["un"], self._p(W, p + "out_proj"), 1.0, self.o, 0.0, T, di, c.d_model)
             self._L("addition", sv["h_in"], self.o, h_next, T * c.d_model)
         self._L("rmsnorm_ij_j", self.h_out, self._p(W, "normf_w"), c.eps, self.hn, self.rstdf, T, c.d_model)
@@ -345,10 +345,8 @@ class MambaLM:
             # out_proj
             self._L("inner_product_ij_kj_ik", self.gh, self._p(W, p + "out_proj"), 1.0, self.gun, 0.0, T, c.d_model, di)
             self._L("inner_product_ji_jk_ik", sv["un"], self.gh, 1.0, self._p(G16, p + "out_proj"), 0.0, di, T, c.d_model)
-            self._L("rmsnorm_ij_j_reverse", sv["u"], self._p(W, p + "gnorm_w"), sv["rstd2"], self.gun, c.eps, self.gu,
-                    self._p(G16, p + "gnorm_w"), 0.0, self.rms_scratch, T, di)
-            self._L("ssd_gate_reverse", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, self.gu, self.gy, gzx, dip,
-                    self._p(G32, p + "D"), T, H, P)
+            self._L("ssd_gate_rmsnorm_reverse", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, self._p(W, p + "gnorm_w"), sv["rstd2"],
+                    self.gun, self.gy, gzx, dip, self._p(G32, p + "D"), self._p(G16, p + "gnorm_w"), 0.0, self.rms_scratch, T, H, P)
             self._L("ssd_scan_reverse", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], self.gy, self.gxs, self.gdt, self.gA,
                     self.gBs, self.gCs, self.ssd_scratch, *self.ssd_dims)
             self._L("head_scale_accumulate", self._p(self.w32, p + "D"), self.gy, self.gxs, T, H, P)

@@ -171,6 +171,51 @@ def test_ssd_gate(mp, stream, orc, sfx, rows, H, P, pitch):
     assert_close(host(gx), ref, TOL[sfx], "skip accumulate")
 
 
+# Gate and RMSNorm in one kernel: against the oracle's gate followed by its RMSNorm (and the reverses in the opposite
+# order).  Shapes: a row that fits the register plan of every dtype, a scalar ragged one, the language model's
+# [*, 24 x 64] inside a 3352-wide projection output, and a vectorised width outside the register plan.
+@pytest.mark.parametrize("sfx", DTYPES)
+@pytest.mark.parametrize("rows,H,P,pitch", [(257, 4, 64, 300), (3, 2, 5, 10), (70, 24, 64, 3352), (33, 3, 40, 128)])
+def test_ssd_gate_rmsnorm(mp, stream, orc, sfx, rows, H, P, pitch):
+    rng = np.random.default_rng(13)
+    width = H * P
+    eps = 1e-5
+    y, x, gout = (draw(rng, (rows, width), sfx) for _ in range(3))
+    zfull = draw(rng, (rows, pitch), sfx)
+    D = rng.standard_normal(H).astype(ACC[sfx])
+    gain = (1.0 + 0.1 * rng.standard_normal(width)).astype(NP_OF[sfx])
+    f64 = lambda a: a.astype(np.float64)
+    z = f64(zfull[:, :width])
+    u = orc.ssd_gate(f64(y), f64(x), D, z, H, P)
+    want, want_rstd = orc.rmsnorm_ij_j(u, f64(gain), eps)
+    out = dev(np.zeros((rows, width), NP_OF[sfx]))
+    rstd = dev(np.zeros(rows, ACC[sfx]))
+    dz = dev(zfull)
+    run(mp, stream, "ssd_gate_rmsnorm", sfx, dev(y), dev(x), dev(D), dz, pitch, dev(gain), eps, out, rstd, rows, H, P)
+    assert_close(host(out), want, TOL[sfx], "gated norm")
+    assert_close(host(rstd), want_rstd, 1e-5 if sfx != "r64" else 1e-12, "gated norm rstd")
+    # reverse, with the oracle's rstd so that both sides start from the same numbers
+    gu, want_ggain = orc.rmsnorm_ij_j_reverse(u, f64(gain), f64(gout), eps)
+    rgy, rgz, rgD = orc.ssd_gate_reverse(f64(y), f64(x), D, z, gu, H, P)
+    gy = dev(np.zeros((rows, width), NP_OF[sfx]))
+    gz = dev(np.full((rows, pitch), 2, NP_OF[sfx]))
+    gD0 = rng.standard_normal(H).astype(ACC[sfx])
+    gD = dev(gD0.copy())
+    gg0 = draw(rng, width, sfx)
+    nbytes = mp.lib().mpSsdGateRmsnormReverseScratchBytes(rows, H, P, stream.ctx)
+    scratch = dev(np.zeros(max(1, nbytes // 8), np.float64))
+    for alpha in (0.0, 1.0):
+        ggain = dev(gg0.copy())
+        gD = dev(gD0.copy())
+        run(mp, stream, "ssd_gate_rmsnorm_reverse", sfx, dev(y), dev(x), dev(D), dz, pitch, dev(gain), dev(want_rstd.astype(ACC[sfx])),
+            dev(gout), gy, gz, pitch, gD, ggain, alpha, scratch, rows, H, P)
+        assert_close(host(gy), rgy, TOL[sfx], "gated norm gy")
+        assert_close(host(gz)[:, :width], rgz, TOL[sfx], "gated norm gz")
+        assert np.all(host(gz)[:, width:] == 2)
+        assert_close(host(gD), f64(gD0) + rgD, 1e-2 if sfx == "r16" else (1e-4 if sfx == "r32" else 1e-11), "gated norm gD")
+        assert_close(host(ggain), alpha * f64(gg0) + want_ggain, 1e-2 if sfx == "r16" else (1e-4 if sfx == "r32" else 1e-11), "gated norm ggain")
+
+
 @pytest.mark.parametrize("sfx", DTYPES)
 @pytest.mark.parametrize("m,n", [(64, 50280), (7, 1024), (3, 37), (2, 120000)])
 def test_cross_entropy(mp, stream, orc, sfx, m, n):
