@@ -32,8 +32,15 @@ __device__ __forceinline__ void store_vec(T* p, const typename Acc<T>::type* in)
   *reinterpret_cast<VecT<T, V>*>(p) = x;
 }
 
-// ex2 + rcp on the special-function unit (an IEEE division would cost ten instructions per element)
-__device__ __forceinline__ float sigmoid_a(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+// ex2 + rcp on the special-function unit, four instructions: an IEEE division costs ten, and the non-flushing forms
+// behind __expf / __fdividef add range fix-ups that the conv and gate kernels, which are bound by instruction issue,
+// pay per element.  Saturates correctly: x -> -inf gives ex2 = +inf, rcp = 0; x -> +inf gives ex2 = 0, rcp = 1.
+__device__ __forceinline__ float sigmoid_a(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return r;
+}
 __device__ __forceinline__ double sigmoid_a(double x) { return 1.0 / (1.0 + exp(-x)); }
 __device__ __forceinline__ float exp_a(float x) { return __expf(x); }
 __device__ __forceinline__ double exp_a(double x) { return exp(x); }
@@ -307,8 +314,12 @@ __global__ void __launch_bounds__(32 * CONV_TY) conv1d_silu_reverse_kernel(const
 // in registers over the CTA's time tiles and end in one atomic per (CTA, channel, tap).
 constexpr int CT_C = 64;            // channels per tile
 constexpr int CT_L = 64;            // steps per tile
-constexpr int CT_LANES = 4;         // time lanes: 256 threads = 64 channels x 4 lanes
+constexpr int CT_LANES = 4;         // time lanes: 128 threads = 32 channel PAIRS x 4 lanes (one warp per lane)
 constexpr int CT_STEPS = CT_L / CT_LANES;
+constexpr int CT_THREADS = (CT_C / 2) * CT_LANES;
+// A thread owns two neighbouring channels: one 4-byte shared-memory access, one packed conversion and one packed
+// store serve two elements (with a channel per thread and 2-byte accesses both kernels were bound by instruction
+// issue at 35 / 59 instructions per element).
 
 // 16-byte asynchronous global -> shared copies (LDGSTS); `valid == false` writes 16 zero bytes without touching global memory.
 __device__ __forceinline__ void cp_async_16_zfill(void* smem_dst, const void* gmem_src, bool valid) {
@@ -337,35 +348,38 @@ __device__ __forceinline__ int conv_segment_of(const ConvSegs& sg, int block) {
   return s;
 }
 
-// Forward with the same staging: x tile (+ W - 1 rows before it) in, y tile out, 16 steps per thread.
+// Forward with the same staging: x tile (+ W - 1 rows before it) in, y tile out, 16 steps of two channels per thread.
 template <int W>
-__global__ void __launch_bounds__(256) conv1d_silu_tiled_kernel(const __half* __restrict__ x, size_t xp, const __half* __restrict__ w,
-                                                                const __half* __restrict__ bias, const ConvSegs sg, int L,
-                                                                int tiles_per_cta) {
+__global__ void __launch_bounds__(CT_THREADS) conv1d_silu_tiled_kernel(const __half* __restrict__ x, size_t xp, const __half* __restrict__ w,
+                                                                       const __half* __restrict__ bias, const ConvSegs sg, int L,
+                                                                       int tiles_per_cta) {
   constexpr int H = W - 1;
   __shared__ __align__(16) __half xs[2][CT_L + H][CT_C];    // two tiles in turn; row r = step l0 - H + r
   __shared__ __align__(16) __half ys[CT_L][CT_C];
   const int tid = threadIdx.x;
-  const int c = tid % CT_C, lane = tid / CT_C;
+  const int c = (tid % (CT_C / 2)) * 2, lane = tid / (CT_C / 2);
   const int seg = conv_segment_of(sg, blockIdx.x);
   const int local = (blockIdx.x - sg.blk_begin[seg]) * CT_C;   // first channel of the tile inside its segment
   const int cbase = sg.ch_begin[seg] + local;                  // ... and in x / w / bias
   const int C = sg.ch_begin[seg] + sg.ch_count[seg];           // channels past the segment's end belong to the next tile row
-  const bool live_c = cbase + c < C;
+  const bool live_c = cbase + c < C;                           // (channel counts are multiples of 8: a pair is live or dead as one)
   const size_t b = blockIdx.z;
   const size_t yp = sg.pitch[seg];
   const __half* xb = x + b * L * xp + cbase;
   __half* yb = static_cast<__half*>(const_cast<void*>(sg.ptr[seg])) + b * L * yp + local;
-  float wk[W], bs = 0.f;
+  float wk[2][W], bs[2] = {0.f, 0.f};
 #pragma unroll
-  for (int k = 0; k < W; ++k) wk[k] = live_c ? __half2float(w[static_cast<size_t>(cbase + c) * W + k]) : 0.f;
-  if (live_c && bias != nullptr) bs = __half2float(bias[cbase + c]);
+  for (int e = 0; e < 2; ++e) {
+#pragma unroll
+    for (int k = 0; k < W; ++k) wk[e][k] = live_c ? __half2float(w[static_cast<size_t>(cbase + c + e) * W + k]) : 0.f;
+    if (live_c && bias != nullptr) bs[e] = __half2float(bias[cbase + c + e]);
+  }
   constexpr int PPR = CT_C / 8;
   const int packs_live = min(PPR, (C - cbase) / 8);
   // tile t + 1 is fetched (asynchronous copies, zero-filled outside the sequence / the segment) while tile t is computed
   auto stage = [&](int t) {
     const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
-    for (int v = tid; v < (CT_L + H) * PPR; v += 256) {
+    for (int v = tid; v < (CT_L + H) * PPR; v += CT_THREADS) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 - H + r;
       const bool ok = l >= 0 && l < L && pk < packs_live;
@@ -383,22 +397,22 @@ __global__ void __launch_bounds__(256) conv1d_silu_tiled_kernel(const __half* __
     {
       const __half (*xt)[CT_C] = xs[t & 1];
       const int s0 = lane * CT_STEPS;
-      float xw[W];
+      float2 xw[W];
 #pragma unroll
-      for (int k = 0; k < H; ++k) xw[k + 1] = __half2float(xt[s0 + k][c]);
+      for (int k = 0; k < H; ++k) xw[k + 1] = __half22float2(*reinterpret_cast<const __half2*>(&xt[s0 + k][c]));
 #pragma unroll
       for (int j = 0; j < CT_STEPS; ++j) {
 #pragma unroll
         for (int k = 0; k < H; ++k) xw[k] = xw[k + 1];
-        xw[H] = __half2float(xt[s0 + j + H][c]);
-        float pre = bs;
+        xw[H] = __half22float2(*reinterpret_cast<const __half2*>(&xt[s0 + j + H][c]));
+        float p0 = bs[0], p1 = bs[1];
 #pragma unroll
-        for (int k = 0; k < W; ++k) pre += wk[k] * xw[k];
-        ys[s0 + j][c] = __float2half_rn(pre * sigmoid_a(pre));
+        for (int k = 0; k < W; ++k) { p0 += wk[0][k] * xw[k].x; p1 += wk[1][k] * xw[k].y; }
+        *reinterpret_cast<__half2*>(&ys[s0 + j][c]) = __floats2half2_rn(p0 * sigmoid_a(p0), p1 * sigmoid_a(p1));
       }
     }
     __syncthreads();
-    for (int v = tid; v < CT_L * PPR; v += 256) {
+    for (int v = tid; v < CT_L * PPR; v += CT_THREADS) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 + r;
       if (l < L && pk < packs_live) *reinterpret_cast<uint4*>(yb + static_cast<size_t>(l) * yp + pk * 8) = *reinterpret_cast<const uint4*>(&ys[r][pk * 8]);
@@ -407,18 +421,18 @@ __global__ void __launch_bounds__(256) conv1d_silu_tiled_kernel(const __half* __
 }
 
 template <int W>
-__global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __half* __restrict__ x, size_t xp,
-                                                                        const __half* __restrict__ w, const __half* __restrict__ bias,
-                                                                        const ConvSegs sg, __half* __restrict__ gx, size_t gxp,
-                                                                        float* __restrict__ gw, float* __restrict__ gbias, int L,
-                                                                        int tiles_per_cta) {
+__global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(const __half* __restrict__ x, size_t xp,
+                                                                               const __half* __restrict__ w, const __half* __restrict__ bias,
+                                                                               const ConvSegs sg, __half* __restrict__ gx, size_t gxp,
+                                                                               float* __restrict__ gw, float* __restrict__ gbias, int L,
+                                                                               int tiles_per_cta) {
   constexpr int H = W - 1;
   __shared__ __align__(16) __half xs[2][CT_L + 2 * H][CT_C];    // two tiles in turn; row r = step l0 - H + r
   __shared__ __align__(16) __half gys[2][CT_L + H][CT_C];       // row r = step l0 + r
   __shared__ __align__(16) __half gxs[CT_L][CT_C];
   __shared__ float red[CT_LANES][CT_C][W + 1];
   const int tid = threadIdx.x;
-  const int c = tid % CT_C, lane = tid / CT_C;
+  const int c = (tid % (CT_C / 2)) * 2, lane = tid / (CT_C / 2);
   const int seg = conv_segment_of(sg, blockIdx.x);
   const int local = (blockIdx.x - sg.blk_begin[seg]) * CT_C;
   const int cbase = sg.ch_begin[seg] + local;
@@ -429,10 +443,13 @@ __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __
   const __half* xb = x + b * L * xp + cbase;
   const __half* gyb = static_cast<const __half*>(sg.ptr[seg]) + b * L * gyp + local;
   __half* gxb = gx + b * L * gxp + cbase;
-  float wk[W], bs = 0.f, gwk[W], gbs = 0.f;
+  float wk[2][W], bs[2] = {0.f, 0.f}, gwk[2][W], gbs[2] = {0.f, 0.f};
 #pragma unroll
-  for (int k = 0; k < W; ++k) { wk[k] = live_c ? __half2float(w[static_cast<size_t>(cbase + c) * W + k]) : 0.f; gwk[k] = 0.f; }
-  if (live_c && bias != nullptr) bs = __half2float(bias[cbase + c]);
+  for (int e = 0; e < 2; ++e) {
+#pragma unroll
+    for (int k = 0; k < W; ++k) { wk[e][k] = live_c ? __half2float(w[static_cast<size_t>(cbase + c + e) * W + k]) : 0.f; gwk[e][k] = 0.f; }
+    if (live_c && bias != nullptr) bs[e] = __half2float(bias[cbase + c + e]);
+  }
   constexpr int PPR = CT_C / 8;   // 16-byte packs per tile row
   const int packs_live = min(PPR, (C - cbase) / 8);   // C is a multiple of 8 on this path
 
@@ -440,13 +457,13 @@ __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __
   //      tile t + 1 is in flight while tile t is walked ----
   auto stage = [&](int t) {
     const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
-    for (int v = tid; v < (CT_L + 2 * H) * PPR; v += 256) {
+    for (int v = tid; v < (CT_L + 2 * H) * PPR; v += CT_THREADS) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 - H + r;
       const bool ok = l >= 0 && l < L && pk < packs_live;
       cp_async_16_zfill(&xs[t & 1][r][pk * 8], ok ? xb + static_cast<size_t>(l) * xp + pk * 8 : xb, ok);
     }
-    for (int v = tid; v < (CT_L + H) * PPR; v += 256) {
+    for (int v = tid; v < (CT_L + H) * PPR; v += CT_THREADS) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 + r;
       const bool ok = l < L && pk < packs_live;
@@ -461,46 +478,47 @@ __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __
     const bool more = t + 1 < tiles_per_cta && l0 + CT_L < L;
     if (more) { stage(t + 1); cp_async_wait<1>(); } else cp_async_wait<0>();
     __syncthreads();
-    // ---- walk CT_STEPS (+ H look-ahead) steps of one channel ----
+    // ---- walk CT_STEPS (+ H look-ahead) steps of two channels ----
     {
       const __half (*xt)[CT_C] = xs[t & 1];
       const __half (*gt)[CT_C] = gys[t & 1];
       const int s0 = lane * CT_STEPS;
-      float xw[W], d[W];   // xw[k] = x at step s + k - H (tile row s + k); d[k] = dpre at step s - k
+      float2 xw[W], d[W];   // xw[k] = x at step s + k - H (tile row s + k); d[k] = dpre at step s - k
 #pragma unroll
-      for (int k = 0; k < W; ++k) d[k] = 0.f;
+      for (int k = 0; k < W; ++k) d[k] = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int k = 0; k < H; ++k) xw[k + 1] = __half2float(xt[s0 + k][c]);
+      for (int k = 0; k < H; ++k) xw[k + 1] = __half22float2(*reinterpret_cast<const __half2*>(&xt[s0 + k][c]));
 #pragma unroll
       for (int j = 0; j < CT_STEPS + H; ++j) {
         const int s = s0 + j;
 #pragma unroll
         for (int k = 0; k < H; ++k) xw[k] = xw[k + 1];
-        xw[H] = __half2float(xt[s + H][c]);
-        float pre = bs;
+        xw[H] = __half22float2(*reinterpret_cast<const __half2*>(&xt[s + H][c]));
+        float p0 = bs[0], p1 = bs[1];
 #pragma unroll
-        for (int k = 0; k < W; ++k) pre += wk[k] * xw[k];
-        const float sg = sigmoid_a(pre);
-        const float dp = __half2float(gt[s][c]) * sg * (1.f + pre * (1.f - sg));
+        for (int k = 0; k < W; ++k) { p0 += wk[0][k] * xw[k].x; p1 += wk[1][k] * xw[k].y; }
+        const float g0 = sigmoid_a(p0), g1 = sigmoid_a(p1);
+        const float2 gyv = __half22float2(*reinterpret_cast<const __half2*>(&gt[s][c]));
+        const float2 dp = make_float2(gyv.x * g0 * (1.f + p0 * (1.f - g0)), gyv.y * g1 * (1.f + p1 * (1.f - g1)));
 #pragma unroll
         for (int k = H; k > 0; --k) d[k] = d[k - 1];
         d[0] = dp;
         if (j < CT_STEPS) {   // own steps only: the look-ahead belongs to the next lane / tile
-          gbs += dp;
+          gbs[0] += dp.x; gbs[1] += dp.y;
 #pragma unroll
-          for (int k = 0; k < W; ++k) gwk[k] += dp * xw[k];
+          for (int k = 0; k < W; ++k) { gwk[0][k] += dp.x * xw[k].x; gwk[1][k] += dp.y * xw[k].y; }
         }
         if (j >= H) {         // gx at step s - H = sum_k w[k] dpre[s - k]
-          float acc = 0.f;
+          float a0 = 0.f, a1 = 0.f;
 #pragma unroll
-          for (int k = 0; k < W; ++k) acc += wk[k] * d[k];
-          gxs[s - H][c] = __float2half_rn(acc);
+          for (int k = 0; k < W; ++k) { a0 += wk[0][k] * d[k].x; a1 += wk[1][k] * d[k].y; }
+          *reinterpret_cast<__half2*>(&gxs[s - H][c]) = __floats2half2_rn(a0, a1);
         }
       }
     }
     __syncthreads();
     // ---- gx tile -> global ----
-    for (int v = tid; v < CT_L * PPR; v += 256) {
+    for (int v = tid; v < CT_L * PPR; v += CT_THREADS) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 + r;
       if (l < L && pk < packs_live) *reinterpret_cast<uint4*>(gxb + static_cast<size_t>(l) * gxp + pk * 8) = *reinterpret_cast<const uint4*>(&gxs[r][pk * 8]);
@@ -510,17 +528,20 @@ __global__ void __launch_bounds__(256) conv1d_silu_reverse_tiled_kernel(const __
   }
   // ---- fold the time lanes, one atomic per (channel, tap) ----
 #pragma unroll
-  for (int k = 0; k < W; ++k) red[lane][c][k] = gwk[k];
-  red[lane][c][W] = gbs;
-  __syncthreads();
-  if (lane == 0 && live_c) {
+  for (int e = 0; e < 2; ++e) {
 #pragma unroll
-    for (int k = 0; k <= W; ++k) {
+    for (int k = 0; k < W; ++k) red[lane][c + e][k] = gwk[e][k];
+    red[lane][c + e][W] = gbs[e];
+  }
+  __syncthreads();
+  for (int i = tid; i < CT_C * (W + 1); i += CT_THREADS) {
+    const int ch = i / (W + 1), k = i % (W + 1);
+    if (cbase + ch < C) {
       float sum = 0.f;
 #pragma unroll
-      for (int q = 0; q < CT_LANES; ++q) sum += red[q][c][k];
-      if (k < W) atomicAdd(gw + static_cast<size_t>(cbase + c) * W + k, sum);
-      else if (gbias != nullptr) atomicAdd(gbias + cbase + c, sum);
+      for (int q = 0; q < CT_LANES; ++q) sum += red[q][ch][k];
+      if (k < W) atomicAdd(gw + static_cast<size_t>(cbase + ch) * W + k, sum);
+      else if (gbias != nullptr) atomicAdd(gbias + cbase + ch, sum);
     }
   }
 }
@@ -1461,9 +1482,9 @@ static void conv_tiled_forward(const void* x, len_t x_pitch, const void* w, cons
   cudaStream_t st = mp_stream(ctx);
   const __half* xh = static_cast<const __half*>(x); const __half* wh = static_cast<const __half*>(w);
   const __half* bh = static_cast<const __half*>(bias);
-  if (width == 4) conv1d_silu_tiled_kernel<4><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
-  else if (width == 3) conv1d_silu_tiled_kernel<3><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
-  else conv1d_silu_tiled_kernel<2><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
+  if (width == 4) conv1d_silu_tiled_kernel<4><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
+  else if (width == 3) conv1d_silu_tiled_kernel<3><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
+  else conv1d_silu_tiled_kernel<2><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, L, tp);
   MP_LAUNCH_CHECK();
 }
 static void conv_tiled_reverse(const void* x, len_t x_pitch, const void* w, const void* bias, const ConvSegs& sg, void* gx, len_t gx_pitch,
@@ -1476,9 +1497,9 @@ static void conv_tiled_reverse(const void* x, len_t x_pitch, const void* w, cons
   const __half* bh = static_cast<const __half*>(bias);
   __half* gxh = static_cast<__half*>(gx);
   float* gwf = static_cast<float*>(gw); float* gbf = static_cast<float*>(gbias);
-  if (width == 4) conv1d_silu_reverse_tiled_kernel<4><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
-  else if (width == 3) conv1d_silu_reverse_tiled_kernel<3><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
-  else conv1d_silu_reverse_tiled_kernel<2><<<grid, 256, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
+  if (width == 4) conv1d_silu_reverse_tiled_kernel<4><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
+  else if (width == 3) conv1d_silu_reverse_tiled_kernel<3><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
+  else conv1d_silu_reverse_tiled_kernel<2><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
   MP_LAUNCH_CHECK();
 }
 

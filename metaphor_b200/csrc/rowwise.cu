@@ -441,6 +441,84 @@ __global__ void __launch_bounds__(WROW_THREADS, 3) rmsnorm_rev_warp_kernel(
   for (int i = threadIdx.x; i < NP * 32 * PN; i += WROW_THREADS) pr[i] = cols[i];
 }
 
+// r16 rows with rstd supplied: gx = rstd * gxh - coef * x (+ alpha * gx) is linear in the row's coef, which is only
+// known after the row sum, so the first pass leaves gxh = gy o gain as packed halves beside the raw x packs and the
+// second pass is two or three packed multiply-adds per pair of elements; no value is decoded twice and nothing is
+// prefetched into a second register set (at most 128 registers: sixteen warps per SM, and one partial row of gain
+// gradients per 256-thread CTA, two per SM, so one small fold finishes the call).
+constexpr int WROWH_THREADS = 256;
+
+template <int NP, bool BLEND>
+__global__ void __launch_bounds__(WROWH_THREADS, 2) rmsnorm_rev_warp_h_kernel(const __half* x, const __half* __restrict__ gain,
+                                                                         const float* __restrict__ rstd_in, const __half* gy, __half* gx,
+                                                                         float alpha, float* __restrict__ partial, size_t m) {
+  constexpr size_t n = static_cast<size_t>(NP) * 256;
+  __shared__ float cols[NP * 256];
+  for (int i = threadIdx.x; i < NP * 256; i += WROWH_THREADS) cols[i] = 0.f;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float acc[NP][8];
+#pragma unroll
+  for (int u = 0; u < NP; ++u) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[u][k] = 0.f;
+  }
+  const float inv_n = 1.f / static_cast<float>(n);
+  const __half2 al2 = __float2half2_rn(alpha);
+  const size_t stride = static_cast<size_t>(gridDim.x) * (WROWH_THREADS / 32);
+  for (size_t row = static_cast<size_t>(blockIdx.x) * (WROWH_THREADS / 32) + warp; row < m; row += stride) {
+    uint4 px[NP], pg[NP], po[BLEND ? NP : 1];
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      px[u] = __ldcs(reinterpret_cast<const uint4*>(x + row * n) + u * 32 + lane);
+      pg[u] = __ldcs(reinterpret_cast<const uint4*>(gy + row * n) + u * 32 + lane);
+      if constexpr (BLEND) po[u] = __ldcs(reinterpret_cast<const uint4*>(gx + row * n) + u * 32 + lane);
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      const uint4 pn = __ldg(reinterpret_cast<const uint4*>(gain) + u * 32 + lane);
+      const __half2* hx = reinterpret_cast<const __half2*>(&px[u]);
+      __half2* hg = reinterpret_cast<__half2*>(&pg[u]);
+      const __half2* hn = reinterpret_cast<const __half2*>(&pn);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 fx = __half22float2(hx[q]), fg = __half22float2(hg[q]), fn = __half22float2(hn[q]);
+        const float ux = fg.x * fn.x, uy = fg.y * fn.y;
+        dot += ux * fx.x + uy * fx.y;
+        acc[u][2 * q] += fg.x * fx.x * rstd;
+        acc[u][2 * q + 1] += fg.y * fx.y * rstd;
+        hg[q] = __floats2half2_rn(ux * rstd, uy * rstd);   // rstd * gxh replaces gy in place
+      }
+    }
+    dot = warp_reduce<SumOp>(dot);
+    const __half2 nc = __float2half2_rn(-rstd * rstd * rstd * dot * inv_n);
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      const __half2* hx = reinterpret_cast<const __half2*>(&px[u]);
+      const __half2* hg = reinterpret_cast<const __half2*>(&pg[u]);
+      uint4 o;
+      __half2* ho = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        __half2 r = __hfma2(nc, hx[q], hg[q]);
+        if constexpr (BLEND) r = __hfma2(al2, reinterpret_cast<const __half2*>(&po[u])[q], r);
+        ho[q] = r;
+      }
+      __stcs(reinterpret_cast<uint4*>(gx + row * n) + u * 32 + lane, o);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < NP; ++u) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) atomicAdd(cols + (u * 32 + lane) * 8 + k, acc[u][k]);
+  }
+  __syncthreads();
+  float* pr = partial + static_cast<size_t>(blockIdx.x) * n;
+  for (int i = threadIdx.x; i < NP * 256; i += WROWH_THREADS) pr[i] = cols[i];
+}
+
 // Shared-memory staged variant of the RMSNorm reverse kernel: the rows of x and
 // gy that a CTA will need are fetched ahead of time by 1-D bulk async copies
 // (TMA unit) into a ring of `stages` buffers, each guarded by an mbarrier, so
@@ -841,8 +919,8 @@ int rms_rev_warp_packs(size_t n, bool aligned) {
   const size_t np = n / (32 * PN);
   return np <= (sizeof(T) == 4 ? 5 : 4) ? static_cast<int>(np) : 0;   // wider rows spill the register plan
 }
-inline size_t rms_rev_warp_grid(size_t m, int sm_count) {
-  const size_t want = (m + WROW_THREADS / 32 - 1) / (WROW_THREADS / 32), cap = 3 * static_cast<size_t>(sm_count > 0 ? sm_count : 148);
+inline size_t rms_rev_warp_grid(size_t m, int sm_count, int per_sm = 3) {
+  const size_t want = (m + WROW_THREADS / 32 - 1) / (WROW_THREADS / 32), cap = per_sm * static_cast<size_t>(sm_count > 0 ? sm_count : 148);
   return want < 1 ? 1 : (want < cap ? want : cap);
 }
 inline size_t rms_rev_grid(const RowPlan& p, size_t m, int sm_count) {
@@ -931,7 +1009,7 @@ static size_t rmsnorm_rev_slots(size_t m, size_t n, int sm_count, bool aligned) 
   size_t slots = rms_rev_grid(p, m, sm_count) * p.rows;
   const size_t staged = (m + rms_rev_rows_per_cta(m, sm_count) - 1) / rms_rev_rows_per_cta(m, sm_count);  // one slot per CTA
   if (staged > slots) slots = staged;
-  const size_t warp_rows = rms_rev_warp_grid(m, sm_count);
+  const size_t warp_rows = rms_rev_warp_grid(m, sm_count, 3);
   return slots > warp_rows ? slots : warp_rows;
 }
 
@@ -964,7 +1042,31 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
     slots = static_cast<size_t>(grid) * p.rows;
     MpStreamState* state = mp_state_or_null(ctx);  // the staged kernel reports timeouts through the status word
     const int wnp = rms_rev_warp_packs<T>(n, aligned);
-    if (wnp > 0) {
+    bool half_plan = false;
+    if constexpr (std::is_same<T, __half>::value) {
+      // alpha must be exactly representable so that the packed blend equals the fp32 one (0, 1 and small powers of two are)
+      half_plan = aligned && rstd != nullptr && n % 256 == 0 && n / 256 <= 4 && getenv("MP_RMS_REV_NO_WARP") == nullptr &&
+                  static_cast<float>(__half2float(__float2half_rn(a))) == a;
+      if (half_plan) {
+        const size_t want = (m + WROWH_THREADS / 32 - 1) / (WROWH_THREADS / 32), cap = 2 * static_cast<size_t>(sms);
+        grid = static_cast<unsigned>(want < cap ? want : cap);
+        slots = grid;
+#define WROWH(NPV)                                                                                                     \
+  do {                                                                                                                 \
+    if (blend) rmsnorm_rev_warp_h_kernel<NPV, true><<<grid, WROWH_THREADS, 0, st>>>(x, gain, rstd, gy, gx, a, partial, m);   \
+    else rmsnorm_rev_warp_h_kernel<NPV, false><<<grid, WROWH_THREADS, 0, st>>>(x, gain, rstd, gy, gx, a, partial, m);        \
+  } while (0)
+        switch (n / 256) {
+          case 1: WROWH(1); break;
+          case 2: WROWH(2); break;
+          case 3: WROWH(3); break;
+          default: WROWH(4); break;
+        }
+#undef WROWH
+      }
+    }
+    if (half_plan) {
+    } else if (wnp > 0) {
       grid = static_cast<unsigned>(rms_rev_warp_grid(m, sms));
       slots = grid;
 #define WROW(NPV)                                                                                                          \
