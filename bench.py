@@ -503,7 +503,7 @@ def lm_launcher_work(label, cfg, batch, seqlen):
         return {"flops": ssd_flops(*dims, cfg.chunk, True), "bytes": ssd_bytes(*dims, True)}, "both"
     if label.startswith("ssd_scan"):
         return {"flops": ssd_flops(*dims, cfg.chunk, False), "bytes": ssd_bytes(*dims, False)}, "both"
-    m = re.match(r"inner_product_\w+\[(\d+)x(\d+)x(\d+)\]", label)
+    m = re.match(r"(?:inner_product|linear)_\w+\[(\d+)x(\d+)x(\d+)\]", label)
     if m:
         a, b, c = (int(v) for v in m.groups())
         return {"flops": 2.0 * a * b * c}, "tensor"

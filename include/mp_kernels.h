@@ -135,6 +135,8 @@ MP_DECL3(inner_product_ji_jk_ik, const void* a_data, const void* b_data, const d
 /* linear (README.md:81): C[m,k] = alpha*A[m,n]*B[n,k] + bias[k] + beta*C,
  * bias added in the GEMM epilogue. */
 MP_DECL3(linear_ij_jk_ik, const void* a_data, const void* b_data, const void* bias, const double alpha, void* c_data, const double beta, len_t m, len_t n, len_t k, StreamContext stream)
+/* c = alpha * a b + r + beta * c with a full [m, k] term r ("ij,jk,ik->ik": the residual form of linear; r may alias c when beta = 0) */
+MP_DECL3(linear_ij_jk_ik_ik, const void* a, const void* b, const void* r, double alpha, void* c, double beta, len_t m, len_t n, len_t k, StreamContext stream)
 
 /* Mamba-2 SSD chunked scan (no reference kernel; the op is named by the
  * project's roadmap only).  Per batch b, head h (group g = h / (heads/ngroups)):

@@ -59,6 +59,7 @@ LAUNCHERS = {
     "inner_product_ij_kj_ik": [P, P, D, P, D, L, L, L, CTX],
     "inner_product_ji_jk_ik": [P, P, D, P, D, L, L, L, CTX],
     "linear_ij_jk_ik": [P, P, P, D, P, D, L, L, L, CTX],
+    "linear_ij_jk_ik_ik": [P, P, P, D, P, D, L, L, L, CTX],
     "ssd_scan": [P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
     "ssd_scan_reverse": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
     # operators around the scan in a language-model step

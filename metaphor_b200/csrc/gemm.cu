@@ -5,6 +5,7 @@
 //   launch_inner_product_ij_kj_ik : A[M,K]      B[N,K]^T     (reference: transpose to
 //   launch_inner_product_ji_jk_ik : A[K,M]^T    B[K,N]        scratch + the call above)
 //   launch_linear_ij_jk_ik        : A[M,K]      B[K,N] + bias[N]
+//   launch_linear_ij_jk_ik_ik     : A[M,K]      B[K,N] + R[M,N]
 //
 // r16 and r32 run on the tcgen05 tensor cores: operand tiles are brought into
 // 128-byte-swizzled shared memory by TMA (one warp's elected thread), a single
@@ -32,7 +33,7 @@ template <typename T>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ a, const T* __restrict__ b,
                                                         const T* __restrict__ bias, typename Acc<T>::type alpha, T* c,
                                                         typename Acc<T>::type beta, size_t M, size_t N, size_t K, int a_mn,
-                                                        int b_mn) {
+                                                        int b_mn, size_t bias_pitch = 0) {
   using A = typename Acc<T>::type;
   constexpr int TS = 64, KS = 16;
   a += static_cast<size_t>(blockIdx.z) * M * K;   // batch entries are densely packed
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ a,
       const size_t gn = n0 + tx * 4 + j;
       if (gn >= N) continue;
       A r = alpha * acc[i][j];
-      if (bias != nullptr) r += mp_up(bias[gn]);
+      if (bias != nullptr) r += mp_up(bias[gm * bias_pitch + gn]);
       if (beta != A(0)) r += beta * mp_up(c[gm * N + gn]);
       c[gm * N + gn] = mp_down<T>(r);
     }
@@ -119,12 +120,15 @@ template <> struct GemmT<float> {
 };
 
 struct GemmArgs {
-  const void* bias;   // N values of T or nullptr
+  const void* bias;   // N values of T (bias_pitch = 0), a full [M, N] matrix (bias_pitch = N), or nullptr
+  size_t bias_pitch = 0;
   void* c;            // [M, N] row-major
   float alpha, beta;
   int M, N, K;
   int a_mn, b_mn;     // operand major-ness: 0 = K contiguous, 1 = M resp. N contiguous
   int stages;
+  int epi_boxes = 2;  // pair kernel: 64-column staging boxes per epilogue warp
+  int hot = 0;        // pair kernel: bit 0: producer / MMA thread poll their barriers before suspending; bit 1: epilogue warps too
   int split;          // r32 only: 1 = error-compensated hi/lo split (3 MMAs per k-slice)
   int ksplit;         // > 1: the K range of every tile is cut into ksplit work units whose raw fp32
   float* partial;     //      accumulators go to partial[unit_split][M][N]; a fold kernel finishes C
@@ -386,10 +390,11 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
         float r[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[j]);
-        if (bias != nullptr) {
+        if (bias != nullptr && (g.bias_pitch == 0 || row < g.M)) {
+          const T* brow = bias + static_cast<size_t>(row) * g.bias_pitch;
 #pragma unroll
           for (int j = 0; j < 32; ++j)
-            if (col0 + j < g.N) r[j] += mp_up(bias[col0 + j]);
+            if (col0 + j < g.N) r[j] += mp_up(brow[col0 + j]);
         }
         if (use_tma) {
           constexpr int PN = Pack<T>::N;
@@ -478,9 +483,9 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
 //   both ranks  warp 0: TMA producer; warps 2-9: epilogue of the rank's own 128 rows
 //   rank 0      warp 1: issues the pair MMAs, commits to its own barriers
 // Barriers live at the same offsets in both CTAs.  full[s]: rank 0 only, credited by both ranks' loads.
-// empty[s] / acc_full[b]: rank 0 gets the MMA commit, rank 1 a relayed arrival (rank 0's producer thread
-// resp. an epilogue thread forwards it once its own wait has passed).  acc_empty[b]: rank 0 only, one
-// arrival per epilogue warp of both ranks.  Every wait is bounded.
+// empty[s] / acc_full[b]: the MMA commit arrives on both CTAs' barriers (tcgen05.commit to a CTA mask).
+// acc_empty[b]: rank 0 only, one arrival per epilogue warp of both ranks.  Every wait is bounded; the waits on
+// the ring and the accumulators poll before they suspend.
 // ---------------------------------------------------------------------------
 constexpr int PAIR_BN = 256;
 constexpr int PAIR_STAGE_BYTES = BM * SWIZZLE_BYTES + (PAIR_BN / 2) * SWIZZLE_BYTES;   // 32 KB
@@ -504,7 +509,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   uint64_t* acc_empty = acc_full + ACC_BUFS;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
   volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  unsigned char* epi_stage = smem + static_cast<size_t>(stages) * PAIR_STAGE_BYTES + 1024;   // 8 warps x 2 boxes
+  unsigned char* epi_stage = smem + static_cast<size_t>(stages) * PAIR_STAGE_BYTES + 1024;   // 8 warps x 1 or 2 boxes
+  const int epi_boxes = g.epi_boxes;   // 1: a deeper operand ring; every box then waits for the previous store's read
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -544,11 +550,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         const int n0 = (tile / tiles_m) * BN + static_cast<int>(rank) * (BN / 2);
         const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) { ok = false; break; }
-          if (rank == 0) {
-            if (it >= stages) mbar_arrive_cluster(empty + s, 1);   // forward the stage release to rank 1
-            mbar_arrive_expect_tx(full + s, 2 * (A_BYTES + B_BYTES));
-          }
+          if (!((g.hot & 1) ? mbar_wait_hot(empty + s, phase ^ 1u, g.status, abort) : mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort))) { ok = false; break; }
+          if (rank == 0) mbar_arrive_expect_tx(full + s, 2 * (A_BYTES + B_BYTES));
           unsigned char* sa = smem + static_cast<size_t>(s) * PAIR_STAGE_BYTES;
           unsigned char* sb = sa + A_BYTES;
           const int k0 = kb * BK;
@@ -587,7 +590,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         const int sp = unit / num_tiles;
         const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait_abortable(full + s, phase, g.status, abort)) { ok = false; break; }
+          if (!((g.hot & 1) ? mbar_wait_hot(full + s, phase, g.status, abort) : mbar_wait_abortable(full + s, phase, g.status, abort))) { ok = false; break; }
           tcgen05_fence_after_sync();
           const uint32_t sa = mp_smem_u32(smem + static_cast<size_t>(s) * PAIR_STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -597,10 +600,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
             const uint64_t bd = umma_smem_desc(sb + ks * b_kstep, b_lbo, 1024);
             umma_pair_f16(tmem_acc, ad, bd, idesc, (kb != kb0 || ks != 0) ? 1u : 0u);
           }
-          umma_commit_pair(empty + s);
+          umma_commit_pair_to(empty + s, 3);   // the stage is free in both CTAs
           if (++s == stages) { s = 0; phase ^= 1u; }
         }
-        if (ok) umma_commit_pair(acc_full + buf);
+        if (ok) umma_commit_pair_to(acc_full + buf, 3);
       }
     }
   } else {
@@ -610,17 +613,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     const T* bias = static_cast<const T*>(g.bias);
     const bool vec_ok = (static_cast<size_t>(g.N) * sizeof(T)) % 16 == 0 && mp_aligned16(g.c);
     const bool use_tma = vec_ok && g.beta == 0.0f && g.ksplit == 1;
-    unsigned char* stage_base = epi_stage + (warp - 2) * (2 * BOX_BYTES);
+    unsigned char* stage_base = epi_stage + (warp - 2) * (epi_boxes * BOX_BYTES);
     int local = 0;
     for (int unit = pair; unit < num_units; unit += num_pairs, ++local) {
       const int tile = unit % num_tiles, sp = unit / num_tiles;
       const int buf = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       const int m0 = (tile % tiles_m) * 2 * BM + static_cast<int>(rank) * BM, n0 = (tile / tiles_m) * BN;
-      const bool acc_ready = mbar_wait_abortable(acc_full + buf, use & 1u, g.status, abort);
+      const bool acc_ready = (g.hot & 2) ? mbar_wait_hot(acc_full + buf, use & 1u, g.status, abort) : mbar_wait_abortable(acc_full + buf, use & 1u, g.status, abort);
       __syncwarp();
       if (!acc_ready) break;
-      if (rank == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(acc_full + buf, 1);   // forward to rank 1
       tcgen05_fence_after_sync();
       const uint32_t tmem_acc = tmem_base + buf * BN;
       const int row = m0 + quarter * 32 + lane;
@@ -655,8 +657,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
           continue;
         }
         constexpr int PN = Pack<T>::N;
-        unsigned char* box = stage_base + boxi * BOX_BYTES;
-        if (use_tma && boxi == 0) {   // the previous tile's stores have finished reading the staging boxes
+        unsigned char* box = stage_base + (epi_boxes == 2 ? boxi : 0) * BOX_BYTES;
+        if (use_tma && (boxi == 0 || epi_boxes == 1)) {   // the earlier stores have finished reading the staging box(es)
           if (lane == 0) bulk_wait_read<0>();
           __syncwarp();
         }
@@ -667,10 +669,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
           float r[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) r[j] = g.alpha * __uint_as_float(v[hb][j]);
-          if (bias != nullptr) {
+          if (bias != nullptr && (g.bias_pitch == 0 || row < g.M)) {
+            const T* brow = bias + static_cast<size_t>(row) * g.bias_pitch;
+            if (g.bias_pitch != 0 && colb + 32 <= g.N && (g.bias_pitch * sizeof(T)) % 16 == 0 && mp_aligned16(bias)) {
+              // a full-matrix term (a residual): the lane's 32 values are one contiguous 64-byte piece of its row
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (colb + j < g.N) r[j] += mp_up(bias[colb + j]);
+              for (int p = 0; p < 32 / PN; ++p) {
+                float add[PN];
+                unpack<T>(ld_pack(brow + colb, p), add);
+#pragma unroll
+                for (int e = 0; e < PN; ++e) r[p * PN + e] += add[e];
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (colb + j < g.N) r[j] += mp_up(brow[colb + j]);
+            }
           }
           if (use_tma) {
 #pragma unroll
@@ -730,7 +744,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 // C = alpha * sum_s partial[s] + bias + beta * C  (finishes a split-K contraction)
 template <typename T>
 __global__ void __launch_bounds__(256) gemm_fold_kernel(const float* __restrict__ partial, int ksplit, size_t mn, int N, float alpha,
-                                                        const T* __restrict__ bias, float beta, T* __restrict__ c) {
+                                                        const T* __restrict__ bias, float beta, T* __restrict__ c, size_t bias_pitch = 0) {
   const size_t i0 = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) * 4;
   if (i0 >= mn) return;
   const bool vec = (mn & 3) == 0;
@@ -747,7 +761,7 @@ __global__ void __launch_bounds__(256) gemm_fold_kernel(const float* __restrict_
   }
   for (int e = 0; e < cnt; ++e) {
     float o = alpha * acc[e];
-    if (bias != nullptr) o += mp_up(bias[(i0 + e) % N]);
+    if (bias != nullptr) o += mp_up(bias_pitch != 0 ? bias[(i0 + e) / N * bias_pitch + (i0 + e) % N] : bias[(i0 + e) % N]);
     if (beta != 0.0f) o += beta * mp_up(c[i0 + e]);
     c[i0 + e] = mp_down<T>(o);
   }
@@ -833,7 +847,7 @@ void launch_tc(const T* a, const T* b, const GemmArgs& args, int sm_count, cudaS
     const size_t mn = static_cast<size_t>(M) * N;
     gemm_fold_kernel<T><<<static_cast<unsigned>((mn / 4 + 256) / 256), 256, 0, st>>>(args.partial, args.ksplit, mn, N, args.alpha,
                                                                                   static_cast<const T*>(args.bias), args.beta,
-                                                                                  static_cast<T*>(args.c));
+                                                                                  static_cast<T*>(args.c), args.bias_pitch);
     MP_LAUNCH_CHECK();
   }
 }
@@ -846,8 +860,16 @@ void launch_pair(const __half* a, const __half* b, GemmArgs args, int sm_count, 
   const CUtensorMap tb = args.b_mn ? make_map<T>(b, K, N, G::BK, G::BK) : make_map<T>(b, N, K, G::BK, PAIR_BN / 2);
   CUtensorMap tc = ta;
   if ((static_cast<size_t>(N) * sizeof(T)) % 16 == 0 && mp_aligned16(args.c)) tc = make_store_map<T>(args.c, M, N, true);
-  args.stages = 5;
-  const size_t smem = static_cast<size_t>(args.stages) * PAIR_STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers*/ + 8 * 2 * 32 * 64 * sizeof(T);
+  // 227 KB: six 32 KB stages + one 4 KB staging box per epilogue warp, or five stages + two boxes.  The ring depth is what
+  // feeds the tensor pipe: a stage is refilled only after its MMAs have completed, so (stages - 1) x 32 KB are in flight
+  // per SM against an L2 latency of 2 - 3 k cycles under load (measured: the MMA thread waited for operands 35 - 40 % of
+  // every tile with five stages).
+  args.stages = 6;
+  args.epi_boxes = 1;
+  if (const char* e = getenv("MP_GEMM_HOT")) args.hot = atoi(e);
+  if (const char* e = getenv("MP_GEMM_PAIR_STAGES")) { if (atoi(e) == 5) { args.stages = 5; args.epi_boxes = 2; } }
+  const size_t smem = static_cast<size_t>(args.stages) * PAIR_STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers*/ +
+                      8 * args.epi_boxes * 32 * 64 * sizeof(T);
   MP_CUDA_CHECK(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   const int tiles = ((N + PAIR_BN - 1) / PAIR_BN) * ((M + 2 * BM - 1) / (2 * BM)) * args.ksplit;
   const int pairs = tiles < sm_count / 2 ? tiles : sm_count / 2;
@@ -857,7 +879,7 @@ void launch_pair(const __half* a, const __half* b, GemmArgs args, int sm_count, 
     const size_t mn = static_cast<size_t>(M) * N;
     gemm_fold_kernel<T><<<static_cast<unsigned>((mn / 4 + 256) / 256), 256, 0, st>>>(args.partial, args.ksplit, mn, N, args.alpha,
                                                                                   static_cast<const T*>(args.bias), args.beta,
-                                                                                  static_cast<T*>(args.c));
+                                                                                  static_cast<T*>(args.c), args.bias_pitch);
     MP_LAUNCH_CHECK();
   }
 }
@@ -914,7 +936,7 @@ void pick_split_k(GemmArgs& args, size_t elem, int sms, size_t workspace_bytes, 
 
 template <typename T>
 void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alpha, void* c_, double beta, len_t M, len_t N,
-                   len_t K, int a_mn, int b_mn, StreamContext ctx, len_t batch = 1) {
+                   len_t K, int a_mn, int b_mn, StreamContext ctx, len_t batch = 1, len_t bias_pitch = 0) {
   using A = typename Acc<T>::type;
   if (M == 0 || N == 0 || batch == 0) return;
   cudaStream_t st = mp_stream(ctx);
@@ -939,7 +961,7 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
       const len_t nb = batch - b0 < 65535 ? batch - b0 : 65535;
       const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((M + 63) / 64), static_cast<unsigned>(nb));
       gemm_simt_kernel<T><<<grid, 256, 0, st>>>(a + b0 * M * K, b + b0 * K * N, static_cast<const T*>(bias), static_cast<A>(alpha),
-                                                c + b0 * M * N, static_cast<A>(beta), M, N, K, a_mn, b_mn);
+                                                c + b0 * M * N, static_cast<A>(beta), M, N, K, a_mn, b_mn, bias_pitch);
       MP_LAUNCH_CHECK();
     }
     return;
@@ -948,6 +970,7 @@ void gemm_dispatch(const void* a_, const void* b_, const void* bias, double alph
     MpStreamState* state = mp_state(ctx);
     GemmArgs args;
     args.bias = bias;
+    args.bias_pitch = bias_pitch;
     args.c = c;
     args.alpha = static_cast<float>(alpha);
     args.beta = static_cast<float>(beta);
@@ -1021,6 +1044,13 @@ static void inner_product_ji_jk_ik_impl(const void* a, const void* b, double alp
                                         len_t k, StreamContext ctx) {
   gemm_dispatch<T>(a, b, nullptr, alpha, c, beta, m, k, n, 1, 1, ctx);  // A[n,m] M-contiguous
 }
+// C = alpha * A B + R + beta * C with a full [m, k] term R (a residual stream: R may be C itself when beta = 0)
+template <typename T>
+static void linear_ij_jk_ik_ik_impl(const void* a, const void* b, const void* r, double alpha, void* c, double beta, len_t m, len_t n, len_t k,
+                                    StreamContext ctx) {
+  gemm_dispatch<T>(a, b, r, alpha, c, beta, m, k, n, 0, 1, ctx, 1, r != nullptr ? k : 0);
+}
+
 template <typename T>
 static void linear_ij_jk_ik_impl(const void* a, const void* b, const void* bias, double alpha, void* c, double beta, len_t m,
                                  len_t n, len_t k, StreamContext ctx) {
@@ -1050,4 +1080,5 @@ MP_STAMP3(inner_product_bji_bjk_bik, (const void* a, const void* b, const double
 MP_STAMP3(inner_product_ij_jk_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))
 MP_STAMP3(inner_product_ij_kj_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))
 MP_STAMP3(inner_product_ji_jk_ik, (const void* a, const void* b, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, alpha, c, beta, m, n, k, s))
+MP_STAMP3(linear_ij_jk_ik_ik, (const void* a, const void* b, const void* r, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, r, alpha, c, beta, m, n, k, s))
 MP_STAMP3(linear_ij_jk_ik, (const void* a, const void* b, const void* bias, const double alpha, void* c, const double beta, len_t m, len_t n, len_t k, StreamContext s), (a, b, bias, alpha, c, beta, m, n, k, s))

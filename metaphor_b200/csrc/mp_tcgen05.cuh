@@ -168,6 +168,23 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
   }
 }
 
+// The same wait for hand-offs that sit on a kernel's critical path (a stage of an operand ring coming free, an
+// accumulator becoming ready): polls without a suspend hint first - a suspended warp wakes up hundreds of cycles
+// after the phase completes - and only then falls back to the bounded, abortable wait above.
+__device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, uint32_t* status, volatile int* abort) {
+#pragma unroll 1
+  for (int i = 0; i < 2048; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(mp_smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
+  return mbar_wait_abortable(bar, parity, status, abort);
+}
+
 // ------------------------------ CTA pairs (cta_group::2) ---------------------
 // Two CTAs of a cluster (ranks 0 and 1) work on one 256-row tile: each holds its 128 rows of A and one
 // half of B's columns in its own shared memory and its 128 accumulator rows in its own TMEM; the MMA is
@@ -215,6 +232,14 @@ __device__ __forceinline__ void umma_pair_f16(uint32_t tmem_d, uint64_t adesc, u
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// One arrival on the barrier at `bar`'s offset in EVERY CTA of `cta_mask` (bit i = cluster rank i) when every pair
+// MMA issued so far by this thread has completed: both CTAs of a pair learn of a free stage / a finished
+// accumulator from the hardware instead of through a relayed software arrival.
+__device__ __forceinline__ void umma_commit_pair_to(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(mp_smem_u32(bar)),
+               "h"(cta_mask)
+               : "memory");
 }
 // One arrival on rank 0's barrier when every pair MMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {

@@ -176,7 +176,6 @@ class MambaLM:
         # residual stream: the input of layer i is saved[i]["h_in"], its output is written straight into the next
         # layer's h_in (the last one into h_out), so nothing is copied
         self.h_out = f16(T, c.d_model)
-        self.o = f16(T, c.d_model)
         self.hn = f16(T, c.d_model)
         self.rstdf = f32(T)
         self.logits = f16(T, c.vocab)
@@ -224,7 +223,7 @@ class MambaLM:
     def _L(self, name, *args):
         import torch
         label = name + "_r16"
-        if name.startswith("inner_product"):
+        if name.startswith(("inner_product", "linear")):
             label += "[%dx%dx%d]" % tuple(args[-3:])
         self._timed(label, lambda: launch(name, torch.float16, *args, self.stream))
 
@@ -291,8 +290,8 @@ class MambaLM:
             # skip, gate and the gated norm in one pass; the gated activation itself is never stored
             self._L("ssd_gate_rmsnorm", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, self._p(W, p + "gnorm_w"), c.eps, sv["un"],
                     sv["rstd2"], T, H, P)
-            self._L("inner_product_ij_jk_ik", sv["un"], self._p(W, p + "out_proj"), 1.0, self.o, 0.0, T, di, c.d_model)
-            self._L("addition", sv["h_in"], self.o, h_next, T * c.d_model)
+            # out-projection with the residual added in its epilogue: h_next = un W + h_in
+            self._L("linear_ij_jk_ik_ik", sv["un"], self._p(W, p + "out_proj"), sv["h_in"], 1.0, h_next, 0.0, T, di, c.d_model)
         self._L("rmsnorm_ij_j", self.h_out, self._p(W, "normf_w"), c.eps, self.hn, self.rstdf, T, c.d_model)
         self._L("inner_product_ij_kj_ik", self.hn, self._p(W, "embedding"), 1.0, self.logits, 0.0, T, c.d_model, c.vocab)
 

@@ -53,6 +53,25 @@ def test_linear_adds_bias_in_the_epilogue(mp, stream, orc, sfx, shape):
     assert_close(host(c), narrow(ref, sfx), TOL_RED[sfx], f"linear {sfx} {shape}")
 
 
+# The residual form "ij,jk,ik->ik": a full [m, k] term added in the epilogue.  Shapes reach the FP-pipe kernel, the
+# single-CTA tensor kernel, the CTA-pair kernel (>= 74 tiles of 256 x 256, ragged last column tile) and the split-K fold.
+@pytest.mark.parametrize("sfx", DTYPES)
+@pytest.mark.parametrize("shape", [(5, 7, 3), (129, 72, 200), (300, 40, 264), (2560, 64, 1992), (256, 4096, 512)])
+def test_linear_with_a_full_matrix_term(mp, stream, orc, sfx, shape):
+    m, n, k = shape
+    a, b = operands(sfx, m, n, k, False, False, seed=5)
+    r = rng_normal(11, (m, k), sfx)
+    c = dev(np.full((m, k), np.nan, a.dtype))
+    run(mp, stream, "linear_ij_jk_ik_ik", sfx, dev(a), dev(b), dev(r), 0.5, c, 0.0, m, n, k)
+    ref = orc.inner_product(wide(a), wide(b), 0.5) + wide(r)
+    assert_close(host(c), narrow(ref, sfx), TOL_RED[sfx], f"linear + matrix {sfx} {shape}")
+    # in place on the residual stream: r is also the output
+    rc = dev(r.copy())
+    run(mp, stream, "linear_ij_jk_ik_ik", sfx, dev(a), dev(b), rc, 0.5, rc, 0.0, m, n, k)
+    assert_close(host(rc), narrow(ref, sfx), TOL_RED[sfx], f"linear + matrix in place {sfx} {shape}")
+    assert stream.status() == 0
+
+
 BATCHED = [("inner_product_bij_bjk_bik", False, False), ("inner_product_bij_bkj_bik", False, True),
            ("inner_product_bji_bjk_bik", True, False)]
 # (batch, m, n, k): tiles cut at the edges of every batch entry, one entry, odd pitches (FP-pipe kernel), deep n
