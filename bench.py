@@ -699,7 +699,7 @@ def run_lm(args):
             roofline.update({k: v for k, v in rr.items() if k.startswith("algorithmic")})
         roofline["step_model_flops"] = {"achieved_TFLOP/s": round(flops / (ms_per_step * 1e-3) / 1e12, 1), "flops": flops,
                                         "frac_of_sustained_peak": round(flops / (ms_per_step * 1e-3) / 1e12 / sustained, 4)}
-        roofline["launchers_ms"] = {k: {"ms": round(v["ms"], 3), "calls": v["calls"]} for k, v in top[:14]}
+        roofline["launchers_ms"] = {k: {"ms": round(v["ms"], 3), "calls": v["calls"]} for k, v in top}
         out = {
             "metric": LM_METRIC, "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3), "higher_is_better": True,

@@ -128,7 +128,6 @@ struct GemmArgs {
   int a_mn, b_mn;     // operand major-ness: 0 = K contiguous, 1 = M resp. N contiguous
   int stages;
   int epi_boxes = 2;  // pair kernel: 64-column staging boxes per epilogue warp
-  int hot = 0;        // pair kernel: bit 0: producer / MMA thread poll their barriers before suspending; bit 1: epilogue warps too
   int split;          // r32 only: 1 = error-compensated hi/lo split (3 MMAs per k-slice)
   int ksplit;         // > 1: the K range of every tile is cut into ksplit work units whose raw fp32
   float* partial;     //      accumulators go to partial[unit_split][M][N]; a fold kernel finishes C
@@ -484,8 +483,8 @@ __global__ void __launch_bounds__(GEMM_MAX_THREADS, 1) gemm_tcgen05_kernel(const
 //   rank 0      warp 1: issues the pair MMAs, commits to its own barriers
 // Barriers live at the same offsets in both CTAs.  full[s]: rank 0 only, credited by both ranks' loads.
 // empty[s] / acc_full[b]: the MMA commit arrives on both CTAs' barriers (tcgen05.commit to a CTA mask).
-// acc_empty[b]: rank 0 only, one arrival per epilogue warp of both ranks.  Every wait is bounded; the waits on
-// the ring and the accumulators poll before they suspend.
+// acc_empty[b]: rank 0 only, one arrival per epilogue warp of both ranks.  Every wait is bounded and suspends between
+// polls: polling the ring barriers without a suspend hint (as the scan's chunk walk does) made every shape 5 - 8 % slower.
 // ---------------------------------------------------------------------------
 constexpr int PAIR_BN = 256;
 constexpr int PAIR_STAGE_BYTES = BM * SWIZZLE_BYTES + (PAIR_BN / 2) * SWIZZLE_BYTES;   // 32 KB
@@ -550,7 +549,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         const int n0 = (tile / tiles_m) * BN + static_cast<int>(rank) * (BN / 2);
         const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb, ++it) {
-          if (!((g.hot & 1) ? mbar_wait_hot(empty + s, phase ^ 1u, g.status, abort) : mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort))) { ok = false; break; }
+          if (!mbar_wait_abortable(empty + s, phase ^ 1u, g.status, abort)) { ok = false; break; }
           if (rank == 0) mbar_arrive_expect_tx(full + s, 2 * (A_BYTES + B_BYTES));
           unsigned char* sa = smem + static_cast<size_t>(s) * PAIR_STAGE_BYTES;
           unsigned char* sb = sa + A_BYTES;
@@ -590,7 +589,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         const int sp = unit / num_tiles;
         const int kb0 = sp * kb_per, kb1 = min(num_kb, kb0 + kb_per);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!((g.hot & 1) ? mbar_wait_hot(full + s, phase, g.status, abort) : mbar_wait_abortable(full + s, phase, g.status, abort))) { ok = false; break; }
+          if (!mbar_wait_abortable(full + s, phase, g.status, abort)) { ok = false; break; }
           tcgen05_fence_after_sync();
           const uint32_t sa = mp_smem_u32(smem + static_cast<size_t>(s) * PAIR_STAGE_BYTES);
           const uint32_t sb = sa + A_BYTES;
@@ -620,7 +619,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       const int buf = local & 1;
       const uint32_t use = static_cast<uint32_t>(local >> 1);
       const int m0 = (tile % tiles_m) * 2 * BM + static_cast<int>(rank) * BM, n0 = (tile / tiles_m) * BN;
-      const bool acc_ready = (g.hot & 2) ? mbar_wait_hot(acc_full + buf, use & 1u, g.status, abort) : mbar_wait_abortable(acc_full + buf, use & 1u, g.status, abort);
+      const bool acc_ready = mbar_wait_abortable(acc_full + buf, use & 1u, g.status, abort);
       __syncwarp();
       if (!acc_ready) break;
       tcgen05_fence_after_sync();
@@ -866,7 +865,6 @@ void launch_pair(const __half* a, const __half* b, GemmArgs args, int sm_count, 
   // every tile with five stages).
   args.stages = 6;
   args.epi_boxes = 1;
-  if (const char* e = getenv("MP_GEMM_HOT")) args.hot = atoi(e);
   if (const char* e = getenv("MP_GEMM_PAIR_STAGES")) { if (atoi(e) == 5) { args.stages = 5; args.epi_boxes = 2; } }
   const size_t smem = static_cast<size_t>(args.stages) * PAIR_STAGE_BYTES + 1024 /*align*/ + 1024 /*barriers*/ +
                       8 * args.epi_boxes * 32 * 64 * sizeof(T);

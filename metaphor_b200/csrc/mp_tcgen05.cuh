@@ -168,23 +168,6 @@ __device__ __forceinline__ bool mbar_wait_abortable(uint64_t* bar, uint32_t pari
   }
 }
 
-// The same wait for hand-offs that sit on a kernel's critical path (a stage of an operand ring coming free, an
-// accumulator becoming ready): polls without a suspend hint first - a suspended warp wakes up hundreds of cycles
-// after the phase completes - and only then falls back to the bounded, abortable wait above.
-__device__ __forceinline__ bool mbar_wait_hot(uint64_t* bar, uint32_t parity, uint32_t* status, volatile int* abort) {
-#pragma unroll 1
-  for (int i = 0; i < 2048; ++i) {
-    uint32_t done;
-    asm volatile(
-        "{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-        : "=r"(done)
-        : "r"(mp_smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (done) return true;
-  }
-  return mbar_wait_abortable(bar, parity, status, abort);
-}
-
 // ------------------------------ CTA pairs (cta_group::2) ---------------------
 // Two CTAs of a cluster (ranks 0 and 1) work on one 256-row tile: each holds its 128 rows of A and one
 // half of B's columns in its own shared memory and its 128 accumulator rows in its own TMEM; the MMA is

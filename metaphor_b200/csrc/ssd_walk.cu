@@ -186,7 +186,6 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
             umma<false>(ty + 64, umma_smem_desc(sq + o, 16, 1024), umma_smem_desc(sh + ks * 2048, W_TILE_V, 1024), id_y, ks != 0 ? 1u : 0u);
           }
         }
-        if (g.hs_out != nullptr && k > 0) bulk_wait_read<0>();   // the workers rewrite the state tile after this phase
         umma_commit(bars + B_YFULL);
         // scores of the next chunk (its stage was released by S(k-1); the workers are past G(k))
         if (k + 1 < nc) {
@@ -201,6 +200,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
         for (int ks = 0; ks < 8; ++ks)
           umma<false>(tmem + TC_S, umma_smem_desc(sk + ks * 2048, WQ * 128, 1024), umma_smem_desc(svs + ks * 2048, W_TILE_V, 1024), id_s,
                       ks != 0 ? 1u : 0u);
+        // The workers rewrite the state tile once S(k) is complete: the store issued above must have read it by then.
+        // (Waiting here, behind the next chunk's score MMAs, costs nothing; waiting right after the store held back
+        // the commit of the output accumulators by the store's whole latency in every chunk.)
+        if (g.hs_out != nullptr && k > 0) bulk_wait_read<0>();
         umma_commit(bars + B_SFULL);
         umma_commit(bars + B_EMPTY0 + s);
       }
