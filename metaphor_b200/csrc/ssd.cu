@@ -949,8 +949,8 @@ extern "C" len_t mpSsdScanScratchBytes(len_t batch, len_t seqlen, len_t heads, l
   if (!ssd_tensor_path(d)) return mpSsdScanGenericScratchBytes(0, batch, seqlen, heads, headdim, dstate, ngroups, reverse);
   if (mp_ssd_walk_supported(d.L, d.H, d.P, d.N, d.G)) {
     if (reverse != 0) return walk_carve(nullptr, d, true, 0).total;
-    const size_t a = walk_carve(nullptr, d, false, 0).total, b = ssd_carve(nullptr, d, false).total;   // either forward path
-    return a > b ? a : b;
+    // (the three-phase forward, an A/B switch, needs its own larger scratch: ask with the switch set)
+    return getenv("MP_SSD_LEGACY_FORWARD") == nullptr ? walk_carve(nullptr, d, false, 0).total : ssd_carve(nullptr, d, false).total;
   }
   return ssd_carve(nullptr, d, reverse != 0).total;
 }
