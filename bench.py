@@ -281,7 +281,7 @@ def run_rows(args, standalone=True):
             "ref_cuda": "no reference kernel (the reference has neither softmax nor RMSNorm)",
         }
         if standalone:
-            print(json.dumps(out), flush=True)
+            emit(json.dumps(out), flush=True)
     del bufs
     torch.cuda.empty_cache()
     stream.close()
@@ -449,7 +449,7 @@ def run_reference_rows(args):
     value = round(nbytes / dt / 1e9, 3)
     sample = (f"each step = first {rows} of {M} rows, scalar C oracle port (the reference has no kernel for these "
               f"ops), {threads} host threads")
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded)",
@@ -561,7 +561,7 @@ def run_reference_lm(args):
     sample = (f"each step = the full-width model (24 layers, vocab 50280) on {ORACLE_BATCH} x {ORACLE_SEQ} tokens instead of 8 x 2048 "
               f"(tokens/s is size-normalised), float64 oracle port: sequential-recurrence scan, torch autograd, Adam; {threads} host threads; "
               f"{steps} timed steps (of the {args.steps} asked for) after {warmup} warm-up; the reference itself has no CPU code and no kernels for most of this step")
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": LM_METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup, "ms_per_step": round(dt * 1e3, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f64", "data": "synthetic (token ids ~ U[0, 50280), seed 1000; weights N(0, 0.02), seed 0)",
@@ -737,7 +737,7 @@ def run_lm(args):
             out["per_config"] = run_per_config(args, mp)
         else:
             out["per_config"] = "skipped (--no-per-config)" if world == 1 else "reported at N = 1 only (rank 0 of a single-GPU run)"
-        print(json.dumps(out), flush=True)
+        emit(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -791,13 +791,34 @@ def run_profile_case(spec: str, timed: bool = False):
     if timed:
         rec = case.measure(s, bc.Flusher(mp, s), iters=20)
         rec["case"] = spec
-        print(json.dumps(rec))
+        emit(json.dumps(rec))
     if s.status() != 0:
         raise SystemExit("status word set")
     s.close()
 
 
+_RESULT_FD = None
+
+
+def own_stdout():
+    """Libraries loaded by the run (NCCL with NCCL_DEBUG set, torchrun's children) write to file descriptor 1; the result
+    line must be the only thing on it.  From here on descriptor 1 is a copy of stderr and `emit` writes to the old one."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line, flush=True):
+    if _RESULT_FD is None:
+        sys.stdout.write(line + "\n"); sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, (line + "\n").encode())
+
+
 def main():
+    own_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
