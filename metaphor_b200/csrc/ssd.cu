@@ -908,9 +908,10 @@ void mp_ssd_generic_reverse_r16(const void* x, const void* dt, const void* A, co
 // chunk-walk kernels (ssd_walk.cu)
 bool mp_ssd_walk_supported(int L, int H, int P, int N, int G);
 void mp_ssd_walk_cumsum(const float* dt, const float* A, float* cum, float* dtt, float* colf_c, float* colf_a, int B, int L, int H,
-                        cudaStream_t st);
+                        int* carry_flags, int n_flags, cudaStream_t st);
 void mp_ssd_walk(int anti, const __half* q, const __half* k, const __half* v, const float* cum, const float* dtt, const float* colf, __half* out,
-                 const __half* z, float* dot_out, __half* hs_out, int B, int L, int H, int G, uint32_t* status, cudaStream_t st);
+                 const __half* z, float* dot_out, __half* hs_out, float* carry, int* carry_flag, int max_ctas, int B, int L, int H, int G,
+                 uint32_t* status, cudaStream_t st);
 
 void mp_ssd_group_grads(const __half* gy, const __half* x, const __half* Bm, const __half* Cm, const __half* hs_causal, const __half* hs_anti,
                         const float* cum, const float* dtt, const float* colf_c, __half* gB, __half* gC, int B, int L, int H, int G,
@@ -919,7 +920,7 @@ void mp_ssd_group_grads(const __half* gy, const __half* x, const __half* Bm, con
 namespace {
 // Scratch of the walk path: prefix sums and dt in [B,H,L] order; for the reverse also the states every 128-step
 // chunk receives from its predecessors and from its successors (r16 [B,H,L/128][128][64]).
-struct WalkScratch { float* cum; float* dtt; float* colf_c; float* colf_a; __half* hs_causal; __half* hs_anti; float* pin; float* u; float* v; float* ga_part; size_t total; };
+struct WalkScratch { float* cum; float* dtt; float* colf_c; float* colf_a; __half* hs_causal; __half* hs_anti; float* pin; float* u; float* v; float* ga_part; float* carry_c; float* carry_a; int* flags; size_t total; };
 WalkScratch walk_carve(void* base, const SsdDims& d, bool reverse, size_t off0) {
   WalkScratch w;
   size_t off = off0;
@@ -936,6 +937,11 @@ WalkScratch walk_carve(void* base, const SsdDims& d, bool reverse, size_t off0) 
   w.u = static_cast<float*>(take(reverse ? 2 * bhl * 4 : 0));     // one array per half of the columns
   w.v = static_cast<float*>(take(reverse ? 2 * bhl * 4 : 0));
   w.ga_part = static_cast<float*>(take(reverse ? static_cast<size_t>(d.B) * d.H * 4 : 0));
+  // states handed from CTA to CTA inside a walk (fp32 [128][64] per sequence and walk) and their arrival counters
+  const size_t carry = static_cast<size_t>(d.B) * d.H * 128 * 64 * 4;
+  w.carry_c = static_cast<float*>(take(carry));
+  w.carry_a = static_cast<float*>(take(reverse ? carry : 0));
+  w.flags = static_cast<int*>(take(2 * static_cast<size_t>(d.B) * d.H * 4));
   w.total = off;
   return w;
 }
@@ -973,9 +979,11 @@ extern "C" void launch_ssd_scan_r16(const void* x, const void* dt, const void* A
   // path (scores, chunk states, scan, output as separate kernels), which also serves head size 128.
   if (mp_ssd_walk_supported(d.L, d.H, d.P, d.N, d.G) && getenv("MP_SSD_LEGACY_FORWARD") == nullptr) {
     const WalkScratch w = walk_carve(scratch, d, false, 0);
-    mp_ssd_walk_cumsum(static_cast<const float*>(dt), static_cast<const float*>(A), w.cum, w.dtt, w.colf_c, nullptr, d.B, d.L, d.H, st);
+    mp_ssd_walk_cumsum(static_cast<const float*>(dt), static_cast<const float*>(A), w.cum, w.dtt, w.colf_c, nullptr, d.B, d.L, d.H, w.flags,
+                       2 * d.B * d.H, st);
     mp_ssd_walk(0, static_cast<const __half*>(Cm), static_cast<const __half*>(Bm), static_cast<const __half*>(x), w.cum, w.dtt, w.colf_c,
-                static_cast<__half*>(y), nullptr, nullptr, nullptr, d.B, d.L, d.H, d.G, state->status_dev, st);
+                static_cast<__half*>(y), nullptr, nullptr, nullptr, w.carry_c, w.flags, state->sm_count, d.B, d.L, d.H, d.G, state->status_dev,
+                st);
     return;
   }
   const SsdScratch sc = ssd_carve(scratch, d, false);
@@ -1021,15 +1029,20 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
     const WalkScratch w = walk_carve(scratch, d, true, 0);
     const bool side = getenv("MP_SSD_SERIAL") == nullptr;
     cudaStream_t lane1 = st;
-    mp_ssd_walk_cumsum(static_cast<const float*>(dt), static_cast<const float*>(A), w.cum, w.dtt, w.colf_c, w.colf_a, d.B, d.L, d.H, st);
+    mp_ssd_walk_cumsum(static_cast<const float*>(dt), static_cast<const float*>(A), w.cum, w.dtt, w.colf_c, w.colf_a, d.B, d.L, d.H, w.flags,
+                       2 * d.B * d.H, st);
+    // side by side each walk takes half of the SMs (a CTA fills an SM), one after the other all of them
+    const int walk_ctas = side ? state->sm_count / 2 : state->sm_count;
     if (side) {
       mp_aux_init(state);
       lane1 = state->aux_stream[0];
       MP_CUDA_CHECK(cudaEventRecord(state->aux_fork, st));
       MP_CUDA_CHECK(cudaStreamWaitEvent(lane1, state->aux_fork, 0));
     }
-    mp_ssd_walk(1, bh, ch, gyh, w.cum, w.dtt, w.colf_a, static_cast<__half*>(gx), xh, w.v, w.hs_anti, d.B, d.L, d.H, d.G, state->status_dev, st);
-    mp_ssd_walk(0, ch, bh, xh, w.cum, w.dtt, w.colf_c, nullptr, gyh, w.u, w.hs_causal, d.B, d.L, d.H, d.G, state->status_dev, lane1);
+    mp_ssd_walk(1, bh, ch, gyh, w.cum, w.dtt, w.colf_a, static_cast<__half*>(gx), xh, w.v, w.hs_anti, w.carry_a, w.flags + d.B * d.H, walk_ctas,
+                d.B, d.L, d.H, d.G, state->status_dev, st);
+    mp_ssd_walk(0, ch, bh, xh, w.cum, w.dtt, w.colf_c, nullptr, gyh, w.u, w.hs_causal, w.carry_c, w.flags, walk_ctas, d.B, d.L, d.H, d.G,
+                state->status_dev, lane1);
     if (side) {
       MP_CUDA_CHECK(cudaEventRecord(state->aux_join[0], lane1));
       MP_CUDA_CHECK(cudaStreamWaitEvent(st, state->aux_join[0], 0));

@@ -1,7 +1,9 @@
-// Mamba-2 SSD scan as a chunk walk: one CTA per (batch, head) goes through the
-// sequence 128 steps at a time and keeps the carried state on chip, so no chunk
-// state is written to or scanned from global memory.  The same kernel evaluates
-// the operator in both directions,
+// Mamba-2 SSD scan as a chunk walk: a CTA goes through a (batch, head) sequence
+// 128 steps at a time and keeps the carried state on chip, so no chunk state is
+// written to or scanned from global memory.  The grid is one CTA per SM slot and
+// every CTA walks the same number of chunks: where a CTA's range ends inside a
+// sequence, the state crosses to the next CTA once, through global memory
+// (walk_segment).  The same kernel evaluates the operator in both directions,
 //     out_i = r_i * sum_j mask(i,j) * decay(i,j) * c_j * <q_i, k_j> * v_j
 //   causal      : j <= i, decay = exp(cum_i - cum_j), c_j = dt_j, r_i = 1       (chunks first to last)
 //   anti-causal : j >= i, decay = exp(cum_j - cum_i), c_j = 1,    r_i = dt_i    (chunks last to first)
@@ -55,8 +57,33 @@ struct WalkArgs {
   const __half* z;         // dot partner, same indexing as out, or null
   float* dot_out;          // [2][B, H, L] row dots <z, out> from the fp32 accumulators, one array per half of the columns, or null
   __half* hs_out;          // [B, H, nc][128][64]: state every chunk receives, or null
+  float* carry;            // [B * H][128][64] fp32: state handed from the CTA that walked the first part of a sequence to the next
+  int* carry_flag;         // [B * H]: number of worker warps (of 8) that have written their part of `carry`; zero before the launch
   uint32_t* status;
 };
+
+// A CTA walks a contiguous range of the B * H * nc chunk positions (position = index in walk order, so that every CTA
+// gets the same number of chunks whatever B * H is against the number of SMs).  A range is at least one sequence
+// long, hence: the last part of one sequence, whole sequences, the first part of another.  The first part is walked
+// FIRST and leaves its final state in `carry`; the last part is walked LAST and starts from the state the
+// neighbouring CTA left there - long before, so the wait on `carry_flag` does not hold anything up (it is bounded).
+struct WalkSeg { int seq, p0, n, cin, cout; };
+__device__ __forceinline__ bool walk_segment(int cta, int ncta, int nseq, int nc, int idx, WalkSeg& sg) {
+  const long long U = static_cast<long long>(nseq) * nc;
+  const long long lo = cta * U / ncta, hi = (cta + 1) * U / ncta;
+  const int s_lo = static_cast<int>(lo / nc), j_lo = static_cast<int>(lo % nc);
+  const int s_hi = static_cast<int>(hi / nc), j_hi = static_cast<int>(hi % nc);
+  const int first_whole = s_lo + (j_lo != 0 ? 1 : 0), n_whole = s_hi - first_whole;
+  int i = idx;
+  if (j_hi != 0) {
+    if (i == 0) { sg.seq = s_hi; sg.p0 = 0; sg.n = j_hi; sg.cin = 0; sg.cout = 1; return true; }
+    --i;
+  }
+  if (i < n_whole) { sg.seq = first_whole + i; sg.p0 = 0; sg.n = nc; sg.cin = 0; sg.cout = 0; return true; }
+  i -= n_whole;
+  if (j_lo != 0 && i == 0) { sg.seq = s_lo; sg.p0 = j_lo; sg.n = nc - j_lo; sg.cin = 1; sg.cout = 0; return true; }
+  return false;
+}
 
 __device__ __forceinline__ float w_exp(float x) { return __expf(x); }
 
@@ -104,9 +131,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
   float* s_colf = s_cum + WQ;                                         // [128]
   float* s_dt = s_colf + WQ;                                          // [128]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int h = blockIdx.x % g.H, b = blockIdx.x / g.H;
-  const int grp = h / (g.H / g.G);
   const int nc = g.nc;
+  const int nseq = g.B * g.H, cta = blockIdx.x, ncta = gridDim.x;
 
   if (threadIdx.x == 0) {
     mbar_init(bars + B_FULL0, 1); mbar_init(bars + B_FULL1, 1);
@@ -127,18 +153,27 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      for (int k = 0; k < nc; ++k) {
-        const int c = ANTI ? nc - 1 - k : k;
-        const int s = k & 1;
-        if (!walk_wait(bars + B_EMPTY0 + s, ((k >> 1) & 1) ^ 1u, g.status, abort)) break;
-        unsigned char* st = smem + s * W_STAGE;
-        const int row0 = b * g.L + c * WQ;
-        mbar_arrive_expect_tx(bars + B_FULL0 + s, W_STAGE);
-        tma_load_2d(st, &map_q, grp * WN, row0, bars + B_FULL0 + s);
-        tma_load_2d(st + WQ * 128, &map_q, grp * WN + 64, row0, bars + B_FULL0 + s);
-        tma_load_2d(st + W_TILE_QK, &map_k, grp * WN, row0, bars + B_FULL0 + s);
-        tma_load_2d(st + W_TILE_QK + WQ * 128, &map_k, grp * WN + 64, row0, bars + B_FULL0 + s);
-        tma_load_2d(st + 2 * W_TILE_QK, &map_v, h * WP, row0, bars + B_FULL0 + s);
+      WalkSeg sg;
+      int qb = 0;   // chunks walked by this CTA before the segment in hand: the barriers' phases run on across segments
+      bool ok = true;
+      for (int si = 0; ok && walk_segment(cta, ncta, nseq, nc, si, sg); ++si) {
+        const int h = sg.seq % g.H, b = sg.seq / g.H;
+        const int grp = h / (g.H / g.G);
+        for (int k = 0; k < sg.n; ++k) {
+          const int q = qb + k;
+          const int c = ANTI ? nc - 1 - (sg.p0 + k) : sg.p0 + k;
+          const int s = q & 1;
+          if (!walk_wait(bars + B_EMPTY0 + s, ((q >> 1) & 1) ^ 1u, g.status, abort)) { ok = false; break; }
+          unsigned char* st = smem + s * W_STAGE;
+          const int row0 = b * g.L + c * WQ;
+          mbar_arrive_expect_tx(bars + B_FULL0 + s, W_STAGE);
+          tma_load_2d(st, &map_q, grp * WN, row0, bars + B_FULL0 + s);
+          tma_load_2d(st + WQ * 128, &map_q, grp * WN + 64, row0, bars + B_FULL0 + s);
+          tma_load_2d(st + W_TILE_QK, &map_k, grp * WN, row0, bars + B_FULL0 + s);
+          tma_load_2d(st + W_TILE_QK + WQ * 128, &map_k, grp * WN + 64, row0, bars + B_FULL0 + s);
+          tma_load_2d(st + 2 * W_TILE_QK, &map_v, h * WP, row0, bars + B_FULL0 + s);
+        }
+        qb += sg.n;
       }
     }
   } else if (warp == 1) {
@@ -159,53 +194,63 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
         }
         umma_commit(bars + B_GFULL);
       };
-      bool ok = walk_wait(bars + B_FULL0, 0, g.status, abort);
-      if (ok) { tcgen05_fence_after_sync(); issue_g(0); }
-      for (int k = 0; ok && k < nc; ++k) {
-        const int s = k & 1;
-        const uint32_t sq = mp_smem_u32(smem + s * W_STAGE), sk = sq + W_TILE_QK, sv = sk + W_TILE_QK;
-        const uint32_t ty = tmem + TC_Y + (k & 1) * 128;
-        if (!walk_wait(bars + B_PREADY, k & 1, g.status, abort)) { ok = false; break; }
-        tcgen05_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t o = (ks >> 2) * (WQ * 128) + (ks & 3) * 32;
-          umma<false>(ty, umma_smem_desc(sp + o, 16, 1024), umma_smem_desc(sv + ks * 2048, W_TILE_V, 1024), id_y, ks != 0 ? 1u : 0u);
-        }
-        if (k > 0) {
-          if (!walk_wait(bars + B_HREADY, (k - 1) & 1, g.status, abort)) { ok = false; break; }
+      WalkSeg sg;
+      int qb = 0;          // chunks walked before this segment
+      uint32_t hq = 0;     // completions of B_HREADY consumed so far (one per received state, incl. a carried-in one)
+      bool ok = true;
+      for (int si = 0; ok && walk_segment(cta, ncta, nseq, nc, si, sg); ++si) {
+        ok = walk_wait(bars + B_FULL0 + (qb & 1), (qb >> 1) & 1, g.status, abort);
+        if (ok) { tcgen05_fence_after_sync(); issue_g(qb & 1); }
+        for (int k = 0; ok && k < sg.n; ++k) {
+          const int q = qb + k;
+          const int s = q & 1;
+          const uint32_t sq = mp_smem_u32(smem + s * W_STAGE), sk = sq + W_TILE_QK, sv = sk + W_TILE_QK;
+          const uint32_t ty = tmem + TC_Y + (q & 1) * 128;
+          if (!walk_wait(bars + B_PREADY, q & 1, g.status, abort)) { ok = false; break; }
           tcgen05_fence_after_sync();
-          if (g.hs_out != nullptr) {   // the state this chunk receives, straight from its operand tile
-            const int c = ANTI ? nc - 1 - k : k;
-            tma_store_2d(&map_hs, sH, 0, static_cast<int>(((static_cast<size_t>(b) * g.H + h) * nc + c) * WN));
-            bulk_commit();
-          }
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint32_t o = (ks >> 2) * (WQ * 128) + (ks & 3) * 32;
-            umma<false>(ty + 64, umma_smem_desc(sq + o, 16, 1024), umma_smem_desc(sh + ks * 2048, W_TILE_V, 1024), id_y, ks != 0 ? 1u : 0u);
+            umma<false>(ty, umma_smem_desc(sp + o, 16, 1024), umma_smem_desc(sv + ks * 2048, W_TILE_V, 1024), id_y, ks != 0 ? 1u : 0u);
           }
-        }
-        umma_commit(bars + B_YFULL);
-        // scores of the next chunk (its stage was released by S(k-1); the workers are past G(k))
-        if (k + 1 < nc) {
-          const int s1 = (k + 1) & 1;
-          if (!walk_wait(bars + B_FULL0 + s1, ((k + 1) >> 1) & 1, g.status, abort)) { ok = false; break; }
-          tcgen05_fence_after_sync();
-          issue_g(s1);
-        }
-        if (!walk_wait(bars + B_VSREADY, k & 1, g.status, abort)) { ok = false; break; }
-        tcgen05_fence_after_sync();
+          const bool has_state = k > 0 || sg.cin != 0;
+          if (has_state) {
+            if (!walk_wait(bars + B_HREADY, hq & 1u, g.status, abort)) { ok = false; break; }
+            ++hq;
+            tcgen05_fence_after_sync();
+            if (g.hs_out != nullptr) {   // the state this chunk receives, straight from its operand tile
+              const int c = ANTI ? nc - 1 - (sg.p0 + k) : sg.p0 + k;
+              tma_store_2d(&map_hs, sH, 0, static_cast<int>((static_cast<size_t>(sg.seq) * nc + c) * WN));
+              bulk_commit();
+            }
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks)
-          umma<false>(tmem + TC_S, umma_smem_desc(sk + ks * 2048, WQ * 128, 1024), umma_smem_desc(svs + ks * 2048, W_TILE_V, 1024), id_s,
-                      ks != 0 ? 1u : 0u);
-        // The workers rewrite the state tile once S(k) is complete: the store issued above must have read it by then.
-        // (Waiting here, behind the next chunk's score MMAs, costs nothing; waiting right after the store held back
-        // the commit of the output accumulators by the store's whole latency in every chunk.)
-        if (g.hs_out != nullptr && k > 0) bulk_wait_read<0>();
-        umma_commit(bars + B_SFULL);
-        umma_commit(bars + B_EMPTY0 + s);
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint32_t o = (ks >> 2) * (WQ * 128) + (ks & 3) * 32;
+              umma<false>(ty + 64, umma_smem_desc(sq + o, 16, 1024), umma_smem_desc(sh + ks * 2048, W_TILE_V, 1024), id_y, ks != 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(bars + B_YFULL);
+          // scores of the next chunk (its stage was released by S(k-1); the workers are past G(k))
+          if (k + 1 < sg.n) {
+            const int s1 = (q + 1) & 1;
+            if (!walk_wait(bars + B_FULL0 + s1, ((q + 1) >> 1) & 1, g.status, abort)) { ok = false; break; }
+            tcgen05_fence_after_sync();
+            issue_g(s1);
+          }
+          if (!walk_wait(bars + B_VSREADY, q & 1, g.status, abort)) { ok = false; break; }
+          tcgen05_fence_after_sync();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            umma<false>(tmem + TC_S, umma_smem_desc(sk + ks * 2048, WQ * 128, 1024), umma_smem_desc(svs + ks * 2048, W_TILE_V, 1024), id_s,
+                        ks != 0 ? 1u : 0u);
+          // The workers rewrite the state tile once S(k) is complete: the store issued above must have read it by then.
+          // (Waiting here, behind the next chunk's score MMAs, costs nothing; waiting right after the store held back
+          // the commit of the output accumulators by the store's whole latency in every chunk.)
+          if (g.hs_out != nullptr && has_state) bulk_wait_read<0>();
+          umma_commit(bars + B_SFULL);
+          umma_commit(bars + B_EMPTY0 + s);
+        }
+        qb += sg.n;
       }
       if (g.hs_out != nullptr) bulk_wait_all<0>();
     }
@@ -217,20 +262,68 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
     const int quarter = warp & 3;              // TMEM lane quarter this warp may read
     const int ch = (warp - 2) >> 2;            // column half
     const int r = quarter * 32 + lane;         // row of every 128-row tile
-    const size_t bh = static_cast<size_t>(b) * g.H + h;
+    const uint32_t tl = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int pitch = g.H * WP;
+    WalkSeg sg;
+    int qb = 0;          // chunks walked before this segment (barrier phases run on across segments)
+    bool alive = true;
+    for (int si = 0; alive && walk_segment(cta, ncta, nseq, nc, si, sg); ++si) {
+    const int n = sg.n;
+    const int h = sg.seq % g.H, b = sg.seq / g.H;
+    const size_t bh = static_cast<size_t>(sg.seq);
     const float* cum_g = g.cum + bh * g.L;
     const float* dt_g = g.dtt + bh * g.L;
     const float* colf_g = g.colf + bh * g.L;
-    const uint32_t tl = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
-    const int pitch = g.H * WP;
     float state[32];
+    const int c_first = ANTI ? nc - 1 - sg.p0 : sg.p0;
+    if (sg.cin) {
+      // the state the first part of this sequence ended with: written by all eight worker warps of the CTA that walked it
+      if (lane == 0) {
+        const uint64_t t0 = mp_globaltimer_ns();
+        const uint64_t limit = mp_wait_limit_ns(g.status);
+        while (true) {
+          int seen;
+          asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(seen) : "l"(g.carry_flag + sg.seq) : "memory");
+          if (seen >= 8) break;
+          if (*abort != 0) break;
+          if (mp_globaltimer_ns() - t0 > limit) {
+            *abort = 1;
+            if (g.status != nullptr) atomicExch(g.status, MP_STATUS_WAIT_TIMEOUT);
+            break;
+          }
+          __nanosleep(200);
+        }
+      }
+      __syncwarp();
+      if (*abort != 0) { alive = false; break; }
+      const float4* src = reinterpret_cast<const float4*>(g.carry + (bh * WN + r) * WP + ch * 32);
 #pragma unroll
-    for (int e = 0; e < 32; ++e) state[e] = 0.f;
-    const int c_first = ANTI ? nc - 1 : 0;
-    if (g.hs_out != nullptr) {   // the first chunk of the walk receives nothing
-      uint4* dst = reinterpret_cast<uint4*>(g.hs_out + ((bh * nc + c_first) * WN + r) * WP + ch * 32);
+      for (int q4 = 0; q4 < 8; ++q4) {
+        const float4 v4 = __ldcg(src + q4);
+        state[q4 * 4] = v4.x; state[q4 * 4 + 1] = v4.y; state[q4 * 4 + 2] = v4.z; state[q4 * 4 + 3] = v4.w;
+      }
+      // its r16 copy is the operand of the first chunk's q H (the tile is free: the previous segment's last readers,
+      // q H and the state store, were complete before that segment's last S accumulator was released)
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(0u, 0u, 0u, 0u);
+      for (int q4 = 0; q4 < 4; ++q4) {
+        uint4 pk;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __half2 hv = __floats2half2_rn(state[q4 * 8 + 2 * e], state[q4 * 8 + 2 * e + 1]);
+          ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+        }
+        *reinterpret_cast<uint4*>(sH + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4)) = pk;
+      }
+      warp_arrive(bars + B_HREADY, lane);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 32; ++e) state[e] = 0.f;
+      if (g.hs_out != nullptr) {   // the first chunk of a sequence's walk receives nothing
+        uint4* dst = reinterpret_cast<uint4*>(g.hs_out + ((bh * nc + c_first) * WN + r) * WP + ch * 32);
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) dst[q4] = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
     // scalars of the walk: chunk in hand (cur), the one after it (nxt), and one more in flight (pre), so that
     // their loads are never waited for
@@ -238,31 +331,33 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
     float cum_nxt = cum_g[c_first * WQ + r], dt_nxt = dt_g[c_first * WQ + r], colf_nxt = colf_g[c_first * WQ + r];
     float last_nxt = 0.f;
     float cum_pre = 0.f, dt_pre = 0.f, colf_pre = 0.f;
-    if (nc > 1) {
-      const int c1 = ANTI ? nc - 2 : 1;
+    if (n > 1) {
+      const int c1 = ANTI ? c_first - 1 : c_first + 1;
       cum_pre = cum_g[c1 * WQ + r]; dt_pre = dt_g[c1 * WQ + r]; colf_pre = colf_g[c1 * WQ + r];
     }
 
-    // Iteration k finishes chunk k and prepares chunk k+1; k = -1 is the lead-in that only prepares chunk 0.
+    // Iteration k finishes chunk k of the segment and prepares chunk k+1; k = -1 is the lead-in that only prepares chunk 0.
 #pragma unroll 1
-    for (int k = -1; k < nc; ++k) {
+    for (int k = -1; k < n; ++k) {
       const bool cur = k >= 0;
-      const bool more = k + 1 < nc;
-      const int c = ANTI ? nc - 1 - k : k;                 // chunk in hand (meaningless in the lead-in)
-      const uint32_t par = static_cast<uint32_t>(k) & 1u;
-      const uint32_t parn = static_cast<uint32_t>(k + 1) & 1u;
+      const bool more = k + 1 < n;
+      const int c = ANTI ? c_first - k : c_first + k;      // chunk in hand (meaningless in the lead-in)
+      const int q = qb + k;                                // its index among the chunks this CTA walks
+      const uint32_t par = static_cast<uint32_t>(q) & 1u;
+      const uint32_t parn = static_cast<uint32_t>(q + 1) & 1u;
+      const bool has_state = k > 0 || sg.cin != 0;         // the chunk in hand received a state
       uint4 zc[4];
       if (cur) {
         cum_cur = cum_nxt; dt_cur = dt_nxt; last_cur = last_nxt;
         if (more) {
           cum_nxt = cum_pre; dt_nxt = dt_pre; colf_nxt = colf_pre;
-          if (k + 2 < nc) {
-            const int c2 = ANTI ? nc - 3 - k : k + 2;
+          if (k + 2 < n) {
+            const int c2 = ANTI ? c_first - k - 2 : c_first + k + 2;
             cum_pre = cum_g[c2 * WQ + r]; dt_pre = dt_g[c2 * WQ + r]; colf_pre = colf_g[c2 * WQ + r];
           }
         }
         // Yd(k) has consumed the P tile, and every warp is past the shared scalars of chunk k
-        if (!walk_wait(bars + B_YFULL, par, g.status, abort)) break;
+        if (!walk_wait(bars + B_YFULL, par, g.status, abort)) { alive = false; break; }
       }
       if (more) {
         // ---- scalars of chunk k+1 into shared memory ------------------------------------------
@@ -271,10 +366,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
           __syncwarp();
           if (lane == 0) mbar_arrive(bars + B_SCAL);
         }
-        if (!walk_wait(bars + B_SCAL, parn, g.status, abort)) break;
+        if (!walk_wait(bars + B_SCAL, parn, g.status, abort)) { alive = false; break; }
         last_nxt = s_cum[WQ - 1];
         // ---- P = G o F of chunk k+1 ----------------------------------------------------------------
-        if (!walk_wait(bars + B_GFULL, parn, g.status, abort)) break;
+        if (!walk_wait(bars + B_GFULL, parn, g.status, abort)) { alive = false; break; }
         tcgen05_fence_after_sync();
 #pragma unroll 1
         for (int pp = 0; pp < 2; ++pp) {
@@ -337,27 +432,37 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
           }
         }
         // ---- H' = D H + S ---------------------------------------------------------------
-        if (!walk_wait(bars + B_SFULL, par, g.status, abort)) break;
+        if (!walk_wait(bars + B_SFULL, par, g.status, abort)) { alive = false; break; }
         tcgen05_fence_after_sync();
-        if (more) {
+        if (more || sg.cout) {
           uint32_t sv[32];
           tmem_ld_32x32(tl + TC_S + ch * 32, sv);
           const float D = w_exp(last_cur);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 32; ++e) state[e] = D * state[e] + __uint_as_float(sv[e]);
+          if (more) {
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            uint4 pk;
-            uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 pk;
+              uint32_t* ow = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const __half2 hv = __floats2half2_rn(state[q4 * 8 + 2 * e], state[q4 * 8 + 2 * e + 1]);
-              ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+              for (int e = 0; e < 4; ++e) {
+                const __half2 hv = __floats2half2_rn(state[q4 * 8 + 2 * e], state[q4 * 8 + 2 * e + 1]);
+                ow[e] = *reinterpret_cast<const uint32_t*>(&hv);
+              }
+              *reinterpret_cast<uint4*>(sH + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4)) = pk;
             }
-            *reinterpret_cast<uint4*>(sH + r * 128 + (((ch * 4 + q4) ^ (r & 7)) << 4)) = pk;
+            warp_arrive(bars + B_HREADY, lane);
+          } else {
+            // the first part of a sequence ends here: its state goes to the CTA that walks the rest
+            float4* dst = reinterpret_cast<float4*>(g.carry + (bh * WN + r) * WP + ch * 32);
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4) __stcg(dst + q4, make_float4(state[q4 * 4], state[q4 * 4 + 1], state[q4 * 4 + 2], state[q4 * 4 + 3]));
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(g.carry_flag + sg.seq, 1);
           }
-          warp_arrive(bars + B_HREADY, lane);
         }
         // ---- out = r o (Yd + f o Yo) of chunk k -------------------------------------------
         // staging = this warp's own positions of the scaled-value tile (S(k), its last reader, has completed, and the
@@ -374,11 +479,11 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
         uint32_t yd[32], yo[32];
         const uint32_t ty = tl + TC_Y + par * 128 + ch * 32;
         tmem_ld_32x32(ty, yd);
-        if (k > 0) tmem_ld_32x32(ty + 64, yo);
-        const float fo = k > 0 ? (ANTI ? w_exp(last_cur - cum_cur) : w_exp(cum_cur)) : 0.f;
+        if (has_state) tmem_ld_32x32(ty + 64, yo);
+        const float fo = has_state ? (ANTI ? w_exp(last_cur - cum_cur) : w_exp(cum_cur)) : 0.f;
         const float ro = ANTI ? dt_cur : 1.f;
         tmem_ld_wait();
-        if (k == 0) {
+        if (!has_state) {
 #pragma unroll
           for (int e = 0; e < 32; ++e) yo[e] = 0u;
         }
@@ -427,8 +532,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
       }
       if (more) {
         // ---- w o v of chunk k+1 -> operand of its state update ------------------------------------
-        const int s1 = (k + 1) & 1;
-        if (!walk_wait(bars + B_FULL0 + s1, static_cast<uint32_t>((k + 1) >> 1) & 1u, g.status, abort)) break;
+        const int s1 = (q + 1) & 1;
+        if (!walk_wait(bars + B_FULL0 + s1, static_cast<uint32_t>((q + 1) >> 1) & 1u, g.status, abort)) { alive = false; break; }
         const float wt = ANTI ? w_exp(cum_nxt) : w_exp(last_nxt - cum_nxt) * dt_nxt;
         const __half2 wt2 = __float2half2_rn(wt);
         const unsigned char* src = smem + s1 * W_STAGE + 2 * W_TILE_QK + r * 128;
@@ -444,6 +549,8 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_walk_kernel(const __grid_con
         }
         warp_arrive(bars + B_VSREADY, lane);
       }
+    }
+    qb += n;
     }
   }
   tcgen05_fence_before_sync();
@@ -737,8 +844,10 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_group_grads_kernel(const __g
 // piece: causal exp(cum[t | 7] - cum[t]) dt[t], anti-causal exp(cum[t] - cum[t & ~7]); both are at most one (dt).
 __global__ void __launch_bounds__(WQ) ssd_walk_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A, float* __restrict__ cum,
                                                              float* __restrict__ dtt, float* __restrict__ colf_c, float* __restrict__ colf_a,
-                                                             int L, int H) {
+                                                             int L, int H, int* __restrict__ carry_flags, int n_flags) {
   __shared__ float warp_tot[4];
+  if (blockIdx.x == 0)   // the walks that follow in stream order hand states from CTA to CTA through these counters
+    for (int i = threadIdx.x; i < n_flags; i += WQ) carry_flags[i] = 0;
   const int nc = L / WQ;
   const int c = blockIdx.x % nc, h = (blockIdx.x / nc) % H, b = blockIdx.x / (nc * H);
   const int t = threadIdx.x;
@@ -800,25 +909,31 @@ bool mp_ssd_walk_supported(int L, int H, int P, int N, int G) {
 }
 
 void mp_ssd_walk_cumsum(const float* dt, const float* A, float* cum, float* dtt, float* colf_c, float* colf_a, int B, int L, int H,
-                        cudaStream_t st) {
-  ssd_walk_cumsum_kernel<<<B * H * (L / WQ), WQ, 0, st>>>(dt, A, cum, dtt, colf_c, colf_a, L, H);
+                        int* carry_flags, int n_flags, cudaStream_t st) {
+  ssd_walk_cumsum_kernel<<<B * H * (L / WQ), WQ, 0, st>>>(dt, A, cum, dtt, colf_c, colf_a, L, H, carry_flags, n_flags);
   MP_LAUNCH_CHECK();
 }
 
 // One walk.  q, k: [B*L, G*128]; v, z, out: [B*L, H*64]; cum, dtt, colf (of the walk's direction): [B, H, L] from mp_ssd_walk_cumsum.
 void mp_ssd_walk(int anti, const __half* q, const __half* k, const __half* v, const float* cum, const float* dtt, const float* colf, __half* out,
                  const __half* z,
-                 float* dot_out, __half* hs_out, int B, int L, int H, int G, uint32_t* status, cudaStream_t st) {
+                 float* dot_out, __half* hs_out, float* carry, int* carry_flag, int max_ctas, int B, int L, int H, int G, uint32_t* status,
+                 cudaStream_t st) {
   WalkArgs g;
   g.B = B; g.L = L; g.H = H; g.G = G; g.nc = L / WQ;
   g.cum = cum; g.dtt = dtt; g.colf = colf; g.out = out; g.z = z; g.dot_out = dot_out; g.hs_out = hs_out; g.status = status;
+  g.carry = carry; g.carry_flag = carry_flag;
+  // One CTA per SM slot it may use, every CTA the same number of chunks; never more CTAs than sequences, so that a CTA's
+  // range is at least one sequence long (see walk_segment).  MP_SSD_WALK_PER_SEQUENCE: one CTA per sequence, no hand-off.
+  int grid = B * H;
+  if (max_ctas > 0 && max_ctas < grid && getenv("MP_SSD_WALK_PER_SEQUENCE") == nullptr) grid = max_ctas;
   const size_t rows = static_cast<size_t>(B) * L;
   const CUtensorMap mq = walk_map(q, rows, static_cast<size_t>(G) * WN), mk = walk_map(k, rows, static_cast<size_t>(G) * WN);
   const CUtensorMap mv = walk_map(v, rows, static_cast<size_t>(H) * WP);
   const CUtensorMap mh = hs_out != nullptr ? walk_map(hs_out, static_cast<size_t>(B) * H * g.nc * WN, WP) : mv;
   auto launch = [&](auto kernel) {
     MP_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W_SMEM_BYTES));
-    kernel<<<B * H, W_THREADS, W_SMEM_BYTES, st>>>(mq, mk, mv, mh, g);
+    kernel<<<grid, W_THREADS, W_SMEM_BYTES, st>>>(mq, mk, mv, mh, g);
   };
   const bool dot = z != nullptr && dot_out != nullptr;
   if (!dot) { g.z = nullptr; g.dot_out = nullptr; }

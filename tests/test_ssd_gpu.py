@@ -34,6 +34,10 @@ CASES = [  # (batch, seqlen, heads, headdim, dstate, groups, chunk)
     (1, 768, 4, 64, 128, 2, 256),
     (2, 256, 2, 64, 128, 1, 128),
     (1, 512, 2, 128, 128, 1, 256),
+    # more sequences than SMs (and than half of them, the reverse's share per walk): the chunk walk gives every CTA the
+    # same number of chunks, so sequences are cut between CTAs and their state crosses through global memory
+    (10, 384, 16, 64, 128, 1, 128),
+    (5, 640, 20, 64, 128, 2, 128),
 ]
 
 
