@@ -231,6 +231,72 @@ __device__ __forceinline__ void rmsnorm_rev_row(const Pack<T>* px, const Pack<T>
                                                 typename Acc<T>::type* red) {
   using A = typename Acc<T>::type;
   constexpr int PN = Pack<T>::N;
+  if constexpr (std::is_same<T, __half>::value) {
+    // r16: gx = rstd * (gy o gain) - coef * x (+ alpha * gx) is linear in the row's coef, which is
+    // only known after the row sum.  The first pass leaves rstd * gy o gain as packed halves and the second is one or
+    // two packed multiply-adds per pair of elements on the raw x packs: ten instructions per element instead of
+    // nineteen, which is what kept the r16 kernel below the copy bandwidth.  (alpha must be exact in r16: 0, 1, ...)
+    if (!BLEND || __half2float(__float2half_rn(alpha)) == alpha) {
+      float rstd;
+      float dot = 0.f, unused = 0.f;
+      if (rstd_in != nullptr) {
+        rstd = rstd_in[row];
+      } else {   // one more reduction round for the row's own sum of squares
+        float ss = 0.f;
+#pragma unroll
+        for (int u = 0; u < PPT; ++u) {
+          if (MP_PACK_VALID(u)) {
+            const __half2* hx = reinterpret_cast<const __half2*>(&px[u]);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 fx = __half22float2(hx[q]);
+              ss += fx.x * fx.x + fx.y * fx.y;
+            }
+          }
+        }
+        group_sum2<GROUP>(ss, unused, red);
+        rstd = mp_rsqrt(ss * inv_n + eps);
+      }
+      __half2 pa[PPT][4];
+#pragma unroll
+      for (int u = 0; u < PPT; ++u) {
+        if (MP_PACK_VALID(u)) {
+          const __half2* hx = reinterpret_cast<const __half2*>(&px[u]);
+          const __half2* hg = reinterpret_cast<const __half2*>(&pg[u]);
+          const __half2* hn = reinterpret_cast<const __half2*>(&pgain[u]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 fx = __half22float2(hx[q]), fg = __half22float2(hg[q]), fn = __half22float2(hn[q]);
+            const float ux = fg.x * fn.x, uy = fg.y * fn.y;
+            dot += ux * fx.x + uy * fx.y;
+            acc[u][2 * q] += fg.x * fx.x * rstd;
+            acc[u][2 * q + 1] += fg.y * fx.y * rstd;
+            pa[u][q] = __floats2half2_rn(ux * rstd, uy * rstd);
+          }
+        }
+      }
+      group_sum2<GROUP>(unused, dot, red);
+      const __half2 nc = __float2half2_rn(-rstd * rstd * rstd * dot * inv_n);
+      const __half2 al2 = __float2half2_rn(alpha);
+#pragma unroll
+      for (int u = 0; u < PPT; ++u) {
+        if (MP_PACK_VALID(u)) {
+          const __half2* hx = reinterpret_cast<const __half2*>(&px[u]);
+          Pack<T> po, out;
+          if constexpr (BLEND) po = ld_pack_stream(out_row, MP_PACK_INDEX(u));
+          __half2* ho = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            __half2 r = __hfma2(nc, hx[q], pa[u][q]);
+            if constexpr (BLEND) r = __hfma2(al2, reinterpret_cast<const __half2*>(&po)[q], r);
+            ho[q] = r;
+          }
+          st_pack_stream(out_row, MP_PACK_INDEX(u), out);
+        }
+      }
+      return;
+    }
+  }
   A fx[PPT][PN], fu[PPT][PN], ft[PPT][PN];  // x, gy*gain, gy*x
   A ss = A(0), dot = A(0);
 #pragma unroll
@@ -1084,6 +1150,8 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
 #undef WROW
     } else if (sp.ok && state != nullptr) {
       rpc = rms_rev_rows_per_cta(m, sms);
+      // (one resident wave of CTAs with ~150 rows each was measured slower than waves of 32-row CTAs: 312 vs 277 us at
+      // [65536, 4096] r16, 521 vs 498 us r32)
       grid = static_cast<unsigned>((m + rpc - 1) / rpc);
       slots = grid;
       uint32_t* status = state->status_dev;
