@@ -45,7 +45,7 @@ def header_arities():
     triples, functions = {}, {}
     for h in sorted((ROOT / "include").glob("*.h")):
         text = re.sub(r"/\*.*?\*/", "", h.read_text(), flags=re.S)
-        for m in re.finditer(r"MP_DECL3\(", text):
+        for m in re.finditer(r"^MP_DECL3\(", text, flags=re.M):   # (declarations, not the macro's own #define)
             body = split_top_level(balanced(text, m.end() - 1, "(", ")"))
             triples[body[0]] = len(body) - 1
         for m in re.finditer(r"MP_EXTERN_C\s+[\w\s\*]+?\b(\w+)\(", text):
@@ -77,6 +77,9 @@ def test_kernel_arrays_name_only_declared_launchers():
         base, sfx = sym[len("launch_"):].rsplit("_", 1)
         assert sfx in ("r16", "r32", "r64") and base in triples, sym
     # the twenty launchers of the reference must all be there (src/cuda/kernel_decls.h)
+    # ... and every triple the headers declare has its array
+    for name in triples:
+        assert name in arrays, f"include/mp_kernels.h declares launch_{name}_*, kernels.zig has no array for it"
     for ref in ("reduce_ij_i", "reduce_ij_j", "broadcast_i_ij", "dilate_reverse", "subtraction", "relu_reverse", "dilate", "translate",
                 "permutate_ij_ji", "negate", "hadamard_reverse", "inner_product_ij_jk_ik", "hadamard", "fill", "relu", "addition",
                 "broadcast_j_ij", "copy", "sequence", "stepwise"):

@@ -8,12 +8,6 @@ fn dispatch_array(comptime _: anytype, comptime tuple: anytype) [tuple.len]@Type
     return tuple;
 }
 
-pub const name = dispatch_array(opaque {}, .{
-    decls.launch_name_r16,
-    decls.launch_name_r32,
-    decls.launch_name_r64,
-});
-
 pub const reduce_ij_i = dispatch_array(opaque {}, .{
     decls.launch_reduce_ij_i_r16,
     decls.launch_reduce_ij_i_r32,
@@ -330,4 +324,22 @@ pub const inner_product_bji_bjk_bik = dispatch_array(opaque {}, .{
     decls.launch_inner_product_bji_bjk_bik_r16,
     decls.launch_inner_product_bji_bjk_bik_r32,
     decls.launch_inner_product_bji_bjk_bik_r64,
+});
+
+pub const linear_ij_jk_ik_ik = dispatch_array(opaque {}, .{
+    decls.launch_linear_ij_jk_ik_ik_r16,
+    decls.launch_linear_ij_jk_ik_ik_r32,
+    decls.launch_linear_ij_jk_ik_ik_r64,
+});
+
+pub const ssd_gate_rmsnorm = dispatch_array(opaque {}, .{
+    decls.launch_ssd_gate_rmsnorm_r16,
+    decls.launch_ssd_gate_rmsnorm_r32,
+    decls.launch_ssd_gate_rmsnorm_r64,
+});
+
+pub const ssd_gate_rmsnorm_reverse = dispatch_array(opaque {}, .{
+    decls.launch_ssd_gate_rmsnorm_reverse_r16,
+    decls.launch_ssd_gate_rmsnorm_reverse_r32,
+    decls.launch_ssd_gate_rmsnorm_reverse_r64,
 });
