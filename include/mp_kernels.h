@@ -184,6 +184,11 @@ MP_DECL3(causal_conv1d_silu_reverse, const void* x, len_t x_pitch, const void* w
  * block are neighbouring column ranges of one projection), otherwise one launch per segment. */
 MP_DECL3(causal_conv1d_silu_segments, const void* x, len_t x_pitch, const void* w, const void* bias, void* const* ys, const len_t* y_pitches, const len_t* seg_channels, len_t nseg, len_t batch, len_t len, len_t width, StreamContext stream)
 MP_DECL3(causal_conv1d_silu_segments_reverse, const void* x, len_t x_pitch, const void* w, const void* bias, const void* const* gys, const len_t* gy_pitches, const len_t* seg_channels, len_t nseg, void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t width, StreamContext stream)
+/* The same with a second upstream term on chosen segments (host arrays of nseg entries; skips[i] NULL: none):
+ *   gy_total[i] = gys[i] + skip_scales[i][channel / skip_group] * skips[i]      (skip_scales[i]: acc [seg_channels[i] / skip_group])
+ * i.e. the reverse of y_total = conv(...) feeding both an operator and a per-group scaled skip around it.  The upstream
+ * buffers of segments with a skip term are unspecified afterwards. */
+MP_DECL3(causal_conv1d_silu_segments_reverse_skip, const void* x, len_t x_pitch, const void* w, const void* bias, const void* const* gys, const len_t* gy_pitches, const len_t* seg_channels, len_t nseg, const void* const* skips, const len_t* skip_pitches, const void* const* skip_scales, len_t skip_group, void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t width, StreamContext stream)
 /* out[r,h] = softplus(raw[r,h] + bias[h]); raw: T with row pitch; bias, out: acc */
 MP_DECL3(softplus_bias, const void* raw, len_t raw_pitch, const void* bias, void* out, len_t rows, len_t heads, StreamContext stream)
 /* graw[r,h] = gdt[r,h]*sigmoid(raw[r,h] + bias[h]) (T, pitched); gbias[h] += sum_r graw (acc, may be NULL) */

@@ -69,6 +69,7 @@ LAUNCHERS = {
     "causal_conv1d_silu_reverse": [P, L, P, P, P, L, P, L, P, P, L, L, L, L, CTX],
     "causal_conv1d_silu_segments": [P, L, P, P, P, P, P, L, L, L, L, CTX],
     "causal_conv1d_silu_segments_reverse": [P, L, P, P, P, P, P, L, P, L, P, P, L, L, L, CTX],
+    "causal_conv1d_silu_segments_reverse_skip": [P, L, P, P, P, P, P, L, P, P, P, L, P, L, P, P, L, L, L, CTX],
     "softplus_bias": [P, L, P, P, L, L, CTX],
     "softplus_bias_reverse": [P, L, P, P, P, L, P, L, L, CTX],
     "ssd_gate": [P, P, P, P, L, P, L, L, L, CTX],

@@ -339,6 +339,11 @@ struct ConvSegs {
   int ch_count[CONV_MAX_SEGS];        // channels (a multiple of 8)
   const void* ptr[CONV_MAX_SEGS];     // the segment's own buffer (y resp. gy), channel 0 of the segment at column 0
   unsigned long long pitch[CONV_MAX_SEGS];
+  // reverse only: a second upstream term per segment, gy_total = gy + scale[channel / skip_group] * skip (or nullptr)
+  const void* skip_ptr[CONV_MAX_SEGS];
+  unsigned long long skip_pitch[CONV_MAX_SEGS];
+  const float* skip_scale[CONV_MAX_SEGS];
+  int skip_group;
 };
 __device__ __forceinline__ int conv_segment_of(const ConvSegs& sg, int block) {
   int s = 0;
@@ -420,17 +425,23 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_tiled_kernel(const __h
   }
 }
 
-template <int W>
+// SKIP: segments may carry a second upstream term (ConvSegs::skip_*), staged beside gy; that variant takes its tiles
+// from dynamic shared memory (64 KB).
+template <int W, bool SKIP>
 __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(const __half* __restrict__ x, size_t xp,
                                                                                const __half* __restrict__ w, const __half* __restrict__ bias,
                                                                                const ConvSegs sg, __half* __restrict__ gx, size_t gxp,
                                                                                float* __restrict__ gw, float* __restrict__ gbias, int L,
                                                                                int tiles_per_cta) {
   constexpr int H = W - 1;
-  __shared__ __align__(16) __half xs[2][CT_L + 2 * H][CT_C];    // two tiles in turn; row r = step l0 - H + r
-  __shared__ __align__(16) __half gys[2][CT_L + H][CT_C];       // row r = step l0 + r
-  __shared__ __align__(16) __half gxs[CT_L][CT_C];
-  __shared__ float red[CT_LANES][CT_C][W + 1];
+  extern __shared__ __align__(16) unsigned char conv_rev_smem[];
+  typedef __half (*TileX)[CT_L + 2 * H][CT_C];
+  typedef __half (*TileG)[CT_L + H][CT_C];
+  TileX xs = reinterpret_cast<TileX>(conv_rev_smem);                                   // [2]: two tiles in turn; row r = step l0 - H + r
+  TileG gys = reinterpret_cast<TileG>(conv_rev_smem + sizeof(__half) * 2 * (CT_L + 2 * H) * CT_C);   // [2]: row r = step l0 + r
+  __half (*gxs)[CT_C] = reinterpret_cast<__half (*)[CT_C]>(reinterpret_cast<unsigned char*>(gys) + sizeof(__half) * 2 * (CT_L + H) * CT_C);
+  float (*red)[CT_C][W + 1] = reinterpret_cast<float (*)[CT_C][W + 1]>(reinterpret_cast<unsigned char*>(gxs) + sizeof(__half) * CT_L * CT_C);
+  TileG g2s = reinterpret_cast<TileG>(reinterpret_cast<unsigned char*>(red) + sizeof(float) * CT_LANES * CT_C * (W + 1));   // [2], SKIP only
   const int tid = threadIdx.x;
   const int c = (tid % (CT_C / 2)) * 2, lane = tid / (CT_C / 2);
   const int seg = conv_segment_of(sg, blockIdx.x);
@@ -443,6 +454,14 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(c
   const __half* xb = x + b * L * xp + cbase;
   const __half* gyb = static_cast<const __half*>(sg.ptr[seg]) + b * L * gyp + local;
   __half* gxb = gx + b * L * gxp + cbase;
+  const bool skip = SKIP && sg.skip_ptr[seg] != nullptr;
+  const size_t g2p = SKIP ? sg.skip_pitch[seg] : 0;
+  const __half* g2b = skip ? static_cast<const __half*>(sg.skip_ptr[seg]) + b * L * g2p + local : nullptr;
+  float sk[2] = {0.f, 0.f};   // the skip term's factor for this thread's two channels
+  if (skip && cbase + c < C) {
+    sk[0] = sg.skip_scale[seg][(local + c) / sg.skip_group];
+    sk[1] = sg.skip_scale[seg][(local + c + 1) / sg.skip_group];
+  }
   float wk[2][W], bs[2] = {0.f, 0.f}, gwk[2][W], gbs[2] = {0.f, 0.f};
 #pragma unroll
   for (int e = 0; e < 2; ++e) {
@@ -468,6 +487,7 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(c
       const int l = l0 + r;
       const bool ok = l < L && pk < packs_live;
       cp_async_16_zfill(&gys[t & 1][r][pk * 8], ok ? gyb + static_cast<size_t>(l) * gyp + pk * 8 : gyb, ok);
+      if (SKIP && skip) cp_async_16_zfill(&g2s[t & 1][r][pk * 8], ok ? g2b + static_cast<size_t>(l) * g2p + pk * 8 : g2b, ok);
     }
     cp_async_commit();
   };
@@ -482,6 +502,7 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(c
     {
       const __half (*xt)[CT_C] = xs[t & 1];
       const __half (*gt)[CT_C] = gys[t & 1];
+      const __half (*g2t)[CT_C] = g2s[t & 1];
       const int s0 = lane * CT_STEPS;
       float2 xw[W], d[W];   // xw[k] = x at step s + k - H (tile row s + k); d[k] = dpre at step s - k
 #pragma unroll
@@ -498,7 +519,11 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(c
 #pragma unroll
         for (int k = 0; k < W; ++k) { p0 += wk[0][k] * xw[k].x; p1 += wk[1][k] * xw[k].y; }
         const float g0 = sigmoid_a(p0), g1 = sigmoid_a(p1);
-        const float2 gyv = __half22float2(*reinterpret_cast<const __half2*>(&gt[s][c]));
+        float2 gyv = __half22float2(*reinterpret_cast<const __half2*>(&gt[s][c]));
+        if (SKIP && skip) {
+          const float2 g2v = __half22float2(*reinterpret_cast<const __half2*>(&g2t[s][c]));
+          gyv.x += sk[0] * g2v.x; gyv.y += sk[1] * g2v.y;
+        }
         const float2 dp = make_float2(gyv.x * g0 * (1.f + p0 * (1.f - g0)), gyv.y * g1 * (1.f + p1 * (1.f - g1)));
 #pragma unroll
         for (int k = H; k > 0; --k) d[k] = d[k - 1];
@@ -1460,10 +1485,13 @@ static bool conv_make_segs(ConvSegs& sg, const void* const* bufs, const len_t* p
     sg.ch_count[i] = static_cast<int>(counts[i]);
     sg.ptr[i] = bufs[i];
     sg.pitch[i] = pitches[i];
+    sg.skip_ptr[i] = nullptr; sg.skip_pitch[i] = 0; sg.skip_scale[i] = nullptr;
     blk += static_cast<int>((counts[i] + CT_C - 1) / CT_C);
     ch += static_cast<int>(counts[i]);
   }
   for (int i = sg.nseg; i <= CONV_MAX_SEGS; ++i) sg.blk_begin[i] = blk;
+  for (int i = sg.nseg; i < CONV_MAX_SEGS; ++i) { sg.skip_ptr[i] = nullptr; sg.skip_pitch[i] = 0; sg.skip_scale[i] = nullptr; }
+  sg.skip_group = 1;
   return true;
 }
 static dim3 conv_tiled_grid(const ConvSegs& sg, len_t len, len_t batch, int* tiles_per_cta) {
@@ -1497,9 +1525,21 @@ static void conv_tiled_reverse(const void* x, len_t x_pitch, const void* w, cons
   const __half* bh = static_cast<const __half*>(bias);
   __half* gxh = static_cast<__half*>(gx);
   float* gwf = static_cast<float*>(gw); float* gbf = static_cast<float*>(gbias);
-  if (width == 4) conv1d_silu_reverse_tiled_kernel<4><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
-  else if (width == 3) conv1d_silu_reverse_tiled_kernel<3><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
-  else conv1d_silu_reverse_tiled_kernel<2><<<grid, CT_THREADS, 0, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp);
+  bool skip = false;
+  for (int i = 0; i < sg.nseg; ++i) skip = skip || sg.skip_ptr[i] != nullptr;
+#define CONV_REV(WV, SK)                                                                                                            \
+  do {                                                                                                                              \
+    constexpr int HV = WV - 1;                                                                                                      \
+    const size_t smem = sizeof(__half) * (2 * (CT_L + 2 * HV) * CT_C + 2 * (CT_L + HV) * CT_C + CT_L * CT_C) +                       \
+                        sizeof(float) * CT_LANES * CT_C * (WV + 1) + (SK ? sizeof(__half) * 2 * (CT_L + HV) * CT_C : 0);             \
+    if (smem > 48 * 1024)                                                                                                           \
+      MP_CUDA_CHECK(cudaFuncSetAttribute(conv1d_silu_reverse_tiled_kernel<WV, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                         static_cast<int>(smem)));                                                                  \
+    conv1d_silu_reverse_tiled_kernel<WV, SK><<<grid, CT_THREADS, smem, st>>>(xh, x_pitch, wh, bh, sg, gxh, gx_pitch, gwf, gbf, L, tp); \
+  } while (0)
+  if (skip) { if (width == 4) CONV_REV(4, true); else if (width == 3) CONV_REV(3, true); else CONV_REV(2, true); }
+  else { if (width == 4) CONV_REV(4, false); else if (width == 3) CONV_REV(3, false); else CONV_REV(2, false); }
+#undef CONV_REV
   MP_LAUNCH_CHECK();
 }
 
@@ -1598,6 +1638,51 @@ void causal_conv1d_silu_segments_reverse_impl(const void* x, len_t x_pitch, cons
                                        seg_channels[i], width, ctx);
     c0 += seg_channels[i];
   }
+}
+
+template <typename T>
+void head_scale_accumulate_impl(const void* D, const void* gy, void* gx, len_t rows, len_t heads, len_t headdim, StreamContext ctx);
+
+// The same with a second upstream term on chosen segments: gy_total = gys[i] + scale_i[channel / group] * skips[i]
+// (skips[i] NULL: none).  One launch on the tiled r16 path; elsewhere the term is first added into gys[i] in place
+// (the upstream buffers of segments with a skip term are unspecified afterwards).
+template <typename T>
+void causal_conv1d_silu_segments_reverse_skip_impl(const void* x, len_t x_pitch, const void* w, const void* bias, const void* const* gys,
+                                                   const len_t* gy_pitches, const len_t* seg_channels, len_t nseg, const void* const* skips,
+                                                   const len_t* skip_pitches, const void* const* skip_scales, len_t skip_group, void* gx,
+                                                   len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t width,
+                                                   StreamContext ctx) {
+  if (batch == 0 || len == 0 || nseg == 0) return;
+  if (gys == nullptr || gy_pitches == nullptr || seg_channels == nullptr || skips == nullptr || skip_pitches == nullptr || skip_scales == nullptr ||
+      skip_group == 0)
+    MP_FATAL("causal_conv1d_silu_segments_reverse_skip: the segment arrays are host arrays of nseg entries, skip_group > 0");
+  len_t total = 0;
+  for (len_t i = 0; i < nseg; ++i) total += seg_channels[i];
+  if constexpr (std::is_same<T, __half>::value) {
+    ConvSegs sg;
+    bool ok = vec_ok<T>(x, x_pitch, total) && vec_ok<T>(gx, gx_pitch, total) && conv_tiles_enabled(width) &&
+              conv_make_segs(sg, gys, gy_pitches, seg_channels, nseg) && skip_group % 2 == 0;
+    for (len_t i = 0; ok && i < nseg; ++i)
+      if (skips[i] != nullptr) ok = vec_ok<T>(skips[i], skip_pitches[i], seg_channels[i]) && skip_scales[i] != nullptr;
+    if (ok) {
+      for (len_t i = 0; i < nseg; ++i) {
+        sg.skip_ptr[i] = skips[i];
+        sg.skip_pitch[i] = skip_pitches[i];
+        sg.skip_scale[i] = static_cast<const float*>(skip_scales[i]);
+      }
+      sg.skip_group = static_cast<int>(skip_group);
+      conv_tiled_reverse(x, x_pitch, w, bias, sg, gx, gx_pitch, gw, gbias, batch, len, width, ctx);
+      return;
+    }
+  }
+  for (len_t i = 0; i < nseg; ++i) {
+    if (skips[i] == nullptr) continue;
+    if (gy_pitches[i] != seg_channels[i] || skip_pitches[i] != seg_channels[i] || seg_channels[i] % skip_group != 0)
+      MP_FATAL("causal_conv1d_silu_segments_reverse_skip: outside the tiled r16 path a skip term needs densely packed buffers");
+    head_scale_accumulate_impl<T>(skip_scales[i], skips[i], const_cast<void*>(gys[i]), batch * len, seg_channels[i] / skip_group, skip_group, ctx);
+  }
+  causal_conv1d_silu_segments_reverse_impl<T>(x, x_pitch, w, bias, gys, gy_pitches, seg_channels, nseg, gx, gx_pitch, gw, gbias, batch, len, width,
+                                              ctx);
 }
 
 template <typename T>
@@ -1882,6 +1967,12 @@ MP_STAMP3(causal_conv1d_silu_segments_reverse,
            const len_t* seg_channels, len_t nseg, void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t width,
            StreamContext ctx),
           (x, x_pitch, w, bias, gys, gy_pitches, seg_channels, nseg, gx, gx_pitch, gw, gbias, batch, len, width, ctx))
+MP_STAMP3(causal_conv1d_silu_segments_reverse_skip,
+          (const void* x, len_t x_pitch, const void* w, const void* bias, const void* const* gys, const len_t* gy_pitches,
+           const len_t* seg_channels, len_t nseg, const void* const* skips, const len_t* skip_pitches, const void* const* skip_scales,
+           len_t skip_group, void* gx, len_t gx_pitch, void* gw, void* gbias, len_t batch, len_t len, len_t width, StreamContext ctx),
+          (x, x_pitch, w, bias, gys, gy_pitches, seg_channels, nseg, skips, skip_pitches, skip_scales, skip_group, gx, gx_pitch, gw, gbias, batch,
+           len, width, ctx))
 MP_STAMP3(softplus_bias, (const void* raw, len_t raw_pitch, const void* bias, void* out, len_t rows, len_t heads, StreamContext ctx),
           (raw, raw_pitch, bias, out, rows, heads, ctx))
 MP_STAMP3(softplus_bias_reverse,

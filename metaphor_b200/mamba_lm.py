@@ -348,12 +348,14 @@ class MambaLM:
                     self.gun, self.gy, gzx, dip, self._p(G32, p + "D"), self._p(G16, p + "gnorm_w"), 0.0, self.rms_scratch, T, H, P)
             self._L("ssd_scan_reverse", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], self.gy, self.gxs, self.gdt, self.gA,
                     self.gBs, self.gCs, self.ssd_scratch, *self.ssd_dims)
-            self._L("head_scale_accumulate", self._p(self.w32, p + "D"), self.gy, self.gxs, T, H, P)
             self._L32("hadamard_reverse", self.gA, sv["A"], self._p(G32, p + "A_log"), H)   # dA/dA_log = A
             self._L("softplus_bias_reverse", zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), self.gdt,
                     gzx + (di + c.conv_dim) * esz, dip, self._p(G32, p + "dt_bias"), T, H)
-            self._L("causal_conv1d_silu_segments_reverse", zx + di * esz, dip, self._p(W, p + "conv_w"), self._p(W, p + "conv_b"),
+            # the D skip's share of the x gradient (D[h] * gy) joins the scan's inside the convolution's reverse
+            self._L("causal_conv1d_silu_segments_reverse_skip", zx + di * esz, dip, self._p(W, p + "conv_w"), self._p(W, p + "conv_b"),
                     (C.c_void_p * 3)(self.gxs.data_ptr(), self.gBs.data_ptr(), self.gCs.data_ptr()), seg_widths, seg_widths, 3,
+                    (C.c_void_p * 3)(self.gy.data_ptr(), None, None), (C.c_ulong * 3)(di, 0, 0),
+                    (C.c_void_p * 3)(self._p(self.w32, p + "D"), None, None), P,
                     gzx + di * esz, dip, self._p(G32, p + "conv_w"), self._p(G32, p + "conv_b"), self.batch, self.seqlen, c.d_conv)
             # in_proj
             self._L("inner_product_ij_kj_ik", self.gzx, self._p(W, p + "in_proj"), 1.0, self.gt, 0.0, T, dip, c.d_model)

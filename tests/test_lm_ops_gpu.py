@@ -118,6 +118,51 @@ def test_causal_conv1d_silu_segments(mp, stream, orc, sfx, nb, L, widths, W, pit
     assert_close(host(gb), gb0.astype(np.float64) + rgb, ptol, "segments gbias")
 
 
+# The reverse with a scaled skip term on the first segment (the scan's D skip in a Mamba-2 block): against the oracle
+# fed with gys[0] + D[channel / group] * skip.  Tiled r16 path (group = one 64-channel tile, and a group that spans
+# tiles), a segment that ends inside a tile, and the dense fallback of the other dtypes.
+@pytest.mark.parametrize("sfx", DTYPES)
+@pytest.mark.parametrize("nb,L,widths,W,pitch,group", [(2, 200, (128, 64, 64), 4, 320, 64), (1, 70, (96, 8, 40), 4, 160, 32),
+                                                       (2, 33, (32, 16), 3, 56, 16), (1, 130, (256, 64), 4, 320, 128)])
+def test_causal_conv1d_silu_segments_reverse_with_a_skip_term(mp, stream, orc, sfx, nb, L, widths, W, pitch, group):
+    import ctypes as C
+    rng = np.random.default_rng(17)
+    Cn = sum(widths)
+    off = pitch - Cn
+    xfull = draw(rng, (nb, L, pitch), sfx)
+    w = draw(rng, (Cn, W), sfx, 0.5)
+    bias = draw(rng, (Cn,), sfx, 0.1)
+    x = xfull[:, :, off:]
+    dx, dw, db = dev(xfull), dev(w), dev(bias)
+    esz = xfull.itemsize
+    cw = (C.c_ulong * len(widths))(*widths)
+    gys_np = [draw(rng, (nb, L, cwid), sfx) for cwid in widths]
+    skip_np = draw(rng, (nb, L, widths[0]), sfx)
+    scale = rng.standard_normal(widths[0] // group).astype(ACC[sfx])
+    gys = [dev(g) for g in gys_np]
+    dskip, dscale = dev(skip_np), dev(scale)
+    gptrs = (C.c_void_p * len(widths))(*[t.data_ptr() for t in gys])
+    sptrs = (C.c_void_p * len(widths))(*([dskip.data_ptr()] + [None] * (len(widths) - 1)))
+    spitch = (C.c_ulong * len(widths))(*([widths[0]] + [0] * (len(widths) - 1)))
+    scales = (C.c_void_p * len(widths))(*([dscale.data_ptr()] + [None] * (len(widths) - 1)))
+    gxfull = dev(np.full((nb, L, pitch), 3, NP_OF[sfx]))
+    gw0 = rng.standard_normal((Cn, W)).astype(ACC[sfx]); gb0 = rng.standard_normal((Cn,)).astype(ACC[sfx])
+    gw, gb = dev(gw0.copy()), dev(gb0.copy())
+    run(mp, stream, "causal_conv1d_silu_segments_reverse_skip", sfx, dx.data_ptr() + off * esz, pitch, dw, db, gptrs, cw, cw, len(widths),
+        sptrs, spitch, scales, group, gxfull.data_ptr() + off * esz, pitch, gw, gb, nb, L, W)
+    f64 = lambda a: a.astype(np.float64)
+    gy = np.concatenate([f64(g) for g in gys_np], axis=2)
+    gy[:, :, :widths[0]] += np.repeat(f64(scale), group) * f64(skip_np)
+    rgx, rgw, rgb = orc.causal_conv1d_silu_reverse(f64(x), f64(w), f64(bias), gy)
+    got = host(gxfull)
+    assert_close(got[:, :, off:], rgx, TOL[sfx], "skip segments gx")
+    assert np.all(got[:, :, :off] == 3), "columns outside the slice were written"
+    ptol = 1e-4 if sfx != "r64" else 1e-11
+    assert_close(host(gw), f64(gw0) + rgw, ptol, "skip segments gw")
+    assert_close(host(gb), f64(gb0) + rgb, ptol, "skip segments gbias")
+    assert stream.status() == 0
+
+
 @pytest.mark.parametrize("sfx", DTYPES)
 @pytest.mark.parametrize("rows,H,pitch", [(1000, 24, 40), (3, 5, 5), (70, 300, 304), (50, 256, 256), (4099, 32, 32)])
 def test_softplus_bias(mp, stream, orc, sfx, rows, H, pitch):

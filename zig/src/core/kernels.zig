@@ -343,3 +343,9 @@ pub const ssd_gate_rmsnorm_reverse = dispatch_array(opaque {}, .{
     decls.launch_ssd_gate_rmsnorm_reverse_r32,
     decls.launch_ssd_gate_rmsnorm_reverse_r64,
 });
+
+pub const causal_conv1d_silu_segments_reverse_skip = dispatch_array(opaque {}, .{
+    decls.launch_causal_conv1d_silu_segments_reverse_skip_r16,
+    decls.launch_causal_conv1d_silu_segments_reverse_skip_r32,
+    decls.launch_causal_conv1d_silu_segments_reverse_skip_r64,
+});
