@@ -260,7 +260,7 @@ def bmm_case(mp, s, sfx, nb, n):
 
 
 def conv_case(mp, s, op, sfx, nb, L):
-    """conv_fwd | conv_rev: the segmented causal convolution over the 1792 [x | B | C] columns of a Mamba-2 block."""
+    """conv_fwd | conv_rev | conv_rev_skip: the segmented causal convolution over the 1792 [x | B | C] columns of a Mamba-2 block."""
     import torch
     g, dt = _gen(0), _dt(sfx)
     widths, dip, di, W = (1536, 128, 128), 3352, 1536, 4
@@ -274,6 +274,15 @@ def conv_case(mp, s, op, sfx, nb, L):
     if op == "conv_fwd":
         once = lambda: mp.launch("causal_conv1d_silu_segments", dt, zx.data_ptr() + di * esz, dip, w, bias, ptrs, cw, cw, 3, nb, L, W, s)
         nbytes = 2 * nb * L * Cn * esz
+    elif op == "conv_rev_skip":   # with the scan's D skip (scale per 64-channel head) joining the x segment's upstream gradient
+        skip = torch.randn(nb * L, widths[0], generator=g, device="cuda").to(dt)
+        D = torch.randn(widths[0] // 64, generator=g, device="cuda")
+        sp = (C.c_void_p * 3)(skip.data_ptr(), None, None); spitch = (C.c_ulong * 3)(widths[0], 0, 0)
+        sc = (C.c_void_p * 3)(D.data_ptr(), None, None)
+        once = lambda: mp.launch("causal_conv1d_silu_segments_reverse_skip", dt, zx.data_ptr() + di * esz, dip, w, bias, ptrs, cw, cw, 3,
+                                 sp, spitch, sc, 64, gzx.data_ptr() + di * esz, dip, gw, gb, nb, L, W, s)
+        nbytes = (3 * Cn + widths[0]) * nb * L * esz
+        outs = outs + [skip, D, sp, spitch, sc]
     else:
         once = lambda: mp.launch("causal_conv1d_silu_segments_reverse", dt, zx.data_ptr() + di * esz, dip, w, bias, ptrs, cw, cw, 3,
                                  gzx.data_ptr() + di * esz, dip, gw, gb, nb, L, W, s)
@@ -367,7 +376,7 @@ def build_case(mp, s, spec: str) -> Case:
         return gemm_case(mp, s, sfx, nums[0], nums[1], nums[2], tail[0] if tail else "nn")
     if op == "bmm":
         return bmm_case(mp, s, sfx, nums[0], nums[1])
-    if op in ("conv_fwd", "conv_rev"):
+    if op in ("conv_fwd", "conv_rev", "conv_rev_skip"):
         return conv_case(mp, s, op, sfx, nums[0], nums[1])
     if op in ("gated_norm_fwd", "gated_norm_rev", "gate_unfused_fwd", "gate_unfused_rev"):
         return gated_norm_case(mp, s, op, sfx, nums[0], *nums[1:3])

@@ -425,8 +425,9 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_tiled_kernel(const __h
   }
 }
 
-// SKIP: segments may carry a second upstream term (ConvSegs::skip_*), staged beside gy; that variant takes its tiles
-// from dynamic shared memory (64 KB).
+// SKIP: segments may carry a second upstream term (ConvSegs::skip_*), staged beside gy.  That variant stages ONE time
+// tile at a time (the third tile would otherwise cost a quarter of the resident warps, and the kernel is bound by
+// instruction issue and latency, not by bytes in flight: other CTAs of the SM cover a CTA's load phase).
 template <int W, bool SKIP>
 __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(const __half* __restrict__ x, size_t xp,
                                                                                const __half* __restrict__ w, const __half* __restrict__ bias,
@@ -434,14 +435,15 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(c
                                                                                float* __restrict__ gw, float* __restrict__ gbias, int L,
                                                                                int tiles_per_cta) {
   constexpr int H = W - 1;
+  constexpr int NBUF = SKIP ? 1 : 2;
   extern __shared__ __align__(16) unsigned char conv_rev_smem[];
   typedef __half (*TileX)[CT_L + 2 * H][CT_C];
   typedef __half (*TileG)[CT_L + H][CT_C];
-  TileX xs = reinterpret_cast<TileX>(conv_rev_smem);                                   // [2]: two tiles in turn; row r = step l0 - H + r
-  TileG gys = reinterpret_cast<TileG>(conv_rev_smem + sizeof(__half) * 2 * (CT_L + 2 * H) * CT_C);   // [2]: row r = step l0 + r
-  __half (*gxs)[CT_C] = reinterpret_cast<__half (*)[CT_C]>(reinterpret_cast<unsigned char*>(gys) + sizeof(__half) * 2 * (CT_L + H) * CT_C);
+  TileX xs = reinterpret_cast<TileX>(conv_rev_smem);                                   // [NBUF]: row r = step l0 - H + r
+  TileG gys = reinterpret_cast<TileG>(conv_rev_smem + sizeof(__half) * NBUF * (CT_L + 2 * H) * CT_C);   // [NBUF]: row r = step l0 + r
+  __half (*gxs)[CT_C] = reinterpret_cast<__half (*)[CT_C]>(reinterpret_cast<unsigned char*>(gys) + sizeof(__half) * NBUF * (CT_L + H) * CT_C);
   float (*red)[CT_C][W + 1] = reinterpret_cast<float (*)[CT_C][W + 1]>(reinterpret_cast<unsigned char*>(gxs) + sizeof(__half) * CT_L * CT_C);
-  TileG g2s = reinterpret_cast<TileG>(reinterpret_cast<unsigned char*>(red) + sizeof(float) * CT_LANES * CT_C * (W + 1));   // [2], SKIP only
+  TileG g2s = reinterpret_cast<TileG>(reinterpret_cast<unsigned char*>(red) + sizeof(float) * CT_LANES * CT_C * (W + 1));   // [1], SKIP only
   const int tid = threadIdx.x;
   const int c = (tid % (CT_C / 2)) * 2, lane = tid / (CT_C / 2);
   const int seg = conv_segment_of(sg, blockIdx.x);
@@ -480,14 +482,14 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(c
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 - H + r;
       const bool ok = l >= 0 && l < L && pk < packs_live;
-      cp_async_16_zfill(&xs[t & 1][r][pk * 8], ok ? xb + static_cast<size_t>(l) * xp + pk * 8 : xb, ok);
+      cp_async_16_zfill(&xs[t % NBUF][r][pk * 8], ok ? xb + static_cast<size_t>(l) * xp + pk * 8 : xb, ok);
     }
     for (int v = tid; v < (CT_L + H) * PPR; v += CT_THREADS) {
       const int r = v / PPR, pk = v % PPR;
       const int l = l0 + r;
       const bool ok = l < L && pk < packs_live;
-      cp_async_16_zfill(&gys[t & 1][r][pk * 8], ok ? gyb + static_cast<size_t>(l) * gyp + pk * 8 : gyb, ok);
-      if (SKIP && skip) cp_async_16_zfill(&g2s[t & 1][r][pk * 8], ok ? g2b + static_cast<size_t>(l) * g2p + pk * 8 : g2b, ok);
+      cp_async_16_zfill(&gys[t % NBUF][r][pk * 8], ok ? gyb + static_cast<size_t>(l) * gyp + pk * 8 : gyb, ok);
+      if (SKIP && skip) cp_async_16_zfill(&g2s[0][r][pk * 8], ok ? g2b + static_cast<size_t>(l) * g2p + pk * 8 : g2b, ok);
     }
     cp_async_commit();
   };
@@ -496,13 +498,18 @@ __global__ void __launch_bounds__(CT_THREADS) conv1d_silu_reverse_tiled_kernel(c
     const int l0 = (blockIdx.y * tiles_per_cta + t) * CT_L;
     if (l0 >= L) break;
     const bool more = t + 1 < tiles_per_cta && l0 + CT_L < L;
-    if (more) { stage(t + 1); cp_async_wait<1>(); } else cp_async_wait<0>();
+    if (NBUF == 2) {
+      if (more) { stage(t + 1); cp_async_wait<1>(); } else cp_async_wait<0>();
+    } else {
+      if (t > 0) { __syncthreads(); stage(t); }   // every thread is past the previous tile's walk
+      cp_async_wait<0>();
+    }
     __syncthreads();
     // ---- walk CT_STEPS (+ H look-ahead) steps of two channels ----
     {
-      const __half (*xt)[CT_C] = xs[t & 1];
-      const __half (*gt)[CT_C] = gys[t & 1];
-      const __half (*g2t)[CT_C] = g2s[t & 1];
+      const __half (*xt)[CT_C] = xs[t % NBUF];
+      const __half (*gt)[CT_C] = gys[t % NBUF];
+      const __half (*g2t)[CT_C] = g2s[0];
       const int s0 = lane * CT_STEPS;
       float2 xw[W], d[W];   // xw[k] = x at step s + k - H (tile row s + k); d[k] = dpre at step s - k
 #pragma unroll
@@ -1530,8 +1537,9 @@ static void conv_tiled_reverse(const void* x, len_t x_pitch, const void* w, cons
 #define CONV_REV(WV, SK)                                                                                                            \
   do {                                                                                                                              \
     constexpr int HV = WV - 1;                                                                                                      \
-    const size_t smem = sizeof(__half) * (2 * (CT_L + 2 * HV) * CT_C + 2 * (CT_L + HV) * CT_C + CT_L * CT_C) +                       \
-                        sizeof(float) * CT_LANES * CT_C * (WV + 1) + (SK ? sizeof(__half) * 2 * (CT_L + HV) * CT_C : 0);             \
+    constexpr int NB = SK ? 1 : 2;                                                                                                  \
+    const size_t smem = sizeof(__half) * (NB * (CT_L + 2 * HV) * CT_C + NB * (CT_L + HV) * CT_C + CT_L * CT_C) +                     \
+                        sizeof(float) * CT_LANES * CT_C * (WV + 1) + (SK ? sizeof(__half) * (CT_L + HV) * CT_C : 0);                 \
     if (smem > 48 * 1024)                                                                                                           \
       MP_CUDA_CHECK(cudaFuncSetAttribute(conv1d_silu_reverse_tiled_kernel<WV, SK>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
                                          static_cast<int>(smem)));                                                                  \
