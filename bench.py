@@ -481,6 +481,7 @@ def lm_workload_text(n_layer, batch):
 # (batch, head) sequence, so traffic grows in proportion to batch x seqlen x heads and is scaled to the step's shape.
 # A launcher that is not listed reports traffic null.
 LM_NCU_TRAFFIC = {
+    "ssd_scan_raw_r16": {"bytes": 81.9e6 + 29.9e6, "units": 4 * 4096 * 32},
     "ssd_scan_reverse_r16": {"bytes": 247.2e6 + 194.5e6 + 286.7e6, "units": 4 * 4096 * 32},
     "ssd_scan_r16": {"bytes": 81.9e6 + 29.9e6, "units": 4 * 4096 * 32},
 }

@@ -156,6 +156,10 @@ MP_DECL3(ssd_scan, const void* x, const void* dt, const void* A, const void* B, 
 /* Reverse of the scan: given gy (shape of y) writes (overwrites) gx, gdt (r32),
  * gA (r32, [heads]), gB, gC.  gB and gC are summed over the heads of a group. */
 MP_DECL3(ssd_scan_reverse, const void* x, const void* dt, const void* A, const void* B, const void* C, const void* gy, void* gx, void* gdt, void* gA, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
+/* launch_ssd_scan from the projection's raw outputs: dt = softplus(dt_raw + dt_bias[h]) (dt_raw: T, pitched [batch*seqlen, heads];
+ * dt_bias: acc [heads]) and A = -exp(A_log[h]) (acc) are formed inside the scan and left in dt_out (acc [batch, seqlen, heads])
+ * and A_out (acc [heads]) for launch_ssd_scan_reverse.  Same scratch as launch_ssd_scan. */
+MP_DECL3(ssd_scan_raw, const void* x, const void* dt_raw, len_t dt_pitch, const void* dt_bias, const void* A_log, const void* B, const void* C, void* y, void* dt_out, void* A_out, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
 MP_EXTERN_C len_t mpSsdScanScratchBytes(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, uint32_t reverse);
 MP_EXTERN_C len_t mpSsdScanGenericScratchBytes(uint32_t dtype_key, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, uint32_t reverse);
 

@@ -909,6 +909,8 @@ void mp_ssd_generic_reverse_r16(const void* x, const void* dt, const void* A, co
 bool mp_ssd_walk_supported(int L, int H, int P, int N, int G);
 void mp_ssd_walk_cumsum(const float* dt, const float* A, float* cum, float* dtt, float* colf_c, float* colf_a, int B, int L, int H,
                         int* carry_flags, int n_flags, cudaStream_t st);
+void mp_ssd_walk_cumsum_raw(const __half* raw, size_t raw_pitch, const float* bias, const float* A_log, float* dt_out, float* A_out, float* cum,
+                            float* dtt, float* colf_c, int B, int L, int H, int* carry_flags, int n_flags, cudaStream_t st);
 void mp_ssd_walk(int anti, const __half* q, const __half* k, const __half* v, const float* cum, const float* dtt, const float* colf, __half* out,
                  const __half* z, float* dot_out, __half* hs_out, float* carry, int* carry_flag, int max_ctas, int B, int L, int H, int G,
                  uint32_t* status, cudaStream_t st);
@@ -1002,6 +1004,57 @@ extern "C" void launch_ssd_scan_r16(const void* x, const void* dt, const void* A
   } else {
     ssd_operator(d, r, sc, state->status_dev, st);
   }
+}
+
+// Forward scan from the projection's raw outputs: dt = softplus(dt_raw + dt_bias[h]) and A = -exp(A_log[h]) are formed
+// inside the prefix-sum kernel of the chunk walk (two launches less per call) and left in dt_out [batch, seqlen, heads]
+// and A_out [heads] for launch_ssd_scan_reverse.  Elsewhere: launch_softplus_bias, launch_neg_exp, launch_ssd_scan.
+extern "C" void launch_softplus_bias_r16(const void*, len_t, const void*, void*, len_t, len_t, StreamContext);
+extern "C" void launch_softplus_bias_r32(const void*, len_t, const void*, void*, len_t, len_t, StreamContext);
+extern "C" void launch_softplus_bias_r64(const void*, len_t, const void*, void*, len_t, len_t, StreamContext);
+extern "C" void launch_neg_exp_r32(const void*, void*, len_t, StreamContext);
+extern "C" void launch_neg_exp_r64(const void*, void*, len_t, StreamContext);
+extern "C" void launch_ssd_scan_r32(const void*, const void*, const void*, const void*, const void*, void*, void*, len_t, len_t, len_t, len_t, len_t,
+                                    len_t, len_t, StreamContext);
+extern "C" void launch_ssd_scan_r64(const void*, const void*, const void*, const void*, const void*, void*, void*, len_t, len_t, len_t, len_t, len_t,
+                                    len_t, len_t, StreamContext);
+
+extern "C" void launch_ssd_scan_raw_r16(const void* x, const void* dt_raw, len_t dt_pitch, const void* dt_bias, const void* A_log, const void* Bm,
+                                        const void* Cm, void* y, void* dt_out, void* A_out, void* scratch, len_t batch, len_t seqlen, len_t heads,
+                                        len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext ctx) {
+  if (batch == 0 || seqlen == 0 || heads == 0) return;
+  const SsdDims d = ssd_dims(batch, seqlen, heads, headdim, dstate, ngroups, chunk);
+  if (ssd_tensor_path(d) && mp_ssd_walk_supported(d.L, d.H, d.P, d.N, d.G) && getenv("MP_SSD_LEGACY_FORWARD") == nullptr) {
+    if (scratch == nullptr) MP_FATAL("ssd_scan_raw: scratch must not be NULL");
+    MpStreamState* state = mp_state(ctx);
+    cudaStream_t st = mp_stream(ctx);
+    const WalkScratch w = walk_carve(scratch, d, false, 0);
+    mp_ssd_walk_cumsum_raw(static_cast<const __half*>(dt_raw), dt_pitch, static_cast<const float*>(dt_bias), static_cast<const float*>(A_log),
+                           static_cast<float*>(dt_out), static_cast<float*>(A_out), w.cum, w.dtt, w.colf_c, d.B, d.L, d.H, w.flags, 2 * d.B * d.H, st);
+    mp_ssd_walk(0, static_cast<const __half*>(Cm), static_cast<const __half*>(Bm), static_cast<const __half*>(x), w.cum, w.dtt, w.colf_c,
+                static_cast<__half*>(y), nullptr, nullptr, nullptr, w.carry_c, w.flags, state->sm_count, d.B, d.L, d.H, d.G, state->status_dev,
+                st);
+    return;
+  }
+  launch_softplus_bias_r16(dt_raw, dt_pitch, dt_bias, dt_out, batch * seqlen, heads, ctx);
+  launch_neg_exp_r32(A_log, A_out, heads, ctx);
+  launch_ssd_scan_r16(x, dt_out, A_out, Bm, Cm, y, scratch, batch, seqlen, heads, headdim, dstate, ngroups, chunk, ctx);
+}
+extern "C" void launch_ssd_scan_raw_r32(const void* x, const void* dt_raw, len_t dt_pitch, const void* dt_bias, const void* A_log, const void* Bm,
+                                        const void* Cm, void* y, void* dt_out, void* A_out, void* scratch, len_t batch, len_t seqlen, len_t heads,
+                                        len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext ctx) {
+  if (batch == 0 || seqlen == 0 || heads == 0) return;
+  launch_softplus_bias_r32(dt_raw, dt_pitch, dt_bias, dt_out, batch * seqlen, heads, ctx);
+  launch_neg_exp_r32(A_log, A_out, heads, ctx);
+  launch_ssd_scan_r32(x, dt_out, A_out, Bm, Cm, y, scratch, batch, seqlen, heads, headdim, dstate, ngroups, chunk, ctx);
+}
+extern "C" void launch_ssd_scan_raw_r64(const void* x, const void* dt_raw, len_t dt_pitch, const void* dt_bias, const void* A_log, const void* Bm,
+                                        const void* Cm, void* y, void* dt_out, void* A_out, void* scratch, len_t batch, len_t seqlen, len_t heads,
+                                        len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext ctx) {
+  if (batch == 0 || seqlen == 0 || heads == 0) return;
+  launch_softplus_bias_r64(dt_raw, dt_pitch, dt_bias, dt_out, batch * seqlen, heads, ctx);
+  launch_neg_exp_r64(A_log, A_out, heads, ctx);
+  launch_ssd_scan_r64(x, dt_out, A_out, Bm, Cm, y, scratch, batch, seqlen, heads, headdim, dstate, ngroups, chunk, ctx);
 }
 
 // Gradients of a loss with upstream gradient gy (same shape as y); every output is overwritten.

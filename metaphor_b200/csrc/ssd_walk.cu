@@ -842,17 +842,34 @@ __global__ void __launch_bounds__(W_THREADS, 1) ssd_group_grads_kernel(const __g
 // dt*A prefix sums inside every 128-step chunk, dt, and the column factors of both walk directions, all in
 // [B, H, L] order.  One CTA per (b, h, chunk).  Column factor of step t relative to the far end of its 8-step
 // piece: causal exp(cum[t | 7] - cum[t]) dt[t], anti-causal exp(cum[t] - cum[t & ~7]); both are at most one (dt).
+// RAW: the step sizes arrive as the projection's raw r16 output (row pitch `raw_pitch`) and the decay rates as A_log:
+//   dt = softplus(raw + bias[h]), A = -exp(A_log[h])  (the arithmetic of launch_softplus_bias / launch_neg_exp),
+// both also written out (dt_out [B, L, H], A_out [H]) for the reverse pass.
+template <bool RAW>
 __global__ void __launch_bounds__(WQ) ssd_walk_cumsum_kernel(const float* __restrict__ dt, const float* __restrict__ A, float* __restrict__ cum,
                                                              float* __restrict__ dtt, float* __restrict__ colf_c, float* __restrict__ colf_a,
-                                                             int L, int H, int* __restrict__ carry_flags, int n_flags) {
+                                                             int L, int H, int* __restrict__ carry_flags, int n_flags,
+                                                             const __half* __restrict__ raw, size_t raw_pitch, const float* __restrict__ bias,
+                                                             float* __restrict__ dt_out, float* __restrict__ A_out) {
   __shared__ float warp_tot[4];
   if (blockIdx.x == 0)   // the walks that follow in stream order hand states from CTA to CTA through these counters
     for (int i = threadIdx.x; i < n_flags; i += WQ) carry_flags[i] = 0;
   const int nc = L / WQ;
   const int c = blockIdx.x % nc, h = (blockIdx.x / nc) % H, b = blockIdx.x / (nc * H);
   const int t = threadIdx.x;
-  const float d = dt[(static_cast<size_t>(b) * L + c * WQ + t) * H + h];
-  float v = d * A[h];
+  float d, a;
+  if (RAW) {
+    const size_t row = static_cast<size_t>(b) * L + c * WQ + t;
+    const float pre = __half2float(raw[row * raw_pitch + h]) + bias[h];
+    d = pre > 20.f ? pre : log1pf(__expf(pre));
+    a = -__expf(A[h]);
+    dt_out[row * H + h] = d;
+    if (b == 0 && c == 0 && t == 0) A_out[h] = a;
+  } else {
+    d = dt[(static_cast<size_t>(b) * L + c * WQ + t) * H + h];
+    a = A[h];
+  }
+  float v = d * a;
 #pragma unroll
   for (int off = 1; off < 32; off <<= 1) {
     const float n = __shfl_up_sync(0xffffffffu, v, off);
@@ -910,7 +927,16 @@ bool mp_ssd_walk_supported(int L, int H, int P, int N, int G) {
 
 void mp_ssd_walk_cumsum(const float* dt, const float* A, float* cum, float* dtt, float* colf_c, float* colf_a, int B, int L, int H,
                         int* carry_flags, int n_flags, cudaStream_t st) {
-  ssd_walk_cumsum_kernel<<<B * H * (L / WQ), WQ, 0, st>>>(dt, A, cum, dtt, colf_c, colf_a, L, H, carry_flags, n_flags);
+  ssd_walk_cumsum_kernel<false><<<B * H * (L / WQ), WQ, 0, st>>>(dt, A, cum, dtt, colf_c, colf_a, L, H, carry_flags, n_flags, nullptr, 0, nullptr,
+                                                                 nullptr, nullptr);
+  MP_LAUNCH_CHECK();
+}
+
+// The same from the raw projection output and A_log (see the kernel); dt_out and A_out are what the reverse pass takes.
+void mp_ssd_walk_cumsum_raw(const __half* raw, size_t raw_pitch, const float* bias, const float* A_log, float* dt_out, float* A_out, float* cum,
+                            float* dtt, float* colf_c, int B, int L, int H, int* carry_flags, int n_flags, cudaStream_t st) {
+  ssd_walk_cumsum_kernel<true><<<B * H * (L / WQ), WQ, 0, st>>>(nullptr, A_log, cum, dtt, colf_c, nullptr, L, H, carry_flags, n_flags, raw, raw_pitch,
+                                                                bias, dt_out, A_out);
   MP_LAUNCH_CHECK();
 }
 

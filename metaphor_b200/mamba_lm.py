@@ -284,9 +284,9 @@ class MambaLM:
             self._L("causal_conv1d_silu_segments", zx + di * esz, dip, self._p(W, p + "conv_w"), self._p(W, p + "conv_b"),
                     (C.c_void_p * 3)(sv["xs"].data_ptr(), sv["Bs"].data_ptr(), sv["Cs"].data_ptr()), seg_widths, seg_widths, 3,
                     self.batch, self.seqlen, c.d_conv)
-            self._L("softplus_bias", zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), sv["dt"], T, H)
-            self._L32("neg_exp", self._p(self.w32, p + "A_log"), sv["A"], H)
-            self._L("ssd_scan", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], sv["y"], self.ssd_scratch, *self.ssd_dims)
+            # dt = softplus(raw + dt_bias) and A = -exp(A_log) are formed inside the scan and kept for the reverse pass
+            self._L("ssd_scan_raw", sv["xs"], zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), self._p(self.w32, p + "A_log"),
+                    sv["Bs"], sv["Cs"], sv["y"], sv["dt"], sv["A"], self.ssd_scratch, *self.ssd_dims)
             # skip, gate and the gated norm in one pass; the gated activation itself is never stored
             self._L("ssd_gate_rmsnorm", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, self._p(W, p + "gnorm_w"), c.eps, sv["un"],
                     sv["rstd2"], T, H, P)

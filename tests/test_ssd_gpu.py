@@ -112,3 +112,32 @@ def test_full_length_against_the_sequential_path(mp, stream):
             os.environ.pop("MP_SSD_FORCE_GENERIC", None)
     for got, want, name in zip(out["tensor"], out["sequential"], ("y", "gx", "gdt", "gA", "gB", "gC")):
         assert_close(got, want, 1e-2, f"full-length {name}")
+
+
+@pytest.mark.parametrize("dims", [(2, 512, 4, 64, 128, 1, 256), (10, 384, 16, 64, 128, 1, 128), (1, 512, 2, 128, 128, 1, 256)])
+def test_scan_from_raw_step_sizes_is_the_three_launches_in_one(mp, stream, dims):
+    """launch_ssd_scan_raw (softplus of the raw step sizes and -exp(A_log) inside the scan) against launch_softplus_bias +
+    launch_neg_exp + launch_ssd_scan on the same inputs: dt, A and y bit for bit (the last shape takes the composed path)."""
+    import torch
+    nb, L, H, P, N, G, Q = dims
+    x, _, _, Bm, Cm, _ = make_inputs(5, nb, L, H, P, N, G)
+    r = np.random.default_rng(6)
+    pitch = H + 8
+    raw = (r.standard_normal((nb * L, pitch)) - 4.0).astype(np.float16)
+    bias = (0.5 * r.standard_normal(H)).astype(np.float32)
+    A_log = np.log(r.uniform(1.0, 16.0, H)).astype(np.float32)
+    dx, dB, dC, draw, dbias, dAlog = (dev(a) for a in (x, Bm, Cm, raw, bias, A_log))
+    scratch = scratch_for(mp, dims, False)
+    dt1 = dev(np.full((nb, L, H), np.nan, np.float32)); A1 = dev(np.full(H, np.nan, np.float32)); y1 = dev(np.full(x.shape, np.nan, np.float16))
+    dt2 = dev(np.full((nb, L, H), np.nan, np.float32)); A2 = dev(np.full(H, np.nan, np.float32)); y2 = dev(np.full(x.shape, np.nan, np.float16))
+    torch.cuda.current_stream().synchronize()
+    mp.launch("softplus_bias", torch.float16, draw, pitch, dbias, dt1, nb * L, H, stream)
+    mp.launch("neg_exp", torch.float32, dAlog, A1, H, stream)
+    mp.launch("ssd_scan", torch.float16, dx, dt1, A1, dB, dC, y1, scratch, *dims, stream)
+    mp.launch("ssd_scan_raw", torch.float16, dx, draw, pitch, dbias, dAlog, dB, dC, y2, dt2, A2, scratch, *dims, stream)
+    stream.sync()
+    assert stream.status() == 0
+    assert np.array_equal(host(dt1), host(dt2))
+    assert np.array_equal(host(A1), host(A2))
+    assert np.array_equal(host(y1), host(y2))
+    assert np.isfinite(host(y2).astype(np.float32)).all()

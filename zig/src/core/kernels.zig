@@ -349,3 +349,9 @@ pub const causal_conv1d_silu_segments_reverse_skip = dispatch_array(opaque {}, .
     decls.launch_causal_conv1d_silu_segments_reverse_skip_r32,
     decls.launch_causal_conv1d_silu_segments_reverse_skip_r64,
 });
+
+pub const ssd_scan_raw = dispatch_array(opaque {}, .{
+    decls.launch_ssd_scan_raw_r16,
+    decls.launch_ssd_scan_raw_r32,
+    decls.launch_ssd_scan_raw_r64,
+});
