@@ -160,6 +160,10 @@ MP_DECL3(ssd_scan_reverse, const void* x, const void* dt, const void* A, const v
  * dt_bias: acc [heads]) and A = -exp(A_log[h]) (acc) are formed inside the scan and left in dt_out (acc [batch, seqlen, heads])
  * and A_out (acc [heads]) for launch_ssd_scan_reverse.  Same scratch as launch_ssd_scan. */
 MP_DECL3(ssd_scan_raw, const void* x, const void* dt_raw, len_t dt_pitch, const void* dt_bias, const void* A_log, const void* B, const void* C, void* y, void* dt_out, void* A_out, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
+/* launch_ssd_scan_reverse plus the reverses of dt = softplus(dt_raw + dt_bias[h]) and A = -exp(A_log[h]):
+ *   gdt_raw = gdt * sigmoid(dt_raw + dt_bias) (T, pitched), gdt_bias[h] += its sum (acc, may be NULL), gA_log[h] += gA[h] * A[h] (acc, may be NULL).
+ * gdt and gA are written too.  Same scratch as launch_ssd_scan_reverse. */
+MP_DECL3(ssd_scan_reverse_raw, const void* x, const void* dt, const void* A, const void* B, const void* C, const void* gy, const void* dt_raw, len_t dt_pitch, const void* dt_bias, void* gx, void* gdt, void* gA, void* gdt_raw, len_t gdt_raw_pitch, void* gdt_bias, void* gA_log, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext stream)
 MP_EXTERN_C len_t mpSsdScanScratchBytes(len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk, uint32_t reverse);
 MP_EXTERN_C len_t mpSsdScanGenericScratchBytes(uint32_t dtype_key, len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, uint32_t reverse);
 

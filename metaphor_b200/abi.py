@@ -63,6 +63,7 @@ LAUNCHERS = {
     "ssd_scan": [P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
     "ssd_scan_reverse": [P, P, P, P, P, P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
     "ssd_scan_raw": [P, P, L, P, P, P, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
+    "ssd_scan_reverse_raw": [P, P, P, P, P, P, P, L, P, P, P, P, P, L, P, P, P, P, P, L, L, L, L, L, L, L, CTX],
     # operators around the scan in a language-model step
     "embedding": [P, P, P, L, L, L, CTX],
     "embedding_reverse": [P, P, P, L, L, L, CTX],

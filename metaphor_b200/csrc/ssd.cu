@@ -599,13 +599,26 @@ __global__ void __launch_bounds__(256) ssd_boundary_dot_kernel(const __half* __r
 
 // One CTA per (b, h); one thread per step of a chunk (Q <= 256), chunks walked from the last to the first.
 // `halves` = 2: u and v are the sums of two arrays, the second `B*H*L` elements after the first.
+// With `raw` (the projection's raw step sizes, r16, pitched) the reverse of dt = softplus(raw + bias[h]) is applied on the
+// way out: graw = gdt * sigmoid(raw + bias) (r16, pitched), gbias[h] += its sum (the arithmetic of launch_softplus_bias_reverse).
+__device__ __forceinline__ float ssd_sigmoid(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -1.4426950408889634f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.f + e));
+  return r;
+}
 __global__ void __launch_bounds__(256) ssd_scalar_grads_kernel(const float* __restrict__ u, const float* __restrict__ v,
                                                                const float* __restrict__ dtt, const float* __restrict__ A,
                                                                const float* __restrict__ pin, float* __restrict__ gdt,
-                                                               float* __restrict__ gA_part, int B, int L, int H, int Q, int halves) {
+                                                               float* __restrict__ gA_part, int B, int L, int H, int Q, int halves,
+                                                               const __half* __restrict__ raw = nullptr, size_t raw_pitch = 0,
+                                                               const float* __restrict__ bias = nullptr, __half* __restrict__ graw = nullptr,
+                                                               size_t graw_pitch = 0, float* __restrict__ gbias = nullptr) {
   __shared__ float warp_tot[8];
   __shared__ float total_s;
   __shared__ float ga_red[8];
+  __shared__ float gb_red[8];
+  float gb_acc = 0.f;
   const int h = blockIdx.x % H, b = blockIdx.x / H;
   const size_t base = (static_cast<size_t>(b) * H + h) * L;
   const int nc = L / Q;
@@ -641,18 +654,27 @@ __global__ void __launch_bounds__(256) ssd_scalar_grads_kernel(const float* __re
     if (in) {
       const float ga = right + within + resid * (static_cast<float>(j + 1) / static_cast<float>(Q));
       const float dtv = dtt[base + t];
-      gdt[(static_cast<size_t>(b) * L + t) * H + h] = vt / dtv + Ah * ga;
+      const float gd = vt / dtv + Ah * ga;
+      const size_t row = static_cast<size_t>(b) * L + t;
+      gdt[row * H + h] = gd;
       ga_acc += dtv * ga;
+      if (raw != nullptr) {
+        const float gr = gd * ssd_sigmoid(__half2float(raw[row * raw_pitch + h]) + bias[h]);
+        graw[row * graw_pitch + h] = __float2half_rn(gr);
+        gb_acc += gr;
+      }
     }
     __syncthreads();
   }
   ga_acc = warp_reduce<SumOp>(ga_acc);
-  if ((threadIdx.x & 31) == 0) ga_red[threadIdx.x >> 5] = ga_acc;
+  gb_acc = warp_reduce<SumOp>(gb_acc);
+  if ((threadIdx.x & 31) == 0) { ga_red[threadIdx.x >> 5] = ga_acc; gb_red[threadIdx.x >> 5] = gb_acc; }
   __syncthreads();
   if (threadIdx.x == 0) {
-    float t = 0.f;
-    for (int w = 0; w < 8; ++w) t += ga_red[w];
+    float t = 0.f, tb = 0.f;
+    for (int w = 0; w < 8; ++w) { t += ga_red[w]; tb += gb_red[w]; }
     gA_part[blockIdx.x] = t;
+    if (raw != nullptr && gbias != nullptr) atomicAdd(gbias + h, tb);
   }
 }
 
@@ -673,12 +695,15 @@ __global__ void __launch_bounds__(256) ssd_fold_parts_kernel(const float* __rest
   st_pack(out + i, 0, pack<__half>(acc));
 }
 
-__global__ void ssd_sum_batches_kernel(const float* __restrict__ part, float* __restrict__ gA, int B, int H) {
+// gA[h] = sum over the batch; with A_log's gradient wanted (A = -exp(A_log), so dA / dA_log = A): gA_log[h] += gA[h] * A[h]
+__global__ void ssd_sum_batches_kernel(const float* __restrict__ part, float* __restrict__ gA, int B, int H,
+                                       const float* __restrict__ A = nullptr, float* __restrict__ gA_log = nullptr) {
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   if (h >= H) return;
   float s = 0.f;
   for (int b = 0; b < B; ++b) s += part[b * H + h];
   gA[h] = s;
+  if (gA_log != nullptr) gA_log[h] += s * A[h];
 }
 
 // ---------------------------------------------------------------------------
@@ -1059,15 +1084,30 @@ extern "C" void launch_ssd_scan_raw_r64(const void* x, const void* dt_raw, len_t
 
 // Gradients of a loss with upstream gradient gy (same shape as y); every output is overwritten.
 // gx: like x; gdt: like dt (r32); gA: [heads] r32; gB, gC: like B, C.
+namespace {
+struct RawSide { const __half* raw; size_t raw_pitch; const float* bias; __half* graw; size_t graw_pitch; float* gbias; float* gA_log; };
+}
+static bool ssd_scan_reverse_r16_impl(const void* x, const void* dt, const void* A, const void* Bm, const void* Cm, const void* gy, void* gx,
+                                      void* gdt, void* gA, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads,
+                                      len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext ctx, const RawSide* rs);
+
 extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const void* A, const void* Bm, const void* Cm,
                                             const void* gy, void* gx, void* gdt, void* gA, void* gB, void* gC, void* scratch,
                                             len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups,
                                             len_t chunk, StreamContext ctx) {
-  if (batch == 0 || seqlen == 0 || heads == 0) return;
+  ssd_scan_reverse_r16_impl(x, dt, A, Bm, Cm, gy, gx, gdt, gA, gB, gC, scratch, batch, seqlen, heads, headdim, dstate, ngroups, chunk, ctx,
+                            nullptr);
+}
+
+// Returns true when the raw-side gradients (rs) were produced inside the scan's own kernels.
+static bool ssd_scan_reverse_r16_impl(const void* x, const void* dt, const void* A, const void* Bm, const void* Cm, const void* gy, void* gx,
+                                      void* gdt, void* gA, void* gB, void* gC, void* scratch, len_t batch, len_t seqlen, len_t heads,
+                                      len_t headdim, len_t dstate, len_t ngroups, len_t chunk, StreamContext ctx, const RawSide* rs) {
+  if (batch == 0 || seqlen == 0 || heads == 0) return true;
   const SsdDims d = ssd_dims(batch, seqlen, heads, headdim, dstate, ngroups, chunk);
   if (!ssd_tensor_path(d)) {
     mp_ssd_generic_reverse_r16(x, dt, A, Bm, Cm, gy, gx, gdt, gA, gB, gC, scratch, batch, seqlen, heads, headdim, dstate, ngroups, ctx);
-    return;
+    return false;
   }
   if (scratch == nullptr) MP_FATAL("ssd_scan_reverse: scratch must not be NULL");
   MpStreamState* state = mp_state(ctx);
@@ -1108,16 +1148,22 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
     const int wnc = d.L / 128;
     ssd_boundary_dot_kernel<<<d.B * d.H * wnc, 256, 0, lane1>>>(w.hs_anti, w.hs_causal, w.pin, wnc, d.N * d.P);
     MP_LAUNCH_CHECK();
-    ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, lane1>>>(w.u, w.v, w.dtt, static_cast<const float*>(A), w.pin, static_cast<float*>(gdt), w.ga_part,
-                                                         d.B, d.L, d.H, 128, 2);
+    if (rs != nullptr)
+      ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, lane1>>>(w.u, w.v, w.dtt, static_cast<const float*>(A), w.pin, static_cast<float*>(gdt), w.ga_part,
+                                                           d.B, d.L, d.H, 128, 2, rs->raw, rs->raw_pitch, rs->bias, rs->graw, rs->graw_pitch,
+                                                           rs->gbias);
+    else
+      ssd_scalar_grads_kernel<<<d.B * d.H, 256, 0, lane1>>>(w.u, w.v, w.dtt, static_cast<const float*>(A), w.pin, static_cast<float*>(gdt), w.ga_part,
+                                                           d.B, d.L, d.H, 128, 2);
     MP_LAUNCH_CHECK();
-    ssd_sum_batches_kernel<<<(d.H + 127) / 128, 128, 0, lane1>>>(w.ga_part, static_cast<float*>(gA), d.B, d.H);
+    ssd_sum_batches_kernel<<<(d.H + 127) / 128, 128, 0, lane1>>>(w.ga_part, static_cast<float*>(gA), d.B, d.H, static_cast<const float*>(A),
+                                                                 rs != nullptr ? rs->gA_log : nullptr);
     MP_LAUNCH_CHECK();
     if (side) {
       MP_CUDA_CHECK(cudaEventRecord(state->aux_join[1], lane1));
       MP_CUDA_CHECK(cudaStreamWaitEvent(st, state->aux_join[1], 0));
     }
-    return;
+    return true;
   }
   const SsdScratch sc = ssd_carve(scratch, d, true);
   ssd_cumsum_kernel<<<d.B * d.H * d.nc, 256, 0, st>>>(static_cast<const float*>(dt), static_cast<const float*>(A), sc.cum, sc.dtt,
@@ -1182,4 +1228,53 @@ extern "C" void launch_ssd_scan_reverse_r16(const void* x, const void* dt, const
     MP_LAUNCH_CHECK();
   ssd_sum_batches_kernel<<<(d.H + 127) / 128, 128, 0, st>>>(sc.ga_part, static_cast<float*>(gA), d.B, d.H);
   MP_LAUNCH_CHECK();
+  return false;
+}
+
+// launch_ssd_scan_reverse plus the reverses of dt = softplus(dt_raw + dt_bias[h]) and A = -exp(A_log[h]):
+//   gdt_raw = gdt * sigmoid(dt_raw + dt_bias) (T, pitched), gdt_bias[h] += its sum, gA_log[h] += gA[h] * A[h]
+// inside the scan's scalar-gradient kernels where the chunk walk runs (two launches less per call), else as
+// launch_softplus_bias_reverse and launch_hadamard_reverse after launch_ssd_scan_reverse.  gdt and gA are written as well.
+extern "C" void launch_softplus_bias_reverse_r16(const void*, len_t, const void*, const void*, void*, len_t, void*, len_t, len_t, StreamContext);
+extern "C" void launch_softplus_bias_reverse_r32(const void*, len_t, const void*, const void*, void*, len_t, void*, len_t, len_t, StreamContext);
+extern "C" void launch_softplus_bias_reverse_r64(const void*, len_t, const void*, const void*, void*, len_t, void*, len_t, len_t, StreamContext);
+extern "C" void launch_hadamard_reverse_r32(const void*, const void*, void*, len_t, StreamContext);
+extern "C" void launch_hadamard_reverse_r64(const void*, const void*, void*, len_t, StreamContext);
+extern "C" void launch_ssd_scan_reverse_r32(const void*, const void*, const void*, const void*, const void*, const void*, void*, void*, void*, void*,
+                                            void*, void*, len_t, len_t, len_t, len_t, len_t, len_t, len_t, StreamContext);
+extern "C" void launch_ssd_scan_reverse_r64(const void*, const void*, const void*, const void*, const void*, const void*, void*, void*, void*, void*,
+                                            void*, void*, len_t, len_t, len_t, len_t, len_t, len_t, len_t, StreamContext);
+
+extern "C" void launch_ssd_scan_reverse_raw_r16(const void* x, const void* dt, const void* A, const void* Bm, const void* Cm, const void* gy,
+                                                const void* dt_raw, len_t dt_pitch, const void* dt_bias, void* gx, void* gdt, void* gA,
+                                                void* gdt_raw, len_t gdt_raw_pitch, void* gdt_bias, void* gA_log, void* gB, void* gC, void* scratch,
+                                                len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk,
+                                                StreamContext ctx) {
+  if (batch == 0 || seqlen == 0 || heads == 0) return;
+  RawSide rs{static_cast<const __half*>(dt_raw), dt_pitch, static_cast<const float*>(dt_bias), static_cast<__half*>(gdt_raw), gdt_raw_pitch,
+             static_cast<float*>(gdt_bias), static_cast<float*>(gA_log)};
+  if (ssd_scan_reverse_r16_impl(x, dt, A, Bm, Cm, gy, gx, gdt, gA, gB, gC, scratch, batch, seqlen, heads, headdim, dstate, ngroups, chunk, ctx, &rs))
+    return;
+  launch_softplus_bias_reverse_r16(dt_raw, dt_pitch, dt_bias, gdt, gdt_raw, gdt_raw_pitch, gdt_bias, batch * seqlen, heads, ctx);
+  if (gA_log != nullptr) launch_hadamard_reverse_r32(gA, A, gA_log, heads, ctx);
+}
+extern "C" void launch_ssd_scan_reverse_raw_r32(const void* x, const void* dt, const void* A, const void* Bm, const void* Cm, const void* gy,
+                                                const void* dt_raw, len_t dt_pitch, const void* dt_bias, void* gx, void* gdt, void* gA,
+                                                void* gdt_raw, len_t gdt_raw_pitch, void* gdt_bias, void* gA_log, void* gB, void* gC, void* scratch,
+                                                len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk,
+                                                StreamContext ctx) {
+  if (batch == 0 || seqlen == 0 || heads == 0) return;
+  launch_ssd_scan_reverse_r32(x, dt, A, Bm, Cm, gy, gx, gdt, gA, gB, gC, scratch, batch, seqlen, heads, headdim, dstate, ngroups, chunk, ctx);
+  launch_softplus_bias_reverse_r32(dt_raw, dt_pitch, dt_bias, gdt, gdt_raw, gdt_raw_pitch, gdt_bias, batch * seqlen, heads, ctx);
+  if (gA_log != nullptr) launch_hadamard_reverse_r32(gA, A, gA_log, heads, ctx);
+}
+extern "C" void launch_ssd_scan_reverse_raw_r64(const void* x, const void* dt, const void* A, const void* Bm, const void* Cm, const void* gy,
+                                                const void* dt_raw, len_t dt_pitch, const void* dt_bias, void* gx, void* gdt, void* gA,
+                                                void* gdt_raw, len_t gdt_raw_pitch, void* gdt_bias, void* gA_log, void* gB, void* gC, void* scratch,
+                                                len_t batch, len_t seqlen, len_t heads, len_t headdim, len_t dstate, len_t ngroups, len_t chunk,
+                                                StreamContext ctx) {
+  if (batch == 0 || seqlen == 0 || heads == 0) return;
+  launch_ssd_scan_reverse_r64(x, dt, A, Bm, Cm, gy, gx, gdt, gA, gB, gC, scratch, batch, seqlen, heads, headdim, dstate, ngroups, chunk, ctx);
+  launch_softplus_bias_reverse_r64(dt_raw, dt_pitch, dt_bias, gdt, gdt_raw, gdt_raw_pitch, gdt_bias, batch * seqlen, heads, ctx);
+  if (gA_log != nullptr) launch_hadamard_reverse_r64(gA, A, gA_log, heads, ctx);
 }

@@ -141,3 +141,45 @@ def test_scan_from_raw_step_sizes_is_the_three_launches_in_one(mp, stream, dims)
     assert np.array_equal(host(A1), host(A2))
     assert np.array_equal(host(y1), host(y2))
     assert np.isfinite(host(y2).astype(np.float32)).all()
+
+
+@pytest.mark.parametrize("dims", [(2, 512, 4, 64, 128, 1, 256), (10, 384, 16, 64, 128, 1, 128), (1, 512, 2, 128, 128, 1, 256)])
+def test_reverse_with_the_raw_side_gradients_is_the_three_launches_in_one(mp, stream, dims):
+    """launch_ssd_scan_reverse_raw against launch_ssd_scan_reverse + launch_softplus_bias_reverse + launch_hadamard_reverse:
+    gx, gdt, gA, gB, gC and the raw step sizes' gradient bit for bit, the accumulated dt_bias / A_log gradients to 1e-5."""
+    import torch
+    nb, L, H, P, N, G, Q = dims
+    x, _, _, Bm, Cm, gy = make_inputs(7, nb, L, H, P, N, G)
+    r = np.random.default_rng(8)
+    pitch = H + 8
+    raw = (r.standard_normal((nb * L, pitch)) - 4.0).astype(np.float16)
+    bias = (0.5 * r.standard_normal(H)).astype(np.float32)
+    A_log = np.log(r.uniform(1.0, 16.0, H)).astype(np.float32)
+    dx, dB, dC, dgy, draw, dbias, dAlog = (dev(a) for a in (x, Bm, Cm, gy, raw, bias, A_log))
+    dt = dev(np.zeros((nb, L, H), np.float32)); A = dev(np.zeros(H, np.float32))
+    torch.cuda.current_stream().synchronize()
+    mp.launch("softplus_bias", torch.float16, draw, pitch, dbias, dt, nb * L, H, stream)
+    mp.launch("neg_exp", torch.float32, dAlog, A, H, stream)
+    scratch = scratch_for(mp, dims, True)
+    gb0 = r.standard_normal(H).astype(np.float32); gl0 = r.standard_normal(H).astype(np.float32)
+    outs = []
+    for fused in (False, True):
+        gx = dev(np.full(x.shape, np.nan, np.float16)); gdt = dev(np.full((nb, L, H), np.nan, np.float32)); gA = dev(np.full(H, np.nan, np.float32))
+        gB = dev(np.full(Bm.shape, np.nan, np.float16)); gC = dev(np.full(Cm.shape, np.nan, np.float16))
+        graw = dev(np.full((nb * L, pitch), 2, np.float16)); gbias = dev(gb0.copy()); glog = dev(gl0.copy())
+        torch.cuda.current_stream().synchronize()
+        if fused:
+            mp.launch("ssd_scan_reverse_raw", torch.float16, dx, dt, A, dB, dC, dgy, draw, pitch, dbias, gx, gdt, gA, graw, pitch, gbias, glog,
+                      gB, gC, scratch, *dims, stream)
+        else:
+            mp.launch("ssd_scan_reverse", torch.float16, dx, dt, A, dB, dC, dgy, gx, gdt, gA, gB, gC, scratch, *dims, stream)
+            mp.launch("softplus_bias_reverse", torch.float16, draw, pitch, dbias, gdt, graw, pitch, gbias, nb * L, H, stream)
+            mp.launch("hadamard_reverse", torch.float32, gA, A, glog, H, stream)
+        stream.sync()
+        assert stream.status() == 0
+        outs.append([host(t) for t in (gx, gdt, gA, gB, gC, graw, gbias, glog)])
+    for a, b, name in zip(outs[0][:6], outs[1][:6], ("gx", "gdt", "gA", "gB", "gC", "graw")):
+        assert np.array_equal(a, b), name
+    assert np.all(outs[1][5][:, H:] == 2)
+    for a, b, name in zip(outs[0][6:], outs[1][6:], ("gdt_bias", "gA_log")):
+        assert_close(b, a.astype(np.float64), 1e-5, name)

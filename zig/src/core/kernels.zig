@@ -355,3 +355,9 @@ pub const ssd_scan_raw = dispatch_array(opaque {}, .{
     decls.launch_ssd_scan_raw_r32,
     decls.launch_ssd_scan_raw_r64,
 });
+
+pub const ssd_scan_reverse_raw = dispatch_array(opaque {}, .{
+    decls.launch_ssd_scan_reverse_raw_r16,
+    decls.launch_ssd_scan_reverse_raw_r32,
+    decls.launch_ssd_scan_reverse_raw_r64,
+});
