@@ -483,6 +483,7 @@ def lm_workload_text(n_layer, batch):
 LM_NCU_TRAFFIC = {
     "ssd_scan_raw_r16": {"bytes": 81.9e6 + 29.9e6, "units": 4 * 4096 * 32},
     "ssd_scan_reverse_r16": {"bytes": 247.2e6 + 194.5e6 + 286.7e6, "units": 4 * 4096 * 32},
+    "ssd_scan_reverse_raw_r16": {"bytes": 247.2e6 + 194.5e6 + 286.7e6, "units": 4 * 4096 * 32},   # the same three kernels
     "ssd_scan_r16": {"bytes": 81.9e6 + 29.9e6, "units": 4 * 4096 * 32},
 }
 

@@ -31,6 +31,7 @@ graph launches, on the second stream.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import math
 from dataclasses import dataclass
 
@@ -346,10 +347,17 @@ class MambaLM:
             self._L("inner_product_ji_jk_ik", sv["un"], self.gh, 1.0, self._p(G16, p + "out_proj"), 0.0, di, T, c.d_model)
             self._L("ssd_gate_rmsnorm_reverse", sv["y"], sv["xs"], self._p(self.w32, p + "D"), zx, dip, self._p(W, p + "gnorm_w"), sv["rstd2"],
                     self.gun, self.gy, gzx, dip, self._p(G32, p + "D"), self._p(G16, p + "gnorm_w"), 0.0, self.rms_scratch, T, H, P)
-            # the scan's reverse also hands back the gradients of the raw step sizes (through the softplus), of dt_bias and of A_log
-            self._L("ssd_scan_reverse_raw", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], self.gy, zx + (di + c.conv_dim) * esz, dip,
-                    self._p(self.w32, p + "dt_bias"), self.gxs, self.gdt, self.gA, gzx + (di + c.conv_dim) * esz, dip, self._p(G32, p + "dt_bias"),
-                    self._p(G32, p + "A_log"), self.gBs, self.gCs, self.ssd_scratch, *self.ssd_dims)
+            if os.environ.get("MP_LM_SPLIT_SCAN_REVERSE"):   # A/B: the three launches the fused entry replaces
+                self._L("ssd_scan_reverse", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], self.gy, self.gxs, self.gdt, self.gA,
+                        self.gBs, self.gCs, self.ssd_scratch, *self.ssd_dims)
+                self._L32("hadamard_reverse", self.gA, sv["A"], self._p(G32, p + "A_log"), H)
+                self._L("softplus_bias_reverse", zx + (di + c.conv_dim) * esz, dip, self._p(self.w32, p + "dt_bias"), self.gdt,
+                        gzx + (di + c.conv_dim) * esz, dip, self._p(G32, p + "dt_bias"), T, H)
+            else:
+              # the scan's reverse also hands back the gradients of the raw step sizes (through the softplus), of dt_bias and of A_log
+              self._L("ssd_scan_reverse_raw", sv["xs"], sv["dt"], sv["A"], sv["Bs"], sv["Cs"], self.gy, zx + (di + c.conv_dim) * esz, dip,
+                      self._p(self.w32, p + "dt_bias"), self.gxs, self.gdt, self.gA, gzx + (di + c.conv_dim) * esz, dip, self._p(G32, p + "dt_bias"),
+                      self._p(G32, p + "A_log"), self.gBs, self.gCs, self.ssd_scratch, *self.ssd_dims)
             # the D skip's share of the x gradient (D[h] * gy) joins the scan's inside the convolution's reverse
             self._L("causal_conv1d_silu_segments_reverse_skip", zx + di * esz, dip, self._p(W, p + "conv_w"), self._p(W, p + "conv_b"),
                     (C.c_void_p * 3)(self.gxs.data_ptr(), self.gBs.data_ptr(), self.gCs.data_ptr()), seg_widths, seg_widths, 3,
