@@ -1103,21 +1103,21 @@ __global__ void __launch_bounds__(GN_THREADS) gate_rmsnorm_reverse_h2_kernel(
 
 // ggain = alpha * ggain + sum over the CTAs' partial rows (fixed order)
 template <typename T>
-__global__ void __launch_bounds__(256) gate_rmsnorm_fold_kernel(const typename Acc<T>::type* __restrict__ partial, int nrows, size_t width,
-                                                                typename Acc<T>::type alpha, T* __restrict__ ggain) {
+__global__ void __launch_bounds__(1024) gate_rmsnorm_fold_kernel(const typename Acc<T>::type* __restrict__ partial, int nrows, size_t width,
+                                                                 typename Acc<T>::type alpha, T* __restrict__ ggain) {
   using A = typename Acc<T>::type;
-  __shared__ A part[8][33];
-  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  __shared__ A part[32][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;   // 32 columns x 32 row slices: ~10 dependent additions per thread
   const size_t c = blockIdx.x * static_cast<size_t>(32) + cx;
   A sum = A(0);
   if (c < width)
-    for (int r = ry; r < nrows; r += 8) sum += partial[static_cast<size_t>(r) * width + c];
+    for (int r = ry; r < nrows; r += 32) sum += partial[static_cast<size_t>(r) * width + c];
   part[ry][cx] = sum;
   __syncthreads();
   if (ry == 0 && c < width) {
     A t = A(0);
 #pragma unroll
-    for (int q = 0; q < 8; ++q) t += part[q][cx];
+    for (int q = 0; q < 32; ++q) t += part[q][cx];
     if (alpha != A(0)) t += alpha * mp_up(ggain[c]);
     ggain[c] = mp_down<T>(t);
   }
@@ -1889,7 +1889,7 @@ void ssd_gate_rmsnorm_reverse_impl(const void* y, const void* x, const void* D, 
 #undef GN_REV
   MP_LAUNCH_CHECK();
   if (ggain != nullptr) {
-    gate_rmsnorm_fold_kernel<T><<<static_cast<unsigned>((width + 31) / 32), 256, 0, st>>>(static_cast<const A*>(scratch), static_cast<int>(grid), width,
+    gate_rmsnorm_fold_kernel<T><<<static_cast<unsigned>((width + 31) / 32), 1024, 0, st>>>(static_cast<const A*>(scratch), static_cast<int>(grid), width,
                                                                                           static_cast<A>(alpha), static_cast<T*>(ggain));
     MP_LAUNCH_CHECK();
   }

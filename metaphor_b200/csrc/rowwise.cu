@@ -674,27 +674,28 @@ __global__ void __launch_bounds__(STG_THREADS, StgOcc<T, PPT>::value) rmsnorm_re
   }
 }
 
-// ggain[j] = sum_p partial[p][j] + alpha*ggain[j].  CTA = 32 columns x 8 slices.
+// ggain[j] = sum_p partial[p][j] + alpha*ggain[j].  CTA = 32 columns x blockDim.x / 32 slices (8 or 32: a few hundred
+// partial rows are a chain of ~40 dependent additions per thread with 8 slices, ~10 with 32).
 template <typename T>
-__global__ void __launch_bounds__(256) rmsnorm_fold_kernel(const typename Acc<T>::type* __restrict__ partial, T* ggain,
-                                                           typename Acc<T>::type alpha, bool blend, size_t n, size_t slots) {
+__global__ void __launch_bounds__(1024) rmsnorm_fold_kernel(const typename Acc<T>::type* __restrict__ partial, T* ggain,
+                                                            typename Acc<T>::type alpha, bool blend, size_t n, size_t slots) {
   using A = typename Acc<T>::type;
-  __shared__ A sm[8][33];
-  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5;
+  __shared__ A sm[32][33];
+  const int lane = threadIdx.x & 31, slice = threadIdx.x >> 5, slices = blockDim.x >> 5;
   const size_t col = static_cast<size_t>(blockIdx.x) * 32 + lane;
   A s = A(0);
   if (col < n) {
-    for (size_t p = slice; p < slots; p += 8) s += partial[p * n + col];
+    for (size_t p = slice; p < slots; p += slices) s += partial[p * n + col];
   }
   sm[slice][lane] = s;
   __syncthreads();
   if (slice == 0 && col < n) {
     A r = A(0);
-#pragma unroll
-    for (int w = 0; w < 8; ++w) r += sm[w][lane];
+    for (int w = 0; w < slices; ++w) r += sm[w][lane];
     ggain[col] = mp_down<T>(blend ? r + alpha * mp_up(ggain[col]) : r);
   }
 }
+inline unsigned rmsnorm_fold_threads(size_t slots) { return slots > 64 ? 1024u : 256u; }
 
 // First stage of a two-stage fold for many partial rows: CTA (column block c,
 // split f) sums the partial rows f, f+F, f+2F, ... of 32*W columns (W = values
@@ -1187,9 +1188,9 @@ static void rmsnorm_ij_j_reverse_impl(const void* x_, const void* gain_, const v
     const dim3 g1(static_cast<unsigned>((n + 32 * W - 1) / (32 * W)), FOLD_SPLITS);
     rmsnorm_fold_stage1_kernel<A><<<g1, 256, 0, st>>>(partial, partial2, n, slots);
     MP_LAUNCH_CHECK();
-    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial2, ggain, a, blend, n, FOLD_SPLITS);
+    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), rmsnorm_fold_threads(FOLD_SPLITS), 0, st>>>(partial2, ggain, a, blend, n, FOLD_SPLITS);
   } else {
-    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial, ggain, a, blend, n, slots);
+    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), rmsnorm_fold_threads(slots), 0, st>>>(partial, ggain, a, blend, n, slots);
   }
   MP_LAUNCH_CHECK();
 }
@@ -1327,9 +1328,9 @@ extern "C" int launch_rmsnorm_ij_j_reverse_static_r32(const void* x_, const void
     const dim3 g1(static_cast<unsigned>((n + 32 * W - 1) / (32 * W)), FOLD_SPLITS);
     rmsnorm_fold_stage1_kernel<A><<<g1, 256, 0, st>>>(partial, partial2, n, slots);
     MP_LAUNCH_CHECK();
-    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial2, ggain, a, blend, n, FOLD_SPLITS);
+    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), rmsnorm_fold_threads(FOLD_SPLITS), 0, st>>>(partial2, ggain, a, blend, n, FOLD_SPLITS);
   } else {
-    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), 256, 0, st>>>(partial, ggain, a, blend, n, slots);
+    rmsnorm_fold_kernel<T><<<static_cast<unsigned>((n + 31) / 32), rmsnorm_fold_threads(slots), 0, st>>>(partial, ggain, a, blend, n, slots);
   }
   MP_LAUNCH_CHECK();
   return 0;
