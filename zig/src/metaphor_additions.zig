@@ -9,6 +9,7 @@ pub const ops_additions = struct {
     pub const softmax = @import("ops/softmax.zig").forward;
     pub const rmsnorm = @import("ops/rmsnorm.zig").forward;
     pub const ssd_scan = @import("ops/ssd.zig").forward;
+    pub const gated_norm = @import("ops/gated_norm.zig").forward;
     pub const permutate = @import("ops/permutate.zig").forward; // replaces the rank-2-only version
     // README spellings
     pub const innerProduct = @import("ops/inner_product.zig").forward;
