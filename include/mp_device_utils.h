@@ -59,6 +59,10 @@ MP_EXTERN_C void mpSetWaitLimit(StreamContext, len_t microseconds);
 /* Launches a one-CTA kernel whose wait can never be satisfied: it returns after the stream's wait limit with
  * MP_STATUS_WAIT_TIMEOUT in the status word.  A check of the time-out path that faults nothing. */
 MP_EXTERN_C void mpSelfTestWaitTimeout(StreamContext);
+/* The work partition of the SSD chunk walk as the kernels compute it (host-side copy of the same function, no GPU needed):
+ * segment idx of CTA cta (of ncta <= nseq) for nseq sequences of nc chunks; out[5] = {sequence, first chunk position,
+ * chunks, state carried in, state carried out}; returns 0 past the CTA's last segment. */
+MP_EXTERN_C int mpSsdWalkPartition(int cta, int ncta, int nseq, int nc, int idx, int* out);
 
 /* Bytes of library-owned workspace attached to the stream (split-K partials,
  * column-reduce partials, tensor-map staging).  Allocated once in

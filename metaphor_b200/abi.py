@@ -108,6 +108,7 @@ UTILS = {
     "mpGetStatus": (U32, [CTX]),
     "mpSetWaitLimit": (None, [CTX, L]),
     "mpSelfTestWaitTimeout": (None, [CTX]),
+    "mpSsdWalkPartition": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]),
     "mpWorkspaceBytes": (L, [CTX]),
     "mpDeviceSmCount": (U32, [CTX]),
     "mpHostAlloc": (P, [L]),

@@ -68,7 +68,7 @@ struct WalkArgs {
 // FIRST and leaves its final state in `carry`; the last part is walked LAST and starts from the state the
 // neighbouring CTA left there - long before, so the wait on `carry_flag` does not hold anything up (it is bounded).
 struct WalkSeg { int seq, p0, n, cin, cout; };
-__device__ __forceinline__ bool walk_segment(int cta, int ncta, int nseq, int nc, int idx, WalkSeg& sg) {
+__host__ __device__ __forceinline__ bool walk_segment(int cta, int ncta, int nseq, int nc, int idx, WalkSeg& sg) {
   const long long U = static_cast<long long>(nseq) * nc;
   const long long lo = cta * U / ncta, hi = (cta + 1) * U / ncta;
   const int s_lo = static_cast<int>(lo / nc), j_lo = static_cast<int>(lo % nc);
@@ -917,6 +917,17 @@ CUtensorMap walk_map(const void* base, size_t rows, size_t cols) {
 }
 
 }  // namespace
+
+// Host-side view of the chunk walk's work partition (the function the kernels use, compiled for the host): segment
+// `idx` of CTA `cta` out of `ncta` for `nseq` sequences of `nc` chunks -> out = {sequence, first position, chunks,
+// carried-in state, carried-out state}; returns 0 past the CTA's last segment.  For tests; needs no GPU.
+extern "C" int mpSsdWalkPartition(int cta, int ncta, int nseq, int nc, int idx, int* out) {
+  WalkSeg sg;
+  if (ncta <= 0 || ncta > nseq || nc <= 0 || cta < 0 || cta >= ncta || idx < 0) return 0;
+  if (!walk_segment(cta, ncta, nseq, nc, idx, sg)) return 0;
+  out[0] = sg.seq; out[1] = sg.p0; out[2] = sg.n; out[3] = sg.cin; out[4] = sg.cout;
+  return 1;
+}
 
 // ---------------------------------------------------------------------------
 // Interface to the launchers in ssd.cu.
