@@ -736,6 +736,119 @@ static void gemm(int key, int kind, const void* a, const void* b, double alpha, 
   else if (kind == 1) kernels::ip_ij_kj_ik[key](a, b, alpha, c, beta, m, n, k, ctx);
   else kernels::ip_ji_jk_ik[key](a, b, alpha, c, beta, m, n, k, ctx);
 }
+// --- rank-N contractions (NOTES.md:3-5; grammar expression_parsing.zig:258-317) ---
+// The indices fall into four groups: batch (both operands and the output), rows (first operand and output), columns
+// (second operand and output) and summed (both operands only).  With every group flattened the contraction is
+// C[batch][rows, columns] = A[batch][rows, summed] . B[batch][summed, columns]; an operand whose indices already lie
+// as [batch, rows, summed] / [batch, summed, rows] (second operand: [batch, summed, columns] / [batch, columns,
+// summed]) goes to the kernel of that form where it lies, any other order passes through the general permutation first.
+struct SplitExpr { std::string xs, ys, os; };
+static SplitExpr split_contraction(const std::string& expr) {
+  const size_t comma = expr.find(','), arrow = expr.find("->");
+  if (comma == std::string::npos || arrow == std::string::npos || comma > arrow) panic("inner_product: expression must read \"x,y->z\"");
+  return {expr.substr(0, comma), expr.substr(comma + 1, arrow - comma - 1), expr.substr(arrow + 2)};
+}
+static void check_indices(const std::string& s, size_t rank) {
+  if (s.size() != rank) panic("inner_product: the expression's rank differs from the tensor's");
+  if (s.size() > 6) panic("inner_product: rank above 6");
+  for (size_t i = 0; i < s.size(); ++i)
+    if (s[i] < 'a' || s[i] > 'z' || s.find(s[i]) != i) panic("inner_product: indices must be distinct lower case characters");
+}
+static bool has(const std::string& s, char c) { return s.find(c) != std::string::npos; }
+static std::vector<size_t> order_into(const std::string& from, const std::string& to) {   // perm[i] = position of from[i] in to
+  std::vector<size_t> perm(from.size());
+  for (size_t i = 0; i < from.size(); ++i) perm[i] = to.find(from[i]);
+  return perm;
+}
+static ContractionPlan plan_contraction(const std::string& xs, const std::string& ys, const std::string& os,
+                                        const std::vector<size_t>& xsz, const std::vector<size_t>& ysz, bool may_swap) {
+  check_indices(xs, xsz.size()); check_indices(ys, ysz.size()); check_indices(os, os.size());
+  size_t extent[26] = {};
+  for (size_t i = 0; i < xs.size(); ++i) extent[xs[i] - 'a'] = xsz[i];
+  for (size_t i = 0; i < ys.size(); ++i) {
+    if (has(xs, ys[i]) && extent[ys[i] - 'a'] != ysz[i]) panic("inner_product: the operands' sizes differ at a shared index");
+    extent[ys[i] - 'a'] = ysz[i];
+  }
+  std::string B, M, N, K;   // batch, rows, columns (in the output's order), summed (in the first operand's order)
+  for (char c : os) {
+    const bool in_x = has(xs, c), in_y = has(ys, c);
+    if (in_x && in_y) B += c; else if (in_x) M += c; else if (in_y) N += c;
+    else panic("inner_product: an output index is in neither operand");
+  }
+  for (char c : xs) if (!has(os, c)) { if (!has(ys, c)) panic("inner_product: an index of one operand only must be in the output"); K += c; }
+  for (char c : ys) if (!has(os, c) && !has(xs, c)) panic("inner_product: an index of one operand only must be in the output");
+  // "ik,ij->jk": the output lists the second operand's indices first: C^T = B^T A^T, the same contraction with the operands exchanged
+  if (may_swap && !M.empty() && !N.empty() && os != B + M + N && os == B + N + M) {
+    ContractionPlan p = plan_contraction(ys, xs, os, ysz, xsz, false);
+    p.swap = true;
+    return p;
+  }
+  ContractionPlan p;
+  auto volume = [&](const std::string& s) { size_t v = 1; for (char c : s) v *= extent[c - 'a']; return v; };
+  p.batch = B.empty() ? 0 : volume(B);
+  p.m = volume(M); p.n = volume(K); p.k = volume(N);
+  const std::string x_rows = B + M + K, x_cols = B + K + M, y_rows = B + K + N, y_cols = B + N + K;
+  const bool x_a = xs == x_rows, x_t = xs == x_cols, y_a = ys == y_rows, y_t = ys == y_cols;
+  // kinds the kernels take: (rows, rows) = 0, (rows, cols) = 1, (cols, rows) = 2
+  if (x_a && y_a) p.kind = 0;
+  else if (x_a && y_t) p.kind = 1;
+  else if (x_t && y_a) p.kind = 2;
+  else if (x_a || x_t) { p.kind = x_a ? 0 : 2; p.y_perm = order_into(ys, y_rows); }
+  else if (y_a || y_t) { p.kind = y_a ? 0 : 1; p.x_perm = order_into(xs, x_rows); }
+  else { p.kind = 0; p.x_perm = order_into(xs, x_rows); p.y_perm = order_into(ys, y_rows); }
+  const std::string z_lies = B + M + N;
+  if (os != z_lies) {
+    p.z_perm = order_into(z_lies, os);
+    for (char c : z_lies) p.z_sizes.push_back(extent[c - 'a']);
+  }
+  for (char c : os) p.out_sizes.push_back(extent[c - 'a']);
+  if (p.out_sizes.empty()) p.out_sizes = {1};   // full contraction
+  return p;
+}
+ContractionPlan contraction_plan(const std::string& expr, const std::vector<size_t>& x_sizes, const std::vector<size_t>& y_sizes) {
+  const SplitExpr e = split_contraction(expr);
+  return plan_contraction(e.xs, e.ys, e.os, x_sizes, y_sizes, true);
+}
+// z[os] = scale * sum x[xs] y[ys] + beta * z; the permuted copies live in the stream's scratch buffer
+static void run_contraction(Graph* g, int key, size_t elem, StreamContext ctx, const void* x, const std::vector<size_t>& xsz,
+                            const std::string& xs, const void* y, const std::vector<size_t>& ysz, const std::string& ys, double scale,
+                            void* z, const std::string& os, double beta) {
+  const ContractionPlan p = plan_contraction(xs, ys, os, xsz, ysz, true);
+  if (p.swap) { std::swap(x, y); }
+  const std::vector<size_t>& asz = p.swap ? ysz : xsz;
+  const std::vector<size_t>& bsz = p.swap ? xsz : ysz;
+  auto bytes_of = [&](const std::vector<size_t>& sz) { size_t v = elem; for (size_t e : sz) v *= e; return (v + 255) & ~size_t(255); };
+  const size_t xb = p.x_perm.empty() ? 0 : bytes_of(asz), yb = p.y_perm.empty() ? 0 : bytes_of(bsz),
+               zb = p.z_perm.empty() ? 0 : bytes_of(p.z_sizes);
+  unsigned char* tmp = (xb + yb + zb) != 0 ? static_cast<unsigned char*>(g->scratch(xb + yb + zb)) : nullptr;
+  if (xb != 0) { call_permutate(key, x, tmp, 0.0, asz, p.x_perm, ctx); x = tmp; }
+  if (yb != 0) { call_permutate(key, y, tmp + xb, 0.0, bsz, p.y_perm, ctx); y = tmp + xb; }
+  void* c = zb != 0 ? static_cast<void*>(tmp + xb + yb) : z;
+  gemm(key, p.kind, x, y, scale, c, zb != 0 ? 0.0 : beta, p.m, p.n, p.k, ctx, p.batch);
+  if (zb != 0) call_permutate(key, c, z, beta, p.z_sizes, p.z_perm, ctx);
+}
+// Z = X.Y over the summed indices: dX is the contraction of dZ with Y over the indices X lacks ("os,ys->xs"), dY that
+// of X with dZ ("xs,os->ys"); both accumulate
+static void contraction_rev(const std::vector<OpDatum>& a) {
+  Tensor x = a[0].tensor, y = a[1].tensor, z = a[4].tensor;
+  const SplitExpr e = split_contraction(a[3].expr);
+  enable_gradient(x); enable_gradient(y);
+  const std::vector<size_t> zsz = e.os.empty() ? std::vector<size_t>{} : z.sizes();
+  const int key = dkey(z);
+  const size_t elem = dtype_size(z.dtype());
+  run_contraction(z.ptr, key, elem, z.context(), z.grad_ptr(), zsz, e.os, y.data_ptr(), y.sizes(), e.ys, a[2].scalar, x.grad_ptr(), e.xs, 1.0);
+  run_contraction(z.ptr, key, elem, z.context(), x.data_ptr(), x.sizes(), e.xs, z.grad_ptr(), zsz, e.os, a[2].scalar, y.grad_ptr(), e.ys, 1.0);
+}
+// the expressions the reference spells out (inner_product.zig:116-122) and the batched forms keep their direct path
+static bool named_contraction(const std::string& e) {
+  static const char* const forms[] = {"ij,jk->ik", "ij,kj->ik", "ji,jk->ik", "i,ij->j", "ij,j->i"};
+  for (const char* f : forms) if (e == f) return true;
+  if (e.size() == 12 && e[3] == ',' && e[7] == '-' && e[8] == '>' && e[0] == e[4] && e[0] == e[9] && e.find(e[0], 1) == 4) {
+    const std::string inner = e.substr(1, 2) + "," + e.substr(5, 2) + "->" + e.substr(10, 2);
+    for (int i = 0; i < 3; ++i) if (inner == forms[i]) return true;
+  }
+  return false;
+}
 static void inner_product_rev(const std::vector<OpDatum>& a) {
   Tensor x = a[0].tensor, y = a[1].tensor, z = a[4].tensor;
   const double scale = a[2].scalar;
@@ -760,6 +873,16 @@ static void inner_product_rev(const std::vector<OpDatum>& a) {
 Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string& expr) {
   if (x.dtype() != y.dtype()) panic("inner_product: dtypes differ");
   Graph* g = x.ptr;
+  if (!named_contraction(expr)) {
+    const SplitExpr e = split_contraction(expr);
+    const ContractionPlan p = plan_contraction(e.xs, e.ys, e.os, x.sizes(), y.sizes(), true);
+    Tensor z = g->tensor({Class::hid, x.dtype(), p.out_sizes});
+    run_contraction(g, dkey(z), dtype_size(z.dtype()), z.context(), x.data_ptr(), x.sizes(), e.xs, y.data_ptr(), y.sizes(), e.ys, scale,
+                    z.data_ptr(), e.os, 0.0);
+    if (g->mode == Mode::train)
+      attach_op(contraction_rev, z, {OpDatum::of(x), OpDatum::of(y), OpDatum::of(scale), OpDatum::of(expr), OpDatum::of(z)});
+    return z;
+  }
   std::vector<size_t> out_sizes;
   const Contraction c = parse_contraction(x, y, expr, out_sizes);
   Tensor z = g->tensor({Class::hid, x.dtype(), out_sizes});

@@ -165,6 +165,20 @@ Tensor inner_product(Tensor x, Tensor y, const std::string& expr);      // "ij,j
                                                                         // batched "bij,bjk->bik" (and the kj / ji forms), "_ij,_jk->_ik" = optional batch
 Tensor inner_product_scaled(Tensor x, Tensor y, double scale, const std::string& expr);
 inline Tensor innerProduct(Tensor x, Tensor y, const std::string& e) { return inner_product(x, y, e); }
+// Any other expression is a rank-N contraction (NOTES.md:3-5; grammar expression_parsing.zig:258-317): operands of rank
+// <= 6 with distinct lower-case indices in any order, e.g. "abc,cd->abd", "ikj,lk->lij", "bhqd,bhkd->bhqk".  An index of
+// both operands that is missing on the right is summed; one of both operands and the output is a batch index; every
+// other index must be in the output.  It runs as one (batched) GEMM, with general permutations only around the
+// operands whose index order no kernel takes directly; its reverse is two such contractions.
+struct ContractionPlan {
+  bool swap = false;                       // the GEMM takes the operands in the opposite order; x_* below then describe the caller's second operand
+  int kind = 0;                            // 0 = "ij,jk->ik", 1 = "ij,kj->ik", 2 = "ji,jk->ik" after the permutations below
+  size_t batch = 0, m = 1, n = 1, k = 1;   // batch 0 = the rank-2 kernel; C[m,k] = A[m,n] B[n,k] in the reference's letters
+  std::vector<size_t> x_perm, y_perm;      // empty = the operand is used where it lies; else perm[i] = new position of its i-th index
+  std::vector<size_t> z_sizes, z_perm;     // z_perm empty = the GEMM writes the output itself; else its [batch.., m.., k..] result (z_sizes) is permuted into the output
+  std::vector<size_t> out_sizes;
+};
+ContractionPlan contraction_plan(const std::string& expr, const std::vector<size_t>& x_sizes, const std::vector<size_t>& y_sizes);
 Tensor linear(Tensor x, Tensor A, Tensor b, const std::string& expr);   // "ij,jk->ik", "i,ij->j"; "ij,j->i" = matrix first: linear(A, x, b, ...)
 Tensor permutate(Tensor x, const std::string& expr);                    // any permutation up to rank 6: "ij->ji", "ijk->kij", ...
 std::vector<size_t> permutation_of(const std::string& expr);            // perm[i] = position of the i-th left index on the right

@@ -276,6 +276,64 @@ static void scenario_rank3(mp::Stream stream) {
   G->deinit();
 }
 
+// Rank-N contractions (NOTES.md:3-5; grammar expression_parsing.zig:258-317): forward and both gradients against
+// the contraction summed straight from its expression
+static std::vector<float> contraction_direct(const std::string& xs, const std::string& ys, const std::string& os,
+                                             const std::vector<float>& x, const std::vector<float>& y, const size_t* extent) {
+  std::string letters;
+  for (char c : xs + ys + os) if (letters.find(c) == std::string::npos) letters += c;
+  std::vector<size_t> idx(letters.size(), 0);
+  auto offset = [&](const std::string& s) {
+    size_t off = 0;
+    for (char c : s) off = off * extent[c - 'a'] + idx[letters.find(c)];
+    return off;
+  };
+  size_t zlen = 1;
+  for (char c : os) zlen *= extent[c - 'a'];
+  std::vector<double> z(zlen, 0.0);
+  for (;;) {
+    z[offset(os)] += static_cast<double>(x[offset(xs)]) * y[offset(ys)];
+    size_t i = letters.size();
+    while (i-- > 0) { if (++idx[i] < extent[letters[i] - 'a']) break; idx[i] = 0; }
+    if (i == static_cast<size_t>(-1)) break;
+  }
+  return std::vector<float>(z.begin(), z.end());
+}
+static void scenario_rank_n_contractions(mp::Stream stream) {
+  size_t extent[26] = {};
+  extent['a' - 'a'] = 3; extent['b' - 'a'] = 8; extent['c' - 'a'] = 32; extent['d' - 'a'] = 24; extent['h' - 'a'] = 2;
+  extent['i' - 'a'] = 8; extent['j' - 'a'] = 16; extent['k' - 'a'] = 12; extent['l' - 'a'] = 20; extent['q' - 'a'] = 16;
+  const char* cases[][3] = {{"abc", "cd", "abd"},  {"ikj", "lk", "lij"},      {"bhqd", "bhkd", "bhqk"}, {"abc", "cd", "adb"},
+                            {"ij", "jk", "ki"},    {"acb", "dc", "dab"},      {"bqhd", "bkhd", "bhqk"}, {"i", "j", "ij"},
+                            {"ab", "ab", ""}};
+  unsigned seed = 300;
+  for (const auto& c : cases) {
+    const std::string xs = c[0], ys = c[1], os = c[2], expr = xs + "," + ys + "->" + os;
+    mp::Graph* G = mp::Graph::init({stream, mp::Mode::train});
+    std::vector<size_t> xsz, ysz, osz;
+    for (char ch : xs) xsz.push_back(extent[ch - 'a']);
+    for (char ch : ys) ysz.push_back(extent[ch - 'a']);
+    for (char ch : os) osz.push_back(extent[ch - 'a']);
+    if (osz.empty()) osz = {1};
+    mp::Tensor x = G->tensor({mp::Class::wgt, mp::Dtype::r32, xsz});
+    mp::Tensor y = G->tensor({mp::Class::wgt, mp::Dtype::r32, ysz});
+    mp::Tensor w = G->tensor({mp::Class::inp, mp::Dtype::r32, osz});
+    const std::vector<float> hx = normal(x.len(), seed++, 1.f), hy = normal(y.len(), seed++, 0.5f), hw = normal(w.len(), seed++, 1.f);
+    upload(x, hx); upload(y, hy); upload(w, hw);
+    mp::Tensor z = mp::ops::inner_product(x, y, expr);
+    CHECK(z.sizes() == osz);
+    const double ez = rel_err(z.native(), contraction_direct(xs, ys, os, hx, hy, extent));
+    mp::Tensor loss = mp::ops::hadamard(z, w);
+    loss.reverse(mp::ReverseCleanup::keep);
+    const double ex = rel_err(x.native_grad(), contraction_direct(os, ys, xs, hw, hy, extent));
+    const double ey = rel_err(y.native_grad(), contraction_direct(xs, os, ys, hx, hw, extent));
+    if (!(ez <= 1e-4 && ex <= 1e-4 && ey <= 1e-4)) std::printf("contraction %s: errors %.3g %.3g %.3g\n", expr.c_str(), ez, ex, ey);
+    CHECK(ez <= 1e-4); CHECK(ex <= 1e-4); CHECK(ey <= 1e-4);
+    mp::device::check();
+    G->deinit();
+  }
+}
+
 // Momentum steps (optimizer.zig:182-275) and weight files (graph.zig:633-703): train two steps, save, perturb,
 // load, and compare with the oracle's two steps
 static void scenario_momentum_and_weight_files(mp::Stream stream, const char* dir) {
@@ -420,6 +478,7 @@ int main(int argc, char** argv) {
   scenario_rank3(s);
   scenario_derive(s);
   scenario_rank3_reduce(s);
+  scenario_rank_n_contractions(s);
   scenario_momentum_and_weight_files(s, argc > 2 ? argv[2] : "/tmp");
   mp::stream::deinit(s);
   std::printf(failures == 0 ? "ALL SCENARIOS PASSED\n" : "%d CHECKS FAILED\n", failures);

@@ -26,6 +26,17 @@ def test_host_layer_and_scenarios_compile(mp, orc, tmp_path):
     assert build_scenarios(tmp_path, orc).exists()
 
 
+def test_rank_n_contraction_plans_on_the_cpu(mp, orc, tmp_path):
+    """Every plan of the rank-N contraction planner, carried out with plain loops, equals the contraction summed
+    from its expression (forward and both gradient expressions); no device call."""
+    exe = tmp_path / "contraction_plans"
+    subprocess.run(["g++", "-O2", "-std=c++17", "-Wall", "-o", str(exe), str(ROOT / "tests" / "host" / "contraction_plans.cpp"),
+                    f"-L{LIB}", "-lmp_host", "-lmp_kernels", f"-Wl,-rpath,{LIB}"], check=True, capture_output=True)
+    res = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert "ALL PLANS PASSED" in res.stdout
+
+
 @pytest.mark.gpu
 def test_reference_examples_and_feed_forward_block(mp, orc, tmp_path):
     exe = build_scenarios(tmp_path, orc)
