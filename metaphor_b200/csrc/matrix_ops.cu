@@ -32,12 +32,20 @@ __global__ void __launch_bounds__(TP_THREADS) transpose_kernel(const T* __restri
   const int tid = threadIdx.x;
 
   if constexpr (VL) {
-    for (int v = tid; v < TP_TILE * VPR; v += TP_THREADS) {
-      const int tr = v / VPR, tc = (v % VPR) * PN;
-      if (r0 + tr < row && c0 + tc < col) {
-        const Pack<T> p = ld_pack_stream(src, ((r0 + tr) * col + c0 + tc) / PN);
+    // two stages: every load of the thread is in flight before the first value is used
+    constexpr int TRIPS = TP_TILE * VPR / TP_THREADS;
+    Pack<T> p[TRIPS];
 #pragma unroll
-        for (int e = 0; e < PN; ++e) tile[tc + e][tr] = p.v[e];
+    for (int t = 0; t < TRIPS; ++t) {
+      const int v = tid + t * TP_THREADS, tr = v / VPR, tc = (v % VPR) * PN;
+      if (r0 + tr < row && c0 + tc < col) p[t] = ld_pack_stream(src, ((r0 + tr) * col + c0 + tc) / PN);
+    }
+#pragma unroll
+    for (int t = 0; t < TRIPS; ++t) {
+      const int v = tid + t * TP_THREADS, tr = v / VPR, tc = (v % VPR) * PN;
+      if (r0 + tr < row && c0 + tc < col) {
+#pragma unroll
+        for (int e = 0; e < PN; ++e) tile[tc + e][tr] = p[t].v[e];
       }
     }
   } else {

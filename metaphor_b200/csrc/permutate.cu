@@ -134,6 +134,32 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_rows_kernel(const T* __r
 struct PermSplit { unsigned d_lo, s_lo; unsigned long long s_pitch_hi, d_pitch_hi; };
 template <typename T> struct PermTile { static constexpr int value = sizeof(T) == 2 ? 128 : 64; };
 
+// blockIdx.x -> origin of the CTA's tile and the offsets of its batch indices.  The block index has 32 bits, so
+// the divisions have too (a 64-bit division is ~4 times the instructions, and every warp of the CTA decodes).
+__device__ __forceinline__ void decode_tile(const PermDims& batch, unsigned tiles_s, unsigned tiles_d, int tile, size_t& s0, size_t& d0,
+                                            size_t& sbase, size_t& dbase) {
+  unsigned rem = blockIdx.x;
+  unsigned q = rem / tiles_s;
+  s0 = static_cast<size_t>(rem - q * tiles_s) * tile;
+  rem = q;
+  q = rem / tiles_d;
+  d0 = static_cast<size_t>(rem - q * tiles_d) * tile;
+  rem = q;
+  sbase = 0;
+  dbase = 0;
+#pragma unroll
+  for (int k = PERM_DIMS - 1; k >= 0; --k) {
+    if (k < batch.rank) {
+      const unsigned extent = batch.size[k] > 0xffffffffull ? 0xffffffffu : static_cast<unsigned>(batch.size[k]);   // > rem either way
+      q = rem / extent;
+      const unsigned c = rem - q * extent;
+      rem = q;
+      sbase += static_cast<size_t>(c) * batch.sstride[k];
+      dbase += static_cast<size_t>(c) * batch.dstride[k];
+    }
+  }
+}
+
 template <typename T, bool VL, bool VS, bool BLEND>
 __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __restrict__ src, T* dst, typename Acc<T>::type alpha,
                                                                      const PermDims batch, size_t n_s, size_t n_d, size_t s_pitch,
@@ -143,21 +169,8 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
   constexpr int TILE = PermTile<T>::value;
   constexpr int VPR = TILE / PN;
   __shared__ T tile[TILE][TILE + 1];   // tile[s][d]
-  size_t rem = blockIdx.x;
-  const size_t s0 = (rem % tiles_s) * TILE;
-  rem /= tiles_s;
-  const size_t d0 = (rem % tiles_d) * TILE;
-  rem /= tiles_d;
-  size_t sbase = 0, dbase = 0;
-#pragma unroll
-  for (int k = PERM_DIMS - 1; k >= 0; --k) {
-    if (k < batch.rank) {
-      const size_t c = rem % batch.size[k];
-      rem /= batch.size[k];
-      sbase += c * batch.sstride[k];
-      dbase += c * batch.dstride[k];
-    }
-  }
+  size_t s0, d0, sbase, dbase;
+  decode_tile(batch, tiles_s, tiles_d, TILE, s0, d0, sbase, dbase);
   const int tid = threadIdx.x;
   auto src_row = [&](size_t id) -> size_t {   // offset of source row iD (split extents stay below 2^31)
     if (sp.d_lo == 0) return id * s_pitch;
@@ -170,13 +183,20 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
     return static_cast<size_t>(static_cast<unsigned>(is) - hi * sp.s_lo) * d_pitch + hi * sp.d_pitch_hi;
   };
   if constexpr (VL) {
+    // two stages: every load of the thread is in flight before the first value is used
+    constexpr int TRIPS = TILE * VPR / PERM_THREADS;
+    Pack<T> p[TRIPS];
 #pragma unroll
-    for (int v = tid; v < TILE * VPR; v += PERM_THREADS) {
-      const int td = v / VPR, ts = (v % VPR) * PN;
+    for (int t = 0; t < TRIPS; ++t) {
+      const int v = tid + t * PERM_THREADS, td = v / VPR, ts = (v % VPR) * PN;
+      if (d0 + td < n_d && s0 + ts < n_s) p[t] = ld_pack_stream(src, (sbase + src_row(d0 + td) + s0 + ts) / PN);
+    }
+#pragma unroll
+    for (int t = 0; t < TRIPS; ++t) {
+      const int v = tid + t * PERM_THREADS, td = v / VPR, ts = (v % VPR) * PN;
       if (d0 + td < n_d && s0 + ts < n_s) {
-        const Pack<T> p = ld_pack_stream(src, (sbase + src_row(d0 + td) + s0 + ts) / PN);
 #pragma unroll
-        for (int e = 0; e < PN; ++e) tile[ts + e][td] = p.v[e];
+        for (int e = 0; e < PN; ++e) tile[ts + e][td] = p[t].v[e];
       }
     }
   } else {
@@ -218,29 +238,18 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
 
 // r16 tiles with 16-byte accesses on both sides: two neighbouring output-innermost rows (d, d + 1) travel through
 // shared memory as one 32-bit word per source column, which halves the shared-memory instructions of the
-// 2-byte version and removes its sub-word bank conflicts (rows of TILE / 2 + 1 words: conflict-free both ways).
+// 2-byte version and removes its sub-word bank conflicts.  Rows of TILE / 2 words with the 8-word column group
+// XOR-ed by bits 3-4 of the row: the 32 words of a warp's store (4 rows 8 apart x 8 columns) fall into 32 banks, and
+// the 16-byte chunks stay whole and aligned, so the second pass reads them with one 128-bit load each.
 template <bool BLEND>
-__global__ void __launch_bounds__(PERM_THREADS) permute_tiles_h2_kernel(const __half* __restrict__ src, __half* dst, float alpha,
+__global__ void __launch_bounds__(PERM_THREADS, 4) permute_tiles_h2_kernel(const __half* __restrict__ src, __half* dst, float alpha,
                                                                         const PermDims batch, size_t n_s, size_t n_d, size_t s_pitch,
                                                                         size_t d_pitch, unsigned tiles_s, unsigned tiles_d,
                                                                         const PermSplit sp) {
   constexpr int TILE = 128, PN = 8, VPR = TILE / PN;
-  __shared__ uint32_t tile[TILE][TILE / 2 + 1];   // tile[s][d / 2] = (value at d, value at d + 1)
-  size_t rem = blockIdx.x;
-  const size_t s0 = (rem % tiles_s) * TILE;
-  rem /= tiles_s;
-  const size_t d0 = (rem % tiles_d) * TILE;
-  rem /= tiles_d;
-  size_t sbase = 0, dbase = 0;
-#pragma unroll
-  for (int k = PERM_DIMS - 1; k >= 0; --k) {
-    if (k < batch.rank) {
-      const size_t c = rem % batch.size[k];
-      rem /= batch.size[k];
-      sbase += c * batch.sstride[k];
-      dbase += c * batch.dstride[k];
-    }
-  }
+  __shared__ __align__(16) uint32_t tile[TILE][TILE / 2];   // tile[s][(d / 2) ^ swz(s)] = (value at d, value at d + 1)
+  size_t s0, d0, sbase, dbase;
+  decode_tile(batch, tiles_s, tiles_d, TILE, s0, d0, sbase, dbase);
   auto src_row = [&](size_t id) -> size_t {
     if (sp.d_lo == 0) return id * s_pitch;
     const unsigned hi = static_cast<unsigned>(id) / sp.d_lo;
@@ -252,18 +261,32 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_h2_kernel(const __
     return static_cast<size_t>(static_cast<unsigned>(is) - hi * sp.s_lo) * d_pitch + hi * sp.d_pitch_hi;
   };
   const int tid = threadIdx.x;
+  // a warp covers 8 row pairs x 4 packs: 64 contiguous bytes per source row (whole sectors).  Two stages: all 8
+  // loads of a thread are in flight before the first value is used (written as one loop, each trip waited for its
+  // own two loads)
+  constexpr int TRIPS = (TILE / 2) * VPR / PERM_THREADS;   // 4
+  uint4 lo[TRIPS], hi[TRIPS];
 #pragma unroll
-  for (int v = tid; v < (TILE / 2) * VPR; v += PERM_THREADS) {   // 4 trips: all 8 loads of a thread are issued up front
-    // a warp covers 8 row pairs x 4 packs: 64 contiguous bytes per source row (whole sectors) and 32 distinct banks
-    // per shared-memory store (bank = 8 * pack + pair with rows of 65 words)
-    const int g = v >> 5, l = v & 31;
+  for (int t = 0; t < TRIPS; ++t) {
+    const int v = tid + t * PERM_THREADS, g = v >> 5, l = v & 31;
     const int td = ((g >> 2) * 8 + (l >> 2)) * 2, ts = ((g & 3) * 4 + (l & 3)) * PN;
     if (d0 + td < n_d && s0 + ts < n_s) {   // n_d and n_s are multiples of 8: the pair and the pack are whole
-      union { uint4 u; unsigned short h[8]; } a, b;
-      a.u = *reinterpret_cast<const uint4*>(src + sbase + src_row(d0 + td) + s0 + ts);
-      b.u = *reinterpret_cast<const uint4*>(src + sbase + src_row(d0 + td + 1) + s0 + ts);
+      lo[t] = __ldcs(reinterpret_cast<const uint4*>(src + sbase + src_row(d0 + td) + s0 + ts));
+      hi[t] = __ldcs(reinterpret_cast<const uint4*>(src + sbase + src_row(d0 + td + 1) + s0 + ts));
+    }
+  }
 #pragma unroll
-      for (int e = 0; e < PN; ++e) tile[ts + e][td >> 1] = static_cast<uint32_t>(a.h[e]) | (static_cast<uint32_t>(b.h[e]) << 16);
+  for (int t = 0; t < TRIPS; ++t) {
+    const int v = tid + t * PERM_THREADS, g = v >> 5, l = v & 31;
+    const int td = ((g >> 2) * 8 + (l >> 2)) * 2, ts = ((g & 3) * 4 + (l & 3)) * PN;
+    if (d0 + td < n_d && s0 + ts < n_s) {
+      const uint32_t a[4] = {lo[t].x, lo[t].y, lo[t].z, lo[t].w}, b[4] = {hi[t].x, hi[t].y, hi[t].z, hi[t].w};
+      const int col = (td >> 1) ^ (((ts >> 3) & 3) << 3);   // rows ts .. ts + 7 share bits 3-4
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {   // (a.lo, b.lo) and (a.hi, b.hi) of each word pair: one byte permute each
+        tile[ts + 2 * e][col] = __byte_perm(a[e], b[e], 0x5410);
+        tile[ts + 2 * e + 1][col] = __byte_perm(a[e], b[e], 0x7632);
+      }
     }
   }
   __syncthreads();
@@ -273,8 +296,7 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_h2_kernel(const __
     if (s0 + ts < n_s && d0 + td < n_d) {
       __half* out = dst + dbase + dst_row(s0 + ts) + d0 + td;
       union { uint4 u; uint32_t w[4]; __half2 h2[4]; } p;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) p.w[e] = tile[ts][(td >> 1) + e];
+      p.u = *reinterpret_cast<const uint4*>(&tile[ts][(td >> 1) ^ (((ts >> 3) & 3) << 3)]);
       if constexpr (BLEND) {
         union { uint4 u; __half2 h2[4]; } old;
         old.u = *reinterpret_cast<const uint4*>(out);
