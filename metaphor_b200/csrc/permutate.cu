@@ -238,9 +238,9 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
 
 // r16 tiles with 16-byte accesses on both sides: two neighbouring output-innermost rows (d, d + 1) travel through
 // shared memory as one 32-bit word per source column, which halves the shared-memory instructions of the
-// 2-byte version and removes its sub-word bank conflicts.  Rows of TILE / 2 words with the 8-word column group
-// XOR-ed by bits 3-4 of the row: the 32 words of a warp's store (4 rows 8 apart x 8 columns) fall into 32 banks, and
-// the 16-byte chunks stay whole and aligned, so the second pass reads them with one 128-bit load each.
+// 2-byte version and removes its sub-word bank conflicts.  Rows of TILE / 2 words, the column XOR-ed with twice the
+// row's 8-row group (bits 1-4): the 32 words of a warp's store (16 row groups x 2 columns) fall into 32 banks, and a
+// 16-byte chunk stays whole and aligned (at most its halves swap), so the second pass reads it with one 128-bit load.
 template <bool BLEND>
 __global__ void __launch_bounds__(PERM_THREADS, 4) permute_tiles_h2_kernel(const __half* __restrict__ src, __half* dst, float alpha,
                                                                         const PermDims batch, size_t n_s, size_t n_d, size_t s_pitch,
@@ -261,15 +261,14 @@ __global__ void __launch_bounds__(PERM_THREADS, 4) permute_tiles_h2_kernel(const
     return static_cast<size_t>(static_cast<unsigned>(is) - hi * sp.s_lo) * d_pitch + hi * sp.d_pitch_hi;
   };
   const int tid = threadIdx.x;
-  // a warp covers 8 row pairs x 4 packs: 64 contiguous bytes per source row (whole sectors).  Two stages: all 8
-  // loads of a thread are in flight before the first value is used (written as one loop, each trip waited for its
-  // own two loads)
+  // a warp covers two row pairs x 16 packs: whole 256-byte source rows.  Two stages: all 8 loads of a thread are in
+  // flight before the first value is used (written as one loop, each trip waited for its own two loads)
   constexpr int TRIPS = (TILE / 2) * VPR / PERM_THREADS;   // 4
   uint4 lo[TRIPS], hi[TRIPS];
 #pragma unroll
   for (int t = 0; t < TRIPS; ++t) {
-    const int v = tid + t * PERM_THREADS, g = v >> 5, l = v & 31;
-    const int td = ((g >> 2) * 8 + (l >> 2)) * 2, ts = ((g & 3) * 4 + (l & 3)) * PN;
+    const int v = tid + t * PERM_THREADS;
+    const int td = (v >> 4) * 2, ts = (v & 15) * PN;
     if (d0 + td < n_d && s0 + ts < n_s) {   // n_d and n_s are multiples of 8: the pair and the pack are whole
       lo[t] = __ldcs(reinterpret_cast<const uint4*>(src + sbase + src_row(d0 + td) + s0 + ts));
       hi[t] = __ldcs(reinterpret_cast<const uint4*>(src + sbase + src_row(d0 + td + 1) + s0 + ts));
@@ -277,11 +276,11 @@ __global__ void __launch_bounds__(PERM_THREADS, 4) permute_tiles_h2_kernel(const
   }
 #pragma unroll
   for (int t = 0; t < TRIPS; ++t) {
-    const int v = tid + t * PERM_THREADS, g = v >> 5, l = v & 31;
-    const int td = ((g >> 2) * 8 + (l >> 2)) * 2, ts = ((g & 3) * 4 + (l & 3)) * PN;
+    const int v = tid + t * PERM_THREADS;
+    const int td = (v >> 4) * 2, ts = (v & 15) * PN;
     if (d0 + td < n_d && s0 + ts < n_s) {
       const uint32_t a[4] = {lo[t].x, lo[t].y, lo[t].z, lo[t].w}, b[4] = {hi[t].x, hi[t].y, hi[t].z, hi[t].w};
-      const int col = (td >> 1) ^ (((ts >> 3) & 3) << 3);   // rows ts .. ts + 7 share bits 3-4
+      const int col = (td >> 1) ^ (((ts >> 3) & 15) << 1);   // rows ts .. ts + 7 share these bits
 #pragma unroll
       for (int e = 0; e < 4; ++e) {   // (a.lo, b.lo) and (a.hi, b.hi) of each word pair: one byte permute each
         tile[ts + 2 * e][col] = __byte_perm(a[e], b[e], 0x5410);
@@ -296,7 +295,9 @@ __global__ void __launch_bounds__(PERM_THREADS, 4) permute_tiles_h2_kernel(const
     if (s0 + ts < n_s && d0 + td < n_d) {
       __half* out = dst + dbase + dst_row(s0 + ts) + d0 + td;
       union { uint4 u; uint32_t w[4]; __half2 h2[4]; } p;
-      p.u = *reinterpret_cast<const uint4*>(&tile[ts][(td >> 1) ^ (((ts >> 3) & 3) << 3)]);
+      const int key = ((ts >> 3) & 15) << 1;             // bits 2-4 move the 16-byte chunk, bit 1 swaps its halves
+      const uint4 raw = *reinterpret_cast<const uint4*>(&tile[ts][((td >> 1) ^ key) & ~3]);
+      p.u = (key & 2) ? make_uint4(raw.z, raw.w, raw.x, raw.y) : raw;
       if constexpr (BLEND) {
         union { uint4 u; __half2 h2[4]; } old;
         old.u = *reinterpret_cast<const uint4*>(out);
