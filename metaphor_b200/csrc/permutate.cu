@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
 // row's 8-row group (bits 1-4): the 32 words of a warp's store (16 row groups x 2 columns) fall into 32 banks, and a
 // 16-byte chunk stays whole and aligned (at most its halves swap), so the second pass reads it with one 128-bit load.
 template <bool BLEND>
-__global__ void __launch_bounds__(PERM_THREADS, 4) permute_tiles_h2_kernel(const __half* __restrict__ src, __half* dst, float alpha,
+__global__ void __launch_bounds__(PERM_THREADS, 5) permute_tiles_h2_kernel(const __half* __restrict__ src, __half* dst, float alpha,
                                                                         const PermDims batch, size_t n_s, size_t n_d, size_t s_pitch,
                                                                         size_t d_pitch, unsigned tiles_s, unsigned tiles_d,
                                                                         const PermSplit sp) {
