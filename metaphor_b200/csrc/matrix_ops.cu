@@ -32,20 +32,25 @@ __global__ void __launch_bounds__(TP_THREADS) transpose_kernel(const T* __restri
   const int tid = threadIdx.x;
 
   if constexpr (VL) {
-    // two stages: every load of the thread is in flight before the first value is used
+    // two stages: the loads of a group of trips are in flight before the first value is used (r16 / r32: all of the
+    // thread's loads; r64: groups of 4, because holding all 8 costs a CTA per SM and measured 11 - 15 % slower)
     constexpr int TRIPS = TP_TILE * VPR / TP_THREADS;
-    Pack<T> p[TRIPS];
+    constexpr int GROUP = sizeof(T) == 8 ? 2 : TRIPS;
 #pragma unroll
-    for (int t = 0; t < TRIPS; ++t) {
-      const int v = tid + t * TP_THREADS, tr = v / VPR, tc = (v % VPR) * PN;
-      if (r0 + tr < row && c0 + tc < col) p[t] = ld_pack_stream(src, ((r0 + tr) * col + c0 + tc) / PN);
-    }
+    for (int t0 = 0; t0 < TRIPS; t0 += GROUP) {
+      Pack<T> p[GROUP];
 #pragma unroll
-    for (int t = 0; t < TRIPS; ++t) {
-      const int v = tid + t * TP_THREADS, tr = v / VPR, tc = (v % VPR) * PN;
-      if (r0 + tr < row && c0 + tc < col) {
+      for (int t = 0; t < GROUP; ++t) {
+        const int v = tid + (t0 + t) * TP_THREADS, tr = v / VPR, tc = (v % VPR) * PN;
+        if (r0 + tr < row && c0 + tc < col) p[t] = ld_pack_stream(src, ((r0 + tr) * col + c0 + tc) / PN);
+      }
 #pragma unroll
-        for (int e = 0; e < PN; ++e) tile[tc + e][tr] = p[t].v[e];
+      for (int t = 0; t < GROUP; ++t) {
+        const int v = tid + (t0 + t) * TP_THREADS, tr = v / VPR, tc = (v % VPR) * PN;
+        if (r0 + tr < row && c0 + tc < col) {
+#pragma unroll
+          for (int e = 0; e < PN; ++e) tile[tc + e][tr] = p[t].v[e];
+        }
       }
     }
   } else {

@@ -183,20 +183,25 @@ __global__ void __launch_bounds__(PERM_THREADS) permute_tiles_kernel(const T* __
     return static_cast<size_t>(static_cast<unsigned>(is) - hi * sp.s_lo) * d_pitch + hi * sp.d_pitch_hi;
   };
   if constexpr (VL) {
-    // two stages: every load of the thread is in flight before the first value is used
+    // two stages: the loads of a group of trips are in flight before the first value is used (r16 / r32: all of the
+    // thread's loads; r64: groups of 4, because holding all 8 costs a CTA per SM and measured 11 - 15 % slower)
     constexpr int TRIPS = TILE * VPR / PERM_THREADS;
-    Pack<T> p[TRIPS];
+    constexpr int GROUP = sizeof(T) == 8 ? 2 : TRIPS;
 #pragma unroll
-    for (int t = 0; t < TRIPS; ++t) {
-      const int v = tid + t * PERM_THREADS, td = v / VPR, ts = (v % VPR) * PN;
-      if (d0 + td < n_d && s0 + ts < n_s) p[t] = ld_pack_stream(src, (sbase + src_row(d0 + td) + s0 + ts) / PN);
-    }
+    for (int t0 = 0; t0 < TRIPS; t0 += GROUP) {
+      Pack<T> p[GROUP];
 #pragma unroll
-    for (int t = 0; t < TRIPS; ++t) {
-      const int v = tid + t * PERM_THREADS, td = v / VPR, ts = (v % VPR) * PN;
-      if (d0 + td < n_d && s0 + ts < n_s) {
+      for (int t = 0; t < GROUP; ++t) {
+        const int v = tid + (t0 + t) * PERM_THREADS, td = v / VPR, ts = (v % VPR) * PN;
+        if (d0 + td < n_d && s0 + ts < n_s) p[t] = ld_pack_stream(src, (sbase + src_row(d0 + td) + s0 + ts) / PN);
+      }
 #pragma unroll
-        for (int e = 0; e < PN; ++e) tile[ts + e][td] = p[t].v[e];
+      for (int t = 0; t < GROUP; ++t) {
+        const int v = tid + (t0 + t) * PERM_THREADS, td = v / VPR, ts = (v % VPR) * PN;
+        if (d0 + td < n_d && s0 + ts < n_s) {
+#pragma unroll
+          for (int e = 0; e < PN; ++e) tile[ts + e][td] = p[t].v[e];
+        }
       }
     }
   } else {
