@@ -61,7 +61,7 @@ def strip_comments(src: str) -> str:
 def test_zig_sources_exist():
     names = {p.name for p in ZIG}
     for want in ("kernels.zig", "cimport.zig", "gradients.zig", "selu.zig", "linear.zig", "softmax.zig", "rmsnorm.zig", "ssd.zig",
-                 "permutate.zig", "optimizer.zig", "metaphor_additions.zig"):
+                 "permutate.zig", "contraction.zig", "optimizer.zig", "metaphor_additions.zig"):
         assert want in names, want
     assert (ROOT / "oracle" / "zig" / "oracle.zig").exists()
 

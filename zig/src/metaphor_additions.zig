@@ -11,6 +11,8 @@ pub const ops_additions = struct {
     pub const ssd_scan = @import("ops/ssd.zig").forward;
     pub const gated_norm = @import("ops/gated_norm.zig").forward;
     pub const permutate = @import("ops/permutate.zig").forward; // replaces the rank-2-only version
+    pub const contraction = @import("ops/contraction.zig").forward; // rank-N "abc,cd->abd" through one (batched) launch
+    pub const contractionScaled = @import("ops/contraction.zig").forward_scaled;
     // README spellings
     pub const innerProduct = @import("ops/inner_product.zig").forward;
     pub const innerProductScaled = @import("ops/inner_product.zig").forward_scaled;
